@@ -1,0 +1,603 @@
+// Bandwidth-bound training kernels for sm_100a: RMSNorm fwd/bwd (with fused residual add),
+// SwiGLU / GeGLU fwd/bwd, RoPE fwd/bwd over strided head views, RoPE table generation
+// (piecewise and YaRN scaling), cross-entropy fwd/bwd, fused AdamW on fp32 masters writing bf16
+// weights, and sum-of-squares partials for gradient clipping.
+//
+// Each one replaces a chain of ATen pointwise/reduce launches in the reference
+// (model/norm.py:38-47, model/feed_forward.py:64-75, model/rope.py:98-170,
+//  model/transformer.py:451-458, optim/adamw.py:74-121, train/trainer.py:280-284).
+// All are single-pass over HBM with 16-byte vector accesses.
+#include "common.cuh"
+
+namespace {
+
+constexpr int NT = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = np::warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < (int)(blockDim.x >> 5)) ? red[l] : 0.f;
+  t = np::warp_sum(t);
+  __syncthreads();
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = np::warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < (int)(blockDim.x >> 5)) ? red[l] : -INFINITY;
+  t = np::warp_max(t);
+  __syncthreads();
+  return t;
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 a = np::unpack_bf16(u.x), b = np::unpack_bf16(u.y), c = np::unpack_bf16(u.z), d = np::unpack_bf16(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]),
+                                            np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// y = (x [+ res]) * rsqrt(mean((x+res)^2) + eps) * w ; optionally writes h = x + res.
+// cols must be a multiple of 8 and <= NT*8*MAXV.
+template <int MAXV>
+__global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                         const __nv_bfloat16* __restrict__ res,
+                                                         const float* __restrict__ w,
+                                                         __nv_bfloat16* __restrict__ y,
+                                                         __nv_bfloat16* __restrict__ h_out,
+                                                         float* __restrict__ rstd, int rows, int cols,
+                                                         float eps) {
+  __shared__ float red[32];
+  const int nvec = cols >> 3;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const __nv_bfloat16* xr = x + (size_t)r * cols;
+    float v[MAXV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        load8(xr + c * 8, v[i]);
+        if (res) {
+          float t[8];
+          load8(res + (size_t)r * cols + c * 8, t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] += t[j];
+        }
+        if (h_out) {
+          // round to bf16 first so the normalised value matches what later readers of h see
+          store8(h_out + (size_t)r * cols + c * 8, v[i]);
+          if (res) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16(v[i][j]));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+      }
+    }
+    ss = block_sum(ss, red);
+    const float rs = rsqrtf(ss / (float)cols + eps);
+    if (threadIdx.x == 0 && rstd) rstd[r] = rs;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        float o[8];
+        const float4 w0 = *reinterpret_cast<const float4*>(w + c * 8);
+        const float4 w1 = *reinterpret_cast<const float4*>(w + c * 8 + 4);
+        o[0] = v[i][0] * rs * w0.x; o[1] = v[i][1] * rs * w0.y; o[2] = v[i][2] * rs * w0.z; o[3] = v[i][3] * rs * w0.w;
+        o[4] = v[i][4] * rs * w1.x; o[5] = v[i][5] * rs * w1.y; o[6] = v[i][6] * rs * w1.z; o[7] = v[i][7] * rs * w1.w;
+        store8(y + (size_t)r * cols + c * 8, o);
+      }
+    }
+  }
+}
+
+// dx = rs * (w*dy - xhat * mean(w*dy*xhat)) [+ dres]; per-CTA partial dw into scratch[grid, cols].
+template <int MAXV>
+__global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                         const __nv_bfloat16* __restrict__ x,
+                                                         const float* __restrict__ w,
+                                                         const float* __restrict__ rstd,
+                                                         const __nv_bfloat16* __restrict__ dres,
+                                                         __nv_bfloat16* __restrict__ dx,
+                                                         float* __restrict__ dw_partial, int rows, int cols) {
+  __shared__ float red[32];
+  const int nvec = cols >> 3;
+  float dwacc[MAXV][8];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float rs = rstd[r];
+    float g[MAXV][8], xh[MAXV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        load8(dy + (size_t)r * cols + c * 8, g[i]);
+        load8(x + (size_t)r * cols + c * 8, xh[i]);
+        const float4 w0 = *reinterpret_cast<const float4*>(w + c * 8);
+        const float4 w1 = *reinterpret_cast<const float4*>(w + c * 8 + 4);
+        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] *= rs;
+          dwacc[i][j] += g[i][j] * xh[i][j];
+          g[i][j] *= ww[j];
+          dot += g[i][j] * xh[i][j];
+        }
+      }
+    }
+    dot = block_sum(dot, red) / (float)cols;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - xh[i][j] * dot);
+        if (dres) {
+          float t[8];
+          load8(dres + (size_t)r * cols + c * 8, t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += t[j];
+        }
+        store8(dx + (size_t)r * cols + c * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = threadIdx.x + i * NT;
+    if (c < nvec) {
+      float* dst = dw_partial + (size_t)blockIdx.x * cols + c * 8;
+      *reinterpret_cast<float4*>(dst) = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+    }
+  }
+}
+
+// out[c] (+)= sum_p partial[p, c]
+__global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int parts,
+                              int cols, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int p = 0; p < parts; ++p) s += partial[(size_t)p * cols + c];
+  out[c] = accumulate ? out[c] + s : s;
+}
+
+// ------------------------------------------------------------------ SwiGLU / GeGLU
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float k = 0.7978845608028654f;
+  return 0.5f * x * (1.f + tanhf(k * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+  const float k = 0.7978845608028654f;
+  const float u = k * (x + 0.044715f * x * x * x);
+  const float t = tanhf(u);
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k * (1.f + 3.f * 0.044715f * x * x);
+}
+
+// gu = [gate | up] rows of 2F; h = act(gate) * up
+__global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h,
+                               long long rows, int F, int act) {
+  const long long nvec = rows * (F >> 3);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / (F >> 3);
+    const int c = (int)(i - r * (F >> 3)) * 8;
+    float g[8], u[8], o[8];
+    load8(gu + r * 2 * F + c, g);
+    load8(gu + r * 2 * F + F + c, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = (act == 0 ? np::silu_f(g[j]) : gelu_tanh_f(g[j])) * u[j];
+    store8(h + r * F + c, o);
+  }
+}
+
+__global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dh,
+                               __nv_bfloat16* __restrict__ dgu, long long rows, int F, int act) {
+  const long long nvec = rows * (F >> 3);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / (F >> 3);
+    const int c = (int)(i - r * (F >> 3)) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gu + r * 2 * F + c, g);
+    load8(gu + r * 2 * F + F + c, u);
+    load8(dh + r * F + c, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float a, da;
+      if (act == 0) {
+        const float s = 1.f / (1.f + __expf(-g[j]));
+        a = g[j] * s;
+        da = s * (1.f + g[j] * (1.f - s));
+      } else {
+        a = gelu_tanh_f(g[j]);
+        da = gelu_tanh_grad(g[j]);
+      }
+      dg[j] = d[j] * u[j] * da;
+      du[j] = d[j] * a;
+    }
+    store8(dgu + r * 2 * F + c, dg);
+    store8(dgu + r * 2 * F + F + c, du);
+  }
+}
+
+// ------------------------------------------------------------------ RoPE
+// x: [T, H, hd] viewed with row stride ld (elements) and head stride hd; half-split rotation on
+// the first rot dims: out[i] = x[i]*cos - x[i+rot/2]*sin ; out[i+rot/2] = x[i+rot/2]*cos + x[i]*sin.
+// sign = -1 gives the inverse rotation (the backward pass). pos = pos_ids ? pos_ids[t] : t % S + off.
+__global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                            const int* __restrict__ pos_ids, long long T, int S, int pos_off, int H, int hd,
+                            int rot, long long ld_in, long long ld_out, float sign) {
+  const int half = rot >> 1;
+  const int vec_per_head = hd >> 3;
+  const long long total = T * H * vec_per_head;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(i % vec_per_head);
+    const long long th = i / vec_per_head;
+    const int hh = (int)(th % H);
+    const long long t = th / H;
+    const int d0 = v * 8;
+    const __nv_bfloat16* src = x + t * ld_in + (size_t)hh * hd;
+    __nv_bfloat16* dst = out + t * ld_out + (size_t)hh * hd;
+    float a[8];
+    load8(src + d0, a);
+    if (d0 < rot) {
+      const int pos = pos_ids ? pos_ids[t] : (int)(t % S) + pos_off;
+      const bool lo = d0 < half;
+      const int pd = lo ? d0 + half : d0 - half;
+      float b[8], o[8];
+      load8(src + pd, b);
+      const int f0 = lo ? d0 : d0 - half;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float c = cos_t[(size_t)pos * half + f0 + j];
+        const float s = sin_t[(size_t)pos * half + f0 + j] * sign;
+        o[j] = lo ? (a[j] * c - b[j] * s) : (a[j] * c + b[j] * s);
+      }
+      store8(dst + d0, o);
+    } else if (dst != src) {
+      store8(dst + d0, a);
+    }
+  }
+}
+
+// cos/sin tables [S, rot/2] in fp32.
+// scaling: 0 none; 1 piecewise (wavelen < orig/high_freq keeps, wavelen > orig/low_freq divides by
+// factor, the band between keeps: the reference's rule, model/rope.py:64-80); 2 YaRN (NTK-by-parts
+// linear ramp between beta_fast/beta_slow rotations, cos/sin multiplied by mscale).
+__global__ void rope_table_kernel(float* __restrict__ cos_t, float* __restrict__ sin_t, int S, int rot,
+                                  float base, int scaling, float factor, float orig_len, float low_f,
+                                  float high_f, float mscale) {
+  const int half = rot >> 1;
+  const long long total = (long long)S * half;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int f = (int)(i % half);
+    const int pos = (int)(i / half);
+    float inv = powf(base, -2.f * (float)f / (float)rot);
+    float ms = 1.f;
+    if (scaling == 1) {
+      const float wavelen = 6.283185307179586f / inv;
+      if (!(wavelen < orig_len / high_f) && wavelen > orig_len / low_f) inv = inv / factor;
+    } else if (scaling == 2) {
+      // low_f = beta_slow (default 1), high_f = beta_fast (default 32)
+      const float lnb = logf(base);
+      const float d_lo = (float)rot * logf(orig_len / (high_f * 6.283185307179586f)) / (2.f * lnb);
+      const float d_hi = (float)rot * logf(orig_len / (low_f * 6.283185307179586f)) / (2.f * lnb);
+      const float lo = fmaxf(floorf(d_lo), 0.f), hi = fminf(ceilf(d_hi), (float)(half - 1));
+      float ramp = ((float)f - lo) / fmaxf(hi - lo, 1e-3f);
+      ramp = fminf(fmaxf(ramp, 0.f), 1.f);
+      const float extrap = 1.f - ramp;  // 1 = keep original frequency
+      inv = (inv / factor) * (1.f - extrap) + inv * extrap;
+      ms = mscale;
+    }
+    const float ang = (float)pos * inv;
+    cos_t[i] = cosf(ang) * ms;
+    sin_t[i] = sinf(ang) * ms;
+  }
+}
+
+// ------------------------------------------------------------------ cross-entropy
+// Row-wise: lse[r] = logsumexp(logits[r]), loss[r] = lse - logits[r, label] (0 if label == ignore).
+__global__ void __launch_bounds__(NT) xent_fwd_kernel(const __nv_bfloat16* __restrict__ logits,
+                                                      const long long* __restrict__ labels,
+                                                      float* __restrict__ loss, float* __restrict__ lse,
+                                                      int rows, int V, long long ld, long long ignore) {
+  __shared__ float red[32];
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const __nv_bfloat16* lr = logits + (size_t)r * ld;
+    const int nvec = V >> 3;
+    float mx = -INFINITY;
+    for (int c = threadIdx.x; c < nvec; c += NT) {
+      float f[8];
+      load8(lr + c * 8, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[j]);
+    }
+    for (int c = nvec * 8 + threadIdx.x; c < V; c += NT) mx = fmaxf(mx, __bfloat162float(lr[c]));
+    mx = block_max(mx, red);
+    float se = 0.f;
+    for (int c = threadIdx.x; c < nvec; c += NT) {
+      float f[8];
+      load8(lr + c * 8, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) se += __expf(f[j] - mx);
+    }
+    for (int c = nvec * 8 + threadIdx.x; c < V; c += NT) se += __expf(__bfloat162float(lr[c]) - mx);
+    se = block_sum(se, red);
+    if (threadIdx.x == 0) {
+      const float l = mx + logf(se);
+      lse[r] = l;
+      const long long lab = labels[r];
+      loss[r] = (lab == ignore || lab < 0 || lab >= V) ? 0.f : l - __bfloat162float(lr[lab]);
+    }
+  }
+}
+
+// dlogits[r, c] = (exp(logits - lse) - [c == label]) * gscale[0] * inv_count[0]; ignored rows -> 0.
+__global__ void __launch_bounds__(NT) xent_bwd_kernel(const __nv_bfloat16* __restrict__ logits,
+                                                      const long long* __restrict__ labels,
+                                                      const float* __restrict__ lse,
+                                                      const float* __restrict__ gscale,
+                                                      const float* __restrict__ inv_count,
+                                                      __nv_bfloat16* __restrict__ dlogits, int rows, int V,
+                                                      long long ld, long long ignore) {
+  const float sc = gscale[0] * inv_count[0];
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const __nv_bfloat16* lr = logits + (size_t)r * ld;
+    __nv_bfloat16* dr = dlogits + (size_t)r * ld;
+    const long long lab = labels[r];
+    const bool ign = (lab == ignore || lab < 0 || lab >= V);
+    const float l = lse[r];
+    const int nvec = V >> 3;
+    for (int c = threadIdx.x; c < nvec; c += NT) {
+      float f[8], o[8];
+      load8(lr + c * 8, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float pr = __expf(f[j] - l);
+        o[j] = ign ? 0.f : (pr - ((long long)(c * 8 + j) == lab ? 1.f : 0.f)) * sc;
+      }
+      store8(dr + c * 8, o);
+    }
+    for (int c = nvec * 8 + threadIdx.x; c < V; c += NT) {
+      const float pr = __expf(__bfloat162float(lr[c]) - l);
+      dr[c] = __float2bfloat16(ign ? 0.f : (pr - ((long long)c == lab ? 1.f : 0.f)) * sc);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ AdamW + norms
+// Decoupled weight decay on fp32 masters; writes the bf16 compute copy in the same pass.
+// gscale (device scalar, may be null) multiplies the gradient (gradient clipping coefficient).
+__global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                             float* __restrict__ v, __nv_bfloat16* __restrict__ w16, long long n, float lr,
+                             float b1, float b2, float eps, float wd, float bc1, float bc2,
+                             const float* __restrict__ gscale) {
+  const float gs = gscale ? gscale[0] : 1.f;
+  const long long nvec = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 pp = reinterpret_cast<float4*>(p)[i];
+    const float4 gg = reinterpret_cast<const float4*>(g)[i];
+    float4 mm = reinterpret_cast<float4*>(m)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    float* P = &pp.x; const float* G = &gg.x; float* M = &mm.x; float* V = &vv.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gr = G[j] * gs;
+      M[j] = b1 * M[j] + (1.f - b1) * gr;
+      V[j] = b2 * V[j] + (1.f - b2) * gr * gr;
+      const float den = sqrtf(V[j] / bc2) + eps;
+      P[j] = P[j] * (1.f - lr * wd) - lr * (M[j] / bc1) / den;
+    }
+    reinterpret_cast<float4*>(p)[i] = pp;
+    reinterpret_cast<float4*>(m)[i] = mm;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    if (w16) reinterpret_cast<uint2*>(w16)[i] = make_uint2(np::pack_bf16(pp.x, pp.y), np::pack_bf16(pp.z, pp.w));
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    for (long long i = nvec * 4; i < n; ++i) {
+      const float gr = g[i] * gs;
+      m[i] = b1 * m[i] + (1.f - b1) * gr;
+      v[i] = b2 * v[i] + (1.f - b2) * gr * gr;
+      p[i] = p[i] * (1.f - lr * wd) - lr * (m[i] / bc1) / (sqrtf(v[i] / bc2) + eps);
+      if (w16) w16[i] = __float2bfloat16(p[i]);
+    }
+  }
+}
+
+// partial[b] = sum over this CTA's grid-stride slice of x^2 (fp32 input)
+__global__ void __launch_bounds__(NT) sumsq_kernel(const float* __restrict__ x, long long n,
+                                                   float* __restrict__ partial) {
+  __shared__ float red[32];
+  float s = 0.f;
+  const long long nvec = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 a = reinterpret_cast<const float4*>(x)[i];
+    s += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (long long i = nvec * 4; i < n; ++i) s += x[i] * x[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+
+// out[0] = min(1, max_norm / (sqrt(sum(partial) + extra_sq[0]) + 1e-6)); out[1] = the norm.
+__global__ void clip_coef_kernel(const float* __restrict__ partial, int parts, const float* __restrict__ extra_sq,
+                                 float max_norm, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < parts; i += blockDim.x) s += partial[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) {
+    if (extra_sq) s += extra_sq[0];
+    const float nrm = sqrtf(s);
+    out[1] = nrm;
+    out[0] = max_norm > 0.f ? fminf(1.f, max_norm / (nrm + 1e-6f)) : 1.f;
+  }
+}
+
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n) {
+  const long long nvec = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 a = reinterpret_cast<const float4*>(x)[i];
+    reinterpret_cast<uint2*>(y)[i] = make_uint2(np::pack_bf16(a.x, a.y), np::pack_bf16(a.z, a.w));
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (long long i = nvec * 4; i < n; ++i) y[i] = __float2bfloat16(x[i]);
+}
+
+inline int grid_for(long long work_items, int threads, int cap) {
+  long long g = (work_items + threads - 1) / threads;
+  if (g < 1) g = 1;
+  if (g > cap) g = cap;
+  return (int)g;
+}
+constexpr int GRID_CAP = 148 * 8;
+
+}  // namespace
+
+#define CHECK_LAUNCH() do { cudaError_t e_ = cudaGetLastError(); return e_ == cudaSuccess ? 0 : 500 + (int)e_; } while (0)
+
+NP_API int np_rmsnorm_fwd(const void* x, const void* res, const float* w, void* y, void* h_out, float* rstd,
+                          int rows, int cols, float eps, void* stream) {
+  if (cols % 8 || cols > NT * 8 * 4) return 1;
+  const int grid = rows < GRID_CAP ? rows : GRID_CAP;
+  if (grid <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (cols <= NT * 8)
+    rmsnorm_fwd_kernel<1><<<grid, NT, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, w,
+                                              (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, rows, cols, eps);
+  else if (cols <= NT * 16)
+    rmsnorm_fwd_kernel<2><<<grid, NT, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, w,
+                                              (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, rows, cols, eps);
+  else
+    rmsnorm_fwd_kernel<4><<<grid, NT, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, w,
+                                              (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, rows, cols, eps);
+  CHECK_LAUNCH();
+}
+
+// Number of partial rows np_rmsnorm_bwd writes into its scratch for a given row count.
+NP_API int np_rmsnorm_bwd_parts(int rows) {
+  const int cap = 148 * 2;
+  return rows < cap ? (rows > 0 ? rows : 1) : cap;
+}
+
+// scratch: fp32 [np_rmsnorm_bwd_parts(rows), cols]. dw (+)= column sums of dy * xhat.
+NP_API int np_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* dres,
+                          void* dx, float* dw, float* scratch, int rows, int cols, int accumulate_dw,
+                          void* stream) {
+  if (cols % 8 || cols > NT * 8 * 4) return 1;
+  if (rows <= 0) return 0;
+  const int grid = np_rmsnorm_bwd_parts(rows);
+  cudaStream_t s = (cudaStream_t)stream;
+#define RB(V) rmsnorm_bwd_kernel<V><<<grid, NT, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, \
+                                                       (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, rows, cols)
+  if (cols <= NT * 8) RB(1);
+  else if (cols <= NT * 16) RB(2);
+  else RB(4);
+#undef RB
+  colsum_kernel<<<(cols + 255) / 256, 256, 0, s>>>(scratch, dw, grid, cols, accumulate_dw);
+  CHECK_LAUNCH();
+}
+
+NP_API int np_glu_fwd(const void* gu, void* h, long long rows, int F, int act, void* stream) {
+  if (F % 8) return 1;
+  if (rows <= 0) return 0;
+  glu_fwd_kernel<<<grid_for(rows * (F / 8), 256, GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, rows, F, act);
+  CHECK_LAUNCH();
+}
+NP_API int np_glu_bwd(const void* gu, const void* dh, void* dgu, long long rows, int F, int act, void* stream) {
+  if (F % 8) return 1;
+  if (rows <= 0) return 0;
+  glu_bwd_kernel<<<grid_for(rows * (F / 8), 256, GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)gu, (const __nv_bfloat16*)dh, (__nv_bfloat16*)dgu, rows, F, act);
+  CHECK_LAUNCH();
+}
+
+NP_API int np_rope(const void* x, void* out, const float* cos_t, const float* sin_t, const int* pos_ids,
+                   long long T, int S, int pos_off, int H, int hd, int rot, long long ld_in, long long ld_out,
+                   float sign, void* stream) {
+  if (hd % 8 || rot % 16 || rot > hd || ld_in % 8 || ld_out % 8) return 1;
+  if (T <= 0) return 0;
+  rope_kernel<<<grid_for(T * H * (hd / 8), 256, GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (__nv_bfloat16*)out, cos_t, sin_t, pos_ids, T, S, pos_off, H, hd, rot, ld_in,
+      ld_out, sign);
+  CHECK_LAUNCH();
+}
+
+NP_API int np_rope_table(float* cos_t, float* sin_t, int S, int rot, float base, int scaling, float factor,
+                         float orig_len, float low_f, float high_f, float mscale, void* stream) {
+  if (S <= 0) return 0;
+  rope_table_kernel<<<grid_for((long long)S * (rot / 2), 256, GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
+      cos_t, sin_t, S, rot, base, scaling, factor, orig_len, low_f, high_f, mscale);
+  CHECK_LAUNCH();
+}
+
+NP_API int np_xent_fwd(const void* logits, const long long* labels, float* loss, float* lse, int rows, int V,
+                       long long ld, long long ignore, void* stream) {
+  if (ld % 8) return 1;
+  if (rows <= 0) return 0;
+  xent_fwd_kernel<<<rows < GRID_CAP ? rows : GRID_CAP, NT, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)logits, labels, loss, lse, rows, V, ld, ignore);
+  CHECK_LAUNCH();
+}
+NP_API int np_xent_bwd(const void* logits, const long long* labels, const float* lse, const float* gscale,
+                       const float* inv_count, void* dlogits, int rows, int V, long long ld, long long ignore,
+                       void* stream) {
+  if (ld % 8) return 1;
+  if (rows <= 0) return 0;
+  xent_bwd_kernel<<<rows < GRID_CAP ? rows : GRID_CAP, NT, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)logits, labels, lse, gscale, inv_count, (__nv_bfloat16*)dlogits, rows, V, ld, ignore);
+  CHECK_LAUNCH();
+}
+
+NP_API int np_adamw(float* p, const float* g, float* m, float* v, void* w16, long long n, float lr, float b1,
+                    float b2, float eps, float wd, int step, const float* gscale, void* stream) {
+  if (n <= 0) return 0;
+  const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  adamw_kernel<<<grid_for(n / 4 + 1, 256, GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
+      p, g, m, v, (__nv_bfloat16*)w16, n, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+  CHECK_LAUNCH();
+}
+
+NP_API int np_sumsq_parts() { return 148 * 4; }
+// partial: fp32 [np_sumsq_parts()]
+NP_API int np_sumsq(const float* x, long long n, float* partial, void* stream) {
+  sumsq_kernel<<<np_sumsq_parts(), NT, 0, (cudaStream_t)stream>>>(x, n, partial);
+  CHECK_LAUNCH();
+}
+NP_API int np_clip_coef(const float* partial, int parts, const float* extra_sq, float max_norm, float* out2,
+                        void* stream) {
+  clip_coef_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(partial, parts, extra_sq, max_norm, out2);
+  CHECK_LAUNCH();
+}
+NP_API int np_cast_f32_bf16(const float* x, void* y, long long n, void* stream) {
+  if (n <= 0) return 0;
+  cast_f32_to_bf16_kernel<<<grid_for(n / 4 + 1, 256, GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
+      x, (__nv_bfloat16*)y, n);
+  CHECK_LAUNCH();
+}

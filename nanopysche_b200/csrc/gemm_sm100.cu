@@ -1,0 +1,548 @@
+// bf16 GEMM family for sm_100a: persistent, warp-specialised, tcgen05.mma with the accumulator
+// in TMEM (double buffered), operands staged by TMA into 128-byte-swizzled shared memory.
+//
+// One kernel covers forward (A,B K-major), dgrad (B MN-major) and wgrad (A,B MN-major), the
+// ragged per-expert ("grouped") variants used by the MoE layers, a fused SwiGLU epilogue, and
+// the two hooks that fuse a collective into the GEMM: a per-M-block arrival-flag wait in front
+// of the loads (tokens pushed into this GPU's buffer by its peers) and an epilogue that stores
+// output rows through a per-row destination table into peer memory and signals the peers.
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2..5 = epilogue (TMEM -> registers -> global). All waits are bounded (common.cuh).
+//
+// Replaces the cuBLAS calls behind nn.Linear / torch.bmm in the reference
+// (model/attention.py:141-143,189; model/feed_forward.py:75; model/moe.py:1520-1538).
+#include "common.cuh"
+
+__device__ int g_np_status[8];
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 B = one swizzle row
+constexpr int KID_GEMM = 1;
+
+struct GemmParams {
+  void* C;            // output
+  void* C2;           // swiglu: optional [gate | up] pre-activation output, (M, 2*N_out)
+  int M, N, K;        // output rows / cols, contraction length
+  long long ldc, ldc2;
+  int a_mn, b_mn;     // 0: operand is K-major ([rows, K]); 1: MN-major ([K, rows])
+  int out_f32;        // 0: bf16 output, 1: fp32 output
+  int accumulate;     // C += A*B (read-modify-write)
+  int epilogue;       // 0 plain, 1 swiglu (B tile = 128 gate rows + 128 up rows)
+  int mode;           // 0 dense, 1 grouped rows (per-M-block B offset), 2 grouped K (wgrad)
+  float alpha;
+  const int* mblk_group;      // [m blocks] group of each 128-row block (mode 1) or nullptr
+  const int* mblk_rows;       // [m blocks] valid rows of each block, 0 = skip; nullptr = all
+  long long group_stride_b;   // rows of B per group (mode 1)
+  int num_groups;             // mode 2
+  int blocks_per_group;       // mode 2: 128-row blocks of the token axis per group
+  long long group_stride_c;   // mode 2: elements of C per group
+  const int* ready_flags;     // arrival flags (monotone epochs) or nullptr
+  const int* mblk_flag;       // [m blocks] index into ready_flags
+  int epoch;
+  unsigned long long flag_limit_ns;
+  const long long* row_dst;   // per output row: (peer << 40) | row, or < 0 to drop; nullptr = dense
+  void* const* peer_base;     // [peers] base pointer of each peer's destination buffer
+  int* done_counters;         // [flags] tiles finished per destination (local)
+  const int* done_expected;   // [flags] M blocks expected per destination (x n_blocks tiles each)
+  int* const* done_flag_ptr;  // [flags] peer flag word to release when a destination completes
+  int tiles_n_for_signal;     // unused padding / reserved
+};
+
+template <class F>
+__device__ __forceinline__ void for_each_k(const GemmParams& p, int g, F&& f) {
+  if (p.mode != 2) {
+    const int nkb = (p.K + BK - 1) / BK;
+    for (int kb = 0; kb < nkb; ++kb) {
+      if (!f(kb * BK)) return;
+    }
+  } else {
+    const int b0 = g * p.blocks_per_group;
+    for (int b = b0; b < b0 + p.blocks_per_group; ++b) {
+      const int r = p.mblk_rows ? p.mblk_rows[b] : BM;
+      if (r <= 0) continue;
+      if (!f(b * BM)) return;
+      if (!f(b * BM + BK)) return;
+    }
+  }
+}
+
+__device__ __forceinline__ int count_k(const GemmParams& p, int g) {
+  if (p.mode != 2) return (p.K + BK - 1) / BK;
+  int n = 0;
+  const int b0 = g * p.blocks_per_group;
+  for (int b = b0; b < b0 + p.blocks_per_group; ++b) {
+    const int r = p.mblk_rows ? p.mblk_rows[b] : BM;
+    if (r > 0) n += 2;
+  }
+  return n;
+}
+
+struct Tile {
+  int g, m_blk, n_blk;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (np::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  // barriers: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then tmem ptr, abort flag
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  uint8_t* tail = smem_raw + (bar_base - np::smem_u32(smem_raw)) + 8 * (2 * STAGES + 4);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int m_blocks = (p.M + BM - 1) / BM;
+  const int bn_out = (p.epilogue == 1) ? BN / 2 : BN;  // output columns per tile
+  const int n_blocks = (p.N + bn_out - 1) / bn_out;
+  const int groups = (p.mode == 2) ? p.num_groups : 1;
+  const int tiles_per_group = m_blocks * n_blocks;
+  const int num_tiles = tiles_per_group * groups;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      np::mbar_init(full_bar(s), 1);
+      np::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      np::mbar_init(tfull_bar(a), 1);
+      np::mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    np::mbar_fence_init();
+    np::tma_prefetch_desc(&tmA);
+    np::tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    np::tmem_alloc(np::smem_u32((const void*)tmem_ptr_smem), TMEM_COLS);
+    np::tmem_relinquish();
+  }
+  np::tc_fence_before();
+  __syncthreads();
+  np::tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  auto decode = [&](int t) {
+    Tile tl;
+    tl.g = t / tiles_per_group;
+    const int r = t - tl.g * tiles_per_group;
+    tl.m_blk = r % m_blocks;
+    tl.n_blk = r / m_blocks;
+    return tl;
+  };
+  // rows of this M block that carry data (0 = nothing to do); waits for the arrival flag first.
+  auto tile_rows = [&](const Tile& tl, int role) -> int {
+    if (p.mode != 1) return BM;
+    if (p.ready_flags) {
+      const int fi = p.mblk_flag ? p.mblk_flag[tl.m_blk] : 0;
+      if (!np::wait_flag_ge(p.ready_flags + fi, p.epoch, p.flag_limit_ns, KID_GEMM, 100 + role)) {
+        *abort_flag = 1;
+        return -1;
+      }
+    }
+    return p.mblk_rows ? p.mblk_rows[tl.m_blk] : BM;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
+        const Tile tl = decode(t);
+        const int rows = tile_rows(tl, 0);
+        if (rows < 0) break;
+        if (rows == 0) continue;
+        const int m0 = tl.m_blk * BM;
+        const int n0 = tl.n_blk * bn_out;
+        long long goff = 0;  // row offset of this tile's group inside the stacked B tensor
+        if (p.mode == 1 && p.mblk_group) goff = (long long)p.mblk_group[tl.m_blk] * p.group_stride_b;
+        const long long brow = n0 + (p.b_mn ? 0 : goff);
+        const int bk_off = p.b_mn ? (int)goff : 0;
+        for_each_k(p, tl.g, [&](int k0) -> bool {
+          if (!np::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, KID_GEMM, 1)) return false;
+          const uint32_t sA = smem_base + stage * STAGE_BYTES;
+          const uint32_t sB = sA + A_BYTES;
+          np::mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          if (!p.a_mn) {
+            np::tma_load_2d(sA, &tmA, full_bar(stage), k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              np::tma_load_2d(sA + c * (64 * BK * 2), &tmA, full_bar(stage), m0 + c * 64, k0);
+          }
+          if (!p.b_mn) {
+            if (p.epilogue == 1) {
+              np::tma_load_2d(sB, &tmB, full_bar(stage), k0, (int)brow);
+              np::tma_load_2d(sB + (BN / 2) * BK * 2, &tmB2, full_bar(stage), k0, (int)brow);
+            } else {
+              np::tma_load_2d(sB, &tmB, full_bar(stage), k0, (int)brow);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              np::tma_load_2d(sB + c * (64 * BK * 2), &tmB, full_bar(stage), (int)brow + c * 64, k0 + bk_off);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          return true;
+        });
+      }
+      if (*abort_flag) __nanosleep(1000000);  // let copies already issued land before exit
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = np::make_idesc(BM, BN, 1, 1, p.a_mn, p.b_mn);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
+        const Tile tl = decode(t);
+        const int rows = tile_rows(tl, 1);
+        if (rows < 0) break;
+        if (rows == 0) continue;
+        if (count_k(p, tl.g) == 0) continue;
+        if (!np::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, KID_GEMM, 2)) break;
+        np::tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        uint32_t accum = 0;
+        for_each_k(p, tl.g, [&](int) -> bool {
+          if (!np::mbar_wait(full_bar(stage), phase, abort_flag, KID_GEMM, 3)) return false;
+          np::tc_fence_after();
+          const uint32_t sA = smem_base + stage * STAGE_BYTES;
+          const uint32_t sB = sA + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t ad = p.a_mn ? np::make_smem_desc(sA + kk * 2048, 64 * BK * 2, 1024)
+                                       : np::make_smem_desc(sA + kk * 32, 16, 1024);
+            const uint64_t bd = p.b_mn ? np::make_smem_desc(sB + kk * 2048, 64 * BK * 2, 1024)
+                                       : np::make_smem_desc(sB + kk * 32, 16, 1024);
+            np::tc_mma_f16(tmem_d, ad, bd, idesc, accum);
+            accum = 1;
+          }
+          np::tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          return true;
+        });
+        np::tc_commit(tfull_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (*abort_flag) __nanosleep(1000000);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
+      const Tile tl = decode(t);
+      const int rows = tile_rows(tl, 2);
+      if (rows < 0) break;
+      if (rows == 0) continue;
+      const int nk = count_k(p, tl.g);
+      const int row = tl.m_blk * BM + quarter * 32 + lane;
+      const int n0 = tl.n_blk * bn_out;
+      bool row_ok = row < p.M;
+      char* crow;
+      if (p.row_dst) {
+        const long long d = row_ok ? p.row_dst[row] : -1;
+        row_ok = row_ok && d >= 0;
+        const long long peer = row_ok ? (d >> 40) : 0;
+        const long long drow = d & ((1ll << 40) - 1);
+        crow = (char*)p.peer_base[peer] + (size_t)drow * p.ldc * (p.out_f32 ? 4 : 2);
+      } else {
+        crow = (char*)p.C + ((size_t)tl.g * p.group_stride_c + (size_t)row * p.ldc) * (p.out_f32 ? 4 : 2);
+      }
+      bool have_acc = nk > 0;
+      if (have_acc) {
+        if (!np::mbar_wait(tfull_bar(acc), acc_phase, abort_flag, KID_GEMM, 4)) break;
+        np::tc_fence_after();
+      }
+      const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
+      if (p.epilogue == 1) {
+        // gate = columns [0, BN/2), up = columns [BN/2, BN); out = silu(gate) * up
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          np::tmem_ld32(taddr + c * 32, g);
+          np::tmem_ld32(taddr + BN / 2 + c * 32, u);
+          np::tmem_ld_wait();
+          const int col = n0 + c * 32;
+          if (row_ok && col < p.N) {
+            uint32_t o[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
+              const float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
+              o[i] = np::pack_bf16(np::silu_f(g0) * u0, np::silu_f(g1) * u1);
+            }
+            __nv_bfloat16* dst = (__nv_bfloat16*)crow + col;
+            if (col + 32 <= p.N) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            } else {
+              _Pragma("unroll") for (int i = 0; i < 32; ++i) if (col + i < p.N)
+                dst[i] = reinterpret_cast<__nv_bfloat16*>(o)[i];
+            }
+            if (p.C2) {
+              __nv_bfloat16* d2 = (__nv_bfloat16*)p.C2 + (size_t)row * p.ldc2 + col;
+              if (col + 32 <= p.N) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  reinterpret_cast<uint4*>(d2)[i] =
+                      make_uint4(np::pack_bf16(__uint_as_float(g[8 * i]), __uint_as_float(g[8 * i + 1])),
+                                 np::pack_bf16(__uint_as_float(g[8 * i + 2]), __uint_as_float(g[8 * i + 3])),
+                                 np::pack_bf16(__uint_as_float(g[8 * i + 4]), __uint_as_float(g[8 * i + 5])),
+                                 np::pack_bf16(__uint_as_float(g[8 * i + 6]), __uint_as_float(g[8 * i + 7])));
+                  reinterpret_cast<uint4*>(d2 + p.N)[i] =
+                      make_uint4(np::pack_bf16(__uint_as_float(u[8 * i]), __uint_as_float(u[8 * i + 1])),
+                                 np::pack_bf16(__uint_as_float(u[8 * i + 2]), __uint_as_float(u[8 * i + 3])),
+                                 np::pack_bf16(__uint_as_float(u[8 * i + 4]), __uint_as_float(u[8 * i + 5])),
+                                 np::pack_bf16(__uint_as_float(u[8 * i + 6]), __uint_as_float(u[8 * i + 7])));
+                }
+              } else {
+                _Pragma("unroll") for (int i = 0; i < 32; ++i) if (col + i < p.N) {
+                  d2[i] = __float2bfloat16(__uint_as_float(g[i]));
+                  d2[p.N + i] = __float2bfloat16(__uint_as_float(u[i]));
+                }
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          if (have_acc) {
+            np::tmem_ld32(taddr + c * 32, r);
+            np::tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          const int col = n0 + c * 32;
+          if (!row_ok || col >= p.N) continue;
+          const bool full = col + 32 <= p.N;
+          if (p.out_f32) {
+            float* dst = (float*)crow + col;
+            if (full) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float4 v = make_float4(__uint_as_float(r[4 * i]) * p.alpha, __uint_as_float(r[4 * i + 1]) * p.alpha,
+                                       __uint_as_float(r[4 * i + 2]) * p.alpha, __uint_as_float(r[4 * i + 3]) * p.alpha);
+                if (p.accumulate) {
+                  const float4 o = reinterpret_cast<float4*>(dst)[i];
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                reinterpret_cast<float4*>(dst)[i] = v;
+              }
+            } else {
+              _Pragma("unroll") for (int i = 0; i < 32; ++i) if (col + i < p.N) {
+                float v = __uint_as_float(r[i]) * p.alpha;
+                if (p.accumulate) v += dst[i];
+                dst[i] = v;
+              }
+            }
+          } else {
+            __nv_bfloat16* dst = (__nv_bfloat16*)crow + col;
+            if (full) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[8 * i + j]) * p.alpha;
+                if (p.accumulate) {
+                  const uint4 o = reinterpret_cast<uint4*>(dst)[i];
+                  const float2 o0 = np::unpack_bf16(o.x), o1 = np::unpack_bf16(o.y), o2 = np::unpack_bf16(o.z), o3 = np::unpack_bf16(o.w);
+                  f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
+                  f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
+                }
+                reinterpret_cast<uint4*>(dst)[i] = make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]),
+                                                              np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
+              }
+            } else {
+              _Pragma("unroll") for (int i = 0; i < 32; ++i) if (col + i < p.N) {
+                float v = __uint_as_float(r[i]) * p.alpha;
+                if (p.accumulate) v += __bfloat162float(dst[i]);
+                dst[i] = __float2bfloat16(v);
+              }
+            }
+          }
+        }
+      }
+      if (have_acc) {
+        np::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) np::mbar_arrive(tempty_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (p.done_counters) {
+        // all rows of this tile are stored (possibly into peer memory): publish, then count the
+        // tile against its destination and release the peer's flag when the destination is done.
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          // each of the four epilogue warps counts once per tile: expected is in tiles
+          const int fi = p.mblk_flag ? p.mblk_flag[tl.m_blk] : 0;
+          const int done = atomicAdd(&p.done_counters[fi], 1) + 1;
+          if (done == 4 * n_blocks * p.done_expected[fi]) {  // done_expected counts M blocks
+            __threadfence_system();
+            np::st_release_sys(p.done_flag_ptr[fi], p.epoch);
+          }
+        }
+      }
+    }
+  }
+
+  np::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    np::tc_fence_after();
+    np::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+int g_num_sms = 0;
+
+}  // namespace
+
+// ------------------------------------------------------------------ host side
+static NpEncodeTiledFn g_encode = nullptr;
+NpEncodeTiledFn np_get_encode_tiled() {
+  if (g_encode) return g_encode;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  g_encode = (NpEncodeTiledFn)fn;
+  return g_encode;
+}
+
+int np_make_tmap_2d(CUtensorMap* out, const void* base, int elt_bytes, uint64_t rows, uint64_t cols,
+                    uint64_t ld, uint32_t box_cols, uint32_t box_rows) {
+  NpEncodeTiledFn enc = np_get_encode_tiled();
+  if (!enc) return -1;
+  CUtensorMapDataType dt = elt_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                          : (elt_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * (uint64_t)elt_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+// Arguments of np_gemm_bf16 (mirrored field by field by the ctypes Structure in ops/_lib.py).
+struct NpGemmArgs {
+  const void* A; const void* B; const void* B2; void* C; void* C2;
+  long long lda, ldb, ldc, ldc2;
+  long long a_rows, b_rows;  // total rows (K-major) or total K rows (MN-major) of the A / B tensors
+  int M, N, K;
+  int a_mn, b_mn, out_f32, accumulate, epilogue, mode;
+  float alpha;
+  const int* mblk_group; const int* mblk_rows; long long group_stride_b;
+  int num_groups, blocks_per_group; long long group_stride_c;
+  const int* ready_flags; const int* mblk_flag; int epoch; unsigned long long flag_limit_ns;
+  const long long* row_dst; void* const* peer_base;
+  int* done_counters; const int* done_expected; int* const* done_flag_ptr;
+  int bn;        // 0 = choose, else 128 or 256
+  int max_ctas;  // 0 = all SMs
+};
+
+template <int BN, int STAGES>
+static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
+  CUtensorMap tmA, tmB, tmB2;
+  int rc;
+  if (!a.a_mn) rc = np_make_tmap_2d(&tmA, a.A, 2, (uint64_t)a.a_rows, (uint64_t)a.K, (uint64_t)a.lda, BK, BM);
+  else rc = np_make_tmap_2d(&tmA, a.A, 2, (uint64_t)a.a_rows, (uint64_t)a.M, (uint64_t)a.lda, 64, BK);
+  if (rc) return 100 + rc;
+  const uint32_t b_box_rows = a.epilogue == 1 ? BN / 2 : BN;
+  if (!a.b_mn) rc = np_make_tmap_2d(&tmB, a.B, 2, (uint64_t)a.b_rows, (uint64_t)a.K, (uint64_t)a.ldb, BK, b_box_rows);
+  else rc = np_make_tmap_2d(&tmB, a.B, 2, (uint64_t)a.b_rows, (uint64_t)a.N, (uint64_t)a.ldb, 64, BK);
+  if (rc) return 200 + rc;
+  tmB2 = tmB;
+  if (a.epilogue == 1) {
+    rc = np_make_tmap_2d(&tmB2, a.B2, 2, (uint64_t)a.b_rows, (uint64_t)a.K, (uint64_t)a.ldb, BK, b_box_rows);
+    if (rc) return 300 + rc;
+  }
+  GemmParams p{};
+  p.C = a.C; p.C2 = a.C2; p.M = a.M; p.N = a.N; p.K = a.K; p.ldc = a.ldc; p.ldc2 = a.ldc2;
+  p.a_mn = a.a_mn; p.b_mn = a.b_mn; p.out_f32 = a.out_f32; p.accumulate = a.accumulate;
+  p.epilogue = a.epilogue; p.mode = a.mode; p.alpha = a.alpha;
+  p.mblk_group = a.mblk_group; p.mblk_rows = a.mblk_rows; p.group_stride_b = a.group_stride_b;
+  p.num_groups = a.num_groups; p.blocks_per_group = a.blocks_per_group; p.group_stride_c = a.group_stride_c;
+  p.ready_flags = a.ready_flags; p.mblk_flag = a.mblk_flag; p.epoch = a.epoch;
+  p.flag_limit_ns = a.flag_limit_ns ? a.flag_limit_ns : NP_WAIT_LIMIT_NS;
+  p.row_dst = a.row_dst; p.peer_base = a.peer_base;
+  p.done_counters = a.done_counters; p.done_expected = a.done_expected; p.done_flag_ptr = a.done_flag_ptr;
+
+  constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return 400 + (int)e;
+    attr_set = true;
+  }
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int bn_out = a.epilogue == 1 ? BN / 2 : BN;
+  const int m_blocks = (a.M + BM - 1) / BM, n_blocks = (a.N + bn_out - 1) / bn_out;
+  const long long tiles = (long long)m_blocks * n_blocks * (a.mode == 2 ? a.num_groups : 1);
+  int cap = a.max_ctas > 0 ? a.max_ctas : g_num_sms;
+  int grid = (int)(tiles < cap ? tiles : cap);
+  if (grid <= 0) return 0;
+  gemm_bf16_kernel<BN, STAGES><<<grid, 192, SMEM, stream>>>(tmA, tmB, tmB2, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 500 + (int)e;
+}
+
+// C[M,N] (+)= alpha * A * B^T with the operand layouts described in NpGemmArgs.
+// Returns 0 or a launch/setup error; device-side problems are reported via np_status_read.
+NP_API int np_gemm_bf16(const NpGemmArgs* args, void* stream) {
+  const NpGemmArgs& a = *args;
+  if (a.M <= 0 || a.N <= 0) return 0;
+  if ((a.lda % 8) || (a.ldb % 8) || (((uintptr_t)a.A) & 15) || (((uintptr_t)a.B) & 15)) return 1;
+  int bn = a.bn;
+  if (a.epilogue == 1) bn = 256;
+  if (bn == 0) bn = (a.N >= 256 && (a.N % 256 == 0 || a.N >= 2048)) ? 256 : 128;
+  if (bn == 256) return launch_gemm<256, 4>(a, (cudaStream_t)stream);
+  return launch_gemm<128, 6>(a, (cudaStream_t)stream);
+}
+
+NP_API int np_status_read(int* out8) {
+  return (int)cudaMemcpyFromSymbol(out8, g_np_status, sizeof(int) * 8);
+}
+NP_API int np_status_clear() {
+  int z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  return (int)cudaMemcpyToSymbol(g_np_status, z, sizeof(z));
+}
+NP_API int np_num_sms() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n;
+}

@@ -1,0 +1,164 @@
+"""ctypes binding to the in-tree sm_100a kernel library (``lib/libnpb200.so``).
+
+The library exports plain C entry points that take device pointers and a CUDA stream; the wrappers
+in ``ops/`` pass ``tensor.data_ptr()`` and the current torch stream, so every kernel runs in stream
+order with the surrounding torch ops and can be captured into CUDA graphs by the caller.
+
+On a box with a GPU the library is mandatory: ``lib()`` raises if it cannot be loaded (there is no
+silent eager fallback on CUDA tensors). On a CPU-only box the ops use their PyTorch reference.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LIB_ERR: str | None = None
+LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libnpb200.so"
+
+c_void_p, c_int, c_ll, c_ull, c_float = C.c_void_p, C.c_int, C.c_longlong, C.c_ulonglong, C.c_float
+
+
+class GemmArgs(C.Structure):
+    """Mirror of ``NpGemmArgs`` in csrc/gemm_sm100.cu (field order matters)."""
+
+    _fields_ = [
+        ("A", c_void_p), ("B", c_void_p), ("B2", c_void_p), ("C", c_void_p), ("C2", c_void_p),
+        ("lda", c_ll), ("ldb", c_ll), ("ldc", c_ll), ("ldc2", c_ll),
+        ("a_rows", c_ll), ("b_rows", c_ll),
+        ("M", c_int), ("N", c_int), ("K", c_int),
+        ("a_mn", c_int), ("b_mn", c_int), ("out_f32", c_int), ("accumulate", c_int),
+        ("epilogue", c_int), ("mode", c_int),
+        ("alpha", c_float),
+        ("mblk_group", c_void_p), ("mblk_rows", c_void_p), ("group_stride_b", c_ll),
+        ("num_groups", c_int), ("blocks_per_group", c_int), ("group_stride_c", c_ll),
+        ("ready_flags", c_void_p), ("mblk_flag", c_void_p), ("epoch", c_int), ("flag_limit_ns", c_ull),
+        ("row_dst", c_void_p), ("peer_base", c_void_p),
+        ("done_counters", c_void_p), ("done_expected", c_void_p), ("done_flag_ptr", c_void_p),
+        ("bn", c_int), ("max_ctas", c_int),
+    ]
+
+
+class DispatchArgs(C.Structure):
+    """Mirror of ``NpDispatchArgs`` in csrc/moe.cu."""
+
+    _fields_ = [
+        ("x", c_void_p), ("indices", c_void_p), ("slot_pos", c_void_p), ("counts_kept", c_void_p),
+        ("slot_scale", c_void_p),
+        ("T", c_int), ("K", c_int), ("D", c_int), ("E", c_int), ("E_local", c_int), ("n_ranks", c_int),
+        ("my_rank", c_int), ("region_rows", c_int), ("quant", c_int),
+        ("peer_rows", c_void_p), ("peer_scales", c_void_p), ("peer_row_dst", c_void_p),
+        ("peer_mblk_rows", c_void_p), ("peer_src_blocks", c_void_p), ("peer_flags", c_void_p),
+        ("done_ctr", c_void_p), ("epoch", c_int), ("write_meta", c_int), ("max_ctas", c_int),
+    ]
+
+
+class CombineArgs(C.Structure):
+    """Mirror of ``NpCombineArgs`` in csrc/moe.cu."""
+
+    _fields_ = [
+        ("rows", c_void_p), ("slot_pos", c_void_p), ("weights", c_void_p), ("add1", c_void_p),
+        ("add2", c_void_p), ("dl", c_void_p), ("wg", c_void_p), ("out", c_void_p),
+        ("T", c_int), ("K", c_int), ("D", c_int), ("E", c_int),
+        ("flags", c_void_p), ("sent_to_peer", c_void_p), ("n_ranks", c_int), ("epoch", c_int),
+        ("limit_ns", c_ull),
+    ]
+
+
+class KernelError(RuntimeError):
+    """A kernel launch failed or a kernel reported a device-side status (timeout, bounds)."""
+
+
+STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad argument",
+                4: "bounds check failed"}
+
+
+def load_error() -> str | None:
+    return _LIB_ERR
+
+
+def lib():
+    """Load (building first if the .so is missing and nvcc exists) and return the ctypes library."""
+    global _LIB, _LIB_ERR
+    if _LIB is not None:
+        return _LIB
+    if not LIB_PATH.exists():
+        try:
+            from ..build import build_extension
+
+            build_extension()
+        except Exception as e:  # noqa: BLE001
+            _LIB_ERR = f"build failed: {e}"
+            raise KernelError(f"libnpb200.so missing and could not be built: {e}") from e
+    try:
+        _LIB = C.CDLL(str(LIB_PATH))
+    except OSError as e:
+        _LIB_ERR = str(e)
+        raise KernelError(f"cannot load {LIB_PATH}: {e}") from e
+    _LIB.np_gemm_bf16.argtypes = [C.POINTER(GemmArgs), c_void_p]
+    _LIB.np_ep_dispatch.argtypes = [C.POINTER(DispatchArgs), c_void_p]
+    _LIB.np_ep_combine.argtypes = [C.POINTER(CombineArgs), c_void_p]
+    _LIB.np_status_read.argtypes = [C.POINTER(c_int)]
+    return _LIB
+
+
+def available() -> bool:
+    """True when CUDA tensors should go through the kernels (a GPU is present)."""
+    return torch.cuda.is_available()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def check(rc: int, name: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{name} failed with code {rc}")
+
+
+def status() -> tuple[int, ...]:
+    """Read the device status words (synchronises the device)."""
+    buf = (c_int * 8)()
+    lib().np_status_read(buf)
+    return tuple(buf)
+
+
+def check_status(where: str = "") -> None:
+    st = status()
+    if st[0] != 0:
+        lib().np_status_clear()
+        raise KernelError(
+            f"device status {st[0]} ({STATUS_NAMES.get(st[0], '?')}) kernel={st[1]} block={st[2]} "
+            f"detail={st[3]} {where}")
+
+
+def call(name: str, *args) -> None:
+    """Call ``np_<name>`` with the current stream appended; scalars are wrapped by type."""
+    fn = getattr(lib(), "np_" + name)
+    conv = []
+    for a in args:
+        if isinstance(a, torch.Tensor):
+            conv.append(c_void_p(a.data_ptr()))
+        elif a is None:
+            conv.append(c_void_p(0))
+        elif isinstance(a, float):
+            conv.append(c_float(a))
+        elif isinstance(a, LL):
+            conv.append(c_ll(int(a)))
+        elif isinstance(a, (bool, int)):
+            conv.append(c_int(int(a)))
+        else:
+            conv.append(a)
+    conv.append(c_void_p(stream()))
+    check(fn(*conv), name)
+
+
+class LL(int):
+    """Marks an integer argument that the C side takes as ``long long``."""

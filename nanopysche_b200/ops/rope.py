@@ -1,0 +1,122 @@
+"""Rotary position embedding: table generation and the half-split rotation, forward and backward.
+
+Reference math: model/rope.py:62-106 (inv_freq, optional piecewise scaling, cos/sin of
+``outer(pos, inv_freq)``) and :139-170 (``x*cos + rotate_half(x)*sin``, halves split at ``rot/2``).
+The sm_100a kernel (csrc/elementwise.cu ``rope_kernel``) rotates a strided ``[T, H, hd]`` view, so it
+runs directly on the q and k slices of a fused QKV GEMM output; the backward pass is the same kernel
+with the sine negated. ``yarn`` adds the NTK-by-parts ramp and attention scale that the reference's
+"YaRN" lacks.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+SCALING_IDS = {None: 0, "none": 0, "piecewise": 1, "yarn": 2}
+
+
+def yarn_mscale(factor: float) -> float:
+    return 1.0 if factor <= 1.0 else 0.1 * math.log(factor) + 1.0
+
+
+def rope_tables_ref(seq_len: int, rot: int, base: float = 10000.0, scaling: str | None = None,
+                    factor: float = 1.0, orig_len: float = 8192.0, low_f: float = 1.0, high_f: float = 4.0,
+                    device="cpu"):
+    """(cos, sin), each fp32 ``[seq_len, rot/2]``."""
+    half = rot // 2
+    idx = torch.arange(half, dtype=torch.float32, device=device)
+    inv = base ** (-2.0 * idx / rot)
+    ms = 1.0
+    if scaling == "piecewise" and factor > 1.0:
+        wavelen = 2 * math.pi / inv
+        inv = torch.where(wavelen < orig_len / high_f, inv,
+                          torch.where(wavelen > orig_len / low_f, inv / factor, inv))
+    elif scaling == "yarn" and factor > 1.0:
+        d_lo = rot * math.log(orig_len / (high_f * 2 * math.pi)) / (2 * math.log(base))
+        d_hi = rot * math.log(orig_len / (low_f * 2 * math.pi)) / (2 * math.log(base))
+        lo, hi = max(math.floor(d_lo), 0), min(math.ceil(d_hi), half - 1)
+        ramp = ((idx - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
+        extrap = 1.0 - ramp
+        inv = (inv / factor) * (1 - extrap) + inv * extrap
+        ms = yarn_mscale(factor)
+    ang = torch.outer(torch.arange(seq_len, dtype=torch.float32, device=device), inv)
+    return ang.cos() * ms, ang.sin() * ms
+
+
+def rope_tables(seq_len, rot, base=10000.0, scaling=None, factor=1.0, orig_len=8192.0, low_f=1.0, high_f=4.0,
+                device="cpu"):
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        return rope_tables_ref(seq_len, rot, base, scaling, factor, orig_len, low_f, high_f, device)
+    cos = torch.empty((seq_len, rot // 2), device=dev, dtype=torch.float32)
+    sin = torch.empty_like(cos)
+    sid = SCALING_IDS[scaling] if factor > 1.0 else 0
+    if sid == 2:  # yarn: low_f/high_f are beta_slow/beta_fast
+        ms = yarn_mscale(factor)
+    else:
+        ms = 1.0
+    _lib.call("rope_table", cos, sin, seq_len, rot, float(base), sid, float(factor), float(orig_len),
+              float(low_f), float(high_f), float(ms))
+    return cos, sin
+
+
+def apply_rope_ref(x, cos, sin, pos_offset: int = 0, pos_ids=None, sign: float = 1.0):
+    """x: [B, S, H, hd]; cos/sin: [max_pos, rot/2]."""
+    B, S, H, hd = x.shape
+    half = cos.shape[1]
+    rot = 2 * half
+    if pos_ids is None:
+        pos = torch.arange(S, device=x.device) + pos_offset
+        c, s = cos[pos][None, :, None, :], sin[pos][None, :, None, :]
+    else:
+        p = pos_ids.reshape(B, S).long()
+        c, s = cos[p][:, :, None, :], sin[p][:, :, None, :]
+    s = s * sign
+    xf = x.float()
+    x1, x2, rest = xf[..., :half], xf[..., half:rot], xf[..., rot:]
+    out = torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, rest], dim=-1)
+    return out.to(x.dtype)
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, pos_offset, pos_ids, inplace):
+        B, S, H, hd = x.shape
+        assert x.stride(3) == 1 and x.stride(2) == hd and x.stride(0) == S * x.stride(1)
+        out = x if inplace else torch.empty((B, S, H, hd), device=x.device, dtype=x.dtype)
+        _lib.call("rope", x, out, cos, sin, pos_ids, _lib.LL(B * S), S, int(pos_offset), H, hd, 2 * cos.shape[1],
+                  _lib.LL(x.stride(1)), _lib.LL(out.stride(1)), 1.0)
+        ctx.save_for_backward(cos, sin, pos_ids if pos_ids is not None else cos.new_empty(0))
+        ctx.meta = (pos_offset, pos_ids is not None)
+        if inplace:
+            ctx.mark_dirty(x)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin, pos_ids = ctx.saved_tensors
+        pos_offset, has_ids = ctx.meta
+        B, S, H, hd = dy.shape
+        if not (dy.stride(3) == 1 and dy.stride(2) == hd and dy.stride(0) == S * dy.stride(1)):
+            dy = dy.contiguous()
+        dx = torch.empty((B, S, H, hd), device=dy.device, dtype=dy.dtype)
+        _lib.call("rope", dy, dx, cos, sin, pos_ids if has_ids else None, _lib.LL(B * S), S, int(pos_offset), H, hd,
+                  2 * cos.shape[1], _lib.LL(dy.stride(1)), _lib.LL(dx.stride(1)), -1.0)
+        return dx, None, None, None, None, None
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos_offset: int = 0,
+               pos_ids: torch.Tensor | None = None) -> torch.Tensor:
+    """Rotate ``x [B, S, H, hd]`` (a possibly strided view with contiguous heads) by its positions."""
+    B, S, H, hd = x.shape
+    ok = (x.is_cuda and x.dtype == torch.bfloat16 and hd % 8 == 0 and (2 * cos.shape[1]) % 16 == 0 and
+          x.stride(3) == 1 and x.stride(2) == hd and x.stride(1) % 8 == 0 and x.stride(0) == S * x.stride(1) and
+          cos.dtype == torch.float32)
+    if ok:
+        if pos_ids is not None:
+            pos_ids = pos_ids.reshape(-1).to(torch.int32)
+        return _Rope.apply(x, cos, sin, pos_offset, pos_ids, False)
+    return apply_rope_ref(x, cos, sin, pos_offset, pos_ids)
