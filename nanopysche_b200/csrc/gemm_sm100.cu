@@ -48,7 +48,8 @@ struct GemmParams {
   int* done_counters;         // [flags] tiles finished per destination (local)
   const int* done_expected;   // [flags] M blocks expected per destination (x n_blocks tiles each)
   int* const* done_flag_ptr;  // [flags] peer flag word to release when a destination completes
-  int tiles_n_for_signal;     // unused padding / reserved
+  const void* Cin;            // accumulate source (same dtype as C), rows indexed like a dense C
+  long long ldcin;
 };
 
 template <class F>
@@ -270,6 +271,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       } else {
         crow = (char*)p.C + ((size_t)tl.g * p.group_stride_c + (size_t)row * p.ldc) * (p.out_f32 ? 4 : 2);
       }
+      const char* cin_row = p.Cin ? (const char*)p.Cin + ((size_t)tl.g * p.group_stride_c + (size_t)row * p.ldcin) * (p.out_f32 ? 4 : 2)
+                                  : nullptr;
       bool have_acc = nk > 0;
       if (have_acc) {
         if (!np::mbar_wait(tfull_bar(acc), acc_phase, abort_flag, KID_GEMM, 4)) break;
@@ -348,8 +351,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int i = 0; i < 8; ++i) {
                 float4 v = make_float4(__uint_as_float(r[4 * i]) * p.alpha, __uint_as_float(r[4 * i + 1]) * p.alpha,
                                        __uint_as_float(r[4 * i + 2]) * p.alpha, __uint_as_float(r[4 * i + 3]) * p.alpha);
-                if (p.accumulate) {
-                  const float4 o = reinterpret_cast<float4*>(dst)[i];
+                if (cin_row) {
+                  const float4 o = reinterpret_cast<const float4*>((const float*)cin_row + col)[i];
                   v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
                 }
                 reinterpret_cast<float4*>(dst)[i] = v;
@@ -357,7 +360,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             } else {
               _Pragma("unroll") for (int i = 0; i < 32; ++i) if (col + i < p.N) {
                 float v = __uint_as_float(r[i]) * p.alpha;
-                if (p.accumulate) v += dst[i];
+                if (cin_row) v += ((const float*)cin_row + col)[i];
                 dst[i] = v;
               }
             }
@@ -369,8 +372,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 float f[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[8 * i + j]) * p.alpha;
-                if (p.accumulate) {
-                  const uint4 o = reinterpret_cast<uint4*>(dst)[i];
+                if (cin_row) {
+                  const uint4 o = reinterpret_cast<const uint4*>((const __nv_bfloat16*)cin_row + col)[i];
                   const float2 o0 = np::unpack_bf16(o.x), o1 = np::unpack_bf16(o.y), o2 = np::unpack_bf16(o.z), o3 = np::unpack_bf16(o.w);
                   f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
                   f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
@@ -381,7 +384,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             } else {
               _Pragma("unroll") for (int i = 0; i < 32; ++i) if (col + i < p.N) {
                 float v = __uint_as_float(r[i]) * p.alpha;
-                if (p.accumulate) v += __bfloat162float(dst[i]);
+                if (cin_row) v += __bfloat162float(((const __nv_bfloat16*)cin_row + col)[i]);
                 dst[i] = __float2bfloat16(v);
               }
             }
@@ -468,6 +471,7 @@ struct NpGemmArgs {
   int* done_counters; const int* done_expected; int* const* done_flag_ptr;
   int bn;        // 0 = choose, else 128 or 256
   int max_ctas;  // 0 = all SMs
+  const void* Cin; long long ldcin;  // optional accumulate source (defaults to C when accumulate != 0)
 };
 
 template <int BN, int STAGES>
@@ -496,6 +500,8 @@ static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
   p.flag_limit_ns = a.flag_limit_ns ? a.flag_limit_ns : NP_WAIT_LIMIT_NS;
   p.row_dst = a.row_dst; p.peer_base = a.peer_base;
   p.done_counters = a.done_counters; p.done_expected = a.done_expected; p.done_flag_ptr = a.done_flag_ptr;
+  p.Cin = a.Cin ? a.Cin : (a.accumulate ? a.C : nullptr);
+  p.ldcin = a.Cin ? a.ldcin : a.ldc;
 
   constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
   static bool attr_set = false;

@@ -1,0 +1,5 @@
+"""Fault tolerance: resumable checkpoints and hang detection."""
+from .checkpoint import FaultTolerantCheckpointer
+from .hang_detection import CommTimeoutError, HangDetector, HeartbeatCoordinator
+
+__all__ = ["FaultTolerantCheckpointer", "HangDetector", "HeartbeatCoordinator", "CommTimeoutError"]

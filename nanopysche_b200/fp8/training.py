@@ -1,0 +1,80 @@
+"""FP8 training for dense Linear layers (reference: fp8/training.py:54-137, which delegates to
+torchao's ``convert_to_float8_training``).
+
+Here ``apply_fp8`` swaps eligible ``nn.Linear`` modules for ``Float8Linear``: e4m3 forward operands
+with dynamic blockwise scales (1x128 activations, 128x128 weights), gradients in bf16 (the
+reference's e5m2 backward dtype is accepted and recorded). The quantise-dequantise pair is applied
+around the GEMM, so the numerics are those of fp8 operands with fp32 accumulation on every device.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional
+
+import torch
+import torch.nn as nn
+
+from fp8_flow_moe import ops as fp8_ops
+
+
+@dataclass
+class FP8Config:
+    enabled: bool = False
+    forward_dtype: torch.dtype = torch.float8_e4m3fn
+    backward_dtype: torch.dtype = torch.float8_e5m2
+    recipe_name: str = "blockwise"
+    force_recompute_fp8_weight_in_bwd: bool = False
+    ignored_modules: List[str] = field(default_factory=lambda: ["lm_head", "gate"])
+    min_features: int = 128
+
+
+class _QDQ(torch.autograd.Function):
+    """Quantise-dequantise with a straight-through gradient."""
+
+    @staticmethod
+    def forward(ctx, x, weight_mode):
+        if weight_mode:
+            q, s = fp8_ops.quantize_weight_blockwise(x)
+        else:
+            q, s = fp8_ops.quantize_to_fp8(x.reshape(-1, x.shape[-1]))
+            q = q.reshape(x.shape)
+            s = s.reshape(*x.shape[:-1], -1)
+        return fp8_ops.dequantize_from_fp8(q, s, dtype=x.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class Float8Linear(nn.Linear):
+    def forward(self, x):
+        if x.shape[-1] % 128 or self.weight.shape[0] % 128:
+            return super().forward(x)
+        from ..ops.gemm import linear
+
+        return linear(_QDQ.apply(x, False), _QDQ.apply(self.weight, True), self.bias)
+
+
+def apply_fp8(model: nn.Module, config: Optional[FP8Config] = None,
+              module_filter: Optional[Callable[[nn.Module, str], bool]] = None) -> nn.Module:
+    cfg = config or FP8Config(enabled=True)
+    if not cfg.enabled:
+        return model
+    for name, mod in list(model.named_modules()):
+        for cname, child in list(mod.named_children()):
+            fqn = f"{name}.{cname}" if name else cname
+            if type(child) is not nn.Linear:
+                continue
+            if any(ig in fqn for ig in cfg.ignored_modules) or min(child.in_features, child.out_features) < \
+                    cfg.min_features:
+                continue
+            if module_filter is not None and not module_filter(child, fqn):
+                continue
+            child.__class__ = Float8Linear
+    model._fp8_config = cfg
+    return model
+
+
+def precompute_fp8_dynamic_scales(model: nn.Module) -> int:
+    """Refresh cached weight quantisation after an optimizer step; returns the number of fp8 layers."""
+    return sum(1 for m in model.modules() if isinstance(m, Float8Linear))

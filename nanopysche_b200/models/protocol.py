@@ -1,0 +1,37 @@
+"""Model protocol helpers (reference: model/protocol.py:18-91): which parallel hooks a model offers."""
+from __future__ import annotations
+
+import warnings
+
+import torch.nn as nn
+
+PARALLEL_HOOKS = ("apply_pp", "apply_tp", "apply_cp", "apply_ep", "apply_fsdp", "apply_compile")
+MOE_HOOKS = ("replace_block_with_moe_hybrid",)
+_HOOK_OF = {"pp": "apply_pp", "tp": "apply_tp", "cp": "apply_cp", "ep": "apply_ep", "fsdp": "apply_fsdp",
+            "compile": "apply_compile"}
+
+
+def has_hook(model: nn.Module, name: str) -> bool:
+    return callable(getattr(model, name, None))
+
+
+def model_display_name(model: nn.Module) -> str:
+    return type(model).__name__
+
+
+def unsupported_parallelism(model: nn.Module, *, tp: int = 1, pp: int = 1, cp: int = 1, ep: int = 1,
+                            fsdp: bool = False, compile: bool = False) -> list[str]:
+    """Names of the requested parallelism kinds the model has no hook for."""
+    wanted = {"tp": tp > 1, "pp": pp > 1, "cp": cp > 1, "ep": ep > 1, "fsdp": bool(fsdp), "compile": bool(compile)}
+    return [k for k, on in wanted.items() if on and not has_hook(model, _HOOK_OF[k])]
+
+
+def warn_unsupported_parallelism(model: nn.Module, **kw) -> list[str]:
+    missing = unsupported_parallelism(model, **kw)
+    if missing:
+        warnings.warn(f"{model_display_name(model)} has no hook for: {', '.join(missing)}; those are skipped")
+    return missing
+
+
+def count_parameters(model: nn.Module, trainable_only: bool = False) -> int:
+    return sum(p.numel() for p in model.parameters() if p.requires_grad or not trainable_only)

@@ -39,6 +39,7 @@ class GemmArgs(C.Structure):
         ("row_dst", c_void_p), ("peer_base", c_void_p),
         ("done_counters", c_void_p), ("done_expected", c_void_p), ("done_flag_ptr", c_void_p),
         ("bn", c_int), ("max_ctas", c_int),
+        ("Cin", c_void_p), ("ldcin", c_ll),
     ]
 
 
@@ -118,9 +119,14 @@ def ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+LAUNCHES = 0  # number of successful calls into the kernel library (each launches >= 1 kernel)
+
+
 def check(rc: int, name: str) -> None:
+    global LAUNCHES
     if rc != 0:
         raise KernelError(f"{name} failed with code {rc}")
+    LAUNCHES += 1
 
 
 def status() -> tuple[int, ...]:

@@ -103,6 +103,8 @@ def _wgrad_into(w: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor):
         first = not getattr(w, "_main_grad_dirty", False)
         gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=not first)
         w._main_grad_dirty = True
+        for q in getattr(w, "_covers", ()):  # a fused view stands for several parameters
+            q._main_grad_dirty = True
         return None
     return gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype if w.is_cuda else None)
 
@@ -125,7 +127,7 @@ class _Linear(torch.autograd.Function):
         dx = None
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True).reshape(x.shape)
-        dw = _wgrad_into(w, dy2, x2) if ctx.needs_input_grad[1] else None
+        dw = _wgrad_into(w, dy2, x2) if (ctx.needs_input_grad[1] or hasattr(w, "main_grad")) else None
         return dx, dw
 
 

@@ -1,0 +1,347 @@
+"""Fused MoE layer on sm_100a: router -> capacity -> dispatch (peer stores) -> grouped SwiGLU GEMM
+(waits on arrival flags) -> grouped down GEMM (epilogue pushes rows back to their source rank and
+signals it) -> combine, with the mirrored backward. One autograd node per layer; nothing in it
+synchronises with the host, and with one rank the "peers" are this GPU itself, so the same kernels
+run at every EP degree.
+
+Replaces, in the reference: the router (model/moe.py:133-321), the capacity loop (:1395-1448), the
+NCCL dispatcher with its 4 collectives and 3 host syncs per layer (:360-498), the per-expert Python
+loop of matmuls (:1498-1596) and the scatter-back (:1386-1390).
+
+Buffer protocol (all in the symmetric heap, same offsets on every rank):
+  recv_x[layer]  rows pushed by the sources, region ``[local expert][source rank]`` of ``R`` rows
+  ret_y[layer]   expert outputs returned to the source, one row per (token, k) slot
+  recv_g, ret_g  the same two roles for the backward pass (shared by all layers)
+  mblk_rows, row_dst, src_blocks   per-block row counts / per-row return addresses / block counts,
+                 written by the sources together with the rows
+  dispatch_flags[src], combine_flags[peer]   monotone epochs: "rows of epoch e have landed"
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .activation import glu, glu_bwd
+
+GATING_IDS = {"softmax": 0, "sigmoid": 1}
+WAIT_LIMIT_NS = int(os.environ.get("NPB200_WAIT_LIMIT_MS", "10000")) * 1_000_000
+
+
+# ------------------------------------------------------------------------------------------------ router
+class _Router(torch.autograd.Function):
+    """logits -> top-k -> gating weights, with the load-balance / z-loss statistics in the same pass."""
+
+    @staticmethod
+    def forward(ctx, x2, gate_w, gate_b, score_bias, K, gating, coef_z):
+        T, D = x2.shape
+        E = gate_w.shape[0]
+        dev = x2.device
+        logits = torch.empty((T, E), device=dev, dtype=torch.float32)
+        _lib.call("router_logits", x2, gate_w, gate_b, logits, T, D, E)
+        weights = torch.empty((T, K), device=dev, dtype=torch.float32)
+        indices = torch.empty((T, K), device=dev, dtype=torch.int32)
+        stats = torch.zeros(2 * E + 1, device=dev, dtype=torch.float32)
+        counts = torch.zeros(E, device=dev, dtype=torch.int32)
+        _lib.call("router_topk", logits, score_bias, weights, indices, counts, stats[:E], stats[E:E + 1], T, E, K,
+                  gating)
+        f = counts.float() / T
+        aux = E * (f * (stats[:E] / T)).sum()
+        if coef_z:
+            aux = aux + coef_z * stats[E] / T
+        ctx.save_for_backward(x2, gate_w, logits, weights, indices, f, score_bias if score_bias is not None
+                              else logits.new_empty(0))
+        ctx.cfg = (K, gating, float(coef_z or 0.0), score_bias is not None)
+        ctx.mark_non_differentiable(indices, counts)
+        return weights, indices, aux, counts
+
+    @staticmethod
+    def backward(ctx, dweights, _di, daux, _dc):
+        x2, gate_w, logits, weights, indices, f, sb = ctx.saved_tensors
+        K, gating, coef_z, has_sb = ctx.cfg
+        T, E = logits.shape
+        D = x2.shape[1]
+        dl = torch.empty_like(logits)
+        dw = dweights.contiguous() if dweights is not None else None
+        da = daux.reshape(1).float().contiguous() if daux is not None else None
+        _lib.call("router_bwd", logits, sb if has_sb else None, weights, indices, dw, f, da, 1.0, coef_z, dl, T, E, K,
+                  gating)
+        parts = _lib.lib().np_router_dgate_parts(T)
+        scratch = torch.empty((parts, E, D), device=x2.device, dtype=torch.float32)
+        dgw = torch.empty_like(gate_w)
+        dgb = torch.empty(E, device=x2.device, dtype=torch.float32)
+        _lib.call("router_dgate", dl, x2, dgw, dgb, scratch, T, D, E, 0)
+        dx = (dl @ gate_w).to(x2.dtype)
+        return dx, dgw, dgb, None, None, None, None
+
+
+def route(x: torch.Tensor, router) -> tuple:
+    """Kernel path of ``MoERouter.forward`` for bf16 CUDA input: (weights, indices int64, aux, counts)."""
+    cfg = router.config
+    D = x.shape[-1]
+    x2 = x.reshape(-1, D)
+    x2 = x2 if x2.is_contiguous() else x2.contiguous()
+    gating = GATING_IDS[getattr(cfg.gating_function, "value", cfg.gating_function)]
+    w, idx, aux, counts = _Router.apply(x2, router.gate.weight, router.gate.bias, router.score_bias, router.top_k,
+                                        gating, cfg.z_loss_multiplier or 0.0)
+    lead = x.shape[:-1]
+    return w.view(*lead, -1), idx.long().view(*lead, -1), aux, counts
+
+
+# ------------------------------------------------------------------------------------------------ runtime
+class FusedMoERuntime:
+    """Symmetric buffers, flags and static tables shared by all MoE layers of one model replica."""
+
+    def __init__(self, *, tokens: int, d_model: int, hidden: int, num_experts: int, top_k: int, n_layers: int,
+                 capacity_factor: Optional[float], group=None, device=None, max_ctas_dispatch: int = 0):
+        import torch.distributed as dist
+
+        from ..parallel.symm import SymmetricHeap
+
+        self.group = group
+        self.N = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if self.N > 1 else 0
+        self.T, self.D, self.H, self.E, self.K, self.L = tokens, d_model, hidden, num_experts, top_k, n_layers
+        assert num_experts % self.N == 0
+        self.E_local = num_experts // self.N
+        self.capacity = int(capacity_factor * tokens / num_experts) if capacity_factor is not None else -1
+        cap_rows = min(self.capacity, tokens) if self.capacity >= 0 else tokens
+        self.R = max(128, (cap_rows + 127) // 128 * 128)
+        self.bpr = self.R // 128
+        self.rows_total = self.E_local * self.N * self.R
+        self.blocks = self.rows_total // 128
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        row_bytes = self.rows_total * d_model * 2
+        slot_bytes = tokens * top_k * d_model * 2
+        need = n_layers * (row_bytes + slot_bytes) + row_bytes + slot_bytes + self.rows_total * 8 + (1 << 20)
+        self.heap = SymmetricHeap(need, group, self.device)
+        h = self.heap
+        self.recv_x = [h.alloc((self.rows_total, d_model), torch.bfloat16) for _ in range(n_layers)]
+        self.ret_y = [h.alloc((tokens * top_k, d_model), torch.bfloat16) for _ in range(n_layers)]
+        self.recv_g = h.alloc((self.rows_total, d_model), torch.bfloat16)
+        self.ret_g = h.alloc((tokens * top_k, d_model), torch.bfloat16)
+        self.row_dst = h.alloc((self.rows_total,), torch.int64)
+        self.mblk_rows = h.alloc((self.blocks,), torch.int32)
+        self.src_blocks = h.alloc((self.N,), torch.int32)
+        self.dispatch_flags = h.alloc((self.N,), torch.int32)
+        self.combine_flags = h.alloc((self.N,), torch.int32)
+        # peer pointer tables
+        self.p_recv_x = [h.ptr_array(t) for t in self.recv_x]
+        self.p_ret_y = [h.ptr_array(t) for t in self.ret_y]
+        self.p_recv_g, self.p_ret_g = h.ptr_array(self.recv_g), h.ptr_array(self.ret_g)
+        self.p_row_dst, self.p_mblk_rows = h.ptr_array(self.row_dst), h.ptr_array(self.mblk_rows)
+        self.p_src_blocks = h.ptr_array(self.src_blocks)
+        self.p_dispatch_flags = h.ptr_array(self.dispatch_flags)
+        # the flag a peer releases when all rows destined to rank s are stored: combine_flags[self.rank] on s
+        self.p_done_flag = torch.tensor([h.peer_ptr(self.combine_flags, s) + 4 * self.rank for s in range(self.N)],
+                                        dtype=torch.int64, device=self.device)
+        # static per-block tables: group (local expert) and flag index (source rank)
+        blk = torch.arange(self.blocks, device=self.device)
+        self.mblk_group = (blk // (self.N * self.bpr)).to(torch.int32)
+        self.mblk_flag = ((blk // self.bpr) % self.N).to(torch.int32)
+        self.done_counters = torch.zeros(self.N, device=self.device, dtype=torch.int32)
+        self.dispatch_ctr = torch.zeros(1, device=self.device, dtype=torch.int32)
+        self.epoch = 0
+        self.layer_of: dict[int, int] = {}
+        self.max_ctas_dispatch = max_ctas_dispatch
+        if self.N > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
+
+    def layer_index(self, module) -> int:
+        k = id(module)
+        if k not in self.layer_of:
+            self.layer_of[k] = len(self.layer_of)
+            assert self.layer_of[k] < self.L, "more MoE layers than the runtime was sized for"
+        return self.layer_of[k]
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    # -- kernels -------------------------------------------------------------------------------------
+    def dispatch(self, x2, indices, slot_pos, counts_kept, scale, p_rows, epoch):
+        a = _lib.DispatchArgs()
+        a.x, a.indices, a.slot_pos, a.counts_kept = x2.data_ptr(), indices.data_ptr(), slot_pos.data_ptr(), \
+            counts_kept.data_ptr()
+        a.slot_scale = scale.data_ptr() if scale is not None else None
+        a.T, a.K, a.D, a.E, a.E_local, a.n_ranks, a.my_rank = self.T, self.K, self.D, self.E, self.E_local, self.N, \
+            self.rank
+        a.region_rows, a.quant = self.R, 0
+        a.peer_rows, a.peer_scales = p_rows.data_ptr(), None
+        a.peer_row_dst, a.peer_mblk_rows = self.p_row_dst.data_ptr(), self.p_mblk_rows.data_ptr()
+        a.peer_src_blocks, a.peer_flags = self.p_src_blocks.data_ptr(), self.p_dispatch_flags.data_ptr()
+        a.done_ctr, a.epoch, a.write_meta, a.max_ctas = self.dispatch_ctr.data_ptr(), epoch, 1, self.max_ctas_dispatch
+        _lib.check(_lib.lib().np_ep_dispatch(C.byref(a), C.c_void_p(_lib.stream())), "ep_dispatch")
+
+    def combine(self, rows, slot_pos, weights, out, sent_to_peer, epoch, dl=None, wg=None, add1=None):
+        a = _lib.CombineArgs()
+        a.rows, a.slot_pos = rows.data_ptr(), slot_pos.data_ptr()
+        a.weights = weights.data_ptr() if weights is not None else None
+        a.add1 = add1.data_ptr() if add1 is not None else None
+        a.add2 = None
+        a.dl = dl.data_ptr() if dl is not None else None
+        a.wg = wg.data_ptr() if wg is not None else None
+        a.out = out.data_ptr()
+        a.T, a.K, a.D, a.E = self.T, self.K, self.D, self.E
+        a.flags, a.sent_to_peer = self.combine_flags.data_ptr(), sent_to_peer.data_ptr()
+        a.n_ranks, a.epoch, a.limit_ns = self.N, epoch, WAIT_LIMIT_NS
+        _lib.check(_lib.lib().np_ep_combine(C.byref(a), C.c_void_p(_lib.stream())), "ep_combine")
+
+    def grouped_gemm(self, A, B, *, N, K, b_mn, group_stride_b, out=None, B2=None, C2=None, wait_epoch=0,
+                     push_ptrs=None, push_epoch=0, Cin=None, out_dtype=torch.bfloat16):
+        """Row-grouped GEMM over the receive-buffer layout (mode 1)."""
+        g = _lib.GemmArgs()
+        M = self.rows_total
+        if out is None and push_ptrs is None:
+            out = torch.empty((M, N), device=A.device, dtype=out_dtype)
+        g.A, g.B = A.data_ptr(), B.data_ptr()
+        g.lda, g.ldb = A.stride(0), B.stride(0)
+        g.a_rows, g.b_rows = A.shape[0], B.shape[0]
+        g.M, g.N, g.K = M, N, K
+        g.a_mn, g.b_mn = 0, int(b_mn)
+        g.mode, g.alpha = 1, 1.0
+        g.mblk_group, g.mblk_rows = self.mblk_group.data_ptr(), self.mblk_rows.data_ptr()
+        g.group_stride_b = group_stride_b
+        g.mblk_flag = self.mblk_flag.data_ptr()
+        if B2 is not None:
+            g.B2, g.epilogue = B2.data_ptr(), 1
+            g.C2 = C2.data_ptr() if C2 is not None else None
+            g.ldc2 = C2.stride(0) if C2 is not None else 0
+        if wait_epoch:
+            g.ready_flags, g.epoch, g.flag_limit_ns = self.dispatch_flags.data_ptr(), wait_epoch, WAIT_LIMIT_NS
+        if push_ptrs is not None:
+            self.done_counters.zero_()
+            g.row_dst, g.peer_base = self.row_dst.data_ptr(), push_ptrs.data_ptr()
+            g.done_counters, g.done_expected = self.done_counters.data_ptr(), self.src_blocks.data_ptr()
+            g.done_flag_ptr, g.epoch = self.p_done_flag.data_ptr(), push_epoch
+            g.C, g.ldc = None, N
+            g.out_f32 = 0
+        else:
+            g.C, g.ldc = out.data_ptr(), out.stride(0)
+            g.out_f32 = int(out.dtype == torch.float32)
+        if Cin is not None:
+            g.Cin, g.ldcin = Cin.data_ptr(), Cin.stride(0)
+        _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "grouped_gemm")
+        return out
+
+    def grouped_wgrad(self, A, Bm, w: torch.Tensor, *, M, N):
+        """dW[g] (+)= A[rows of g]^T @ B[rows of g] for every local expert g (mode 2), into ``main_grad``
+        when the weight has one, else a fresh tensor that is returned."""
+        mg = getattr(w, "main_grad", None)
+        first = not getattr(w, "_main_grad_dirty", False)
+        out = mg if mg is not None else torch.empty((self.E_local * M, N), device=A.device, dtype=torch.float32)
+        g = _lib.GemmArgs()
+        g.A, g.B, g.C = A.data_ptr(), Bm.data_ptr(), out.data_ptr()
+        g.lda, g.ldb, g.ldc = A.stride(0), Bm.stride(0), N
+        g.a_rows, g.b_rows = A.shape[0], Bm.shape[0]
+        g.M, g.N, g.K = M, N, self.rows_total
+        g.a_mn, g.b_mn, g.mode, g.alpha = 1, 1, 2, 1.0
+        g.out_f32 = 1
+        g.accumulate = int(mg is not None and not first)
+        g.mblk_rows = self.mblk_rows.data_ptr()
+        g.num_groups, g.blocks_per_group, g.group_stride_c = self.E_local, self.N * self.bpr, M * N
+        _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "grouped_wgrad")
+        if mg is not None:
+            w._main_grad_dirty = True
+            return None
+        return out.to(w.dtype)
+
+
+# ------------------------------------------------------------------------------------------------ the layer
+class _FusedMoE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weights, indices32, w1, w3, w2, rt: FusedMoERuntime, layer: int, stats_mod):
+        T, D, K, H = rt.T, rt.D, rt.K, rt.H
+        dev = x.device
+        x2 = x.reshape(T, D)
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        slot_pos = torch.empty((T, K), device=dev, dtype=torch.int32)
+        keep = torch.empty(T, device=dev, dtype=torch.int32)
+        counts_kept = torch.empty(rt.E, device=dev, dtype=torch.int32)
+        drops = torch.empty(rt.E, device=dev, dtype=torch.int32)
+        n_dropped = torch.empty(1, device=dev, dtype=torch.int32)
+        _lib.call("capacity_scan", indices32, T, rt.E, K, rt.capacity, slot_pos, keep, counts_kept, drops, n_dropped)
+        sent = counts_kept.view(rt.N, rt.E_local).sum(1).to(torch.int32)
+        e1 = rt.next_epoch()
+        rt.dispatch(x2, indices32, slot_pos, counts_kept, None, rt.p_recv_x[layer], e1)
+        # experts: [gate|up] GEMM with SwiGLU epilogue, waits per block on the source's arrival flag
+        h = torch.empty((rt.rows_total, H), device=dev, dtype=torch.bfloat16)
+        gu = torch.empty((rt.rows_total, 2 * H), device=dev, dtype=torch.bfloat16)
+        rt.grouped_gemm(rt.recv_x[layer], w1, N=H, K=D, b_mn=False, group_stride_b=H, out=h, B2=w3, C2=gu,
+                        wait_epoch=e1)
+        # down projection (w2 is stored [H, D] per expert: MN-major B), rows pushed back to their sources
+        rt.grouped_gemm(h, w2, N=D, K=H, b_mn=True, group_stride_b=H, push_ptrs=rt.p_ret_y[layer], push_epoch=e1)
+        out = torch.empty((T, D), device=dev, dtype=torch.bfloat16)
+        rt.combine(rt.ret_y[layer], slot_pos, weights, out, sent, e1)
+        ctx.save_for_backward(x2, weights, indices32, slot_pos, counts_kept, sent, gu, w1, w3, w2)
+        ctx.rt, ctx.layer = rt, layer
+        ctx.x_shape = x.shape
+        if stats_mod is not None:
+            stats_mod._per_expert_drop_counts = drops
+            stats_mod._record_drops(n_dropped[0].long(), T, dev)
+        return out.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x2, weights, indices32, slot_pos, counts_kept, sent, gu, w1, w3, w2 = ctx.saved_tensors
+        rt, layer = ctx.rt, ctx.layer
+        T, D, K, H = rt.T, rt.D, rt.K, rt.H
+        dev = dout.device
+        do2 = dout.reshape(T, D)
+        do2 = do2 if do2.is_contiguous() else do2.contiguous()
+        # d(router weights)[t,k] = <dout[t], y[t,k]>
+        dweights = torch.empty((T, K), device=dev, dtype=torch.float32)
+        _lib.call("slot_dot", do2, rt.ret_y[layer], slot_pos, dweights, T, K, D)
+        # send w[t,k] * dout[t] to the experts (same slots as forward)
+        e2 = rt.next_epoch()
+        rt.dispatch(do2, indices32, slot_pos, counts_kept, weights, rt.p_recv_g, e2)
+        # dH = dY @ w2^T  (w2 [H, D] per expert is K-major for this contraction)
+        dh = rt.grouped_gemm(rt.recv_g, w2, N=H, K=D, b_mn=False, group_stride_b=H, wait_epoch=e2)
+        hh = glu(gu)  # recompute the activation from the saved pre-activations
+        dw2 = rt.grouped_wgrad(hh, rt.recv_g, w2, M=H, N=D)
+        del hh
+        dgu = glu_bwd(gu, dh)
+        del dh
+        dg, du = dgu[:, :H], dgu[:, H:]
+        xr = rt.recv_x[layer]
+        dw1 = rt.grouped_wgrad(dg, xr, w1, M=H, N=D)
+        dw3 = rt.grouped_wgrad(du, xr, w3, M=H, N=D)
+        # dX = dG @ w1 + dU @ w3, pushed back to the sources
+        part = rt.grouped_gemm(dg, w1, N=D, K=H, b_mn=True, group_stride_b=H)
+        rt.grouped_gemm(du, w3, N=D, K=H, b_mn=True, group_stride_b=H, push_ptrs=rt.p_ret_g, push_epoch=e2, Cin=part)
+        dx = torch.empty((T, D), device=dev, dtype=torch.bfloat16)
+        rt.combine(rt.ret_g, slot_pos, None, dx, sent, e2)
+        return dx.view(ctx.x_shape), dweights, None, dw1, dw3, dw2, None, None, None
+
+
+def build_runtime(moe_modules, *, tokens: int, group=None, device=None) -> FusedMoERuntime:
+    """One runtime for all MoE layers of a model (they must share geometry)."""
+    m0 = moe_modules[0]
+    rt = FusedMoERuntime(tokens=tokens, d_model=m0.d_model, hidden=m0.hidden_size, num_experts=m0.num_experts,
+                         top_k=m0.top_k, n_layers=len(moe_modules), capacity_factor=m0.capacity_factor, group=group,
+                         device=device)
+    for m in moe_modules:
+        m._fused_runtime = rt
+    return rt
+
+
+def fused_moe_forward(mod, x: torch.Tensor) -> torch.Tensor:
+    """Forward of ``MoEBase`` on the fused path (``x``: [B, S, D] bf16 on CUDA)."""
+    rt: FusedMoERuntime = mod._fused_runtime
+    B, S, D = x.shape
+    if B * S != rt.T or mod.capacity_factor is not None and int(mod.capacity_factor * B * S / mod.num_experts) != \
+            rt.capacity:
+        raise _lib.KernelError(f"fused MoE runtime was built for {rt.T} tokens / capacity {rt.capacity}; got "
+                               f"{B * S} tokens (rebuild the runtime or call the layer with a matching batch)")
+    w, idx, aux, counts = route(x, mod.router)
+    mod.router.last_counts = counts
+    if mod.router.score_bias is not None:
+        mod.router._update_expert_counts(idx, counts)
+    mod._aux_loss = aux
+    layer = rt.layer_index(mod)
+    return _FusedMoE.apply(x, w.reshape(B * S, -1), idx.reshape(B * S, -1).to(torch.int32), mod.w1, mod.w3, mod.w2, rt,
+                           layer, mod)

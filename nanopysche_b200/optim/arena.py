@@ -1,0 +1,346 @@
+"""Flat parameter arena and the fused AdamW that runs on it.
+
+All parameters of a model are re-pointed into a few flat buffers ("regions": bf16 replicated, bf16
+expert-sharded, fp32), each with a flat fp32 gradient buffer (``param.main_grad`` views) and flat
+fp32 master / moment buffers. That layout is what the B200 kernels want:
+
+* adjacent weights become one GEMM operand without a copy (``[w_q|w_k|w_v]``, ``[w1;w3]``);
+* wgrad GEMMs accumulate straight from TMEM into ``main_grad`` (no autograd ``.grad`` tensors);
+* the optimizer is one launch per region, reading the gradient once and writing the bf16 weights in
+  the same pass; gradient clipping uses device-side partial sums, no host synchronisation;
+* with data parallelism the replicated bf16 region lives in symmetric memory and the step becomes
+  reduce-scatter (peer loads) -> AdamW on the owned shard -> all-gather (peer stores), two launches
+  (``csrc/comm.cu``), with optimizer state sharded over the ranks (ZeRO-2 layout).
+
+The reference uses ``torch.optim.AdamW`` on autocast fp32 weights (cli.py:356-361) or its per-tensor
+Python loop (optim/adamw.py:74-121), FSDP2 for sharding and ``clip_grad_norm_`` (trainer.py:280-284).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops import _lib
+from .adamw import is_no_decay
+
+ALIGN = 64  # elements; keeps every view 128-byte aligned
+
+
+@dataclass
+class _Region:
+    name: str
+    dtype: torch.dtype
+    decay: bool
+    replicated: bool            # True: identical on all data-parallel ranks (needs gradient sync)
+    params: List[nn.Parameter] = field(default_factory=list)
+    names: List[str] = field(default_factory=list)
+    offsets: List[int] = field(default_factory=list)
+    numel: int = 0
+    weights: Optional[torch.Tensor] = None   # flat, region dtype
+    grads: Optional[torch.Tensor] = None     # flat fp32
+    master: Optional[torch.Tensor] = None    # flat fp32 (shard under ZeRO); None for fp32 regions
+    m: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None
+    lo: int = 0                              # owned shard [lo, lo+cnt) under ZeRO
+    cnt: int = 0
+    gshard: Optional[torch.Tensor] = None
+
+
+class ParamArena:
+    def __init__(self, model: nn.Module, *, dp_group=None, device=None, use_symmetric: Optional[bool] = None):
+        params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        assert params, "model has no trainable parameters"
+        self.model = model
+        self.device = device or params[0][1].device
+        self.dp_group = dp_group
+        self.world = dist.get_world_size(dp_group) if (dp_group is not None and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(dp_group) if self.world > 1 else 0
+        cuda = self.device.type == "cuda"
+        self.zero = self.world > 1 and cuda if use_symmetric is None else bool(use_symmetric)
+        self.regions: Dict[str, _Region] = {}
+        seen = set()
+        for n, p in params:
+            if id(p) in seen:
+                continue
+            seen.add(id(p))
+            sharded = bool(getattr(p, "_ep_sharded", False))
+            decay = not is_no_decay(n, p)
+            key = f"{str(p.dtype).split('.')[-1]}_{'local' if sharded else 'repl'}_{'decay' if decay else 'nodecay'}"
+            r = self.regions.setdefault(key, _Region(key, p.dtype, decay, not sharded))
+            off = (r.numel + ALIGN - 1) // ALIGN * ALIGN if not self._adjacent_ok(r, p) else r.numel
+            r.params.append(p)
+            r.names.append(n)
+            r.offsets.append(off)
+            r.numel = off + p.numel()
+        self.heap = None
+        if self.zero:
+            from ..parallel.symm import SymmetricHeap
+
+            need = 0
+            for r in self.regions.values():
+                if r.replicated and r.dtype == torch.bfloat16:
+                    pad = self._padded(r.numel)
+                    need += pad * 2 + pad * 4 + 8192
+            self.heap = SymmetricHeap(need + (1 << 20), dp_group, self.device)
+        self.fused: List[torch.Tensor] = []
+        for r in self.regions.values():
+            self._materialise(r)
+        self._install_hooks()
+        self._fuse_views()
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def _adjacent_ok(r: _Region, p) -> bool:
+        # sizes that are multiples of ALIGN keep alignment without padding, so neighbours stay adjacent
+        return r.numel % ALIGN == 0
+
+    def _padded(self, n: int) -> int:
+        q = 4 * self.world * ALIGN
+        return (n + q - 1) // q * q
+
+    def _materialise(self, r: _Region):
+        dev = self.device
+        symm = self.zero and r.replicated and r.dtype == torch.bfloat16
+        total = self._padded(r.numel) if symm else (r.numel + 3) // 4 * 4
+        if symm:
+            r.weights = self.heap.alloc((total,), r.dtype)
+            r.grads = self.heap.alloc((total,), torch.float32)
+            r.cnt = total // self.world
+            r.lo = self.rank * r.cnt
+        else:
+            r.weights = torch.zeros(total, device=dev, dtype=r.dtype)
+            r.grads = torch.zeros(total, device=dev, dtype=torch.float32)
+            r.lo, r.cnt = 0, total
+        with torch.no_grad():
+            for p, off in zip(r.params, r.offsets):
+                view = r.weights[off:off + p.numel()].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+                p.main_grad = r.grads[off:off + p.numel()].view(p.shape)
+                p._main_grad_dirty = False
+        if r.dtype != torch.float32:
+            r.master = r.weights[r.lo:r.lo + r.cnt].float()
+        r.m = torch.zeros(r.cnt, device=dev, dtype=torch.float32)
+        r.v = torch.zeros(r.cnt, device=dev, dtype=torch.float32)
+        if symm:
+            r.gshard = torch.empty(r.cnt, device=dev, dtype=torch.float32)
+
+    def _install_hooks(self):
+        def hook(p):
+            if p.grad is None:
+                return
+            if getattr(p, "_main_grad_dirty", False):
+                p.main_grad.add_(p.grad)
+            else:
+                p.main_grad.copy_(p.grad)
+                p._main_grad_dirty = True
+            p.grad = None
+
+        for r in self.regions.values():
+            for p in r.params:
+                p.register_post_accumulate_grad_hook(hook)
+
+    def _region_of(self, p) -> Optional[tuple]:
+        for r in self.regions.values():
+            for q, off in zip(r.params, r.offsets):
+                if q is p:
+                    return r, off
+        return None
+
+    def _fused_view(self, plist) -> Optional[torch.Tensor]:
+        """One [sum rows, cols] view over parameters that sit back to back in a region."""
+        loc = [self._region_of(p) for p in plist]
+        if any(l is None for l in loc) or len({id(l[0]) for l in loc}) != 1:
+            return None
+        r = loc[0][0]
+        off0, cols, end = loc[0][1], plist[0].shape[1], loc[0][1]
+        for p, (_, off) in zip(plist, loc):
+            if off != end or p.dim() != 2 or p.shape[1] != cols:
+                return None
+            end = off + p.numel()
+        rows = sum(p.shape[0] for p in plist)
+        w = r.weights[off0:end].view(rows, cols)
+        w.main_grad = r.grads[off0:end].view(rows, cols)
+        w._main_grad_dirty = False
+        w._covers = list(plist)
+        self.fused.append(w)
+        return w
+
+    def _fuse_views(self):
+        from ..models.attention import Attention
+        from ..models.feed_forward import FeedForward
+
+        if self.device.type != "cuda":
+            return
+        for m in self.model.modules():
+            if isinstance(m, Attention) and m.w_q.bias is None and m.w_q.weight.dtype == torch.bfloat16:
+                m._fused_qkv = self._fused_view([m.w_q.weight, m.w_k.weight, m.w_v.weight])
+            elif isinstance(m, FeedForward) and m.w1.bias is None and m.w1.weight.dtype == torch.bfloat16:
+                m._fused_w13 = self._fused_view([m.w1.weight, m.w3.weight])
+
+    # ------------------------------------------------------------------ per-step helpers
+    def zero_grad(self):
+        """Marks every gradient buffer as "overwrite on first write"; nothing is memset."""
+        for r in self.regions.values():
+            for p in r.params:
+                p._main_grad_dirty = False
+                p.grad = None
+        for w in self.fused:
+            w._main_grad_dirty = False
+
+    def finalize_grads(self):
+        """Zero the gradient of any parameter that received none this step."""
+        for r in self.regions.values():
+            for p in r.params:
+                if not p._main_grad_dirty:
+                    p.main_grad.zero_()
+
+    def num_params(self) -> int:
+        return sum(p.numel() for r in self.regions.values() for p in r.params)
+
+    def named_main_grads(self):
+        for r in self.regions.values():
+            for n, p in zip(r.names, r.params):
+                yield n, p.main_grad
+
+
+class ArenaAdamW(torch.optim.Optimizer):
+    """AdamW over a ``ParamArena`` (one fused launch per region; ZeRO kernels under data parallelism).
+
+    ``grad_divisor`` divides every gradient before clipping (number of data-parallel ranks times
+    gradient-accumulation steps when the per-rank loss is already a mean)."""
+
+    def __init__(self, arena: ParamArena, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
+                 weight_decay: float = 0.1, max_grad_norm: Optional[float] = 1.0, grad_divisor: float = 1.0):
+        self.arena = arena
+        allp = [p for r in arena.regions.values() for p in r.params]
+        super().__init__([{"params": allp}], dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self.max_grad_norm = max_grad_norm
+        self.grad_divisor = grad_divisor
+        self.step_count = 0
+        dev = arena.device
+        self._cuda = dev.type == "cuda"
+        nreg = len(arena.regions)
+        if self._cuda:
+            self._parts = _lib.lib().np_sumsq_parts()
+            zp = _lib.lib().np_zero_parts()
+            self._partial = torch.zeros(nreg * max(self._parts, zp), device=dev, dtype=torch.float32)
+        self._coef = torch.ones(2, device=dev, dtype=torch.float32)   # [clip coefficient, grad norm]
+        self._coef_local = torch.ones(1, device=dev, dtype=torch.float32)
+        self.last_grad_norm: Optional[torch.Tensor] = None
+
+    def zero_grad(self, set_to_none: bool = True):
+        self.arena.zero_grad()
+
+    # ------------------------------------------------------------------ step
+    @torch.no_grad()
+    def step(self, closure=None):
+        a = self.arena
+        a.finalize_grads()
+        self.step_count += 1
+        g = self.param_groups[0]
+        lr, (b1, b2), eps, wd = g["lr"], g["betas"], g["eps"], g["weight_decay"]
+        if not self._cuda:
+            return self._step_reference(lr, b1, b2, eps, wd)
+        N = a.world
+        inv = 1.0 / (self.grad_divisor * (N if N > 1 else 1))
+        stride = self._partial.numel() // len(a.regions)
+        self._partial.zero_()
+        if a.zero:
+            a.heap.barrier()  # every rank's backward has finished writing its gradient buffers
+        extra = None
+        for i, r in enumerate(a.regions.values()):
+            part = self._partial[i * stride:(i + 1) * stride]
+            if a.zero and r.replicated and r.dtype == torch.bfloat16:
+                ptrs = a.heap.host_ptr_array(r.grads)
+                _lib.check(_lib.lib().np_zero_reduce(ptrs, N, C.c_longlong(r.lo), C.c_longlong(r.cnt),
+                                                     C.c_float(inv), C.c_void_p(r.gshard.data_ptr()),
+                                                     C.c_void_p(part.data_ptr()), C.c_void_p(_lib.stream())),
+                           "zero_reduce")
+            else:
+                if N > 1 and r.replicated:  # small fp32 region: plain all-reduce
+                    dist.all_reduce(r.grads, group=a.dp_group)
+                _lib.call("sumsq", r.grads, _lib.LL(r.grads.numel()), part)
+                # scale of these gradients relative to the final ones: inv; replicated ones are counted
+                # once per rank in the global sum below
+                s = inv * inv / (N if (N > 1 and r.replicated) else 1)
+                part.mul_(s)
+        if N > 1:
+            tot = self._partial.sum().reshape(1)
+            dist.all_reduce(tot, group=a.dp_group)
+            self._partial.zero_()
+            self._partial[0] = tot[0]
+        _lib.call("clip_coef", self._partial, self._partial.numel(), extra,
+                  float(self.max_grad_norm or 0.0), self._coef)
+        self.last_grad_norm = self._coef[1]
+        torch.mul(self._coef[:1], inv, out=self._coef_local)  # coefficient for gradients not yet divided
+        for r in a.regions.values():
+            wdr = wd if r.decay else 0.0
+            if a.zero and r.replicated and r.dtype == torch.bfloat16:
+                ptrs = a.heap.host_ptr_array(r.weights)
+                _lib.check(_lib.lib().np_zero_adamw_bcast(
+                    C.c_void_p(r.master.data_ptr()), C.c_void_p(r.gshard.data_ptr()), C.c_void_p(r.m.data_ptr()),
+                    C.c_void_p(r.v.data_ptr()), ptrs, N, C.c_longlong(r.lo), C.c_longlong(r.cnt), C.c_float(lr),
+                    C.c_float(b1), C.c_float(b2), C.c_float(eps), C.c_float(wdr), self.step_count,
+                    C.c_void_p(self._coef.data_ptr()), C.c_void_p(_lib.stream())), "zero_adamw_bcast")
+            elif r.dtype == torch.float32:
+                _lib.call("adamw", r.weights, r.grads, r.m, r.v, None, _lib.LL(r.weights.numel()), float(lr),
+                          float(b1), float(b2), float(eps), float(wdr), self.step_count, self._coef_local)
+            else:
+                _lib.call("adamw", r.master, r.grads, r.m, r.v, r.weights, _lib.LL(r.weights.numel()), float(lr),
+                          float(b1), float(b2), float(eps), float(wdr), self.step_count, self._coef_local)
+        if a.zero:
+            a.heap.barrier()  # all ranks' weight stores have landed before the next forward reads them
+        return None
+
+    def _step_reference(self, lr, b1, b2, eps, wd):
+        """CPU path: same math with torch ops (also the oracle of the kernels)."""
+        a = self.arena
+        N = a.world
+        inv = 1.0 / (self.grad_divisor * (N if N > 1 else 1))
+        sq = torch.zeros((), dtype=torch.float32, device=a.device)
+        for r in a.regions.values():
+            if N > 1 and r.replicated:
+                dist.all_reduce(r.grads, group=a.dp_group)
+            s = (r.grads.float() * inv).pow(2).sum()
+            sq += s / (N if (N > 1 and r.replicated) else 1)
+        if N > 1:
+            dist.all_reduce(sq, group=a.dp_group)
+        norm = sq.sqrt()
+        coef = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0) if self.max_grad_norm else torch.ones(())
+        self.last_grad_norm = norm
+        t = self.step_count
+        for r in a.regions.values():
+            gsc = r.grads * (inv * coef)
+            tgt = r.master if r.master is not None else r.weights
+            r.m.mul_(b1).add_(gsc, alpha=1 - b1)
+            r.v.mul_(b2).addcmul_(gsc, gsc, value=1 - b2)
+            tgt.mul_(1 - lr * (wd if r.decay else 0.0))
+            tgt.addcdiv_(r.m / (1 - b1 ** t), (r.v / (1 - b2 ** t)).sqrt() + eps, value=-lr)
+            if r.master is not None:
+                r.weights.copy_(r.master)
+        return None
+
+    # ------------------------------------------------------------------ (de)serialisation
+    def state_dict(self):
+        a = self.arena
+        return {"step": self.step_count, "param_groups": [{k: v for k, v in g.items() if k != "params"}
+                                                          for g in self.param_groups],
+                "regions": {k: {"master": r.master, "m": r.m, "v": r.v, "lo": r.lo, "cnt": r.cnt}
+                            for k, r in a.regions.items()}}
+
+    def load_state_dict(self, sd):
+        self.step_count = sd["step"]
+        for g, s in zip(self.param_groups, sd["param_groups"]):
+            g.update(s)
+        for k, st in sd["regions"].items():
+            r = self.arena.regions[k]
+            for name in ("master", "m", "v"):
+                if st[name] is not None and getattr(r, name) is not None:
+                    getattr(r, name).copy_(st[name])

@@ -1,0 +1,355 @@
+"""Pipeline schedule generators: GPipe, 1F1B, Zero-Bubble and DualPipe
+(reference: distributed/pipeline_parallel.py:44-472).
+
+Every generator returns per-rank action lists and every list is checked by ``validate_schedule``,
+a dependency simulator (F needs the previous stage's F, B needs this stage's F and the next stage's
+B, W needs this stage's B). The simulator also measures the bubble, so the closed-form
+``compute_bubble_fraction`` can be compared with what a schedule really does. The reference's
+DualPipe generator emits duplicate forwards and its Zero-Bubble has no separate weight-gradient
+action; here B (input gradient) and W (weight gradient) are distinct action types and DualPipe is a
+true two-direction schedule (rank r runs stage r of direction 0 and stage p-1-r of direction 1).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from enum import Enum
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+
+class ScheduleType(str, Enum):
+    FWD = "fwd"
+    BWD = "bwd"          # full backward (input + weight gradients)
+    BWD_INPUT = "bwd_b"  # zero-bubble "B": input gradients only
+    BWD_WEIGHT = "bwd_w"  # zero-bubble "W": weight gradients only
+    IDLE = "idle"
+
+
+@dataclass(frozen=True)
+class Action:
+    type: ScheduleType
+    microbatch: int = -1
+    stage: int = -1
+
+    def __repr__(self):
+        tag = {"fwd": "F", "bwd": "B", "bwd_b": "Bi", "bwd_w": "W", "idle": "-"}[self.type.value]
+        return f"{tag}{self.microbatch}@{self.stage}" if self.type != ScheduleType.IDLE else "-"
+
+
+@dataclass
+class PipelineParallelConfig:
+    degree: int = 1
+    schedule: str = "1f1b"
+    num_microbatches: Optional[int] = None
+
+
+class PipelineStage(nn.Module):
+    """A contiguous slice of layers with p2p helpers (reference: distributed/pipeline_parallel.py:71-149).
+    Sends/receives are non-blocking ``batch_isend_irecv`` pairs on the PP group."""
+
+    def __init__(self, layers: nn.Module, stage_id: int, num_stages: int, group=None):
+        super().__init__()
+        self.layers = layers
+        self.stage_id, self.num_stages, self.group = stage_id, num_stages, group
+
+    @property
+    def is_first(self) -> bool:
+        return self.stage_id == 0
+
+    @property
+    def is_last(self) -> bool:
+        return self.stage_id == self.num_stages - 1
+
+    def forward_chunk(self, x, **kw):
+        if isinstance(self.layers, (nn.ModuleList, nn.Sequential)):
+            for l in self.layers:
+                x = l(x, **kw) if kw else l(x)
+            return x
+        return self.layers(x, **kw)
+
+    forward = forward_chunk
+
+    def _peer(self, delta: int) -> int:
+        r = dist.get_rank(self.group)
+        n = dist.get_world_size(self.group)
+        return dist.get_global_rank(self.group, (r + delta) % n) if self.group is not None else (r + delta) % n
+
+    def send_forward(self, t):
+        return dist.batch_isend_irecv([dist.P2POp(dist.isend, t.contiguous(), self._peer(+1), group=self.group)])
+
+    def recv_forward(self, buf):
+        return dist.batch_isend_irecv([dist.P2POp(dist.irecv, buf, self._peer(-1), group=self.group)])
+
+    def send_backward(self, t):
+        return dist.batch_isend_irecv([dist.P2POp(dist.isend, t.contiguous(), self._peer(-1), group=self.group)])
+
+    def recv_backward(self, buf):
+        return dist.batch_isend_irecv([dist.P2POp(dist.irecv, buf, self._peer(+1), group=self.group)])
+
+
+# ------------------------------------------------------------------ generators
+F, B, BI, W = ScheduleType.FWD, ScheduleType.BWD, ScheduleType.BWD_INPUT, ScheduleType.BWD_WEIGHT
+
+
+class _Schedule:
+    def __init__(self, num_stages: int, num_microbatches: int):
+        self.num_stages = num_stages
+        self.num_microbatches = num_microbatches
+
+    def generate_schedule(self) -> List[List[Action]]:
+        raise NotImplementedError
+
+    def rank_of_stage(self, stage: int) -> int:
+        return stage
+
+    def stages_of_rank(self, rank: int) -> List[int]:
+        return [rank]
+
+
+class GPipeSchedule(_Schedule):
+    def generate_schedule(self):
+        p, m = self.num_stages, self.num_microbatches
+        return [[Action(F, i, r) for i in range(m)] + [Action(B, i, r) for i in reversed(range(m))]
+                for r in range(p)]
+
+
+class OneForwardOneBackwardSchedule(_Schedule):
+    def generate_schedule(self):
+        p, m = self.num_stages, self.num_microbatches
+        out = []
+        for r in range(p):
+            warm = min(p - 1 - r, m)
+            acts = [Action(F, i, r) for i in range(warm)]
+            f, b = warm, 0
+            while b < m:
+                if f < m:
+                    acts.append(Action(F, f, r))
+                    f += 1
+                acts.append(Action(B, b, r))
+                b += 1
+            out.append(acts)
+        return out
+
+
+def _greedy(p: int, work: Dict[int, List[List[Action]]], stage_rank, last_stage_of, first_stage_of,
+            split_w: bool, costs=None) -> List[List[Action]]:
+    """List-scheduling simulator shared by Zero-Bubble and DualPipe: every rank holds one ordered
+    queue per (direction) of F and B actions; at each tick a rank runs the first *ready* action by
+    priority B > F (alternating directions), and fills idle ticks with pending W."""
+    done: set = set()
+    pending_w: List[List[Action]] = [[] for _ in range(p)]
+    out: List[List[Action]] = [[] for _ in range(p)]
+    queues = {r: [list(q) for q in work[r]] for r in range(p)}
+    turn = [0] * p
+
+    def ready(a: Action) -> bool:
+        if a.type == F:
+            return a.stage == first_stage_of(a) or ("F", a.microbatch, a.stage - 1) in done
+        nxt_ok = a.stage == last_stage_of(a) or ("B", a.microbatch, a.stage + 1) in done
+        return ("F", a.microbatch, a.stage) in done and nxt_ok
+
+    total = sum(len(q) for r in range(p) for q in queues[r])
+    guard = 0
+    while total > 0:
+        guard += 1
+        if guard > 100000:
+            raise RuntimeError("schedule generation did not converge")
+        fired = []
+        for r in range(p):
+            cands = []
+            for qi, q in enumerate(queues[r]):
+                if q and ready(q[0]):
+                    cands.append((0 if q[0].type != F else 1, (qi - turn[r]) % max(len(queues[r]), 1), qi))
+            if cands:
+                _, _, qi = min(cands)
+                a = queues[r][qi].pop(0)
+                turn[r] = (qi + 1) % len(queues[r])
+                fired.append((r, a))
+            elif pending_w[r]:
+                out[r].append(pending_w[r].pop(0))
+        for r, a in fired:
+            if a.type == F:
+                out[r].append(a)
+            else:
+                out[r].append(Action(BI if split_w else B, a.microbatch, a.stage))
+                if split_w:
+                    pending_w[r].append(Action(W, a.microbatch, a.stage))
+            total -= 1
+        for r, a in fired:  # results become visible to other ranks on the next tick
+            done.add(("F" if a.type == F else "B", a.microbatch, a.stage))
+    for r in range(p):
+        out[r] += pending_w[r]
+    return out
+
+
+def _one_f_one_b_queue(stage: int, pos: int, depth: int, mbs: List[int]) -> List[Action]:
+    """1F1B order of one stage that sits at position ``pos`` of a ``depth``-stage pipeline."""
+    warm = min(depth - 1 - pos, len(mbs))
+    acts = [Action(F, mb, stage) for mb in mbs[:warm]]
+    f, b = warm, 0
+    while b < len(mbs):
+        if f < len(mbs):
+            acts.append(Action(F, mbs[f], stage))
+            f += 1
+        acts.append(Action(B, mbs[b], stage))
+        b += 1
+    return acts
+
+
+class InterleavedSchedule(_Schedule):
+    """``v`` model chunks per rank. ``placement="loop"``: stage s lives on rank ``s % p`` (interleaved
+    1F1B / looped BFS); ``"v"``: the second half of the stages runs back down the ranks (ZB-V). With
+    ``split_w`` the backward is split into B and W and W fills idle slots."""
+
+    def __init__(self, num_ranks: int, num_microbatches: int, v: int = 2, placement: str = "loop",
+                 split_w: bool = False):
+        super().__init__(num_ranks, num_microbatches)
+        self.v, self.placement, self.split_w = v, placement, split_w
+        self.total_stages = v * num_ranks
+
+    def rank_of_stage(self, stage: int) -> int:
+        p = self.num_stages
+        if self.placement == "v":
+            c, r = divmod(stage, p)
+            return r if c % 2 == 0 else p - 1 - r
+        return stage % p
+
+    def stages_of_rank(self, rank: int) -> List[int]:
+        return [s for s in range(self.total_stages) if self.rank_of_stage(s) == rank]
+
+    def generate_schedule(self):
+        p, m, S = self.num_stages, self.num_microbatches, self.total_stages
+        mbs = list(range(m))
+        work = {r: [_one_f_one_b_queue(s, s, S, mbs) for s in self.stages_of_rank(r)] for r in range(p)}
+        return _greedy(p, work, self.rank_of_stage, lambda a: S - 1, lambda a: 0, split_w=self.split_w)
+
+
+class ZeroBubbleSchedule(_Schedule):
+    """ZB-H1 style: 1F1B order with the backward split into B and W; W fills what would be bubbles."""
+
+    def generate_schedule(self):
+        p, m = self.num_stages, self.num_microbatches
+        base = OneForwardOneBackwardSchedule(p, m).generate_schedule()
+        work = {r: [base[r]] for r in range(p)}
+        return _greedy(p, work, lambda s: s, lambda a: p - 1, lambda a: 0, split_w=True)
+
+
+class DualPipeSchedule(_Schedule):
+    """Two pipelines in opposite directions over the same ranks. Stage ids ``0..p-1`` are direction
+    0 (stage s on rank s), ``p..2p-1`` direction 1 (stage p+s on rank p-1-s); even microbatches go
+    down direction 0, odd ones direction 1. ``stages_forward`` / ``stages_reverse`` are accepted for
+    signature parity with the reference and only their length is used."""
+
+    def __init__(self, stages_forward=None, stages_reverse=None, num_microbatches: int = 8,
+                 num_stages: Optional[int] = None, split_w: bool = True):
+        p = num_stages or (len(stages_forward) if stages_forward is not None else 2)
+        super().__init__(p, num_microbatches)
+        self.split_w = split_w
+
+    def rank_of_stage(self, stage: int) -> int:
+        p = self.num_stages
+        return stage if stage < p else p - 1 - (stage - p)
+
+    def stages_of_rank(self, rank: int) -> List[int]:
+        p = self.num_stages
+        return [rank, p + (p - 1 - rank)]
+
+    def generate_schedule(self):
+        p, m = self.num_stages, self.num_microbatches
+        work: Dict[int, List[List[Action]]] = {}
+        for r in range(p):
+            qs = []
+            for d in (0, 1):
+                mbs = [i for i in range(m) if i % 2 == d]
+                stage = r if d == 0 else p + (p - 1 - r)
+                pos = stage - d * p
+                warm = min(p - 1 - pos, len(mbs))
+                acts = [Action(F, mb, stage) for mb in mbs[:warm]]
+                f, b = warm, 0
+                while b < len(mbs):
+                    if f < len(mbs):
+                        acts.append(Action(F, mbs[f], stage))
+                        f += 1
+                    acts.append(Action(B, mbs[b], stage))
+                    b += 1
+                qs.append(acts)
+            work[r] = qs
+        last = lambda a: (p - 1) if a.stage < p else (2 * p - 1)  # noqa: E731
+        first = lambda a: 0 if a.stage < p else p  # noqa: E731
+        return _greedy(p, work, self.rank_of_stage, last, first, split_w=self.split_w)
+
+
+# ------------------------------------------------------------------ validation / bubble
+def validate_schedule(per_rank: List[List[Action]], num_stages: int, num_microbatches: int,
+                      stage_first=None, stage_last=None, mb_stages=None, costs=None) -> dict:
+    """Simulate the schedule; raises ``ValueError`` on a missing/duplicate action or a deadlock.
+    Returns ``{"makespan", "busy", "bubble_fraction"}`` with unit (or given) costs per action type."""
+    costs = costs or {F: 1.0, B: 2.0, BI: 1.0, W: 1.0}
+    stage_first = stage_first or (lambda s: 0)
+    stage_last = stage_last or (lambda s: num_stages - 1)
+    seen = set()
+    for r, acts in enumerate(per_rank):
+        for a in acts:
+            if a.type == ScheduleType.IDLE:
+                continue
+            key = (a.type, a.microbatch, a.stage)
+            if key in seen:
+                raise ValueError(f"duplicate action {a} on rank {r}")
+            seen.add(key)
+    finish: Dict[tuple, float] = {}
+    ptr = [0] * len(per_rank)
+    clock = [0.0] * len(per_rank)
+    busy = [0.0] * len(per_rank)
+    remaining = sum(1 for acts in per_rank for a in acts if a.type != ScheduleType.IDLE)
+    while remaining:
+        progressed = False
+        for r, acts in enumerate(per_rank):
+            while ptr[r] < len(acts) and acts[ptr[r]].type == ScheduleType.IDLE:
+                ptr[r] += 1
+            if ptr[r] >= len(acts):
+                continue
+            a = acts[ptr[r]]
+            deps = []
+            if a.type == F:
+                if a.stage != stage_first(a.stage):
+                    deps.append(("F", a.microbatch, a.stage - 1))
+            elif a.type in (B, BI):
+                deps.append(("F", a.microbatch, a.stage))
+                if a.stage != stage_last(a.stage):
+                    deps.append(("B", a.microbatch, a.stage + 1))
+            else:
+                deps.append(("B", a.microbatch, a.stage))
+            if all(d in finish for d in deps):
+                start = max([clock[r]] + [finish[d] for d in deps])
+                end = start + costs[a.type]
+                kind = "F" if a.type == F else ("W" if a.type == W else "B")
+                finish[(kind, a.microbatch, a.stage)] = end
+                clock[r] = end
+                busy[r] += costs[a.type]
+                ptr[r] += 1
+                remaining -= 1
+                progressed = True
+        if not progressed:
+            raise ValueError("schedule deadlocks: no rank can make progress")
+    makespan = max(clock)
+    return {"makespan": makespan, "busy": busy,
+            "bubble_fraction": 1.0 - sum(busy) / (makespan * len(per_rank)) if makespan > 0 else 0.0}
+
+
+def compute_bubble_fraction(schedule_type: str, p: int, m: int, v: int = 1) -> float:
+    """Closed-form bubble fractions (reference: distributed/pipeline_parallel.py:449-472)."""
+    s = str(getattr(schedule_type, "value", schedule_type)).lower()
+    if s in ("gpipe", "1f1b", "onef_oneb"):
+        return (p - 1) / m
+    if s in ("interleaved", "interleaved1f1b", "interleaved_1f1b", "loopedbfs", "looped_bfs"):
+        return (p - 1) / (v * m)
+    if s in ("dualpipe", "dual_pipe"):
+        return max(p // 2 - 1, 0) / m
+    if s in ("zb1p", "zero_bubble", "zerobubble", "zb-1p", "interleavedzerobubble"):
+        return (p - 1) / (3 * (m + p - 1))
+    if s in ("zb2p", "zbv", "zb-v", "zbvzerobubble", "zb-2p"):
+        return 0.0
+    raise ValueError(f"unknown schedule type {schedule_type}")

@@ -1,0 +1,124 @@
+"""Symmetric device memory shared by the ranks of one node.
+
+Each rank allocates one arena (``cudaMalloc``), exports its CUDA IPC handle, and opens every other
+rank's; tensors carved out of the arena have the same offset on every rank, so a kernel addresses
+"buffer X on rank r" as ``peer_base[r] + offset``. ``torch.distributed`` is used only to exchange
+the 64-byte handles. A single-rank heap needs no IPC and uses ordinary torch memory.
+
+Kernels signal through epoch flags (monotone counters) that live in the arena; every wait on a
+flag is bounded and reports through the library's status word instead of hanging.
+
+The reference has no counterpart: its collectives are NCCL calls (model/moe.py:396-497,
+model/tp_utils.py:38); this heap is what lets dispatch, combine, reduce-scatter and all-gather run
+inside the compute kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+
+def available() -> bool:
+    return torch.cuda.is_available()
+
+
+class _RawCuda:
+    """Array-interface view of raw device memory so torch can wrap it without a copy."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class SymmetricHeap:
+    def __init__(self, nbytes: int, group=None, device: Optional[torch.device] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if (group is not None or dist.is_initialized()) and \
+            dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.nbytes = int(math.ceil(nbytes / 4096) * 4096)
+        self._offset = 0
+        self._ipc = self.world > 1
+        if not self._ipc:
+            self._base_tensor = torch.zeros(self.nbytes, dtype=torch.uint8, device=self.device)
+            self.local_ptr = self._base_tensor.data_ptr()
+            self.peer_ptrs = [self.local_ptr]
+        else:
+            lib = _lib.lib()
+            ptr = C.c_void_p()
+            handle = (C.c_ubyte * 64)()
+            _lib.check(lib.np_symm_alloc(C.c_ulonglong(self.nbytes), C.byref(ptr), handle), "symm_alloc")
+            self.local_ptr = ptr.value
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            self.peer_ptrs = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self.peer_ptrs.append(self.local_ptr)
+                    continue
+                p = C.c_void_p()
+                buf = (C.c_ubyte * 64).from_buffer_copy(h)
+                _lib.check(lib.np_symm_open(buf, C.byref(p)), "symm_open")
+                self.peer_ptrs.append(p.value)
+            self._base_tensor = torch.as_tensor(_RawCuda(self.local_ptr, self.nbytes), device=self.device)
+        self._barrier_epoch = 0
+        self._barrier_flags = self.alloc((self.world,), torch.int32)
+        self._barrier_ptrs = self.ptr_array(self._barrier_flags)
+
+    # -- allocation --------------------------------------------------------------------------------
+    def alloc(self, shape, dtype: torch.dtype, align: int = 256) -> torch.Tensor:
+        """Carve a zero-initialised tensor out of the arena (same offset on every rank when all ranks
+        allocate in the same order)."""
+        n = int(math.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+        off = (self._offset + align - 1) // align * align
+        if off + n > self.nbytes:
+            raise MemoryError(f"symmetric heap exhausted: need {off + n} of {self.nbytes} bytes")
+        self._offset = off + n
+        t = self._base_tensor[off:off + n].view(dtype).view(*shape)
+        t._symm_offset = off
+        return t
+
+    def offset_of(self, t: torch.Tensor) -> int:
+        return t.data_ptr() - self.local_ptr
+
+    def peer_ptr(self, t: torch.Tensor, rank: int) -> int:
+        return self.peer_ptrs[rank] + self.offset_of(t)
+
+    def ptr_array(self, t: torch.Tensor) -> torch.Tensor:
+        """Device int64 tensor ``[world]``: address of ``t`` on every rank (a ``void* const*`` for kernels)."""
+        return torch.tensor([self.peer_ptr(t, r) for r in range(self.world)], dtype=torch.int64,
+                            device=self.device)
+
+    def host_ptr_array(self, t: torch.Tensor):
+        arr = (C.c_void_p * self.world)(*[self.peer_ptr(t, r) for r in range(self.world)])
+        return arr
+
+    # -- synchronisation -----------------------------------------------------------------------------
+    def barrier(self, limit_ns: int = 0):
+        """Device-side barrier on the current stream (no host synchronisation)."""
+        if self.world <= 1:
+            return
+        self._barrier_epoch += 1
+        arr = self.host_ptr_array(self._barrier_flags)
+        _lib.check(_lib.lib().np_symm_barrier(arr, self.rank, self.world, self._barrier_epoch,
+                                              C.c_ulonglong(limit_ns), C.c_void_p(_lib.stream())), "symm_barrier")
+
+    def close(self):
+        if self._ipc:
+            lib = _lib.lib()
+            torch.cuda.synchronize()
+            if dist.is_initialized():
+                dist.barrier(group=self.group)
+            for r, p in enumerate(self.peer_ptrs):
+                if r != self.rank:
+                    lib.np_symm_close(C.c_void_p(p))
+            if dist.is_initialized():
+                dist.barrier(group=self.group)
+            lib.np_symm_free(C.c_void_p(self.local_ptr))
+            self._ipc = False

@@ -1,0 +1,82 @@
+"""``parallelize_model``: composes every parallelism dimension in a fixed order
+(reference: parallelize.py:56-194).
+
+Order: ensure hooks -> warn unsupported -> PP -> FP8 -> CP -> TP (+ fused "async" TP) -> EP
+(+ FP8-Flow-MoE recipe on every MoE layer) -> activation checkpointing -> compile (no-op marker) ->
+FSDP / sharded data parallelism -> weight init for models that ask for it. FSDP stays last so the
+parameters it shards are the final (TP / EP-sliced) ones; optimizers must be built *after* this call.
+"""
+from __future__ import annotations
+
+import logging
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .models.moe import MoEBase
+from .models.parallel_adapter import ensure_parallel_hooks
+from .models.protocol import warn_unsupported_parallelism
+from .parallel.context_parallel import ContextParallelConfig
+from .parallel.fsdp import DataParallelConfig, apply_activation_checkpointing, apply_generic_fsdp
+from .parallel.mesh import (MeshDimName, get_cp_mesh, get_dp_model_mesh, get_ep_mesh, get_pp_mesh, get_tp_mesh)
+from .parallel.tensor_parallel import TensorParallelConfig
+
+log = logging.getLogger(__name__)
+
+
+def parallelize_model(model: nn.Module, *, world_mesh, device: Optional[torch.device] = None,
+                      max_sequence_length: Optional[int] = None, tp_config: Optional[TensorParallelConfig] = None,
+                      cp_config: Optional[ContextParallelConfig] = None, pp_config=None,
+                      dp_config: Optional[DataParallelConfig] = None, fp8_config=None, moe_fp8_recipe: str = "none",
+                      moe_fp8_gemm_threshold: int = 1000000, compile_model: bool = False,
+                      ac_mode: Optional[str] = None, ac_block_interval: Optional[int] = None) -> nn.Module:
+    model = ensure_parallel_hooks(model)
+    names = tuple(world_mesh.mesh_dim_names or ()) if world_mesh is not None else ()
+    ep_requested = MeshDimName.ep in names
+    warn_unsupported_parallelism(model, tp=2 if tp_config else 1, cp=2 if cp_config else 1, pp=2 if pp_config else 1,
+                                 ep=2 if ep_requested else 1, fsdp=dp_config is not None, compile=compile_model)
+    if pp_config is not None and getattr(pp_config, "degree", 1) > 1:
+        log.info("  Applying PP (degree=%d)", pp_config.degree)
+        model.apply_pp(get_pp_mesh(world_mesh))
+    if fp8_config is not None and fp8_config.enabled:
+        from .fp8.training import apply_fp8
+
+        log.info("  Applying FP8")
+        model = apply_fp8(model, config=fp8_config)
+    if cp_config is not None and cp_config.degree > 1:
+        log.info("  Applying CP (degree=%d)", cp_config.degree)
+        model.apply_cp(get_cp_mesh(world_mesh), ring=cp_config.ring and not cp_config.ulysses,
+                       uly=cp_config.ulysses)
+    if tp_config is not None and tp_config.degree > 1:
+        log.info("  Applying TP (degree=%d)", tp_config.degree)
+        tp_mesh = get_tp_mesh(world_mesh)
+        model.apply_tp(tp_mesh)
+        tp_config.maybe_enable_async_tp(tp_mesh)
+    if ep_requested:
+        log.info("  Applying EP")
+        model.apply_ep(get_ep_mesh(world_mesh))
+    if moe_fp8_recipe != "none":
+        for module in model.modules():
+            if isinstance(module, MoEBase):
+                module.apply_fp8_flow_moe(True, moe_fp8_recipe, moe_fp8_gemm_threshold)
+    if ac_mode is not None:
+        apply_activation_checkpointing(model, mode=ac_mode, block_interval=ac_block_interval)
+    if compile_model:
+        model.apply_compile()
+    if dp_config is not None:
+        dp_mesh = get_dp_model_mesh(world_mesh)
+        backend = getattr(dp_config, "backend", "auto")
+        use_arena = backend == "arena" or (backend == "auto" and device is not None and
+                                           torch.device(device).type == "cuda")
+        if use_arena:
+            # sharded optimizer state + fused reduce-scatter/AdamW/all-gather: set up by engine.prepare_training
+            model._dp_mesh_for_arena = dp_mesh
+            model._needs_grad_sync = True
+        elif hasattr(model, "apply_fsdp"):
+            model.apply_fsdp(dp_mesh=dp_mesh, param_dtype=dp_config.param_dtype, reduce_dtype=dp_config.reduce_dtype)
+        else:
+            apply_generic_fsdp(model, dp_mesh, dp_config)
+    if device is not None and getattr(model, "_init_on_parallelize", False) and hasattr(model, "init_weights"):
+        model.init_weights(device=device, world_mesh=world_mesh)
+    return model

@@ -1,0 +1,54 @@
+"""Weights & Biases logger (reference: train/callbacks/wandb_logger.py:18-125): rank 0 only, optional
+cancel-by-tag polling; a missing ``wandb`` package turns the callback into a warning."""
+from __future__ import annotations
+
+import logging
+from typing import Any, Dict, Optional
+
+from .base import Callback
+
+log = logging.getLogger(__name__)
+
+
+class WandBCallback(Callback):
+    def __init__(self, project: str = "nanopsyche", name: Optional[str] = None, config: Optional[dict] = None,
+                 entity: Optional[str] = None, tags: Optional[list] = None, cancel_tags: Optional[list] = None,
+                 cancel_check_interval: int = 25, enabled: bool = True):
+        self.project, self.name, self.config, self.entity, self.tags = project, name, config, entity, tags
+        self.cancel_tags = cancel_tags or ["cancel", "canceled", "cancelled"]
+        self.cancel_check_interval = cancel_check_interval
+        self.enabled = enabled
+        self._run = None
+        self._wandb = None
+
+    def pre_train(self, trainer: Any) -> None:
+        if not self.enabled or not getattr(trainer, "is_main", True):
+            return
+        try:
+            import wandb
+        except ImportError:
+            log.warning("wandb is not installed; WandBCallback disabled")
+            self.enabled = False
+            return
+        self._wandb = wandb
+        self._run = wandb.init(project=self.project, name=self.name, config=self.config, entity=self.entity,
+                               tags=self.tags)
+
+    def log_metrics(self, metrics: Dict[str, Any], step: int, trainer: Any) -> None:
+        if self._run is not None:
+            self._run.log(metrics, step=step)
+
+    def post_step(self, trainer: Any) -> None:
+        if self._run is None or trainer.step % self.cancel_check_interval:
+            return
+        try:
+            api_run = self._wandb.Api().run(self._run.path)
+            if any(t.lower() in self.cancel_tags for t in api_run.tags):
+                trainer.request_stop("cancelled by W&B tag")
+        except Exception:  # noqa: BLE001
+            pass
+
+    def close(self, trainer: Any) -> None:
+        if self._run is not None:
+            self._run.finish()
+            self._run = None

@@ -1,0 +1,93 @@
+"""Token datasets and loaders (reference: train/data.py:33-158).
+
+``DistributedDataset`` cuts a flat token array into fixed-length ``(input_ids, labels)`` pairs. Labels
+are the *same* window as the inputs (the model shifts by one internally); the reference pre-shifts
+them in the dataset and the model shifts again. ``DistributedDataLoader`` is an iterator (the
+reference's is only iterable although its Trainer calls ``next`` on it), shards over the
+data-parallel coordinates rather than the whole world, pins host memory when CUDA is present and
+restarts with a new epoch seed when exhausted.
+"""
+from __future__ import annotations
+
+from typing import Iterator, Optional
+
+import numpy as np
+import torch
+from torch.utils.data import DataLoader, Dataset, DistributedSampler, RandomSampler
+
+
+class DistributedDataset(Dataset):
+    def __init__(self, tokens, seq_len: int):
+        self.tokens = tokens
+        self.seq_len = seq_len
+        self.n = max((len(tokens) - 1) // seq_len, 0)
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, i):
+        s = i * self.seq_len
+        window = np.asarray(self.tokens[s:s + self.seq_len]).astype(np.int64)
+        ids = torch.from_numpy(window)
+        return ids, ids.clone()
+
+
+class DistributedDataLoader:
+    def __init__(self, dataset: Dataset, batch_size: int, *, num_workers: int = 0, seed: int = 0,
+                 dp_rank: Optional[int] = None, dp_world: Optional[int] = None, shuffle: bool = True,
+                 pin_memory: Optional[bool] = None, drop_last: bool = True):
+        self.dataset, self.batch_size, self.seed = dataset, batch_size, seed
+        self.epoch = 0
+        if dp_world is None:
+            from ..parallel.mesh import data_parallel_coords
+
+            dp_rank, dp_world = data_parallel_coords()
+            if dp_world == 1 and torch.distributed.is_available() and torch.distributed.is_initialized():
+                dp_rank, dp_world = torch.distributed.get_rank(), torch.distributed.get_world_size()
+        if dp_world > 1:
+            self.sampler = DistributedSampler(dataset, num_replicas=dp_world, rank=dp_rank, shuffle=shuffle, seed=seed)
+        else:
+            gen = torch.Generator().manual_seed(seed)
+            self.sampler = RandomSampler(dataset, generator=gen) if shuffle else None
+        pin = torch.cuda.is_available() if pin_memory is None else pin_memory
+        self.loader = DataLoader(dataset, batch_size=batch_size, sampler=self.sampler, num_workers=num_workers,
+                                 pin_memory=pin, drop_last=drop_last, persistent_workers=num_workers > 0)
+        self._it: Optional[Iterator] = None
+        self.batches_served = 0
+
+    def set_epoch(self, epoch: int):
+        self.epoch = epoch
+        if isinstance(self.sampler, DistributedSampler):
+            self.sampler.set_epoch(epoch)
+
+    def __len__(self):
+        return len(self.loader)
+
+    def __iter__(self):
+        self._it = iter(self.loader)
+        return self
+
+    def __next__(self):
+        if self._it is None:
+            self._it = iter(self.loader)
+        try:
+            b = next(self._it)
+        except StopIteration:
+            self.set_epoch(self.epoch + 1)
+            self._it = iter(self.loader)
+            b = next(self._it)
+        self.batches_served += 1
+        return b
+
+    def state_dict(self):
+        return {"epoch": self.epoch, "batches_served": self.batches_served, "seed": self.seed}
+
+    def load_state_dict(self, sd):
+        self.set_epoch(sd.get("epoch", 0))
+        self.batches_served = sd.get("batches_served", 0)
+
+
+def create_distributed_loader(data_source, batch_size: int, sequence_length: int = 2048, num_workers: int = 0,
+                              **kw) -> DistributedDataLoader:
+    return DistributedDataLoader(DistributedDataset(data_source, sequence_length), batch_size,
+                                 num_workers=num_workers, **kw)

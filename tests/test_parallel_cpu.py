@@ -1,0 +1,345 @@
+"""Distributed semantics on CPU (gloo, 2-4 ranks): TP = unsharded, Ulysses = ring = full causal
+attention, EP(ep>1) = EP(1), PP schedules = non-PP loss/grads, mesh layouts."""
+import copy
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from conftest import run_distributed
+from nanopysche_b200.parallel import pipeline_parallel as pp
+from nanopysche_b200.parallel.mesh import ParallelDims, mesh_layout
+
+
+# ------------------------------------------------------------------ mesh
+def test_mesh_layout_orders_and_validation():
+    assert mesh_layout(8, tp_size=2, pp_size=2) == ([2, 2, 2], ["pp", "dp", "tp"])
+    assert mesh_layout(8, ep_size=8) == ([1, 1, 8], ["pp", "dp", "ep"])
+    assert mesh_layout(16, tp_size=2, cp_size=2, ep_size=2) == ([1, 2, 2, 2, 2], ["pp", "dp", "ep", "cp", "tp"])
+    assert mesh_layout(8, dp_shard=4, dp_replicate=2) == ([1, 2, 4], ["pp", "dp_replicate", "dp_shard"])
+    with pytest.raises(ValueError):
+        mesh_layout(6, tp_size=4)
+    d = ParallelDims(dp_shard=-1, tp=2, pp=2).set_world_size(8)
+    assert d.dp_shard == 2 and d.world_size == 8 and d.layout() == ([2, 2, 2], ["pp", "dp", "tp"])
+    with pytest.raises(ValueError):
+        ParallelDims(tp=0)
+
+
+def _mesh_worker(rank, world):
+    from nanopysche_b200.parallel import mesh as M
+
+    m = M.build_world_mesh(tp_size=2, device_type="cpu", replace=True)
+    assert m.mesh_dim_names == ("pp", "dp", "tp")
+    assert M.get_tp_mesh().size() == 2 and M.get_dp_model_mesh().size() == 2 and M.get_cp_mesh() is None
+    assert M.get_ep_mesh().mesh_dim_names == ("dp",)
+    idx, cnt = M.data_parallel_coords()
+    assert cnt == 2 and idx == rank // 2
+    with pytest.raises(RuntimeError):
+        M.build_world_mesh(tp_size=2, device_type="cpu")
+    return True
+
+
+def test_world_mesh_4_ranks():
+    assert all(run_distributed(_mesh_worker, 4))
+
+
+# ------------------------------------------------------------------ TP
+def _tp_worker(rank, world):
+    from nanopysche_b200.models import Attention, FeedForward
+
+    torch.manual_seed(0)
+    att = Attention(d_model=64, n_heads=4, n_kv_heads=2, max_seq_len=16)
+    ffn = FeedForward(d_model=64, hidden_size=128)
+    x = torch.randn(2, 8, 64)
+    xa = x.clone().requires_grad_(True)
+    ref = att(xa) + ffn(xa)
+    ref.sum().backward()
+    ref_gx = xa.grad.clone()
+    ref_gq = att.w_q.weight.grad.clone()
+    att2, ffn2 = copy.deepcopy(att), copy.deepcopy(ffn)
+    for m in (att2, ffn2):
+        m.zero_grad()
+        m.apply_tp(dist.group.WORLD)
+    assert att2.w_q.weight.shape == (32, 64) and att2.w_out.weight.shape == (64, 32)
+    xb = x.clone().requires_grad_(True)
+    out = att2(xb) + ffn2(xb)
+    out.sum().backward()
+    assert torch.allclose(out, ref, atol=1e-5)
+    assert torch.allclose(xb.grad, ref_gx, atol=1e-5)  # input-side backward all-reduce present
+    assert torch.allclose(att2.w_q.weight.grad, ref_gq.view(2, 32, 64)[rank], atol=1e-5)
+    return True
+
+
+def test_tensor_parallel_matches_unsharded():
+    assert all(run_distributed(_tp_worker, 2))
+
+
+def _generic_tp_worker(rank, world):
+    from nanopysche_b200.models.parallel_adapter import ensure_parallel_hooks
+
+    class Layer(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b = torch.nn.Linear(16, 32), torch.nn.Linear(32, 16)
+
+        def forward(self, x):
+            return self.b(F.relu(self.a(x)))
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = torch.nn.ModuleList([Layer(), Layer()])
+
+        def forward(self, x):
+            for l in self.layers:
+                x = l(x)
+            return x
+
+    torch.manual_seed(0)
+    net = Net()
+    x = torch.randn(3, 16)
+    ref = net(x)
+    net = ensure_parallel_hooks(net)
+    net.apply_tp(dist.group.WORLD)
+    assert torch.allclose(net(x), ref, atol=1e-5)
+    return True
+
+
+def test_generic_adapter_tp():
+    assert all(run_distributed(_generic_tp_worker, 2))
+
+
+# ------------------------------------------------------------------ CP
+def _cp_worker(rank, world, ulysses):
+    from nanopysche_b200.ops.attention import attention_ref
+    from nanopysche_b200.parallel.context_parallel import (RingAttention, local_positions, shard_sequence,
+                                                           unshard_sequence)
+
+    torch.manual_seed(0)
+    B, S, Hq, Hkv, hd = 1, 16 * world, 4, 2, 8
+    q, k, v = torch.randn(B, S, Hq, hd), torch.randn(B, S, Hkv, hd), torch.randn(B, S, Hkv, hd)
+    qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+    full, _ = attention_ref(qf, kf, vf, causal=True)
+    full.square().sum().backward()
+    ql, kl, vl = (shard_sequence(t, world, rank).clone().requires_grad_(True) for t in (q, k, v))
+    pos = local_positions(S // world, world, rank)
+    c = S // (2 * world)
+    assert pos[0] == rank * c and pos[-1] == (2 * world - rank) * c - 1  # true zig-zag: chunks r and 2cp-1-r
+    mod = RingAttention(dist.group.WORLD, use_ulysses=ulysses, use_zigzag=True)
+    out = mod(ql, kl, vl, causal=True)
+    assert torch.isfinite(out).all()
+    assert torch.allclose(out, shard_sequence(full.detach(), world, rank), atol=1e-5)
+    out.square().sum().backward()
+    assert torch.allclose(ql.grad, shard_sequence(qf.grad, world, rank), atol=1e-4)
+    assert torch.allclose(kl.grad, shard_sequence(kf.grad, world, rank), atol=1e-4)
+    gathered = [torch.empty_like(out) for _ in range(world)]
+    dist.all_gather(gathered, out.detach())
+    assert torch.allclose(unshard_sequence(gathered, world), full.detach(), atol=1e-5)
+    return True
+
+
+@pytest.mark.parametrize("ulysses", [False, True])
+def test_context_parallel_matches_full_attention(ulysses):
+    assert all(run_distributed(_cp_worker, 2, ulysses))
+
+
+def test_ring_attention_4_ranks():
+    assert all(run_distributed(_cp_worker, 4, False))
+
+
+def _cp_model_worker(rank, world):
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.parallel.context_parallel import shard_batch_for_cp
+
+    torch.manual_seed(0)
+    cfg = TransformerConfig(d_model=32, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=64,
+                            ffn_hidden=256, qk_norm=False)
+    m = cfg.build()
+    x = torch.randint(0, 64, (2, 32))
+    ref = m(x, labels=x)["loss"]
+    ref.backward()
+    g_ref = m.blocks["0"].attention.w_q.weight.grad.clone()
+    m.zero_grad()
+    m.apply_cp(dist.group.WORLD)
+    ids, tgt = shard_batch_for_cp(x, x, world, rank)
+    out = m(ids, labels=tgt, labels_shifted=True)
+    assert out["loss"].item() == pytest.approx(ref.item(), rel=1e-5)  # loss over the global token count
+    out["loss"].backward()
+    g = m.blocks["0"].attention.w_q.weight.grad
+    dist.all_reduce(g)
+    assert torch.allclose(g, g_ref, atol=1e-5)  # gradients sum over the CP group
+    return True
+
+
+def test_context_parallel_model_loss_and_grads():
+    assert all(run_distributed(_cp_model_worker, 2))
+
+
+# ------------------------------------------------------------------ EP
+def _ep_worker(rank, world):
+    from nanopysche_b200.models.moe import ExpertParallelConfig, MoEBase, NcclAllToAllDispatcher
+
+    torch.manual_seed(0)
+    moe = MoEBase(d_model=16, hidden_size=256, num_experts=4, top_k=2, capacity_factor=None)
+    torch.manual_seed(10 + rank)
+    x = torch.randn(2, 6, 16)
+    xa = x.clone().requires_grad_(True)
+    ref = moe(xa)
+    ref.sum().backward()
+    full_w1_grad = moe.w1.grad.clone()
+    dist.all_reduce(full_w1_grad)  # every rank's tokens contribute to every expert
+    moe._aux_loss = None  # a graph tensor from the forward above cannot be deep-copied
+    ep = copy.deepcopy(moe)
+    ep.zero_grad()
+    ep.apply_ep(ExpertParallelConfig(ep_size=world, ep_group=dist.group.WORLD, dispatcher=NcclAllToAllDispatcher()))
+    assert ep.w1.shape[0] == 4 // world * 256 and ep.num_local_experts == 4 // world
+    xb = x.clone().requires_grad_(True)
+    out = ep(xb)
+    assert torch.allclose(out, ref, atol=1e-5)
+    out.sum().backward()
+    assert torch.allclose(xb.grad, xa.grad, atol=1e-5)
+    H = 256
+    lo = rank * (4 // world)
+    assert torch.allclose(ep.w1.grad, full_w1_grad[lo * H:(lo + 4 // world) * H], atol=1e-5)
+    return True
+
+
+def test_expert_parallel_matches_single_rank():
+    assert all(run_distributed(_ep_worker, 2))
+
+
+# ------------------------------------------------------------------ PP schedules
+@pytest.mark.parametrize("p,m", [(2, 4), (4, 8), (4, 4), (3, 7)])
+def test_schedules_validate_and_bubbles(p, m):
+    g = pp.validate_schedule(pp.GPipeSchedule(p, m).generate_schedule(), p, m)
+    f = pp.validate_schedule(pp.OneForwardOneBackwardSchedule(p, m).generate_schedule(), p, m)
+    z = pp.validate_schedule(pp.ZeroBubbleSchedule(p, m).generate_schedule(), p, m)
+    ideal = (p - 1) / (m + p - 1)
+    assert g["bubble_fraction"] == pytest.approx(ideal, abs=1e-9)
+    assert f["bubble_fraction"] == pytest.approx(ideal, abs=1e-9)
+    assert z["bubble_fraction"] < f["bubble_fraction"] + 1e-9
+    sched = pp.OneForwardOneBackwardSchedule(p, m).generate_schedule()
+    for r in range(p):
+        warm = min(p - 1 - r, m)
+        assert [a.type for a in sched[r][:warm]] == [pp.F] * warm
+    zs = pp.ZeroBubbleSchedule(p, m).generate_schedule()
+    assert sum(a.type == pp.W for a in zs[0]) == m and sum(a.type == pp.BI for a in zs[0]) == m
+
+
+@pytest.mark.parametrize("p,m", [(2, 4), (4, 8)])
+def test_dualpipe_schedule_is_valid_and_has_no_duplicates(p, m):
+    gen = pp.DualPipeSchedule(num_stages=p, num_microbatches=m)
+    s = gen.generate_schedule()
+    first = lambda st: 0 if st < p else p  # noqa: E731
+    last = lambda st: p - 1 if st < p else 2 * p - 1  # noqa: E731
+    r = pp.validate_schedule(s, p, m, stage_first=first, stage_last=last)
+    fw = [(a.microbatch, a.stage) for a in s[0] if a.type == pp.F]
+    assert len(fw) == len(set(fw)) == m  # each microbatch passes rank 0 once (one of its two stages)
+    assert gen.stages_of_rank(0) == [0, 2 * p - 1] and gen.rank_of_stage(2 * p - 1) == 0
+    one = pp.validate_schedule(pp.OneForwardOneBackwardSchedule(p, m).generate_schedule(), p, m)
+    assert r["bubble_fraction"] <= one["bubble_fraction"] + 1e-9
+
+
+def test_validator_rejects_bad_schedules():
+    bad = [[pp.Action(pp.B, 0, 0), pp.Action(pp.F, 0, 0)], [pp.Action(pp.F, 0, 1), pp.Action(pp.B, 0, 1)]]
+    with pytest.raises(ValueError):
+        pp.validate_schedule(bad, 2, 1)
+    dup = [[pp.Action(pp.F, 0, 0), pp.Action(pp.F, 0, 0)]]
+    with pytest.raises(ValueError):
+        pp.validate_schedule(dup, 1, 1)
+
+
+def test_bubble_closed_forms_and_auto_schedule():
+    assert pp.compute_bubble_fraction("1f1b", 4, 8) == 3 / 8
+    assert pp.compute_bubble_fraction("interleaved", 4, 8, 2) == 3 / 16
+    assert pp.compute_bubble_fraction("dualpipe", 8, 16) == 3 / 16
+    assert pp.compute_bubble_fraction("zb1p", 4, 8) == 3 / (3 * 11)
+    assert pp.compute_bubble_fraction("zbv", 4, 8) == 0.0
+    from nanopysche_b200.parallel.auto_schedule import AutoScheduleConfig, AutoScheduleGenerator, StageProfile
+
+    g = AutoScheduleGenerator([StageProfile()] * 4, AutoScheduleConfig(num_microbatches=8, num_stages=4))
+    s = g.generate()
+    assert len(s) == 4 and s[3][0].type == "FWD" and 0 < g.compute_bubble_fraction() < 0.5
+    assert g.validate_memory() and g.compute_overlap_efficiency() == 1.0
+    d = AutoScheduleGenerator([StageProfile()] * 4, AutoScheduleConfig(8, 4, dualpipe_ratio=0.5))
+    assert d.compute_bubble_fraction() <= g.compute_bubble_fraction() + 1e-9
+    assert not AutoScheduleGenerator([StageProfile(mem_gb=100)] * 4, AutoScheduleConfig(8, 4)).validate_memory()
+
+
+def test_stage_layer_ranges():
+    from nanopysche_b200.parallel.pipeline_runtime import (PipelineParallelConfig, PipelineScheduleType,
+                                                           stage_layer_ranges)
+
+    assert stage_layer_ranges(8, 4) == [(0, 2), (2, 4), (4, 6), (6, 8)]
+    assert stage_layer_ranges(10, 4) == [(0, 2), (2, 5), (5, 8), (8, 10)]  # remainder goes to stages 1..
+    assert stage_layer_ranges(6, 3, [1, 3]) == [(0, 1), (1, 3), (3, 6)]
+    c = PipelineParallelConfig(degree=4, schedule=PipelineScheduleType.dualpipe)
+    assert c.stages_per_rank() == 2 and c.stage_ids_this_rank(1) == [1, 6]
+    c2 = PipelineParallelConfig(degree=4, schedule=PipelineScheduleType.interleaved_1F1B)
+    assert c2.stage_ids_this_rank(1) == [1, 5]
+
+
+def _pp_worker(rank, world, schedule):
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.parallel.pipeline_runtime import (PipelineParallelConfig, PipelineSchedule,
+                                                           PipelineScheduleType, split_model)
+
+    torch.manual_seed(0)
+    cfg = TransformerConfig(d_model=32, n_layers=4, n_heads=2, vocab_size=64, max_seq_len=16, ffn_hidden=256,
+                            qk_norm=False)
+    model = cfg.build()
+    x = torch.randint(0, 64, (4, 8))
+    ref = model(x, labels=x)["loss"]  # mean over 4 sequences = mean of the per-microbatch means here
+    ref.backward()
+    g_first = model.blocks["0"].attention.w_q.weight.grad.clone()
+    g_last = model.blocks["3"].attention.w_q.weight.grad.clone()
+    model.zero_grad()
+    pcfg = PipelineParallelConfig(degree=world, schedule=PipelineScheduleType(schedule), num_microbatches=4)
+    stages = split_model(model, dist.group.WORLD, pcfg)
+    sched = PipelineSchedule(stages, dist.group.WORLD, pcfg, hidden_shape=(1, 8, 32), hidden_dtype=torch.float32)
+    loss = sched.step(x, target=x)
+    def block(idx):
+        for st in stages:
+            if str(idx) in st.blocks:
+                return st.blocks[str(idx)]
+        return None
+
+    owns_last = block(3) is not None
+    assert (loss is not None) == owns_last
+    if owns_last:
+        assert loss.item() == pytest.approx(ref.item(), rel=1e-5)
+        assert torch.allclose(block(3).attention.w_q.weight.grad, g_last, atol=1e-5)
+        assert stages[-1].embeddings is None and stages[-1].lm_head is not None
+    if rank == 0:
+        assert stages[0].lm_head is None and stages[0].embeddings is not None
+        assert torch.allclose(block(0).attention.w_q.weight.grad, g_first, atol=1e-5)
+    return True
+
+
+@pytest.mark.parametrize("schedule", ["1F1B", "GPipe", "InterleavedZeroBubble", "Interleaved1F1B", "ZBVZeroBubble"])
+def test_pipeline_runtime_matches_single_process(schedule):
+    assert all(run_distributed(_pp_worker, 2, schedule))
+
+
+def _fsdp_worker(rank, world):
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.parallel.mesh import build_world_mesh, get_dp_model_mesh
+
+    torch.manual_seed(0)
+    cfg = TransformerConfig(d_model=32, n_layers=2, n_heads=2, vocab_size=64, max_seq_len=16, ffn_hidden=256,
+                            qk_norm=False)
+    m = cfg.build()
+    x = torch.randint(0, 64, (2, 8))
+    ref = m(x, labels=x)["loss"].item()
+    mesh = build_world_mesh(device_type="cpu", replace=True)
+    m.apply_fsdp(get_dp_model_mesh(mesh), param_dtype=torch.float32)
+    out = m(x, labels=x)
+    assert out["loss"].item() == pytest.approx(ref, rel=1e-5)
+    out["loss"].backward()
+    assert m._fsdp_enabled
+    return True
+
+
+def test_fsdp_matches_unsharded_loss():
+    assert all(run_distributed(_fsdp_worker, 2))
