@@ -531,6 +531,15 @@ static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
 NP_API int np_gemm_bf16(const NpGemmArgs* args, void* stream) {
   const NpGemmArgs& a = *args;
   if (a.M <= 0 || a.N <= 0) return 0;
+  // The tensor-map encode below is a driver call: make sure this host thread (e.g. an autograd
+  // worker that has not touched the runtime yet) has the device's primary context bound.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess || cudaFree(nullptr) != cudaSuccess)
+      return 2;
+    ctx_bound = true;
+  }
   if ((a.lda % 8) || (a.ldb % 8) || (((uintptr_t)a.A) & 15) || (((uintptr_t)a.B) & 15)) return 1;
   int bn = a.bn;
   if (a.epilogue == 1) bn = 256;

@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(256) router_bwd_kernel(const float* __restrict
   for (int e = 0; e < E; ++e) dlogits[(size_t)t * E + e] = dl[e];
 }
 
-// partial[c, e, d] = sum over the chunk's tokens of dl[t, e] * x[t, d]   (chunk = 32 tokens)
+// partial[c, e, d] = sum over the chunk's tokens of dl[t, e] * x[t, d]
 template <int EB>
 __global__ void __launch_bounds__(256) router_dgate_kernel(const float* __restrict__ dl,
                                                            const __nv_bfloat16* __restrict__ x,
@@ -242,8 +242,16 @@ __global__ void colsum2_kernel(const float* __restrict__ partial, float* __restr
                                long long cols, int accumulate) {
   const long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (c >= cols) return;
-  float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += partial[(size_t)p * cols + c];
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int p = 0;
+  for (; p + 3 < parts; p += 4) {
+    s0 += partial[(size_t)p * cols + c];
+    s1 += partial[(size_t)(p + 1) * cols + c];
+    s2 += partial[(size_t)(p + 2) * cols + c];
+    s3 += partial[(size_t)(p + 3) * cols + c];
+  }
+  for (; p < parts; ++p) s0 += partial[(size_t)p * cols + c];
+  const float s = (s0 + s1) + (s2 + s3);
   out[c] = accumulate ? out[c] + s : s;
 }
 
@@ -255,10 +263,23 @@ __global__ void colsum2_kernel(const float* __restrict__ partial, float* __restr
 __global__ void __launch_bounds__(1024) capacity_scan_kernel(const int* __restrict__ indices, int T, int E, int K,
                                                              int capacity, int* __restrict__ slot_pos,
                                                              int* __restrict__ keep, int* __restrict__ counts_kept,
-                                                             int* __restrict__ drops, int* __restrict__ n_dropped) {
+                                                             int* __restrict__ drops, int* __restrict__ n_dropped,
+                                                             int use_smem) {
+  // s_idx: the routing table staged once (the scans below walk it serially per expert, so reading it
+  // from global memory would pay one dependent-load latency per 32 tokens); s_keep: one byte per token
+  extern __shared__ int s_dyn[];
+  int* s_idx = s_dyn;
+  unsigned char* s_keep = reinterpret_cast<unsigned char*>(s_dyn + (use_smem ? T * K : 0));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nw = blockDim.x >> 5;
-  for (int t = threadIdx.x; t < T; t += blockDim.x) keep[t] = 1;
+  const int* idx = indices;
+  if (use_smem) {
+    for (int i = threadIdx.x; i < T * K; i += blockDim.x) s_idx[i] = indices[i];
+    for (int t = threadIdx.x; t < T; t += blockDim.x) s_keep[t] = 1;
+    idx = s_idx;
+  } else {
+    for (int t = threadIdx.x; t < T; t += blockDim.x) keep[t] = 1;
+  }
   __syncthreads();
   if (capacity >= 0) {
     for (int e = warp; e < E; e += nw) {
@@ -267,10 +288,12 @@ __global__ void __launch_bounds__(1024) capacity_scan_kernel(const int* __restri
         const int t = t0 + lane;
         bool has = false;
         if (t < T)
-          for (int k = 0; k < K; ++k) has |= indices[(size_t)t * K + k] == e;
+          for (int k = 0; k < K; ++k) has |= idx[(size_t)t * K + k] == e;
         const unsigned m = __ballot_sync(0xffffffffu, has);
         const int pos = base + __popc(m & ((1u << lane) - 1u));
-        if (has && pos >= capacity) keep[t] = 0;  // benign race: only ever written to 0
+        if (has && pos >= capacity) {  // benign race: only ever written to 0
+          if (use_smem) s_keep[t] = 0; else keep[t] = 0;
+        }
         base += __popc(m);
       }
       if (lane == 0) drops[e] = base > capacity ? base - capacity : 0;
@@ -286,8 +309,8 @@ __global__ void __launch_bounds__(1024) capacity_scan_kernel(const int* __restri
       int kk = -1;
       if (t < T)
         for (int k = 0; k < K; ++k)
-          if (indices[(size_t)t * K + k] == e) kk = k;
-      const bool kept = kk >= 0 && keep[t];
+          if (idx[(size_t)t * K + k] == e) kk = k;
+      const bool kept = kk >= 0 && (use_smem ? s_keep[t] : keep[t]);
       const unsigned m = __ballot_sync(0xffffffffu, kept);
       if (kk >= 0) slot_pos[(size_t)t * K + kk] = kept ? base + __popc(m & ((1u << lane) - 1u)) : -1;
       base += __popc(m);
@@ -295,11 +318,20 @@ __global__ void __launch_bounds__(1024) capacity_scan_kernel(const int* __restri
     if (lane == 0) counts_kept[e] = base;
   }
   __syncthreads();
+  int nd = 0;
+  for (int t = threadIdx.x; t < T; t += blockDim.x) {
+    const int kp = use_smem ? (int)s_keep[t] : keep[t];
+    if (use_smem) keep[t] = kp;
+    nd += kp ? 0 : 1;
+  }
+  for (int o = 16; o > 0; o >>= 1) nd += __shfl_xor_sync(0xffffffffu, nd, o);
+  __shared__ int s_nd[32];
+  if (lane == 0) s_nd[warp] = nd;
+  __syncthreads();
   if (warp == 0) {
-    int nd = 0;
-    for (int t = lane; t < T; t += 32) nd += keep[t] ? 0 : 1;
-    for (int o = 16; o > 0; o >>= 1) nd += __shfl_xor_sync(0xffffffffu, nd, o);
-    if (lane == 0) n_dropped[0] = nd;
+    int v = lane < nw ? s_nd[lane] : 0;
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) n_dropped[0] = v;
   }
 }
 
@@ -558,7 +590,7 @@ NP_API int np_router_bwd(const float* logits, const float* score_bias, const flo
   CHECK_LAUNCH();
 }
 
-NP_API int np_router_dgate_parts(int T) { return (T + 31) / 32; }
+NP_API int np_router_dgate_parts(int T) { return (T + 127) / 128; }
 // scratch: fp32 [np_router_dgate_parts(T), E, D]; dwg[E, D] (+)= dl^T x ; dbias[E] (+)= column sums of dl.
 NP_API int np_router_dgate(const float* dl, const void* x, float* dwg, float* dbias, float* scratch, int T, int D,
                            int E, int accumulate, void* stream) {
@@ -567,9 +599,9 @@ NP_API int np_router_dgate(const float* dl, const void* x, float* dwg, float* db
   cudaStream_t s = (cudaStream_t)stream;
   const int parts = np_router_dgate_parts(T);
   dim3 grid((D / 8 + 255) / 256, parts);
-  router_dgate_kernel<8><<<grid, 256, 0, s>>>(dl, (const __nv_bfloat16*)x, scratch, T, D, E, 32);
+  router_dgate_kernel<8><<<grid, 256, 0, s>>>(dl, (const __nv_bfloat16*)x, scratch, T, D, E, 128);
   const long long cols = (long long)E * D;
-  colsum2_kernel<<<(int)((cols + 255) / 256), 256, 0, s>>>(scratch, dwg, parts, cols, accumulate);
+  colsum2_kernel<<<(int)((cols + 63) / 64), 64, 0, s>>>(scratch, dwg, parts, cols, accumulate);
   if (dbias) colsum2_kernel<<<1, 256, 0, s>>>(dl, dbias, T, E, accumulate);
   CHECK_LAUNCH();
 }
@@ -578,8 +610,17 @@ NP_API int np_capacity_scan(const int* indices, int T, int E, int K, int capacit
                             int* counts_kept, int* drops, int* n_dropped, void* stream) {
   if (K > MAX_K) return 1;
   if (T <= 0) return 0;
-  capacity_scan_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(indices, T, E, K, capacity, slot_pos, keep, counts_kept,
-                                                             drops, n_dropped);
+  const size_t smem = (size_t)T * K * 4 + (size_t)((T + 3) / 4) * 4;
+  const int use_smem = smem <= 200 * 1024;
+  static bool attr_set = false;
+  if (use_smem && !attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(capacity_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return 400 + (int)e;
+    attr_set = true;
+  }
+  capacity_scan_kernel<<<1, 1024, use_smem ? smem : 0, (cudaStream_t)stream>>>(indices, T, E, K, capacity, slot_pos,
+                                                                               keep, counts_kept, drops, n_dropped,
+                                                                               use_smem);
   CHECK_LAUNCH();
 }
 

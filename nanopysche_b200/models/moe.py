@@ -58,18 +58,19 @@ class MoERouterConfig:
 class MoERouter(nn.Module):
     """fp32 gate with bias, DeepSeek-V3 score bias, top-k softmax / sigmoid gating, aux + z loss."""
 
-    def __init__(self, *, d_model: int, config: MoERouterConfig):
+    def __init__(self, *, d_model: int, config: MoERouterConfig, device=None):
         super().__init__()
         self.config = config
         self.num_experts = config.num_experts
         self.top_k = config.top_k
-        self.gate = nn.Linear(d_model, config.num_experts, bias=True, dtype=torch.float32)
+        self.gate = nn.Linear(d_model, config.num_experts, bias=True, dtype=torch.float32, device=device)
         if config.bias_init is not None:
             nn.init.constant_(self.gate.bias, config.bias_init)
         if config.bias_gamma is not None:
-            self.register_buffer("score_bias", torch.zeros(config.num_experts))
-            self.register_buffer("_tokens_per_expert_this_batch", torch.zeros(config.num_experts, dtype=torch.long))
-            self.register_buffer("_total_tokens_this_batch", torch.tensor(0, dtype=torch.long))
+            self.register_buffer("score_bias", torch.zeros(config.num_experts, device=device))
+            self.register_buffer("_tokens_per_expert_this_batch",
+                                 torch.zeros(config.num_experts, dtype=torch.long, device=device))
+            self.register_buffer("_total_tokens_this_batch", torch.tensor(0, dtype=torch.long, device=device))
         else:
             self.score_bias = None
         self.routing_replay = config.routing_replay
@@ -370,7 +371,7 @@ class MoEBase(nn.Module):
         self.router = MoERouter(d_model=d_model, config=MoERouterConfig(
             num_experts=num_experts, top_k=top_k, gating_function=GatingFunction(gating_function),
             routing_replay=routing_replay, bias_init=-1.0, bias_gamma=bias_gamma,
-            z_loss_multiplier=z_loss_multiplier, jitter_eps=jitter_eps))
+            z_loss_multiplier=z_loss_multiplier, jitter_eps=jitter_eps), device=device)
         self.init_std = init_std
         self.num_local_experts = num_experts
         self.expert_offset = 0

@@ -64,7 +64,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     args.accumulate = int(accumulate)
     args.alpha = alpha
     args.bn, args.max_ctas = bn, max_ctas
-    _lib.check(_lib.lib().np_gemm_bf16(C.byref(args), C.c_void_p(_lib.stream())), "gemm_bf16")
+    rc = _lib.lib().np_gemm_bf16(C.byref(args), C.c_void_p(_lib.stream()))
+    if rc != 0:
+        raise _lib.KernelError(
+            f"gemm_bf16 failed with code {rc}: M={M} N={N} K={K} a_mn={a_mn} b_mn={b_mn} a={tuple(a.shape)}/"
+            f"{a.stride()} b={tuple(b.shape)}/{b.stride()} out={tuple(out.shape)}/{out.stride()} {out.dtype} "
+            f"ptrs={a.data_ptr() % 256},{b.data_ptr() % 256},{out.data_ptr() % 256} bn={bn}")
+    _lib.LAUNCHES += 1
     return out
 
 

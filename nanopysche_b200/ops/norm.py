@@ -76,6 +76,6 @@ class _RMSNorm(torch.autograd.Function):
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual: torch.Tensor | None = None):
     """``norm(x [+ residual]) * weight``; returns ``(y, x + residual)`` when a residual is given."""
-    if _kernel_ok(x, weight):
+    if _kernel_ok(x, weight) and (residual is None or (residual.dtype == x.dtype and residual.is_cuda)):
         return _RMSNorm.apply(x, weight, residual, eps)
     return rms_norm_ref(x, weight, eps, residual)

@@ -38,8 +38,8 @@ class _RawCuda:
 class SymmetricHeap:
     def __init__(self, nbytes: int, group=None, device: Optional[torch.device] = None):
         self.group = group
-        self.world = dist.get_world_size(group) if (group is not None or dist.is_initialized()) and \
-            dist.is_initialized() else 1
+        # group=None means "this rank alone" (pass dist.group.WORLD explicitly for all ranks)
+        self.world = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.nbytes = int(math.ceil(nbytes / 4096) * 4096)

@@ -1,0 +1,247 @@
+"""sm_100a kernel numerics against plain PyTorch fp32 references of the same op (GPU only)."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    from nanopysche_b200.ops import _lib
+
+    yield
+    torch.cuda.synchronize()
+    _lib.check_status("after test")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 320), (200, 264, 72), (4096, 2048, 2048),
+                                   (384, 32000, 256)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_forward_shapes(M, N, K, bn):
+    from nanopysche_b200.ops.gemm import gemm
+
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    ref = a.float() @ b.float().t()
+    assert rel(gemm(a, b, bn=bn), ref) < 4e-3
+    assert rel(gemm(a, b, bn=bn, out_dtype=torch.float32), ref) < 1e-5
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_dgrad_wgrad_layouts_and_accumulate(bn):
+    from nanopysche_b200.ops.gemm import gemm
+
+    torch.manual_seed(1)
+    dy = torch.randn(512, 384, device="cuda").bfloat16()
+    w = torch.randn(384, 640, device="cuda").bfloat16()
+    x = torch.randn(512, 640, device="cuda").bfloat16()
+    assert rel(gemm(dy, w, b_mn=True, bn=bn), dy.float() @ w.float()) < 4e-3
+    ref_w = dy.float().t() @ x.float()
+    assert rel(gemm(dy, x, a_mn=True, b_mn=True, bn=bn, out_dtype=torch.float32), ref_w) < 1e-5
+    acc = torch.full((384, 640), 2.0, device="cuda")
+    gemm(dy, x, a_mn=True, b_mn=True, out=acc, accumulate=True, bn=bn)
+    assert rel(acc, ref_w + 2.0) < 1e-5
+    at = torch.randn(256, 384, device="cuda").bfloat16()
+    bb = torch.randn(512, 256, device="cuda").bfloat16()
+    assert rel(gemm(at, bb, a_mn=True, bn=bn, alpha=0.5), 0.5 * at.float().t() @ bb.float().t()) < 4e-3
+    # strided operands (views into a wider buffer)
+    wide = torch.randn(512, 1024, device="cuda").bfloat16()
+    assert rel(gemm(wide[:, 128:384], w[:, :256].contiguous()), wide[:, 128:384].float() @ w[:, :256].float().t()) < 4e-3
+
+
+def test_gemm_swiglu_epilogue():
+    from nanopysche_b200.ops.gemm import gemm_swiglu
+
+    torch.manual_seed(2)
+    x = torch.randn(512, 256, device="cuda").bfloat16()
+    w1 = (torch.randn(384, 256, device="cuda") * 0.1).bfloat16()
+    w3 = (torch.randn(384, 256, device="cuda") * 0.1).bfloat16()
+    h, gu = gemm_swiglu(x, w1, w3)
+    g, u = x.float() @ w1.float().t(), x.float() @ w3.float().t()
+    assert rel(h, F.silu(g) * u) < 6e-3 and rel(gu, torch.cat([g, u], 1)) < 4e-3
+
+
+def test_linear_autograd_matches_torch():
+    from nanopysche_b200.ops.gemm import linear
+
+    torch.manual_seed(3)
+    x = torch.randn(4, 96, 256, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(512, 256, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    y = linear(x, w)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = F.linear(xr, wr)
+    yr.backward(gy.float())
+    assert rel(y, yr) < 4e-3 and rel(x.grad, xr.grad) < 4e-3 and rel(w.grad, wr.grad) < 4e-3
+    # main_grad accumulation (the arena path): two backward passes add up in fp32
+    w2 = w.detach().clone().requires_grad_(True)
+    w2.main_grad = torch.zeros(512, 256, device="cuda")
+    for _ in range(2):
+        linear(x.detach(), w2).backward(gy)
+    assert w2.grad is None and rel(w2.main_grad, 2 * wr.grad) < 1e-3
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 256), (4096, 2048), (33, 4096), (7, 8192)])
+def test_rmsnorm_fwd_bwd(rows, cols):
+    from nanopysche_b200.ops.norm import rms_norm, rms_norm_ref
+
+    torch.manual_seed(4)
+    x = torch.randn(rows, cols, device="cuda").bfloat16().requires_grad_(True)
+    r = torch.randn(rows, cols, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.rand(cols, device="cuda") + 0.5).requires_grad_(True)
+    y, h = rms_norm(x, w, 1e-6, r)
+    gy, gh = torch.randn_like(y), torch.randn_like(h)
+    (y * gy + h * gh).sum().backward()
+    xr, rr, wr = (t.detach().float().requires_grad_(True) for t in (x, r, w))
+    yr, hr = rms_norm_ref(xr, wr, 1e-6, rr)
+    (yr * gy.float() + hr * gh.float()).sum().backward()
+    assert rel(y, yr) < 6e-3 and rel(h, hr) < 4e-3
+    assert rel(x.grad, xr.grad) < 8e-3 and rel(r.grad, rr.grad) < 8e-3 and rel(w.grad, wr.grad) < 8e-3
+    y1 = rms_norm(x.detach(), w.detach())
+    assert rel(y1, rms_norm_ref(x.detach().float(), w.detach())) < 6e-3
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
+def test_glu_fwd_bwd(act):
+    from nanopysche_b200.ops.activation import glu, glu_ref
+
+    torch.manual_seed(5)
+    gu = torch.randn(300, 2 * 512, device="cuda").bfloat16().requires_grad_(True)
+    h = glu(gu, act)
+    gh = torch.randn_like(h)
+    h.backward(gh)
+    gr = gu.detach().float().requires_grad_(True)
+    hr = glu_ref(gr, act)
+    hr.backward(gh.float())
+    assert rel(h, hr) < 6e-3 and rel(gu.grad, gr.grad) < 8e-3
+
+
+def test_rope_kernel_and_tables():
+    from nanopysche_b200.ops import rope as R
+
+    for scaling, kw in ((None, {}), ("piecewise", dict(factor=8.0, orig_len=64.0, low_f=1.0, high_f=4.0)),
+                        ("yarn", dict(factor=4.0, orig_len=64.0, low_f=1.0, high_f=32.0))):
+        c, s = R.rope_tables(256, 128, 10000.0, scaling, device="cuda", **kw)
+        cr, sr = R.rope_tables_ref(256, 128, 10000.0, scaling, device="cuda", **kw)
+        assert torch.allclose(c, cr, atol=2e-4) and torch.allclose(s, sr, atol=2e-4), scaling
+    torch.manual_seed(6)
+    cos, sin = R.rope_tables(64, 128, 10000.0, device="cuda")
+    qkv = torch.randn(2, 32, (4 + 2 + 2) * 128, device="cuda").bfloat16().requires_grad_(True)
+    q = qkv[..., :512].unflatten(-1, (4, 128))  # strided view into the fused buffer
+    out = R.apply_rope(q, cos, sin, pos_offset=3)
+    ref = R.apply_rope_ref(q.detach().float(), cos, sin, pos_offset=3)
+    assert rel(out, ref) < 6e-3
+    g = torch.randn_like(out)
+    out.backward(g)
+    gref = R.apply_rope_ref(g.float(), cos, sin, pos_offset=3, sign=-1.0)
+    assert rel(qkv.grad[..., :512].unflatten(-1, (4, 128)), gref) < 6e-3 and qkv.grad[..., 512:].abs().sum() == 0
+    pid = torch.randint(0, 64, (2, 32), device="cuda")
+    assert rel(R.apply_rope(q.detach(), cos, sin, pos_ids=pid),
+               R.apply_rope_ref(q.detach().float(), cos, sin, pos_ids=pid)) < 6e-3
+
+
+def test_cross_entropy_fwd_bwd():
+    from nanopysche_b200.ops.xent import cross_entropy
+
+    torch.manual_seed(7)
+    logits = (torch.randn(300, 32000, device="cuda") * 2).bfloat16().requires_grad_(True)
+    labels = torch.randint(0, 32000, (300,), device="cuda")
+    labels[::7] = -100
+    loss = cross_entropy(logits, labels)
+    (loss * 3.0).backward()
+    lr = logits.detach().float().requires_grad_(True)
+    ref = F.cross_entropy(lr, labels, ignore_index=-100)
+    (ref * 3.0).backward()
+    assert abs(loss.item() - ref.item()) < 2e-3 * abs(ref.item())
+    assert rel(logits.grad, lr.grad) < 1e-2
+
+
+def test_fused_adamw_and_clip():
+    from nanopysche_b200.ops import _lib
+
+    torch.manual_seed(8)
+    n = 100003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    w16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    pr = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([pr], lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
+    parts = _lib.lib().np_sumsq_parts()
+    partial = torch.zeros(parts, device="cuda")
+    coef = torch.zeros(2, device="cuda")
+    for step in (1, 2, 3):
+        _lib.call("sumsq", g, _lib.LL(n), partial)
+        _lib.call("clip_coef", partial, parts, None, 1.0, coef)
+        _lib.call("adamw", p, g, m, v, w16, _lib.LL(n), 1e-2, 0.9, 0.95, 1e-8, 0.1, step, coef[:1])
+        pr.grad = g.clone()
+        nrm = torch.nn.utils.clip_grad_norm_([pr], 1.0)
+        opt.step()
+        assert abs(coef[1].item() - nrm.item()) < 1e-3 * nrm.item()
+    assert torch.allclose(p, pr.detach(), atol=1e-5) and rel(w16, p) < 4e-3
+
+
+def test_router_kernels_match_module_math():
+    from nanopysche_b200.models.moe import MoERouter, MoERouterConfig
+
+    for gating in ("softmax", "sigmoid"):
+        torch.manual_seed(9)
+        r = MoERouter(d_model=512, config=MoERouterConfig(num_experts=8, top_k=2, gating_function=gating,
+                                                         bias_gamma=0.01, z_loss_multiplier=0.001)).cuda()
+        with torch.no_grad():
+            r.score_bias.uniform_(-0.1, 0.1)
+        x = torch.randn(3, 200, 512, device="cuda").bfloat16().requires_grad_(True)
+        w, idx, aux = r(x)  # kernel path
+        gw = torch.randn_like(w)
+        ((w * gw).sum() + 2.0 * aux).backward()
+        gx, ggw, ggb = x.grad.clone(), r.gate.weight.grad.clone(), r.gate.bias.grad.clone()
+        r.zero_grad()
+        xr = x.detach().float().requires_grad_(True)
+        wr, ir, ar = r(xr)  # fp32 input -> PyTorch path
+        ((wr * gw).sum() + 2.0 * ar).backward()
+        same = (idx == ir).all(-1)
+        assert same.float().mean() > 0.99  # bf16 rounding can flip near-ties
+        assert rel(w[same], wr[same]) < 5e-3 and abs(aux.item() - ar.item()) < 5e-3 * abs(ar.item())
+        assert rel(ggw, r.gate.weight.grad) < 2e-2 and rel(ggb, r.gate.bias.grad) < 2e-2
+        assert rel(gx.float()[same], xr.grad[same]) < 3e-2
+
+
+def test_capacity_scan_matches_reference_rule():
+    from nanopysche_b200.ops import _lib
+
+    torch.manual_seed(10)
+    T, E, K = 1000, 8, 2
+    idx = torch.stack([torch.randperm(E)[:K] for _ in range(T)]).to(torch.int32).cuda()
+    for cap in (int(1.25 * T / E), 50, -1):
+        slot_pos = torch.empty(T, K, dtype=torch.int32, device="cuda")
+        keep = torch.empty(T, dtype=torch.int32, device="cuda")
+        ck = torch.empty(E, dtype=torch.int32, device="cuda")
+        drops = torch.empty(E, dtype=torch.int32, device="cuda")
+        nd = torch.empty(1, dtype=torch.int32, device="cuda")
+        _lib.call("capacity_scan", idx, T, E, K, cap, slot_pos, keep, ck, drops, nd)
+        ic = idx.cpu().long()
+        ref_keep = torch.ones(T, dtype=torch.bool)
+        ref_drops = []
+        for e in range(E):
+            ids = (ic == e).any(-1).nonzero(as_tuple=True)[0]
+            over = len(ids) - cap if cap >= 0 else 0
+            ref_drops.append(max(0, over))
+            if cap >= 0 and len(ids) > cap:
+                ref_keep[ids[cap:]] = False
+        assert torch.equal(keep.cpu().bool(), ref_keep) and drops.cpu().tolist() == ref_drops
+        assert nd.item() == int((~ref_keep).sum())
+        sp = slot_pos.cpu()
+        for e in range(E):
+            rows = [(t, k) for t in range(T) for k in range(K) if ic[t, k] == e and ref_keep[t]]
+            assert ck[e].item() == len(rows)
+            assert [sp[t, k].item() for t, k in rows] == list(range(len(rows)))
+        assert (sp[~ref_keep] == -1).all()

@@ -1,0 +1,138 @@
+"""End-to-end GPU checks: the fused MoE layer against the generic PyTorch path, the arena optimizer
+against torch AdamW, and a short training run of the flagship architecture (GPU only)."""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    from nanopysche_b200.ops import _lib
+
+    yield
+    torch.cuda.synchronize()
+    _lib.check_status("after test")
+
+
+@pytest.mark.parametrize("capacity", [1.25, None])
+def test_fused_moe_matches_generic_path(capacity):
+    from nanopysche_b200.models.moe import MoEBase
+    from nanopysche_b200.ops.moe import build_runtime
+
+    torch.manual_seed(0)
+    B, S, D, H, E, K = 2, 256, 256, 256, 4, 2
+    fused = MoEBase(d_model=D, hidden_size=H, num_experts=E, top_k=K, capacity_factor=capacity, dtype=torch.bfloat16,
+                    device="cuda", init_std=0.05)
+    fused.router.cuda()
+    ref = copy.deepcopy(fused).float()
+    build_runtime([fused], tokens=B * S, device=torch.device("cuda"))
+    x = (torch.randn(B, S, D, device="cuda")).bfloat16()
+    xa = x.clone().requires_grad_(True)
+    y = fused(xa)
+    gy = torch.randn_like(y)
+    (y * gy).sum().backward()
+    xb = x.float().requires_grad_(True)
+    yr = ref(xb)
+    (yr * gy.float()).sum().backward()
+    assert fused.last_dropped == ref.last_dropped and fused.total_tokens_routed == B * S
+    if capacity is not None:
+        assert fused.last_dropped > 0 and fused.per_expert_drops.tolist() == ref.per_expert_drops.tolist()
+    assert rel(y, yr) < 2e-2
+    assert rel(xa.grad, xb.grad) < 3e-2
+    for n in ("w1", "w2", "w3"):
+        assert rel(getattr(fused, n).grad, getattr(ref, n).grad) < 3e-2, n
+    assert rel(fused.router.gate.weight.grad, ref.router.gate.weight.grad) < 5e-2
+
+
+def test_flagship_block_matches_fp32_reference_and_trains():
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.engine import prepare_training
+
+    torch.manual_seed(0)
+    cfg = TransformerConfig(vocab_size=2048, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, ffn_hidden=512,
+                            rope_base=10000.0, max_seq_len=256, qk_norm=False, use_moe=True, num_experts=4,
+                            moe_top_k=2, moe_interval=2, moe_offset=1, moe_hidden=256, moe_capacity_factor=None)
+    model = cfg.build(dtype=torch.bfloat16, init_device="cuda")
+    ref = copy.deepcopy(model).float()
+    ids = torch.randint(0, 2048, (2, 256), device="cuda")
+    opt, arena = prepare_training(model, tokens_per_rank=512, lr=2e-3)
+    assert model.blocks["0"].attention._fused_qkv is not None and model.blocks["0"].feed_forward._fused_w13 is not None
+    out = model(ids, labels=ids)
+    outr = ref(ids, labels=ids)
+    assert abs(out["loss"].item() - outr["loss"].item()) < 2e-2 * outr["loss"].item()
+    (out["loss"] + out["aux_loss"]).backward()
+    (outr["loss"] + outr["aux_loss"]).backward()
+    g = dict(arena.named_main_grads())
+    for name in ("blocks.0.attention.w_q.weight", "blocks.0.feed_forward.w2.weight", "blocks.1.moe.w1",
+                 "blocks.0.attention_norm.weight", "embeddings.weight", "lm_head.weight"):
+        assert rel(g[name], dict(ref.named_parameters())[name].grad) < 6e-2, name
+    losses = []
+    opt.step()
+    opt.zero_grad()
+    for _ in range(8):
+        o = model(ids, labels=ids)
+        (o["loss"] + o["aux_loss"]).backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(o["loss"].item())
+    assert losses[-1] < losses[0] - 0.5 and opt.last_grad_norm.item() > 0
+
+
+def test_arena_adamw_gpu_matches_torch():
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.optim.arena import ArenaAdamW, ParamArena
+
+    torch.manual_seed(0)
+    cfg = TransformerConfig(vocab_size=512, d_model=128, n_layers=1, n_heads=2, ffn_hidden=256, max_seq_len=64,
+                            qk_norm=False)
+    m1 = cfg.build(dtype=torch.float32, init_device="cuda")
+    m2 = copy.deepcopy(m1)
+    arena = ParamArena(m1)
+    o1 = ArenaAdamW(arena, lr=1e-2, weight_decay=0.1, max_grad_norm=1.0)
+    decay = [p for n, p in m2.named_parameters() if not ("norm" in n or "emb" in n or p.dim() < 2)]
+    rest = [p for n, p in m2.named_parameters() if ("norm" in n or "emb" in n or p.dim() < 2)]
+    o2 = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": rest, "weight_decay": 0.0}], lr=1e-2,
+                           betas=(0.9, 0.95))
+    ids = torch.randint(0, 512, (2, 64), device="cuda")
+    for _ in range(3):
+        m1(ids, labels=ids)["loss"].backward()
+        o1.step()
+        o1.zero_grad()
+        m2(ids, labels=ids)["loss"].backward()
+        torch.nn.utils.clip_grad_norm_(m2.parameters(), 1.0)
+        o2.step()
+        o2.zero_grad()
+    for (n, p), q in zip(m1.named_parameters(), m2.parameters()):
+        assert torch.allclose(p, q, atol=3e-5), n
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """A flag that nothing sets: the combine kernel gives up after its (short) budget, returns, and
+    the host reads the status; the context stays usable."""
+    import ctypes as C
+
+    from nanopysche_b200.ops import _lib
+
+    T, K, D = 8, 2, 256
+    a = _lib.CombineArgs()
+    rows = torch.zeros(T * K, D, device="cuda", dtype=torch.bfloat16)
+    slot = torch.zeros(T, K, device="cuda", dtype=torch.int32)
+    out = torch.zeros(T, D, device="cuda", dtype=torch.bfloat16)
+    flags = torch.zeros(1, device="cuda", dtype=torch.int32)
+    sent = torch.ones(1, device="cuda", dtype=torch.int32)
+    a.rows, a.slot_pos, a.out = rows.data_ptr(), slot.data_ptr(), out.data_ptr()
+    a.T, a.K, a.D, a.E = T, K, D, 1
+    a.flags, a.sent_to_peer, a.n_ranks, a.epoch, a.limit_ns = flags.data_ptr(), sent.data_ptr(), 1, 5, 200_000_000
+    _lib.check(_lib.lib().np_ep_combine(C.byref(a), C.c_void_p(_lib.stream())), "ep_combine")
+    torch.cuda.synchronize()
+    st = _lib.status()
+    assert st[0] == 2 and st[1] == 11  # flag wait timed out, in the combine kernel
+    _lib.lib().np_status_clear()
+    assert (torch.ones(4, device="cuda") * 2).sum().item() == 8.0

@@ -1,0 +1,340 @@
+"""Trainer loop, callbacks, data, optimizers, checkpointing and fault handling (CPU; faults are
+injected on the host: a stalled rank, a truncated shard, an exception inside a step)."""
+import json
+import os
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import run_distributed
+from nanopysche_b200.checkpoint.distributed import (CheckpointConfig, DistributedCheckpointer,
+                                                    IncrementalCheckpointer, PinnedMemoryStager, PlanCache)
+from nanopysche_b200.config import TransformerConfig
+from nanopysche_b200.fault_tolerance import (CommTimeoutError, FaultTolerantCheckpointer, HangDetector,
+                                             HeartbeatCoordinator)
+from nanopysche_b200.optim import AdamW, DiLoCoCompressor, create_adamw
+from nanopysche_b200.optim.arena import ArenaAdamW, ParamArena
+from nanopysche_b200.train import (CosineWithWarmup, DistributedDataLoader, DistributedDataset, Trainer,
+                                   create_distributed_loader)
+from nanopysche_b200.train.callbacks import (Callback, ConsoleLoggerCallback, ProfilerCallback, SpeedMonitorCallback,
+                                             StabilityMonitorCallback)
+from nanopysche_b200.train.trainer import TrainingConfig
+
+
+def tiny_model(moe=False):
+    torch.manual_seed(0)
+    return TransformerConfig(d_model=32, n_layers=2, n_heads=2, vocab_size=64, max_seq_len=16, ffn_hidden=256,
+                             qk_norm=False, use_moe=moe, num_experts=4, moe_interval=1, moe_hidden=256).build()
+
+
+class Recorder(Callback):
+    def __init__(self):
+        self.events, self.logged = [], []
+
+    def pre_train(self, t): self.events.append("pre_train")
+    def pre_load_batch(self, t): self.events.append("pre_load_batch")
+    def pre_step(self, t, b): self.events.append("pre_step")
+    def post_train_batch(self, t): self.events.append("post_train_batch")
+    def pre_optim_step(self, t): self.events.append("pre_optim_step")
+    def post_step(self, t): self.events.append("post_step")
+    def log_metrics(self, m, s, t): self.logged.append((s, dict(m)))
+    def post_train(self, t): self.events.append("post_train")
+    def on_error(self, t, e): self.events.append("on_error")
+    def close(self, t): self.events.append("close")
+
+
+def test_trainer_trains_and_calls_every_hook(tmp_path):
+    m = tiny_model(moe=True)
+    opt = torch.optim.AdamW(m.parameters(), lr=3e-3)
+    tokens = np.random.RandomState(0).randint(0, 64, size=4000).astype(np.uint16)
+    loader = create_distributed_loader(tokens, 2, 16, shuffle=False)
+    rec = Recorder()
+    tc = TrainingConfig(global_batch_size=2 * 16 * 2, micro_batch_size=2, sequence_length=16, max_steps=6,
+                        log_interval=2, save_interval=0, dtype=torch.float32, vocab_size=64)
+    assert tc.gradient_accumulation_steps == 2
+    tr = Trainer(tc, m, opt, CosineWithWarmup(opt, 1, 6), loader,
+                 [rec, SpeedMonitorCallback(), StabilityMonitorCallback(), ConsoleLoggerCallback()])
+    tr.fit()
+    assert tr.step == 6 and tr.tokens_seen == 6 * 64
+    assert rec.events[0] == "pre_train" and rec.events[-2:] == ["post_train", "close"]
+    assert rec.events[1:7] == ["pre_load_batch", "pre_step", "post_train_batch", "pre_optim_step", "post_step",
+                               "pre_load_batch"]
+    steps = [s for s, _ in rec.logged]
+    assert steps == [2, 4, 6]
+    last = rec.logged[-1][1]
+    for k in ("train/CE loss", "train/PPL", "optim/LR", "optim/total grad norm", "throughput/total tokens",
+              "throughput/device/TPS", "throughput/device/MFU", "spike/SpikeScore", "throughput/step_time (s)"):
+        assert k in last, k
+    assert rec.logged[-1][1]["train/CE loss"] < rec.logged[0][1]["train/CE loss"]
+
+
+def test_trainer_synthetic_batches_and_error_hook():
+    m = tiny_model()
+    opt = torch.optim.SGD(m.parameters(), lr=0.1)
+    rec = Recorder()
+
+    class Boom(Callback):
+        def post_train_batch(self, t):
+            if t.step == 1:
+                raise RuntimeError("injected failure")
+
+    tc = TrainingConfig(global_batch_size=32, micro_batch_size=2, sequence_length=16, max_steps=4, log_interval=1,
+                        save_interval=0, dtype=torch.float32, vocab_size=64)
+    tr = Trainer(tc, m, opt, None, None, [rec, Boom()])
+    with pytest.raises(RuntimeError, match="injected"):
+        tr.fit()
+    assert "on_error" in rec.events and rec.events[-1] == "close" and tr.step == 1
+
+
+def test_dataset_and_loader_iterator_protocol():
+    tokens = np.arange(1000, dtype=np.uint16)
+    ds = DistributedDataset(tokens, 10)
+    ids, labels = ds[3]
+    assert len(ds) == 99 and ids.tolist() == list(range(30, 40)) and torch.equal(ids, labels)
+    dl = DistributedDataLoader(ds, 4, shuffle=False, dp_rank=1, dp_world=2)
+    a, _ = next(dl)
+    assert a.shape == (4, 10) and a[0, 0].item() == 10  # rank 1 of 2 takes odd samples
+    n = len(dl)
+    for _ in range(n + 2):  # runs past the end of an epoch without StopIteration
+        next(dl)
+    assert dl.epoch == 1 and dl.state_dict()["batches_served"] == n + 3
+
+
+def test_adamw_matches_torch_and_param_groups():
+    torch.manual_seed(0)
+    w1 = torch.nn.Parameter(torch.randn(8, 8))
+    w2 = torch.nn.Parameter(w1.detach().clone())
+    a = AdamW([w1], lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1)
+    b = torch.optim.AdamW([w2], lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
+    for _ in range(5):
+        g = torch.randn(8, 8)
+        w1.grad, w2.grad = g.clone(), g.clone()
+        a.step()
+        b.step()
+    assert torch.allclose(w1, w2, atol=1e-6)
+    opt = create_adamw(tiny_model())
+    decay, no_decay = opt.param_groups
+    assert decay["weight_decay"] == 0.1 and no_decay["weight_decay"] == 0.0
+    assert all(p.dim() >= 2 for p in decay["params"]) and any(p.dim() == 1 for p in no_decay["params"])
+
+
+def test_arena_adamw_cpu_matches_torch_adamw():
+    m1, m2 = tiny_model(), tiny_model()
+    arena = ParamArena(m1)
+    opt1 = ArenaAdamW(arena, lr=1e-2, weight_decay=0.1, max_grad_norm=1.0)
+    decay = [p for n, p in m2.named_parameters() if not ("norm" in n or "emb" in n or "bias" in n or p.dim() < 2)]
+    rest = [p for n, p in m2.named_parameters() if ("norm" in n or "emb" in n or "bias" in n or p.dim() < 2)]
+    opt2 = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": rest, "weight_decay": 0.0}],
+                             lr=1e-2, betas=(0.9, 0.95), eps=1e-8)
+    x = torch.randint(0, 64, (2, 8))
+    for _ in range(3):
+        m1(x, labels=x)["loss"].backward()
+        assert all(p.grad is None for p in m1.parameters())  # gradients live in the arena
+        opt1.step()
+        opt1.zero_grad()
+        m2(x, labels=x)["loss"].backward()
+        torch.nn.utils.clip_grad_norm_(m2.parameters(), 1.0)
+        opt2.step()
+        opt2.zero_grad()
+    for (n, p), q in zip(m1.named_parameters(), m2.parameters()):
+        assert torch.allclose(p, q, atol=2e-5), n
+    sd = opt1.state_dict()
+    opt1.load_state_dict(sd)
+    assert sd["step"] == 3 and arena.num_params() == sum(p.numel() for p in m2.parameters())
+
+
+def test_diloco_compressor_roundtrip_and_error_feedback():
+    ps = [torch.nn.Parameter(torch.zeros(1000))]
+    before = torch.random.get_rng_state()
+    c = DiLoCoCompressor(ps, compression_rank=16)
+    assert torch.equal(before, torch.random.get_rng_state())  # the global RNG is left alone
+    g = torch.randn(1000)
+    comp, scale = c.compress(g)
+    assert comp.shape == (16,)
+    rec = c.decompress(comp, scale, 1000)
+    assert rec.shape == (1000,) and torch.allclose(c.error_buffer, -rec)
+    out = c.all_reduce_gradients(g)
+    assert out.shape == (1000,)
+    sd = c.compress_state_dict({"a": torch.randn(10, 50), "b": torch.randn(500)})
+    assert sd["total_params"] == 1000 and sd["shapes"]["a"] == (10, 50)
+
+
+# ------------------------------------------------------------------ checkpoints
+def test_checkpoint_layout_roundtrip_and_retention(tmp_path):
+    m = tiny_model()
+    opt = torch.optim.AdamW(m.parameters(), lr=1e-2)
+    sched = CosineWithWarmup(opt, 2, 10)
+    x = torch.randint(0, 64, (2, 8))
+    m(x, labels=x)["loss"].backward()
+    opt.step()
+    sched.step()
+    ck = DistributedCheckpointer(CheckpointConfig(save_dir=str(tmp_path), keep_last_n=2))
+    ck.dataloader_tracker.update(4)
+    for step in (10, 20, 30):
+        d = ck.save(step, m, opt, scheduler=sched, extra={"tokens_seen": step * 16})
+    assert sorted(os.listdir(tmp_path)) == ["step_000020", "step_000030"]
+    files = sorted(os.listdir(d))
+    assert files == ["metadata.json", "rank_0000_dataloader.json", "rank_0000_model.pt", "rank_0000_optimizer.pt",
+                     "rank_0000_rng.pt", "rank_0000_scheduler.pt"]
+    meta = json.load(open(os.path.join(d, "metadata.json")))
+    assert meta["step"] == 30 and meta["version"] == 2 and meta["world_size"] == 1 and not meta["incremental"]
+    assert "embeddings.weight" in meta["model_keys"] and meta["extra"]["tokens_seen"] == 480
+    assert ck.latest_step() == 30
+    m2 = tiny_model()
+    with torch.no_grad():
+        for p in m2.parameters():
+            p.add_(1.0)
+    opt2 = torch.optim.AdamW(m2.parameters(), lr=1e-2)
+    sched2 = CosineWithWarmup(opt2, 2, 10)
+    torch.manual_seed(123)
+    got = ck.load(model=m2, optimizer=opt2, scheduler=sched2)
+    assert got["step"] == 30 and sched2.last_epoch == sched.last_epoch
+    for p, q in zip(m.parameters(), m2.parameters()):
+        assert torch.equal(p, q)
+    assert opt2.state_dict()["state"][0]["exp_avg"].abs().sum() > 0
+    assert ck.dataloader_tracker.samples_seen == 4
+    # overwrite vs suffix
+    d2 = ck.save(30, m, opt)
+    assert d2.endswith("step_000030_1")
+
+
+def test_incremental_checkpoint_chain(tmp_path):
+    m = tiny_model()
+    ck = DistributedCheckpointer(CheckpointConfig(save_dir=str(tmp_path), incremental=True, keep_last_n=10,
+                                                  full_save_interval=10, incremental_threshold=0.01))
+    ck.save(1, m)
+    with torch.no_grad():
+        m.lm_head.weight.mul_(2.0)
+        m.embeddings.weight.add_(1e-7)  # below the relative-change threshold
+    d = ck.save(2, m)
+    meta = json.load(open(os.path.join(d, "metadata.json")))
+    delta = torch.load(os.path.join(d, "rank_0000_model.pt"), weights_only=False)
+    assert meta["incremental"] and meta["base_checkpoint"] == "step_000001"
+    assert "lm_head.weight" in delta and "embeddings.weight" not in delta and len(delta) < len(m.state_dict())
+    m2 = tiny_model()
+    ck.load(model=m2)
+    assert torch.equal(m2.lm_head.weight, m.lm_head.weight)
+    inc = IncrementalCheckpointer(0.01, 3)
+    assert inc.should_save_full(0) and not inc.should_save_full(1) and inc.should_save_full(3)
+    assert len(IncrementalCheckpointer._hash(torch.randn(100))) == 16
+
+
+def test_async_save_and_helpers(tmp_path):
+    m = tiny_model()
+    ck = DistributedCheckpointer(CheckpointConfig(save_dir=str(tmp_path), async_saves=True))
+    fut = ck.save_async(5, m)
+    ck.wait()
+    assert fut.done() and os.path.isfile(tmp_path / "step_000005" / "metadata.json")
+    ck.close()
+    st = PinnedMemoryStager(enabled=True).stage_state_dict({"a": torch.ones(3), "n": {"b": torch.zeros(2)}, "k": 1})
+    assert st["a"].device.type == "cpu" and st["n"]["b"].shape == (2,) and st["k"] == 1
+    pc = PlanCache()
+    sd = m.state_dict()
+    assert pc.get(sd) is pc.get(sd) and pc.get(sd).total_bytes == sum(v.numel() * 4 for v in sd.values())
+
+
+def _ckpt_worker(rank, world, save_dir):
+    m = tiny_model()
+    with torch.no_grad():
+        m.lm_head.weight.fill_(float(rank))
+    ck = DistributedCheckpointer(CheckpointConfig(save_dir=save_dir))
+    d = ck.save(7, m)
+    files = sorted(os.listdir(d))
+    assert "rank_0000_model.pt" in files and "rank_0001_model.pt" in files and "metadata.json" in files
+    assert not any(f.startswith(".tmp") for f in os.listdir(save_dir))
+    m2 = tiny_model()
+    meta = ck.load(model=m2)
+    assert meta["world_size"] == 2 and float(m2.lm_head.weight[0, 0]) == float(rank)
+    return True
+
+
+def test_checkpoint_two_ranks_single_directory(tmp_path):
+    assert all(run_distributed(_ckpt_worker, 2, str(tmp_path)))
+
+
+def test_fault_tolerant_checkpointer_skips_truncated_shard(tmp_path):
+    m = tiny_model()
+    opt = torch.optim.AdamW(m.parameters(), lr=1e-2)
+    ft = FaultTolerantCheckpointer(str(tmp_path), save_interval=5, keep_last_n=5)
+    assert ft.save(3, m, opt) is None and ft.should_save(5)
+    ft.save(5, m, opt)
+    with torch.no_grad():
+        m.lm_head.weight.add_(1.0)
+    ft.save(10, m, opt)
+    meta = json.load(open(tmp_path / "step_000010" / "metadata.json"))
+    assert set(meta) == {"step", "timestamp", "extra"}
+    with open(tmp_path / "step_000010" / "rank_0000_model.pt", "r+b") as f:  # simulate a crash mid-write
+        f.truncate(100)
+    m2 = tiny_model()
+    assert ft.resume(m2, torch.optim.AdamW(m2.parameters())) == 5
+    os.makedirs(tmp_path / "step_000099")  # no metadata: ignored
+    assert ft.find_latest_checkpoint().endswith("step_000005")
+    assert FaultTolerantCheckpointer(str(tmp_path / "empty")).resume(m2) == 0
+
+
+# ------------------------------------------------------------------ hang detection
+def test_hang_detector_fires_and_heartbeat_prevents():
+    fired = []
+    hd = HangDetector(timeout=0.3, check_interval=0.05, on_hang=lambda: fired.append(1), abort_on_hang=False)
+    hd.start()
+    for _ in range(8):
+        time.sleep(0.05)
+        hd.heartbeat()
+    assert not fired
+    time.sleep(0.6)
+    hd.stop()
+    assert fired and hd.hang_detected
+    with pytest.raises(CommTimeoutError):
+        HangDetector.check_collective_timeout(lambda: (_ for _ in ()).throw(RuntimeError("NCCL watchdog timeout")))
+    with pytest.raises(ValueError):
+        HangDetector.check_collective_timeout(lambda: (_ for _ in ()).throw(ValueError("other")))
+
+
+def test_heartbeat_coordinator_detects_stalled_rank():
+    from nanopysche_b200.fault_tolerance.hang_detection import _DictStore
+
+    store = _DictStore()
+    stalls = []
+    ranks = [HeartbeatCoordinator(check_interval=0.05, hang_timeout=0.2, store=store, rank=r, world_size=3,
+                                  on_stall=stalls.append) for r in range(3)]
+    ranks[0].start()
+    for step in range(1, 12):
+        ranks[0].heartbeat(step)
+        ranks[1].heartbeat(step)  # rank 2 never beats: its message is "dropped"
+        time.sleep(0.05)
+    ranks[0].stop()
+    assert stalls and stalls[0] == [2]
+
+
+def _hb_worker(rank, world):
+    hb = HeartbeatCoordinator(check_interval=0.05, hang_timeout=0.3)
+    assert hb.world_size == world
+    for s in range(1, 6):
+        if rank == 0 or s < 2:  # rank 1 stops making progress after its first step
+            hb.heartbeat(s)
+        time.sleep(0.1)
+    stalled = hb.sync_heartbeats() if rank == 0 else []
+    time.sleep(0.35)
+    if rank == 0:
+        hb.heartbeat(99)
+        stalled = hb.sync_heartbeats()
+    import torch.distributed as dist
+    dist.barrier()
+    return stalled
+
+
+def test_heartbeat_over_process_group_store():
+    res = run_distributed(_hb_worker, 2)
+    assert res[0] == [1]
+
+
+def test_profiler_callback_window(tmp_path):
+    m = tiny_model()
+    opt = torch.optim.SGD(m.parameters(), lr=0.01)
+    prof = ProfilerCallback(save_dir=str(tmp_path), skip_first=1, warmup=0, active=2)
+    tc = TrainingConfig(global_batch_size=32, micro_batch_size=2, sequence_length=16, max_steps=5, log_interval=0,
+                        save_interval=0, dtype=torch.float32, vocab_size=64)
+    Trainer(tc, m, opt, None, None, [prof]).fit()
+    assert any(f.endswith(".chrome_trace.json.gz") for f in os.listdir(tmp_path))
