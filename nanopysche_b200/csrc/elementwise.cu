@@ -8,6 +8,7 @@
 //  model/transformer.py:451-458, optim/adamw.py:74-121, train/trainer.py:280-284).
 // All are single-pass over HBM with 16-byte vector accesses.
 #include "common.cuh"
+#include "noalloc.h"
 
 namespace {
 
@@ -599,5 +600,45 @@ NP_API int np_cast_f32_bf16(const float* x, void* y, long long n, void* stream) 
   if (n <= 0) return 0;
   cast_f32_to_bf16_kernel<<<grid_for(n / 4 + 1, 256, GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
       x, (__nv_bfloat16*)y, n);
+  CHECK_LAUNCH();
+}
+
+// ------------------------------------------------------------------ allocation-free variant
+// Scratch for np_rmsnorm_bwd_noalloc: per-CTA partial sums of the weight gradient, [parts, cols].
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address; the
+// address each device uses is resolved once with cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_noalloc_scratch[NP_NOALLOC_MAX_PARTS * NP_NOALLOC_MAX_COLS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+NP_API int np_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float* w, const float* rstd, const void* dres,
+                                  void* dx, float* dw, int rows, int cols, int accumulate_dw, void* stream) {
+  if (cols % 8) return 1;
+  if (cols > NP_NOALLOC_MAX_COLS) return 3;  // beyond the static scratch: use np_rmsnorm_bwd with your own buffer
+  if (rows <= 0) return 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return 400 + (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return 3;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // one-time set-up for this device (it is the current one): device address of the static array
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) return 400 + (int)e;
+    g_noalloc_ptr[dev] = p;
+  }
+  float* scratch = g_noalloc_ptr[dev];
+  const int grid = np_rmsnorm_bwd_parts(rows);  // <= NP_NOALLOC_MAX_PARTS
+  cudaStream_t s = (cudaStream_t)stream;
+#define RB(V) rmsnorm_bwd_kernel<V><<<grid, NT, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, \
+                                                       (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, rows, cols)
+  if (cols <= NT * 8) RB(1);
+  else RB(2);
+#undef RB
+  // every partial row [0, grid) x [0, cols) was just written by the kernel above, so nothing stale is read
+  colsum_kernel<<<(cols + 255) / 256, 256, 0, s>>>(scratch, dw, grid, cols, accumulate_dw);
   CHECK_LAUNCH();
 }
