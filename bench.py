@@ -142,6 +142,18 @@ def run_ours(args, rank, local, world):
         opt.zero_grad(set_to_none=True)
         last["loss"] = out["loss"].detach()
 
+    from nanopysche_b200.engine import GraphedTrainStep
+
+    graphed = None
+    if not args.no_graph:
+        # the whole step (forward + backward + clip + AdamW) replayed as one CUDA graph
+        l0 = _lib.LAUNCHES
+        graphed = GraphedTrainStep(model, opt, devb[0], warmup=2).capture()
+        per_step = (_lib.LAUNCHES - l0) // 3  # two eager warm-up steps + the captured one
+
+        def train_step(ids):  # noqa: F811
+            last["loss"] = graphed.step(ids)
+
     for i in range(args.warmup):
         train_step(devb[i % n_batches])
     torch.cuda.synchronize()
@@ -151,13 +163,13 @@ def run_ours(args, rank, local, world):
         sampler.start()
     l0 = _lib.LAUNCHES
     ms = timed(lambda i: train_step(devb[i % n_batches]), args.steps, world, dev)
-    launches = _lib.LAUNCHES - l0
+    launches = (_lib.LAUNCHES - l0) if graphed is None else per_step * args.steps
     clocks = sampler.stop() if rank == 0 else {}
     loss_dev = float(last["loss"].detach())
 
     def e2e_step(i):
-        ids = host[i % n_batches].to(dev, non_blocking=True)
-        train_step(ids)
+        ids = host[i % n_batches]
+        train_step(ids if graphed is not None else ids.to(dev, non_blocking=True))  # graph: copied into its static input
         last["host_loss"] = last["loss"].item()
 
     ms_e2e = timed(e2e_step, args.steps, world, dev)
@@ -170,7 +182,7 @@ def run_ours(args, rank, local, world):
         "dtype": "bf16", "data": "synthetic uniform random tokens, random-init N(0,0.02) weights",
         "config": {"model": "1B MoE decoder: 16L d2048 16Q/8KV hd128, 8 experts x 2816 top-2, cf 1.25, vocab 32000",
                    "global_batch": c["batch_per_gpu"] * world, "seq_len": c["seq_len"], "parallelism": f"ep{world}",
-                   "step": "forward+backward+clip+AdamW (fp32 masters)",
+                   "step": "forward+backward+clip+AdamW (fp32 masters)" + ("" if args.no_graph else ", replayed as one CUDA graph"),
                    "l2": "per-step working set (>5 GB of weights, gradients and activations) exceeds the 126 MB L2",
                    "capacity": "int(1.25*T/E) per expert, whole-token drop in index order (reference rule)"},
         "clocks": clocks,
@@ -235,7 +247,7 @@ def run_reference(args, rank, local, world):
         def __next__(self):
             b = self.batches[self.i % len(self.batches)]
             self.i += 1
-            return b, b
+            return {"input_ids": b, "labels": b}
 
     devb = [h.to(dev) for h in host]
     trainer = Trainer(tc, model, opt, None, Loader(devb), [])
@@ -274,6 +286,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a graph")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device visible"}))

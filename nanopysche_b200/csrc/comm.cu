@@ -22,12 +22,89 @@ struct PeerPtrs {
   void* p[MAX_PEERS];
 };
 
-__global__ void symm_barrier_kernel(PeerPtrs flags, int my_rank, int n, int epoch, unsigned long long limit_ns) {
+__global__ void symm_barrier_kernel(PeerPtrs flags, int my_rank, int n, int epoch, const int* epoch_base,
+                                    unsigned long long limit_ns) {
   const int t = threadIdx.x;
+  const int ep = epoch + (epoch_base ? *epoch_base : 0);
   if (t < n) {
     __threadfence_system();
-    np::st_release_sys(reinterpret_cast<int*>(flags.p[t]) + my_rank, epoch);
-    np::wait_flag_ge(reinterpret_cast<int*>(flags.p[my_rank]) + t, epoch, limit_ns, KID_BARRIER, t);
+    np::st_release_sys(reinterpret_cast<int*>(flags.p[t]) + my_rank, ep);
+    np::wait_flag_ge(reinterpret_cast<int*>(flags.p[my_rank]) + t, ep, limit_ns, KID_BARRIER, t);
+  }
+}
+
+// Small all-reduce (sum) over peer memory: every rank stores its vector into slot [my_rank] of every
+// peer's staging buffer, releases an epoch flag, waits for all peers' flags and sums the n slots.
+// staging: [n ranks][count] floats per rank; one CTA per 1024 elements would be overkill - the vectors
+// this is used for (gradient-norm partials, fp32 norm / router gradients) are a few MB at most.
+__global__ void __launch_bounds__(256) symm_allreduce_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                             PeerPtrs staging, PeerPtrs flags, int* __restrict__ ctr,
+                                                             long long half_elems, long long count, int my_rank, int n,
+                                                             int epoch,
+                                                             const int* epoch_base, float scale,
+                                                             unsigned long long limit_ns) {
+  const int ep = epoch + (epoch_base ? *epoch_base : 0);
+  // ctr[1] counts the calls: its parity picks one of two staging halves, so a fast rank that is already
+  // in the next call never overwrites a slot a slow rank is still summing
+  const size_t half = (size_t)(ctr[1] & 1) * (size_t)half_elems;
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  for (long long i = tid; i < count; i += nth) {
+    const float v = src[i];
+    for (int r = 0; r < n; ++r) reinterpret_cast<float*>(staging.p[r])[half + (size_t)my_rank * count + i] = v;
+  }
+  // grid-wide: last CTA to finish its stores releases the flags (threadfence-reduction pattern)
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(ctr, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if ((int)threadIdx.x < n) np::st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + my_rank, ep);
+    if (threadIdx.x == 0) { ctr[0] = 0; ctr[1] += 1; }
+  }
+  // every CTA waits for all ranks' contributions, then reduces its slice
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < n) {
+    if (!np::wait_flag_ge(reinterpret_cast<int*>(flags.p[my_rank]) + threadIdx.x, ep, limit_ns, KID_BARRIER,
+                          100 + threadIdx.x))
+      s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const float* mine = reinterpret_cast<const float*>(staging.p[my_rank]) + half;
+  for (long long i = tid; i < count; i += nth) {
+    float acc = 0.f;
+    for (int r = 0; r < n; ++r) acc += mine[(size_t)r * count + i];
+    dst[i] = acc * scale;
+  }
+}
+
+// All-gather as peer stores: this rank's shard (vecs x 16 bytes) is written into every rank's gather
+// buffer at the shard's offset, then flag [my_rank] is released on every rank. The consumer (a GEMM
+// with a per-M-block flag wait) can start on a shard as soon as that shard's flag arrives.
+__global__ void __launch_bounds__(256) allgather_push_kernel(const uint4* __restrict__ src, PeerPtrs dst,
+                                                             long long vecs, long long dst_off_vecs, PeerPtrs flags,
+                                                             int* __restrict__ ctr, int my_rank, int n, int epoch,
+                                                             const int* epoch_base) {
+  const int ep = epoch + (epoch_base ? *epoch_base : 0);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < vecs;
+       i += (long long)gridDim.x * blockDim.x) {
+    const uint4 v = src[i];
+    for (int r = 0; r < n; ++r) reinterpret_cast<uint4*>(dst.p[r])[dst_off_vecs + i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(ctr, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if ((int)threadIdx.x < n) np::st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + my_rank, ep);
+    if (threadIdx.x == 0) *ctr = 0;
   }
 }
 
@@ -65,8 +142,10 @@ __global__ void __launch_bounds__(256) zero_adamw_bcast_kernel(float* __restrict
                                                                float* __restrict__ m, float* __restrict__ v,
                                                                PeerPtrs w16, int n, long long lo, long long cnt,
                                                                float lr, float b1, float b2, float eps, float wd,
-                                                               float bc1, float bc2, const float* __restrict__ gscale) {
+                                                               float bc1, float bc2, const float* __restrict__ gscale,
+                                                               const float* __restrict__ hyper) {
   const float gs = gscale ? gscale[0] : 1.f;
+  if (hyper) { lr = hyper[0]; bc1 = hyper[1]; bc2 = hyper[2]; }
   const long long nvec = cnt >> 2;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
@@ -117,13 +196,50 @@ NP_API int np_symm_close(void* ptr) { return (int)cudaIpcCloseMemHandle(ptr); }
 NP_API int np_symm_free(void* ptr) { return (int)cudaFree(ptr); }
 
 // flag_ptrs[r] = base of rank r's flag array (n ints per barrier slot).
-NP_API int np_symm_barrier(void* const* flag_ptrs, int my_rank, int n, int epoch, unsigned long long limit_ns,
-                           void* stream) {
+NP_API int np_symm_barrier(void* const* flag_ptrs, int my_rank, int n, int epoch, const int* epoch_base,
+                           unsigned long long limit_ns, void* stream) {
   if (n > MAX_PEERS) return 1;
   PeerPtrs f;
   for (int i = 0; i < n; ++i) f.p[i] = flag_ptrs[i];
-  symm_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, my_rank, n, epoch,
+  symm_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, my_rank, n, epoch, epoch_base,
                                                           limit_ns ? limit_ns : NP_WAIT_LIMIT_NS);
+  CHECK_LAUNCH();
+}
+
+// dst[i] = scale * sum over ranks of src[i]; staging_ptrs[r] = rank r's staging buffer of 2 * half_elems floats
+// (half_elems >= n * count), flag_ptrs[r] = rank r's n-int flag array, ctr = two zeroed local ints.
+// src/dst may alias.
+NP_API int np_symm_allreduce(const float* src, float* dst, void* const* staging_ptrs, void* const* flag_ptrs,
+                             int* ctr, long long half_elems, long long count, int my_rank, int n, int epoch,
+                             const int* epoch_base,
+                             float scale, unsigned long long limit_ns, void* stream) {
+  if (n > MAX_PEERS || n > 256 || (long long)n * count > half_elems) return 1;
+  if (count <= 0) return 0;
+  PeerPtrs st, fl;
+  for (int i = 0; i < n; ++i) { st.p[i] = staging_ptrs[i]; fl.p[i] = flag_ptrs[i]; }
+  long long g = (count + 255) / 256;
+  if (g > 148) g = 148;  // all CTAs are co-resident (they wait on one another through the counter)
+  symm_allreduce_kernel<<<(int)g, 256, 0, (cudaStream_t)stream>>>(src, dst, st, fl, ctr, half_elems, count, my_rank, n,
+                                                                  epoch, epoch_base, scale,
+                                                                  limit_ns ? limit_ns : NP_WAIT_LIMIT_NS);
+  CHECK_LAUNCH();
+}
+
+// src: this rank's shard (bytes, multiple of 16); gather_ptrs[r]: rank r's gather buffer; the shard lands at
+// byte offset my_rank * bytes; flag_ptrs[r]: rank r's n-int flag array; ctr: a zeroed local int.
+NP_API int np_allgather_push(const void* src, void* const* gather_ptrs, long long bytes, void* const* flag_ptrs,
+                             int* ctr, int my_rank, int n, int epoch, const int* epoch_base, int max_ctas,
+                             void* stream) {
+  if (n > MAX_PEERS || (bytes & 15) || (((uintptr_t)src) & 15)) return 1;
+  if (bytes <= 0) return 0;
+  PeerPtrs d, f;
+  for (int i = 0; i < n; ++i) { d.p[i] = gather_ptrs[i]; f.p[i] = flag_ptrs[i]; }
+  const long long vecs = bytes >> 4;
+  long long g = (vecs + 255) / 256;
+  const int cap = max_ctas > 0 ? max_ctas : 148 * 2;
+  if (g > cap) g = cap;
+  allgather_push_kernel<<<(int)g, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, d, vecs, (long long)my_rank * vecs,
+                                                                  f, ctr, my_rank, n, epoch, epoch_base);
   CHECK_LAUNCH();
 }
 
@@ -141,13 +257,13 @@ NP_API int np_zero_reduce(void* const* grad_ptrs, int n, long long lo, long long
 
 NP_API int np_zero_adamw_bcast(float* p, const float* g, float* m, float* v, void* const* w16_ptrs, int n,
                                long long lo, long long cnt, float lr, float b1, float b2, float eps, float wd,
-                               int step, const float* gscale, void* stream) {
+                               int step, const float* gscale, const float* hyper, void* stream) {
   if (n > MAX_PEERS || (lo & 3) || (cnt & 3)) return 1;
   if (cnt <= 0) return 0;
   PeerPtrs w;
   for (int i = 0; i < n; ++i) w.p[i] = w16_ptrs[i];
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
   zero_adamw_bcast_kernel<<<148 * 4, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, w, n, lo, cnt, lr, b1, b2, eps, wd,
-                                                                    bc1, bc2, gscale);
+                                                                    bc1, bc2, gscale, hyper);
   CHECK_LAUNCH();
 }

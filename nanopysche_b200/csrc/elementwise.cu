@@ -393,8 +393,9 @@ __global__ void __launch_bounds__(NT) xent_bwd_kernel(const __nv_bfloat16* __res
 __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
                              float* __restrict__ v, __nv_bfloat16* __restrict__ w16, long long n, float lr,
                              float b1, float b2, float eps, float wd, float bc1, float bc2,
-                             const float* __restrict__ gscale) {
+                             const float* __restrict__ gscale, const float* __restrict__ hyper) {
   const float gs = gscale ? gscale[0] : 1.f;
+  if (hyper) { lr = hyper[0]; bc1 = hyper[1]; bc2 = hyper[2]; }  // device-resident schedule (graph replay)
   const long long nvec = n >> 2;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
@@ -577,11 +578,11 @@ NP_API int np_xent_bwd(const void* logits, const long long* labels, const float*
 }
 
 NP_API int np_adamw(float* p, const float* g, float* m, float* v, void* w16, long long n, float lr, float b1,
-                    float b2, float eps, float wd, int step, const float* gscale, void* stream) {
+                    float b2, float eps, float wd, int step, const float* gscale, const float* hyper, void* stream) {
   if (n <= 0) return 0;
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
   adamw_kernel<<<grid_for(n / 4 + 1, 256, GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
-      p, g, m, v, (__nv_bfloat16*)w16, n, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+      p, g, m, v, (__nv_bfloat16*)w16, n, lr, b1, b2, eps, wd, bc1, bc2, gscale, hyper);
   CHECK_LAUNCH();
 }
 

@@ -50,6 +50,7 @@ struct GemmParams {
   int* const* done_flag_ptr;  // [flags] peer flag word to release when a destination completes
   const void* Cin;            // accumulate source (same dtype as C), rows indexed like a dense C
   long long ldcin;
+  const int* epoch_base;      // optional device counter added to `epoch` (keeps epochs valid under graph replay)
 };
 
 template <class F>
@@ -108,6 +109,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int epoch = p.epoch + (p.epoch_base ? *p.epoch_base : 0);
 
   const int m_blocks = (p.M + BM - 1) / BM;
   const int bn_out = (p.epilogue == 1) ? BN / 2 : BN;  // output columns per tile
@@ -152,7 +154,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (p.mode != 1) return BM;
     if (p.ready_flags) {
       const int fi = p.mblk_flag ? p.mblk_flag[tl.m_blk] : 0;
-      if (!np::wait_flag_ge(p.ready_flags + fi, p.epoch, p.flag_limit_ns, KID_GEMM, 100 + role)) {
+      if (!np::wait_flag_ge(p.ready_flags + fi, epoch, p.flag_limit_ns, KID_GEMM, 100 + role)) {
         *abort_flag = 1;
         return -1;
       }
@@ -408,7 +410,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int done = atomicAdd(&p.done_counters[fi], 1) + 1;
           if (done == 4 * n_blocks * p.done_expected[fi]) {  // done_expected counts M blocks
             __threadfence_system();
-            np::st_release_sys(p.done_flag_ptr[fi], p.epoch);
+            np::st_release_sys(p.done_flag_ptr[fi], epoch);
           }
         }
       }
@@ -472,6 +474,7 @@ struct NpGemmArgs {
   int bn;        // 0 = choose, else 128 or 256
   int max_ctas;  // 0 = all SMs
   const void* Cin; long long ldcin;  // optional accumulate source (defaults to C when accumulate != 0)
+  const int* epoch_base;             // optional device counter added to `epoch`
 };
 
 template <int BN, int STAGES>
@@ -502,6 +505,7 @@ static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
   p.done_counters = a.done_counters; p.done_expected = a.done_expected; p.done_flag_ptr = a.done_flag_ptr;
   p.Cin = a.Cin ? a.Cin : (a.accumulate ? a.C : nullptr);
   p.ldcin = a.Cin ? a.ldcin : a.ldc;
+  p.epoch_base = a.epoch_base;
 
   constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
   static bool attr_set = false;

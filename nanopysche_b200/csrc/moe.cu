@@ -354,6 +354,7 @@ struct DispatchParams {
   int* done_ctr;               // local CTA counter (zero between launches)
   int epoch;
   int write_meta;              // 1: also write row_dst / mblk_rows / src_blocks (forward); 0: rows only
+  const int* epoch_base;       // optional device counter added to `epoch`
 };
 
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(const DispatchParams p) {
@@ -460,7 +461,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const DispatchParams p
   __threadfence_system();
   __syncthreads();
   for (int peer = threadIdx.x; peer < p.n_ranks; peer += blockDim.x)
-    np::st_release_sys(p.peer_flags[peer] + p.my_rank, p.epoch);
+    np::st_release_sys(p.peer_flags[peer] + p.my_rank, p.epoch + (p.epoch_base ? *p.epoch_base : 0));
   if (threadIdx.x == 0) *p.done_ctr = 0;
 }
 
@@ -479,6 +480,7 @@ struct CombineParams {
   const int* sent_to_peer;     // [n_ranks] rows this rank sent to each peer (0 = nothing to wait for)
   int n_ranks, epoch;
   unsigned long long limit_ns;
+  const int* epoch_base;
 };
 
 __global__ void __launch_bounds__(256) ep_combine_kernel(const CombineParams p) {
@@ -487,7 +489,8 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const CombineParams p) 
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
     if ((int)threadIdx.x < p.n_ranks && p.sent_to_peer[threadIdx.x] > 0) {
-      if (!np::wait_flag_ge(p.flags + threadIdx.x, p.epoch, p.limit_ns, KID_COMBINE, threadIdx.x)) s_ok = 0;
+      if (!np::wait_flag_ge(p.flags + threadIdx.x, p.epoch + (p.epoch_base ? *p.epoch_base : 0), p.limit_ns, KID_COMBINE,
+                            threadIdx.x)) s_ok = 0;
     }
     __syncthreads();
     if (!s_ok) return;
@@ -629,7 +632,7 @@ struct NpDispatchArgs {
   int T, K, D, E, E_local, n_ranks, my_rank, region_rows, quant;
   void* const* peer_rows; float* const* peer_scales; long long* const* peer_row_dst;
   int* const* peer_mblk_rows; int* const* peer_src_blocks; int* const* peer_flags;
-  int* done_ctr; int epoch; int write_meta; int max_ctas;
+  int* done_ctr; int epoch; int write_meta; int max_ctas; const int* epoch_base;
 };
 NP_API int np_ep_dispatch(const NpDispatchArgs* a, void* stream) {
   if (a->D % 128 || a->region_rows % 128 || a->E % a->E_local || (a->quant && a->D % 256)) return 1;
@@ -640,6 +643,7 @@ NP_API int np_ep_dispatch(const NpDispatchArgs* a, void* stream) {
   p.peer_rows = a->peer_rows; p.peer_scales = a->peer_scales; p.peer_row_dst = a->peer_row_dst;
   p.peer_mblk_rows = a->peer_mblk_rows; p.peer_src_blocks = a->peer_src_blocks; p.peer_flags = a->peer_flags;
   p.done_ctr = a->done_ctr; p.epoch = a->epoch; p.write_meta = a->write_meta;
+  p.epoch_base = a->epoch_base;
   const int items = a->T * a->K + a->E * 128;
   int grid = (items + 7) / 8;
   const int cap = a->max_ctas > 0 ? a->max_ctas : 148 * 4;
@@ -653,6 +657,7 @@ struct NpCombineArgs {
   const void* rows; const int* slot_pos; const float* weights; const void* add1; const void* add2;
   const float* dl; const float* wg; void* out; int T, K, D, E;
   const int* flags; const int* sent_to_peer; int n_ranks, epoch; unsigned long long limit_ns;
+  const int* epoch_base;
 };
 NP_API int np_ep_combine(const NpCombineArgs* a, void* stream) {
   if (a->D % 8 || a->n_ranks > 256) return 1;
@@ -663,6 +668,7 @@ NP_API int np_ep_combine(const NpCombineArgs* a, void* stream) {
   p.out = (__nv_bfloat16*)a->out; p.T = a->T; p.K = a->K; p.D = a->D; p.E = a->E; p.flags = a->flags;
   p.sent_to_peer = a->sent_to_peer; p.n_ranks = a->n_ranks; p.epoch = a->epoch;
   p.limit_ns = a->limit_ns ? a->limit_ns : NP_WAIT_LIMIT_NS;
+  p.epoch_base = a->epoch_base;
   long long work = (long long)a->T * (a->D / 8);
   int grid = (int)((work + 255) / 256);
   if (grid > 148 * 8) grid = 148 * 8;

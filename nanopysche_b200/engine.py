@@ -41,4 +41,61 @@ def prepare_training(model: nn.Module, *, tokens_per_rank: Optional[int] = None,
         grp = ep_group if ep_group is not None else moes[0].ep.ep_group
         build_runtime(moes, tokens=tokens_per_rank, group=grp if moes[0].ep.ep_size > 1 else None, device=p0.device)
     opt = ArenaAdamW(arena, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, max_grad_norm=max_grad_norm)
+    rt = getattr(moes[0], "_fused_runtime", None) if moes else None
+    if rt is not None:
+        opt.post_step_hooks.append(rt.end_step)
     return opt, arena
+
+
+class GraphedTrainStep:
+    """One training step (forward + backward + clip + AdamW) captured into a CUDA graph.
+
+    The step launches well over a thousand kernels; replaying them as one graph removes the host from
+    the critical path. What makes the step capturable: nothing in it synchronises with the host, flag
+    epochs and the optimizer schedule are read from device memory (``SymmetricHeap.epoch_base``,
+    ``ArenaAdamW._hyper``), gradient synchronisation runs as in-tree kernels over peer memory, and the
+    batch is copied into a static input buffer before each replay.
+
+    ``step(ids)`` returns the (device) loss tensor of that step; ``loss_fn(out)`` picks what is
+    back-propagated (default ``loss + aux_loss``).
+    """
+
+    def __init__(self, model: nn.Module, optimizer: ArenaAdamW, sample_ids: torch.Tensor, warmup: int = 3,
+                 loss_fn=None):
+        self.model, self.opt = model, optimizer
+        self.static_ids = sample_ids.clone()
+        self.loss_fn = loss_fn or (lambda out: out["loss"] if out.get("aux_loss") is None
+                                   else out["loss"] + out["aux_loss"])
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.static_loss: Optional[torch.Tensor] = None
+        self._warm = warmup
+
+    def _eager(self, hyper_ready: bool):
+        out = self.model(self.static_ids, labels=self.static_ids)
+        self.loss_fn(out).backward()
+        self.opt.step(_hyper_ready=hyper_ready)
+        self.opt.zero_grad(set_to_none=True)
+        return out["loss"].detach()
+
+    def capture(self):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(self._warm):
+                self._eager(False)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.opt.update_hyper()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.static_loss = self._eager(True)
+        return self
+
+    def step(self, ids: torch.Tensor) -> torch.Tensor:
+        if self.graph is None:
+            self.capture()
+            # the capture itself does not execute; fall through to a first replay with this batch
+        self.static_ids.copy_(ids, non_blocking=True)
+        self.opt.update_hyper()
+        self.graph.replay()
+        return self.static_loss

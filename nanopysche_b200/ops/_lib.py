@@ -39,7 +39,7 @@ class GemmArgs(C.Structure):
         ("row_dst", c_void_p), ("peer_base", c_void_p),
         ("done_counters", c_void_p), ("done_expected", c_void_p), ("done_flag_ptr", c_void_p),
         ("bn", c_int), ("max_ctas", c_int),
-        ("Cin", c_void_p), ("ldcin", c_ll),
+        ("Cin", c_void_p), ("ldcin", c_ll), ("epoch_base", c_void_p),
     ]
 
 
@@ -54,6 +54,7 @@ class DispatchArgs(C.Structure):
         ("peer_rows", c_void_p), ("peer_scales", c_void_p), ("peer_row_dst", c_void_p),
         ("peer_mblk_rows", c_void_p), ("peer_src_blocks", c_void_p), ("peer_flags", c_void_p),
         ("done_ctr", c_void_p), ("epoch", c_int), ("write_meta", c_int), ("max_ctas", c_int),
+        ("epoch_base", c_void_p),
     ]
 
 
@@ -65,7 +66,7 @@ class CombineArgs(C.Structure):
         ("add2", c_void_p), ("dl", c_void_p), ("wg", c_void_p), ("out", c_void_p),
         ("T", c_int), ("K", c_int), ("D", c_int), ("E", c_int),
         ("flags", c_void_p), ("sent_to_peer", c_void_p), ("n_ranks", c_int), ("epoch", c_int),
-        ("limit_ns", c_ull),
+        ("limit_ns", c_ull), ("epoch_base", c_void_p),
     ]
 
 

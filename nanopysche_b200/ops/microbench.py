@@ -1,0 +1,182 @@
+"""Kernel micro-benchmarks: ``python -m nanopysche_b200.ops.microbench <case> [options]``.
+
+Each case times one in-tree kernel with CUDA events after warm-up, flushing L2 between iterations
+(a 512 MB write), and prints one JSON line with the achieved rate and its fraction of the measured
+roofline (``MEASURED_PEAKS.json`` at the repository root when present, else 6.65 TB/s and
+1.59 PFLOP/s). The same command lines are what the ``ncu`` captures under ``profiles/`` run.
+
+Cases: gemm (fwd / dgrad / wgrad layouts, optional cuBLAS comparison), swiglu (fused GEMM + SwiGLU),
+rmsnorm, adamw, xent, moe (one fused MoE layer forward + backward).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from pathlib import Path
+
+import torch
+
+
+def peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timeit(fn, iters: int, warmup: int = 3, flush: bool = True):
+    scratch = torch.empty(512 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush:
+            scratch.fill_(1)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2], times[0]
+
+
+def case_gemm(a):
+    from .gemm import gemm
+
+    M, N, K = a.m, a.n, a.k
+    dev = "cuda"
+    if a.layout == "fwd":
+        A, B = torch.randn(M, K, device=dev).bfloat16(), torch.randn(N, K, device=dev).bfloat16()
+        kw, ref = {}, (lambda: torch.matmul(A, B.t()))
+    elif a.layout == "dgrad":
+        A, B = torch.randn(M, K, device=dev).bfloat16(), torch.randn(K, N, device=dev).bfloat16()
+        kw, ref = dict(b_mn=True), (lambda: torch.matmul(A, B))
+    else:
+        A, B = torch.randn(K, M, device=dev).bfloat16(), torch.randn(K, N, device=dev).bfloat16()
+        kw, ref = dict(a_mn=True, b_mn=True), (lambda: torch.matmul(A.t(), B))
+    out = torch.empty(M, N, device=dev, dtype=torch.float32 if a.f32 else torch.bfloat16)
+    med, best = timeit(lambda: gemm(A, B, out=out, bn=a.bn, **kw), a.iters)
+    flops = 2.0 * M * N * K
+    res = {"case": "gemm", "layout": a.layout, "M": M, "N": N, "K": K, "ms": med, "ms_best": best,
+           "tflops": flops / med / 1e9}
+    if a.cublas:
+        m2, _ = timeit(ref, a.iters)
+        res["cublas_ms"], res["cublas_tflops"] = m2, flops / m2 / 1e9
+    return res, flops, None
+
+
+def case_swiglu(a):
+    from .gemm import gemm_swiglu
+
+    x = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    w1 = torch.randn(a.n, a.k, device="cuda").bfloat16()
+    w3 = torch.randn(a.n, a.k, device="cuda").bfloat16()
+    med, best = timeit(lambda: gemm_swiglu(x, w1, w3, save_gu=not a.no_gu), a.iters)
+    flops = 4.0 * a.m * a.n * a.k
+    return {"case": "swiglu", "M": a.m, "N": a.n, "K": a.k, "ms": med, "tflops": flops / med / 1e9}, flops, None
+
+
+def case_rmsnorm(a):
+    from .norm import rms_norm
+
+    x = torch.randn(a.m, a.n, device="cuda").bfloat16()
+    r = torch.randn(a.m, a.n, device="cuda").bfloat16()
+    w = torch.ones(a.n, device="cuda")
+    med, best = timeit(lambda: rms_norm(x, w, 1e-6, r), a.iters)
+    nbytes = a.m * a.n * 2 * 4  # read x, res; write y, h
+    return {"case": "rmsnorm", "rows": a.m, "cols": a.n, "ms": med, "gbs": nbytes / med / 1e6}, None, nbytes
+
+
+def case_adamw(a):
+    from . import _lib
+
+    n = a.m * a.n
+    p, g = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    w16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    med, best = timeit(lambda: _lib.call("adamw", p, g, m, v, w16, _lib.LL(n), 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, None,
+                                         None), a.iters)
+    nbytes = n * 30
+    return {"case": "adamw", "n": n, "ms": med, "gbs": nbytes / med / 1e6}, None, nbytes
+
+
+def case_xent(a):
+    from .xent import cross_entropy
+
+    logits = torch.randn(a.m, a.n, device="cuda").bfloat16().requires_grad_(True)
+    labels = torch.randint(0, a.n, (a.m,), device="cuda")
+
+    def run():
+        cross_entropy(logits, labels).backward()
+        logits.grad = None
+
+    med, best = timeit(run, a.iters)
+    nbytes = a.m * a.n * 2 * 4  # fwd reads twice, bwd reads once and writes once
+    return {"case": "xent", "rows": a.m, "V": a.n, "ms": med, "gbs": nbytes / med / 1e6}, None, nbytes
+
+
+def case_moe(a):
+    from ..models.moe import MoEBase
+    from .moe import build_runtime
+
+    T, D, H, E, K = a.m, a.k, a.n, a.experts, a.topk
+    moe = MoEBase(d_model=D, hidden_size=H, num_experts=E, top_k=K, capacity_factor=a.capacity, dtype=torch.bfloat16,
+                  device="cuda", init_std=0.02)
+    for w in (moe.w1, moe.w2, moe.w3):
+        w.main_grad = torch.zeros(w.shape, device="cuda")
+    build_runtime([moe], tokens=T, device=torch.device("cuda"))
+    x = torch.randn(1, T, D, device="cuda").bfloat16().requires_grad_(True)
+    gy = torch.randn(1, T, D, device="cuda").bfloat16()
+
+    def run():
+        for w in (moe.w1, moe.w2, moe.w3):
+            w._main_grad_dirty = False
+        moe(x).backward(gy)
+        x.grad = None
+
+    med, best = timeit(run, a.iters)
+    kept = T * K if a.capacity is None else min(T * K, E * int(a.capacity * T / E))
+    flops = 3.0 * kept * 6.0 * D * H
+    return {"case": "moe", "T": T, "D": D, "H": H, "E": E, "K": K, "capacity": a.capacity, "ms": med,
+            "tflops_upper_bound_rows": flops / med / 1e9}, None, None
+
+
+CASES = {"gemm": case_gemm, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "xent": case_xent,
+         "moe": case_moe}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=sorted(CASES))
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=5632)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--layout", choices=["fwd", "dgrad", "wgrad"], default="fwd")
+    ap.add_argument("--f32", action="store_true", help="fp32 output")
+    ap.add_argument("--cublas", action="store_true", help="also time torch.matmul")
+    ap.add_argument("--no-gu", action="store_true")
+    ap.add_argument("--experts", type=int, default=8)
+    ap.add_argument("--topk", type=int, default=2)
+    ap.add_argument("--capacity", type=float, default=None)
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args(argv)
+    hbm, tf, src = peaks()
+    res, flops, nbytes = CASES[a.case](a)
+    if flops:
+        res["frac_of_" + src + "_bf16_peak"] = res.get("tflops", 0.0) / tf
+    if nbytes:
+        res["frac_of_" + src + "_hbm"] = res["gbs"] / hbm
+    from . import _lib
+
+    res["status"] = list(_lib.status())
+    print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    main()

@@ -144,7 +144,6 @@ class FusedMoERuntime:
         self.mblk_flag = ((blk // self.bpr) % self.N).to(torch.int32)
         self.done_counters = torch.zeros(self.N, device=self.device, dtype=torch.int32)
         self.dispatch_ctr = torch.zeros(1, device=self.device, dtype=torch.int32)
-        self.epoch = 0
         self.layer_of: dict[int, int] = {}
         self.max_ctas_dispatch = max_ctas_dispatch
         if self.N > 1:
@@ -159,8 +158,10 @@ class FusedMoERuntime:
         return self.layer_of[k]
 
     def next_epoch(self) -> int:
-        self.epoch += 1
-        return self.epoch
+        return self.heap.next_epoch()
+
+    def end_step(self):
+        self.heap.end_step()
 
     # -- kernels -------------------------------------------------------------------------------------
     def dispatch(self, x2, indices, slot_pos, counts_kept, scale, p_rows, epoch):
@@ -175,6 +176,7 @@ class FusedMoERuntime:
         a.peer_row_dst, a.peer_mblk_rows = self.p_row_dst.data_ptr(), self.p_mblk_rows.data_ptr()
         a.peer_src_blocks, a.peer_flags = self.p_src_blocks.data_ptr(), self.p_dispatch_flags.data_ptr()
         a.done_ctr, a.epoch, a.write_meta, a.max_ctas = self.dispatch_ctr.data_ptr(), epoch, 1, self.max_ctas_dispatch
+        a.epoch_base = self.heap.epoch_base.data_ptr()
         _lib.check(_lib.lib().np_ep_dispatch(C.byref(a), C.c_void_p(_lib.stream())), "ep_dispatch")
 
     def combine(self, rows, slot_pos, weights, out, sent_to_peer, epoch, dl=None, wg=None, add1=None):
@@ -189,6 +191,7 @@ class FusedMoERuntime:
         a.T, a.K, a.D, a.E = self.T, self.K, self.D, self.E
         a.flags, a.sent_to_peer = self.combine_flags.data_ptr(), sent_to_peer.data_ptr()
         a.n_ranks, a.epoch, a.limit_ns = self.N, epoch, WAIT_LIMIT_NS
+        a.epoch_base = self.heap.epoch_base.data_ptr()
         _lib.check(_lib.lib().np_ep_combine(C.byref(a), C.c_void_p(_lib.stream())), "ep_combine")
 
     def grouped_gemm(self, A, B, *, N, K, b_mn, group_stride_b, out=None, B2=None, C2=None, wait_epoch=0,
@@ -225,6 +228,7 @@ class FusedMoERuntime:
             g.out_f32 = int(out.dtype == torch.float32)
         if Cin is not None:
             g.Cin, g.ldcin = Cin.data_ptr(), Cin.stride(0)
+        g.epoch_base = self.heap.epoch_base.data_ptr()
         _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "grouped_gemm")
         return out
 

@@ -46,7 +46,7 @@ class AdamW(Optimizer):
                          p.is_contiguous() and p.grad.is_contiguous() and not group["amsgrad"])
                 if fused:
                     _lib.call("adamw", p, p.grad, m, v, None, _lib.LL(p.numel()), float(lr), float(b1), float(b2),
-                              float(eps), float(wd), int(st["step"]), None)
+                              float(eps), float(wd), int(st["step"]), None, None)
                     continue
                 g = p.grad
                 if wd > 0:

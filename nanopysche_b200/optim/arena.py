@@ -87,7 +87,10 @@ class ParamArena:
                 if r.replicated and r.dtype == torch.bfloat16:
                     pad = self._padded(r.numel)
                     need += pad * 2 + pad * 4 + 8192
-            self.heap = SymmetricHeap(need + (1 << 20), dp_group, self.device)
+            f32_elems = sum(r.numel for r in self.regions.values() if r.replicated and r.dtype == torch.float32)
+            self._ar_max = max(f32_elems + 64, 4096)
+            self.heap = SymmetricHeap(need + 2 * self.world * self._ar_max * 4 + (1 << 20), dp_group, self.device)
+            self.heap.reserve_allreduce(self._ar_max)
         self.fused: List[torch.Tensor] = []
         for r in self.regions.values():
             self._materialise(r)
@@ -231,6 +234,12 @@ class ArenaAdamW(torch.optim.Optimizer):
             self._parts = _lib.lib().np_sumsq_parts()
             zp = _lib.lib().np_zero_parts()
             self._partial = torch.zeros(nreg * max(self._parts, zp), device=dev, dtype=torch.float32)
+        # [lr, 1 - b1^t, 1 - b2^t]: read by the kernels from device memory so a captured step replays
+        # with the current schedule; refreshed by ``update_hyper()`` (a pinned-host -> device copy)
+        self._hyper = torch.zeros(3, device=dev, dtype=torch.float32)
+        self._hyper_host = torch.zeros(3, dtype=torch.float32).pin_memory() if self._cuda else torch.zeros(3)
+        self.post_step_hooks = []  # callables run at the end of every step (e.g. epoch bookkeeping)
+        self._tot = torch.zeros(1, device=dev, dtype=torch.float32)
         self._coef = torch.ones(2, device=dev, dtype=torch.float32)   # [clip coefficient, grad norm]
         self._coef_local = torch.ones(1, device=dev, dtype=torch.float32)
         self.last_grad_norm: Optional[torch.Tensor] = None
@@ -239,11 +248,24 @@ class ArenaAdamW(torch.optim.Optimizer):
         self.arena.zero_grad()
 
     # ------------------------------------------------------------------ step
+    def update_hyper(self, advance: bool = True):
+        """Advance the step counter and publish lr / bias corrections to the device buffer. ``step()``
+        does this itself; a captured graph replays ``step(_hyper_ready=True)`` after calling this."""
+        if advance:
+            self.step_count += 1
+        g = self.param_groups[0]
+        b1, b2 = g["betas"]
+        self._hyper_host[0] = g["lr"]
+        self._hyper_host[1] = 1.0 - b1 ** self.step_count
+        self._hyper_host[2] = 1.0 - b2 ** self.step_count
+        self._hyper.copy_(self._hyper_host, non_blocking=True)
+
     @torch.no_grad()
-    def step(self, closure=None):
+    def step(self, closure=None, _hyper_ready: bool = False):
         a = self.arena
         a.finalize_grads()
-        self.step_count += 1
+        if not _hyper_ready:
+            self.update_hyper()
         g = self.param_groups[0]
         lr, (b1, b2), eps, wd = g["lr"], g["betas"], g["eps"], g["weight_decay"]
         if not self._cuda:
@@ -264,18 +286,24 @@ class ArenaAdamW(torch.optim.Optimizer):
                                                      C.c_void_p(part.data_ptr()), C.c_void_p(_lib.stream())),
                            "zero_reduce")
             else:
-                if N > 1 and r.replicated:  # small fp32 region: plain all-reduce
-                    dist.all_reduce(r.grads, group=a.dp_group)
+                if N > 1 and r.replicated:  # small fp32 region: all-reduce through peer memory (NCCL otherwise)
+                    if a.zero:
+                        a.heap.all_reduce_(r.grads)
+                    else:
+                        dist.all_reduce(r.grads, group=a.dp_group)
                 _lib.call("sumsq", r.grads, _lib.LL(r.grads.numel()), part)
                 # scale of these gradients relative to the final ones: inv; replicated ones are counted
                 # once per rank in the global sum below
                 s = inv * inv / (N if (N > 1 and r.replicated) else 1)
                 part.mul_(s)
         if N > 1:
-            tot = self._partial.sum().reshape(1)
-            dist.all_reduce(tot, group=a.dp_group)
+            torch.sum(self._partial, dim=0, keepdim=True, out=self._tot)
+            if a.zero:
+                a.heap.all_reduce_(self._tot)
+            else:
+                dist.all_reduce(self._tot, group=a.dp_group)
             self._partial.zero_()
-            self._partial[0] = tot[0]
+            self._partial[:1].copy_(self._tot)
         _lib.call("clip_coef", self._partial, self._partial.numel(), extra,
                   float(self.max_grad_norm or 0.0), self._coef)
         self.last_grad_norm = self._coef[1]
@@ -288,15 +316,19 @@ class ArenaAdamW(torch.optim.Optimizer):
                     C.c_void_p(r.master.data_ptr()), C.c_void_p(r.gshard.data_ptr()), C.c_void_p(r.m.data_ptr()),
                     C.c_void_p(r.v.data_ptr()), ptrs, N, C.c_longlong(r.lo), C.c_longlong(r.cnt), C.c_float(lr),
                     C.c_float(b1), C.c_float(b2), C.c_float(eps), C.c_float(wdr), self.step_count,
-                    C.c_void_p(self._coef.data_ptr()), C.c_void_p(_lib.stream())), "zero_adamw_bcast")
+                    C.c_void_p(self._coef.data_ptr()), C.c_void_p(self._hyper.data_ptr()),
+                    C.c_void_p(_lib.stream())), "zero_adamw_bcast")
             elif r.dtype == torch.float32:
                 _lib.call("adamw", r.weights, r.grads, r.m, r.v, None, _lib.LL(r.weights.numel()), float(lr),
-                          float(b1), float(b2), float(eps), float(wdr), self.step_count, self._coef_local)
+                          float(b1), float(b2), float(eps), float(wdr), self.step_count, self._coef_local, self._hyper)
             else:
                 _lib.call("adamw", r.master, r.grads, r.m, r.v, r.weights, _lib.LL(r.weights.numel()), float(lr),
-                          float(b1), float(b2), float(eps), float(wdr), self.step_count, self._coef_local)
+                          float(b1), float(b2), float(eps), float(wdr), self.step_count, self._coef_local, self._hyper)
         if a.zero:
             a.heap.barrier()  # all ranks' weight stores have landed before the next forward reads them
+            a.heap.end_step()
+        for hook in self.post_step_hooks:
+            hook()
         return None
 
     def _step_reference(self, lr, b1, b2, eps, wd):
@@ -313,6 +345,8 @@ class ArenaAdamW(torch.optim.Optimizer):
         if N > 1:
             dist.all_reduce(sq, group=a.dp_group)
         norm = sq.sqrt()
+        for hook in self.post_step_hooks:
+            hook()
         coef = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0) if self.max_grad_norm else torch.ones(())
         self.last_grad_norm = norm
         t = self.step_count

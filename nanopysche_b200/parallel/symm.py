@@ -67,9 +67,16 @@ class SymmetricHeap:
                 _lib.check(lib.np_symm_open(buf, C.byref(p)), "symm_open")
                 self.peer_ptrs.append(p.value)
             self._base_tensor = torch.as_tensor(_RawCuda(self.local_ptr, self.nbytes), device=self.device)
-        self._barrier_epoch = 0
+        # Epochs are ``*epoch_base + offset``: the offset is a host integer that restarts every step, the
+        # base lives on the device and is advanced by ``end_step()`` with an ordinary stream-ordered add,
+        # so a captured CUDA graph of one step replays with fresh, still monotone epochs.
+        self.epoch_base = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._epoch_off = 0
         self._barrier_flags = self.alloc((self.world,), torch.int32)
-        self._barrier_ptrs = self.ptr_array(self._barrier_flags)
+        self._ar_flags = self.alloc((self.world,), torch.int32)
+        self._ar_ctr = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self._ar_half = 0
+        self._ar_staging = None
 
     # -- allocation --------------------------------------------------------------------------------
     def alloc(self, shape, dtype: torch.dtype, align: int = 256) -> torch.Tensor:
@@ -100,14 +107,45 @@ class SymmetricHeap:
         return arr
 
     # -- synchronisation -----------------------------------------------------------------------------
+    def next_epoch(self) -> int:
+        self._epoch_off += 1
+        return self._epoch_off
+
+    def end_step(self):
+        """Fold this step's epoch offsets into the device-side base (call once per optimizer step)."""
+        if self._epoch_off:
+            self.epoch_base.add_(self._epoch_off)
+            self._epoch_off = 0
+
     def barrier(self, limit_ns: int = 0):
         """Device-side barrier on the current stream (no host synchronisation)."""
         if self.world <= 1:
             return
-        self._barrier_epoch += 1
         arr = self.host_ptr_array(self._barrier_flags)
-        _lib.check(_lib.lib().np_symm_barrier(arr, self.rank, self.world, self._barrier_epoch,
-                                              C.c_ulonglong(limit_ns), C.c_void_p(_lib.stream())), "symm_barrier")
+        _lib.check(_lib.lib().np_symm_barrier(arr, self.rank, self.world, self.next_epoch(),
+                                              C.c_void_p(self.epoch_base.data_ptr()), C.c_ulonglong(limit_ns),
+                                              C.c_void_p(_lib.stream())), "symm_barrier")
+
+    def reserve_allreduce(self, max_count: int):
+        """Allocate the staging area of ``all_reduce_`` (every rank, same order as other allocations)."""
+        self._ar_half = self.world * max_count
+        self._ar_staging = self.alloc((2 * self._ar_half,), torch.float32)
+
+    def all_reduce_(self, t: torch.Tensor, scale: float = 1.0, limit_ns: int = 0) -> torch.Tensor:
+        """In-place sum of a (small) fp32 tensor over the ranks through peer stores; no NCCL involved."""
+        if self.world <= 1:
+            if scale != 1.0:
+                t.mul_(scale)
+            return t
+        assert t.dtype == torch.float32 and t.is_contiguous() and self._ar_staging is not None
+        assert self.world * t.numel() <= self._ar_half, "reserve_allreduce() was sized too small"
+        st, fl = self.host_ptr_array(self._ar_staging), self.host_ptr_array(self._ar_flags)
+        _lib.check(_lib.lib().np_symm_allreduce(
+            C.c_void_p(t.data_ptr()), C.c_void_p(t.data_ptr()), st, fl, C.c_void_p(self._ar_ctr.data_ptr()),
+            C.c_longlong(self._ar_half), C.c_longlong(t.numel()), self.rank, self.world, self.next_epoch(),
+            C.c_void_p(self.epoch_base.data_ptr()), C.c_float(scale), C.c_ulonglong(limit_ns),
+            C.c_void_p(_lib.stream())), "symm_allreduce")
+        return t
 
     def close(self):
         if self._ipc:

@@ -182,7 +182,7 @@ def test_fused_adamw_and_clip():
     for step in (1, 2, 3):
         _lib.call("sumsq", g, _lib.LL(n), partial)
         _lib.call("clip_coef", partial, parts, None, 1.0, coef)
-        _lib.call("adamw", p, g, m, v, w16, _lib.LL(n), 1e-2, 0.9, 0.95, 1e-8, 0.1, step, coef[:1])
+        _lib.call("adamw", p, g, m, v, w16, _lib.LL(n), 1e-2, 0.9, 0.95, 1e-8, 0.1, step, coef[:1], None)
         pr.grad = g.clone()
         nrm = torch.nn.utils.clip_grad_norm_([pr], 1.0)
         opt.step()
