@@ -55,6 +55,7 @@ class Attention(nn.Module):
         self._local_heads = n_heads
         self._local_kv_heads = self.n_kv_heads
         self._fused_qkv: Optional[torch.Tensor] = None  # [q|k|v] weight view, set by the parameter arena
+        self._tp_rt = None  # ops.tp_fused.TPRuntime when the fused sequence-parallel TP path is on
 
     # ------------------------------------------------------------------ forward
     def _project_qkv(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -79,9 +80,23 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, *, causal: bool = True, attn_mask: Optional[torch.Tensor] = None,
                 kv_cache: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, start_pos: int = 0,
                 position_ids: Optional[torch.Tensor] = None, return_kv: bool = False, **_):
-        B, S, _ = x.shape
-        x = copy_to_tp_region(x, self._tp_group, self._tp_size)
-        q, k, v = self._project_qkv(x)
+        rt = self._tp_rt if (self._tp_rt is not None and x.is_cuda and x.dtype == torch.bfloat16) else None
+        if rt is not None:
+            # sequence-parallel input [1, M/tp, D]: all-gather fused into the QKV GEMM
+            from ..ops import tp_fused
+
+            B, S = rt.batch_shape
+            hq, hkv, hd = self._local_heads, self._local_kv_heads, self.head_dim
+            w = self._fused_qkv if self._fused_qkv is not None else \
+                torch.cat([self.w_q.weight, self.w_k.weight, self.w_v.weight], dim=0)
+            qkv = tp_fused.ag_linear(x.reshape(-1, x.shape[-1]), w, rt).view(B, S, -1)
+            q = qkv[..., : hq * hd].unflatten(-1, (hq, hd))
+            k = qkv[..., hq * hd:(hq + hkv) * hd].unflatten(-1, (hkv, hd))
+            v = qkv[..., (hq + hkv) * hd:].unflatten(-1, (hkv, hd))
+        else:
+            B, S, _ = x.shape
+            x = copy_to_tp_region(x, self._tp_group, self._tp_size)
+            q, k, v = self._project_qkv(x)
         if self.q_norm is not None:
             q = self.q_norm(q.float()).to(x.dtype) if q.dtype != torch.float32 else self.q_norm(q)
             k = self.k_norm(k.float()).to(x.dtype) if k.dtype != torch.float32 else self.k_norm(k)
@@ -105,8 +120,14 @@ class Attention(nn.Module):
         else:
             o = self.sdpa(q, k, v, causal=causal, attn_mask=attn_mask)
         o = o.reshape(B, S, self._local_heads * self.head_dim)
-        out = gemm_ops.linear(o, self.w_out.weight, None)
-        out = differentiable_all_reduce(out, self._tp_group, self._tp_size)
+        if rt is not None:
+            from ..ops import tp_fused
+
+            # GEMM -> reduce-scatter fused: back to the sequence shard [1, M/tp, D]
+            out = tp_fused.linear_rs(o.reshape(B * S, -1), self.w_out.weight, rt).unsqueeze(0)
+        else:
+            out = gemm_ops.linear(o, self.w_out.weight, None)
+            out = differentiable_all_reduce(out, self._tp_group, self._tp_size)
         if self.w_out.bias is not None:
             out = out + self.w_out.bias
         out = self.dropout(out)

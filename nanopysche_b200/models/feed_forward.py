@@ -40,10 +40,18 @@ class FeedForward(nn.Module):
         self._tp_size = 1
         self._tp_group = None
         self._fused_w13: Optional[torch.Tensor] = None
+        self._tp_rt = None  # ops.tp_fused.TPRuntime when the fused sequence-parallel TP path is on
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        x = copy_to_tp_region(x, self._tp_group, self._tp_size)
         act = self.activation.value
+        if self._tp_rt is not None and x.is_cuda and x.dtype == torch.bfloat16 and self.w1.bias is None:
+            from ..ops import tp_fused
+
+            rt = self._tp_rt
+            w13 = self._fused_w13 if self._fused_w13 is not None else torch.cat([self.w1.weight, self.w3.weight], 0)
+            h = act_ops.glu(tp_fused.ag_linear(x.reshape(-1, x.shape[-1]), w13, rt), act)
+            return tp_fused.linear_rs(h, self.w2.weight, rt).view(*x.shape[:-1], -1)
+        x = copy_to_tp_region(x, self._tp_group, self._tp_size)
         fused = self._fused_w13
         if fused is not None and x.is_cuda and x.dtype == fused.dtype and self.w1.bias is None:
             h = act_ops.glu(gemm_ops.linear(x, fused), act)

@@ -193,8 +193,17 @@ class Transformer(nn.Module):
                 x = self.embedding_norm(x)
         else:
             x = input_ids  # hidden states from the previous pipeline stage
+        tp_rt = None
+        if getattr(self, "_tp_fused", False) and x.is_cuda and x.dtype == torch.bfloat16 and self._is_first_stage:
+            B0, S0, D0 = x.shape
+            tp_rt = self._ensure_tp_runtime(B0, S0, x.device)
+            x = x.reshape(B0 * S0, D0)[tp_rt.rank * tp_rt.Ms:(tp_rt.rank + 1) * tp_rt.Ms].unsqueeze(0)
         for blk in self.blocks.values():
             x = blk(x, **kwargs)
+        if tp_rt is not None:
+            from ..ops.tp_fused import gather_rows_replicated
+
+            x = gather_rows_replicated(x.reshape(tp_rt.Ms, -1), self._tp_group).view(B0, S0, -1)
         aux = self._collect_aux(x)
         if not self._is_last_stage or (self.lm_head is None and not self.tie_word_embeddings):
             return {"hidden_states": x, "aux_loss": aux}
@@ -241,10 +250,49 @@ class Transformer(nn.Module):
         return aux
 
     # ------------------------------------------------------------------ hooks
-    def apply_tp(self, tp_mesh, **kw):
+    def apply_tp(self, tp_mesh, *, fused: bool = False, **kw):
+        """Megatron TP over ``tp_mesh``. ``fused=True`` (CUDA, bf16) switches to the sequence-parallel
+        layout with the all-gather fused into the column-parallel GEMMs and the reduce-scatter into the
+        row-parallel ones (``ops/tp_fused.py``); activations between blocks are then row shards."""
         for blk in self.blocks.values():
             blk.apply_tp(tp_mesh)
         self._tp_enabled = True
+        self._tp_group = tp_mesh.get_group() if hasattr(tp_mesh, "get_group") else tp_mesh
+        self._tp_fused = bool(fused)
+        self._tp_rt = None
+        if fused:
+            import torch.distributed as dist
+
+            group = self._tp_group
+
+            def reduce_hook(p):
+                if p.grad is not None:
+                    dist.all_reduce(p.grad, group=group)
+
+            # parameters applied to row shards (or to this rank's heads only) see a partial gradient
+            for name, p in self.named_parameters():
+                if "norm" in name or name.startswith("embeddings") or ".router." in name:
+                    p._tp_partial = True
+                    p.register_post_accumulate_grad_hook(reduce_hook)
+
+    def _ensure_tp_runtime(self, B: int, S: int, device):
+        from ..models.attention import Attention
+        from ..models.feed_forward import FeedForward
+        from ..ops.tp_fused import TPRuntime
+
+        if self._tp_rt is None or self._tp_rt.M != B * S:
+            cols = self.d_model
+            for m in self.modules():
+                if isinstance(m, Attention):
+                    cols = max(cols, (m._local_heads + 2 * m._local_kv_heads) * m.head_dim)
+                elif isinstance(m, FeedForward):
+                    cols = max(cols, 2 * m.w1.weight.shape[0])
+            self._tp_rt = TPRuntime(self._tp_group, B * S, cols, device)
+            for m in self.modules():
+                if isinstance(m, (Attention, FeedForward)):
+                    m._tp_rt = self._tp_rt
+        self._tp_rt.batch_shape = (B, S)
+        return self._tp_rt
 
     def apply_cp(self, cp_mesh, *, ring=None, uly=None):
         for blk in self.blocks.values():

@@ -59,7 +59,8 @@ class _RMSNorm(torch.autograd.Function):
         dx = torch.empty_like(xin)
         parts = _lib.lib().np_rmsnorm_bwd_parts(rows)
         scratch = torch.empty((parts, D), device=xin.device, dtype=torch.float32)
-        mg = getattr(weight, "main_grad", None)
+        # weights whose gradient is partial per TP rank go through autograd so their reduce hook runs
+        mg = None if getattr(weight, "_tp_partial", False) else getattr(weight, "main_grad", None)
         if mg is not None:
             first = not getattr(weight, "_main_grad_dirty", False)
             _lib.call("rmsnorm_bwd", dy2, xin, weight, rstd, dres, dx, mg, scratch, rows, D, int(not first))

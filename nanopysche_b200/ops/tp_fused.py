@@ -1,0 +1,206 @@
+"""Fused tensor-parallel linears over peer memory (Megatron sequence-parallel layout).
+
+``ag_linear``  : ``y[M, Nl] = all_gather(x_shard)[M, K] @ w[Nl, K]^T`` - every rank stores its row shard
+                 into all ranks' gather buffers (one push kernel) and the tcgen05 GEMM starts on each
+                 128-row block as soon as the flag of the rank that owns those rows arrives, so the
+                 transfer overlaps the math block by block.
+``linear_rs``  : ``y_shard[M/tp, N] = reduce_scatter(x[M, Kl] @ w[N, Kl]^T)`` - the GEMM epilogue stores
+                 every output row straight from TMEM into the owning rank's slot buffer and releases
+                 that rank's flag when its blocks are done; the owner sums the ``tp`` partial rows.
+Backward passes are the conjugates (``ag_linear`` <-> ``linear_rs``) plus local wgrad GEMMs.
+
+They replace ``differentiable_all_reduce`` after the row-parallel projections of the reference
+(model/tp_utils.py:25-57, model/attention.py:189-192, model/feed_forward.py:75-78) and halve the bytes
+moved (all-gather + reduce-scatter of activations instead of an all-reduce of replicated ones).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .gemm import _wgrad_into, gemm
+from .moe import WAIT_LIMIT_NS
+
+
+class TPRuntime:
+    """Symmetric buffers and flag tables for one tensor-parallel group (shared by all layers)."""
+
+    def __init__(self, group, rows: int, max_cols: int, device=None):
+        from ..parallel.symm import SymmetricHeap
+
+        self.group = group
+        self.N = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.M = rows
+        assert rows % (128 * self.N) == 0, "token count must be a multiple of 128 * tp"
+        self.Ms = rows // self.N
+        self.max_cols = max_cols
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        nbytes = 2 * rows * max_cols * 2 + (1 << 20)
+        self.heap = SymmetricHeap(nbytes, group, self.device)
+        h = self.heap
+        self.gather = h.alloc((rows * max_cols,), torch.bfloat16)
+        self.slots = h.alloc((rows * max_cols,), torch.bfloat16)   # [Ms * N, cols]: row_local * N + src
+        self.ag_flags = h.alloc((self.N,), torch.int32)
+        self.rs_flags = h.alloc((self.N,), torch.int32)
+        self.p_gather, self.p_slots = h.ptr_array(self.gather), h.ptr_array(self.slots)
+        self.p_done_flag = torch.tensor([h.peer_ptr(self.rs_flags, s) + 4 * self.rank for s in range(self.N)],
+                                        dtype=torch.int64, device=self.device)
+        r = torch.arange(rows, device=self.device)
+        owner, local = r // self.Ms, r % self.Ms
+        self.row_dst = (owner << 40) | (local * self.N + self.rank)
+        self.mblk_owner = ((torch.arange(rows // 128, device=self.device) * 128) // self.Ms).to(torch.int32)
+        self.done_expected = torch.full((self.N,), self.Ms // 128, dtype=torch.int32, device=self.device)
+        self.done_counters = torch.zeros(self.N, dtype=torch.int32, device=self.device)
+        self.ctr = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.slot_pos = torch.zeros((self.Ms, self.N), dtype=torch.int32, device=self.device)
+        self.sent = torch.ones(self.N, dtype=torch.int32, device=self.device)
+        self.batch_shape: Optional[tuple] = None  # (B, S) of the full batch, set by the model per forward
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def end_step(self):
+        self.heap.end_step()
+
+    # -- building blocks -------------------------------------------------------------------------------
+    def all_gather_push(self, x_shard: torch.Tensor) -> tuple:
+        """Push this rank's ``[Ms, cols]`` shard to every rank; returns (local gather view [M, cols], epoch)."""
+        Ms, cols = x_shard.shape
+        assert Ms == self.Ms and cols <= self.max_cols and x_shard.is_contiguous()
+        e = self.heap.next_epoch()
+        h = self.heap
+        _lib.check(_lib.lib().np_allgather_push(
+            C.c_void_p(x_shard.data_ptr()), h.host_ptr_array(self.gather), C.c_longlong(Ms * cols * 2),
+            h.host_ptr_array(self.ag_flags), C.c_void_p(self.ctr.data_ptr()), self.rank, self.N, e,
+            C.c_void_p(h.epoch_base.data_ptr()), 32, C.c_void_p(_lib.stream())), "allgather_push")
+        return self.gather[: self.M * cols].view(self.M, cols), e
+
+    def gemm_wait(self, A, B, *, b_mn: bool, epoch: int, out_dtype=torch.bfloat16):
+        """``A @ B^T`` where A is the gather buffer: each M block waits for its owner's arrival flag."""
+        M, K = A.shape
+        N = B.shape[1] if b_mn else B.shape[0]
+        out = torch.empty((M, N), device=A.device, dtype=out_dtype)
+        g = _lib.GemmArgs()
+        g.A, g.B, g.C = A.data_ptr(), B.data_ptr(), out.data_ptr()
+        g.lda, g.ldb, g.ldc = A.stride(0), B.stride(0), N
+        g.a_rows, g.b_rows = A.shape[0], B.shape[0]
+        g.M, g.N, g.K = M, N, K
+        g.b_mn, g.mode, g.alpha = int(b_mn), 1, 1.0
+        g.ready_flags, g.mblk_flag = self.ag_flags.data_ptr(), self.mblk_owner.data_ptr()
+        g.epoch, g.flag_limit_ns = epoch, WAIT_LIMIT_NS
+        g.epoch_base = self.heap.epoch_base.data_ptr()
+        _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "tp_gemm_wait")
+        return out
+
+    def gemm_reduce_scatter(self, A, B, *, b_mn: bool) -> torch.Tensor:
+        """``reduce_scatter(A @ B^T)`` over the rows: returns this rank's ``[Ms, N]`` shard."""
+        M, K = A.shape
+        N = B.shape[1] if b_mn else B.shape[0]
+        assert M == self.M and N <= self.max_cols
+        e = self.heap.next_epoch()
+        self.done_counters.zero_()
+        g = _lib.GemmArgs()
+        g.A, g.B = A.data_ptr(), B.data_ptr()
+        g.lda, g.ldb, g.ldc = A.stride(0), B.stride(0), N
+        g.a_rows, g.b_rows = A.shape[0], B.shape[0]
+        g.M, g.N, g.K = M, N, K
+        g.b_mn, g.mode, g.alpha = int(b_mn), 0, 1.0
+        g.row_dst, g.peer_base = self.row_dst.data_ptr(), self.p_slots.data_ptr()
+        g.mblk_flag = self.mblk_owner.data_ptr()
+        g.done_counters, g.done_expected = self.done_counters.data_ptr(), self.done_expected.data_ptr()
+        g.done_flag_ptr, g.epoch = self.p_done_flag.data_ptr(), e
+        g.epoch_base = self.heap.epoch_base.data_ptr()
+        _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "tp_gemm_rs")
+        out = torch.empty((self.Ms, N), device=A.device, dtype=torch.bfloat16)
+        c = _lib.CombineArgs()
+        c.rows, c.slot_pos, c.out = self.slots.data_ptr(), self.slot_pos.data_ptr(), out.data_ptr()
+        c.T, c.K, c.D, c.E = self.Ms, self.N, N, 1
+        c.flags, c.sent_to_peer = self.rs_flags.data_ptr(), self.sent.data_ptr()
+        c.n_ranks, c.epoch, c.limit_ns = self.N, e, WAIT_LIMIT_NS
+        c.epoch_base = self.heap.epoch_base.data_ptr()
+        _lib.check(_lib.lib().np_ep_combine(C.byref(c), C.c_void_p(_lib.stream())), "tp_reduce")
+        return out
+
+
+class _AGLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_shard, w, rt: TPRuntime):
+        xs = x_shard.reshape(-1, x_shard.shape[-1])
+        xs = xs if xs.is_contiguous() else xs.contiguous()
+        full, e = rt.all_gather_push(xs)
+        y = rt.gemm_wait(full, w, b_mn=False, epoch=e)
+        ctx.save_for_backward(full.clone(), w)  # the gather buffer is reused by the next layer
+        ctx.rt = rt
+        ctx.x_shape = x_shard.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_full, w = ctx.saved_tensors
+        rt = ctx.rt
+        dy = dy if dy.is_contiguous() else dy.contiguous()
+        dx_shard = rt.gemm_reduce_scatter(dy, w, b_mn=True)
+        dw = _wgrad_into(w, dy, x_full) if (ctx.needs_input_grad[1] or hasattr(w, "main_grad")) else None
+        return dx_shard.view(ctx.x_shape), dw, None
+
+
+class _LinearRS(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, rt: TPRuntime):
+        x2 = x.reshape(-1, x.shape[-1])
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        y = rt.gemm_reduce_scatter(x2, w, b_mn=False)
+        ctx.save_for_backward(x2, w)
+        ctx.rt = rt
+        ctx.x_shape = x.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        x2, w = ctx.saved_tensors
+        rt = ctx.rt
+        dys = dy_shard.reshape(-1, dy_shard.shape[-1])
+        dys = dys if dys.is_contiguous() else dys.contiguous()
+        dy_full, e = rt.all_gather_push(dys)
+        dx = rt.gemm_wait(dy_full, w, b_mn=True, epoch=e)
+        dw = None
+        if ctx.needs_input_grad[1] or hasattr(w, "main_grad"):
+            dw = _wgrad_into(w, dy_full, x2)  # runs after the dgrad GEMM, which has seen every flag
+        return dx.view(ctx.x_shape), dw, None
+
+
+def ag_linear(x_shard: torch.Tensor, w: torch.Tensor, rt: TPRuntime) -> torch.Tensor:
+    """Column-parallel linear on a sequence shard: ``[Ms, K] -> [M, Nl]``."""
+    return _AGLinear.apply(x_shard, w, rt)
+
+
+def linear_rs(x: torch.Tensor, w: torch.Tensor, rt: TPRuntime) -> torch.Tensor:
+    """Row-parallel linear with the sum scattered over the rows: ``[M, Kl] -> [Ms, N]``."""
+    return _LinearRS.apply(x, w, rt)
+
+
+class _GatherRowsSliceBackward(torch.autograd.Function):
+    """All-gather rows for a computation that is *replicated* afterwards (final norm / LM head): every
+    rank then holds the same gradient, so backward just takes this rank's slice."""
+
+    @staticmethod
+    def forward(ctx, x_shard, group):
+        ctx.group = group
+        n = dist.get_world_size(group)
+        out = torch.empty((n * x_shard.shape[0], *x_shard.shape[1:]), device=x_shard.device, dtype=x_shard.dtype)
+        dist.all_gather_into_tensor(out, x_shard.contiguous(), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        n, r = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
+        rows = g.shape[0] // n
+        return g[r * rows:(r + 1) * rows].contiguous(), None
+
+
+def gather_rows_replicated(x_shard: torch.Tensor, group) -> torch.Tensor:
+    return _GatherRowsSliceBackward.apply(x_shard, group)

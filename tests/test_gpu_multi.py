@@ -139,3 +139,48 @@ def _zero_worker(rank, world):
 def test_sharded_fused_optimizer_two_gpus():
     _need2()
     assert all(run_distributed(_zero_worker, 2, backend="nccl"))
+
+
+def _tp_fused_worker(rank, world):
+    import copy
+
+    import torch.distributed as dist
+
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.ops import _lib
+
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    cfg = TransformerConfig(vocab_size=512, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, ffn_hidden=512,
+                            max_seq_len=256, qk_norm=False, rope_base=10000.0)
+    model = cfg.build(dtype=torch.bfloat16, init_device=str(dev))
+    ref = copy.deepcopy(model).float()
+    model.apply_tp(dist.group.WORLD, fused=True)
+    ids = torch.randint(0, 512, (2, 256), device=dev)
+    dist.broadcast(ids, 0)
+    out = model(ids, labels=ids)
+    out["loss"].backward()
+    outr = ref(ids, labels=ids)
+    outr["loss"].backward()
+    torch.cuda.synchronize()
+    _lib.check_status("tp_fused")
+    assert abs(out["loss"].item() - outr["loss"].item()) < 2e-2 * outr["loss"].item()
+    rp = dict(ref.named_parameters())
+    att = model.blocks["0"].attention
+    gq = rp["blocks.0.attention.w_q.weight"].grad.view(world, -1, 256)[rank]
+    assert rel(att.w_q.weight.grad, gq) < 6e-2
+    go = rp["blocks.1.attention.w_out.weight"].grad
+    n_in = go.shape[1] // world
+    assert rel(model.blocks["1"].attention.w_out.weight.grad, go[:, rank * n_in:(rank + 1) * n_in]) < 6e-2
+    gw2 = rp["blocks.0.feed_forward.w2.weight"].grad
+    nf = gw2.shape[1] // world
+    assert rel(model.blocks["0"].feed_forward.w2.weight.grad, gw2[:, rank * nf:(rank + 1) * nf]) < 6e-2
+    assert rel(model.blocks["0"].attention_norm.weight.grad, rp["blocks.0.attention_norm.weight"].grad) < 6e-2
+    assert rel(model.embeddings.weight.grad, rp["embeddings.weight"].grad) < 6e-2
+    assert rel(model.lm_head.weight.grad, rp["lm_head.weight"].grad) < 6e-2
+    return True
+
+
+def test_fused_tensor_parallel_two_gpus():
+    _need2()
+    assert all(run_distributed(_tp_fused_worker, 2, backend="nccl"))
