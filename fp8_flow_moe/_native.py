@@ -42,7 +42,9 @@ class _Native:
         s = torch.empty((*gate.shape[:-1], cols // 128), device=gate.device, dtype=torch.float32)
         self._check(self.lib.np_swiglu_quant(C.c_void_p(gate.data_ptr()), C.c_void_p(up.data_ptr()),
                                              C.c_void_p(q.data_ptr()), C.c_void_p(s.data_ptr()), C.c_longlong(rows),
-                                             C.c_longlong(cols), self._stream()), "swiglu_quant")
+                                             C.c_longlong(cols), C.c_longlong(gate.stride(-2) if gate.dim() > 1 else 0),
+                                             C.c_longlong(up.stride(-2) if up.dim() > 1 else 0), self._stream()),
+                    "swiglu_quant")
         return q, s
 
     def dequant_1x128(self, q, s):

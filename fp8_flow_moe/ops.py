@@ -102,15 +102,17 @@ def fused_silu_multiply_quantize(gate: torch.Tensor, up: torch.Tensor, block_siz
                                  ) -> Tuple[torch.Tensor, torch.Tensor]:
     """``quantize(silu(gate) * up)`` in one pass."""
     k = _kernels()
-    if k is not None and gate.is_cuda and gate.dtype == torch.bfloat16 and block_size == 128 and \
-            gate.is_contiguous() and up.is_contiguous():
-        return k.swiglu_quant(gate, up)
+    if k is not None and gate.is_cuda and gate.dtype == torch.bfloat16 and block_size == 128 and gate.dim() == 2 \
+            and gate.stride(1) == 1 and up.stride(1) == 1 and gate.shape[1] % 128 == 0:
+        return k.swiglu_quant(gate, up)  # row-strided views (halves of a [gate | up] buffer) are fine
     return quantize_to_fp8((F.silu(gate.float()) * up.float()).to(gate.dtype), block_size)
 
 
 def fused_swiglu_quantize(gate_up: torch.Tensor, block_size: int = FP8_BLOCK_SIZE):
     """Same for a fused ``[gate | up]`` tensor."""
     g, u = gate_up.chunk(2, dim=-1)
+    if gate_up.is_cuda and gate_up.dim() == 2:
+        return fused_silu_multiply_quantize(g, u, block_size)
     return fused_silu_multiply_quantize(g.contiguous(), u.contiguous(), block_size)
 
 

@@ -281,6 +281,56 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* 
   }
 }
 
+// Fused "split QKV + RoPE": one pass over the [T, H, hd] output of the QKV GEMM (H = hq + 2*hkv heads).
+// Forward (sign=+1): heads [0, rot_heads) are rotated, the rest (V) copied, into one contiguous [T, H, hd]
+// buffer whose q / k / v slices are then used as strided views. Backward (sign=-1): the three gradient
+// tensors (separate row / head strides) are gathered into one contiguous dqkv with the inverse rotation.
+struct HeadSrc {
+  const __nv_bfloat16* p;
+  long long row_stride, head_stride;
+  int heads;
+};
+__global__ void qkv_rope_kernel(HeadSrc s0, HeadSrc s1, HeadSrc s2, __nv_bfloat16* __restrict__ out,
+                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                const int* __restrict__ pos_ids, long long T, int S, int pos_off, int hd, int rot,
+                                int rot_heads, float sign) {
+  const int H = s0.heads + s1.heads + s2.heads;
+  const int half = rot >> 1;
+  const int vec_per_head = hd >> 3;
+  const long long total = T * H * vec_per_head;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(i % vec_per_head);
+    const long long th = i / vec_per_head;
+    const int hh = (int)(th % H);
+    const long long t = th / H;
+    const int d0 = v * 8;
+    const __nv_bfloat16* src;
+    if (hh < s0.heads) src = s0.p + t * s0.row_stride + (long long)hh * s0.head_stride;
+    else if (hh < s0.heads + s1.heads) src = s1.p + t * s1.row_stride + (long long)(hh - s0.heads) * s1.head_stride;
+    else src = s2.p + t * s2.row_stride + (long long)(hh - s0.heads - s1.heads) * s2.head_stride;
+    __nv_bfloat16* dst = out + (t * H + hh) * (long long)hd;
+    float a[8];
+    load8(src + d0, a);
+    if (hh < rot_heads && d0 < rot) {
+      const int pos = pos_ids ? pos_ids[t] : (int)(t % S) + pos_off;
+      const bool lo = d0 < half;
+      float b[8], o[8];
+      load8(src + (lo ? d0 + half : d0 - half), b);
+      const int f0 = lo ? d0 : d0 - half;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float c = cos_t[(size_t)pos * half + f0 + j];
+        const float sn = sin_t[(size_t)pos * half + f0 + j] * sign;
+        o[j] = lo ? (a[j] * c - b[j] * sn) : (a[j] * c + b[j] * sn);
+      }
+      store8(dst + d0, o);
+    } else {
+      store8(dst + d0, a);
+    }
+  }
+}
+
 // cos/sin tables [S, rot/2] in fp32.
 // scaling: 0 none; 1 piecewise (wavelen < orig/high_freq keeps, wavelen > orig/low_freq divides by
 // factor, the band between keeps: the reference's rule, model/rope.py:64-80); 2 YaRN (NTK-by-parts
@@ -548,6 +598,20 @@ NP_API int np_rope(const void* x, void* out, const float* cos_t, const float* si
   rope_kernel<<<grid_for(T * H * (hd / 8), 256, GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (__nv_bfloat16*)out, cos_t, sin_t, pos_ids, T, S, pos_off, H, hd, rot, ld_in,
       ld_out, sign);
+  CHECK_LAUNCH();
+}
+
+// Sources i = 0..2: pointer, row stride and head stride (elements), head count; out: contiguous [T, H, hd].
+NP_API int np_qkv_rope(const void* p0, long long rs0, long long hs0, int h0, const void* p1, long long rs1,
+                       long long hs1, int h1, const void* p2, long long rs2, long long hs2, int h2, void* out,
+                       const float* cos_t, const float* sin_t, const int* pos_ids, long long T, int S, int pos_off,
+                       int hd, int rot, int rot_heads, float sign, void* stream) {
+  if (hd % 8 || rot % 16 || rot > hd || (rs0 | hs0 | rs1 | hs1 | rs2 | hs2) % 8) return 1;
+  if (T <= 0) return 0;
+  HeadSrc s0{(const __nv_bfloat16*)p0, rs0, hs0, h0}, s1{(const __nv_bfloat16*)p1, rs1, hs1, h1},
+      s2{(const __nv_bfloat16*)p2, rs2, hs2, h2};
+  qkv_rope_kernel<<<grid_for(T * (h0 + h1 + h2) * (hd / 8), 256, GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
+      s0, s1, s2, (__nv_bfloat16*)out, cos_t, sin_t, pos_ids, T, S, pos_off, hd, rot, rot_heads, sign);
   CHECK_LAUNCH();
 }
 

@@ -145,8 +145,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     Tile tl;
     tl.g = t / tiles_per_group;
     const int r = t - tl.g * tiles_per_group;
-    tl.m_blk = r % m_blocks;
-    tl.n_blk = r / m_blocks;
+    // bands of 16 M blocks: one wave of CTAs touches ~16 A row-blocks and ~9 B row-blocks instead of all
+    // of A, so both operands are re-read from L2 rather than from DRAM
+    constexpr int BAND = 16;
+    const int per_band = BAND * n_blocks;
+    const int band = r / per_band;
+    const int first_m = band * BAND;
+    const int gsize = (m_blocks - first_m) < BAND ? (m_blocks - first_m) : BAND;
+    const int within = r - band * per_band;
+    tl.m_blk = first_m + within % gsize;
+    tl.n_blk = within / gsize;
     return tl;
   };
   // rows of this M block that carry data (0 = nothing to do); waits for the arrival flag first.

@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const __nv_bfloat16*
 
 // One thread per token. gating: 0 softmax over the selected logits, 1 sigmoid + renormalise.
 // stats: counts[E] (int), psum[E] (sum of full-softmax probabilities), zsum[1] (sum of lse^2).
+template <int EMAX>
 __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restrict__ logits,
                                                           const float* __restrict__ score_bias,
                                                           float* __restrict__ weights, int* __restrict__ indices,
@@ -87,19 +88,21 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
   __syncthreads();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t < T) {
-    float l[MAX_E];
+    float l[EMAX];  // EMAX is a compile-time bound so the logits stay in registers
     float mx = -INFINITY;
-#pragma unroll 1
-    for (int e = 0; e < E; ++e) {
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) {
+      if (e >= E) { l[e] = -INFINITY; continue; }
       l[e] = logits[(size_t)t * E + e] + (score_bias ? score_bias[e] : 0.f);
       mx = fmaxf(mx, l[e]);
     }
     float se = 0.f;
-#pragma unroll 1
-    for (int e = 0; e < E; ++e) se += __expf(l[e] - mx);
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) se += (e < E) ? __expf(l[e] - mx) : 0.f;
     const float lse = mx + logf(se);
-#pragma unroll 1
-    for (int e = 0; e < E; ++e) atomicAdd(&s_p[e], __expf(l[e] - lse));
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e)
+      if (e < E) atomicAdd(&s_p[e], __expf(l[e] - lse));
     atomicAdd(&s_z, lse * lse);
     // top-k by repeated argmax (ties -> lowest index, as torch.topk on distinct values)
     int sel[MAX_K];
@@ -108,8 +111,9 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
     for (int k = 0; k < K; ++k) {
       int best = -1;
       float bv = -INFINITY;
-#pragma unroll 1
-      for (int e = 0; e < E; ++e) {
+#pragma unroll
+      for (int e = 0; e < EMAX; ++e) {
+        if (e >= E) continue;
         const float v = gating == 1 ? 1.f / (1.f + __expf(-l[e])) : l[e];
         if (!((used >> e) & 1ull) && (best < 0 || v > bv)) { best = e; bv = v; }
       }
@@ -255,6 +259,23 @@ __global__ void colsum2_kernel(const float* __restrict__ partial, float* __restr
   out[c] = accumulate ? out[c] + s : s;
 }
 
+// out[c] (+)= sum over rows of a[r, c] for a narrow matrix (cols <= 64): 1024 threads, thread -> (row group, col)
+__global__ void __launch_bounds__(1024) colsum_narrow_kernel(const float* __restrict__ a, float* __restrict__ out,
+                                                             int rows, int cols, int accumulate) {
+  __shared__ float red[1024];
+  const int c = threadIdx.x % cols, g = threadIdx.x / cols, ng = 1024 / cols;
+  float s = 0.f;
+  if (g < ng)
+    for (int r = g; r < rows; r += ng) s += a[(size_t)r * cols + c];
+  red[threadIdx.x] = (g < ng) ? s : 0.f;
+  __syncthreads();
+  if (threadIdx.x < cols) {
+    float t = 0.f;
+    for (int i = 0; i < ng; ++i) t += red[i * cols + threadIdx.x];
+    out[threadIdx.x] = accumulate ? out[threadIdx.x] + t : t;
+  }
+}
+
 // ------------------------------------------------------------------ capacity / positions
 // One CTA, one warp per expert. Phase 1: rank of token t among all tokens that picked expert e.
 // keep[t] = every pick of t is below `capacity` (capacity < 0: keep all). Phase 2: rank among kept.
@@ -281,41 +302,72 @@ __global__ void __launch_bounds__(1024) capacity_scan_kernel(const int* __restri
     for (int t = threadIdx.x; t < T; t += blockDim.x) keep[t] = 1;
   }
   __syncthreads();
-  if (capacity >= 0) {
-    for (int e = warp; e < E; e += nw) {
-      int base = 0;
-      for (int t0 = 0; t0 < T; t0 += 32) {
-        const int t = t0 + lane;
-        bool has = false;
-        if (t < T)
-          for (int k = 0; k < K; ++k) has |= idx[(size_t)t * K + k] == e;
-        const unsigned m = __ballot_sync(0xffffffffu, has);
-        const int pos = base + __popc(m & ((1u << lane) - 1u));
-        if (has && pos >= capacity) {  // benign race: only ever written to 0
-          if (use_smem) s_keep[t] = 0; else keep[t] = 0;
-        }
-        base += __popc(m);
+  // Two-level scan: warp w handles expert (w % E) over segment (w / E) of the tokens; segment totals are
+  // exchanged through shared memory, so the serial ballot loop is T / (32 * segments) long.
+  __shared__ int s_seg[32];
+  const int nseg = (E <= nw) ? nw / E : 1;
+  const int seg_len = ((T + nseg - 1) / nseg + 31) & ~31;
+  for (int e0 = 0; e0 < E; e0 += nw) {
+    const int e = e0 + (E <= nw ? warp % E : warp);
+    const int sg = (E <= nw) ? warp / E : 0;
+    const bool active = e < E && sg < nseg;
+    const int t_lo = sg * seg_len, t_hi = min(T, t_lo + seg_len);
+    for (int phase = 0; phase < 2; ++phase) {
+      if (phase == 0 && capacity < 0) {
+        if (active && lane == 0 && sg == 0) drops[e] = 0;
+        continue;
       }
-      if (lane == 0) drops[e] = base > capacity ? base - capacity : 0;
+      // pass A: count this segment
+      int cnt = 0;
+      if (active) {
+        for (int t0 = t_lo; t0 < t_hi; t0 += 32) {
+          const int t = t0 + lane;
+          bool has = false;
+          if (t < t_hi)
+            for (int k = 0; k < K; ++k) has |= idx[(size_t)t * K + k] == e;
+          if (phase == 1) has = has && (use_smem ? s_keep[t < T ? t : 0] : keep[t < T ? t : 0]) && t < t_hi;
+          cnt += __popc(__ballot_sync(0xffffffffu, has));
+        }
+        if (lane == 0) s_seg[warp] = cnt;
+      }
+      __syncthreads();
+      int base = 0, total = 0;
+      if (active) {
+        for (int q = 0; q < nseg; ++q) {
+          const int v = s_seg[(E <= nw) ? q * E + e : warp];
+          if (q < sg) base += v;
+          total += v;
+        }
+      }
+      __syncthreads();
+      // pass B: positions
+      if (active) {
+        for (int t0 = t_lo; t0 < t_hi; t0 += 32) {
+          const int t = t0 + lane;
+          int kk = -1;
+          if (t < t_hi)
+            for (int k = 0; k < K; ++k)
+              if (idx[(size_t)t * K + k] == e) kk = k;
+          bool has = kk >= 0;
+          if (phase == 1) has = has && (use_smem ? s_keep[t] : keep[t]);
+          const unsigned m = __ballot_sync(0xffffffffu, has);
+          const int pos = base + __popc(m & ((1u << lane) - 1u));
+          if (phase == 0) {
+            if (has && pos >= capacity) {  // benign race: only ever written to 0
+              if (use_smem) s_keep[t] = 0; else keep[t] = 0;
+            }
+          } else if (kk >= 0) {
+            slot_pos[(size_t)t * K + kk] = has ? pos : -1;
+          }
+          base += __popc(m);
+        }
+        if (lane == 0 && sg == 0) {
+          if (phase == 0) drops[e] = total > capacity ? total - capacity : 0;
+          else counts_kept[e] = total;
+        }
+      }
+      __syncthreads();
     }
-  } else {
-    for (int e = threadIdx.x; e < E; e += blockDim.x) drops[e] = 0;
-  }
-  __syncthreads();
-  for (int e = warp; e < E; e += nw) {
-    int base = 0;
-    for (int t0 = 0; t0 < T; t0 += 32) {
-      const int t = t0 + lane;
-      int kk = -1;
-      if (t < T)
-        for (int k = 0; k < K; ++k)
-          if (idx[(size_t)t * K + k] == e) kk = k;
-      const bool kept = kk >= 0 && (use_smem ? s_keep[t] : keep[t]);
-      const unsigned m = __ballot_sync(0xffffffffu, kept);
-      if (kk >= 0) slot_pos[(size_t)t * K + kk] = kept ? base + __popc(m & ((1u << lane) - 1u)) : -1;
-      base += __popc(m);
-    }
-    if (lane == 0) counts_kept[e] = base;
   }
   __syncthreads();
   int nd = 0;
@@ -577,8 +629,13 @@ NP_API int np_router_topk(const float* logits, const float* score_bias, float* w
                           float* psum, float* zsum, int T, int E, int K, int gating, void* stream) {
   if (E > MAX_E || K > MAX_K || K > E) return 1;
   if (T <= 0) return 0;
-  router_topk_kernel<<<(T + 255) / 256, 256, 0, (cudaStream_t)stream>>>(logits, score_bias, weights, indices, counts,
-                                                                        psum, zsum, T, E, K, gating);
+#define TOPK(EM) router_topk_kernel<EM><<<(T + 127) / 128, 128, 0, (cudaStream_t)stream>>>( \
+      logits, score_bias, weights, indices, counts, psum, zsum, T, E, K, gating)
+  if (E <= 8) TOPK(8);
+  else if (E <= 16) TOPK(16);
+  else if (E <= 32) TOPK(32);
+  else TOPK(64);
+#undef TOPK
   CHECK_LAUNCH();
 }
 
@@ -593,7 +650,7 @@ NP_API int np_router_bwd(const float* logits, const float* score_bias, const flo
   CHECK_LAUNCH();
 }
 
-NP_API int np_router_dgate_parts(int T) { return (T + 127) / 128; }
+NP_API int np_router_dgate_parts(int T) { return (T + 31) / 32; }
 // scratch: fp32 [np_router_dgate_parts(T), E, D]; dwg[E, D] (+)= dl^T x ; dbias[E] (+)= column sums of dl.
 NP_API int np_router_dgate(const float* dl, const void* x, float* dwg, float* dbias, float* scratch, int T, int D,
                            int E, int accumulate, void* stream) {
@@ -602,10 +659,10 @@ NP_API int np_router_dgate(const float* dl, const void* x, float* dwg, float* db
   cudaStream_t s = (cudaStream_t)stream;
   const int parts = np_router_dgate_parts(T);
   dim3 grid((D / 8 + 255) / 256, parts);
-  router_dgate_kernel<8><<<grid, 256, 0, s>>>(dl, (const __nv_bfloat16*)x, scratch, T, D, E, 128);
+  router_dgate_kernel<8><<<grid, 256, 0, s>>>(dl, (const __nv_bfloat16*)x, scratch, T, D, E, 32);
   const long long cols = (long long)E * D;
   colsum2_kernel<<<(int)((cols + 63) / 64), 64, 0, s>>>(scratch, dwg, parts, cols, accumulate);
-  if (dbias) colsum2_kernel<<<1, 256, 0, s>>>(dl, dbias, T, E, accumulate);
+  if (dbias) colsum_narrow_kernel<<<1, 1024, 0, s>>>(dl, dbias, T, E, accumulate);
   CHECK_LAUNCH();
 }
 

@@ -36,7 +36,8 @@ __device__ __forceinline__ uint2 quant8(const float* f, float inv) {
 // One half-warp (16 lanes x 8 elements) per 128-element block. mode 0: x; mode 1: silu(x) * y.
 __global__ void __launch_bounds__(256) quant_1x128_kernel(const __nv_bfloat16* __restrict__ x,
                                                           const __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ q,
-                                                          float* __restrict__ scales, long long nblocks, int mode) {
+                                                          float* __restrict__ scales, long long nblocks, int mode,
+                                                          int bpr, long long x_ld, long long y_ld) {
   const int lane16 = threadIdx.x & 15;
   const long long hw = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 4;
   const long long nhw = ((long long)gridDim.x * blockDim.x) >> 4;
@@ -46,10 +47,12 @@ __global__ void __launch_bounds__(256) quant_1x128_kernel(const __nv_bfloat16* _
     const bool ok = b < nblocks;
     float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (ok) {
-      load8(x + b * 128 + lane16 * 8, f);
+      const long long row = b / bpr;
+      const int kb = (int)(b - row * bpr);  // inputs may be strided rows (views into a wider buffer)
+      load8(x + row * x_ld + kb * 128 + lane16 * 8, f);
       if (mode == 1) {
         float g[8];
-        load8(y + b * 128 + lane16 * 8, g);
+        load8(y + row * y_ld + kb * 128 + lane16 * 8, g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = np::silu_f(f[j]) * g[j];
       }
@@ -165,16 +168,19 @@ NP_API int np_quant_1x128(const void* x, void* q, float* scales, long long rows,
   const long long nb = rows * (cols / 128);
   if (nb <= 0) return 0;
   quant_1x128_kernel<<<grid_for_blocks(nb), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, nullptr,
-                                                                           (uint8_t*)q, scales, nb, 0);
+                                                                           (uint8_t*)q, scales, nb, 0,
+                                                                           (int)(cols / 128), cols, cols);
   CHECK_LAUNCH();
 }
+// gate / up: [rows, cols] views with row strides gate_ld / up_ld (elements; 0 = contiguous)
 NP_API int np_swiglu_quant(const void* gate, const void* up, void* q, float* scales, long long rows, long long cols,
-                           void* stream) {
-  if (cols % 128) return 1;
+                           long long gate_ld, long long up_ld, void* stream) {
+  if (cols % 128 || gate_ld % 8 || up_ld % 8) return 1;
   const long long nb = rows * (cols / 128);
   if (nb <= 0) return 0;
   quant_1x128_kernel<<<grid_for_blocks(nb), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (uint8_t*)q, scales, nb, 1);
+      (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (uint8_t*)q, scales, nb, 1, (int)(cols / 128),
+      gate_ld ? gate_ld : cols, up_ld ? up_ld : cols);
   CHECK_LAUNCH();
 }
 NP_API int np_dequant_1x128(const void* q, const float* scales, void* out, long long rows, long long cols,

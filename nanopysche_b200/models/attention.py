@@ -81,25 +81,22 @@ class Attention(nn.Module):
                 kv_cache: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, start_pos: int = 0,
                 position_ids: Optional[torch.Tensor] = None, return_kv: bool = False, **_):
         rt = self._tp_rt if (self._tp_rt is not None and x.is_cuda and x.dtype == torch.bfloat16) else None
+        hq, hkv, hd = self._local_heads, self._local_kv_heads, self.head_dim
+        qkv = None  # fused projection output [B, S, (hq + 2 hkv) * hd] when one GEMM produced all three
         if rt is not None:
             # sequence-parallel input [1, M/tp, D]: all-gather fused into the QKV GEMM
             from ..ops import tp_fused
 
             B, S = rt.batch_shape
-            hq, hkv, hd = self._local_heads, self._local_kv_heads, self.head_dim
             w = self._fused_qkv if self._fused_qkv is not None else \
                 torch.cat([self.w_q.weight, self.w_k.weight, self.w_v.weight], dim=0)
             qkv = tp_fused.ag_linear(x.reshape(-1, x.shape[-1]), w, rt).view(B, S, -1)
-            q = qkv[..., : hq * hd].unflatten(-1, (hq, hd))
-            k = qkv[..., hq * hd:(hq + hkv) * hd].unflatten(-1, (hkv, hd))
-            v = qkv[..., (hq + hkv) * hd:].unflatten(-1, (hkv, hd))
         else:
             B, S, _ = x.shape
             x = copy_to_tp_region(x, self._tp_group, self._tp_size)
-            q, k, v = self._project_qkv(x)
-        if self.q_norm is not None:
-            q = self.q_norm(q.float()).to(x.dtype) if q.dtype != torch.float32 else self.q_norm(q)
-            k = self.k_norm(k.float()).to(x.dtype) if k.dtype != torch.float32 else self.k_norm(k)
+            fused = self._fused_qkv
+            if fused is not None and x.is_cuda and x.dtype == fused.dtype and self.w_q.bias is None:
+                qkv = gemm_ops.linear(x, fused)
         if position_ids is None and self._cp_module is not None:
             position_ids = self._cp_module.local_positions(S, x.device)
         max_pos = start_pos + S if position_ids is None else None
@@ -110,8 +107,20 @@ class Attention(nn.Module):
         pid = None
         if position_ids is not None:
             pid = position_ids if position_ids.dim() == 2 else position_ids[None, :].expand(B, S)
-        q = rope_ops.apply_rope(q, cos, sin, start_pos, pid)
-        k = rope_ops.apply_rope(k, cos, sin, start_pos, pid)
+        if qkv is not None and self.q_norm is None:
+            q, k, v = rope_ops.qkv_rope(qkv, cos, sin, hq, hkv, hd, start_pos, pid)  # split + rotate in one kernel
+        else:
+            if qkv is not None:
+                q = qkv[..., : hq * hd].unflatten(-1, (hq, hd))
+                k = qkv[..., hq * hd:(hq + hkv) * hd].unflatten(-1, (hkv, hd))
+                v = qkv[..., (hq + hkv) * hd:].unflatten(-1, (hkv, hd))
+            else:
+                q, k, v = self._project_qkv(x)
+            if self.q_norm is not None:
+                q = self.q_norm(q.float()).to(x.dtype) if q.dtype != torch.float32 else self.q_norm(q)
+                k = self.k_norm(k.float()).to(x.dtype) if k.dtype != torch.float32 else self.k_norm(k)
+            q = rope_ops.apply_rope(q, cos, sin, start_pos, pid)
+            k = rope_ops.apply_rope(k, cos, sin, start_pos, pid)
         if kv_cache is not None:
             k = torch.cat([kv_cache[0], k], dim=1)
             v = torch.cat([kv_cache[1], v], dim=1)

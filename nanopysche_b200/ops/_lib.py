@@ -70,6 +70,22 @@ class CombineArgs(C.Structure):
     ]
 
 
+class Fp8GemmArgs(C.Structure):
+    """Mirror of ``NpFp8GemmArgs`` in csrc/gemm_fp8_sm100.cu."""
+
+    _fields_ = [
+        ("A", c_void_p), ("B", c_void_p), ("C", c_void_p), ("sa", c_void_p), ("sb", c_void_p),
+        ("lda", c_ll), ("ldb", c_ll), ("ldc", c_ll), ("a_rows", c_ll), ("b_rows", c_ll),
+        ("M", c_int), ("N", c_int), ("K", c_int), ("out_f32", c_int), ("mode", c_int),
+        ("mblk_group", c_void_p), ("mblk_rows", c_void_p), ("group_stride_b", c_ll),
+        ("ready_flags", c_void_p), ("mblk_flag", c_void_p), ("epoch", c_int), ("epoch_base", c_void_p),
+        ("flag_limit_ns", c_ull),
+        ("row_dst", c_void_p), ("peer_base", c_void_p),
+        ("done_counters", c_void_p), ("done_expected", c_void_p), ("done_flag_ptr", c_void_p),
+        ("max_ctas", c_int),
+    ]
+
+
 class KernelError(RuntimeError):
     """A kernel launch failed or a kernel reported a device-side status (timeout, bounds)."""
 
@@ -103,6 +119,7 @@ def lib():
     _LIB.np_gemm_bf16.argtypes = [C.POINTER(GemmArgs), c_void_p]
     _LIB.np_ep_dispatch.argtypes = [C.POINTER(DispatchArgs), c_void_p]
     _LIB.np_ep_combine.argtypes = [C.POINTER(CombineArgs), c_void_p]
+    _LIB.np_gemm_fp8_block.argtypes = [C.POINTER(Fp8GemmArgs), c_void_p]
     _LIB.np_status_read.argtypes = [C.POINTER(c_int)]
     return _LIB
 

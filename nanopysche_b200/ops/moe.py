@@ -96,7 +96,8 @@ class FusedMoERuntime:
     """Symmetric buffers, flags and static tables shared by all MoE layers of one model replica."""
 
     def __init__(self, *, tokens: int, d_model: int, hidden: int, num_experts: int, top_k: int, n_layers: int,
-                 capacity_factor: Optional[float], group=None, device=None, max_ctas_dispatch: int = 0):
+                 capacity_factor: Optional[float], group=None, device=None, max_ctas_dispatch: int = 0,
+                 fp8: bool = False):
         import torch.distributed as dist
 
         from ..parallel.symm import SymmetricHeap
@@ -116,11 +117,20 @@ class FusedMoERuntime:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         row_bytes = self.rows_total * d_model * 2
         slot_bytes = tokens * top_k * d_model * 2
+        self.fp8 = bool(fp8) and d_model % 256 == 0 and hidden % 128 == 0
         need = n_layers * (row_bytes + slot_bytes) + row_bytes + slot_bytes + self.rows_total * 8 + (1 << 20)
+        if self.fp8:  # e4m3 rows + 1x128 scales per layer instead of... in addition to the bf16 buffers
+            need += n_layers * (self.rows_total * d_model + self.rows_total * (d_model // 128) * 4 + 8192)
         self.heap = SymmetricHeap(need, group, self.device)
         h = self.heap
         self.recv_x = [h.alloc((self.rows_total, d_model), torch.bfloat16) for _ in range(n_layers)]
         self.ret_y = [h.alloc((tokens * top_k, d_model), torch.bfloat16) for _ in range(n_layers)]
+        self.recv_xq = self.recv_xs = self.p_recv_xq = self.p_recv_xs = None
+        if self.fp8:
+            self.recv_xq = [h.alloc((self.rows_total, d_model), torch.uint8) for _ in range(n_layers)]
+            self.recv_xs = [h.alloc((self.rows_total, d_model // 128), torch.float32) for _ in range(n_layers)]
+            self.p_recv_xq = [h.ptr_array(t) for t in self.recv_xq]
+            self.p_recv_xs = [h.ptr_array(t) for t in self.recv_xs]
         self.recv_g = h.alloc((self.rows_total, d_model), torch.bfloat16)
         self.ret_g = h.alloc((tokens * top_k, d_model), torch.bfloat16)
         self.row_dst = h.alloc((self.rows_total,), torch.int64)
@@ -164,15 +174,15 @@ class FusedMoERuntime:
         self.heap.end_step()
 
     # -- kernels -------------------------------------------------------------------------------------
-    def dispatch(self, x2, indices, slot_pos, counts_kept, scale, p_rows, epoch):
+    def dispatch(self, x2, indices, slot_pos, counts_kept, scale, p_rows, epoch, p_scales=None):
         a = _lib.DispatchArgs()
         a.x, a.indices, a.slot_pos, a.counts_kept = x2.data_ptr(), indices.data_ptr(), slot_pos.data_ptr(), \
             counts_kept.data_ptr()
         a.slot_scale = scale.data_ptr() if scale is not None else None
         a.T, a.K, a.D, a.E, a.E_local, a.n_ranks, a.my_rank = self.T, self.K, self.D, self.E, self.E_local, self.N, \
             self.rank
-        a.region_rows, a.quant = self.R, 0
-        a.peer_rows, a.peer_scales = p_rows.data_ptr(), None
+        a.region_rows, a.quant = self.R, int(p_scales is not None)
+        a.peer_rows, a.peer_scales = p_rows.data_ptr(), (p_scales.data_ptr() if p_scales is not None else None)
         a.peer_row_dst, a.peer_mblk_rows = self.p_row_dst.data_ptr(), self.p_mblk_rows.data_ptr()
         a.peer_src_blocks, a.peer_flags = self.p_src_blocks.data_ptr(), self.p_dispatch_flags.data_ptr()
         a.done_ctr, a.epoch, a.write_meta, a.max_ctas = self.dispatch_ctr.data_ptr(), epoch, 1, self.max_ctas_dispatch
@@ -232,6 +242,21 @@ class FusedMoERuntime:
         _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "grouped_gemm")
         return out
 
+    def grouped_gemm_fp8(self, aq, sa, bq, sb, *, N, out=None, wait_epoch=0, push_ptrs=None, push_epoch=0):
+        """Row-grouped block-scaled fp8 GEMM over the receive-buffer layout (B K-major, N rows per expert)."""
+        from .gemm_fp8 import gemm_fp8_block
+
+        fill = {"mblk_flag": self.mblk_flag.data_ptr(), "epoch_base": self.heap.epoch_base.data_ptr()}
+        if wait_epoch:
+            fill.update(ready_flags=self.dispatch_flags.data_ptr(), epoch=wait_epoch, flag_limit_ns=WAIT_LIMIT_NS)
+        if push_ptrs is not None:
+            self.done_counters.zero_()
+            fill.update(row_dst=self.row_dst.data_ptr(), peer_base=push_ptrs.data_ptr(),
+                        done_counters=self.done_counters.data_ptr(), done_expected=self.src_blocks.data_ptr(),
+                        done_flag_ptr=self.p_done_flag.data_ptr(), epoch=push_epoch)
+        return gemm_fp8_block(aq, sa, bq, sb, out=out, mblk_group=self.mblk_group, mblk_rows=self.mblk_rows,
+                              rows_per_group=N, fill=fill)
+
     def grouped_wgrad(self, A, Bm, w: torch.Tensor, *, M, N):
         """dW[g] (+)= A[rows of g]^T @ B[rows of g] for every local expert g (mode 2), into ``main_grad``
         when the weight has one, else a fresh tensor that is returned."""
@@ -271,14 +296,33 @@ class _FusedMoE(torch.autograd.Function):
         _lib.call("capacity_scan", indices32, T, rt.E, K, rt.capacity, slot_pos, keep, counts_kept, drops, n_dropped)
         sent = counts_kept.view(rt.N, rt.E_local).sum(1).to(torch.int32)
         e1 = rt.next_epoch()
-        rt.dispatch(x2, indices32, slot_pos, counts_kept, None, rt.p_recv_x[layer], e1)
-        # experts: [gate|up] GEMM with SwiGLU epilogue, waits per block on the source's arrival flag
-        h = torch.empty((rt.rows_total, H), device=dev, dtype=torch.bfloat16)
         gu = torch.empty((rt.rows_total, 2 * H), device=dev, dtype=torch.bfloat16)
-        rt.grouped_gemm(rt.recv_x[layer], w1, N=H, K=D, b_mn=False, group_stride_b=H, out=h, B2=w3, C2=gu,
-                        wait_epoch=e1)
-        # down projection (w2 is stored [H, D] per expert: MN-major B), rows pushed back to their sources
-        rt.grouped_gemm(h, w2, N=D, K=H, b_mn=True, group_stride_b=H, push_ptrs=rt.p_ret_y[layer], push_epoch=e1)
+        if rt.fp8:
+            # FP8-Flow-MoE forward: rows travel as e4m3 + 1x128 scales, both expert GEMMs run on the fp8
+            # tensor-core path with fp32 per-block scaling, SwiGLU and re-quantisation are one kernel
+            from fp8_flow_moe import ops as fops
+
+            E_l = rt.E_local
+            w1q, s1 = fops.quantize_weight_blockwise(w1.detach())
+            w3q, s3 = fops.quantize_weight_blockwise(w3.detach())
+            w2t = w2.detach().view(E_l, H, D).transpose(1, 2).contiguous().view(E_l * D, H)
+            w2q, s2 = fops.quantize_weight_blockwise(w2t)
+            rt.dispatch(x2, indices32, slot_pos, counts_kept, None, rt.p_recv_xq[layer], e1,
+                        p_scales=rt.p_recv_xs[layer])
+            xq, xs = rt.recv_xq[layer].view(torch.float8_e4m3fn), rt.recv_xs[layer]
+            rt.grouped_gemm_fp8(xq, xs, w1q, s1, N=H, out=gu[:, :H], wait_epoch=e1)
+            rt.grouped_gemm_fp8(xq, xs, w3q, s3, N=H, out=gu[:, H:], wait_epoch=e1)
+            hq, hs = fops.fused_silu_multiply_quantize(gu[:, :H], gu[:, H:])
+            rt.grouped_gemm_fp8(hq, hs, w2q, s2, N=D, push_ptrs=rt.p_ret_y[layer], push_epoch=e1)
+        else:
+            rt.dispatch(x2, indices32, slot_pos, counts_kept, None, rt.p_recv_x[layer], e1)
+            # experts: [gate|up] GEMM with SwiGLU epilogue, waits per block on the source's arrival flag
+            h = torch.empty((rt.rows_total, H), device=dev, dtype=torch.bfloat16)
+            rt.grouped_gemm(rt.recv_x[layer], w1, N=H, K=D, b_mn=False, group_stride_b=H, out=h, B2=w3, C2=gu,
+                            wait_epoch=e1)
+            # down projection (w2 is stored [H, D] per expert: MN-major B), rows pushed back to their sources
+            rt.grouped_gemm(h, w2, N=D, K=H, b_mn=True, group_stride_b=H, push_ptrs=rt.p_ret_y[layer],
+                            push_epoch=e1)
         out = torch.empty((T, D), device=dev, dtype=torch.bfloat16)
         rt.combine(rt.ret_y[layer], slot_pos, weights, out, sent, e1)
         ctx.save_for_backward(x2, weights, indices32, slot_pos, counts_kept, sent, gu, w1, w3, w2)
@@ -311,7 +355,12 @@ class _FusedMoE(torch.autograd.Function):
         dgu = glu_bwd(gu, dh)
         del dh
         dg, du = dgu[:, :H], dgu[:, H:]
-        xr = rt.recv_x[layer]
+        if rt.fp8:  # the rows arrived as e4m3: dequantise once for the (bf16) weight-gradient GEMMs
+            from fp8_flow_moe import ops as fops
+
+            xr = fops.dequantize_from_fp8(rt.recv_xq[layer].view(torch.float8_e4m3fn), rt.recv_xs[layer])
+        else:
+            xr = rt.recv_x[layer]
         dw1 = rt.grouped_wgrad(dg, xr, w1, M=H, N=D)
         dw3 = rt.grouped_wgrad(du, xr, w3, M=H, N=D)
         # dX = dG @ w1 + dU @ w3, pushed back to the sources
@@ -324,10 +373,17 @@ class _FusedMoE(torch.autograd.Function):
 
 def build_runtime(moe_modules, *, tokens: int, group=None, device=None) -> FusedMoERuntime:
     """One runtime for all MoE layers of a model (they must share geometry)."""
+    import torch.distributed as dist
+
     m0 = moe_modules[0]
+    world = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
+    # FP8-Flow-MoE switch: fp8 expert GEMMs once the expected tokens per expert reach the threshold
+    per_expert = tokens * m0.top_k * world / m0.num_experts
+    fp8 = bool(m0.fp8_flow_moe_enabled and m0.fp8_recipe in ("blockwise", "flow_moe") and
+               per_expert >= m0.fp8_gemm_threshold)
     rt = FusedMoERuntime(tokens=tokens, d_model=m0.d_model, hidden=m0.hidden_size, num_experts=m0.num_experts,
                          top_k=m0.top_k, n_layers=len(moe_modules), capacity_factor=m0.capacity_factor, group=group,
-                         device=device)
+                         device=device, fp8=fp8)
     for m in moe_modules:
         m._fused_runtime = rt
     return rt

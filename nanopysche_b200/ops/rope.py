@@ -9,6 +9,7 @@ with the sine negated. ``yarn`` adds the NTK-by-parts ramp and attention scale t
 """
 from __future__ import annotations
 
+import ctypes as C
 import math
 
 import torch
@@ -120,3 +121,66 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos_offset
             pos_ids = pos_ids.reshape(-1).to(torch.int32)
         return _Rope.apply(x, cos, sin, pos_offset, pos_ids, False)
     return apply_rope_ref(x, cos, sin, pos_offset, pos_ids)
+
+
+class _QKVRope(torch.autograd.Function):
+    """Split the fused QKV GEMM output into q / k / v and rotate q and k, one kernel each way."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, hq, hkv, hd, pos_offset, pos_ids):
+        B, S, W = qkv.shape
+        H = hq + 2 * hkv
+        out = torch.empty((B, S, H, hd), device=qkv.device, dtype=qkv.dtype)
+        rs = qkv.stride(1)
+        base = qkv.data_ptr()
+        es = qkv.element_size()
+        _lib.check(_lib.lib().np_qkv_rope(
+            C.c_void_p(base), C.c_longlong(rs), C.c_longlong(hd), hq,
+            C.c_void_p(base + hq * hd * es), C.c_longlong(rs), C.c_longlong(hd), hkv,
+            C.c_void_p(base + (hq + hkv) * hd * es), C.c_longlong(rs), C.c_longlong(hd), hkv,
+            C.c_void_p(out.data_ptr()), C.c_void_p(cos.data_ptr()), C.c_void_p(sin.data_ptr()),
+            C.c_void_p(pos_ids.data_ptr() if pos_ids is not None else 0), C.c_longlong(B * S), S, int(pos_offset), hd,
+            2 * cos.shape[1], hq + hkv, C.c_float(1.0), C.c_void_p(_lib.stream())), "qkv_rope")
+        ctx.save_for_backward(cos, sin, pos_ids if pos_ids is not None else cos.new_empty(0))
+        ctx.meta = (hq, hkv, hd, pos_offset, pos_ids is not None, qkv.shape)
+        return out[:, :, :hq], out[:, :, hq:hq + hkv], out[:, :, hq + hkv:]
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        cos, sin, pos_ids = ctx.saved_tensors
+        hq, hkv, hd, pos_offset, has_ids, shape = ctx.meta
+        B, S, W = shape
+        fixed = []
+        for g, h in ((dq, hq), (dk, hkv), (dv, hkv)):
+            if g is None:
+                g = torch.zeros((B, S, h, hd), device=cos.device, dtype=torch.bfloat16)
+            if g.stride(3) != 1 or g.stride(0) != S * g.stride(1) or g.stride(1) % 8 or g.stride(2) % 8:
+                g = g.contiguous()
+            fixed.append(g)
+        dq, dk, dv = fixed
+        out = torch.empty((B, S, W), device=dq.device, dtype=dq.dtype)
+        _lib.check(_lib.lib().np_qkv_rope(
+            C.c_void_p(dq.data_ptr()), C.c_longlong(dq.stride(1)), C.c_longlong(dq.stride(2)), hq,
+            C.c_void_p(dk.data_ptr()), C.c_longlong(dk.stride(1)), C.c_longlong(dk.stride(2)), hkv,
+            C.c_void_p(dv.data_ptr()), C.c_longlong(dv.stride(1)), C.c_longlong(dv.stride(2)), hkv,
+            C.c_void_p(out.data_ptr()), C.c_void_p(cos.data_ptr()), C.c_void_p(sin.data_ptr()),
+            C.c_void_p(pos_ids.data_ptr() if has_ids else 0), C.c_longlong(B * S), S, int(pos_offset), hd,
+            2 * cos.shape[1], hq + hkv, C.c_float(-1.0), C.c_void_p(_lib.stream())), "qkv_rope_bwd")
+        return out, None, None, None, None, None, None, None
+
+
+def qkv_rope(qkv: torch.Tensor, cos, sin, hq: int, hkv: int, hd: int, pos_offset: int = 0, pos_ids=None):
+    """``qkv [B, S, (hq+2*hkv)*hd]`` -> rotated ``q [B,S,hq,hd]``, ``k [B,S,hkv,hd]`` and ``v`` (strided views of
+    one buffer). Falls back to slicing + ``apply_rope`` off the kernel path."""
+    B, S, W = qkv.shape
+    ok = (qkv.is_cuda and qkv.dtype == torch.bfloat16 and hd % 8 == 0 and (2 * cos.shape[1]) % 16 == 0 and
+          qkv.stride(2) == 1 and qkv.stride(1) % 8 == 0 and qkv.stride(0) == S * qkv.stride(1) and
+          cos.dtype == torch.float32)
+    if ok:
+        if pos_ids is not None:
+            pos_ids = pos_ids.reshape(-1).to(torch.int32)
+        return _QKVRope.apply(qkv, cos, sin, hq, hkv, hd, pos_offset, pos_ids)
+    q = qkv[..., : hq * hd].unflatten(-1, (hq, hd))
+    k = qkv[..., hq * hd:(hq + hkv) * hd].unflatten(-1, (hkv, hd))
+    v = qkv[..., (hq + hkv) * hd:].unflatten(-1, (hkv, hd))
+    return apply_rope(q, cos, sin, pos_offset, pos_ids), apply_rope(k, cos, sin, pos_offset, pos_ids), v

@@ -245,3 +245,59 @@ def test_capacity_scan_matches_reference_rule():
             assert ck[e].item() == len(rows)
             assert [sp[t, k].item() for t, k in rows] == list(range(len(rows)))
         assert (sp[~ref_keep] == -1).all()
+
+
+def test_qkv_rope_fused_split():
+    from nanopysche_b200.ops import rope as R
+
+    torch.manual_seed(11)
+    hq, hkv, hd = 4, 2, 128
+    cos, sin = R.rope_tables(64, hd, 10000.0, device="cuda")
+    qkv = torch.randn(2, 32, (hq + 2 * hkv) * hd, device="cuda").bfloat16().requires_grad_(True)
+    q, k, v = R.qkv_rope(qkv, cos, sin, hq, hkv, hd, 5)
+    qs = qkv.detach().float()[..., : hq * hd].unflatten(-1, (hq, hd))
+    ks = qkv.detach().float()[..., hq * hd:(hq + hkv) * hd].unflatten(-1, (hkv, hd))
+    vs = qkv.detach()[..., (hq + hkv) * hd:].unflatten(-1, (hkv, hd))
+    assert rel(q, R.apply_rope_ref(qs, cos, sin, 5)) < 6e-3 and rel(k, R.apply_rope_ref(ks, cos, sin, 5)) < 6e-3
+    assert torch.equal(v, vs)
+    gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+    torch.autograd.backward([q, k, v], [gq, gk, gv])
+    g = qkv.grad
+    assert rel(g[..., : hq * hd].unflatten(-1, (hq, hd)), R.apply_rope_ref(gq.float(), cos, sin, 5, sign=-1.0)) < 6e-3
+    assert rel(g[..., hq * hd:(hq + hkv) * hd].unflatten(-1, (hkv, hd)),
+               R.apply_rope_ref(gk.float(), cos, sin, 5, sign=-1.0)) < 6e-3
+    assert torch.equal(g[..., (hq + hkv) * hd:].unflatten(-1, (hkv, hd)), gv)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (512, 384, 640), (4096, 2816, 2048), (4096, 2048, 2816)])
+def test_fp8_block_gemm_matches_dequantised_reference(M, N, K):
+    from fp8_flow_moe import ops as fops
+    from nanopysche_b200.ops.gemm_fp8 import gemm_fp8_block, gemm_fp8_block_ref
+
+    torch.manual_seed(12)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    xq, xs = fops.quantize_to_fp8(x)
+    wq, ws = fops.quantize_weight_blockwise(w)
+    got = gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.float32)
+    ref = gemm_fp8_block_ref(xq, xs, wq, ws, out_dtype=torch.float32)
+    assert rel(got, ref) < 1e-4
+    assert rel(got, x.float() @ w.float().t()) < 0.06  # fp8 quantisation error
+
+
+def test_fp8_block_gemm_grouped():
+    from fp8_flow_moe import ops as fops
+    from nanopysche_b200.ops.gemm_fp8 import gemm_fp8_block, gemm_fp8_block_ref
+
+    torch.manual_seed(13)
+    E, N, K, blocks = 4, 256, 512, 10
+    x = torch.randn(blocks * 128, K, device="cuda").bfloat16()
+    w = (torch.randn(E * N, K, device="cuda") * 0.05).bfloat16()
+    grp = torch.tensor([0, 0, 1, 3, 3, 3, 2, -1, 1, 0], dtype=torch.int32, device="cuda")
+    rows = torch.where(grp >= 0, 128, 0).to(torch.int32)
+    xq, xs = fops.quantize_to_fp8(x)
+    wq, ws = fops.quantize_weight_blockwise(w)
+    out = torch.zeros(blocks * 128, N, device="cuda", dtype=torch.float32)
+    gemm_fp8_block(xq, xs, wq, ws, out=out, mblk_group=grp.clamp_min(0), mblk_rows=rows, rows_per_group=N)
+    ref = gemm_fp8_block_ref(xq, xs, wq, ws, grp, N, torch.float32)
+    assert rel(out, ref) < 1e-4
