@@ -1,0 +1,988 @@
+// Flash attention for sm_100a (head_dim 128, bf16, causal or full, GQA-native), forward and backward,
+// on tcgen05 tensor cores: S = Q K^T and O += P V (and the five backward products) are tcgen05.mma with
+// TMEM accumulators, Q/K/V/dO tiles arrive by 4-D TMA straight from the strided [B, S, H, hd] tensors
+// (so the q / k / v slices of the fused QKV GEMM output need no copy), softmax runs in registers on
+// four warps that read S out of TMEM, and P / dS go back to shared memory in the 128-byte-swizzled
+// operand layout for the next MMA. Scores are never written to global memory.
+//
+// K/V (forward, dQ) and Q/dO (dK/dV) may come from a *list* of tensor maps - one per context-parallel
+// rank, pointing into that rank's symmetric memory - so a sequence sharded over GPUs is attended to by
+// loading the peers' tiles directly over NVLink inside the kernel (plain TMA loads, no multicast):
+// the context-parallel KV exchange is fused into the attention kernel. Causality uses global token
+// positions of each 128-row block, which also expresses the zig-zag layout.
+//
+// Replaces F.scaled_dot_product_attention (reference: model/attention.py:121-127) and the dense
+// per-step matmul+softmax of its ring attention (distributed/context_parallel.py:301-317).
+#include "common.cuh"
+
+namespace {
+
+constexpr int KID_ATTN = 30;
+constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int TILE_BYTES = 128 * 128 * 2;   // one [128 x 128] bf16 tile = two 64-column swizzled chunks
+constexpr int CHUNK_BYTES = 128 * 64 * 2;
+constexpr int MAX_SRC = 8;
+
+struct TmapList {
+  CUtensorMap m[MAX_SRC];
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+// [128 rows x 128 cols] tile (cols = hd) of head `h`, rows starting at `s0`, batch `b`: two 64-col chunks
+__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int h, int s0, int b) {
+  tma_load_4d(dst, tm, bar, 0, h, s0, b);
+  tma_load_4d(dst + CHUNK_BYTES, tm, bar, 64, h, s0, b);
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// K-major operand [rows, 128 k]: k-step kk (16 elements) -> chunk kk/4, +32 B per step inside the chunk
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int kk) {
+  return np::make_smem_desc(tile + (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
+}
+// MN-major operand stored as [k rows, 128 mn cols] (two 64-col chunks): k-step = 16 rows = +2048 B,
+// LBO = distance between the two 64-wide chunks
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int kk) {
+  return np::make_smem_desc(tile + kk * 2048, CHUNK_BYTES, 1024);
+}
+// byte offset of element (row r, col c..c+7) inside a swizzled [128 x 128] bf16 tile
+__device__ __forceinline__ uint32_t swz_off(int r, int cgroup) {  // cgroup = c / 8 in [0, 16)
+  const int chunk = cgroup >> 3, u = cgroup & 7;
+  return chunk * CHUNK_BYTES + r * 128 + ((u ^ (r & 7)) << 4);
+}
+
+struct FwdParams {
+  __nv_bfloat16* O; long long o_sb, o_ss, o_sh;   // output strides (elements): batch, seq, head
+  float* lse;                                      // [B, Hq, Sq]
+  int B, Sq, Hq, Hkv, causal;
+  float scale_log2;
+  int n_src;                                       // number of KV sources (1 without context parallelism)
+  int src_blocks;                                  // 128-row KV blocks per source
+  int src_len;                                     // valid KV rows per source
+  const int* q_blk_pos;                            // [Sq/128] global position of each local Q block (nullptr: i*128 + q_off)
+  const int* k_blk_pos;                            // [n_src * src_blocks] global position of each KV block (nullptr: j*128)
+  int q_off;
+};
+
+// tcgen05.mma with the A operand in tensor memory: D[tmem] (+)= A[tmem, 128 lanes x K] * B[smem desc]
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// mbarrier wait whose outcome is the same for every lane of the warp, so that the .sync.aligned tensor-memory
+// instructions that follow are never reached by part of a warp
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int kid, int where) {
+  return __all_sync(0xffffffffu, np::mbar_wait(bar, parity, abort_flag, kid, where));
+}
+
+constexpr int MAX_VIS = 1024;   // visible KV (or Q) blocks one CTA may iterate over
+
+// Barrier slots of the forward kernel
+enum { FB_Q = 0, FB_K = 1, FB_V = 3, FB_KVE = 5, FB_S = 7, FB_P = 9, FB_O = 10, FB_OE = 11, FB_COUNT = 12 };
+
+// P_TMEM: the probabilities go back into tensor memory (over the S columns they came from) and feed
+// the P V product as a TMEM A operand; otherwise they go through shared memory.
+template <bool P_TMEM>
+__global__ void __launch_bounds__(192, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ TmapList tmK,
+                const __grid_constant__ TmapList tmV, const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (np::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = base, sK0 = base + TILE_BYTES, sV0 = sK0 + 2 * TILE_BYTES, sP = sV0 + 2 * TILE_BYTES;
+  const uint32_t after_tiles = sP + (P_TMEM ? 0 : TILE_BYTES);
+  const uint32_t bar = after_tiles;
+  auto B_ = [&](int i) { return bar + 8u * i; };
+  uint8_t* gen0 = smem_raw + (base - np::smem_u32(smem_raw));
+  uint8_t* tail = gen0 + (after_tiles - base) + 8 * FB_COUNT;
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
+  volatile int* nvis_s = reinterpret_cast<volatile int*>(tail + 12);
+  volatile short* vis = reinterpret_cast<volatile short*>(tail + 16);
+  uint8_t* sP_gen = gen0 + (sP - base);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.Sq + BQ - 1) / BQ;
+  const int qb = nqb - 1 - (int)blockIdx.x;  // heaviest (latest) blocks first under causal masking
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / (p.Hq / p.Hkv);
+  const int q_pos0 = p.q_blk_pos ? p.q_blk_pos[qb] : qb * BQ + p.q_off;
+  const int total_blocks = p.n_src * p.src_blocks;
+  auto k_pos0 = [&](int j) { return p.k_blk_pos ? p.k_blk_pos[j] : (j % p.src_blocks) * BKV; };
+
+  if (threadIdx.x == 0) {
+    np::mbar_init(B_(FB_Q), 1);
+    for (int s = 0; s < 2; ++s) {
+      np::mbar_init(B_(FB_K + s), 1); np::mbar_init(B_(FB_V + s), 1); np::mbar_init(B_(FB_KVE + s), 1);
+      np::mbar_init(B_(FB_S + s), 1);
+    }
+    np::mbar_init(B_(FB_P), 4); np::mbar_init(B_(FB_O), 1); np::mbar_init(B_(FB_OE), 4);
+    *abort_flag = 0;
+    np::mbar_fence_init();
+    // a KV block takes part unless causality hides all of it from every row of this Q block
+    int n = 0;
+    for (int j = 0; j < total_blocks && n < MAX_VIS; ++j)
+      if (!p.causal || k_pos0(j) <= q_pos0 + BQ - 1) vis[n++] = (short)j;
+    *nvis_s = n;
+  }
+  if (warp == 1) {
+    np::tmem_alloc(np::smem_u32((const void*)tmem_ptr_smem), 512);
+    np::tmem_relinquish();
+  }
+  np::tc_fence_before();
+  __syncthreads();
+  np::tc_fence_after();
+  const uint32_t tmem = *tmem_ptr_smem;
+  const uint32_t tO = tmem + 256;   // S buffers at columns 0 and 128
+  const int nvis = *nvis_s;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      np::mbar_expect_tx(B_(FB_Q), TILE_BYTES);
+      load_tile(sQ, &tmQ, B_(FB_Q), h, qb * BQ, b);
+      for (int i = 0; i < nvis && !*abort_flag; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = (uint32_t)(i >> 1) & 1u;
+        if (!np::mbar_wait(B_(FB_KVE + st), ph ^ 1u, abort_flag, KID_ATTN, 1)) break;
+        const int j = vis[i];
+        const int src = j / p.src_blocks, jb = j - src * p.src_blocks;
+        np::mbar_expect_tx(B_(FB_K + st), TILE_BYTES);
+        load_tile(sK0 + st * TILE_BYTES, &tmK.m[src], B_(FB_K + st), hkv, jb * BKV, b);
+        np::mbar_expect_tx(B_(FB_V + st), TILE_BYTES);
+        load_tile(sV0 + st * TILE_BYTES, &tmV.m[src], B_(FB_V + st), hkv, jb * BKV, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_qk = np::make_idesc(128, 128, 1, 1, 0, 0);   // Q (K-major) x K (K-major)
+      const uint32_t idesc_pv = np::make_idesc(128, 128, 1, 1, 0, 1);   // P (K-major) x V (MN-major)
+      bool ok = np::mbar_wait(B_(FB_Q), 0, abort_flag, KID_ATTN, 2);
+      auto issue_qk = [&](int i) {
+        const int st = i & 1;
+        if (!np::mbar_wait(B_(FB_K + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN, 3)) return false;
+        np::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          np::tc_mma_f16(tmem + st * 128, desc_kmajor(sQ, kk), desc_kmajor(sK0 + st * TILE_BYTES, kk), idesc_qk, kk > 0);
+        np::tc_commit(B_(FB_S + st));
+        return true;
+      };
+      if (ok && nvis > 0) ok = issue_qk(0);
+      for (int i = 0; i < nvis && ok && !*abort_flag; ++i) {
+        const int st = i & 1;
+        // S of the next block is computed while the softmax warps work on this one. Its buffer was last
+        // read for block i-1, whose probabilities were awaited before P V of block i-1 was issued.
+        if (i + 1 < nvis) ok = issue_qk(i + 1);
+        ok = ok && np::mbar_wait(B_(FB_P), (uint32_t)i & 1u, abort_flag, KID_ATTN, 5) &&      // P is ready
+             np::mbar_wait(B_(FB_V + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN, 4) &&
+             np::mbar_wait(B_(FB_OE), ((uint32_t)i & 1u) ^ 1u, abort_flag, KID_ATTN, 6);      // previous O partial consumed
+        if (!ok) break;
+        np::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          if (P_TMEM)
+            tc_mma_f16_ts(tO, tmem + st * 128 + kk * 8, desc_mnmajor(sV0 + st * TILE_BYTES, kk), idesc_pv, kk > 0);
+          else
+            np::tc_mma_f16(tO, desc_kmajor(sP, kk), desc_mnmajor(sV0 + st * TILE_BYTES, kk), idesc_pv, kk > 0);
+        }
+        np::tc_commit(B_(FB_O));
+        np::tc_commit(B_(FB_KVE + st));
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                 // row inside the Q block
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const int q_pos = q_pos0 + r;
+    float m = -INFINITY, l = 0.f;
+    float o[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    bool ok = true;
+    for (int i = 0; i < nvis && ok && !*abort_flag; ++i) {
+      const int st = i & 1;
+      const int j = vis[i];
+      const int jb = j % p.src_blocks;
+      const int kp0 = k_pos0(j);
+      const int valid_cols = p.src_len - jb * BKV;      // columns beyond the source's length are padding
+      const bool need_mask = (p.causal && kp0 + BKV - 1 > q_pos0) || valid_cols < BKV;
+      const uint32_t tS = tmem + st * 128 + lane_off;
+      ok = warp_wait(B_(FB_S + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN, 7);
+      if (!ok) break;
+      np::tc_fence_after();
+      // pass 1: row maximum
+      float mx = m;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32];
+        np::tmem_ld32(tS + c * 32, s);
+        np::tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float v = __uint_as_float(s[e]) * p.scale_log2;
+          if (need_mask) {
+            const int col = c * 32 + e;
+            if (col >= valid_cols || (p.causal && kp0 + col > q_pos)) v = -INFINITY;
+          }
+          mx = fmaxf(mx, v);
+        }
+      }
+      const float m_use = (mx == -INFINITY) ? 0.f : mx;
+      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
+      // pass 2: probabilities (bf16) -> operand of the P V product; row sum
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32];
+        np::tmem_ld32(tS + c * 32, s);
+        np::tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float v0 = __uint_as_float(s[e]) * p.scale_log2, v1 = __uint_as_float(s[e + 1]) * p.scale_log2;
+          if (need_mask) {
+            const int col = c * 32 + e;
+            if (col >= valid_cols || (p.causal && kp0 + col > q_pos)) v0 = -INFINITY;
+            if (col + 1 >= valid_cols || (p.causal && kp0 + col + 1 > q_pos)) v1 = -INFINITY;
+          }
+          const float p0 = exp2f(v0 - m_use), p1 = exp2f(v1 - m_use);
+          rs += p0 + p1;
+          pk[e >> 1] = np::pack_bf16(p0, p1);
+        }
+        if (P_TMEM) {
+          tmem_st16(tS + c * 16, pk);   // columns [16c, 16c+16) were read in this or an earlier chunk
+        } else {
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(sP_gen + swz_off(r, c * 4 + g)) =
+                make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+        }
+      }
+      m = mx;
+      l = l * alpha + rs;
+      if (P_TMEM) tmem_st_wait(); else fence_async_smem();
+      np::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) np::mbar_arrive(B_(FB_P));
+      // accumulate this block's P V
+      ok = warp_wait(B_(FB_O), (uint32_t)i & 1u, abort_flag, KID_ATTN, 8);
+      if (!ok) break;
+      np::tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t t[32];
+        np::tmem_ld32(tO + lane_off + c * 32, t);
+        np::tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[c * 32 + e] = fmaf(o[c * 32 + e], alpha, __uint_as_float(t[e]));
+      }
+      np::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) np::mbar_arrive(B_(FB_OE));
+    }
+    const int row = qb * BQ + r;
+    if (ok && row < p.Sq) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = p.O + (size_t)b * p.o_sb + (size_t)row * p.o_ss + (size_t)h * p.o_sh;
+#pragma unroll
+      for (int g = 0; g < HD / 8; ++g)
+        reinterpret_cast<uint4*>(dst)[g] =
+            make_uint4(np::pack_bf16(o[8 * g] * inv, o[8 * g + 1] * inv), np::pack_bf16(o[8 * g + 2] * inv, o[8 * g + 3] * inv),
+                       np::pack_bf16(o[8 * g + 4] * inv, o[8 * g + 5] * inv), np::pack_bf16(o[8 * g + 6] * inv, o[8 * g + 7] * inv));
+      if (p.lse)
+        p.lse[((size_t)b * p.Hq + h) * p.Sq + row] = l > 0.f ? (m * 0.6931471805599453f + logf(l)) : -INFINITY;
+    }
+  }
+  np::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    np::tc_fence_after();
+    np::tmem_dealloc(tmem, 512);
+  }
+}
+
+int make_tmap_4d(CUtensorMap* out, const void* base, long long B, long long S, long long H, long long sb, long long ss,
+                 long long sh) {
+  NpEncodeTiledFn enc = np_get_encode_tiled();
+  if (!enc) return -1;
+  cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)ss * 2, (cuuint64_t)sb * 2};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+bool bind_ctx() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess || cudaFree(nullptr) != cudaSuccess)
+      return false;
+    bound = true;
+  }
+  return true;
+}
+
+}  // namespace
+
+// Tensor layout of q / k / v / o: [B, S, H, 128] bf16 with element strides (sb, ss, sh); the last dim is
+// contiguous. k_ptrs / v_ptrs: one base pointer per KV source (n_src = 1 without context parallelism).
+struct NpAttnFwdArgs {
+  const void* q; long long q_sb, q_ss, q_sh;
+  const void* const* k_ptrs; const void* const* v_ptrs; long long k_sb, k_ss, k_sh;
+  void* o; long long o_sb, o_ss, o_sh;
+  float* lse;
+  int B, Sq, Hq, Hkv, causal, n_src, src_len, q_off;
+  float scale;
+  const int* q_blk_pos; const int* k_blk_pos;
+  int p_in_smem;   // 1: pass the probabilities through shared memory instead of tensor memory
+};
+
+NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
+  if (a->B <= 0 || a->Sq <= 0 || a->src_len <= 0) return 0;
+  if (a->n_src < 1 || a->n_src > MAX_SRC || a->Hq % a->Hkv) return 1;
+  if ((a->q_ss | a->q_sh | a->q_sb | a->k_ss | a->k_sh | a->k_sb) % 8 || (((uintptr_t)a->q) & 15)) return 1;
+  if (!bind_ctx()) return 2;
+  CUtensorMap tmQ;
+  TmapList tmK, tmV;
+  int rc = make_tmap_4d(&tmQ, a->q, a->B, a->Sq, a->Hq, a->q_sb, a->q_ss, a->q_sh);
+  if (rc) return 100 + rc;
+  for (int s = 0; s < a->n_src; ++s) {
+    rc = make_tmap_4d(&tmK.m[s], a->k_ptrs[s], a->B, a->src_len, a->Hkv, a->k_sb, a->k_ss, a->k_sh);
+    if (rc) return 200 + rc;
+    rc = make_tmap_4d(&tmV.m[s], a->v_ptrs[s], a->B, a->src_len, a->Hkv, a->k_sb, a->k_ss, a->k_sh);
+    if (rc) return 300 + rc;
+  }
+  for (int s = a->n_src; s < MAX_SRC; ++s) { tmK.m[s] = tmK.m[0]; tmV.m[s] = tmV.m[0]; }
+  FwdParams p{};
+  p.O = (__nv_bfloat16*)a->o; p.o_sb = a->o_sb; p.o_ss = a->o_ss; p.o_sh = a->o_sh; p.lse = a->lse;
+  p.B = a->B; p.Sq = a->Sq; p.Hq = a->Hq; p.Hkv = a->Hkv; p.causal = a->causal;
+  p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.n_src = a->n_src; p.src_len = a->src_len; p.src_blocks = (a->src_len + BKV - 1) / BKV;
+  p.q_blk_pos = a->q_blk_pos; p.k_blk_pos = a->k_blk_pos; p.q_off = a->q_off;
+  if (p.n_src * p.src_blocks > MAX_VIS) return 1;
+  constexpr int TAIL = 1024 + 8 * FB_COUNT + 16 + 2 * MAX_VIS + 64;
+  constexpr int SMEM_T = 5 * TILE_BYTES + TAIL, SMEM_S = 6 * TILE_BYTES + TAIL;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_T);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_S);
+    if (e != cudaSuccess) return 400 + (int)e;
+    attr_set = true;
+  }
+  dim3 grid((a->Sq + BQ - 1) / BQ, a->Hq, a->B);
+  if (a->p_in_smem)
+    attn_fwd_kernel<false><<<grid, 192, SMEM_S, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
+  else
+    attn_fwd_kernel<true><<<grid, 192, SMEM_T, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 500 + (int)e;
+}
+
+// ====================================================================================== backward
+// Two kernels, neither needs atomics and each only *reads* remote tensors, so with a sharded sequence
+// they pull the peers' tiles over NVLink exactly like the forward:
+//   dQ  kernel: one CTA per (Q block, head, batch) loops over the visible KV blocks of every source:
+//               S = Q K^T, dP = dO V^T, dS = P o (dP - delta), dQ += dS K  (dQ stays in TMEM).
+//   dKV kernel: one CTA per (local KV block, kv head, batch) loops over every query head of the group
+//               and every visible Q block of every source, on the transposed problem so that the
+//               operands land in TMEM lanes the way the next MMA wants them:
+//               S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q  (dV, dK stay in TMEM).
+// P and dS never leave tensor memory: they are written as bf16 over the S / dP columns they were
+// computed from and consumed as TMEM A operands.
+namespace {
+
+constexpr int KID_ATTN_DQ = 31, KID_ATTN_DKV = 32;
+constexpr int MAX_VIS_BWD = 4096;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct PtrList {
+  const float* p[MAX_SRC];
+};
+
+struct BwdParams {
+  int B, Sq, Hq, Hkv, causal;      // Sq: rows of the (local or per-source) Q tensor
+  float scale, scale_log2;
+  int n_src, src_blocks, src_len;  // sources of the *looped* operand (KV for dQ, Q/dO for dKV)
+  const int* q_blk_pos; const int* k_blk_pos; int q_off;
+  // dQ kernel
+  const float* lse; const float* delta;         // local [B, Hq, Sq]
+  __nv_bfloat16* dQ; long long dq_sb, dq_ss, dq_sh;
+  // dKV kernel
+  PtrList lse_src, delta_src;                   // per Q source [B, Hq, src_len]
+  int Sk;                                       // local KV rows
+  __nv_bfloat16* dK; __nv_bfloat16* dV; long long dk_sb, dk_ss, dk_sh;
+};
+
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long o_sb, long long o_ss, long long o_sh,
+                                  const __nv_bfloat16* __restrict__ d_o, long long d_sb, long long d_ss, long long d_sh,
+                                  float* __restrict__ delta, int B, int S, int H) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= B * S * H) return;
+  const int h = w % H, s = (w / H) % S, b = w / (H * S);
+  const uint2 a = *reinterpret_cast<const uint2*>(o + (size_t)b * o_sb + (size_t)s * o_ss + (size_t)h * o_sh + lane * 4);
+  const uint2 g = *reinterpret_cast<const uint2*>(d_o + (size_t)b * d_sb + (size_t)s * d_ss + (size_t)h * d_sh + lane * 4);
+  const float2 a0 = np::unpack_bf16(a.x), a1 = np::unpack_bf16(a.y), g0 = np::unpack_bf16(g.x), g1 = np::unpack_bf16(g.y);
+  float v = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+  v = np::warp_sum(v);
+  if (lane == 0) delta[((size_t)b * H + h) * S + s] = v;
+}
+
+enum { QB_QDO = 0, QB_K = 1, QB_V = 3, QB_KVE = 5, QB_S = 7, QB_DP = 9, QB_DS = 10, QB_FIN = 11, QB_COUNT = 12 };
+
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                   const __grid_constant__ TmapList tmK, const __grid_constant__ TmapList tmV, const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (np::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = base, sdO = base + TILE_BYTES, sK0 = sdO + TILE_BYTES, sV0 = sK0 + 2 * TILE_BYTES;
+  const uint32_t bar = sV0 + 2 * TILE_BYTES;
+  auto B_ = [&](int i) { return bar + 8u * i; };
+  uint8_t* tail = smem_raw + (bar - np::smem_u32(smem_raw)) + 8 * QB_COUNT;
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
+  volatile int* nvis_s = reinterpret_cast<volatile int*>(tail + 12);
+  volatile short* vis = reinterpret_cast<volatile short*>(tail + 16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.Sq + BQ - 1) / BQ;
+  const int qb = nqb - 1 - (int)blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / (p.Hq / p.Hkv);
+  const int q_pos0 = p.q_blk_pos ? p.q_blk_pos[qb] : qb * BQ + p.q_off;
+  const int total_blocks = p.n_src * p.src_blocks;
+  auto k_pos0 = [&](int j) { return p.k_blk_pos ? p.k_blk_pos[j] : (j % p.src_blocks) * BKV; };
+
+  if (threadIdx.x == 0) {
+    np::mbar_init(B_(QB_QDO), 1);
+    for (int s = 0; s < 2; ++s) {
+      np::mbar_init(B_(QB_K + s), 1); np::mbar_init(B_(QB_V + s), 1); np::mbar_init(B_(QB_KVE + s), 1);
+      np::mbar_init(B_(QB_S + s), 1);
+    }
+    np::mbar_init(B_(QB_DP), 1); np::mbar_init(B_(QB_DS), 4); np::mbar_init(B_(QB_FIN), 1);
+    *abort_flag = 0;
+    np::mbar_fence_init();
+    int n = 0;
+    for (int j = 0; j < total_blocks && n < MAX_VIS; ++j)
+      if (!p.causal || k_pos0(j) <= q_pos0 + BQ - 1) vis[n++] = (short)j;
+    *nvis_s = n;
+  }
+  if (warp == 1) {
+    np::tmem_alloc(np::smem_u32((const void*)tmem_ptr_smem), 512);
+    np::tmem_relinquish();
+  }
+  np::tc_fence_before();
+  __syncthreads();
+  np::tc_fence_after();
+  const uint32_t tmem = *tmem_ptr_smem;
+  const uint32_t tdP = tmem + 256, tdQ = tmem + 384;   // S buffers at columns 0 and 128
+  const int nvis = *nvis_s;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      np::mbar_expect_tx(B_(QB_QDO), 2 * TILE_BYTES);
+      load_tile(sQ, &tmQ, B_(QB_QDO), h, qb * BQ, b);
+      load_tile(sdO, &tmdO, B_(QB_QDO), h, qb * BQ, b);
+      for (int i = 0; i < nvis && !*abort_flag; ++i) {
+        const int st = i & 1;
+        if (!np::mbar_wait(B_(QB_KVE + st), ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag, KID_ATTN_DQ, 1)) break;
+        const int j = vis[i];
+        const int src = j / p.src_blocks, jb = j - src * p.src_blocks;
+        np::mbar_expect_tx(B_(QB_K + st), TILE_BYTES);
+        load_tile(sK0 + st * TILE_BYTES, &tmK.m[src], B_(QB_K + st), hkv, jb * BKV, b);
+        np::mbar_expect_tx(B_(QB_V + st), TILE_BYTES);
+        load_tile(sV0 + st * TILE_BYTES, &tmV.m[src], B_(QB_V + st), hkv, jb * BKV, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_kk = np::make_idesc(128, 128, 1, 1, 0, 0);   // both operands K-major (over hd)
+      const uint32_t idesc_mn = np::make_idesc(128, 128, 1, 1, 0, 1);   // A from TMEM, B MN-major
+      bool ok = np::mbar_wait(B_(QB_QDO), 0, abort_flag, KID_ATTN_DQ, 2);
+      auto issue_s = [&](int i) {
+        const int st = i & 1;
+        if (!np::mbar_wait(B_(QB_K + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN_DQ, 3)) return false;
+        np::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          np::tc_mma_f16(tmem + st * 128, desc_kmajor(sQ, kk), desc_kmajor(sK0 + st * TILE_BYTES, kk), idesc_kk, kk > 0);
+        np::tc_commit(B_(QB_S + st));
+        return true;
+      };
+      auto issue_dp = [&](int i) {
+        const int st = i & 1;
+        if (!np::mbar_wait(B_(QB_V + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN_DQ, 4)) return false;
+        np::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          np::tc_mma_f16(tdP, desc_kmajor(sdO, kk), desc_kmajor(sV0 + st * TILE_BYTES, kk), idesc_kk, kk > 0);
+        np::tc_commit(B_(QB_DP));
+        return true;
+      };
+      if (ok && nvis > 0) ok = issue_s(0) && issue_dp(0);
+      for (int i = 0; i < nvis && ok && !*abort_flag; ++i) {
+        const int st = i & 1;
+        if (i + 1 < nvis) ok = issue_s(i + 1);   // its buffer was read for block i-1 before dS of block i-1 arrived
+        ok = ok && np::mbar_wait(B_(QB_DS), (uint32_t)i & 1u, abort_flag, KID_ATTN_DQ, 5);
+        if (!ok) break;
+        np::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tc_mma_f16_ts(tdQ, tdP + kk * 8, desc_mnmajor(sK0 + st * TILE_BYTES, kk), idesc_mn, (i > 0) || (kk > 0));
+        np::tc_commit(B_(QB_KVE + st));
+        if (i + 1 < nvis) ok = issue_dp(i + 1);  // overwrites dS after the dQ product above has consumed it
+      }
+      np::tc_commit(B_(QB_FIN));
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const int row = qb * BQ + r;
+    const int q_pos = q_pos0 + r;
+    float lse2 = INFINITY, dlt = 0.f;
+    if (row < p.Sq) {
+      const size_t idx = ((size_t)b * p.Hq + h) * p.Sq + row;
+      const float l = p.lse[idx];
+      lse2 = (l == -INFINITY) ? INFINITY : l * LOG2E;
+      dlt = p.delta[idx];
+    }
+    bool ok = true;
+    for (int i = 0; i < nvis && ok && !*abort_flag; ++i) {
+      const int st = i & 1;
+      const int j = vis[i];
+      const int jb = j % p.src_blocks;
+      const int kp0 = k_pos0(j);
+      const int valid_cols = p.src_len - jb * BKV;
+      const bool need_mask = (p.causal && kp0 + BKV - 1 > q_pos0) || valid_cols < BKV;
+      const uint32_t tS = tmem + st * 128 + lane_off;
+      ok = warp_wait(B_(QB_S + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN_DQ, 7);
+      if (!ok) break;
+      np::tc_fence_after();
+      float pr[BKV];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32];
+        np::tmem_ld32(tS + c * 32, s);
+        np::tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float v = exp2f(__uint_as_float(s[e]) * p.scale_log2 - lse2);
+          if (need_mask) {
+            const int col = c * 32 + e;
+            if (col >= valid_cols || (p.causal && kp0 + col > q_pos)) v = 0.f;
+          }
+          pr[c * 32 + e] = v;
+        }
+      }
+      ok = warp_wait(B_(QB_DP), (uint32_t)i & 1u, abort_flag, KID_ATTN_DQ, 8);
+      if (!ok) break;
+      np::tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32];
+        np::tmem_ld32(tdP + lane_off + c * 32, s);
+        np::tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2)
+          pk[e >> 1] = np::pack_bf16(pr[c * 32 + e] * (__uint_as_float(s[e]) - dlt),
+                                     pr[c * 32 + e + 1] * (__uint_as_float(s[e + 1]) - dlt));
+        tmem_st16(tdP + lane_off + c * 16, pk);
+      }
+      tmem_st_wait();
+      np::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) np::mbar_arrive(B_(QB_DS));
+    }
+    ok = __all_sync(0xffffffffu, ok) && warp_wait(B_(QB_FIN), 0, abort_flag, KID_ATTN_DQ, 9);
+    if (ok) {   // warp-uniform: the tensor-memory loads below are executed by whole warps, only the stores are guarded
+      np::tc_fence_after();
+      __nv_bfloat16* dst = p.dQ + (size_t)b * p.dq_sb + (size_t)row * p.dq_ss + (size_t)h * p.dq_sh;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t t[32];
+        if (nvis > 0) {
+          np::tmem_ld32(tdQ + lane_off + c * 32, t);
+          np::tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) t[e] = 0u;
+        }
+        if (row < p.Sq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(t[8 * g + e]) * p.scale;
+            reinterpret_cast<uint4*>(dst)[c * 4 + g] = make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]),
+                                                                  np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
+          }
+        }
+      }
+    }
+  }
+  np::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    np::tc_fence_after();
+    np::tmem_dealloc(tmem, 512);
+  }
+}
+
+enum { KB_KV = 0, KB_Q = 1, KB_DO = 3, KB_QE = 5, KB_DOE = 7, KB_ST = 9, KB_DPT = 10, KB_P = 11, KB_DS = 12, KB_FIN = 13,
+       KB_COUNT = 14 };
+
+// iteration descriptor: source << 24 | head-in-group << 16 | q block
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                    const __grid_constant__ TmapList tmQ, const __grid_constant__ TmapList tmdO, const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (np::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sK = base, sV = base + TILE_BYTES, sQ0 = sV + TILE_BYTES, sdO0 = sQ0 + 2 * TILE_BYTES;
+  const uint32_t bar = sdO0 + 2 * TILE_BYTES;
+  auto B_ = [&](int i) { return bar + 8u * i; };
+  uint8_t* tail = smem_raw + (bar - np::smem_u32(smem_raw)) + 8 * KB_COUNT;
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
+  volatile int* nvis_s = reinterpret_cast<volatile int*>(tail + 12);
+  float* s_lse = reinterpret_cast<float*>(tail + 16);          // [2][128]
+  float* s_dlt = s_lse + 256;                                   // [2][128]
+  volatile int* vis = reinterpret_cast<volatile int*>(s_dlt + 256);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jb = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int n_rep = p.Hq / p.Hkv;
+  const int k_pos0 = p.k_blk_pos ? p.k_blk_pos[jb] : jb * BKV;
+  auto q_pos0_of = [&](int src, int i) {
+    return p.q_blk_pos ? p.q_blk_pos[src * p.src_blocks + i] : i * BQ + p.q_off;
+  };
+
+  if (threadIdx.x == 0) {
+    np::mbar_init(B_(KB_KV), 1);
+    for (int s = 0; s < 2; ++s) {
+      np::mbar_init(B_(KB_Q + s), 1); np::mbar_init(B_(KB_DO + s), 1);
+      np::mbar_init(B_(KB_QE + s), 1); np::mbar_init(B_(KB_DOE + s), 1);
+    }
+    np::mbar_init(B_(KB_ST), 1); np::mbar_init(B_(KB_DPT), 1);
+    np::mbar_init(B_(KB_P), 4); np::mbar_init(B_(KB_DS), 4); np::mbar_init(B_(KB_FIN), 1);
+    *abort_flag = 0;
+    np::mbar_fence_init();
+    int n = 0;
+    for (int src = 0; src < p.n_src; ++src)
+      for (int hh = 0; hh < n_rep; ++hh)
+        for (int i = 0; i < p.src_blocks && n < MAX_VIS_BWD; ++i)
+          if (!p.causal || k_pos0 <= q_pos0_of(src, i) + BQ - 1) vis[n++] = (src << 24) | (hh << 16) | i;
+    *nvis_s = n;
+  }
+  if (warp == 1) {
+    np::tmem_alloc(np::smem_u32((const void*)tmem_ptr_smem), 512);
+    np::tmem_relinquish();
+  }
+  np::tc_fence_before();
+  __syncthreads();
+  np::tc_fence_after();
+  const uint32_t tmem = *tmem_ptr_smem;
+  const uint32_t tSt = tmem, tdPt = tmem + 128, tdV = tmem + 256, tdK = tmem + 384;
+  const int nvis = *nvis_s;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      np::mbar_expect_tx(B_(KB_KV), 2 * TILE_BYTES);
+      load_tile(sK, &tmK, B_(KB_KV), hkv, jb * BKV, b);
+      load_tile(sV, &tmV, B_(KB_KV), hkv, jb * BKV, b);
+      for (int i = 0; i < nvis && !*abort_flag; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = ((uint32_t)(i >> 1) & 1u) ^ 1u;
+        const int d = vis[i];
+        const int src = d >> 24, h = hkv * n_rep + ((d >> 16) & 0xff), qi = d & 0xffff;
+        if (!np::mbar_wait(B_(KB_QE + st), ph, abort_flag, KID_ATTN_DKV, 1)) break;
+        np::mbar_expect_tx(B_(KB_Q + st), TILE_BYTES);
+        load_tile(sQ0 + st * TILE_BYTES, &tmQ.m[src], B_(KB_Q + st), h, qi * BQ, b);
+        if (!np::mbar_wait(B_(KB_DOE + st), ph, abort_flag, KID_ATTN_DKV, 2)) break;
+        np::mbar_expect_tx(B_(KB_DO + st), TILE_BYTES);
+        load_tile(sdO0 + st * TILE_BYTES, &tmdO.m[src], B_(KB_DO + st), h, qi * BQ, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_kk = np::make_idesc(128, 128, 1, 1, 0, 0);
+      const uint32_t idesc_mn = np::make_idesc(128, 128, 1, 1, 0, 1);
+      bool ok = np::mbar_wait(B_(KB_KV), 0, abort_flag, KID_ATTN_DKV, 3);
+      auto issue_st = [&](int i) {
+        const int st = i & 1;
+        if (!np::mbar_wait(B_(KB_Q + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN_DKV, 4)) return false;
+        np::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          np::tc_mma_f16(tSt, desc_kmajor(sK, kk), desc_kmajor(sQ0 + st * TILE_BYTES, kk), idesc_kk, kk > 0);
+        np::tc_commit(B_(KB_ST));
+        return true;
+      };
+      auto issue_dpt = [&](int i) {
+        const int st = i & 1;
+        if (!np::mbar_wait(B_(KB_DO + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN_DKV, 5)) return false;
+        np::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          np::tc_mma_f16(tdPt, desc_kmajor(sV, kk), desc_kmajor(sdO0 + st * TILE_BYTES, kk), idesc_kk, kk > 0);
+        np::tc_commit(B_(KB_DPT));
+        return true;
+      };
+      if (ok && nvis > 0) ok = issue_st(0) && issue_dpt(0);
+      for (int i = 0; i < nvis && ok && !*abort_flag; ++i) {
+        const int st = i & 1;
+        ok = np::mbar_wait(B_(KB_P), (uint32_t)i & 1u, abort_flag, KID_ATTN_DKV, 6);
+        if (!ok) break;
+        np::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)   // dV += P^T dO
+          tc_mma_f16_ts(tdV, tSt + kk * 8, desc_mnmajor(sdO0 + st * TILE_BYTES, kk), idesc_mn, (i > 0) || (kk > 0));
+        np::tc_commit(B_(KB_DOE + st));
+        if (i + 1 < nvis) ok = issue_st(i + 1);     // overwrites P^T after the product above consumed it
+        ok = ok && np::mbar_wait(B_(KB_DS), (uint32_t)i & 1u, abort_flag, KID_ATTN_DKV, 7);
+        if (!ok) break;
+        np::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)   // dK += dS^T Q
+          tc_mma_f16_ts(tdK, tdPt + kk * 8, desc_mnmajor(sQ0 + st * TILE_BYTES, kk), idesc_mn, (i > 0) || (kk > 0));
+        np::tc_commit(B_(KB_QE + st));
+        if (i + 1 < nvis) ok = issue_dpt(i + 1);    // overwrites dS^T after the product above consumed it
+      }
+      np::tc_commit(B_(KB_FIN));
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;               // KV row of this thread
+    const int t128 = threadIdx.x - 64;               // 0..127 among the softmax threads
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const int k_pos = k_pos0 + r;
+    bool ok = true;
+    for (int i = 0; i < nvis; ++i) {   // every thread runs every iteration: the named barrier below needs all 128
+      const int st = i & 1;
+      const int d = vis[i];
+      const int src = d >> 24, h = hkv * n_rep + ((d >> 16) & 0xff), qi = d & 0xffff;
+      const int q_pos0 = q_pos0_of(src, qi);
+      {  // stage this Q block's log-sum-exp and delta (one column each per thread)
+        const int qrow = qi * BQ + t128;
+        float l2 = INFINITY, dl = 0.f;
+        if (qrow < p.src_len) {
+          const size_t idx = ((size_t)b * p.Hq + h) * p.src_len + qrow;
+          const float l = p.lse_src.p[src][idx];
+          l2 = (l == -INFINITY) ? INFINITY : l * LOG2E;
+          dl = p.delta_src.p[src][idx];
+        }
+        s_lse[st * 128 + t128] = l2;
+        s_dlt[st * 128 + t128] = dl;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      if (!ok || *abort_flag) { ok = false; continue; }   // after a failed wait only the barrier above is kept up
+      const bool need_mask = p.causal && k_pos0 + BKV - 1 > q_pos0;
+      ok = warp_wait(B_(KB_ST), (uint32_t)i & 1u, abort_flag, KID_ATTN_DKV, 8);
+      if (!ok) continue;
+      np::tc_fence_after();
+      float pr[BQ];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32];
+        np::tmem_ld32(tSt + lane_off + c * 32, s);
+        np::tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(&s_lse[st * 128 + c * 32 + e]);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float v = exp2f(__uint_as_float(s[e + u]) * p.scale_log2 - ls[u]);
+            if (need_mask && k_pos > q_pos0 + c * 32 + e + u) v = 0.f;
+            pr[c * 32 + e + u] = v;
+          }
+          pk[e >> 1] = np::pack_bf16(pr[c * 32 + e], pr[c * 32 + e + 1]);
+          pk[(e >> 1) + 1] = np::pack_bf16(pr[c * 32 + e + 2], pr[c * 32 + e + 3]);
+        }
+        tmem_st16(tSt + lane_off + c * 16, pk);
+      }
+      tmem_st_wait();
+      np::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) np::mbar_arrive(B_(KB_P));
+      ok = warp_wait(B_(KB_DPT), (uint32_t)i & 1u, abort_flag, KID_ATTN_DKV, 9);
+      if (!ok) continue;
+      np::tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32];
+        np::tmem_ld32(tdPt + lane_off + c * 32, s);
+        np::tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          const float4 d4 = *reinterpret_cast<const float4*>(&s_dlt[st * 128 + c * 32 + e]);
+          pk[e >> 1] = np::pack_bf16(pr[c * 32 + e] * (__uint_as_float(s[e]) - d4.x),
+                                     pr[c * 32 + e + 1] * (__uint_as_float(s[e + 1]) - d4.y));
+          pk[(e >> 1) + 1] = np::pack_bf16(pr[c * 32 + e + 2] * (__uint_as_float(s[e + 2]) - d4.z),
+                                           pr[c * 32 + e + 3] * (__uint_as_float(s[e + 3]) - d4.w));
+        }
+        tmem_st16(tdPt + lane_off + c * 16, pk);
+      }
+      tmem_st_wait();
+      np::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) np::mbar_arrive(B_(KB_DS));
+    }
+    ok = __all_sync(0xffffffffu, ok && !*abort_flag) && warp_wait(B_(KB_FIN), 0, abort_flag, KID_ATTN_DKV, 10);
+    const int row = jb * BKV + r;
+    if (ok) {   // warp-uniform; only the stores are guarded by the row bound
+      np::tc_fence_after();
+      const size_t off = (size_t)b * p.dk_sb + (size_t)row * p.dk_ss + (size_t)hkv * p.dk_sh;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dst = (which ? p.dK : p.dV) + off;
+        const float mul = which ? p.scale : 1.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t t[32];
+          if (nvis > 0) {
+            np::tmem_ld32((which ? tdK : tdV) + lane_off + c * 32, t);
+            np::tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) t[e] = 0u;
+          }
+          if (row < p.Sk) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(t[8 * g + e]) * mul;
+              reinterpret_cast<uint4*>(dst)[c * 4 + g] = make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]),
+                                                                    np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
+            }
+          }
+        }
+      }
+    }
+  }
+  np::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    np::tc_fence_after();
+    np::tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace
+
+// Backward of np_attn_fwd. q / o / d_o / dq are local [B, Sq, Hq, 128]; k / v / dk / dv local
+// [B, Sk, Hkv, 128]. kv sources (for dQ) and q / d_o / lse / delta sources (for dK, dV) are lists so a
+// context-parallel rank reads its peers' tensors in place; without context parallelism both lists have
+// one entry, the local tensors. delta = rowsum(dO o O) is computed here into `delta` ([B, Hq, Sq] fp32).
+// phase: 1 = delta only, 2 = dQ + dKV only (delta already published), 3 = all.
+struct NpAttnBwdArgs {
+  const void* q; long long q_sb, q_ss, q_sh;
+  const void* k; const void* v; long long k_sb, k_ss, k_sh;
+  const void* o; long long o_sb, o_ss, o_sh;
+  const void* d_o; long long do_sb, do_ss, do_sh;
+  const float* lse; float* delta;
+  void* dq; long long dq_sb, dq_ss, dq_sh;
+  void* dk; void* dv; long long dk_sb, dk_ss, dk_sh;
+  const void* const* k_src; const void* const* v_src;           // n_src KV sources (layout of k)
+  const void* const* q_src; const void* const* do_src;          // n_src Q / dO sources (layouts of q / d_o)
+  const float* const* lse_src; const float* const* delta_src;   // n_src [B, Hq, Sq] sources
+  int B, Sq, Sk, Hq, Hkv, causal, n_src, q_off, phase;
+  float scale;
+  const int* q_blk_pos_local; const int* k_blk_pos_all;         // for dQ: local Q blocks vs all KV blocks
+  const int* k_blk_pos_local; const int* q_blk_pos_all;         // for dKV: local KV blocks vs all Q blocks
+};
+
+NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (a->B <= 0 || a->Sq <= 0 || a->Sk <= 0) return 0;
+  if (a->n_src < 1 || a->n_src > MAX_SRC || a->Hq % a->Hkv) return 1;
+  if (!bind_ctx()) return 2;
+  if (a->phase & 1) {
+    const long long warps = (long long)a->B * a->Sq * a->Hq;
+    attn_delta_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>(
+        (const __nv_bfloat16*)a->o, a->o_sb, a->o_ss, a->o_sh, (const __nv_bfloat16*)a->d_o, a->do_sb, a->do_ss, a->do_sh,
+        a->delta, a->B, a->Sq, a->Hq);
+  }
+  if (!(a->phase & 2)) return cudaGetLastError() == cudaSuccess ? 0 : 500;
+  const int qblocks = (a->Sq + BQ - 1) / BQ, kblocks = (a->Sk + BKV - 1) / BKV;
+  if (a->n_src * kblocks > MAX_VIS || a->n_src * (a->Hq / a->Hkv) * qblocks > MAX_VIS_BWD) return 1;
+  CUtensorMap tmQ, tmdO, tmK, tmV;
+  TmapList lK, lV, lQ, ldO;
+  int rc = make_tmap_4d(&tmQ, a->q, a->B, a->Sq, a->Hq, a->q_sb, a->q_ss, a->q_sh);
+  rc = rc ? rc : make_tmap_4d(&tmdO, a->d_o, a->B, a->Sq, a->Hq, a->do_sb, a->do_ss, a->do_sh);
+  rc = rc ? rc : make_tmap_4d(&tmK, a->k, a->B, a->Sk, a->Hkv, a->k_sb, a->k_ss, a->k_sh);
+  rc = rc ? rc : make_tmap_4d(&tmV, a->v, a->B, a->Sk, a->Hkv, a->k_sb, a->k_ss, a->k_sh);
+  for (int s = 0; s < a->n_src && !rc; ++s) {
+    rc = make_tmap_4d(&lK.m[s], a->k_src[s], a->B, a->Sk, a->Hkv, a->k_sb, a->k_ss, a->k_sh);
+    rc = rc ? rc : make_tmap_4d(&lV.m[s], a->v_src[s], a->B, a->Sk, a->Hkv, a->k_sb, a->k_ss, a->k_sh);
+    rc = rc ? rc : make_tmap_4d(&lQ.m[s], a->q_src[s], a->B, a->Sq, a->Hq, a->q_sb, a->q_ss, a->q_sh);
+    rc = rc ? rc : make_tmap_4d(&ldO.m[s], a->do_src[s], a->B, a->Sq, a->Hq, a->do_sb, a->do_ss, a->do_sh);
+  }
+  if (rc) return 100 + rc;
+  for (int s = a->n_src; s < MAX_SRC; ++s) { lK.m[s] = lK.m[0]; lV.m[s] = lV.m[0]; lQ.m[s] = lQ.m[0]; ldO.m[s] = ldO.m[0]; }
+  BwdParams p{};
+  p.B = a->B; p.Sq = a->Sq; p.Hq = a->Hq; p.Hkv = a->Hkv; p.causal = a->causal;
+  p.scale = a->scale; p.scale_log2 = a->scale * LOG2E;
+  p.n_src = a->n_src; p.q_off = a->q_off;
+  p.lse = a->lse; p.delta = a->delta;
+  p.dQ = (__nv_bfloat16*)a->dq; p.dq_sb = a->dq_sb; p.dq_ss = a->dq_ss; p.dq_sh = a->dq_sh;
+  p.Sk = a->Sk; p.dK = (__nv_bfloat16*)a->dk; p.dV = (__nv_bfloat16*)a->dv;
+  p.dk_sb = a->dk_sb; p.dk_ss = a->dk_ss; p.dk_sh = a->dk_sh;
+  for (int s = 0; s < MAX_SRC; ++s) {
+    p.lse_src.p[s] = a->lse_src[s < a->n_src ? s : 0];
+    p.delta_src.p[s] = a->delta_src[s < a->n_src ? s : 0];
+  }
+  constexpr int SMEM_DQ = 6 * TILE_BYTES + 1024 + 8 * QB_COUNT + 16 + 2 * MAX_VIS + 64;
+  constexpr int SMEM_DKV = 6 * TILE_BYTES + 1024 + 8 * KB_COUNT + 16 + 2048 + 4 * MAX_VIS_BWD + 64;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DQ);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DKV);
+    if (e != cudaSuccess) return 400 + (int)e;
+    attr_set = true;
+  }
+  // dQ: local Q blocks against every source's KV blocks
+  BwdParams pq = p;
+  pq.src_blocks = kblocks; pq.src_len = a->Sk;
+  pq.q_blk_pos = a->q_blk_pos_local; pq.k_blk_pos = a->k_blk_pos_all;
+  attn_bwd_dq_kernel<<<dim3(qblocks, a->Hq, a->B), 192, SMEM_DQ, stream>>>(tmQ, tmdO, lK, lV, pq);
+  // dK, dV: local KV blocks against every source's Q blocks
+  BwdParams pk = p;
+  pk.src_blocks = qblocks; pk.src_len = a->Sq;
+  pk.q_blk_pos = a->q_blk_pos_all; pk.k_blk_pos = a->k_blk_pos_local;
+  attn_bwd_dkv_kernel<<<dim3(kblocks, a->Hkv, a->B), 192, SMEM_DKV, stream>>>(tmK, tmV, lQ, ldO, pk);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 500 + (int)e;
+}

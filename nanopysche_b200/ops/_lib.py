@@ -70,6 +70,43 @@ class CombineArgs(C.Structure):
     ]
 
 
+class AttnFwdArgs(C.Structure):
+    """Mirror of ``NpAttnFwdArgs`` in csrc/attn_sm100.cu."""
+
+    _fields_ = [
+        ("q", c_void_p), ("q_sb", c_ll), ("q_ss", c_ll), ("q_sh", c_ll),
+        ("k_ptrs", c_void_p), ("v_ptrs", c_void_p), ("k_sb", c_ll), ("k_ss", c_ll), ("k_sh", c_ll),
+        ("o", c_void_p), ("o_sb", c_ll), ("o_ss", c_ll), ("o_sh", c_ll),
+        ("lse", c_void_p),
+        ("B", c_int), ("Sq", c_int), ("Hq", c_int), ("Hkv", c_int), ("causal", c_int), ("n_src", c_int),
+        ("src_len", c_int), ("q_off", c_int),
+        ("scale", c_float),
+        ("q_blk_pos", c_void_p), ("k_blk_pos", c_void_p),
+        ("p_in_smem", c_int),
+    ]
+
+
+class AttnBwdArgs(C.Structure):
+    """Mirror of ``NpAttnBwdArgs`` in csrc/attn_sm100.cu."""
+
+    _fields_ = [
+        ("q", c_void_p), ("q_sb", c_ll), ("q_ss", c_ll), ("q_sh", c_ll),
+        ("k", c_void_p), ("v", c_void_p), ("k_sb", c_ll), ("k_ss", c_ll), ("k_sh", c_ll),
+        ("o", c_void_p), ("o_sb", c_ll), ("o_ss", c_ll), ("o_sh", c_ll),
+        ("d_o", c_void_p), ("do_sb", c_ll), ("do_ss", c_ll), ("do_sh", c_ll),
+        ("lse", c_void_p), ("delta", c_void_p),
+        ("dq", c_void_p), ("dq_sb", c_ll), ("dq_ss", c_ll), ("dq_sh", c_ll),
+        ("dk", c_void_p), ("dv", c_void_p), ("dk_sb", c_ll), ("dk_ss", c_ll), ("dk_sh", c_ll),
+        ("k_src", c_void_p), ("v_src", c_void_p), ("q_src", c_void_p), ("do_src", c_void_p),
+        ("lse_src", c_void_p), ("delta_src", c_void_p),
+        ("B", c_int), ("Sq", c_int), ("Sk", c_int), ("Hq", c_int), ("Hkv", c_int), ("causal", c_int),
+        ("n_src", c_int), ("q_off", c_int), ("phase", c_int),
+        ("scale", c_float),
+        ("q_blk_pos_local", c_void_p), ("k_blk_pos_all", c_void_p),
+        ("k_blk_pos_local", c_void_p), ("q_blk_pos_all", c_void_p),
+    ]
+
+
 class Fp8GemmArgs(C.Structure):
     """Mirror of ``NpFp8GemmArgs`` in csrc/gemm_fp8_sm100.cu."""
 
@@ -120,6 +157,8 @@ def lib():
     _LIB.np_ep_dispatch.argtypes = [C.POINTER(DispatchArgs), c_void_p]
     _LIB.np_ep_combine.argtypes = [C.POINTER(CombineArgs), c_void_p]
     _LIB.np_gemm_fp8_block.argtypes = [C.POINTER(Fp8GemmArgs), c_void_p]
+    _LIB.np_attn_fwd.argtypes = [C.POINTER(AttnFwdArgs), c_void_p]
+    _LIB.np_attn_bwd.argtypes = [C.POINTER(AttnBwdArgs), c_void_p]
     _LIB.np_status_read.argtypes = [C.POINTER(c_int)]
     return _LIB
 

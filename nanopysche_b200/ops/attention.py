@@ -16,6 +16,8 @@ import math
 import torch
 import torch.nn.functional as F
 
+from . import _lib
+
 
 def attention_ref(q, k, v, causal=True, q_pos=None, k_pos=None, scale=None):
     """fp32 reference with explicit positions; returns (out [B,S,H,hd], lse [B,H,S]).
@@ -52,6 +54,127 @@ def merge_attention(o1, lse1, o2, lse2):
     w2 = w2.permute(0, 2, 1).unsqueeze(-1)
     o = o1.float() * w1 + o2.float() * w2
     return o.to(o1.dtype), lse
+
+
+def _strides3(t: torch.Tensor):
+    assert t.stride(3) == 1, "head_dim must be contiguous"
+    return t.stride(0), t.stride(1), t.stride(2)
+
+
+def flash_supported(q: torch.Tensor, k: torch.Tensor) -> bool:
+    """The tcgen05 kernels cover bf16, head_dim 128, 16-byte aligned strided ``[B, S, H, 128]`` views."""
+    return (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and q.shape[-1] == 128
+            and k.shape[-1] == 128 and q.stride(-1) == 1 and k.stride(-1) == 1 and _lib.available()
+            and all(s % 8 == 0 for s in q.stride()[:3]) and all(s % 8 == 0 for s in k.stride()[:3]))
+
+
+def flash_fwd(q, k_list, v_list, *, causal=True, scale=None, q_off=0, q_blk_pos=None, k_blk_pos=None,
+              p_in_smem=False):
+    """Forward flash attention on the tcgen05 kernel. ``k_list`` / ``v_list`` are lists of equally shaped
+    ``[B, Sk, Hkv, 128]`` KV sources (one entry without context parallelism; one per rank's shard - any of
+    them may live in a peer's memory - with it). Returns ``(out [B,Sq,Hq,128] bf16, lse [B,Hq,Sq] fp32)``."""
+    import ctypes as C
+
+    if not isinstance(k_list, (list, tuple)):
+        k_list, v_list = [k_list], [v_list]
+    B, Sq, Hq, hd = q.shape
+    Sk, Hkv = k_list[0].shape[1], k_list[0].shape[2]
+    n = len(k_list)
+    o = torch.empty((B, Sq, Hq, hd), device=q.device, dtype=torch.bfloat16)
+    lse = torch.empty((B, Hq, Sq), device=q.device, dtype=torch.float32)
+    a = _lib.AttnFwdArgs()
+    a.q = q.data_ptr()
+    a.q_sb, a.q_ss, a.q_sh = _strides3(q)
+    kp = (C.c_void_p * n)(*[t.data_ptr() if isinstance(t, torch.Tensor) else int(t) for t in k_list])
+    vp = (C.c_void_p * n)(*[t.data_ptr() if isinstance(t, torch.Tensor) else int(t) for t in v_list])
+    a.k_ptrs, a.v_ptrs = C.cast(kp, C.c_void_p), C.cast(vp, C.c_void_p)
+    a.k_sb, a.k_ss, a.k_sh = _strides3(k_list[0])
+    a.o = o.data_ptr()
+    a.o_sb, a.o_ss, a.o_sh = _strides3(o)
+    a.lse = lse.data_ptr()
+    a.B, a.Sq, a.Hq, a.Hkv, a.causal, a.n_src, a.src_len, a.q_off = B, Sq, Hq, Hkv, int(causal), n, Sk, q_off
+    a.scale = scale or 1.0 / math.sqrt(hd)
+    a.q_blk_pos = q_blk_pos.data_ptr() if q_blk_pos is not None else None
+    a.k_blk_pos = k_blk_pos.data_ptr() if k_blk_pos is not None else None
+    a.p_in_smem = int(p_in_smem)
+    _lib.check(_lib.lib().np_attn_fwd(C.byref(a), C.c_void_p(_lib.stream())), "attn_fwd")
+    return o, lse
+
+
+def _ptr_array(items):
+    import ctypes as C
+
+    arr = (C.c_void_p * len(items))(*[t.data_ptr() if isinstance(t, torch.Tensor) else int(t) for t in items])
+    return arr, C.cast(arr, C.c_void_p)
+
+
+def flash_bwd(q, k, v, o, d_o, lse, *, causal=True, scale=None, q_off=0, delta=None, sources=None, phase=3,
+              q_blk_pos_local=None, k_blk_pos_all=None, k_blk_pos_local=None, q_blk_pos_all=None):
+    """Backward of ``flash_fwd``: returns ``(dq, dk, dv)`` in bf16 with the shapes of q / k / v.
+
+    ``sources`` (context parallelism) is a dict of equally long lists ``k, v, q, d_o, lse, delta`` holding one
+    tensor (or raw device pointer into a peer's memory) per rank of the group; the local tensors are used
+    when it is ``None``. ``phase=1`` only computes ``delta`` (so that it can be published to the peers
+    before ``phase=2`` runs the dQ and dK/dV kernels)."""
+    import ctypes as C
+
+    B, Sq, Hq, hd = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    if delta is None:
+        delta = torch.empty((B, Hq, Sq), device=q.device, dtype=torch.float32)
+    if d_o.stride(3) != 1 or any(s % 8 for s in d_o.stride()[:3]):
+        d_o = d_o.contiguous()
+    dq = torch.empty((B, Sq, Hq, hd), device=q.device, dtype=torch.bfloat16) if phase & 2 else None
+    dk = torch.empty((B, Sk, Hkv, hd), device=q.device, dtype=torch.bfloat16) if phase & 2 else None
+    dv = torch.empty_like(dk) if phase & 2 else None
+    a = _lib.AttnBwdArgs()
+    a.q, a.k, a.v, a.o, a.d_o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr()
+    a.q_sb, a.q_ss, a.q_sh = _strides3(q)
+    a.k_sb, a.k_ss, a.k_sh = _strides3(k)
+    assert _strides3(v) == _strides3(k), "k and v must share their strides"
+    a.o_sb, a.o_ss, a.o_sh = _strides3(o)
+    a.do_sb, a.do_ss, a.do_sh = _strides3(d_o)
+    a.lse, a.delta = lse.data_ptr(), delta.data_ptr()
+    if phase & 2:
+        a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+        a.dq_sb, a.dq_ss, a.dq_sh = _strides3(dq)
+        a.dk_sb, a.dk_ss, a.dk_sh = _strides3(dk)
+    src = sources or dict(k=[k], v=[v], q=[q], d_o=[d_o], lse=[lse], delta=[delta])
+    keep = [_ptr_array(src[n]) for n in ("k", "v", "q", "d_o", "lse", "delta")]
+    a.k_src, a.v_src, a.q_src, a.do_src, a.lse_src, a.delta_src = [x[1] for x in keep]
+    a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.causal, a.n_src, a.q_off, a.phase = \
+        B, Sq, Sk, Hq, Hkv, int(causal), len(src["k"]), q_off, phase
+    a.scale = scale or 1.0 / math.sqrt(hd)
+    for name, t in (("q_blk_pos_local", q_blk_pos_local), ("k_blk_pos_all", k_blk_pos_all),
+                    ("k_blk_pos_local", k_blk_pos_local), ("q_blk_pos_all", q_blk_pos_all)):
+        setattr(a, name, t.data_ptr() if t is not None else None)
+    _lib.check(_lib.lib().np_attn_bwd(C.byref(a), C.c_void_p(_lib.stream())), "attn_bwd")
+    return dq, dk, dv, delta
+
+
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        o, lse = flash_fwd(q, k, v, causal=causal, scale=scale, q_off=(k.shape[1] - q.shape[1]) if causal else 0)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv, _ = flash_bwd(q, k, v, o, d_o, lse, causal=ctx.causal, scale=ctx.scale,
+                                  q_off=(k.shape[1] - q.shape[1]) if ctx.causal else 0)
+        return dq, dk, dv, None, None
+
+
+def flash_attention(q, k, v, causal=True, scale=None):
+    """Differentiable attention on the tcgen05 flash kernels (see ``flash_supported``)."""
+    if k.stride() != v.stride():
+        v = v.contiguous() if k.is_contiguous() else v
+        if k.stride() != v.stride():
+            k, v = k.contiguous(), v.contiguous()
+    return _FlashAttention.apply(q, k, v, causal, scale)
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True,
