@@ -2,8 +2,9 @@
 // on tcgen05 tensor cores: S = Q K^T and O += P V (and the five backward products) are tcgen05.mma with
 // TMEM accumulators, Q/K/V/dO tiles arrive by 4-D TMA straight from the strided [B, S, H, hd] tensors
 // (so the q / k / v slices of the fused QKV GEMM output need no copy), softmax runs in registers on
-// four warps that read S out of TMEM, and P / dS go back to shared memory in the 128-byte-swizzled
-// operand layout for the next MMA. Scores are never written to global memory.
+// eight warps that read S out of TMEM (two threads per row, 64 columns each), and P / dS go back to tensor
+// memory as bf16 and feed the next MMA as its TMEM A operand. The output accumulator stays in TMEM as well and
+// is only rescaled when a row maximum has grown by more than 2^8. Scores never touch shared or global memory.
 //
 // K/V (forward, dQ) and Q/dO (dK/dV) may come from a *list* of tensor maps - one per context-parallel
 // rank, pointing into that rank's symmetric memory - so a sequence sharded over GPUs is attended to by
@@ -39,9 +40,6 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* tm, u
   tma_load_4d(dst, tm, bar, 0, h, s0, b);
   tma_load_4d(dst + CHUNK_BYTES, tm, bar, 64, h, s0, b);
 }
-__device__ __forceinline__ void fence_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 // K-major operand [rows, 128 k]: k-step kk (16 elements) -> chunk kk/4, +32 B per step inside the chunk
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int kk) {
   return np::make_smem_desc(tile + (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
@@ -51,12 +49,6 @@ __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int kk) {
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int kk) {
   return np::make_smem_desc(tile + kk * 2048, CHUNK_BYTES, 1024);
 }
-// byte offset of element (row r, col c..c+7) inside a swizzled [128 x 128] bf16 tile
-__device__ __forceinline__ uint32_t swz_off(int r, int cgroup) {  // cgroup = c / 8 in [0, 16)
-  const int chunk = cgroup >> 3, u = cgroup & 7;
-  return chunk * CHUNK_BYTES + r * 128 + ((u ^ (r & 7)) << 4);
-}
-
 struct FwdParams {
   __nv_bfloat16* O; long long o_sb, o_ss, o_sh;   // output strides (elements): batch, seq, head
   float* lse;                                      // [B, Hq, Sq]
@@ -92,37 +84,49 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
-
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // mbarrier wait whose outcome is the same for every lane of the warp, so that the .sync.aligned tensor-memory
 // instructions that follow are never reached by part of a warp
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int kid, int where) {
   return __all_sync(0xffffffffu, np::mbar_wait(bar, parity, abort_flag, kid, where));
 }
+// Named barrier of the two warps (64 threads) that share the rows of one TMEM lane quarter. Every softmax
+// thread reaches every such barrier in every iteration, also after a failed wait, so none is left waiting.
+__device__ __forceinline__ void pair_sync(int quarter) {
+  asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+}
+__device__ __forceinline__ void softmax_sync_all() {
+  asm volatile("bar.sync 5, 256;" ::: "memory");
+}
 
-constexpr int MAX_VIS = 1024;   // visible KV (or Q) blocks one CTA may iterate over
+constexpr int MAX_VIS = 1024;      // visible KV blocks one forward / dQ CTA may iterate over
+constexpr int NTHREADS = 320;      // warp 0: TMA, warp 1: MMA issue, warps 2-9: softmax (two per TMEM lane quarter)
+constexpr float RESCALE_LOG2 = 8.f;
 
 // Barrier slots of the forward kernel
-enum { FB_Q = 0, FB_K = 1, FB_V = 3, FB_KVE = 5, FB_S = 7, FB_P = 9, FB_O = 10, FB_OE = 11, FB_COUNT = 12 };
+enum { FB_Q = 0, FB_K = 1, FB_V = 3, FB_KVE = 5, FB_S = 7, FB_P = 9, FB_O = 10, FB_COUNT = 11 };
 
-// P_TMEM: the probabilities go back into tensor memory (over the S columns they came from) and feed
-// the P V product as a TMEM A operand; otherwise they go through shared memory.
-template <bool P_TMEM>
-__global__ void __launch_bounds__(192, 1)
+// Tensor memory map of the forward kernel (columns): S double buffer, O accumulator, P double buffer (bf16 pairs)
+constexpr uint32_t F_S = 0, F_O = 256, F_P = 384;
+
+__global__ void __launch_bounds__(NTHREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ TmapList tmK,
                 const __grid_constant__ TmapList tmV, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (np::smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sK0 = base + TILE_BYTES, sV0 = sK0 + 2 * TILE_BYTES, sP = sV0 + 2 * TILE_BYTES;
-  const uint32_t after_tiles = sP + (P_TMEM ? 0 : TILE_BYTES);
-  const uint32_t bar = after_tiles;
+  const uint32_t sQ = base, sK0 = base + TILE_BYTES, sV0 = sK0 + 2 * TILE_BYTES;
+  const uint32_t bar = sV0 + 2 * TILE_BYTES;
   auto B_ = [&](int i) { return bar + 8u * i; };
-  uint8_t* gen0 = smem_raw + (base - np::smem_u32(smem_raw));
-  uint8_t* tail = gen0 + (after_tiles - base) + 8 * FB_COUNT;
+  uint8_t* tail = smem_raw + (bar - np::smem_u32(smem_raw)) + 8 * FB_COUNT + 8;   // 16-byte aligned
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
-  volatile int* nvis_s = reinterpret_cast<volatile int*>(tail + 12);
-  volatile short* vis = reinterpret_cast<volatile short*>(tail + 16);
-  uint8_t* sP_gen = gen0 + (sP - base);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
+  volatile int* nvis_s = reinterpret_cast<volatile int*>(tail + 8);
+  float* xch = reinterpret_cast<float*>(tail + 16);                 // [2 iterations][2 halves][128 rows] maxima, then [2][128] sums
+  volatile short* vis = reinterpret_cast<volatile short*>(tail + 16 + 3072);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (p.Sq + BQ - 1) / BQ;
@@ -139,7 +143,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       np::mbar_init(B_(FB_K + s), 1); np::mbar_init(B_(FB_V + s), 1); np::mbar_init(B_(FB_KVE + s), 1);
       np::mbar_init(B_(FB_S + s), 1);
     }
-    np::mbar_init(B_(FB_P), 4); np::mbar_init(B_(FB_O), 1); np::mbar_init(B_(FB_OE), 4);
+    np::mbar_init(B_(FB_P), 8); np::mbar_init(B_(FB_O), 1);
     *abort_flag = 0;
     np::mbar_fence_init();
     // a KV block takes part unless causality hides all of it from every row of this Q block
@@ -156,7 +160,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   np::tc_fence_after();
   const uint32_t tmem = *tmem_ptr_smem;
-  const uint32_t tO = tmem + 256;   // S buffers at columns 0 and 128
+  const uint32_t tO = tmem + F_O;
   const int nvis = *nvis_s;
 
   if (warp == 0) {
@@ -178,7 +182,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_qk = np::make_idesc(128, 128, 1, 1, 0, 0);   // Q (K-major) x K (K-major)
-      const uint32_t idesc_pv = np::make_idesc(128, 128, 1, 1, 0, 1);   // P (K-major) x V (MN-major)
+      const uint32_t idesc_pv = np::make_idesc(128, 128, 1, 1, 0, 1);   // P (TMEM) x V (MN-major)
       bool ok = np::mbar_wait(B_(FB_Q), 0, abort_flag, KID_ATTN, 2);
       auto issue_qk = [&](int i) {
         const int st = i & 1;
@@ -186,134 +190,142 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         np::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          np::tc_mma_f16(tmem + st * 128, desc_kmajor(sQ, kk), desc_kmajor(sK0 + st * TILE_BYTES, kk), idesc_qk, kk > 0);
+          np::tc_mma_f16(tmem + F_S + st * 128, desc_kmajor(sQ, kk), desc_kmajor(sK0 + st * TILE_BYTES, kk), idesc_qk, kk > 0);
         np::tc_commit(B_(FB_S + st));
         return true;
       };
       if (ok && nvis > 0) ok = issue_qk(0);
       for (int i = 0; i < nvis && ok && !*abort_flag; ++i) {
         const int st = i & 1;
-        // S of the next block is computed while the softmax warps work on this one. Its buffer was last
-        // read for block i-1, whose probabilities were awaited before P V of block i-1 was issued.
+        // S of the next block is computed while the softmax warps work on this one. Its S and P buffers were
+        // last used for block i-1: S read before P of block i-1 arrived, P consumed by P V of block i-1 (issued).
         if (i + 1 < nvis) ok = issue_qk(i + 1);
-        ok = ok && np::mbar_wait(B_(FB_P), (uint32_t)i & 1u, abort_flag, KID_ATTN, 5) &&      // P is ready
-             np::mbar_wait(B_(FB_V + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN, 4) &&
-             np::mbar_wait(B_(FB_OE), ((uint32_t)i & 1u) ^ 1u, abort_flag, KID_ATTN, 6);      // previous O partial consumed
+        ok = ok && np::mbar_wait(B_(FB_P), (uint32_t)i & 1u, abort_flag, KID_ATTN, 5) &&   // P ready, O rescaled
+             np::mbar_wait(B_(FB_V + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN, 4);
         if (!ok) break;
         np::tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          if (P_TMEM)
-            tc_mma_f16_ts(tO, tmem + st * 128 + kk * 8, desc_mnmajor(sV0 + st * TILE_BYTES, kk), idesc_pv, kk > 0);
-          else
-            np::tc_mma_f16(tO, desc_kmajor(sP, kk), desc_mnmajor(sV0 + st * TILE_BYTES, kk), idesc_pv, kk > 0);
-        }
+        for (int kk = 0; kk < 8; ++kk)
+          tc_mma_f16_ts(tO, tmem + F_P + st * 64 + kk * 8, desc_mnmajor(sV0 + st * TILE_BYTES, kk), idesc_pv,
+                        (i > 0) || (kk > 0));
         np::tc_commit(B_(FB_O));
         np::tc_commit(B_(FB_KVE + st));
       }
     }
   } else {
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;                 // row inside the Q block
+    const int quarter = warp & 3, hf = (warp - 2) >> 2;     // this thread: row r, columns [64 hf, 64 hf + 64)
+    const int r = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int q_pos = q_pos0 + r;
-    float m = -INFINITY, l = 0.f;
-    float o[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    float m = -INFINITY, l = 0.f;                            // running maximum (log2 domain) and row sum
     bool ok = true;
-    for (int i = 0; i < nvis && ok && !*abort_flag; ++i) {
+    for (int i = 0; i < nvis; ++i) {
       const int st = i & 1;
       const int j = vis[i];
       const int jb = j % p.src_blocks;
       const int kp0 = k_pos0(j);
-      const int valid_cols = p.src_len - jb * BKV;      // columns beyond the source's length are padding
+      const int valid_cols = p.src_len - jb * BKV;           // columns beyond the source's length are padding
       const bool need_mask = (p.causal && kp0 + BKV - 1 > q_pos0) || valid_cols < BKV;
-      const uint32_t tS = tmem + st * 128 + lane_off;
-      ok = warp_wait(B_(FB_S + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN, 7);
-      if (!ok) break;
-      np::tc_fence_after();
-      // pass 1: row maximum
-      float mx = m;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        np::tmem_ld32(tS + c * 32, s);
+      ok = ok && !*abort_flag && warp_wait(B_(FB_S + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN, 7);
+      uint32_t s[64];
+      float mloc = -INFINITY;
+      if (ok) {
+        np::tc_fence_after();
+        np::tmem_ld32(tmem + F_S + st * 128 + lane_off + hf * 64, s);
+        np::tmem_ld32(tmem + F_S + st * 128 + lane_off + hf * 64 + 32, s + 32);
         np::tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float v = __uint_as_float(s[e]) * p.scale_log2;
-          if (need_mask) {
-            const int col = c * 32 + e;
-            if (col >= valid_cols || (p.causal && kp0 + col > q_pos)) v = -INFINITY;
+          for (int e = 0; e < 64; ++e) {
+            const int col = hf * 64 + e;
+            if (col >= valid_cols || (p.causal && kp0 + col > q_pos)) s[e] = 0xff800000u;   // -inf
           }
-          mx = fmaxf(mx, v);
+        }
+#pragma unroll
+        for (int e = 0; e < 64; ++e) mloc = fmaxf(mloc, __uint_as_float(s[e]));
+        mloc *= p.scale_log2;
+      }
+      xch[(st * 2 + hf) * 128 + r] = mloc;
+      pair_sync(quarter);
+      if (ok) {
+        const float mx = fmaxf(mloc, xch[(st * 2 + (hf ^ 1)) * 128 + r]);   // both threads of the row agree on it
+        // the accumulator is only rescaled when some row of the warp outgrew its reference maximum by 2^8
+        const bool grow = mx > m + RESCALE_LOG2 || (m == -INFINITY && mx > -INFINITY);
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = fmaxf(m, mx);
+          const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m - m_new);
+          if (i > 0) {
+            ok = warp_wait(B_(FB_O), (uint32_t)(i - 1) & 1u, abort_flag, KID_ATTN, 8);   // P V of block i-1 is done
+            if (ok) {
+              np::tc_fence_after();
+              uint32_t t[64];
+              np::tmem_ld32(tO + lane_off + hf * 64, t);
+              np::tmem_ld32(tO + lane_off + hf * 64 + 32, t + 32);
+              np::tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 64; ++e) t[e] = __float_as_uint(__uint_as_float(t[e]) * alpha);
+#pragma unroll
+              for (int c = 0; c < 4; ++c) tmem_st16(tO + lane_off + hf * 64 + c * 16, t + c * 16);
+            }
+          }
+          l *= alpha;
+          m = m_new;
         }
       }
-      const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
-      // pass 2: probabilities (bf16) -> operand of the P V product; row sum
-      float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        np::tmem_ld32(tS + c * 32, s);
-        np::tmem_ld_wait();
-        uint32_t pk[16];
+      if (ok) {
+        const float m_use = (m == -INFINITY) ? 0.f : m;
+        float rs0 = 0.f, rs1 = 0.f;
+        uint32_t pk[32];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float v0 = __uint_as_float(s[e]) * p.scale_log2, v1 = __uint_as_float(s[e + 1]) * p.scale_log2;
-          if (need_mask) {
-            const int col = c * 32 + e;
-            if (col >= valid_cols || (p.causal && kp0 + col > q_pos)) v0 = -INFINITY;
-            if (col + 1 >= valid_cols || (p.causal && kp0 + col + 1 > q_pos)) v1 = -INFINITY;
-          }
-          const float p0 = exp2f(v0 - m_use), p1 = exp2f(v1 - m_use);
-          rs += p0 + p1;
+        for (int e = 0; e < 64; e += 2) {
+          const float p0 = ex2(fmaf(__uint_as_float(s[e]), p.scale_log2, -m_use));
+          const float p1 = ex2(fmaf(__uint_as_float(s[e + 1]), p.scale_log2, -m_use));
+          rs0 += p0;
+          rs1 += p1;
           pk[e >> 1] = np::pack_bf16(p0, p1);
         }
-        if (P_TMEM) {
-          tmem_st16(tS + c * 16, pk);   // columns [16c, 16c+16) were read in this or an earlier chunk
-        } else {
-#pragma unroll
-          for (int g = 0; g < 4; ++g)
-            *reinterpret_cast<uint4*>(sP_gen + swz_off(r, c * 4 + g)) =
-                make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
-        }
+        l += rs0 + rs1;
+        tmem_st16(tmem + F_P + st * 64 + lane_off + hf * 32, pk);
+        tmem_st16(tmem + F_P + st * 64 + lane_off + hf * 32 + 16, pk + 16);
+        tmem_st_wait();
+        np::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) np::mbar_arrive(B_(FB_P));
       }
-      m = mx;
-      l = l * alpha + rs;
-      if (P_TMEM) tmem_st_wait(); else fence_async_smem();
-      np::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) np::mbar_arrive(B_(FB_P));
-      // accumulate this block's P V
-      ok = warp_wait(B_(FB_O), (uint32_t)i & 1u, abort_flag, KID_ATTN, 8);
-      if (!ok) break;
-      np::tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t t[32];
-        np::tmem_ld32(tO + lane_off + c * 32, t);
-        np::tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) o[c * 32 + e] = fmaf(o[c * 32 + e], alpha, __uint_as_float(t[e]));
-      }
-      np::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) np::mbar_arrive(B_(FB_OE));
     }
+    // both halves of a row hold the same maximum; their partial sums add up
+    xch[512 + hf * 128 + r] = l;
+    pair_sync(quarter);
+    const float l_tot = l + xch[512 + (hf ^ 1) * 128 + r];
+    ok = ok && !*abort_flag;
+    if (nvis > 0) ok = ok && warp_wait(B_(FB_O), (uint32_t)(nvis - 1) & 1u, abort_flag, KID_ATTN, 9);
+    ok = __all_sync(0xffffffffu, ok);
     const int row = qb * BQ + r;
-    if (ok && row < p.Sq) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = p.O + (size_t)b * p.o_sb + (size_t)row * p.o_ss + (size_t)h * p.o_sh;
+    if (ok) {
+      uint32_t t[64];
+      if (nvis > 0) {
+        np::tc_fence_after();
+        np::tmem_ld32(tO + lane_off + hf * 64, t);
+        np::tmem_ld32(tO + lane_off + hf * 64 + 32, t + 32);
+        np::tmem_ld_wait();
+      } else {
 #pragma unroll
-      for (int g = 0; g < HD / 8; ++g)
-        reinterpret_cast<uint4*>(dst)[g] =
-            make_uint4(np::pack_bf16(o[8 * g] * inv, o[8 * g + 1] * inv), np::pack_bf16(o[8 * g + 2] * inv, o[8 * g + 3] * inv),
-                       np::pack_bf16(o[8 * g + 4] * inv, o[8 * g + 5] * inv), np::pack_bf16(o[8 * g + 6] * inv, o[8 * g + 7] * inv));
-      if (p.lse)
-        p.lse[((size_t)b * p.Hq + h) * p.Sq + row] = l > 0.f ? (m * 0.6931471805599453f + logf(l)) : -INFINITY;
+        for (int e = 0; e < 64; ++e) t[e] = 0u;
+      }
+      if (row < p.Sq) {
+        const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+        __nv_bfloat16* dst = p.O + (size_t)b * p.o_sb + (size_t)row * p.o_ss + (size_t)h * p.o_sh + hf * 64;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(t[8 * g + e]) * inv;
+          reinterpret_cast<uint4*>(dst)[g] = make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]),
+                                                        np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
+        }
+        if (p.lse && hf == 0)
+          p.lse[((size_t)b * p.Hq + h) * p.Sq + row] = l_tot > 0.f ? (m * 0.6931471805599453f + logf(l_tot)) : -INFINITY;
+      }
     }
   }
   np::tc_fence_before();
@@ -361,13 +373,14 @@ struct NpAttnFwdArgs {
   int B, Sq, Hq, Hkv, causal, n_src, src_len, q_off;
   float scale;
   const int* q_blk_pos; const int* k_blk_pos;
-  int p_in_smem;   // 1: pass the probabilities through shared memory instead of tensor memory
 };
 
 NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
   if (a->B <= 0 || a->Sq <= 0 || a->src_len <= 0) return 0;
   if (a->n_src < 1 || a->n_src > MAX_SRC || a->Hq % a->Hkv) return 1;
-  if ((a->q_ss | a->q_sh | a->q_sb | a->k_ss | a->k_sh | a->k_sb) % 8 || (((uintptr_t)a->q) & 15)) return 1;
+  if ((a->q_ss | a->q_sh | a->q_sb | a->k_ss | a->k_sh | a->k_sb | a->o_ss | a->o_sh | a->o_sb) % 8 ||
+      (((uintptr_t)a->q | (uintptr_t)a->o) & 15))
+    return 1;
   if (!bind_ctx()) return 2;
   CUtensorMap tmQ;
   TmapList tmK, tmV;
@@ -387,21 +400,15 @@ NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
   p.n_src = a->n_src; p.src_len = a->src_len; p.src_blocks = (a->src_len + BKV - 1) / BKV;
   p.q_blk_pos = a->q_blk_pos; p.k_blk_pos = a->k_blk_pos; p.q_off = a->q_off;
   if (p.n_src * p.src_blocks > MAX_VIS) return 1;
-  constexpr int TAIL = 1024 + 8 * FB_COUNT + 16 + 2 * MAX_VIS + 64;
-  constexpr int SMEM_T = 5 * TILE_BYTES + TAIL, SMEM_S = 6 * TILE_BYTES + TAIL;
+  constexpr int SMEM = 5 * TILE_BYTES + 1024 + 8 * FB_COUNT + 8 + 16 + 3072 + 2 * MAX_VIS + 64;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_T);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_S);
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return 400 + (int)e;
     attr_set = true;
   }
   dim3 grid((a->Sq + BQ - 1) / BQ, a->Hq, a->B);
-  if (a->p_in_smem)
-    attn_fwd_kernel<false><<<grid, 192, SMEM_S, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
-  else
-    attn_fwd_kernel<true><<<grid, 192, SMEM_T, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
+  attn_fwd_kernel<<<grid, NTHREADS, SMEM, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 500 + (int)e;
 }
@@ -457,7 +464,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long
 
 enum { QB_QDO = 0, QB_K = 1, QB_V = 3, QB_KVE = 5, QB_S = 7, QB_DP = 9, QB_DS = 10, QB_FIN = 11, QB_COUNT = 12 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(NTHREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ TmapList tmK, const __grid_constant__ TmapList tmV, const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -486,7 +493,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       np::mbar_init(B_(QB_K + s), 1); np::mbar_init(B_(QB_V + s), 1); np::mbar_init(B_(QB_KVE + s), 1);
       np::mbar_init(B_(QB_S + s), 1);
     }
-    np::mbar_init(B_(QB_DP), 1); np::mbar_init(B_(QB_DS), 4); np::mbar_init(B_(QB_FIN), 1);
+    np::mbar_init(B_(QB_DP), 1); np::mbar_init(B_(QB_DS), 8); np::mbar_init(B_(QB_FIN), 1);
     *abort_flag = 0;
     np::mbar_fence_init();
     int n = 0;
@@ -562,7 +569,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       np::tc_commit(B_(QB_FIN));
     }
   } else {
-    const int quarter = warp & 3;
+    const int quarter = warp & 3, hf = (warp - 2) >> 2;     // this thread: row r, KV columns [64 hf, 64 hf + 64)
     const int r = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int row = qb * BQ + r;
@@ -575,76 +582,73 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       dlt = p.delta[idx];
     }
     bool ok = true;
-    for (int i = 0; i < nvis && ok && !*abort_flag; ++i) {
+    for (int i = 0; i < nvis; ++i) {
       const int st = i & 1;
       const int j = vis[i];
       const int jb = j % p.src_blocks;
       const int kp0 = k_pos0(j);
       const int valid_cols = p.src_len - jb * BKV;
       const bool need_mask = (p.causal && kp0 + BKV - 1 > q_pos0) || valid_cols < BKV;
-      const uint32_t tS = tmem + st * 128 + lane_off;
-      ok = warp_wait(B_(QB_S + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN_DQ, 7);
-      if (!ok) break;
-      np::tc_fence_after();
-      float pr[BKV];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        np::tmem_ld32(tS + c * 32, s);
+      ok = ok && !*abort_flag && warp_wait(B_(QB_S + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN_DQ, 7);
+      float pr[64];
+      uint32_t t[64];
+      if (ok) {
+        np::tc_fence_after();
+        np::tmem_ld32(tmem + st * 128 + lane_off + hf * 64, t);
+        np::tmem_ld32(tmem + st * 128 + lane_off + hf * 64 + 32, t + 32);
         np::tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float v = exp2f(__uint_as_float(s[e]) * p.scale_log2 - lse2);
-          if (need_mask) {
-            const int col = c * 32 + e;
-            if (col >= valid_cols || (p.causal && kp0 + col > q_pos)) v = 0.f;
+        for (int e = 0; e < 64; ++e) pr[e] = ex2(fmaf(__uint_as_float(t[e]), p.scale_log2, -lse2));
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 64; ++e) {
+            const int col = hf * 64 + e;
+            if (col >= valid_cols || (p.causal && kp0 + col > q_pos)) pr[e] = 0.f;
           }
-          pr[c * 32 + e] = v;
         }
+        ok = warp_wait(B_(QB_DP), (uint32_t)i & 1u, abort_flag, KID_ATTN_DQ, 8);
       }
-      ok = warp_wait(B_(QB_DP), (uint32_t)i & 1u, abort_flag, KID_ATTN_DQ, 8);
-      if (!ok) break;
-      np::tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        np::tmem_ld32(tdP + lane_off + c * 32, s);
+      if (ok) {
+        np::tc_fence_after();
+        np::tmem_ld32(tdP + lane_off + hf * 64, t);
+        np::tmem_ld32(tdP + lane_off + hf * 64 + 32, t + 32);
         np::tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2)
-          pk[e >> 1] = np::pack_bf16(pr[c * 32 + e] * (__uint_as_float(s[e]) - dlt),
-                                     pr[c * 32 + e + 1] * (__uint_as_float(s[e + 1]) - dlt));
-        tmem_st16(tdP + lane_off + c * 16, pk);
       }
-      tmem_st_wait();
-      np::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) np::mbar_arrive(B_(QB_DS));
+      pair_sync(quarter);   // both threads of the row hold their dP values: dS may now overwrite those columns
+      if (ok) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int e = 0; e < 64; e += 2)
+          pk[e >> 1] = np::pack_bf16(pr[e] * (__uint_as_float(t[e]) - dlt), pr[e + 1] * (__uint_as_float(t[e + 1]) - dlt));
+        tmem_st16(tdP + lane_off + hf * 32, pk);
+        tmem_st16(tdP + lane_off + hf * 32 + 16, pk + 16);
+        tmem_st_wait();
+        np::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) np::mbar_arrive(B_(QB_DS));
+      }
     }
-    ok = __all_sync(0xffffffffu, ok) && warp_wait(B_(QB_FIN), 0, abort_flag, KID_ATTN_DQ, 9);
-    if (ok) {   // warp-uniform: the tensor-memory loads below are executed by whole warps, only the stores are guarded
-      np::tc_fence_after();
-      __nv_bfloat16* dst = p.dQ + (size_t)b * p.dq_sb + (size_t)row * p.dq_ss + (size_t)h * p.dq_sh;
+    ok = __all_sync(0xffffffffu, ok && !*abort_flag) && warp_wait(B_(QB_FIN), 0, abort_flag, KID_ATTN_DQ, 9);
+    if (ok) {   // warp-uniform: the tensor-memory loads are executed by whole warps, only the stores are guarded
+      uint32_t t[64];
+      if (nvis > 0) {
+        np::tc_fence_after();
+        np::tmem_ld32(tdQ + lane_off + hf * 64, t);
+        np::tmem_ld32(tdQ + lane_off + hf * 64 + 32, t + 32);
+        np::tmem_ld_wait();
+      } else {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t t[32];
-        if (nvis > 0) {
-          np::tmem_ld32(tdQ + lane_off + c * 32, t);
-          np::tmem_ld_wait();
-        } else {
+        for (int e = 0; e < 64; ++e) t[e] = 0u;
+      }
+      if (row < p.Sq) {
+        __nv_bfloat16* dst = p.dQ + (size_t)b * p.dq_sb + (size_t)row * p.dq_ss + (size_t)h * p.dq_sh + hf * 64;
 #pragma unroll
-          for (int e = 0; e < 32; ++e) t[e] = 0u;
-        }
-        if (row < p.Sq) {
+        for (int g = 0; g < 8; ++g) {
+          float f[8];
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float f[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(t[8 * g + e]) * p.scale;
-            reinterpret_cast<uint4*>(dst)[c * 4 + g] = make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]),
-                                                                  np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
-          }
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(t[8 * g + e]) * p.scale;
+          reinterpret_cast<uint4*>(dst)[g] = make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]),
+                                                        np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
         }
       }
     }
@@ -661,7 +665,7 @@ enum { KB_KV = 0, KB_Q = 1, KB_DO = 3, KB_QE = 5, KB_DOE = 7, KB_ST = 9, KB_DPT 
        KB_COUNT = 14 };
 
 // iteration descriptor: source << 24 | head-in-group << 16 | q block
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(NTHREADS, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const __grid_constant__ TmapList tmQ, const __grid_constant__ TmapList tmdO, const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -692,7 +696,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
       np::mbar_init(B_(KB_QE + s), 1); np::mbar_init(B_(KB_DOE + s), 1);
     }
     np::mbar_init(B_(KB_ST), 1); np::mbar_init(B_(KB_DPT), 1);
-    np::mbar_init(B_(KB_P), 4); np::mbar_init(B_(KB_DS), 4); np::mbar_init(B_(KB_FIN), 1);
+    np::mbar_init(B_(KB_P), 8); np::mbar_init(B_(KB_DS), 8); np::mbar_init(B_(KB_FIN), 1);
     *abort_flag = 0;
     np::mbar_fence_init();
     int n = 0;
@@ -779,113 +783,116 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
       np::tc_commit(B_(KB_FIN));
     }
   } else {
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;               // KV row of this thread
-    const int t128 = threadIdx.x - 64;               // 0..127 among the softmax threads
+    const int quarter = warp & 3, hf = (warp - 2) >> 2;   // this thread: KV row r, Q columns [64 hf, 64 hf + 64)
+    const int r = quarter * 32 + lane;
+    const int t256 = threadIdx.x - 64;                    // 0..255 among the softmax threads
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int k_pos = k_pos0 + r;
     bool ok = true;
-    for (int i = 0; i < nvis; ++i) {   // every thread runs every iteration: the named barrier below needs all 128
+    for (int i = 0; i < nvis; ++i) {   // every thread runs every iteration: the named barriers need all of them
       const int st = i & 1;
       const int d = vis[i];
       const int src = d >> 24, h = hkv * n_rep + ((d >> 16) & 0xff), qi = d & 0xffff;
       const int q_pos0 = q_pos0_of(src, qi);
-      {  // stage this Q block's log-sum-exp and delta (one column each per thread)
-        const int qrow = qi * BQ + t128;
-        float l2 = INFINITY, dl = 0.f;
+      {  // stage this Q block's log-sum-exp (threads 0-127) and delta (threads 128-255), one column each
+        const int qrow = qi * BQ + (t256 & 127);
+        float val = (t256 < 128) ? INFINITY : 0.f;
         if (qrow < p.src_len) {
           const size_t idx = ((size_t)b * p.Hq + h) * p.src_len + qrow;
-          const float l = p.lse_src.p[src][idx];
-          l2 = (l == -INFINITY) ? INFINITY : l * LOG2E;
-          dl = p.delta_src.p[src][idx];
-        }
-        s_lse[st * 128 + t128] = l2;
-        s_dlt[st * 128 + t128] = dl;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
-      if (!ok || *abort_flag) { ok = false; continue; }   // after a failed wait only the barrier above is kept up
-      const bool need_mask = p.causal && k_pos0 + BKV - 1 > q_pos0;
-      ok = warp_wait(B_(KB_ST), (uint32_t)i & 1u, abort_flag, KID_ATTN_DKV, 8);
-      if (!ok) continue;
-      np::tc_fence_after();
-      float pr[BQ];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        np::tmem_ld32(tSt + lane_off + c * 32, s);
-        np::tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(&s_lse[st * 128 + c * 32 + e]);
-          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float v = exp2f(__uint_as_float(s[e + u]) * p.scale_log2 - ls[u]);
-            if (need_mask && k_pos > q_pos0 + c * 32 + e + u) v = 0.f;
-            pr[c * 32 + e + u] = v;
+          if (t256 < 128) {
+            const float l = p.lse_src.p[src][idx];
+            val = (l == -INFINITY) ? INFINITY : l * LOG2E;
+          } else {
+            val = p.delta_src.p[src][idx];
           }
-          pk[e >> 1] = np::pack_bf16(pr[c * 32 + e], pr[c * 32 + e + 1]);
-          pk[(e >> 1) + 1] = np::pack_bf16(pr[c * 32 + e + 2], pr[c * 32 + e + 3]);
         }
-        tmem_st16(tSt + lane_off + c * 16, pk);
+        (t256 < 128 ? s_lse : s_dlt)[st * 128 + (t256 & 127)] = val;
+        softmax_sync_all();
       }
-      tmem_st_wait();
-      np::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) np::mbar_arrive(B_(KB_P));
-      ok = warp_wait(B_(KB_DPT), (uint32_t)i & 1u, abort_flag, KID_ATTN_DKV, 9);
-      if (!ok) continue;
-      np::tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        np::tmem_ld32(tdPt + lane_off + c * 32, s);
+      const bool need_mask = p.causal && k_pos0 + BKV - 1 > q_pos0;
+      ok = ok && !*abort_flag && warp_wait(B_(KB_ST), (uint32_t)i & 1u, abort_flag, KID_ATTN_DKV, 8);
+      float pr[64];
+      uint32_t t[64], pk[32];
+      if (ok) {
+        np::tc_fence_after();
+        np::tmem_ld32(tSt + lane_off + hf * 64, t);
+        np::tmem_ld32(tSt + lane_off + hf * 64 + 32, t + 32);
         np::tmem_ld_wait();
-        uint32_t pk[16];
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const float4 d4 = *reinterpret_cast<const float4*>(&s_dlt[st * 128 + c * 32 + e]);
-          pk[e >> 1] = np::pack_bf16(pr[c * 32 + e] * (__uint_as_float(s[e]) - d4.x),
-                                     pr[c * 32 + e + 1] * (__uint_as_float(s[e + 1]) - d4.y));
-          pk[(e >> 1) + 1] = np::pack_bf16(pr[c * 32 + e + 2] * (__uint_as_float(s[e + 2]) - d4.z),
-                                           pr[c * 32 + e + 3] * (__uint_as_float(s[e + 3]) - d4.w));
+        for (int e = 0; e < 64; e += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(&s_lse[st * 128 + hf * 64 + e]);
+          pr[e] = ex2(fmaf(__uint_as_float(t[e]), p.scale_log2, -l4.x));
+          pr[e + 1] = ex2(fmaf(__uint_as_float(t[e + 1]), p.scale_log2, -l4.y));
+          pr[e + 2] = ex2(fmaf(__uint_as_float(t[e + 2]), p.scale_log2, -l4.z));
+          pr[e + 3] = ex2(fmaf(__uint_as_float(t[e + 3]), p.scale_log2, -l4.w));
         }
-        tmem_st16(tdPt + lane_off + c * 16, pk);
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 64; ++e)
+            if (k_pos > q_pos0 + hf * 64 + e) pr[e] = 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 64; e += 2) pk[e >> 1] = np::pack_bf16(pr[e], pr[e + 1]);
       }
-      tmem_st_wait();
-      np::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) np::mbar_arrive(B_(KB_DS));
+      pair_sync(quarter);   // both threads of the row hold their S^T values: P^T may now overwrite those columns
+      if (ok) {
+        tmem_st16(tSt + lane_off + hf * 32, pk);
+        tmem_st16(tSt + lane_off + hf * 32 + 16, pk + 16);
+        tmem_st_wait();
+        np::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) np::mbar_arrive(B_(KB_P));
+        ok = warp_wait(B_(KB_DPT), (uint32_t)i & 1u, abort_flag, KID_ATTN_DKV, 9);
+      }
+      if (ok) {
+        np::tc_fence_after();
+        np::tmem_ld32(tdPt + lane_off + hf * 64, t);
+        np::tmem_ld32(tdPt + lane_off + hf * 64 + 32, t + 32);
+        np::tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 64; e += 4) {
+          const float4 d4 = *reinterpret_cast<const float4*>(&s_dlt[st * 128 + hf * 64 + e]);
+          pk[e >> 1] = np::pack_bf16(pr[e] * (__uint_as_float(t[e]) - d4.x), pr[e + 1] * (__uint_as_float(t[e + 1]) - d4.y));
+          pk[(e >> 1) + 1] =
+              np::pack_bf16(pr[e + 2] * (__uint_as_float(t[e + 2]) - d4.z), pr[e + 3] * (__uint_as_float(t[e + 3]) - d4.w));
+        }
+      }
+      pair_sync(quarter);   // same for dP^T -> dS^T
+      if (ok) {
+        tmem_st16(tdPt + lane_off + hf * 32, pk);
+        tmem_st16(tdPt + lane_off + hf * 32 + 16, pk + 16);
+        tmem_st_wait();
+        np::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) np::mbar_arrive(B_(KB_DS));
+      }
     }
     ok = __all_sync(0xffffffffu, ok && !*abort_flag) && warp_wait(B_(KB_FIN), 0, abort_flag, KID_ATTN_DKV, 10);
     const int row = jb * BKV + r;
     if (ok) {   // warp-uniform; only the stores are guarded by the row bound
       np::tc_fence_after();
-      const size_t off = (size_t)b * p.dk_sb + (size_t)row * p.dk_ss + (size_t)hkv * p.dk_sh;
+      const size_t off = (size_t)b * p.dk_sb + (size_t)row * p.dk_ss + (size_t)hkv * p.dk_sh + hf * 64;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dst = (which ? p.dK : p.dV) + off;
         const float mul = which ? p.scale : 1.f;
+        uint32_t t[64];
+        if (nvis > 0) {
+          np::tmem_ld32((which ? tdK : tdV) + lane_off + hf * 64, t);
+          np::tmem_ld32((which ? tdK : tdV) + lane_off + hf * 64 + 32, t + 32);
+          np::tmem_ld_wait();
+        } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t t[32];
-          if (nvis > 0) {
-            np::tmem_ld32((which ? tdK : tdV) + lane_off + c * 32, t);
-            np::tmem_ld_wait();
-          } else {
+          for (int e = 0; e < 64; ++e) t[e] = 0u;
+        }
+        if (row < p.Sk) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) t[e] = 0u;
-          }
-          if (row < p.Sk) {
+          for (int g = 0; g < 8; ++g) {
+            float f[8];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              float f[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(t[8 * g + e]) * mul;
-              reinterpret_cast<uint4*>(dst)[c * 4 + g] = make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]),
-                                                                    np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
-            }
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(t[8 * g + e]) * mul;
+            reinterpret_cast<uint4*>(dst)[g] = make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]),
+                                                          np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
           }
         }
       }
@@ -977,12 +984,12 @@ NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
   BwdParams pq = p;
   pq.src_blocks = kblocks; pq.src_len = a->Sk;
   pq.q_blk_pos = a->q_blk_pos_local; pq.k_blk_pos = a->k_blk_pos_all;
-  attn_bwd_dq_kernel<<<dim3(qblocks, a->Hq, a->B), 192, SMEM_DQ, stream>>>(tmQ, tmdO, lK, lV, pq);
+  attn_bwd_dq_kernel<<<dim3(qblocks, a->Hq, a->B), NTHREADS, SMEM_DQ, stream>>>(tmQ, tmdO, lK, lV, pq);
   // dK, dV: local KV blocks against every source's Q blocks
   BwdParams pk = p;
   pk.src_blocks = qblocks; pk.src_len = a->Sq;
   pk.q_blk_pos = a->q_blk_pos_all; pk.k_blk_pos = a->k_blk_pos_local;
-  attn_bwd_dkv_kernel<<<dim3(kblocks, a->Hkv, a->B), 192, SMEM_DKV, stream>>>(tmK, tmV, lQ, ldO, pk);
+  attn_bwd_dkv_kernel<<<dim3(kblocks, a->Hkv, a->B), NTHREADS, SMEM_DKV, stream>>>(tmK, tmV, lQ, ldO, pk);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 500 + (int)e;
 }

@@ -82,7 +82,6 @@ class AttnFwdArgs(C.Structure):
         ("src_len", c_int), ("q_off", c_int),
         ("scale", c_float),
         ("q_blk_pos", c_void_p), ("k_blk_pos", c_void_p),
-        ("p_in_smem", c_int),
     ]
 
 

@@ -68,8 +68,7 @@ def flash_supported(q: torch.Tensor, k: torch.Tensor) -> bool:
             and all(s % 8 == 0 for s in q.stride()[:3]) and all(s % 8 == 0 for s in k.stride()[:3]))
 
 
-def flash_fwd(q, k_list, v_list, *, causal=True, scale=None, q_off=0, q_blk_pos=None, k_blk_pos=None,
-              p_in_smem=False):
+def flash_fwd(q, k_list, v_list, *, causal=True, scale=None, q_off=0, q_blk_pos=None, k_blk_pos=None):
     """Forward flash attention on the tcgen05 kernel. ``k_list`` / ``v_list`` are lists of equally shaped
     ``[B, Sk, Hkv, 128]`` KV sources (one entry without context parallelism; one per rank's shard - any of
     them may live in a peer's memory - with it). Returns ``(out [B,Sq,Hq,128] bf16, lse [B,Hq,Sq] fp32)``."""
@@ -96,7 +95,6 @@ def flash_fwd(q, k_list, v_list, *, causal=True, scale=None, q_off=0, q_blk_pos=
     a.scale = scale or 1.0 / math.sqrt(hd)
     a.q_blk_pos = q_blk_pos.data_ptr() if q_blk_pos is not None else None
     a.k_blk_pos = k_blk_pos.data_ptr() if k_blk_pos is not None else None
-    a.p_in_smem = int(p_in_smem)
     _lib.check(_lib.lib().np_attn_fwd(C.byref(a), C.c_void_p(_lib.stream())), "attn_fwd")
     return o, lse
 
