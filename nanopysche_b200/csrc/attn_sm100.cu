@@ -103,12 +103,12 @@ __device__ __forceinline__ void softmax_sync_all() {
   asm volatile("bar.sync 5, 256;" ::: "memory");
 }
 
-constexpr int MAX_VIS = 1024;      // visible KV blocks one forward / dQ CTA may iterate over
 constexpr int NTHREADS = 320;      // warp 0: TMA, warp 1: MMA issue, warps 2-9: softmax (two per TMEM lane quarter)
 constexpr float RESCALE_LOG2 = 8.f;
 
 // Barrier slots of the forward kernel
-enum { FB_Q = 0, FB_K = 1, FB_V = 3, FB_KVE = 5, FB_S = 7, FB_P = 9, FB_O = 10, FB_COUNT = 11 };
+enum { FB_Q = 0, FB_K = 1, FB_KE = 3, FB_V = 5, FB_VE = 8, FB_S = 11, FB_P = 13, FB_O = 14, FB_COUNT = 15 };
+constexpr int F_KST = 2, F_VST = 3;   // K tiles are free again after Q K^T, V tiles only after P V: V gets the deeper ring
 
 // Tensor memory map of the forward kernel (columns): S double buffer, O accumulator, P double buffer (bf16 pairs)
 constexpr uint32_t F_S = 0, F_O = 256, F_P = 384;
@@ -118,15 +118,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const __grid_constant__ TmapList tmV, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (np::smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sK0 = base + TILE_BYTES, sV0 = sK0 + 2 * TILE_BYTES;
-  const uint32_t bar = sV0 + 2 * TILE_BYTES;
+  const uint32_t sQ = base, sK0 = base + TILE_BYTES, sV0 = sK0 + F_KST * TILE_BYTES;
+  const uint32_t bar = sV0 + F_VST * TILE_BYTES;
   auto B_ = [&](int i) { return bar + 8u * i; };
   uint8_t* tail = smem_raw + (bar - np::smem_u32(smem_raw)) + 8 * FB_COUNT + 8;   // 16-byte aligned
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
-  volatile int* nvis_s = reinterpret_cast<volatile int*>(tail + 8);
   float* xch = reinterpret_cast<float*>(tail + 16);                 // [2 iterations][2 halves][128 rows] maxima, then [2][128] sums
-  volatile short* vis = reinterpret_cast<volatile short*>(tail + 16 + 3072);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (p.Sq + BQ - 1) / BQ;
@@ -136,21 +134,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int q_pos0 = p.q_blk_pos ? p.q_blk_pos[qb] : qb * BQ + p.q_off;
   const int total_blocks = p.n_src * p.src_blocks;
   auto k_pos0 = [&](int j) { return p.k_blk_pos ? p.k_blk_pos[j] : (j % p.src_blocks) * BKV; };
+  // Every role walks the same list: the KV blocks that causality does not hide from all rows of this Q block.
+  auto next_vis = [&](int j) {
+    while (j < total_blocks && p.causal && k_pos0(j) > q_pos0 + BQ - 1) ++j;
+    return j;
+  };
 
   if (threadIdx.x == 0) {
-    np::mbar_init(B_(FB_Q), 1);
-    for (int s = 0; s < 2; ++s) {
-      np::mbar_init(B_(FB_K + s), 1); np::mbar_init(B_(FB_V + s), 1); np::mbar_init(B_(FB_KVE + s), 1);
-      np::mbar_init(B_(FB_S + s), 1);
-    }
-    np::mbar_init(B_(FB_P), 8); np::mbar_init(B_(FB_O), 1);
+    for (int i = 0; i < FB_COUNT; ++i) np::mbar_init(B_(i), i == FB_P ? 8 : 1);
     *abort_flag = 0;
     np::mbar_fence_init();
-    // a KV block takes part unless causality hides all of it from every row of this Q block
-    int n = 0;
-    for (int j = 0; j < total_blocks && n < MAX_VIS; ++j)
-      if (!p.causal || k_pos0(j) <= q_pos0 + BQ - 1) vis[n++] = (short)j;
-    *nvis_s = n;
   }
   if (warp == 1) {
     np::tmem_alloc(np::smem_u32((const void*)tmem_ptr_smem), 512);
@@ -161,22 +154,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   np::tc_fence_after();
   const uint32_t tmem = *tmem_ptr_smem;
   const uint32_t tO = tmem + F_O;
-  const int nvis = *nvis_s;
 
   if (warp == 0) {
     if (lane == 0) {
       np::mbar_expect_tx(B_(FB_Q), TILE_BYTES);
       load_tile(sQ, &tmQ, B_(FB_Q), h, qb * BQ, b);
-      for (int i = 0; i < nvis && !*abort_flag; ++i) {
-        const int st = i & 1;
-        const uint32_t ph = (uint32_t)(i >> 1) & 1u;
-        if (!np::mbar_wait(B_(FB_KVE + st), ph ^ 1u, abort_flag, KID_ATTN, 1)) break;
-        const int j = vis[i];
+      int i = 0;
+      for (int j = next_vis(0); j < total_blocks && !*abort_flag; j = next_vis(j + 1), ++i) {
+        const int ks = i % F_KST, vs = i % F_VST;
         const int src = j / p.src_blocks, jb = j - src * p.src_blocks;
-        np::mbar_expect_tx(B_(FB_K + st), TILE_BYTES);
-        load_tile(sK0 + st * TILE_BYTES, &tmK.m[src], B_(FB_K + st), hkv, jb * BKV, b);
-        np::mbar_expect_tx(B_(FB_V + st), TILE_BYTES);
-        load_tile(sV0 + st * TILE_BYTES, &tmV.m[src], B_(FB_V + st), hkv, jb * BKV, b);
+        if (!np::mbar_wait(B_(FB_KE + ks), ((uint32_t)(i / F_KST) & 1u) ^ 1u, abort_flag, KID_ATTN, 1)) break;
+        np::mbar_expect_tx(B_(FB_K + ks), TILE_BYTES);
+        load_tile(sK0 + ks * TILE_BYTES, &tmK.m[src], B_(FB_K + ks), hkv, jb * BKV, b);
+        if (!np::mbar_wait(B_(FB_VE + vs), ((uint32_t)(i / F_VST) & 1u) ^ 1u, abort_flag, KID_ATTN, 10)) break;
+        np::mbar_expect_tx(B_(FB_V + vs), TILE_BYTES);
+        load_tile(sV0 + vs * TILE_BYTES, &tmV.m[src], B_(FB_V + vs), hkv, jb * BKV, b);
       }
     }
   } else if (warp == 1) {
@@ -185,31 +177,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t idesc_pv = np::make_idesc(128, 128, 1, 1, 0, 1);   // P (TMEM) x V (MN-major)
       bool ok = np::mbar_wait(B_(FB_Q), 0, abort_flag, KID_ATTN, 2);
       auto issue_qk = [&](int i) {
-        const int st = i & 1;
-        if (!np::mbar_wait(B_(FB_K + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN, 3)) return false;
+        const int st = i & 1, ks = i % F_KST;
+        if (!np::mbar_wait(B_(FB_K + ks), (uint32_t)(i / F_KST) & 1u, abort_flag, KID_ATTN, 3)) return false;
         np::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          np::tc_mma_f16(tmem + F_S + st * 128, desc_kmajor(sQ, kk), desc_kmajor(sK0 + st * TILE_BYTES, kk), idesc_qk, kk > 0);
+          np::tc_mma_f16(tmem + F_S + st * 128, desc_kmajor(sQ, kk), desc_kmajor(sK0 + ks * TILE_BYTES, kk), idesc_qk, kk > 0);
         np::tc_commit(B_(FB_S + st));
+        np::tc_commit(B_(FB_KE + ks));
         return true;
       };
-      if (ok && nvis > 0) ok = issue_qk(0);
-      for (int i = 0; i < nvis && ok && !*abort_flag; ++i) {
-        const int st = i & 1;
+      int j = next_vis(0);
+      if (ok && j < total_blocks) ok = issue_qk(0);
+      for (int i = 0; j < total_blocks && ok && !*abort_flag; ++i) {
+        const int st = i & 1, vs = i % F_VST;
         // S of the next block is computed while the softmax warps work on this one. Its S and P buffers were
         // last used for block i-1: S read before P of block i-1 arrived, P consumed by P V of block i-1 (issued).
-        if (i + 1 < nvis) ok = issue_qk(i + 1);
+        j = next_vis(j + 1);
+        if (j < total_blocks) ok = issue_qk(i + 1);
         ok = ok && np::mbar_wait(B_(FB_P), (uint32_t)i & 1u, abort_flag, KID_ATTN, 5) &&   // P ready, O rescaled
-             np::mbar_wait(B_(FB_V + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN, 4);
+             np::mbar_wait(B_(FB_V + vs), (uint32_t)(i / F_VST) & 1u, abort_flag, KID_ATTN, 4);
         if (!ok) break;
         np::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          tc_mma_f16_ts(tO, tmem + F_P + st * 64 + kk * 8, desc_mnmajor(sV0 + st * TILE_BYTES, kk), idesc_pv,
+          tc_mma_f16_ts(tO, tmem + F_P + st * 64 + kk * 8, desc_mnmajor(sV0 + vs * TILE_BYTES, kk), idesc_pv,
                         (i > 0) || (kk > 0));
         np::tc_commit(B_(FB_O));
-        np::tc_commit(B_(FB_KVE + st));
+        np::tc_commit(B_(FB_VE + vs));
       }
     }
   } else {
@@ -219,9 +214,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int q_pos = q_pos0 + r;
     float m = -INFINITY, l = 0.f;                            // running maximum (log2 domain) and row sum
     bool ok = true;
-    for (int i = 0; i < nvis; ++i) {
-      const int st = i & 1;
-      const int j = vis[i];
+    int nvis = 0;
+    for (int j = next_vis(0); j < total_blocks; j = next_vis(j + 1), ++nvis) {
+      const int i = nvis, st = i & 1;
       const int jb = j % p.src_blocks;
       const int kp0 = k_pos0(j);
       const int valid_cols = p.src_len - jb * BKV;           // columns beyond the source's length are padding
@@ -241,9 +236,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (col >= valid_cols || (p.causal && kp0 + col > q_pos)) s[e] = 0xff800000u;   // -inf
           }
         }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int e = 0; e < 64; ++e) mloc = fmaxf(mloc, __uint_as_float(s[e]));
-        mloc *= p.scale_log2;
+        for (int e = 0; e < 64; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(s[e]));
+        mloc = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       }
       xch[(st * 2 + hf) * 128 + r] = mloc;
       pair_sync(quarter);
@@ -274,17 +270,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       if (ok) {
         const float m_use = (m == -INFINITY) ? 0.f : m;
-        float rs0 = 0.f, rs1 = 0.f;
+        float rs[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[32];
 #pragma unroll
         for (int e = 0; e < 64; e += 2) {
           const float p0 = ex2(fmaf(__uint_as_float(s[e]), p.scale_log2, -m_use));
           const float p1 = ex2(fmaf(__uint_as_float(s[e + 1]), p.scale_log2, -m_use));
-          rs0 += p0;
-          rs1 += p1;
+          rs[e & 2] += p0;
+          rs[(e & 2) + 1] += p1;
           pk[e >> 1] = np::pack_bf16(p0, p1);
         }
-        l += rs0 + rs1;
+        l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
         tmem_st16(tmem + F_P + st * 64 + lane_off + hf * 32, pk);
         tmem_st16(tmem + F_P + st * 64 + lane_off + hf * 32 + 16, pk + 16);
         tmem_st_wait();
@@ -399,8 +395,7 @@ NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.n_src = a->n_src; p.src_len = a->src_len; p.src_blocks = (a->src_len + BKV - 1) / BKV;
   p.q_blk_pos = a->q_blk_pos; p.k_blk_pos = a->k_blk_pos; p.q_off = a->q_off;
-  if (p.n_src * p.src_blocks > MAX_VIS) return 1;
-  constexpr int SMEM = 5 * TILE_BYTES + 1024 + 8 * FB_COUNT + 8 + 16 + 3072 + 2 * MAX_VIS + 64;
+  constexpr int SMEM = (1 + F_KST + F_VST) * TILE_BYTES + 1024 + 8 * FB_COUNT + 8 + 16 + 3072 + 64;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -427,7 +422,6 @@ NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
 namespace {
 
 constexpr int KID_ATTN_DQ = 31, KID_ATTN_DKV = 32;
-constexpr int MAX_VIS_BWD = 4096;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct PtrList {
@@ -462,21 +456,26 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long
   if (lane == 0) delta[((size_t)b * H + h) * S + s] = v;
 }
 
-enum { QB_QDO = 0, QB_K = 1, QB_V = 3, QB_KVE = 5, QB_S = 7, QB_DP = 9, QB_DS = 10, QB_FIN = 11, QB_COUNT = 12 };
+enum { QB_QDO = 0, QB_K = 1, QB_KE = 4, QB_V = 7, QB_VE = 9, QB_S = 11, QB_DP = 13, QB_DS = 14, QB_FIN = 15, QB_COUNT = 16 };
+// K tiles live from S = Q K^T (issued one block ahead) to dQ += dS K: three of them; V tiles only feed dP: two.
+constexpr int Q_KST = 3, Q_VST = 2;
+constexpr int BWD_TILES = 7;   // seven 32 KB tiles: the dynamic shared memory must itself start on a 1024-byte boundary
 
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ TmapList tmK, const __grid_constant__ TmapList tmV, const BwdParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (np::smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sdO = base + TILE_BYTES, sK0 = sdO + TILE_BYTES, sV0 = sK0 + 2 * TILE_BYTES;
-  const uint32_t bar = sV0 + 2 * TILE_BYTES;
+  extern __shared__ __align__(1024) uint8_t smem_al[];
+  const uint32_t base = np::smem_u32(smem_al);
+  if (base & 1023u) {   // the swizzled tiles need it; nothing has been allocated or started yet
+    if (threadIdx.x == 0) np::report(NP_ERR_BAD_ARG, KID_ATTN_DQ, (int)(base & 1023u));
+    return;
+  }
+  const uint32_t sQ = base, sdO = base + TILE_BYTES, sK0 = sdO + TILE_BYTES, sV0 = sK0 + Q_KST * TILE_BYTES;
+  const uint32_t bar = sV0 + Q_VST * TILE_BYTES;
   auto B_ = [&](int i) { return bar + 8u * i; };
-  uint8_t* tail = smem_raw + (bar - np::smem_u32(smem_raw)) + 8 * QB_COUNT;
+  uint8_t* tail = smem_al + BWD_TILES * TILE_BYTES + 8 * QB_COUNT;
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
-  volatile int* nvis_s = reinterpret_cast<volatile int*>(tail + 12);
-  volatile short* vis = reinterpret_cast<volatile short*>(tail + 16);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (p.Sq + BQ - 1) / BQ;
@@ -486,20 +485,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int q_pos0 = p.q_blk_pos ? p.q_blk_pos[qb] : qb * BQ + p.q_off;
   const int total_blocks = p.n_src * p.src_blocks;
   auto k_pos0 = [&](int j) { return p.k_blk_pos ? p.k_blk_pos[j] : (j % p.src_blocks) * BKV; };
+  auto next_vis = [&](int j) {   // next KV block that causality does not hide from every row of this Q block
+    while (j < total_blocks && p.causal && k_pos0(j) > q_pos0 + BQ - 1) ++j;
+    return j;
+  };
 
   if (threadIdx.x == 0) {
-    np::mbar_init(B_(QB_QDO), 1);
-    for (int s = 0; s < 2; ++s) {
-      np::mbar_init(B_(QB_K + s), 1); np::mbar_init(B_(QB_V + s), 1); np::mbar_init(B_(QB_KVE + s), 1);
-      np::mbar_init(B_(QB_S + s), 1);
-    }
-    np::mbar_init(B_(QB_DP), 1); np::mbar_init(B_(QB_DS), 8); np::mbar_init(B_(QB_FIN), 1);
+    for (int i = 0; i < QB_COUNT; ++i) np::mbar_init(B_(i), i == QB_DS ? 8 : 1);
     *abort_flag = 0;
     np::mbar_fence_init();
-    int n = 0;
-    for (int j = 0; j < total_blocks && n < MAX_VIS; ++j)
-      if (!p.causal || k_pos0(j) <= q_pos0 + BQ - 1) vis[n++] = (short)j;
-    *nvis_s = n;
   }
   if (warp == 1) {
     np::tmem_alloc(np::smem_u32((const void*)tmem_ptr_smem), 512);
@@ -510,22 +504,22 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   np::tc_fence_after();
   const uint32_t tmem = *tmem_ptr_smem;
   const uint32_t tdP = tmem + 256, tdQ = tmem + 384;   // S buffers at columns 0 and 128
-  const int nvis = *nvis_s;
 
   if (warp == 0) {
     if (lane == 0) {
       np::mbar_expect_tx(B_(QB_QDO), 2 * TILE_BYTES);
       load_tile(sQ, &tmQ, B_(QB_QDO), h, qb * BQ, b);
       load_tile(sdO, &tmdO, B_(QB_QDO), h, qb * BQ, b);
-      for (int i = 0; i < nvis && !*abort_flag; ++i) {
-        const int st = i & 1;
-        if (!np::mbar_wait(B_(QB_KVE + st), ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag, KID_ATTN_DQ, 1)) break;
-        const int j = vis[i];
+      int i = 0;
+      for (int j = next_vis(0); j < total_blocks && !*abort_flag; j = next_vis(j + 1), ++i) {
+        const int ks = i % Q_KST, vs = i % Q_VST;
         const int src = j / p.src_blocks, jb = j - src * p.src_blocks;
-        np::mbar_expect_tx(B_(QB_K + st), TILE_BYTES);
-        load_tile(sK0 + st * TILE_BYTES, &tmK.m[src], B_(QB_K + st), hkv, jb * BKV, b);
-        np::mbar_expect_tx(B_(QB_V + st), TILE_BYTES);
-        load_tile(sV0 + st * TILE_BYTES, &tmV.m[src], B_(QB_V + st), hkv, jb * BKV, b);
+        if (!np::mbar_wait(B_(QB_KE + ks), ((uint32_t)(i / Q_KST) & 1u) ^ 1u, abort_flag, KID_ATTN_DQ, 1)) break;
+        np::mbar_expect_tx(B_(QB_K + ks), TILE_BYTES);
+        load_tile(sK0 + ks * TILE_BYTES, &tmK.m[src], B_(QB_K + ks), hkv, jb * BKV, b);
+        if (!np::mbar_wait(B_(QB_VE + vs), ((uint32_t)(i / Q_VST) & 1u) ^ 1u, abort_flag, KID_ATTN_DQ, 10)) break;
+        np::mbar_expect_tx(B_(QB_V + vs), TILE_BYTES);
+        load_tile(sV0 + vs * TILE_BYTES, &tmV.m[src], B_(QB_V + vs), hkv, jb * BKV, b);
       }
     }
   } else if (warp == 1) {
@@ -534,37 +528,40 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t idesc_mn = np::make_idesc(128, 128, 1, 1, 0, 1);   // A from TMEM, B MN-major
       bool ok = np::mbar_wait(B_(QB_QDO), 0, abort_flag, KID_ATTN_DQ, 2);
       auto issue_s = [&](int i) {
-        const int st = i & 1;
-        if (!np::mbar_wait(B_(QB_K + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN_DQ, 3)) return false;
+        const int st = i & 1, ks = i % Q_KST;
+        if (!np::mbar_wait(B_(QB_K + ks), (uint32_t)(i / Q_KST) & 1u, abort_flag, KID_ATTN_DQ, 3)) return false;
         np::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          np::tc_mma_f16(tmem + st * 128, desc_kmajor(sQ, kk), desc_kmajor(sK0 + st * TILE_BYTES, kk), idesc_kk, kk > 0);
+          np::tc_mma_f16(tmem + st * 128, desc_kmajor(sQ, kk), desc_kmajor(sK0 + ks * TILE_BYTES, kk), idesc_kk, kk > 0);
         np::tc_commit(B_(QB_S + st));
         return true;
       };
       auto issue_dp = [&](int i) {
-        const int st = i & 1;
-        if (!np::mbar_wait(B_(QB_V + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN_DQ, 4)) return false;
+        const int vs = i % Q_VST;
+        if (!np::mbar_wait(B_(QB_V + vs), (uint32_t)(i / Q_VST) & 1u, abort_flag, KID_ATTN_DQ, 4)) return false;
         np::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          np::tc_mma_f16(tdP, desc_kmajor(sdO, kk), desc_kmajor(sV0 + st * TILE_BYTES, kk), idesc_kk, kk > 0);
+          np::tc_mma_f16(tdP, desc_kmajor(sdO, kk), desc_kmajor(sV0 + vs * TILE_BYTES, kk), idesc_kk, kk > 0);
         np::tc_commit(B_(QB_DP));
+        np::tc_commit(B_(QB_VE + vs));
         return true;
       };
-      if (ok && nvis > 0) ok = issue_s(0) && issue_dp(0);
-      for (int i = 0; i < nvis && ok && !*abort_flag; ++i) {
-        const int st = i & 1;
-        if (i + 1 < nvis) ok = issue_s(i + 1);   // its buffer was read for block i-1 before dS of block i-1 arrived
+      int j = next_vis(0);
+      if (ok && j < total_blocks) ok = issue_s(0) && issue_dp(0);
+      for (int i = 0; j < total_blocks && ok && !*abort_flag; ++i) {
+        const int ks = i % Q_KST;
+        j = next_vis(j + 1);
+        if (j < total_blocks) ok = issue_s(i + 1);   // its buffer was read for block i-1 before dS of block i-1 arrived
         ok = ok && np::mbar_wait(B_(QB_DS), (uint32_t)i & 1u, abort_flag, KID_ATTN_DQ, 5);
         if (!ok) break;
         np::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          tc_mma_f16_ts(tdQ, tdP + kk * 8, desc_mnmajor(sK0 + st * TILE_BYTES, kk), idesc_mn, (i > 0) || (kk > 0));
-        np::tc_commit(B_(QB_KVE + st));
-        if (i + 1 < nvis) ok = issue_dp(i + 1);  // overwrites dS after the dQ product above has consumed it
+          tc_mma_f16_ts(tdQ, tdP + kk * 8, desc_mnmajor(sK0 + ks * TILE_BYTES, kk), idesc_mn, (i > 0) || (kk > 0));
+        np::tc_commit(B_(QB_KE + ks));
+        if (j < total_blocks) ok = issue_dp(i + 1);  // overwrites dS after the dQ product above has consumed it
       }
       np::tc_commit(B_(QB_FIN));
     }
@@ -582,9 +579,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       dlt = p.delta[idx];
     }
     bool ok = true;
-    for (int i = 0; i < nvis; ++i) {
-      const int st = i & 1;
-      const int j = vis[i];
+    int nvis = 0;
+    for (int j = next_vis(0); j < total_blocks; j = next_vis(j + 1), ++nvis) {
+      const int i = nvis, st = i & 1;
       const int jb = j % p.src_blocks;
       const int kp0 = k_pos0(j);
       const int valid_cols = p.src_len - jb * BKV;
@@ -661,25 +658,29 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
-enum { KB_KV = 0, KB_Q = 1, KB_DO = 3, KB_QE = 5, KB_DOE = 7, KB_ST = 9, KB_DPT = 10, KB_P = 11, KB_DS = 12, KB_FIN = 13,
-       KB_COUNT = 14 };
+enum { KB_KV = 0, KB_Q = 1, KB_QE = 4, KB_DO = 7, KB_DOE = 9, KB_ST = 11, KB_DPT = 12, KB_P = 13, KB_DS = 14, KB_FIN = 15,
+       KB_COUNT = 16 };
+// Q tiles live from S^T = K Q^T (issued one block ahead) to dK += dS^T Q: three of them; dO tiles are done after
+// dV += P^T dO: two.
+constexpr int K_QST = 3, K_DOST = 2;
 
-// iteration descriptor: source << 24 | head-in-group << 16 | q block
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const __grid_constant__ TmapList tmQ, const __grid_constant__ TmapList tmdO, const BwdParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (np::smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sK = base, sV = base + TILE_BYTES, sQ0 = sV + TILE_BYTES, sdO0 = sQ0 + 2 * TILE_BYTES;
-  const uint32_t bar = sdO0 + 2 * TILE_BYTES;
+  extern __shared__ __align__(1024) uint8_t smem_al[];
+  const uint32_t base = np::smem_u32(smem_al);
+  if (base & 1023u) {   // the swizzled tiles need it; nothing has been allocated or started yet
+    if (threadIdx.x == 0) np::report(NP_ERR_BAD_ARG, KID_ATTN_DKV, (int)(base & 1023u));
+    return;
+  }
+  const uint32_t sK = base, sV = base + TILE_BYTES, sQ0 = sV + TILE_BYTES, sdO0 = sQ0 + K_QST * TILE_BYTES;
+  const uint32_t bar = sdO0 + K_DOST * TILE_BYTES;
   auto B_ = [&](int i) { return bar + 8u * i; };
-  uint8_t* tail = smem_raw + (bar - np::smem_u32(smem_raw)) + 8 * KB_COUNT;
+  uint8_t* tail = smem_al + BWD_TILES * TILE_BYTES + 8 * KB_COUNT;
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
-  volatile int* nvis_s = reinterpret_cast<volatile int*>(tail + 12);
   float* s_lse = reinterpret_cast<float*>(tail + 16);          // [2][128]
   float* s_dlt = s_lse + 256;                                   // [2][128]
-  volatile int* vis = reinterpret_cast<volatile int*>(s_dlt + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int jb = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
@@ -689,22 +690,22 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     return p.q_blk_pos ? p.q_blk_pos[src * p.src_blocks + i] : i * BQ + p.q_off;
   };
 
-  if (threadIdx.x == 0) {
-    np::mbar_init(B_(KB_KV), 1);
-    for (int s = 0; s < 2; ++s) {
-      np::mbar_init(B_(KB_Q + s), 1); np::mbar_init(B_(KB_DO + s), 1);
-      np::mbar_init(B_(KB_QE + s), 1); np::mbar_init(B_(KB_DOE + s), 1);
+  // Work list, walked identically by every role: candidate c = (source, head of the group, Q block), kept when
+  // causality lets at least one row of the Q block see this KV block.
+  const int total = p.n_src * n_rep * p.src_blocks;
+  auto next_vis = [&](int c) {
+    while (c < total && p.causal) {
+      const int i = c % p.src_blocks, src = c / (p.src_blocks * n_rep);
+      if (k_pos0 <= q_pos0_of(src, i) + BQ - 1) break;
+      ++c;
     }
-    np::mbar_init(B_(KB_ST), 1); np::mbar_init(B_(KB_DPT), 1);
-    np::mbar_init(B_(KB_P), 8); np::mbar_init(B_(KB_DS), 8); np::mbar_init(B_(KB_FIN), 1);
+    return c;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < KB_COUNT; ++i) np::mbar_init(B_(i), (i == KB_P || i == KB_DS) ? 8 : 1);
     *abort_flag = 0;
     np::mbar_fence_init();
-    int n = 0;
-    for (int src = 0; src < p.n_src; ++src)
-      for (int hh = 0; hh < n_rep; ++hh)
-        for (int i = 0; i < p.src_blocks && n < MAX_VIS_BWD; ++i)
-          if (!p.causal || k_pos0 <= q_pos0_of(src, i) + BQ - 1) vis[n++] = (src << 24) | (hh << 16) | i;
-    *nvis_s = n;
   }
   if (warp == 1) {
     np::tmem_alloc(np::smem_u32((const void*)tmem_ptr_smem), 512);
@@ -715,24 +716,22 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
   np::tc_fence_after();
   const uint32_t tmem = *tmem_ptr_smem;
   const uint32_t tSt = tmem, tdPt = tmem + 128, tdV = tmem + 256, tdK = tmem + 384;
-  const int nvis = *nvis_s;
 
   if (warp == 0) {
     if (lane == 0) {
       np::mbar_expect_tx(B_(KB_KV), 2 * TILE_BYTES);
       load_tile(sK, &tmK, B_(KB_KV), hkv, jb * BKV, b);
       load_tile(sV, &tmV, B_(KB_KV), hkv, jb * BKV, b);
-      for (int i = 0; i < nvis && !*abort_flag; ++i) {
-        const int st = i & 1;
-        const uint32_t ph = ((uint32_t)(i >> 1) & 1u) ^ 1u;
-        const int d = vis[i];
-        const int src = d >> 24, h = hkv * n_rep + ((d >> 16) & 0xff), qi = d & 0xffff;
-        if (!np::mbar_wait(B_(KB_QE + st), ph, abort_flag, KID_ATTN_DKV, 1)) break;
-        np::mbar_expect_tx(B_(KB_Q + st), TILE_BYTES);
-        load_tile(sQ0 + st * TILE_BYTES, &tmQ.m[src], B_(KB_Q + st), h, qi * BQ, b);
-        if (!np::mbar_wait(B_(KB_DOE + st), ph, abort_flag, KID_ATTN_DKV, 2)) break;
-        np::mbar_expect_tx(B_(KB_DO + st), TILE_BYTES);
-        load_tile(sdO0 + st * TILE_BYTES, &tmdO.m[src], B_(KB_DO + st), h, qi * BQ, b);
+      int i = 0;
+      for (int c = next_vis(0); c < total && !*abort_flag; c = next_vis(c + 1), ++i) {
+        const int qs = i % K_QST, ds = i % K_DOST;
+        const int qi = c % p.src_blocks, h = hkv * n_rep + (c / p.src_blocks) % n_rep, src = c / (p.src_blocks * n_rep);
+        if (!np::mbar_wait(B_(KB_QE + qs), ((uint32_t)(i / K_QST) & 1u) ^ 1u, abort_flag, KID_ATTN_DKV, 1)) break;
+        np::mbar_expect_tx(B_(KB_Q + qs), TILE_BYTES);
+        load_tile(sQ0 + qs * TILE_BYTES, &tmQ.m[src], B_(KB_Q + qs), h, qi * BQ, b);
+        if (!np::mbar_wait(B_(KB_DOE + ds), ((uint32_t)(i / K_DOST) & 1u) ^ 1u, abort_flag, KID_ATTN_DKV, 2)) break;
+        np::mbar_expect_tx(B_(KB_DO + ds), TILE_BYTES);
+        load_tile(sdO0 + ds * TILE_BYTES, &tmdO.m[src], B_(KB_DO + ds), h, qi * BQ, b);
       }
     }
   } else if (warp == 1) {
@@ -741,44 +740,46 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
       const uint32_t idesc_mn = np::make_idesc(128, 128, 1, 1, 0, 1);
       bool ok = np::mbar_wait(B_(KB_KV), 0, abort_flag, KID_ATTN_DKV, 3);
       auto issue_st = [&](int i) {
-        const int st = i & 1;
-        if (!np::mbar_wait(B_(KB_Q + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN_DKV, 4)) return false;
+        const int qs = i % K_QST;
+        if (!np::mbar_wait(B_(KB_Q + qs), (uint32_t)(i / K_QST) & 1u, abort_flag, KID_ATTN_DKV, 4)) return false;
         np::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          np::tc_mma_f16(tSt, desc_kmajor(sK, kk), desc_kmajor(sQ0 + st * TILE_BYTES, kk), idesc_kk, kk > 0);
+          np::tc_mma_f16(tSt, desc_kmajor(sK, kk), desc_kmajor(sQ0 + qs * TILE_BYTES, kk), idesc_kk, kk > 0);
         np::tc_commit(B_(KB_ST));
         return true;
       };
       auto issue_dpt = [&](int i) {
-        const int st = i & 1;
-        if (!np::mbar_wait(B_(KB_DO + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN_DKV, 5)) return false;
+        const int ds = i % K_DOST;
+        if (!np::mbar_wait(B_(KB_DO + ds), (uint32_t)(i / K_DOST) & 1u, abort_flag, KID_ATTN_DKV, 5)) return false;
         np::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          np::tc_mma_f16(tdPt, desc_kmajor(sV, kk), desc_kmajor(sdO0 + st * TILE_BYTES, kk), idesc_kk, kk > 0);
+          np::tc_mma_f16(tdPt, desc_kmajor(sV, kk), desc_kmajor(sdO0 + ds * TILE_BYTES, kk), idesc_kk, kk > 0);
         np::tc_commit(B_(KB_DPT));
         return true;
       };
-      if (ok && nvis > 0) ok = issue_st(0) && issue_dpt(0);
-      for (int i = 0; i < nvis && ok && !*abort_flag; ++i) {
-        const int st = i & 1;
+      int c = next_vis(0);
+      if (ok && c < total) ok = issue_st(0) && issue_dpt(0);
+      for (int i = 0; c < total && ok && !*abort_flag; ++i) {
+        const int qs = i % K_QST, ds = i % K_DOST;
+        c = next_vis(c + 1);
         ok = np::mbar_wait(B_(KB_P), (uint32_t)i & 1u, abort_flag, KID_ATTN_DKV, 6);
         if (!ok) break;
         np::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)   // dV += P^T dO
-          tc_mma_f16_ts(tdV, tSt + kk * 8, desc_mnmajor(sdO0 + st * TILE_BYTES, kk), idesc_mn, (i > 0) || (kk > 0));
-        np::tc_commit(B_(KB_DOE + st));
-        if (i + 1 < nvis) ok = issue_st(i + 1);     // overwrites P^T after the product above consumed it
+          tc_mma_f16_ts(tdV, tSt + kk * 8, desc_mnmajor(sdO0 + ds * TILE_BYTES, kk), idesc_mn, (i > 0) || (kk > 0));
+        np::tc_commit(B_(KB_DOE + ds));
+        if (c < total) ok = issue_st(i + 1);        // overwrites P^T after the product above consumed it
         ok = ok && np::mbar_wait(B_(KB_DS), (uint32_t)i & 1u, abort_flag, KID_ATTN_DKV, 7);
         if (!ok) break;
         np::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)   // dK += dS^T Q
-          tc_mma_f16_ts(tdK, tdPt + kk * 8, desc_mnmajor(sQ0 + st * TILE_BYTES, kk), idesc_mn, (i > 0) || (kk > 0));
-        np::tc_commit(B_(KB_QE + st));
-        if (i + 1 < nvis) ok = issue_dpt(i + 1);    // overwrites dS^T after the product above consumed it
+          tc_mma_f16_ts(tdK, tdPt + kk * 8, desc_mnmajor(sQ0 + qs * TILE_BYTES, kk), idesc_mn, (i > 0) || (kk > 0));
+        np::tc_commit(B_(KB_QE + qs));
+        if (c < total) ok = issue_dpt(i + 1);       // overwrites dS^T after the product above consumed it
       }
       np::tc_commit(B_(KB_FIN));
     }
@@ -789,10 +790,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int k_pos = k_pos0 + r;
     bool ok = true;
-    for (int i = 0; i < nvis; ++i) {   // every thread runs every iteration: the named barriers need all of them
-      const int st = i & 1;
-      const int d = vis[i];
-      const int src = d >> 24, h = hkv * n_rep + ((d >> 16) & 0xff), qi = d & 0xffff;
+    int nvis = 0;
+    // every thread runs every iteration: the named barriers need all of them
+    for (int c = next_vis(0); c < total; c = next_vis(c + 1), ++nvis) {
+      const int i = nvis, st = i & 1;
+      const int qi = c % p.src_blocks, h = hkv * n_rep + (c / p.src_blocks) % n_rep, src = c / (p.src_blocks * n_rep);
       const int q_pos0 = q_pos0_of(src, qi);
       {  // stage this Q block's log-sum-exp (threads 0-127) and delta (threads 128-255), one column each
         const int qrow = qi * BQ + (t256 & 127);
@@ -943,7 +945,6 @@ NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
   }
   if (!(a->phase & 2)) return cudaGetLastError() == cudaSuccess ? 0 : 500;
   const int qblocks = (a->Sq + BQ - 1) / BQ, kblocks = (a->Sk + BKV - 1) / BKV;
-  if (a->n_src * kblocks > MAX_VIS || a->n_src * (a->Hq / a->Hkv) * qblocks > MAX_VIS_BWD) return 1;
   CUtensorMap tmQ, tmdO, tmK, tmV;
   TmapList lK, lV, lQ, ldO;
   int rc = make_tmap_4d(&tmQ, a->q, a->B, a->Sq, a->Hq, a->q_sb, a->q_ss, a->q_sh);
@@ -970,8 +971,9 @@ NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
     p.lse_src.p[s] = a->lse_src[s < a->n_src ? s : 0];
     p.delta_src.p[s] = a->delta_src[s < a->n_src ? s : 0];
   }
-  constexpr int SMEM_DQ = 6 * TILE_BYTES + 1024 + 8 * QB_COUNT + 16 + 2 * MAX_VIS + 64;
-  constexpr int SMEM_DKV = 6 * TILE_BYTES + 1024 + 8 * KB_COUNT + 16 + 2048 + 4 * MAX_VIS_BWD + 64;
+  constexpr int SMEM_DQ = BWD_TILES * TILE_BYTES + 8 * QB_COUNT + 16 + 16;
+  constexpr int SMEM_DKV = BWD_TILES * TILE_BYTES + 8 * KB_COUNT + 16 + 2048 + 16;
+  static_assert(SMEM_DKV <= 227 * 1024, "shared memory budget");
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DQ);
