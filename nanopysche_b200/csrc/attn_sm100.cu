@@ -94,42 +94,64 @@ __device__ __forceinline__ float ex2(float x) {
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int kid, int where) {
   return __all_sync(0xffffffffu, np::mbar_wait(bar, parity, abort_flag, kid, where));
 }
-// Named barrier of the two warps (64 threads) that share the rows of one TMEM lane quarter. Every softmax
+// Named barrier of the NS warps that share the rows of one TMEM lane quarter (NS threads per row, 128/NS columns each). Every softmax
 // thread reaches every such barrier in every iteration, also after a failed wait, so none is left waiting.
-__device__ __forceinline__ void pair_sync(int quarter) {
-  asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+template <int NS>
+__device__ __forceinline__ void row_sync(int quarter) {
+  asm volatile("bar.sync %0, %1;" ::"r"(1 + quarter), "n"(NS * 32) : "memory");
 }
+template <int NS>
 __device__ __forceinline__ void softmax_sync_all() {
-  asm volatile("bar.sync 5, 256;" ::: "memory");
+  asm volatile("bar.sync 5, %0;" ::"n"(NS * 128) : "memory");
+}
+// CW consecutive fp32 columns of this thread's lane into registers / CW/2 packed columns back
+template <int CW>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
+#pragma unroll
+  for (int c = 0; c < CW / 32; ++c) np::tmem_ld32(taddr + c * 32, r + c * 32);
+  np::tmem_ld_wait();
+}
+template <int NCOLS>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* r) {
+#pragma unroll
+  for (int c = 0; c < NCOLS / 16; ++c) tmem_st16(taddr + c * 16, r + c * 16);
 }
 
-constexpr int NTHREADS = 320;      // warp 0: TMA, warp 1: MMA issue, warps 2-9: softmax (two per TMEM lane quarter)
+// warp 0: TMA, warp 1: MMA issue, then 4*NS softmax warps (NS per TMEM lane quarter)
+constexpr int nthreads(int ns) { return 64 + ns * 128; }
 constexpr float RESCALE_LOG2 = 8.f;
 
 // Barrier slots of the forward kernel
-enum { FB_Q = 0, FB_K = 1, FB_KE = 3, FB_V = 5, FB_VE = 8, FB_S = 11, FB_P = 13, FB_O = 14, FB_COUNT = 15 };
-constexpr int F_KST = 2, F_VST = 3;   // K tiles are free again after Q K^T, V tiles only after P V: V gets the deeper ring
+enum { FB_Q = 0, FB_K = 1, FB_KE = 4, FB_V = 7, FB_VE = 10, FB_S = 13, FB_P = 15, FB_O = 16, FB_COUNT = 17 };
+constexpr int F_KST = 3, F_VST = 3;   // three-deep K and V rings: a TMA load has two iterations to land
 
 // Tensor memory map of the forward kernel (columns): S double buffer, O accumulator, P double buffer (bf16 pairs)
 constexpr uint32_t F_S = 0, F_O = 256, F_P = 384;
 
-__global__ void __launch_bounds__(NTHREADS, 1)
+template <int NS>
+__global__ void __launch_bounds__(nthreads(NS), 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ TmapList tmK,
                 const __grid_constant__ TmapList tmV, const FwdParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (np::smem_u32(smem_raw) + 1023u) & ~1023u;
+  extern __shared__ __align__(1024) uint8_t smem_al[];
+  const uint32_t base = np::smem_u32(smem_al);
+  if (base & 1023u) {   // the swizzled tiles need it; nothing has been allocated or started yet
+    if (threadIdx.x == 0) np::report(NP_ERR_BAD_ARG, KID_ATTN, (int)(base & 1023u));
+    return;
+  }
   const uint32_t sQ = base, sK0 = base + TILE_BYTES, sV0 = sK0 + F_KST * TILE_BYTES;
   const uint32_t bar = sV0 + F_VST * TILE_BYTES;
   auto B_ = [&](int i) { return bar + 8u * i; };
-  uint8_t* tail = smem_raw + (bar - np::smem_u32(smem_raw)) + 8 * FB_COUNT + 8;   // 16-byte aligned
+  uint8_t* tail = smem_al + (1 + F_KST + F_VST) * TILE_BYTES + 8 * FB_COUNT + 8;   // 16-byte aligned
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
-  float* xch = reinterpret_cast<float*>(tail + 16);                 // [2 iterations][2 halves][128 rows] maxima, then [2][128] sums
+  float* xch = reinterpret_cast<float*>(tail + 16);   // [2 iterations][NS][128 rows]: row maxima, at the end row sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (p.Sq + BQ - 1) / BQ;
-  const int qb = nqb - 1 - (int)blockIdx.x;  // heaviest (latest) blocks first under causal masking
-  const int h = blockIdx.y, b = blockIdx.z;
+  // grid.x runs over (head, batch), grid.y over the Q blocks from the last (most KV blocks under causal
+  // masking) to the first: CTAs are issued heaviest first across the whole grid
+  const int qb = nqb - 1 - (int)blockIdx.y;
+  const int h = blockIdx.x % p.Hq, b = blockIdx.x / p.Hq;
   const int hkv = h / (p.Hq / p.Hkv);
   const int q_pos0 = p.q_blk_pos ? p.q_blk_pos[qb] : qb * BQ + p.q_off;
   const int total_blocks = p.n_src * p.src_blocks;
@@ -141,7 +163,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < FB_COUNT; ++i) np::mbar_init(B_(i), i == FB_P ? 8 : 1);
+    for (int i = 0; i < FB_COUNT; ++i) np::mbar_init(B_(i), i == FB_P ? 4 * NS : 1);
     *abort_flag = 0;
     np::mbar_fence_init();
   }
@@ -208,7 +230,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   } else {
-    const int quarter = warp & 3, hf = (warp - 2) >> 2;     // this thread: row r, columns [64 hf, 64 hf + 64)
+    constexpr int CW = 128 / NS;
+    const int quarter = warp & 3, hf = (warp - 2) >> 2;     // this thread: row r, columns [CW hf, CW hf + CW)
     const int r = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int q_pos = q_pos0 + r;
@@ -222,29 +245,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int valid_cols = p.src_len - jb * BKV;           // columns beyond the source's length are padding
       const bool need_mask = (p.causal && kp0 + BKV - 1 > q_pos0) || valid_cols < BKV;
       ok = ok && !*abort_flag && warp_wait(B_(FB_S + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN, 7);
-      uint32_t s[64];
+      uint32_t s[CW];
       float mloc = -INFINITY;
       if (ok) {
         np::tc_fence_after();
-        np::tmem_ld32(tmem + F_S + st * 128 + lane_off + hf * 64, s);
-        np::tmem_ld32(tmem + F_S + st * 128 + lane_off + hf * 64 + 32, s + 32);
-        np::tmem_ld_wait();
+        tmem_ld_cols<CW>(tmem + F_S + st * 128 + lane_off + hf * CW, s);
         if (need_mask) {
 #pragma unroll
-          for (int e = 0; e < 64; ++e) {
-            const int col = hf * 64 + e;
+          for (int e = 0; e < CW; ++e) {
+            const int col = hf * CW + e;
             if (col >= valid_cols || (p.causal && kp0 + col > q_pos)) s[e] = 0xff800000u;   // -inf
           }
         }
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int e = 0; e < 64; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(s[e]));
+        for (int e = 0; e < CW; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(s[e]));
         mloc = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       }
-      xch[(st * 2 + hf) * 128 + r] = mloc;
-      pair_sync(quarter);
+      xch[(st * NS + hf) * 128 + r] = mloc;
+      row_sync<NS>(quarter);
       if (ok) {
-        const float mx = fmaxf(mloc, xch[(st * 2 + (hf ^ 1)) * 128 + r]);   // both threads of the row agree on it
+        float mx = mloc;   // all NS threads of the row agree on it
+#pragma unroll
+        for (int o = 0; o < NS; ++o) mx = fmaxf(mx, xch[(st * NS + o) * 128 + r]);
         // the accumulator is only rescaled when some row of the warp outgrew its reference maximum by 2^8
         const bool grow = mx > m + RESCALE_LOG2 || (m == -INFINITY && mx > -INFINITY);
         if (__any_sync(0xffffffffu, grow)) {
@@ -254,14 +277,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             ok = warp_wait(B_(FB_O), (uint32_t)(i - 1) & 1u, abort_flag, KID_ATTN, 8);   // P V of block i-1 is done
             if (ok) {
               np::tc_fence_after();
-              uint32_t t[64];
-              np::tmem_ld32(tO + lane_off + hf * 64, t);
-              np::tmem_ld32(tO + lane_off + hf * 64 + 32, t + 32);
-              np::tmem_ld_wait();
+              uint32_t t[CW];
+              tmem_ld_cols<CW>(tO + lane_off + hf * CW, t);
 #pragma unroll
-              for (int e = 0; e < 64; ++e) t[e] = __float_as_uint(__uint_as_float(t[e]) * alpha);
-#pragma unroll
-              for (int c = 0; c < 4; ++c) tmem_st16(tO + lane_off + hf * 64 + c * 16, t + c * 16);
+              for (int e = 0; e < CW; ++e) t[e] = __float_as_uint(__uint_as_float(t[e]) * alpha);
+              tmem_st_cols<CW>(tO + lane_off + hf * CW, t);
             }
           }
           l *= alpha;
@@ -271,9 +291,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok) {
         const float m_use = (m == -INFINITY) ? 0.f : m;
         float rs[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t pk[32];
+        uint32_t pk[CW / 2];
 #pragma unroll
-        for (int e = 0; e < 64; e += 2) {
+        for (int e = 0; e < CW; e += 2) {
           const float p0 = ex2(fmaf(__uint_as_float(s[e]), p.scale_log2, -m_use));
           const float p1 = ex2(fmaf(__uint_as_float(s[e + 1]), p.scale_log2, -m_use));
           rs[e & 2] += p0;
@@ -281,38 +301,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           pk[e >> 1] = np::pack_bf16(p0, p1);
         }
         l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
-        tmem_st16(tmem + F_P + st * 64 + lane_off + hf * 32, pk);
-        tmem_st16(tmem + F_P + st * 64 + lane_off + hf * 32 + 16, pk + 16);
+        tmem_st_cols<CW / 2>(tmem + F_P + st * 64 + lane_off + hf * (CW / 2), pk);
         tmem_st_wait();
         np::tc_fence_before();
         __syncwarp();
         if (lane == 0) np::mbar_arrive(B_(FB_P));
       }
     }
-    // both halves of a row hold the same maximum; their partial sums add up
-    xch[512 + hf * 128 + r] = l;
-    pair_sync(quarter);
-    const float l_tot = l + xch[512 + (hf ^ 1) * 128 + r];
+    // all threads of a row hold the same maximum; their partial sums add up
+    row_sync<NS>(quarter);   // everyone has read the last maxima: the slots can carry the sums now
+    xch[hf * 128 + r] = l;
+    row_sync<NS>(quarter);
+    float l_tot = 0.f;
+#pragma unroll
+    for (int o = 0; o < NS; ++o) l_tot += xch[o * 128 + r];
     ok = ok && !*abort_flag;
     if (nvis > 0) ok = ok && warp_wait(B_(FB_O), (uint32_t)(nvis - 1) & 1u, abort_flag, KID_ATTN, 9);
     ok = __all_sync(0xffffffffu, ok);
     const int row = qb * BQ + r;
     if (ok) {
-      uint32_t t[64];
+      uint32_t t[CW];
       if (nvis > 0) {
         np::tc_fence_after();
-        np::tmem_ld32(tO + lane_off + hf * 64, t);
-        np::tmem_ld32(tO + lane_off + hf * 64 + 32, t + 32);
-        np::tmem_ld_wait();
+        tmem_ld_cols<CW>(tO + lane_off + hf * CW, t);
       } else {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) t[e] = 0u;
+        for (int e = 0; e < CW; ++e) t[e] = 0u;
       }
       if (row < p.Sq) {
         const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-        __nv_bfloat16* dst = p.O + (size_t)b * p.o_sb + (size_t)row * p.o_ss + (size_t)h * p.o_sh + hf * 64;
+        __nv_bfloat16* dst = p.O + (size_t)b * p.o_sb + (size_t)row * p.o_ss + (size_t)h * p.o_sh + hf * CW;
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
+        for (int g = 0; g < CW / 8; ++g) {
           float f[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(t[8 * g + e]) * inv;
@@ -369,6 +389,7 @@ struct NpAttnFwdArgs {
   int B, Sq, Hq, Hkv, causal, n_src, src_len, q_off;
   float scale;
   const int* q_blk_pos; const int* k_blk_pos;
+  int split;   // unused (two softmax threads per row)
 };
 
 NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
@@ -395,15 +416,17 @@ NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.n_src = a->n_src; p.src_len = a->src_len; p.src_blocks = (a->src_len + BKV - 1) / BKV;
   p.q_blk_pos = a->q_blk_pos; p.k_blk_pos = a->k_blk_pos; p.q_off = a->q_off;
-  constexpr int SMEM = (1 + F_KST + F_VST) * TILE_BYTES + 1024 + 8 * FB_COUNT + 8 + 16 + 3072 + 64;
+  constexpr int NS = 2;   // softmax threads per row
+  constexpr int SMEM = (1 + F_KST + F_VST) * TILE_BYTES + 8 * FB_COUNT + 8 + 16 + 2 * NS * 128 * 4 + 16;
+  static_assert(SMEM <= 227 * 1024, "shared memory budget");
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return 400 + (int)e;
     attr_set = true;
   }
-  dim3 grid((a->Sq + BQ - 1) / BQ, a->Hq, a->B);
-  attn_fwd_kernel<<<grid, NTHREADS, SMEM, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
+  dim3 grid(a->Hq * a->B, (a->Sq + BQ - 1) / BQ);
+  attn_fwd_kernel<NS><<<grid, nthreads(NS), SMEM, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 500 + (int)e;
 }
@@ -461,7 +484,8 @@ enum { QB_QDO = 0, QB_K = 1, QB_KE = 4, QB_V = 7, QB_VE = 9, QB_S = 11, QB_DP = 
 constexpr int Q_KST = 3, Q_VST = 2;
 constexpr int BWD_TILES = 7;   // seven 32 KB tiles: the dynamic shared memory must itself start on a 1024-byte boundary
 
-__global__ void __launch_bounds__(NTHREADS, 1)
+template <int NS>
+__global__ void __launch_bounds__(nthreads(NS), 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ TmapList tmK, const __grid_constant__ TmapList tmV, const BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_al[];
@@ -479,8 +503,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (p.Sq + BQ - 1) / BQ;
-  const int qb = nqb - 1 - (int)blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int qb = nqb - 1 - (int)blockIdx.y;   // heaviest first across the whole grid, as in the forward
+  const int h = blockIdx.x % p.Hq, b = blockIdx.x / p.Hq;
   const int hkv = h / (p.Hq / p.Hkv);
   const int q_pos0 = p.q_blk_pos ? p.q_blk_pos[qb] : qb * BQ + p.q_off;
   const int total_blocks = p.n_src * p.src_blocks;
@@ -491,7 +515,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < QB_COUNT; ++i) np::mbar_init(B_(i), i == QB_DS ? 8 : 1);
+    for (int i = 0; i < QB_COUNT; ++i) np::mbar_init(B_(i), i == QB_DS ? 4 * NS : 1);
     *abort_flag = 0;
     np::mbar_fence_init();
   }
@@ -566,7 +590,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       np::tc_commit(B_(QB_FIN));
     }
   } else {
-    const int quarter = warp & 3, hf = (warp - 2) >> 2;     // this thread: row r, KV columns [64 hf, 64 hf + 64)
+    constexpr int CW = 128 / NS;
+    const int quarter = warp & 3, hf = (warp - 2) >> 2;     // this thread: row r, KV columns [CW hf, CW hf + CW)
     const int r = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int row = qb * BQ + r;
@@ -587,19 +612,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int valid_cols = p.src_len - jb * BKV;
       const bool need_mask = (p.causal && kp0 + BKV - 1 > q_pos0) || valid_cols < BKV;
       ok = ok && !*abort_flag && warp_wait(B_(QB_S + st), (uint32_t)(i >> 1) & 1u, abort_flag, KID_ATTN_DQ, 7);
-      float pr[64];
-      uint32_t t[64];
+      float pr[CW];
+      uint32_t t[CW];
       if (ok) {
         np::tc_fence_after();
-        np::tmem_ld32(tmem + st * 128 + lane_off + hf * 64, t);
-        np::tmem_ld32(tmem + st * 128 + lane_off + hf * 64 + 32, t + 32);
-        np::tmem_ld_wait();
+        tmem_ld_cols<CW>(tmem + st * 128 + lane_off + hf * CW, t);
 #pragma unroll
-        for (int e = 0; e < 64; ++e) pr[e] = ex2(fmaf(__uint_as_float(t[e]), p.scale_log2, -lse2));
+        for (int e = 0; e < CW; ++e) pr[e] = ex2(fmaf(__uint_as_float(t[e]), p.scale_log2, -lse2));
         if (need_mask) {
 #pragma unroll
-          for (int e = 0; e < 64; ++e) {
-            const int col = hf * 64 + e;
+          for (int e = 0; e < CW; ++e) {
+            const int col = hf * CW + e;
             if (col >= valid_cols || (p.causal && kp0 + col > q_pos)) pr[e] = 0.f;
           }
         }
@@ -607,18 +630,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       if (ok) {
         np::tc_fence_after();
-        np::tmem_ld32(tdP + lane_off + hf * 64, t);
-        np::tmem_ld32(tdP + lane_off + hf * 64 + 32, t + 32);
-        np::tmem_ld_wait();
+        tmem_ld_cols<CW>(tdP + lane_off + hf * CW, t);
       }
-      pair_sync(quarter);   // both threads of the row hold their dP values: dS may now overwrite those columns
+      row_sync<NS>(quarter);   // both threads of the row hold their dP values: dS may now overwrite those columns
       if (ok) {
-        uint32_t pk[32];
+        uint32_t pk[CW / 2];
 #pragma unroll
-        for (int e = 0; e < 64; e += 2)
+        for (int e = 0; e < CW; e += 2)
           pk[e >> 1] = np::pack_bf16(pr[e] * (__uint_as_float(t[e]) - dlt), pr[e + 1] * (__uint_as_float(t[e + 1]) - dlt));
-        tmem_st16(tdP + lane_off + hf * 32, pk);
-        tmem_st16(tdP + lane_off + hf * 32 + 16, pk + 16);
+        tmem_st_cols<CW / 2>(tdP + lane_off + hf * (CW / 2), pk);
         tmem_st_wait();
         np::tc_fence_before();
         __syncwarp();
@@ -627,20 +647,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     ok = __all_sync(0xffffffffu, ok && !*abort_flag) && warp_wait(B_(QB_FIN), 0, abort_flag, KID_ATTN_DQ, 9);
     if (ok) {   // warp-uniform: the tensor-memory loads are executed by whole warps, only the stores are guarded
-      uint32_t t[64];
+      uint32_t t[CW];
       if (nvis > 0) {
         np::tc_fence_after();
-        np::tmem_ld32(tdQ + lane_off + hf * 64, t);
-        np::tmem_ld32(tdQ + lane_off + hf * 64 + 32, t + 32);
-        np::tmem_ld_wait();
+        tmem_ld_cols<CW>(tdQ + lane_off + hf * CW, t);
       } else {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) t[e] = 0u;
+        for (int e = 0; e < CW; ++e) t[e] = 0u;
       }
       if (row < p.Sq) {
-        __nv_bfloat16* dst = p.dQ + (size_t)b * p.dq_sb + (size_t)row * p.dq_ss + (size_t)h * p.dq_sh + hf * 64;
+        __nv_bfloat16* dst = p.dQ + (size_t)b * p.dq_sb + (size_t)row * p.dq_ss + (size_t)h * p.dq_sh + hf * CW;
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
+        for (int g = 0; g < CW / 8; ++g) {
           float f[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(t[8 * g + e]) * p.scale;
@@ -664,7 +682,8 @@ enum { KB_KV = 0, KB_Q = 1, KB_QE = 4, KB_DO = 7, KB_DOE = 9, KB_ST = 11, KB_DPT
 // dV += P^T dO: two.
 constexpr int K_QST = 3, K_DOST = 2;
 
-__global__ void __launch_bounds__(NTHREADS, 1)
+template <int NS>
+__global__ void __launch_bounds__(nthreads(NS), 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const __grid_constant__ TmapList tmQ, const __grid_constant__ TmapList tmdO, const BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_al[];
@@ -683,7 +702,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
   float* s_dlt = s_lse + 256;                                   // [2][128]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jb = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  // grid.x over (kv head, batch), grid.y over KV blocks: the first KV block is seen by the most Q blocks
+  const int jb = blockIdx.y, hkv = blockIdx.x % p.Hkv, b = blockIdx.x / p.Hkv;
   const int n_rep = p.Hq / p.Hkv;
   const int k_pos0 = p.k_blk_pos ? p.k_blk_pos[jb] : jb * BKV;
   auto q_pos0_of = [&](int src, int i) {
@@ -703,7 +723,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < KB_COUNT; ++i) np::mbar_init(B_(i), (i == KB_P || i == KB_DS) ? 8 : 1);
+    for (int i = 0; i < KB_COUNT; ++i) np::mbar_init(B_(i), (i == KB_P || i == KB_DS) ? 4 * NS : 1);
     *abort_flag = 0;
     np::mbar_fence_init();
   }
@@ -784,9 +804,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
       np::tc_commit(B_(KB_FIN));
     }
   } else {
-    const int quarter = warp & 3, hf = (warp - 2) >> 2;   // this thread: KV row r, Q columns [64 hf, 64 hf + 64)
+    constexpr int CW = 128 / NS;
+    const int quarter = warp & 3, hf = (warp - 2) >> 2;   // this thread: KV row r, Q columns [CW hf, CW hf + CW)
     const int r = quarter * 32 + lane;
-    const int t256 = threadIdx.x - 64;                    // 0..255 among the softmax threads
+    const int t256 = threadIdx.x - 64;                    // index among the softmax threads
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int k_pos = k_pos0 + r;
     bool ok = true;
@@ -799,7 +820,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
       {  // stage this Q block's log-sum-exp (threads 0-127) and delta (threads 128-255), one column each
         const int qrow = qi * BQ + (t256 & 127);
         float val = (t256 < 128) ? INFINITY : 0.f;
-        if (qrow < p.src_len) {
+        if (qrow < p.src_len && t256 < 256) {
           const size_t idx = ((size_t)b * p.Hq + h) * p.src_len + qrow;
           if (t256 < 128) {
             const float l = p.lse_src.p[src][idx];
@@ -808,21 +829,19 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
             val = p.delta_src.p[src][idx];
           }
         }
-        (t256 < 128 ? s_lse : s_dlt)[st * 128 + (t256 & 127)] = val;
-        softmax_sync_all();
+        if (t256 < 256) (t256 < 128 ? s_lse : s_dlt)[st * 128 + (t256 & 127)] = val;
+        softmax_sync_all<NS>();
       }
       const bool need_mask = p.causal && k_pos0 + BKV - 1 > q_pos0;
       ok = ok && !*abort_flag && warp_wait(B_(KB_ST), (uint32_t)i & 1u, abort_flag, KID_ATTN_DKV, 8);
-      float pr[64];
-      uint32_t t[64], pk[32];
+      float pr[CW];
+      uint32_t t[CW], pk[CW / 2];
       if (ok) {
         np::tc_fence_after();
-        np::tmem_ld32(tSt + lane_off + hf * 64, t);
-        np::tmem_ld32(tSt + lane_off + hf * 64 + 32, t + 32);
-        np::tmem_ld_wait();
+        tmem_ld_cols<CW>(tSt + lane_off + hf * CW, t);
 #pragma unroll
-        for (int e = 0; e < 64; e += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(&s_lse[st * 128 + hf * 64 + e]);
+        for (int e = 0; e < CW; e += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(&s_lse[st * 128 + hf * CW + e]);
           pr[e] = ex2(fmaf(__uint_as_float(t[e]), p.scale_log2, -l4.x));
           pr[e + 1] = ex2(fmaf(__uint_as_float(t[e + 1]), p.scale_log2, -l4.y));
           pr[e + 2] = ex2(fmaf(__uint_as_float(t[e + 2]), p.scale_log2, -l4.z));
@@ -830,16 +849,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         }
         if (need_mask) {
 #pragma unroll
-          for (int e = 0; e < 64; ++e)
-            if (k_pos > q_pos0 + hf * 64 + e) pr[e] = 0.f;
+          for (int e = 0; e < CW; ++e)
+            if (k_pos > q_pos0 + hf * CW + e) pr[e] = 0.f;
         }
 #pragma unroll
-        for (int e = 0; e < 64; e += 2) pk[e >> 1] = np::pack_bf16(pr[e], pr[e + 1]);
+        for (int e = 0; e < CW; e += 2) pk[e >> 1] = np::pack_bf16(pr[e], pr[e + 1]);
       }
-      pair_sync(quarter);   // both threads of the row hold their S^T values: P^T may now overwrite those columns
+      row_sync<NS>(quarter);   // both threads of the row hold their S^T values: P^T may now overwrite those columns
       if (ok) {
-        tmem_st16(tSt + lane_off + hf * 32, pk);
-        tmem_st16(tSt + lane_off + hf * 32 + 16, pk + 16);
+        tmem_st_cols<CW / 2>(tSt + lane_off + hf * (CW / 2), pk);
         tmem_st_wait();
         np::tc_fence_before();
         __syncwarp();
@@ -848,21 +866,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
       }
       if (ok) {
         np::tc_fence_after();
-        np::tmem_ld32(tdPt + lane_off + hf * 64, t);
-        np::tmem_ld32(tdPt + lane_off + hf * 64 + 32, t + 32);
-        np::tmem_ld_wait();
+        tmem_ld_cols<CW>(tdPt + lane_off + hf * CW, t);
 #pragma unroll
-        for (int e = 0; e < 64; e += 4) {
-          const float4 d4 = *reinterpret_cast<const float4*>(&s_dlt[st * 128 + hf * 64 + e]);
+        for (int e = 0; e < CW; e += 4) {
+          const float4 d4 = *reinterpret_cast<const float4*>(&s_dlt[st * 128 + hf * CW + e]);
           pk[e >> 1] = np::pack_bf16(pr[e] * (__uint_as_float(t[e]) - d4.x), pr[e + 1] * (__uint_as_float(t[e + 1]) - d4.y));
           pk[(e >> 1) + 1] =
               np::pack_bf16(pr[e + 2] * (__uint_as_float(t[e + 2]) - d4.z), pr[e + 3] * (__uint_as_float(t[e + 3]) - d4.w));
         }
       }
-      pair_sync(quarter);   // same for dP^T -> dS^T
+      row_sync<NS>(quarter);   // same for dP^T -> dS^T
       if (ok) {
-        tmem_st16(tdPt + lane_off + hf * 32, pk);
-        tmem_st16(tdPt + lane_off + hf * 32 + 16, pk + 16);
+        tmem_st_cols<CW / 2>(tdPt + lane_off + hf * (CW / 2), pk);
         tmem_st_wait();
         np::tc_fence_before();
         __syncwarp();
@@ -873,23 +888,21 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     const int row = jb * BKV + r;
     if (ok) {   // warp-uniform; only the stores are guarded by the row bound
       np::tc_fence_after();
-      const size_t off = (size_t)b * p.dk_sb + (size_t)row * p.dk_ss + (size_t)hkv * p.dk_sh + hf * 64;
+      const size_t off = (size_t)b * p.dk_sb + (size_t)row * p.dk_ss + (size_t)hkv * p.dk_sh + hf * CW;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dst = (which ? p.dK : p.dV) + off;
         const float mul = which ? p.scale : 1.f;
-        uint32_t t[64];
+        uint32_t t[CW];
         if (nvis > 0) {
-          np::tmem_ld32((which ? tdK : tdV) + lane_off + hf * 64, t);
-          np::tmem_ld32((which ? tdK : tdV) + lane_off + hf * 64 + 32, t + 32);
-          np::tmem_ld_wait();
+          tmem_ld_cols<CW>((which ? tdK : tdV) + lane_off + hf * CW, t);
         } else {
 #pragma unroll
-          for (int e = 0; e < 64; ++e) t[e] = 0u;
+          for (int e = 0; e < CW; ++e) t[e] = 0u;
         }
         if (row < p.Sk) {
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
+          for (int g = 0; g < CW / 8; ++g) {
             float f[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(t[8 * g + e]) * mul;
@@ -930,6 +943,7 @@ struct NpAttnBwdArgs {
   float scale;
   const int* q_blk_pos_local; const int* k_blk_pos_all;         // for dQ: local Q blocks vs all KV blocks
   const int* k_blk_pos_local; const int* q_blk_pos_all;         // for dKV: local KV blocks vs all Q blocks
+  int split;                                                    // softmax threads per row: 2 (default) or 4
 };
 
 NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
@@ -976,9 +990,10 @@ NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
   static_assert(SMEM_DKV <= 227 * 1024, "shared memory budget");
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DQ);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DKV);
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DQ);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd_dq_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DQ);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd_dkv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DKV);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd_dkv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DKV);
     if (e != cudaSuccess) return 400 + (int)e;
     attr_set = true;
   }
@@ -986,12 +1001,18 @@ NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
   BwdParams pq = p;
   pq.src_blocks = kblocks; pq.src_len = a->Sk;
   pq.q_blk_pos = a->q_blk_pos_local; pq.k_blk_pos = a->k_blk_pos_all;
-  attn_bwd_dq_kernel<<<dim3(qblocks, a->Hq, a->B), NTHREADS, SMEM_DQ, stream>>>(tmQ, tmdO, lK, lV, pq);
   // dK, dV: local KV blocks against every source's Q blocks
   BwdParams pk = p;
   pk.src_blocks = qblocks; pk.src_len = a->Sq;
   pk.q_blk_pos = a->q_blk_pos_all; pk.k_blk_pos = a->k_blk_pos_local;
-  attn_bwd_dkv_kernel<<<dim3(kblocks, a->Hkv, a->B), NTHREADS, SMEM_DKV, stream>>>(tmK, tmV, lQ, ldO, pk);
+  const dim3 gq(a->Hq * a->B, qblocks), gk(a->Hkv * a->B, kblocks);
+  if (a->split == 4) {
+    attn_bwd_dq_kernel<4><<<gq, nthreads(4), SMEM_DQ, stream>>>(tmQ, tmdO, lK, lV, pq);
+    attn_bwd_dkv_kernel<4><<<gk, nthreads(4), SMEM_DKV, stream>>>(tmK, tmV, lQ, ldO, pk);
+  } else {
+    attn_bwd_dq_kernel<2><<<gq, nthreads(2), SMEM_DQ, stream>>>(tmQ, tmdO, lK, lV, pq);
+    attn_bwd_dkv_kernel<2><<<gk, nthreads(2), SMEM_DKV, stream>>>(tmK, tmV, lQ, ldO, pk);
+  }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 500 + (int)e;
 }

@@ -44,7 +44,16 @@ def prepare_training(model: nn.Module, *, tokens_per_rank: Optional[int] = None,
     rt = getattr(moes[0], "_fused_runtime", None) if moes else None
     if rt is not None:
         opt.post_step_hooks.append(rt.end_step)
+    opt.post_step_hooks.append(_cp_end_step)
     return opt, arena
+
+
+def _cp_end_step():
+    """Fold the epochs of the fused context-parallel runtimes (created lazily by the attention layers)."""
+    from .parallel.context_parallel import _FUSED_RUNTIMES
+
+    for rt in _FUSED_RUNTIMES.values():
+        rt.end_step()
 
 
 class GraphedTrainStep:

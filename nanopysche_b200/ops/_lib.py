@@ -82,6 +82,7 @@ class AttnFwdArgs(C.Structure):
         ("src_len", c_int), ("q_off", c_int),
         ("scale", c_float),
         ("q_blk_pos", c_void_p), ("k_blk_pos", c_void_p),
+        ("split", c_int),
     ]
 
 
@@ -103,6 +104,7 @@ class AttnBwdArgs(C.Structure):
         ("scale", c_float),
         ("q_blk_pos_local", c_void_p), ("k_blk_pos_all", c_void_p),
         ("k_blk_pos_local", c_void_p), ("q_blk_pos_all", c_void_p),
+        ("split", c_int),
     ]
 
 

@@ -6,17 +6,28 @@ Returns the log-sum-exp as well when asked, which the context-parallel ring uses
 results (the reference sums per-chunk softmax outputs with no LSE merge,
 distributed/context_parallel.py:307-317).
 
-Single-device attention currently goes through PyTorch SDPA (a library flash kernel on CUDA); the
-chunked LSE form below is the oracle and the CPU path for ring attention.
+On bf16 CUDA tensors with head_dim 128 attention runs on this library's tcgen05 flash kernels
+(csrc/attn_sm100.cu: forward, dQ and dK/dV kernels; scores, probabilities and the output accumulator live
+in tensor memory); other shapes and the CPU use PyTorch SDPA. The explicit-position fp32 form below is the
+oracle of the kernels and the CPU path of ring attention.
 """
 from __future__ import annotations
 
 import math
 
 import torch
+import os
+
 import torch.nn.functional as F
 
 from . import _lib
+
+# Limit of every in-kernel wait of the multi-GPU paths (default 10 s); on expiry the kernel reports through the
+# library status word and returns.
+WAIT_LIMIT_NS = int(float(os.environ.get("NPB200_WAIT_LIMIT_MS", "10000")) * 1e6)
+# Single-device attention runs on the tcgen05 flash kernels whenever they cover the case; NPB200_SDPA=1 routes it
+# through PyTorch SDPA instead.
+USE_FLASH = os.environ.get("NPB200_SDPA", "0") != "1"
 
 
 def attention_ref(q, k, v, causal=True, q_pos=None, k_pos=None, scale=None):
@@ -68,7 +79,7 @@ def flash_supported(q: torch.Tensor, k: torch.Tensor) -> bool:
             and all(s % 8 == 0 for s in q.stride()[:3]) and all(s % 8 == 0 for s in k.stride()[:3]))
 
 
-def flash_fwd(q, k_list, v_list, *, causal=True, scale=None, q_off=0, q_blk_pos=None, k_blk_pos=None):
+def flash_fwd(q, k_list, v_list, *, causal=True, scale=None, q_off=0, q_blk_pos=None, k_blk_pos=None, split=0):
     """Forward flash attention on the tcgen05 kernel. ``k_list`` / ``v_list`` are lists of equally shaped
     ``[B, Sk, Hkv, 128]`` KV sources (one entry without context parallelism; one per rank's shard - any of
     them may live in a peer's memory - with it). Returns ``(out [B,Sq,Hq,128] bf16, lse [B,Hq,Sq] fp32)``."""
@@ -77,7 +88,8 @@ def flash_fwd(q, k_list, v_list, *, causal=True, scale=None, q_off=0, q_blk_pos=
     if not isinstance(k_list, (list, tuple)):
         k_list, v_list = [k_list], [v_list]
     B, Sq, Hq, hd = q.shape
-    Sk, Hkv = k_list[0].shape[1], k_list[0].shape[2]
+    k_ref = next(t for t in k_list if isinstance(t, torch.Tensor))   # peers may be given as raw device pointers
+    Sk, Hkv = k_ref.shape[1], k_ref.shape[2]
     n = len(k_list)
     o = torch.empty((B, Sq, Hq, hd), device=q.device, dtype=torch.bfloat16)
     lse = torch.empty((B, Hq, Sq), device=q.device, dtype=torch.float32)
@@ -87,7 +99,7 @@ def flash_fwd(q, k_list, v_list, *, causal=True, scale=None, q_off=0, q_blk_pos=
     kp = (C.c_void_p * n)(*[t.data_ptr() if isinstance(t, torch.Tensor) else int(t) for t in k_list])
     vp = (C.c_void_p * n)(*[t.data_ptr() if isinstance(t, torch.Tensor) else int(t) for t in v_list])
     a.k_ptrs, a.v_ptrs = C.cast(kp, C.c_void_p), C.cast(vp, C.c_void_p)
-    a.k_sb, a.k_ss, a.k_sh = _strides3(k_list[0])
+    a.k_sb, a.k_ss, a.k_sh = _strides3(k_ref)
     a.o = o.data_ptr()
     a.o_sb, a.o_ss, a.o_sh = _strides3(o)
     a.lse = lse.data_ptr()
@@ -95,6 +107,7 @@ def flash_fwd(q, k_list, v_list, *, causal=True, scale=None, q_off=0, q_blk_pos=
     a.scale = scale or 1.0 / math.sqrt(hd)
     a.q_blk_pos = q_blk_pos.data_ptr() if q_blk_pos is not None else None
     a.k_blk_pos = k_blk_pos.data_ptr() if k_blk_pos is not None else None
+    a.split = split
     _lib.check(_lib.lib().np_attn_fwd(C.byref(a), C.c_void_p(_lib.stream())), "attn_fwd")
     return o, lse
 
@@ -106,7 +119,7 @@ def _ptr_array(items):
     return arr, C.cast(arr, C.c_void_p)
 
 
-def flash_bwd(q, k, v, o, d_o, lse, *, causal=True, scale=None, q_off=0, delta=None, sources=None, phase=3,
+def flash_bwd(q, k, v, o, d_o, lse, *, causal=True, scale=None, q_off=0, delta=None, sources=None, phase=3, split=0,
               q_blk_pos_local=None, k_blk_pos_all=None, k_blk_pos_local=None, q_blk_pos_all=None):
     """Backward of ``flash_fwd``: returns ``(dq, dk, dv)`` in bf16 with the shapes of q / k / v.
 
@@ -143,6 +156,7 @@ def flash_bwd(q, k, v, o, d_o, lse, *, causal=True, scale=None, q_off=0, delta=N
     a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.causal, a.n_src, a.q_off, a.phase = \
         B, Sq, Sk, Hq, Hkv, int(causal), len(src["k"]), q_off, phase
     a.scale = scale or 1.0 / math.sqrt(hd)
+    a.split = split
     for name, t in (("q_blk_pos_local", q_blk_pos_local), ("k_blk_pos_all", k_blk_pos_all),
                     ("k_blk_pos_local", k_blk_pos_local), ("q_blk_pos_all", q_blk_pos_all)):
         setattr(a, name, t.data_ptr() if t is not None else None)
@@ -179,6 +193,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
               attn_mask: torch.Tensor | None = None, scale: float | None = None) -> torch.Tensor:
     """``softmax(q k^T / sqrt(hd)) v`` for ``q [B,S,Hq,hd]``, ``k/v [B,Sk,Hkv,hd]`` -> ``[B,S,Hq,hd]``."""
     Hq, Hkv = q.shape[2], k.shape[2]
+    if USE_FLASH and attn_mask is None and flash_supported(q, k) and (not causal or q.shape[1] <= k.shape[1]):
+        return flash_attention(q, k, v, causal=causal, scale=scale)
     qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
     is_causal = causal and attn_mask is None and q.shape[1] == k.shape[1]
     if causal and not is_causal and attn_mask is None:

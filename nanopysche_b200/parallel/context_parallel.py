@@ -165,6 +165,9 @@ def _all_to_all_single_hp2cp(x, group):
 
 
 # ------------------------------------------------------------------ the module
+_FUSED_RUNTIMES: dict = {}   # one symmetric-memory runtime per process group, shared by all layers
+
+
 class RingAttention(nn.Module):
     """Context-parallel attention over ``group``: ring (default) or Ulysses.
 
@@ -172,11 +175,13 @@ class RingAttention(nn.Module):
     (zig-zag layout when ``use_zigzag``); the output has q's shape.
     """
 
-    def __init__(self, group=None, *, use_ulysses: bool = False, use_zigzag: bool = True):
+    def __init__(self, group=None, *, use_ulysses: bool = False, use_zigzag: bool = True, fused: bool = True):
         super().__init__()
         self.group = group
         self.use_ulysses = use_ulysses
         self.use_zigzag = use_zigzag
+        self.fused = fused          # ring attention as one kernel over the peers' memory when the case allows it
+        self._fused_rt = None
 
     @property
     def cp(self) -> int:
@@ -197,7 +202,24 @@ class RingAttention(nn.Module):
             return attn_ops.attention(q, k, v, causal=causal)
         if self.use_ulysses:
             return self._ulysses_forward(q, k, v, causal)
+        if self.fused and q.is_cuda:
+            from ..ops import cp_fused
+
+            if cp_fused.supported(q, k, self.cp, self.use_zigzag):
+                return cp_fused.cp_attention(q, k, v, self.fused_runtime(), causal=causal)
         return self._ring_forward(q, k, v, causal)
+
+    def fused_runtime(self):
+        """Symmetric-memory runtime of the fused kernels; one per context-parallel group."""
+        if self._fused_rt is None:
+            from ..ops import cp_fused
+
+            rt = _FUSED_RUNTIMES.get(id(self.group))
+            if rt is None or rt.zigzag != self.use_zigzag:
+                rt = cp_fused.CPRuntime(self.group, zigzag=self.use_zigzag)
+                _FUSED_RUNTIMES[id(self.group)] = rt
+            self._fused_rt = rt
+        return self._fused_rt
 
     # -- ring ------------------------------------------------------------------------------------
     def _ring_forward(self, q, k, v, causal: bool):

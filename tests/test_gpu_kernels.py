@@ -301,3 +301,45 @@ def test_fp8_block_gemm_grouped():
     gemm_fp8_block(xq, xs, wq, ws, out=out, mblk_group=grp.clamp_min(0), mblk_rows=rows, rows_per_group=N)
     ref = gemm_fp8_block_ref(xq, xs, wq, ws, grp, N, torch.float32)
     assert rel(out, ref) < 1e-4
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,causal", [
+    (1, 128, 128, 1, 1, False), (2, 512, 512, 4, 2, True), (1, 200, 200, 2, 2, True),
+    (1, 128, 384, 2, 1, True), (1, 384, 256, 2, 2, False), (1, 1, 300, 4, 2, True)])
+def test_flash_attention_fwd_bwd(B, Sq, Sk, Hq, Hkv, causal):
+    """tcgen05 flash kernels (forward, dQ, dK/dV) against the fp32 reference of the same op."""
+    from nanopysche_b200.ops import _lib
+    from nanopysche_b200.ops import attention as A
+
+    torch.manual_seed(0)
+    q = torch.randn(B, Sq, Hq, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(B, Sk, Hkv, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(B, Sk, Hkv, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(B, Sq, Hq, 128, device="cuda", dtype=torch.bfloat16)
+    assert A.flash_supported(q, k)
+    o, lse = A.flash_fwd(q.detach(), k.detach(), v.detach(), causal=causal, q_off=(Sk - Sq) if causal else 0)
+    A.attention(q, k, v, causal=causal).backward(g)     # the public op takes the same kernels
+    torch.cuda.synchronize()
+    _lib.check_status("flash")
+    qf, kf, vf = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    ro, rl = A.attention_ref(qf, kf, vf, causal=causal)
+    ro.backward(g.float())
+    assert (o.float() - ro).abs().max().item() < 3e-2
+    assert (lse - rl).abs().max().item() < 1e-3
+    for got, ref in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
+        assert ((got.float() - ref).abs().max() / ref.abs().max()).item() < 2e-2
+
+
+def test_flash_attention_strided_qkv_views():
+    """q / k / v as slices of one fused projection output (no copies) give the same result."""
+    from nanopysche_b200.ops import attention as A
+
+    torch.manual_seed(1)
+    B, S, Hq, Hkv = 2, 256, 4, 2
+    qkv = torch.randn(B, S, (Hq + 2 * Hkv) * 128, device="cuda", dtype=torch.bfloat16)
+    q = qkv[..., : Hq * 128].unflatten(-1, (Hq, 128))
+    k = qkv[..., Hq * 128:(Hq + Hkv) * 128].unflatten(-1, (Hkv, 128))
+    v = qkv[..., (Hq + Hkv) * 128:].unflatten(-1, (Hkv, 128))
+    o, _ = A.flash_fwd(q, k, v, causal=True)
+    o2, _ = A.flash_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal=True)
+    assert torch.equal(o, o2)

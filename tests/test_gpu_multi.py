@@ -184,3 +184,44 @@ def _tp_fused_worker(rank, world):
 def test_fused_tensor_parallel_two_gpus():
     _need2()
     assert all(run_distributed(_tp_fused_worker, 2, backend="nccl"))
+
+
+def _cp_fused_worker(rank, world):
+    import torch.distributed as dist
+
+    from nanopysche_b200.ops import _lib
+    from nanopysche_b200.ops import attention as A
+    from nanopysche_b200.parallel.context_parallel import RingAttention, shard_sequence
+
+    torch.manual_seed(0)
+    dev = torch.device("cuda", rank)
+    B, S, Hq, Hkv, hd = 1, 1024, 4, 2, 128
+    full = [torch.randn(B, S, h, hd, device=dev, dtype=torch.bfloat16) for h in (Hq, Hkv, Hkv)]
+    g_full = torch.randn(B, S, Hq, hd, device=dev, dtype=torch.bfloat16)
+    for t in full + [g_full]:
+        dist.broadcast(t, 0)
+    for causal in (True, False):
+        # oracle: plain attention over the whole sequence, fp32
+        qf, kf, vf = [t.float().requires_grad_() for t in full]
+        ro, _ = A.attention_ref(qf, kf, vf, causal=causal)
+        ro.backward(g_full.float())
+        ring = RingAttention(dist.group.WORLD, use_zigzag=True, fused=True)
+        q, k, v = [shard_sequence(t, world, rank).clone().requires_grad_() for t in full]
+        for _ in range(2):   # twice: exercises both buffer parities
+            q.grad = k.grad = v.grad = None
+            o = ring(q, k, v, causal=causal)
+            o.backward(shard_sequence(g_full, world, rank))
+        torch.cuda.synchronize()
+        _lib.check_status("cp_fused")
+        assert ring._fused_rt is not None, "the fused kernels were not used"
+        assert rel(o, shard_sequence(ro, world, rank)) < 2e-2
+        assert rel(q.grad, shard_sequence(qf.grad, world, rank)) < 3e-2
+        assert rel(k.grad, shard_sequence(kf.grad, world, rank)) < 3e-2
+        assert rel(v.grad, shard_sequence(vf.grad, world, rank)) < 3e-2
+    dist.barrier()
+    return True
+
+
+def test_fused_context_parallel_two_gpus():
+    _need2()
+    assert all(run_distributed(_cp_fused_worker, 2, backend="nccl"))
