@@ -53,6 +53,7 @@ struct FwdParams {
   __nv_bfloat16* O; long long o_sb, o_ss, o_sh;   // output strides (elements): batch, seq, head
   float* lse;                                      // [B, Hq, Sq]
   int B, Sq, Hq, Hkv, causal;
+  int lse_H;                                       // heads of the lse array (>= Hq when this launch covers a head slice)
   float scale_log2;
   int n_src;                                       // number of KV sources (1 without context parallelism)
   int src_blocks;                                  // 128-row KV blocks per source
@@ -340,7 +341,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                                         np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
         }
         if (p.lse && hf == 0)
-          p.lse[((size_t)b * p.Hq + h) * p.Sq + row] = l_tot > 0.f ? (m * 0.6931471805599453f + logf(l_tot)) : -INFINITY;
+          p.lse[((size_t)b * p.lse_H + h) * p.Sq + row] = l_tot > 0.f ? (m * 0.6931471805599453f + logf(l_tot)) : -INFINITY;
       }
     }
   }
@@ -389,7 +390,8 @@ struct NpAttnFwdArgs {
   int B, Sq, Hq, Hkv, causal, n_src, src_len, q_off;
   float scale;
   const int* q_blk_pos; const int* k_blk_pos;
-  int split;   // unused (two softmax threads per row)
+  int split;       // unused (two softmax threads per row)
+  int lse_heads;   // heads of the lse array when q / o are a head slice of larger tensors (0: Hq)
 };
 
 NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
@@ -413,6 +415,7 @@ NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
   FwdParams p{};
   p.O = (__nv_bfloat16*)a->o; p.o_sb = a->o_sb; p.o_ss = a->o_ss; p.o_sh = a->o_sh; p.lse = a->lse;
   p.B = a->B; p.Sq = a->Sq; p.Hq = a->Hq; p.Hkv = a->Hkv; p.causal = a->causal;
+  p.lse_H = a->lse_heads > 0 ? a->lse_heads : a->Hq;
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.n_src = a->n_src; p.src_len = a->src_len; p.src_blocks = (a->src_len + BKV - 1) / BKV;
   p.q_blk_pos = a->q_blk_pos; p.k_blk_pos = a->k_blk_pos; p.q_off = a->q_off;
@@ -453,6 +456,7 @@ struct PtrList {
 
 struct BwdParams {
   int B, Sq, Hq, Hkv, causal;      // Sq: rows of the (local or per-source) Q tensor
+  int lse_H;                       // heads of the lse / delta arrays (>= Hq for a head slice)
   float scale, scale_log2;
   int n_src, src_blocks, src_len;  // sources of the *looped* operand (KV for dQ, Q/dO for dKV)
   const int* q_blk_pos; const int* k_blk_pos; int q_off;
@@ -598,7 +602,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int q_pos = q_pos0 + r;
     float lse2 = INFINITY, dlt = 0.f;
     if (row < p.Sq) {
-      const size_t idx = ((size_t)b * p.Hq + h) * p.Sq + row;
+      const size_t idx = ((size_t)b * p.lse_H + h) * p.Sq + row;
       const float l = p.lse[idx];
       lse2 = (l == -INFINITY) ? INFINITY : l * LOG2E;
       dlt = p.delta[idx];
@@ -821,7 +825,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         const int qrow = qi * BQ + (t256 & 127);
         float val = (t256 < 128) ? INFINITY : 0.f;
         if (qrow < p.src_len && t256 < 256) {
-          const size_t idx = ((size_t)b * p.Hq + h) * p.src_len + qrow;
+          const size_t idx = ((size_t)b * p.lse_H + h) * p.src_len + qrow;
           if (t256 < 128) {
             const float l = p.lse_src.p[src][idx];
             val = (l == -INFINITY) ? INFINITY : l * LOG2E;
@@ -944,6 +948,7 @@ struct NpAttnBwdArgs {
   const int* q_blk_pos_local; const int* k_blk_pos_all;         // for dQ: local Q blocks vs all KV blocks
   const int* k_blk_pos_local; const int* q_blk_pos_all;         // for dKV: local KV blocks vs all Q blocks
   int split;                                                    // softmax threads per row: 2 (default) or 4
+  int lse_heads;                                                // heads of the lse / delta arrays (0: Hq)
 };
 
 NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
@@ -975,6 +980,7 @@ NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
   for (int s = a->n_src; s < MAX_SRC; ++s) { lK.m[s] = lK.m[0]; lV.m[s] = lV.m[0]; lQ.m[s] = lQ.m[0]; ldO.m[s] = ldO.m[0]; }
   BwdParams p{};
   p.B = a->B; p.Sq = a->Sq; p.Hq = a->Hq; p.Hkv = a->Hkv; p.causal = a->causal;
+  p.lse_H = a->lse_heads > 0 ? a->lse_heads : a->Hq;
   p.scale = a->scale; p.scale_log2 = a->scale * LOG2E;
   p.n_src = a->n_src; p.q_off = a->q_off;
   p.lse = a->lse; p.delta = a->delta;

@@ -51,6 +51,8 @@ struct GemmParams {
   const void* Cin;            // accumulate source (same dtype as C), rows indexed like a dense C
   long long ldcin;
   const int* epoch_base;      // optional device counter added to `epoch` (keeps epochs valid under graph replay)
+  const int* b_ready_flags;   // arrival flags of the B operand: flag i covers B rows [i * b_rows_per_flag, ...)
+  int b_rows_per_flag;
 };
 
 template <class F>
@@ -186,7 +188,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (p.mode == 1 && p.mblk_group) goff = (long long)p.mblk_group[tl.m_blk] * p.group_stride_b;
         const long long brow = n0 + (p.b_mn ? 0 : goff);
         const int bk_off = p.b_mn ? (int)goff : 0;
+        int b_flag_hi = -1;   // highest B shard this tile has already waited for (its row ranges only move up)
+        auto wait_b_rows = [&](long long r0, long long r1) -> bool {   // rows [r0, r1] of B are about to be loaded
+          if (!p.b_ready_flags) return true;
+          const int f0 = (int)(r0 / p.b_rows_per_flag), f1 = (int)(r1 / p.b_rows_per_flag);
+          for (int f = f0 > b_flag_hi ? f0 : b_flag_hi + 1; f <= f1; ++f)
+            if (!np::wait_flag_ge(p.b_ready_flags + f, epoch, p.flag_limit_ns, KID_GEMM, 110)) {
+              *abort_flag = 1;
+              return false;
+            }
+          if (f1 > b_flag_hi) b_flag_hi = f1;
+          return true;
+        };
+        if (!p.b_mn) {
+          const long long last = brow + bn_out - 1 < p.N + goff - 1 ? brow + bn_out - 1 : p.N + goff - 1;
+          if (!wait_b_rows(brow, last)) break;
+        }
         for_each_k(p, tl.g, [&](int k0) -> bool {
+          if (p.b_mn && p.b_ready_flags) {
+            const long long last = k0 + bk_off + BK - 1 < p.K + bk_off - 1 ? k0 + bk_off + BK - 1 : p.K + bk_off - 1;
+            if (!wait_b_rows(k0 + bk_off, last)) return false;
+          }
           if (!np::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, KID_GEMM, 1)) return false;
           const uint32_t sA = smem_base + stage * STAGE_BYTES;
           const uint32_t sB = sA + A_BYTES;
@@ -483,6 +505,9 @@ struct NpGemmArgs {
   int max_ctas;  // 0 = all SMs
   const void* Cin; long long ldcin;  // optional accumulate source (defaults to C when accumulate != 0)
   const int* epoch_base;             // optional device counter added to `epoch`
+  // B arriving in row shards (a sharded weight being all-gathered while the GEMM runs): the producer waits for
+  // the flag of every shard a tile touches before it loads from it
+  const int* b_ready_flags; int b_rows_per_flag;
 };
 
 template <int BN, int STAGES>
@@ -514,6 +539,7 @@ static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
   p.Cin = a.Cin ? a.Cin : (a.accumulate ? a.C : nullptr);
   p.ldcin = a.Cin ? a.ldcin : a.ldc;
   p.epoch_base = a.epoch_base;
+  p.b_ready_flags = a.b_ready_flags; p.b_rows_per_flag = a.b_rows_per_flag;
 
   constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
   static bool attr_set = false;

@@ -40,6 +40,7 @@ class GemmArgs(C.Structure):
         ("done_counters", c_void_p), ("done_expected", c_void_p), ("done_flag_ptr", c_void_p),
         ("bn", c_int), ("max_ctas", c_int),
         ("Cin", c_void_p), ("ldcin", c_ll), ("epoch_base", c_void_p),
+        ("b_ready_flags", c_void_p), ("b_rows_per_flag", c_int),
     ]
 
 
@@ -82,7 +83,7 @@ class AttnFwdArgs(C.Structure):
         ("src_len", c_int), ("q_off", c_int),
         ("scale", c_float),
         ("q_blk_pos", c_void_p), ("k_blk_pos", c_void_p),
-        ("split", c_int),
+        ("split", c_int), ("lse_heads", c_int),
     ]
 
 
@@ -104,7 +105,7 @@ class AttnBwdArgs(C.Structure):
         ("scale", c_float),
         ("q_blk_pos_local", c_void_p), ("k_blk_pos_all", c_void_p),
         ("k_blk_pos_local", c_void_p), ("q_blk_pos_all", c_void_p),
-        ("split", c_int),
+        ("split", c_int), ("lse_heads", c_int),
     ]
 
 

@@ -164,6 +164,59 @@ def flash_bwd(q, k, v, o, d_o, lse, *, causal=True, scale=None, q_off=0, delta=N
     return dq, dk, dv, delta
 
 
+def flash_fwd_raw(q_ptr, k_ptrs, v_ptrs, o_ptr, lse_ptr, *, like_q, like_k, heads, lse_heads, causal=True, scale=None,
+                  q_blk_pos=None, k_blk_pos=None):
+    """``flash_fwd`` on raw device pointers (any of them may point into a peer's memory). The tensors have the
+    shapes and strides of ``like_q`` / ``like_k`` except for the head count, which is ``heads = (Hq, Hkv)``: a launch
+    can cover a head slice of larger buffers. The output and the log-sum-exp are stored through ``o_ptr`` /
+    ``lse_ptr`` (layout of ``like_q`` and ``[B, lse_heads, Sq]``)."""
+    import ctypes as C
+
+    B, Sq, _, hd = like_q.shape
+    a = _lib.AttnFwdArgs()
+    a.q, a.o, a.lse = int(q_ptr), int(o_ptr), int(lse_ptr)
+    a.q_sb, a.q_ss, a.q_sh = _strides3(like_q)
+    a.o_sb, a.o_ss, a.o_sh = _strides3(like_q)
+    a.k_sb, a.k_ss, a.k_sh = _strides3(like_k)
+    kk, vv = _ptr_array(k_ptrs), _ptr_array(v_ptrs)
+    a.k_ptrs, a.v_ptrs = kk[1], vv[1]
+    a.B, a.Sq, a.Hq, a.Hkv, a.causal, a.n_src, a.src_len, a.q_off = \
+        B, Sq, heads[0], heads[1], int(causal), len(k_ptrs), like_k.shape[1], 0
+    a.scale = scale or 1.0 / math.sqrt(hd)
+    a.q_blk_pos = q_blk_pos.data_ptr() if q_blk_pos is not None else None
+    a.k_blk_pos = k_blk_pos.data_ptr() if k_blk_pos is not None else None
+    a.lse_heads = lse_heads
+    _lib.check(_lib.lib().np_attn_fwd(C.byref(a), C.c_void_p(_lib.stream())), "attn_fwd")
+
+
+def flash_bwd_raw(ptr, src, *, lse, delta, like_q, like_k, heads, lse_heads, causal=True, scale=None, blk_local=None,
+                  blk_all=None):
+    """dQ and dK/dV kernels on raw device pointers. ``ptr``: dict ``q, d_o, k, v, dq, dk, dv`` of the tensors this
+    launch owns (inputs of the layouts of ``like_q`` / ``like_k`` with ``heads = (Hq, Hkv)`` heads; the gradients
+    are stored through ``dq / dk / dv``); ``src``: dict of per-rank pointer lists ``k, v, q, d_o, lse, delta``."""
+    import ctypes as C
+
+    B, Sq, _, hd = like_q.shape
+    a = _lib.AttnBwdArgs()
+    a.q, a.d_o, a.k, a.v = int(ptr["q"]), int(ptr["d_o"]), int(ptr["k"]), int(ptr["v"])
+    a.dq, a.dk, a.dv = int(ptr["dq"]), int(ptr["dk"]), int(ptr["dv"])
+    a.lse, a.delta = int(lse), int(delta)
+    a.q_sb, a.q_ss, a.q_sh = _strides3(like_q)
+    a.do_sb, a.do_ss, a.do_sh = _strides3(like_q)
+    a.dq_sb, a.dq_ss, a.dq_sh = _strides3(like_q)
+    a.k_sb, a.k_ss, a.k_sh = _strides3(like_k)
+    a.dk_sb, a.dk_ss, a.dk_sh = _strides3(like_k)
+    keep = [_ptr_array(src[n]) for n in ("k", "v", "q", "d_o", "lse", "delta")]
+    a.k_src, a.v_src, a.q_src, a.do_src, a.lse_src, a.delta_src = [x[1] for x in keep]
+    a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.causal, a.n_src, a.q_off, a.phase = \
+        B, Sq, like_k.shape[1], heads[0], heads[1], int(causal), len(src["k"]), 0, 2
+    a.scale = scale or 1.0 / math.sqrt(hd)
+    a.lse_heads = lse_heads
+    a.q_blk_pos_local = a.k_blk_pos_local = blk_local.data_ptr() if blk_local is not None else None
+    a.k_blk_pos_all = a.q_blk_pos_all = blk_all.data_ptr() if blk_all is not None else None
+    _lib.check(_lib.lib().np_attn_bwd(C.byref(a), C.c_void_p(_lib.stream())), "attn_bwd")
+
+
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, causal, scale):

@@ -139,3 +139,107 @@ def supported(q: torch.Tensor, k: torch.Tensor, cp: int, zigzag: bool) -> bool:
 def cp_attention(q, k, v, rt: CPRuntime, causal: bool = True, scale: Optional[float] = None) -> torch.Tensor:
     """Attention of the local query shard over the whole (sharded) sequence; ``[B, S/cp, H, 128]`` in and out."""
     return _FusedCPAttention.apply(q, k, v, rt, causal, scale)
+
+
+# ------------------------------------------------------------------------------------------ Ulysses
+class UlyssesRuntime(CPRuntime):
+    """Ulysses attention without the four all-to-alls: rank ``r`` computes heads ``[r H/cp, (r+1) H/cp)`` for the
+    *whole* sequence by running the flash kernels once per sequence shard - Q tiles are TMA-loaded from the rank
+    that owns the shard, K/V tiles from every rank, and the output rows are stored straight into the owner's
+    buffer. The head/sequence exchange of the reference (distributed/context_parallel.py:334-375, four
+    ``all_to_all_single`` calls) happens inside the kernels' loads and stores.
+
+    Backward mirrors it: dQ rows are stored into the owner's buffer by the dQ kernel; dK/dV of shard ``s`` (my
+    head slice) are computed by the dK/dV kernel over every rank's Q/dO and stored into rank ``s``'s buffer.
+    """
+
+    def _ensure(self, q, k):
+        shape = (tuple(q.shape), tuple(k.shape))
+        if self._shape == shape:
+            return
+        assert self.heap is None, "the fused context-parallel runtime serves one (batch, sequence) shape"
+        from ..parallel.symm import SymmetricHeap
+
+        B, S, Hq, hd = q.shape
+        Hkv = k.shape[2]
+        assert Hq % self.cp == 0 and Hkv % self.cp == 0, "Ulysses needs both head counts divisible by cp"
+        qb, kb, lb = B * S * Hq * hd * 2, B * S * Hkv * hd * 2, B * Hq * S * 4
+        nbytes = 2 * (2 * qb + 2 * kb + lb) + 2 * (3 * qb + 4 * kb + 2 * lb) + (1 << 20)
+        self.heap = SymmetricHeap(nbytes, self.group, self.device)
+        h = self.heap
+        bf, f32 = torch.bfloat16, torch.float32
+        self.fwd = [dict(q=h.alloc(q.shape, bf), k=h.alloc(k.shape, bf), v=h.alloc(k.shape, bf),
+                         o=h.alloc(q.shape, bf), lse=h.alloc((B, Hq, S), f32)) for _ in range(2)]
+        self.bwd = [dict(q=h.alloc(q.shape, bf), d_o=h.alloc(q.shape, bf), k=h.alloc(k.shape, bf),
+                         v=h.alloc(k.shape, bf), lse=h.alloc((B, Hq, S), f32), delta=h.alloc((B, Hq, S), f32),
+                         dq=h.alloc(q.shape, bf), dk=h.alloc(k.shape, bf), dv=h.alloc(k.shape, bf))
+                    for _ in range(2)]
+        self._block_positions(S)
+        from ..parallel.context_parallel import local_positions
+
+        self.blk_of = [local_positions(S, self.cp, r, self.device, self.zigzag)[::128].to(torch.int32).contiguous()
+                       for r in range(self.cp)]
+        self._shape = shape
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+
+    def _head_view(self, buf: torch.Tensor, rank: int, heads_total: int):
+        """``buf`` on ``rank`` restricted to this rank's head slice: (device pointer, local head count)."""
+        hl = heads_total // self.cp
+        return self.heap.peer_ptr(buf, rank) + self.rank * hl * buf.shape[-1] * buf.element_size(), hl
+
+    def forward(self, q, k, v, causal, scale):
+        self._ensure(q, k)
+        buf = self.fwd[self._calls_f & 1]
+        self._calls_f += 1
+        buf["q"].copy_(q)
+        buf["k"].copy_(k)
+        buf["v"].copy_(v)
+        self.heap.barrier(attn_ops.WAIT_LIMIT_NS)
+        Hq, Hkv = q.shape[2], k.shape[2]
+        ks = [self._head_view(buf["k"], r, Hkv)[0] for r in self.order]
+        vs = [self._head_view(buf["v"], r, Hkv)[0] for r in self.order]
+        for s in self.order:   # one launch per sequence shard: its Q rows against the whole sequence
+            qp, hq = self._head_view(buf["q"], s, Hq)
+            op, _ = self._head_view(buf["o"], s, Hq)
+            lp = self.heap.peer_ptr(buf["lse"], s) + self.rank * hq * q.shape[1] * 4
+            attn_ops.flash_fwd_raw(qp, ks, vs, op, lp, like_q=buf["q"], like_k=buf["k"], heads=(hq, Hkv // self.cp),
+                                   lse_heads=Hq, causal=causal, scale=scale, q_blk_pos=self.blk_of[s],
+                                   k_blk_pos=self.blk_all)
+        self.heap.barrier(attn_ops.WAIT_LIMIT_NS)   # every rank's rows of my output have landed
+        return buf["o"].clone(), buf["lse"].clone()
+
+    def backward(self, q, k, v, o, d_o, lse, causal, scale):
+        buf = self.bwd[self._calls_b & 1]
+        self._calls_b += 1
+        for name, t in (("q", q), ("d_o", d_o), ("k", k), ("v", v), ("lse", lse)):
+            buf[name].copy_(t)
+        attn_ops.flash_bwd(buf["q"], buf["k"], buf["v"], o, buf["d_o"], buf["lse"], causal=causal, scale=scale,
+                           delta=buf["delta"], phase=1)
+        self.heap.barrier(attn_ops.WAIT_LIMIT_NS)
+        Hq, Hkv = q.shape[2], k.shape[2]
+        hq, hkv = Hq // self.cp, Hkv // self.cp
+        S = q.shape[1]
+        lse_off = self.rank * hq * S * 4
+        src = {n: [self._head_view(buf[n], r, Hkv if n in ("k", "v") else Hq)[0] for r in self.order]
+               for n in ("k", "v", "q", "d_o")}
+        src["lse"] = [self.heap.peer_ptr(buf["lse"], r) + lse_off for r in self.order]
+        src["delta"] = [self.heap.peer_ptr(buf["delta"], r) + lse_off for r in self.order]
+        for s in self.order:
+            ptr = {n: self._head_view(buf[n], s, Hkv if n in ("k", "v", "dk", "dv") else Hq)[0]
+                   for n in ("q", "d_o", "k", "v", "dq", "dk", "dv")}
+            attn_ops.flash_bwd_raw(ptr, src, lse=self.heap.peer_ptr(buf["lse"], s) + lse_off,
+                                   delta=self.heap.peer_ptr(buf["delta"], s) + lse_off, like_q=buf["q"],
+                                   like_k=buf["k"], heads=(hq, hkv), lse_heads=Hq, causal=causal, scale=scale,
+                                   blk_local=self.blk_of[s], blk_all=self.blk_all)
+        self.heap.barrier(attn_ops.WAIT_LIMIT_NS)
+        return buf["dq"].clone(), buf["dk"].clone(), buf["dv"].clone()
+
+
+def ulysses_attention(q, k, v, rt: UlyssesRuntime, causal: bool = True, scale: Optional[float] = None):
+    """Ulysses attention with the head/sequence exchange done by the kernels' loads and stores."""
+    return _FusedCPAttention.apply(q, k, v, rt, causal, scale)
+
+
+def ulysses_supported(q: torch.Tensor, k: torch.Tensor, cp: int, zigzag: bool) -> bool:
+    return supported(q, k, cp, zigzag) and q.shape[2] % cp == 0 and k.shape[2] % cp == 0

@@ -1,0 +1,166 @@
+"""Fully-sharded (ZeRO-3 style) linear layers with the collectives inside the GEMMs.
+
+Each rank owns ``N/n`` rows of a weight ``[N, K]``.
+
+* forward   : every rank stores its row shard into all ranks' gather buffers (one push kernel) and the tcgen05
+              GEMM ``y = x W^T`` starts right away: its TMA producer waits for the arrival flag of the shard a
+              tile's B rows belong to, so tiles of shards that have landed run while later shards are still
+              on the wire (parameter all-gather fused into the first consuming GEMM).
+* dgrad     : the shards are gathered again (the buffer is shared by all layers) and ``dx = dy W`` waits per
+              K-slice of B in the same way.
+* wgrad     : ``dW = dy^T x`` is computed for all ``N`` rows and every output row is stored straight from TMEM
+              into the owning rank's slot buffer (GEMM -> reduce-scatter); the owner sums the ``n`` partials
+              into the gradient of its shard.
+
+Replaces ``fully_shard`` (reference: distributed/fsdp.py:18-83: NCCL all-gather before every layer forward and
+backward, NCCL reduce-scatter after backward).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .attention import WAIT_LIMIT_NS
+
+
+class FSDPRuntime:
+    """Gather / slot buffers and flag tables for one shard group, shared by every sharded linear."""
+
+    def __init__(self, group, max_weight_elems: int, device=None):
+        from ..parallel.symm import SymmetricHeap
+
+        self.group = group
+        self.n = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.max_elems = max_weight_elems
+        self.heap = SymmetricHeap(3 * max_weight_elems * 2 + (1 << 20), group, self.device)
+        h = self.heap
+        self.gather = [h.alloc((max_weight_elems,), torch.bfloat16) for _ in range(2)]
+        self.slots = h.alloc((max_weight_elems,), torch.bfloat16)
+        self.ag_flags = [h.alloc((self.n,), torch.int32) for _ in range(2)]
+        self.rs_flags = h.alloc((self.n,), torch.int32)
+        self.p_slots = h.ptr_array(self.slots)
+        self.p_done_flag = torch.tensor([h.peer_ptr(self.rs_flags, s) + 4 * self.rank for s in range(self.n)],
+                                        dtype=torch.int64, device=self.device)
+        self.done_counters = torch.zeros(self.n, dtype=torch.int32, device=self.device)
+        self.ctr = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.sent = torch.ones(self.n, dtype=torch.int32, device=self.device)
+        self._calls = 0
+        self._tables: dict = {}
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def end_step(self):
+        self.heap.end_step()
+
+    @staticmethod
+    def supported(n_rows: int, world: int) -> bool:
+        return n_rows % world == 0 and (n_rows // world) % 128 == 0
+
+    def _rs_tables(self, N: int):
+        t = self._tables.get(N)
+        if t is None:
+            ns = N // self.n
+            r = torch.arange(N, device=self.device)
+            owner, local = r // ns, r % ns
+            t = dict(row_dst=(owner << 40) | (local * self.n + self.rank),
+                     mblk_owner=((torch.arange(N // 128, device=self.device) * 128) // ns).to(torch.int32),
+                     done_expected=torch.full((self.n,), ns // 128, dtype=torch.int32, device=self.device),
+                     slot_pos=torch.zeros((ns, self.n), dtype=torch.int32, device=self.device))
+            self._tables[N] = t
+        return t
+
+    # -- building blocks ---------------------------------------------------------------------------------
+    def gather_push(self, w_shard: torch.Tensor):
+        """Start the all-gather of a row-sharded weight; returns (full view [N, K], flags tensor, epoch)."""
+        ns, K = w_shard.shape
+        assert ns * self.n * K <= self.max_elems and w_shard.is_contiguous() and w_shard.dtype == torch.bfloat16
+        par = self._calls & 1
+        self._calls += 1
+        e = self.heap.next_epoch()
+        h = self.heap
+        _lib.check(_lib.lib().np_allgather_push(
+            C.c_void_p(w_shard.data_ptr()), h.host_ptr_array(self.gather[par]), C.c_longlong(ns * K * 2),
+            h.host_ptr_array(self.ag_flags[par]), C.c_void_p(self.ctr.data_ptr()), self.rank, self.n, e,
+            C.c_void_p(h.epoch_base.data_ptr()), 32, C.c_void_p(_lib.stream())), "fsdp_gather_push")
+        return self.gather[par][: ns * self.n * K].view(ns * self.n, K), self.ag_flags[par], e
+
+    def gemm_b_arriving(self, A, W_full, flags, epoch, rows_per_flag, *, b_mn: bool):
+        """``A @ W^T`` (``b_mn=False``) or ``A @ W`` (``b_mn=True``) while W's row shards are still arriving."""
+        M, K = A.shape
+        N = W_full.shape[1] if b_mn else W_full.shape[0]
+        out = torch.empty((M, N), device=A.device, dtype=torch.bfloat16)
+        g = _lib.GemmArgs()
+        g.A, g.B, g.C = A.data_ptr(), W_full.data_ptr(), out.data_ptr()
+        g.lda, g.ldb, g.ldc = A.stride(0), W_full.stride(0), N
+        g.a_rows, g.b_rows = A.shape[0], W_full.shape[0]
+        g.M, g.N, g.K = M, N, K
+        g.b_mn, g.mode, g.alpha = int(b_mn), 0, 1.0
+        g.b_ready_flags, g.b_rows_per_flag = flags.data_ptr(), rows_per_flag
+        g.epoch, g.flag_limit_ns = epoch, WAIT_LIMIT_NS
+        g.epoch_base = self.heap.epoch_base.data_ptr()
+        _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "fsdp_gemm")
+        return out
+
+    def wgrad_reduce_scatter(self, dy, x):
+        """``reduce_scatter(dy^T x)`` over the weight rows: this rank's ``[N/n, K]`` fp32 gradient shard."""
+        T, N = dy.shape
+        K = x.shape[1]
+        assert N * K <= self.max_elems
+        tb = self._rs_tables(N)
+        e = self.heap.next_epoch()
+        self.done_counters.zero_()
+        g = _lib.GemmArgs()
+        g.A, g.B = dy.data_ptr(), x.data_ptr()
+        g.lda, g.ldb, g.ldc = dy.stride(0), x.stride(0), K
+        g.a_rows, g.b_rows = T, T
+        g.M, g.N, g.K = N, K, T
+        g.a_mn, g.b_mn, g.mode, g.alpha = 1, 1, 0, 1.0
+        g.row_dst, g.peer_base = tb["row_dst"].data_ptr(), self.p_slots.data_ptr()
+        g.mblk_flag = tb["mblk_owner"].data_ptr()
+        g.done_counters, g.done_expected = self.done_counters.data_ptr(), tb["done_expected"].data_ptr()
+        g.done_flag_ptr, g.epoch = self.p_done_flag.data_ptr(), e
+        g.epoch_base = self.heap.epoch_base.data_ptr()
+        _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "fsdp_wgrad_rs")
+        ns = N // self.n
+        out = torch.empty((ns, K), device=dy.device, dtype=torch.bfloat16)
+        c = _lib.CombineArgs()
+        c.rows, c.slot_pos, c.out = self.slots.data_ptr(), tb["slot_pos"].data_ptr(), out.data_ptr()
+        c.T, c.K, c.D, c.E = ns, self.n, K, 1
+        c.flags, c.sent_to_peer = self.rs_flags.data_ptr(), self.sent.data_ptr()
+        c.n_ranks, c.epoch, c.limit_ns = self.n, e, WAIT_LIMIT_NS
+        c.epoch_base = self.heap.epoch_base.data_ptr()
+        _lib.check(_lib.lib().np_ep_combine(C.byref(c), C.c_void_p(_lib.stream())), "fsdp_reduce")
+        return out
+
+
+class _ShardedLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_shard, rt: FSDPRuntime):
+        x2 = x.reshape(-1, x.shape[-1])
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        full, flags, e = rt.gather_push(w_shard)
+        y = rt.gemm_b_arriving(x2, full, flags, e, w_shard.shape[0], b_mn=False)
+        ctx.save_for_backward(x2, w_shard)
+        ctx.rt, ctx.x_shape = rt, x.shape
+        return y.view(*x.shape[:-1], full.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_shard = ctx.saved_tensors
+        rt = ctx.rt
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+        full, flags, e = rt.gather_push(w_shard)   # the parameters are gathered again, not kept
+        dx = rt.gemm_b_arriving(dy2, full, flags, e, w_shard.shape[0], b_mn=True)
+        dw = rt.wgrad_reduce_scatter(dy2, x2)
+        return dx.view(ctx.x_shape), dw.to(w_shard.dtype), None
+
+
+def sharded_linear(x: torch.Tensor, w_shard: torch.Tensor, rt: FSDPRuntime) -> torch.Tensor:
+    """``x @ all_gather(w_shard)^T`` with the all-gather inside the GEMM; gradients arrive reduce-scattered."""
+    return _ShardedLinear.apply(x, w_shard, rt)

@@ -201,6 +201,11 @@ class RingAttention(nn.Module):
         if self.cp <= 1:
             return attn_ops.attention(q, k, v, causal=causal)
         if self.use_ulysses:
+            if self.fused and q.is_cuda:
+                from ..ops import cp_fused
+
+                if cp_fused.ulysses_supported(q, k, self.cp, self.use_zigzag):
+                    return cp_fused.ulysses_attention(q, k, v, self.fused_runtime(), causal=causal)
             return self._ulysses_forward(q, k, v, causal)
         if self.fused and q.is_cuda:
             from ..ops import cp_fused
@@ -214,10 +219,12 @@ class RingAttention(nn.Module):
         if self._fused_rt is None:
             from ..ops import cp_fused
 
-            rt = _FUSED_RUNTIMES.get(id(self.group))
-            if rt is None or rt.zigzag != self.use_zigzag:
-                rt = cp_fused.CPRuntime(self.group, zigzag=self.use_zigzag)
-                _FUSED_RUNTIMES[id(self.group)] = rt
+            key = (id(self.group), self.use_ulysses, self.use_zigzag)
+            rt = _FUSED_RUNTIMES.get(key)
+            if rt is None:
+                cls = cp_fused.UlyssesRuntime if self.use_ulysses else cp_fused.CPRuntime
+                rt = cls(self.group, zigzag=self.use_zigzag)
+                _FUSED_RUNTIMES[key] = rt
             self._fused_rt = rt
         return self._fused_rt
 

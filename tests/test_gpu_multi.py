@@ -200,12 +200,12 @@ def _cp_fused_worker(rank, world):
     g_full = torch.randn(B, S, Hq, hd, device=dev, dtype=torch.bfloat16)
     for t in full + [g_full]:
         dist.broadcast(t, 0)
-    for causal in (True, False):
+    for causal, ulysses in ((True, False), (False, False), (True, True), (False, True)):
         # oracle: plain attention over the whole sequence, fp32
         qf, kf, vf = [t.float().requires_grad_() for t in full]
         ro, _ = A.attention_ref(qf, kf, vf, causal=causal)
         ro.backward(g_full.float())
-        ring = RingAttention(dist.group.WORLD, use_zigzag=True, fused=True)
+        ring = RingAttention(dist.group.WORLD, use_ulysses=ulysses, use_zigzag=True, fused=True)
         q, k, v = [shard_sequence(t, world, rank).clone().requires_grad_() for t in full]
         for _ in range(2):   # twice: exercises both buffer parities
             q.grad = k.grad = v.grad = None
