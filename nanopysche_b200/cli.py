@@ -58,6 +58,8 @@ def build_parser() -> argparse.ArgumentParser:
     common.add_argument("--moe-keep-dense-ffn", action="store_true")
     common.add_argument("--tp-size", type=int, default=1)
     common.add_argument("--pp-size", type=int, default=1)
+    common.add_argument("--pp-schedule", default="1F1B", help="GPipe | 1F1B | ZBVZeroBubble | Interleaved1F1B | ...")
+    common.add_argument("--pp-microbatches", type=int, default=0, help="microbatches per step (0: one per PP rank)")
     common.add_argument("--cp-size", type=int, default=1)
     common.add_argument("--ep-size", type=int, default=1)
     common.add_argument("--fsdp", action="store_true")
@@ -216,6 +218,10 @@ def _build_optimizer_and_scheduler(model, args, tokens_per_rank: int, max_steps:
     from .engine import prepare_training
     from .train.scheduler import CosineWithWarmup
 
+    if getattr(model, "_pp_enabled", False):
+        # a pipeline stage clips by the norm over all stages (trainer), so it takes the plain optimizer
+        opt = torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.1, betas=(0.9, 0.95))
+        return opt, CosineWithWarmup(opt, warmup_steps=min(10, max(max_steps // 10, 1)), max_steps=max_steps)
     opt, arena = prepare_training(model, tokens_per_rank=tokens_per_rank, lr=args.lr, weight_decay=0.1,
                                   betas=(0.9, 0.95))
     sched = CosineWithWarmup(opt, warmup_steps=min(10, max(max_steps // 10, 1)), max_steps=max_steps)
@@ -248,7 +254,8 @@ def cmd_train(args) -> int:
     tc = TrainingConfig(global_batch_size=gbs, micro_batch_size=args.batch_size, sequence_length=args.seq_len,
                         learning_rate=args.lr, max_steps=args.max_steps, dtype=torch.bfloat16, save_dir=args.save_dir,
                         save_interval=args.save_interval, log_interval=args.log_interval, dp_world_size=dp,
-                        vocab_size=vocab, cp_size=args.cp_size)
+                        vocab_size=vocab, cp_size=args.cp_size, pp_schedule=args.pp_schedule,
+                        pp_microbatches=args.pp_microbatches)
     ckpt = DistributedCheckpointer(CheckpointConfig(save_dir=args.save_dir, save_interval=args.save_interval or 10**9))
     callbacks = [SpeedMonitorCallback(device=device), StabilityMonitorCallback(), ConsoleLoggerCallback(log_interval=1)]
     if device.type == "cuda":

@@ -52,6 +52,8 @@ class TrainingConfig:
     enable_gradient_compression: bool = False
     vocab_size: int = 32000
     cp_size: int = 1
+    pp_schedule: str = "1F1B"          # pipeline schedule when the model is a pipeline stage
+    pp_microbatches: int = 0           # 0: one microbatch per pipeline rank
 
     @property
     def tokens_per_micro_step(self) -> int:
@@ -114,6 +116,7 @@ class Trainer:
             p = next(self.model.parameters(), None)
             self.device = p.device if p is not None else torch.device("cpu")
         self._arena_opt = type(self.optimizer).__name__ == "ArenaAdamW"
+        self._pp_schedule = None       # built on the first step when the model is one stage of a pipeline
 
     @property
     def tokens_per_step(self) -> int:
@@ -212,7 +215,11 @@ class Trainer:
             self._sync_replicated_grads()
             if c.max_grad_norm and c.max_grad_norm > 0:
                 params = [p for p in self.model.parameters() if p.grad is not None]
-                if params:
+                if getattr(self.model, "_pp_enabled", False):
+                    from ..parallel.pipeline_runtime import clip_grad_norm_pp
+
+                    grad_norm = clip_grad_norm_pp(params, c.max_grad_norm, getattr(self.model, "_pp_group", None))
+                elif params:
                     grad_norm = torch.nn.utils.clip_grad_norm_(params, c.max_grad_norm)
             self.optimizer.step()
         if self.scheduler is not None:
@@ -251,7 +258,46 @@ class Trainer:
             if hasattr(m, "post_batch") and hasattr(m, "score_bias"):
                 m.post_batch()
 
+    def _pipeline_step(self, batches):
+        """One optimizer step of a pipeline stage: every batch runs through this rank's action list of the
+        configured schedule (activations and gradients travel point to point); the loss is computed on the
+        last stage and broadcast so that every rank logs the same value."""
+        from ..parallel.pipeline_runtime import PipelineParallelConfig, PipelineSchedule, PipelineScheduleType
+
+        c = self.config
+        group = self.model._pp_group
+        pp = dist.get_world_size(group)
+        if self._pp_schedule is None:
+            m = c.pp_microbatches or pp
+            assert c.micro_batch_size % m == 0, "micro_batch_size must be a multiple of the pipeline microbatch count"
+            cfg = PipelineParallelConfig(degree=pp, schedule=PipelineScheduleType(c.pp_schedule), num_microbatches=m)
+            assert cfg.stages_per_rank() == 1, \
+                "the trainer drives one stage per rank (GPipe, 1F1B); schedules with several stages per rank take " \
+                "split_model() + PipelineSchedule directly"
+            d_model = self.model.d_model
+            dtype = next(self.model.parameters()).dtype
+            self._pp_schedule = PipelineSchedule([self.model], group, cfg, num_microbatches=m,
+                                                 hidden_shape=(c.micro_batch_size // m, c.sequence_length, d_model),
+                                                 hidden_dtype=dtype)
+        self.model.train()
+        total = torch.zeros((), device=self.device)
+        for input_ids, labels in batches:
+            input_ids = input_ids.to(self.device, non_blocking=True)
+            labels = labels.to(self.device, non_blocking=True)
+            loss = self._pp_schedule.step(input_ids, target=labels)
+            if loss is not None:
+                total += loss.detach().float()
+        total /= len(batches)
+        if len(batches) > 1:
+            for p in self.model.parameters():
+                if p.grad is not None:
+                    p.grad.div_(len(batches))
+        dist.broadcast(total, dist.get_global_rank(group, pp - 1), group=group)
+        return total
+
     def _train_step(self, batches):
+        if getattr(self.model, "_pp_enabled", False) and dist.is_initialized():
+            return self._pipeline_step(batches)
         c = self.config
         accum = len(batches)
         total = None

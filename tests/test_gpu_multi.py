@@ -225,3 +225,44 @@ def _cp_fused_worker(rank, world):
 def test_fused_context_parallel_two_gpus():
     _need2()
     assert all(run_distributed(_cp_fused_worker, 2, backend="nccl"))
+
+
+def _fsdp_fused_worker(rank, world):
+    import torch.distributed as dist
+
+    from nanopysche_b200.ops import _lib
+    from nanopysche_b200.ops.fsdp_fused import FSDPRuntime, sharded_linear
+
+    torch.manual_seed(0)
+    dev = torch.device("cuda", rank)
+    T, K, N = 512, 1024, 1536
+    assert FSDPRuntime.supported(N, world)
+    w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
+    dist.broadcast(w, 0)
+    torch.manual_seed(100 + rank)                       # every rank has its own batch (data parallel)
+    x = torch.randn(T, K, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(T, N, device=dev, dtype=torch.bfloat16)
+    rt = FSDPRuntime(dist.group.WORLD, max_weight_elems=N * K)
+    ns = N // world
+    w_shard = w[rank * ns:(rank + 1) * ns].clone().requires_grad_()
+    for _ in range(2):                                   # both buffer parities
+        x.grad = w_shard.grad = None
+        y = sharded_linear(x, w_shard, rt)
+        y.backward(g)
+    torch.cuda.synchronize()
+    _lib.check_status("fsdp_fused")
+    xf, wf = x.detach().float().requires_grad_(), w.float().requires_grad_()
+    ref = xf @ wf.t()
+    ref.backward(g.float())
+    dw_sum = wf.grad.clone()
+    dist.all_reduce(dw_sum)                              # the reduce-scatter sums over the ranks' batches
+    assert rel(y, ref) < 1e-2
+    assert rel(x.grad, xf.grad) < 1e-2
+    assert rel(w_shard.grad, dw_sum[rank * ns:(rank + 1) * ns]) < 2e-2
+    dist.barrier()
+    return True
+
+
+def test_fused_fully_sharded_linear_two_gpus():
+    _need2()
+    assert all(run_distributed(_fsdp_fused_worker, 2, backend="nccl"))
