@@ -144,6 +144,7 @@ def run_ours(args, rank, local, world):
 
     from nanopysche_b200.engine import GraphedTrainStep
 
+    eager_step = train_step
     graphed = None
     if not args.no_graph:
         # the whole step (forward + backward + clip + AdamW) replayed as one CUDA graph
@@ -192,6 +193,35 @@ def run_ours(args, rank, local, world):
     }
     if rank == 0:
         print(json.dumps(res), flush=True)
+    if args.kernel_table:
+        kernel_table(eager_step, devb, args.kernel_table, rank, world)
+
+
+def kernel_table(step_fn, batches, path, rank, world):
+    """Per-kernel device time of two eagerly launched steps (torch.profiler / CUPTI, outside the timed region):
+    rank 0 writes ``name, launches, total_us, avg_us`` sorted by total time, plus the sum, to ``path``. Time a
+    kernel spends spinning on a peer's flag is inside its duration, so comparing the table at N=1 and N>1 shows
+    where communication is exposed."""
+    from torch.profiler import ProfilerActivity, profile
+
+    for i in range(2):
+        step_fn(batches[i % len(batches)])
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for i in range(2):
+            step_fn(batches[i % len(batches)])
+        torch.cuda.synchronize()
+    rows = [(e.key, e.count, e.device_time_total) for e in prof.key_averages() if e.device_time_total > 0]
+    rows.sort(key=lambda r: -r[2])
+    if rank == 0:
+        total = sum(r[2] for r in rows)
+        with open(path, "w") as f:
+            f.write(f"# world={world} steps=2 sum_device_time_us={total:.0f} per_step_us={total / 2:.0f}\n")
+            f.write("name\tlaunches\ttotal_us\tavg_us\n")
+            for name, n, t in rows:
+                f.write(f"{name[:110]}\t{n}\t{t:.0f}\t{t / n:.1f}\n")
 
 
 def run_reference(args, rank, local, world):
@@ -287,6 +317,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a graph")
+    ap.add_argument("--kernel-table", default="", help="after the timed runs, write a per-kernel device-time table here")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device visible"}))

@@ -40,6 +40,10 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
   float2 a = np::unpack_bf16(u.x), b = np::unpack_bf16(u.y), c = np::unpack_bf16(u.z), d = np::unpack_bf16(u.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
 }
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  float2 a = np::unpack_bf16(u.x), b = np::unpack_bf16(u.y), c = np::unpack_bf16(u.z), d = np::unpack_bf16(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
 __device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
   *reinterpret_cast<uint4*>(p) = make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]),
                                             np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
@@ -119,6 +123,19 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
   for (int i = 0; i < MAXV; ++i)
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+  // The next row's loads are issued before this row's block-wide reduction, so their latency overlaps it.
+  uint4 gq[MAXV], xq[MAXV];
+  auto fetch = [&](int r) {
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = threadIdx.x + i * NT;
+      if (r < rows && c < nvec) {
+        gq[i] = *reinterpret_cast<const uint4*>(dy + (size_t)r * cols + c * 8);
+        xq[i] = *reinterpret_cast<const uint4*>(x + (size_t)r * cols + c * 8);
+      }
+    }
+  };
+  fetch(blockIdx.x);
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     const float rs = rstd[r];
     float g[MAXV][8], xh[MAXV][8];
@@ -127,8 +144,15 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
     for (int i = 0; i < MAXV; ++i) {
       const int c = threadIdx.x + i * NT;
       if (c < nvec) {
-        load8(dy + (size_t)r * cols + c * 8, g[i]);
-        load8(x + (size_t)r * cols + c * 8, xh[i]);
+        unpack8(gq[i], g[i]);
+        unpack8(xq[i], xh[i]);
+      }
+    }
+    fetch(r + gridDim.x);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = threadIdx.x + i * NT;
+      if (c < nvec) {
         const float4 w0 = *reinterpret_cast<const float4*>(w + c * 8);
         const float4 w1 = *reinterpret_cast<const float4*>(w + c * 8 + 4);
         const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
@@ -141,6 +165,14 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
         }
       }
     }
+    uint4 rq[MAXV];   // residual gradient of this row, in flight during the reduction
+    if (dres) {
+#pragma unroll
+      for (int i = 0; i < MAXV; ++i) {
+        const int c = threadIdx.x + i * NT;
+        if (c < nvec) rq[i] = *reinterpret_cast<const uint4*>(dres + (size_t)r * cols + c * 8);
+      }
+    }
     dot = block_sum(dot, red) / (float)cols;
 #pragma unroll
     for (int i = 0; i < MAXV; ++i) {
@@ -151,7 +183,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
         for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - xh[i][j] * dot);
         if (dres) {
           float t[8];
-          load8(dres + (size_t)r * cols + c * 8, t);
+          unpack8(rq[i], t);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += t[j];
         }
@@ -170,14 +202,31 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
   }
 }
 
-// out[c] (+)= sum_p partial[p, c]
-__global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int parts,
-                              int cols, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
-  float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += partial[(size_t)p * cols + c];
-  out[c] = accumulate ? out[c] + s : s;
+// out[c] (+)= sum_p partial[p, c] with 8 row lanes per 32-column strip (block 32 x 8) and four loads in flight per
+// thread: the partial matrix is a few hundred rows tall, so one thread per column would be a serial chain of
+// dependent loads.
+__global__ void __launch_bounds__(256) colsum_tall_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                                          int parts, int cols, int accumulate) {
+  __shared__ float red[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
+  float a4[4] = {0.f, 0.f, 0.f, 0.f};
+  if (c < cols) {
+    int p = ty;
+    for (; p + 24 < parts; p += 32) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) a4[u] += partial[(size_t)(p + 8 * u) * cols + c];
+    }
+    for (; p < parts; p += 8) a4[0] += partial[(size_t)p * cols + c];
+  }
+  red[ty][tx] = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+  __syncthreads();
+  if (ty == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += red[i][tx];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 
 // ------------------------------------------------------------------ SwiGLU / GeGLU
@@ -290,43 +339,63 @@ struct HeadSrc {
   long long row_stride, head_stride;
   int heads;
 };
-__global__ void qkv_rope_kernel(HeadSrc s0, HeadSrc s1, HeadSrc s2, __nv_bfloat16* __restrict__ out,
-                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                const int* __restrict__ pos_ids, long long T, int S, int pos_off, int hd, int rot,
-                                int rot_heads, float sign) {
+// One CTA per token; a thread takes a (head, 8-wide slice of the lower half) pair and produces both halves of the
+// rotation from two 16-byte loads, so every input element is read once. Slices outside the rotated range and the
+// V heads are copied.
+__global__ void __launch_bounds__(256) qkv_rope_kernel(HeadSrc s0, HeadSrc s1, HeadSrc s2,
+                                                       __nv_bfloat16* __restrict__ out,
+                                                       const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                       const int* __restrict__ pos_ids, long long T, int S, int pos_off,
+                                                       int hd, int rot, int rot_heads, float sign) {
   const int H = s0.heads + s1.heads + s2.heads;
   const int half = rot >> 1;
-  const int vec_per_head = hd >> 3;
-  const long long total = T * H * vec_per_head;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int v = (int)(i % vec_per_head);
-    const long long th = i / vec_per_head;
-    const int hh = (int)(th % H);
-    const long long t = th / H;
-    const int d0 = v * 8;
-    const __nv_bfloat16* src;
-    if (hh < s0.heads) src = s0.p + t * s0.row_stride + (long long)hh * s0.head_stride;
-    else if (hh < s0.heads + s1.heads) src = s1.p + t * s1.row_stride + (long long)(hh - s0.heads) * s1.head_stride;
-    else src = s2.p + t * s2.row_stride + (long long)(hh - s0.heads - s1.heads) * s2.head_stride;
-    __nv_bfloat16* dst = out + (t * H + hh) * (long long)hd;
-    float a[8];
-    load8(src + d0, a);
-    if (hh < rot_heads && d0 < rot) {
-      const int pos = pos_ids ? pos_ids[t] : (int)(t % S) + pos_off;
-      const bool lo = d0 < half;
-      float b[8], o[8];
-      load8(src + (lo ? d0 + half : d0 - half), b);
-      const int f0 = lo ? d0 : d0 - half;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float c = cos_t[(size_t)pos * half + f0 + j];
-        const float sn = sin_t[(size_t)pos * half + f0 + j] * sign;
-        o[j] = lo ? (a[j] * c - b[j] * sn) : (a[j] * c + b[j] * sn);
+  const int hv = half >> 3;                    // 8-wide slices in one half of the rotated range
+  const int cv = (hd - rot) >> 3;              // slices of a rotated head that are only copied
+  const int per_rot = hv + cv, per_plain = hd >> 3;
+  const int items = rot_heads * per_rot + (H - rot_heads) * per_plain;
+  for (long long t = blockIdx.x; t < T; t += gridDim.x) {
+    const int pos = pos_ids ? pos_ids[t] : (int)(t % S) + pos_off;
+    for (int it = threadIdx.x; it < items; it += blockDim.x) {
+      int hh, v;
+      bool rotate;
+      if (it < rot_heads * per_rot) {
+        hh = it / per_rot;
+        v = it - hh * per_rot;
+        rotate = v < hv;
+      } else {
+        const int r = it - rot_heads * per_rot;
+        hh = rot_heads + r / per_plain;
+        v = r % per_plain;
+        rotate = false;
       }
-      store8(dst + d0, o);
-    } else {
-      store8(dst + d0, a);
+      const __nv_bfloat16* src;
+      if (hh < s0.heads) src = s0.p + t * s0.row_stride + (long long)hh * s0.head_stride;
+      else if (hh < s0.heads + s1.heads) src = s1.p + t * s1.row_stride + (long long)(hh - s0.heads) * s1.head_stride;
+      else src = s2.p + t * s2.row_stride + (long long)(hh - s0.heads - s1.heads) * s2.head_stride;
+      __nv_bfloat16* dst = out + (t * H + hh) * (long long)hd;
+      if (rotate) {
+        const int d0 = v * 8;
+        float a[8], b[8], lo[8], hi[8];
+        load8(src + d0, a);
+        load8(src + d0 + half, b);
+        const float4 c0 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + d0);
+        const float4 c1 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + d0 + 4);
+        const float4 n0 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + d0);
+        const float4 n1 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + d0 + 4);
+        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float sn[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float sj = sn[j] * sign;
+          lo[j] = a[j] * c[j] - b[j] * sj;
+          hi[j] = b[j] * c[j] + a[j] * sj;
+        }
+        store8(dst + d0, lo);
+        store8(dst + d0 + half, hi);
+      } else {
+        const int d0 = (it < rot_heads * per_rot) ? rot + (v - hv) * 8 : v * 8;
+        *reinterpret_cast<uint4*>(dst + d0) = *reinterpret_cast<const uint4*>(src + d0);
+      }
     }
   }
 }
@@ -551,6 +620,19 @@ NP_API int np_rmsnorm_fwd(const void* x, const void* res, const float* w, void* 
   CHECK_LAUNCH();
 }
 
+// The backward kernel followed by the column sum of its partials.
+static void launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* dres,
+                               void* dx, float* dw, float* scratch, int rows, int cols, int accumulate_dw, int grid,
+                               cudaStream_t s) {
+#define RB(V) rmsnorm_bwd_kernel<V><<<grid, NT, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, \
+                                                       (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, rows, cols)
+  if (cols <= NT * 8) RB(1);
+  else if (cols <= NT * 16) RB(2);
+  else RB(4);
+#undef RB
+  colsum_tall_kernel<<<(cols + 31) / 32, 256, 0, s>>>(scratch, dw, grid, cols, accumulate_dw);
+}
+
 // Number of partial rows np_rmsnorm_bwd writes into its scratch for a given row count.
 NP_API int np_rmsnorm_bwd_parts(int rows) {
   const int cap = 148 * 2;
@@ -564,14 +646,7 @@ NP_API int np_rmsnorm_bwd(const void* dy, const void* x, const float* w, const f
   if (cols % 8 || cols > NT * 8 * 4) return 1;
   if (rows <= 0) return 0;
   const int grid = np_rmsnorm_bwd_parts(rows);
-  cudaStream_t s = (cudaStream_t)stream;
-#define RB(V) rmsnorm_bwd_kernel<V><<<grid, NT, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, \
-                                                       (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, rows, cols)
-  if (cols <= NT * 8) RB(1);
-  else if (cols <= NT * 16) RB(2);
-  else RB(4);
-#undef RB
-  colsum_kernel<<<(cols + 255) / 256, 256, 0, s>>>(scratch, dw, grid, cols, accumulate_dw);
+  launch_rmsnorm_bwd(dy, x, w, rstd, dres, dx, dw, scratch, rows, cols, accumulate_dw, grid, (cudaStream_t)stream);
   CHECK_LAUNCH();
 }
 
@@ -610,7 +685,7 @@ NP_API int np_qkv_rope(const void* p0, long long rs0, long long hs0, int h0, con
   if (T <= 0) return 0;
   HeadSrc s0{(const __nv_bfloat16*)p0, rs0, hs0, h0}, s1{(const __nv_bfloat16*)p1, rs1, hs1, h1},
       s2{(const __nv_bfloat16*)p2, rs2, hs2, h2};
-  qkv_rope_kernel<<<grid_for(T * (h0 + h1 + h2) * (hd / 8), 256, GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
+  qkv_rope_kernel<<<(unsigned)(T < GRID_CAP ? T : GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
       s0, s1, s2, (__nv_bfloat16*)out, cos_t, sin_t, pos_ids, T, S, pos_off, hd, rot, rot_heads, sign);
   CHECK_LAUNCH();
 }
@@ -697,13 +772,7 @@ NP_API int np_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float* w,
   }
   float* scratch = g_noalloc_ptr[dev];
   const int grid = np_rmsnorm_bwd_parts(rows);  // <= NP_NOALLOC_MAX_PARTS
-  cudaStream_t s = (cudaStream_t)stream;
-#define RB(V) rmsnorm_bwd_kernel<V><<<grid, NT, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, \
-                                                       (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, rows, cols)
-  if (cols <= NT * 8) RB(1);
-  else RB(2);
-#undef RB
-  // every partial row [0, grid) x [0, cols) was just written by the kernel above, so nothing stale is read
-  colsum_kernel<<<(cols + 255) / 256, 256, 0, s>>>(scratch, dw, grid, cols, accumulate_dw);
+  // every partial row [0, grid) x [0, cols) is written by the first kernel, so the column sum reads nothing stale
+  launch_rmsnorm_bwd(dy, x, w, rstd, dres, dx, dw, scratch, rows, cols, accumulate_dw, grid, (cudaStream_t)stream);
   CHECK_LAUNCH();
 }

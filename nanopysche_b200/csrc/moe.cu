@@ -35,12 +35,13 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
 }
 
 // ------------------------------------------------------------------ router
-// logits[t, e] = <x[t], Wg[e]> + bias[e]  (fp32 accumulate, fp32 gate weights). One warp per token.
+// logits[t, e] = <x[t], Wg[e]> + bias[e]  (fp32 accumulate, fp32 gate weights). One warp per token; the register
+// cap keeps four CTAs per SM resident so that enough row loads are in flight; the gate weights come from L1.
 template <int EB>
-__global__ void __launch_bounds__(256) router_logits_kernel(const __nv_bfloat16* __restrict__ x,
-                                                            const float* __restrict__ wg,
-                                                            const float* __restrict__ bias,
-                                                            float* __restrict__ logits, int T, int D, int E) {
+__global__ void __launch_bounds__(256, 4) router_logits_kernel(const __nv_bfloat16* __restrict__ x,
+                                                               const float* __restrict__ wg,
+                                                               const float* __restrict__ bias,
+                                                               float* __restrict__ logits, int T, int D, int E) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -49,23 +50,33 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const __nv_bfloat16*
       float acc[EB];
 #pragma unroll
       for (int e = 0; e < EB; ++e) acc[e] = 0.f;
-      for (int d = lane * 8; d < D; d += 256) {
-        float xv[8];
-        load8(x + (size_t)t * D + d, xv);
+      for (int d = lane * 8; d < D; d += 512) {
+        const bool two = d + 256 < D;
+        const uint4 q0 = *reinterpret_cast<const uint4*>(x + (size_t)t * D + d);
+        const uint4 q1 = two ? *reinterpret_cast<const uint4*>(x + (size_t)t * D + d + 256) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int e = 0; e < EB; ++e) {
-          if (e0 + e < E) {
-            const float4 w0 = *reinterpret_cast<const float4*>(wg + (size_t)(e0 + e) * D + d);
-            const float4 w1 = *reinterpret_cast<const float4*>(wg + (size_t)(e0 + e) * D + d + 4);
-            acc[e] += xv[0] * w0.x + xv[1] * w0.y + xv[2] * w0.z + xv[3] * w0.w + xv[4] * w1.x +
-                      xv[5] * w1.y + xv[6] * w1.z + xv[7] * w1.w;
+        for (int h = 0; h < 2; ++h) {
+          if (h == 1 && !two) break;
+          float xv[8];
+          const uint4 q = h ? q1 : q0;
+          float2 a = np::unpack_bf16(q.x), b = np::unpack_bf16(q.y), c = np::unpack_bf16(q.z), dd = np::unpack_bf16(q.w);
+          xv[0] = a.x; xv[1] = a.y; xv[2] = b.x; xv[3] = b.y; xv[4] = c.x; xv[5] = c.y; xv[6] = dd.x; xv[7] = dd.y;
+#pragma unroll
+          for (int e = 0; e < EB; ++e) {
+            if (e0 + e < E) {
+              const float* wp = wg + (size_t)(e0 + e) * D + d + h * 256;
+              const float4 w0 = __ldg(reinterpret_cast<const float4*>(wp));
+              const float4 w1 = __ldg(reinterpret_cast<const float4*>(wp + 4));
+              acc[e] += xv[0] * w0.x + xv[1] * w0.y + xv[2] * w0.z + xv[3] * w0.w + xv[4] * w1.x + xv[5] * w1.y +
+                        xv[6] * w1.z + xv[7] * w1.w;
+            }
           }
         }
       }
 #pragma unroll
       for (int e = 0; e < EB; ++e) {
-        const float s = np::warp_sum(acc[e]);
-        if (lane == 0 && e0 + e < E) logits[(size_t)t * E + e0 + e] = s + (bias ? bias[e0 + e] : 0.f);
+        const float sm = np::warp_sum(acc[e]);
+        if (lane == 0 && e0 + e < E) logits[(size_t)t * E + e0 + e] = sm + (bias ? bias[e0 + e] : 0.f);
       }
     }
   }
@@ -87,6 +98,12 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
   if (threadIdx.x == 0) s_z = 0.f;
   __syncthreads();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  // per-thread contributions to the statistics; reduced over the warp before they touch shared memory
+  float pe[EMAX];
+  float pz = 0.f;
+  unsigned long long picked = 0ull;
+#pragma unroll
+  for (int e = 0; e < EMAX; ++e) pe[e] = 0.f;
   if (t < T) {
     float l[EMAX];  // EMAX is a compile-time bound so the logits stay in registers
     float mx = -INFINITY;
@@ -100,10 +117,9 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
 #pragma unroll
     for (int e = 0; e < EMAX; ++e) se += (e < E) ? __expf(l[e] - mx) : 0.f;
     const float lse = mx + logf(se);
+    pz = lse * lse;
 #pragma unroll
-    for (int e = 0; e < EMAX; ++e)
-      if (e < E) atomicAdd(&s_p[e], __expf(l[e] - lse));
-    atomicAdd(&s_z, lse * lse);
+    for (int e = 0; e < EMAX; ++e) pe[e] = (e < E) ? __expf(l[e] - lse) : 0.f;
     // top-k by repeated argmax (ties -> lowest index, as torch.topk on distinct values)
     int sel[MAX_K];
     float sv[MAX_K];
@@ -120,8 +136,8 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
       used |= 1ull << best;
       sel[k] = best;
       sv[k] = bv;
-      atomicAdd(&s_cnt[best], 1);
     }
+    picked = used;
     float den = 0.f;
     if (gating == 1) {
       for (int k = 0; k < K; ++k) den += sv[k];
@@ -136,6 +152,21 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
       weights[(size_t)t * K + k] = sv[k];
       indices[(size_t)t * K + k] = sel[k];
     }
+  }
+  {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) {
+      if (e >= E) break;
+      const float ps = np::warp_sum(pe[e]);
+      const int c = __popc(__ballot_sync(0xffffffffu, (picked >> e) & 1ull));
+      if (lane == 0) {
+        atomicAdd(&s_p[e], ps);
+        if (c) atomicAdd(&s_cnt[e], c);
+      }
+    }
+    pz = np::warp_sum(pz);
+    if (lane == 0) atomicAdd(&s_z, pz);
   }
   __syncthreads();
   for (int i = threadIdx.x; i < E; i += blockDim.x) {
@@ -203,42 +234,84 @@ __global__ void __launch_bounds__(256) router_bwd_kernel(const float* __restrict
   for (int e = 0; e < E; ++e) dlogits[(size_t)t * E + e] = dl[e];
 }
 
-// partial[c, e, d] = sum over the chunk's tokens of dl[t, e] * x[t, d]
+// partial[c, e, d] = sum over the chunk's tokens of dl[t, e] * x[t, d]. CTA = 64 column threads (8 columns each) x 4
+// token lanes; a lane walks every fourth token of the chunk with four row loads in flight, the lanes are summed
+// through shared memory.
 template <int EB>
 __global__ void __launch_bounds__(256) router_dgate_kernel(const float* __restrict__ dl,
                                                            const __nv_bfloat16* __restrict__ x,
                                                            float* __restrict__ partial, int T, int D, int E,
                                                            int chunk) {
+  __shared__ float red[2][64][EB * 8 + 1];
   const int c = blockIdx.y;
   const int t0 = c * chunk, t1 = min(T, t0 + chunk);
-  const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  if (d >= D) return;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  const int d = (blockIdx.x * 64 + tx) * 8;
+  const bool col_ok = d < D;
   for (int e0 = 0; e0 < E; e0 += EB) {
     float acc[EB][8];
 #pragma unroll
     for (int e = 0; e < EB; ++e)
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[e][j] = 0.f;
-    for (int t = t0; t < t1; ++t) {
-      float xv[8];
-      load8(x + (size_t)t * D + d, xv);
+    if (col_ok) {
+      for (int tb = t0 + ty; tb < t1; tb += 16) {   // tokens tb, tb+4, tb+8, tb+12
+        uint4 q[4];
 #pragma unroll
-      for (int e = 0; e < EB; ++e) {
-        if (e0 + e < E) {
-          const float g = dl[(size_t)t * E + e0 + e];
+        for (int u = 0; u < 4; ++u)
+          q[u] = (tb + 4 * u < t1) ? *reinterpret_cast<const uint4*>(x + (size_t)(tb + 4 * u) * D + d)
+                                   : make_uint4(0, 0, 0, 0);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[e][j] += g * xv[j];
+        for (int u = 0; u < 4; ++u) {
+          if (tb + 4 * u >= t1) break;
+          float2 a = np::unpack_bf16(q[u].x), b = np::unpack_bf16(q[u].y), cc = np::unpack_bf16(q[u].z),
+                 dd = np::unpack_bf16(q[u].w);
+          const float xv[8] = {a.x, a.y, b.x, b.y, cc.x, cc.y, dd.x, dd.y};
+#pragma unroll
+          for (int e = 0; e < EB; ++e) {
+            if (e0 + e < E) {
+              const float g = __ldg(dl + (size_t)(tb + 4 * u) * E + e0 + e);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[e][j] += g * xv[j];
+            }
+          }
         }
       }
     }
+    if (ty >= 2) {   // lanes 2, 3 -> lanes 0, 1
 #pragma unroll
-    for (int e = 0; e < EB; ++e) {
-      if (e0 + e < E) {
-        float* dst = partial + ((size_t)c * E + e0 + e) * D + d;
-        *reinterpret_cast<float4*>(dst) = make_float4(acc[e][0], acc[e][1], acc[e][2], acc[e][3]);
-        *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[e][4], acc[e][5], acc[e][6], acc[e][7]);
+      for (int e = 0; e < EB; ++e)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) red[ty - 2][tx][e * 8 + j] = acc[e][j];
+    }
+    __syncthreads();
+    if (ty < 2) {
+#pragma unroll
+      for (int e = 0; e < EB; ++e)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[e][j] += red[ty][tx][e * 8 + j];
+    }
+    __syncthreads();
+    if (ty == 1) {   // lane 1 -> lane 0
+#pragma unroll
+      for (int e = 0; e < EB; ++e)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) red[0][tx][e * 8 + j] = acc[e][j];
+    }
+    __syncthreads();
+    if (ty == 0 && col_ok) {
+#pragma unroll
+      for (int e = 0; e < EB; ++e) {
+        if (e0 + e < E) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[e][j] += red[0][tx][e * 8 + j];
+          float* dst = partial + ((size_t)c * E + e0 + e) * D + d;
+          *reinterpret_cast<float4*>(dst) = make_float4(acc[e][0], acc[e][1], acc[e][2], acc[e][3]);
+          *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[e][4], acc[e][5], acc[e][6], acc[e][7]);
+        }
       }
     }
+    __syncthreads();
   }
 }
 
@@ -246,16 +319,14 @@ __global__ void colsum2_kernel(const float* __restrict__ partial, float* __restr
                                long long cols, int accumulate) {
   const long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (c >= cols) return;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  float a8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   int p = 0;
-  for (; p + 3 < parts; p += 4) {
-    s0 += partial[(size_t)p * cols + c];
-    s1 += partial[(size_t)(p + 1) * cols + c];
-    s2 += partial[(size_t)(p + 2) * cols + c];
-    s3 += partial[(size_t)(p + 3) * cols + c];
+  for (; p + 7 < parts; p += 8) {   // eight independent loads in flight
+#pragma unroll
+    for (int u = 0; u < 8; ++u) a8[u] += partial[(size_t)(p + u) * cols + c];
   }
-  for (; p < parts; ++p) s0 += partial[(size_t)p * cols + c];
-  const float s = (s0 + s1) + (s2 + s3);
+  for (; p < parts; ++p) a8[0] += partial[(size_t)p * cols + c];
+  const float s = ((a8[0] + a8[1]) + (a8[2] + a8[3])) + ((a8[4] + a8[5]) + (a8[6] + a8[7]));
   out[c] = accumulate ? out[c] + s : s;
 }
 
@@ -265,8 +336,16 @@ __global__ void __launch_bounds__(1024) colsum_narrow_kernel(const float* __rest
   __shared__ float red[1024];
   const int c = threadIdx.x % cols, g = threadIdx.x / cols, ng = 1024 / cols;
   float s = 0.f;
-  if (g < ng)
-    for (int r = g; r < rows; r += ng) s += a[(size_t)r * cols + c];
+  if (g < ng) {
+    float a4[4] = {0.f, 0.f, 0.f, 0.f};
+    int r = g;
+    for (; r + 3 * ng < rows; r += 4 * ng) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) a4[u] += a[(size_t)(r + u * ng) * cols + c];
+    }
+    for (; r < rows; r += ng) a4[0] += a[(size_t)r * cols + c];
+    s = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+  }
   red[threadIdx.x] = (g < ng) ? s : 0.f;
   __syncthreads();
   if (threadIdx.x < cols) {
@@ -277,22 +356,72 @@ __global__ void __launch_bounds__(1024) colsum_narrow_kernel(const float* __rest
 }
 
 // ------------------------------------------------------------------ capacity / positions
-// One CTA, one warp per expert. Phase 1: rank of token t among all tokens that picked expert e.
-// keep[t] = every pick of t is below `capacity` (capacity < 0: keep all). Phase 2: rank among kept.
+// One CTA of 1024 threads; thread i owns a contiguous run of tokens, so a block-wide exclusive scan of
+// per-thread pick counts gives positions in token order. The counters of a group of experts are packed into up to
+// four 64-bit words (16-bit fields while T < 65536, else 32-bit) and scanned together. Phase 0 ranks every pick
+// among all tokens that picked the expert and clears keep[t] when any pick of t lies at or beyond `capacity`
+// (capacity < 0: keep all); phase 1 ranks among the kept tokens.
 // Outputs: slot_pos[t,k] (position among kept for expert idx[t,k], -1 if dropped), keep[T],
 // counts_kept[E], drops[E] (tokens beyond capacity per expert), n_dropped[1].
+struct U64x4 {
+  unsigned long long w[4];
+};
+__device__ __forceinline__ U64x4 block_excl_scan4(const U64x4& v, int nw_used, U64x4* s_warp, U64x4* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  U64x4 inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (q < nw_used) {
+        const unsigned long long n = __shfl_up_sync(0xffffffffu, inc.w[q], o);
+        if (lane >= o) inc.w[q] += n;
+      }
+    }
+  }
+  if (lane == 31) s_warp[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    U64x4 wv = lane < nwarps ? s_warp[lane] : U64x4{{0ull, 0ull, 0ull, 0ull}};
+    U64x4 winc = wv;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (q < nw_used) {
+          const unsigned long long n = __shfl_up_sync(0xffffffffu, winc.w[q], o);
+          if (lane >= o) winc.w[q] += n;
+        }
+      }
+    }
+    U64x4 ex;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) ex.w[q] = winc.w[q] - wv.w[q];
+    s_warp[lane] = ex;                 // exclusive offset of each warp
+    if (lane == 31) s_warp[32] = winc;  // grand total
+  }
+  __syncthreads();
+  U64x4 res;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) res.w[q] = s_warp[warp].w[q] + inc.w[q] - v.w[q];
+  *total = s_warp[32];
+  __syncthreads();                     // s_warp is reused by the next scan
+  return res;
+}
+
+template <int FB>   // bits per counter: 16 or 32
 __global__ void __launch_bounds__(1024) capacity_scan_kernel(const int* __restrict__ indices, int T, int E, int K,
                                                              int capacity, int* __restrict__ slot_pos,
                                                              int* __restrict__ keep, int* __restrict__ counts_kept,
                                                              int* __restrict__ drops, int* __restrict__ n_dropped,
                                                              int use_smem) {
-  // s_idx: the routing table staged once (the scans below walk it serially per expert, so reading it
-  // from global memory would pay one dependent-load latency per 32 tokens); s_keep: one byte per token
-  extern __shared__ int s_dyn[];
+  constexpr int EPW = 64 / FB;          // experts per 64-bit word
+  constexpr int GROUP = 4 * EPW;        // experts per pass
+  constexpr unsigned long long FMASK = (FB == 16) ? 0xffffull : 0xffffffffull;
+  extern __shared__ int s_dyn[];        // routing table staged once, then one keep byte per token
+  __shared__ U64x4 s_warp[33];
   int* s_idx = s_dyn;
   unsigned char* s_keep = reinterpret_cast<unsigned char*>(s_dyn + (use_smem ? T * K : 0));
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nw = blockDim.x >> 5;
   const int* idx = indices;
   if (use_smem) {
     for (int i = threadIdx.x; i < T * K; i += blockDim.x) s_idx[i] = indices[i];
@@ -302,89 +431,65 @@ __global__ void __launch_bounds__(1024) capacity_scan_kernel(const int* __restri
     for (int t = threadIdx.x; t < T; t += blockDim.x) keep[t] = 1;
   }
   __syncthreads();
-  // Two-level scan: warp w handles expert (w % E) over segment (w / E) of the tokens; segment totals are
-  // exchanged through shared memory, so the serial ballot loop is T / (32 * segments) long.
-  __shared__ int s_seg[32];
-  const int nseg = (E <= nw) ? nw / E : 1;
-  const int seg_len = ((T + nseg - 1) / nseg + 31) & ~31;
-  for (int e0 = 0; e0 < E; e0 += nw) {
-    const int e = e0 + (E <= nw ? warp % E : warp);
-    const int sg = (E <= nw) ? warp / E : 0;
-    const bool active = e < E && sg < nseg;
-    const int t_lo = sg * seg_len, t_hi = min(T, t_lo + seg_len);
-    for (int phase = 0; phase < 2; ++phase) {
-      if (phase == 0 && capacity < 0) {
-        if (active && lane == 0 && sg == 0) drops[e] = 0;
-        continue;
-      }
-      // pass A: count this segment
-      int cnt = 0;
-      if (active) {
-        for (int t0 = t_lo; t0 < t_hi; t0 += 32) {
-          const int t = t0 + lane;
-          bool has = false;
-          if (t < t_hi)
-            for (int k = 0; k < K; ++k) has |= idx[(size_t)t * K + k] == e;
-          if (phase == 1) has = has && (use_smem ? s_keep[t < T ? t : 0] : keep[t < T ? t : 0]) && t < t_hi;
-          cnt += __popc(__ballot_sync(0xffffffffu, has));
-        }
-        if (lane == 0) s_seg[warp] = cnt;
-      }
-      __syncthreads();
-      int base = 0, total = 0;
-      if (active) {
-        for (int q = 0; q < nseg; ++q) {
-          const int v = s_seg[(E <= nw) ? q * E + e : warp];
-          if (q < sg) base += v;
-          total += v;
+  const int per = (T + blockDim.x - 1) / blockDim.x;
+  const int t_lo = min(T, (int)threadIdx.x * per), t_hi = min(T, t_lo + per);
+  for (int phase = (capacity < 0 ? 1 : 0); phase < 2; ++phase) {
+    for (int e0 = 0; e0 < E; e0 += GROUP) {
+      const int n_e = min(GROUP, E - e0);
+      const int nw_used = (n_e + EPW - 1) / EPW;
+      U64x4 loc{{0ull, 0ull, 0ull, 0ull}};
+      for (int t = t_lo; t < t_hi; ++t) {
+        if (phase == 1 && !(use_smem ? s_keep[t] : keep[t])) continue;
+        for (int k = 0; k < K; ++k) {
+          const int e = idx[(size_t)t * K + k] - e0;
+          if (e >= 0 && e < n_e) loc.w[e / EPW] += 1ull << (FB * (e % EPW));
         }
       }
-      __syncthreads();
-      // pass B: positions
-      if (active) {
-        for (int t0 = t_lo; t0 < t_hi; t0 += 32) {
-          const int t = t0 + lane;
-          int kk = -1;
-          if (t < t_hi)
-            for (int k = 0; k < K; ++k)
-              if (idx[(size_t)t * K + k] == e) kk = k;
-          bool has = kk >= 0;
-          if (phase == 1) has = has && (use_smem ? s_keep[t] : keep[t]);
-          const unsigned m = __ballot_sync(0xffffffffu, has);
-          const int pos = base + __popc(m & ((1u << lane) - 1u));
+      U64x4 total;
+      U64x4 run = block_excl_scan4(loc, nw_used, s_warp, &total);
+      for (int t = t_lo; t < t_hi; ++t) {
+        const bool kept = phase == 0 || (use_smem ? s_keep[t] : keep[t]);
+        for (int k = 0; k < K; ++k) {
+          const int e = idx[(size_t)t * K + k] - e0;
+          if (e < 0 || e >= n_e) continue;
+          if (!kept) {
+            slot_pos[(size_t)t * K + k] = -1;
+            continue;
+          }
+          const int q = e / EPW, sh = FB * (e % EPW);
+          const int pos = (int)((run.w[q] >> sh) & FMASK);
+          run.w[q] += 1ull << sh;
           if (phase == 0) {
-            if (has && pos >= capacity) {  // benign race: only ever written to 0
+            if (pos >= capacity) {   // only ever written to 0, by the thread that owns the token
               if (use_smem) s_keep[t] = 0; else keep[t] = 0;
             }
-          } else if (kk >= 0) {
-            slot_pos[(size_t)t * K + kk] = has ? pos : -1;
+          } else {
+            slot_pos[(size_t)t * K + k] = pos;
           }
-          base += __popc(m);
-        }
-        if (lane == 0 && sg == 0) {
-          if (phase == 0) drops[e] = total > capacity ? total - capacity : 0;
-          else counts_kept[e] = total;
         }
       }
-      __syncthreads();
+      if ((int)threadIdx.x < n_e) {
+        const int e = threadIdx.x;
+        const int c = (int)((total.w[e / EPW] >> (FB * (e % EPW))) & FMASK);
+        if (phase == 0) {
+          drops[e0 + e] = c > capacity ? c - capacity : 0;
+        } else {
+          counts_kept[e0 + e] = c;
+          if (capacity < 0) drops[e0 + e] = 0;
+        }
+      }
     }
+    __syncthreads();   // keep flags of phase 0 are complete before phase 1 reads them
   }
-  __syncthreads();
   int nd = 0;
   for (int t = threadIdx.x; t < T; t += blockDim.x) {
     const int kp = use_smem ? (int)s_keep[t] : keep[t];
     if (use_smem) keep[t] = kp;
     nd += kp ? 0 : 1;
   }
-  for (int o = 16; o > 0; o >>= 1) nd += __shfl_xor_sync(0xffffffffu, nd, o);
-  __shared__ int s_nd[32];
-  if (lane == 0) s_nd[warp] = nd;
-  __syncthreads();
-  if (warp == 0) {
-    int v = lane < nw ? s_nd[lane] : 0;
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == 0) n_dropped[0] = v;
-  }
+  U64x4 ndv{{(unsigned long long)nd, 0ull, 0ull, 0ull}}, total;
+  block_excl_scan4(ndv, 1, s_warp, &total);
+  if (threadIdx.x == 0) n_dropped[0] = (int)total.w[0];
 }
 
 // ------------------------------------------------------------------ EP dispatch (peer stores)
@@ -650,7 +755,7 @@ NP_API int np_router_bwd(const float* logits, const float* score_bias, const flo
   CHECK_LAUNCH();
 }
 
-NP_API int np_router_dgate_parts(int T) { return (T + 31) / 32; }
+NP_API int np_router_dgate_parts(int T) { return (T + 63) / 64; }
 // scratch: fp32 [np_router_dgate_parts(T), E, D]; dwg[E, D] (+)= dl^T x ; dbias[E] (+)= column sums of dl.
 NP_API int np_router_dgate(const float* dl, const void* x, float* dwg, float* dbias, float* scratch, int T, int D,
                            int E, int accumulate, void* stream) {
@@ -658,8 +763,8 @@ NP_API int np_router_dgate(const float* dl, const void* x, float* dwg, float* db
   if (T <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int parts = np_router_dgate_parts(T);
-  dim3 grid((D / 8 + 255) / 256, parts);
-  router_dgate_kernel<8><<<grid, 256, 0, s>>>(dl, (const __nv_bfloat16*)x, scratch, T, D, E, 32);
+  dim3 grid((D / 8 + 63) / 64, parts);
+  router_dgate_kernel<8><<<grid, 256, 0, s>>>(dl, (const __nv_bfloat16*)x, scratch, T, D, E, 64);
   const long long cols = (long long)E * D;
   colsum2_kernel<<<(int)((cols + 63) / 64), 64, 0, s>>>(scratch, dwg, parts, cols, accumulate);
   if (dbias) colsum_narrow_kernel<<<1, 1024, 0, s>>>(dl, dbias, T, E, accumulate);
@@ -674,13 +779,18 @@ NP_API int np_capacity_scan(const int* indices, int T, int E, int K, int capacit
   const int use_smem = smem <= 200 * 1024;
   static bool attr_set = false;
   if (use_smem && !attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(capacity_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(capacity_scan_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(capacity_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return 400 + (int)e;
     attr_set = true;
   }
-  capacity_scan_kernel<<<1, 1024, use_smem ? smem : 0, (cudaStream_t)stream>>>(indices, T, E, K, capacity, slot_pos,
-                                                                               keep, counts_kept, drops, n_dropped,
-                                                                               use_smem);
+  if (T < 65536)   // a 16-bit counter holds any per-expert count
+    capacity_scan_kernel<16><<<1, 1024, use_smem ? smem : 0, (cudaStream_t)stream>>>(
+        indices, T, E, K, capacity, slot_pos, keep, counts_kept, drops, n_dropped, use_smem);
+  else
+    capacity_scan_kernel<32><<<1, 1024, use_smem ? smem : 0, (cudaStream_t)stream>>>(
+        indices, T, E, K, capacity, slot_pos, keep, counts_kept, drops, n_dropped, use_smem);
   CHECK_LAUNCH();
 }
 
