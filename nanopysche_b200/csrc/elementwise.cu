@@ -400,6 +400,170 @@ __global__ void __launch_bounds__(256) qkv_rope_kernel(HeadSrc s0, HeadSrc s1, H
   }
 }
 
+// Fused "split QKV + per-head LayerNorm(q), LayerNorm(k) + RoPE" for head_dim 128 with full rotary. A head is
+// handled by 8 neighbouring threads (16 elements each: an 8-wide slice of the lower half and its partner in the
+// upper half), which share the LayerNorm statistics through shuffles inside their 8-lane group.
+// Replaces q_norm / k_norm (nn.LayerNorm over head_dim) + apply_rotary_emb in the reference
+// (model/attention.py:152-164, model/rope.py:139-170).
+__device__ __forceinline__ float group8_sum(float v, unsigned mask) {
+  v += __shfl_xor_sync(mask, v, 1);
+  v += __shfl_xor_sync(mask, v, 2);
+  v += __shfl_xor_sync(mask, v, 4);
+  return v;
+}
+__device__ __forceinline__ void ld8f(const float* p, float* f) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+__global__ void __launch_bounds__(256) qkv_norm_rope_fwd_kernel(
+    const __nv_bfloat16* __restrict__ qkv, long long row_stride, int hq, int hkv, const float* __restrict__ gq,
+    const float* __restrict__ bq, const float* __restrict__ gk, const float* __restrict__ bk, float eps,
+    __nv_bfloat16* __restrict__ out, float2* __restrict__ stats, const float* __restrict__ cos_t,
+    const float* __restrict__ sin_t, const int* __restrict__ pos_ids, long long T, int S, int pos_off) {
+  constexpr int HD = 128, HALF = 64;
+  const int nrot = hq + hkv, H = hq + 2 * hkv;
+  const int items = nrot * 8 + hkv * 16;
+  const unsigned mask = 0xffu << (threadIdx.x & 24);
+  for (long long t = blockIdx.x; t < T; t += gridDim.x) {
+    const int pos = pos_ids ? pos_ids[t] : (int)(t % S) + pos_off;
+    const __nv_bfloat16* row = qkv + t * row_stride;
+    __nv_bfloat16* orow = out + t * (long long)H * HD;
+    for (int it = threadIdx.x; it < items; it += blockDim.x) {
+      if (it < nrot * 8) {
+        const int hh = it >> 3, d0 = (it & 7) * 8;
+        float a[8], b[8];
+        load8(row + hh * HD + d0, a);
+        load8(row + hh * HD + d0 + HALF, b);
+        float sm = 0.f, sq = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { sm += a[j] + b[j]; sq += a[j] * a[j] + b[j] * b[j]; }
+        sm = group8_sum(sm, mask);
+        sq = group8_sum(sq, mask);
+        const float mean = sm * (1.f / HD);
+        const float rstd = rsqrtf(fmaxf(sq * (1.f / HD) - mean * mean, 0.f) + eps);
+        const float* g = hh < hq ? gq : gk;
+        const float* be = hh < hq ? bq : bk;
+        float gl[8], gh[8], bl[8], bh[8], c[8], sn[8], lo[8], hi[8];
+        ld8f(g + d0, gl); ld8f(g + d0 + HALF, gh); ld8f(be + d0, bl); ld8f(be + d0 + HALF, bh);
+        ld8f(cos_t + (size_t)pos * HALF + d0, c);
+        ld8f(sin_t + (size_t)pos * HALF + d0, sn);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          // the normalised value passes through bf16 like the output of the unfused LayerNorm
+          const float na = __bfloat162float(__float2bfloat16((a[j] - mean) * rstd * gl[j] + bl[j]));
+          const float nb = __bfloat162float(__float2bfloat16((b[j] - mean) * rstd * gh[j] + bh[j]));
+          lo[j] = na * c[j] - nb * sn[j];
+          hi[j] = nb * c[j] + na * sn[j];
+        }
+        store8(orow + hh * HD + d0, lo);
+        store8(orow + hh * HD + d0 + HALF, hi);
+        if ((it & 7) == 0) stats[t * nrot + hh] = make_float2(mean, rstd);
+      } else {
+        const int r = it - nrot * 8;
+        const int off = (nrot + (r >> 4)) * HD + (r & 15) * 8;
+        *reinterpret_cast<uint4*>(orow + off) = *reinterpret_cast<const uint4*>(row + off);
+      }
+    }
+  }
+}
+
+// Backward: inverse rotation of dq / dk, LayerNorm backward against the saved pre-norm values and statistics,
+// dv copied; the three results form one contiguous dqkv. The gamma / beta gradients are accumulated per thread
+// (a thread keeps its (head, slice) across tokens), summed over the heads of a kind in shared memory and written as
+// one partial row [4 x 128] per CTA (dgamma_q, dbeta_q, dgamma_k, dbeta_k).
+__global__ void __launch_bounds__(256) qkv_norm_rope_bwd_kernel(
+    HeadSrc s0, HeadSrc s1, HeadSrc s2, const __nv_bfloat16* __restrict__ qkv, long long row_stride, int hq, int hkv,
+    const float* __restrict__ gq, const float* __restrict__ gk, const float2* __restrict__ stats,
+    __nv_bfloat16* __restrict__ dqkv, float* __restrict__ partial, const float* __restrict__ cos_t,
+    const float* __restrict__ sin_t, const int* __restrict__ pos_ids, long long T, int S, int pos_off) {
+  constexpr int HD = 128, HALF = 64;
+  __shared__ float s_acc[4][HD];
+  const int nrot = hq + hkv, H = hq + 2 * hkv;
+  const int items = nrot * 8 + hkv * 16;
+  const unsigned mask = 0xffu << (threadIdx.x & 24);
+  for (int i = threadIdx.x; i < 4 * HD; i += blockDim.x) (&s_acc[0][0])[i] = 0.f;
+  float dg[2][16], db[2][16];   // up to two rotated items per thread (nrot * 8 <= 512)
+#pragma unroll
+  for (int u = 0; u < 2; ++u)
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { dg[u][j] = 0.f; db[u][j] = 0.f; }
+  for (long long t = blockIdx.x; t < T; t += gridDim.x) {
+    const int pos = pos_ids ? pos_ids[t] : (int)(t % S) + pos_off;
+    const __nv_bfloat16* row = qkv + t * row_stride;
+    __nv_bfloat16* orow = dqkv + t * (long long)H * HD;
+#pragma unroll
+    for (int u = 0; u < 3; ++u) {
+      const int it = threadIdx.x + u * 256;
+      if (it >= items) break;
+      if (it < nrot * 8) {
+        const int hh = it >> 3, d0 = (it & 7) * 8;
+        const __nv_bfloat16* gsrc = hh < hq ? s0.p + t * s0.row_stride + (long long)hh * s0.head_stride
+                                            : s1.p + t * s1.row_stride + (long long)(hh - hq) * s1.head_stride;
+        float dl[8], dh[8], a[8], b[8], c[8], sn[8], gl[8], gh[8];
+        load8(gsrc + d0, dl);
+        load8(gsrc + d0 + HALF, dh);
+        load8(row + hh * HD + d0, a);
+        load8(row + hh * HD + d0 + HALF, b);
+        ld8f(cos_t + (size_t)pos * HALF + d0, c);
+        ld8f(sin_t + (size_t)pos * HALF + d0, sn);
+        const float* g = hh < hq ? gq : gk;
+        ld8f(g + d0, gl); ld8f(g + d0 + HALF, gh);
+        const float2 st = stats[t * nrot + hh];
+        float ya[8], yb[8], xa[8], xb[8];
+        float m1 = 0.f, m2 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          ya[j] = dl[j] * c[j] + dh[j] * sn[j];   // gradient at the LayerNorm output
+          yb[j] = dh[j] * c[j] - dl[j] * sn[j];
+          xa[j] = (a[j] - st.x) * st.y;
+          xb[j] = (b[j] - st.x) * st.y;
+          if (u < 2) {
+            dg[u][j] += ya[j] * xa[j]; dg[u][8 + j] += yb[j] * xb[j];
+            db[u][j] += ya[j]; db[u][8 + j] += yb[j];
+          }
+          ya[j] *= gl[j];
+          yb[j] *= gh[j];
+          m1 += ya[j] + yb[j];
+          m2 += ya[j] * xa[j] + yb[j] * xb[j];
+        }
+        m1 = group8_sum(m1, mask) * (1.f / HD);
+        m2 = group8_sum(m2, mask) * (1.f / HD);
+        float oa[8], ob[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          oa[j] = st.y * (ya[j] - m1 - xa[j] * m2);
+          ob[j] = st.y * (yb[j] - m1 - xb[j] * m2);
+        }
+        store8(orow + hh * HD + d0, oa);
+        store8(orow + hh * HD + d0 + HALF, ob);
+      } else {
+        const int r = it - nrot * 8;
+        const int hv = r >> 4, d0 = (r & 15) * 8;
+        *reinterpret_cast<uint4*>(orow + (nrot + hv) * HD + d0) =
+            *reinterpret_cast<const uint4*>(s2.p + t * s2.row_stride + (long long)hv * s2.head_stride + d0);
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int it = threadIdx.x + u * 256;
+    if (it < nrot * 8) {
+      const int kind = (it >> 3) < hq ? 0 : 2, d0 = (it & 7) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        atomicAdd(&s_acc[kind][d0 + j], dg[u][j]);
+        atomicAdd(&s_acc[kind][d0 + HALF + j], dg[u][8 + j]);
+        atomicAdd(&s_acc[kind + 1][d0 + j], db[u][j]);
+        atomicAdd(&s_acc[kind + 1][d0 + HALF + j], db[u][8 + j]);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 4 * HD; i += blockDim.x) partial[(size_t)blockIdx.x * 4 * HD + i] = (&s_acc[0][0])[i];
+}
+
 // cos/sin tables [S, rot/2] in fp32.
 // scaling: 0 none; 1 piecewise (wavelen < orig/high_freq keeps, wavelen > orig/low_freq divides by
 // factor, the band between keeps: the reference's rule, model/rope.py:64-80); 2 YaRN (NTK-by-parts
@@ -687,6 +851,41 @@ NP_API int np_qkv_rope(const void* p0, long long rs0, long long hs0, int h0, con
       s2{(const __nv_bfloat16*)p2, rs2, hs2, h2};
   qkv_rope_kernel<<<(unsigned)(T < GRID_CAP ? T : GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
       s0, s1, s2, (__nv_bfloat16*)out, cos_t, sin_t, pos_ids, T, S, pos_off, hd, rot, rot_heads, sign);
+  CHECK_LAUNCH();
+}
+
+// Fused split + LayerNorm(q), LayerNorm(k) + RoPE (head_dim 128, full rotary). qkv: rows of (hq + 2 hkv) * 128 with
+// row stride `row_stride`; out: contiguous [T, hq + 2 hkv, 128]; stats: (mean, rstd) per (token, q or k head).
+NP_API int np_qkv_norm_rope_fwd(const void* qkv, long long row_stride, int hq, int hkv, const float* gq,
+                                const float* bq, const float* gk, const float* bk, float eps, void* out, void* stats,
+                                const float* cos_t, const float* sin_t, const int* pos_ids, long long T, int S,
+                                int pos_off, void* stream) {
+  if (row_stride % 8 || (hq + hkv) * 8 > 512 || (hq + hkv) * 8 + hkv * 16 > 768) return 1;
+  if (T <= 0) return 0;
+  qkv_norm_rope_fwd_kernel<<<(unsigned)(T < GRID_CAP ? T : GRID_CAP), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)qkv, row_stride, hq, hkv, gq, bq, gk, bk, eps, (__nv_bfloat16*)out, (float2*)stats, cos_t,
+      sin_t, pos_ids, T, S, pos_off);
+  CHECK_LAUNCH();
+}
+NP_API int np_qkv_norm_rope_parts(long long T) { return (int)(T < 296 ? (T > 0 ? T : 1) : 296); }
+// dparams[4 * 128] (+)= (dgamma_q, dbeta_q, dgamma_k, dbeta_k); scratch: fp32 [np_qkv_norm_rope_parts(T), 4 * 128].
+NP_API int np_qkv_norm_rope_bwd(const void* dq, long long rs0, long long hs0, const void* dk, long long rs1,
+                                long long hs1, const void* dv, long long rs2, long long hs2, const void* qkv,
+                                long long row_stride, int hq, int hkv, const float* gq, const float* gk,
+                                const void* stats, void* dqkv, float* dparams, float* scratch, const float* cos_t,
+                                const float* sin_t, const int* pos_ids, long long T, int S, int pos_off,
+                                int accumulate, void* stream) {
+  if ((row_stride | rs0 | hs0 | rs1 | hs1 | rs2 | hs2) % 8 || (hq + hkv) * 8 > 512 || (hq + hkv) * 8 + hkv * 16 > 768)
+    return 1;
+  if (T <= 0) return 0;
+  HeadSrc s0{(const __nv_bfloat16*)dq, rs0, hs0, hq}, s1{(const __nv_bfloat16*)dk, rs1, hs1, hkv},
+      s2{(const __nv_bfloat16*)dv, rs2, hs2, hkv};
+  const int grid = np_qkv_norm_rope_parts(T);
+  cudaStream_t s = (cudaStream_t)stream;
+  qkv_norm_rope_bwd_kernel<<<grid, 256, 0, s>>>(s0, s1, s2, (const __nv_bfloat16*)qkv, row_stride, hq, hkv, gq, gk,
+                                                (const float2*)stats, (__nv_bfloat16*)dqkv, scratch, cos_t, sin_t,
+                                                pos_ids, T, S, pos_off);
+  colsum_tall_kernel<<<(4 * 128 + 31) / 32, 256, 0, s>>>(scratch, dparams, grid, 4 * 128, accumulate);
   CHECK_LAUNCH();
 }
 

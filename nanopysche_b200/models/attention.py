@@ -43,8 +43,8 @@ class Attention(nn.Module):
         self.w_k = nn.Linear(d_model, self.n_kv_heads * self.head_dim, bias=bias, **kw)
         self.w_v = nn.Linear(d_model, self.n_kv_heads * self.head_dim, bias=bias, **kw)
         self.w_out = nn.Linear(n_heads * self.head_dim, d_model, bias=bias, **kw)
-        self.q_norm = nn.LayerNorm(self.head_dim) if qk_norm else None
-        self.k_norm = nn.LayerNorm(self.head_dim) if qk_norm else None
+        self.q_norm = nn.LayerNorm(self.head_dim, device=device) if qk_norm else None
+        self.k_norm = nn.LayerNorm(self.head_dim, device=device) if qk_norm else None
         self.rope = RotaryEmbedding(self.head_dim, base=rope_base, max_seq_len=max_seq_len,
                                     head_first=rope_head_first, partial_rotary_factor=partial_rotary_factor,
                                     scaling=rope_scaling)
@@ -109,6 +109,10 @@ class Attention(nn.Module):
             pid = position_ids if position_ids.dim() == 2 else position_ids[None, :].expand(B, S)
         if qkv is not None and self.q_norm is None:
             q, k, v = rope_ops.qkv_rope(qkv, cos, sin, hq, hkv, hd, start_pos, pid)  # split + rotate in one kernel
+        elif qkv is not None and self.q_norm.bias is not None and \
+                rope_ops.qkv_norm_rope_supported(qkv, cos, hq, hkv, hd):
+            # split + per-head LayerNorm of q and k + rotate in one kernel
+            q, k, v = rope_ops.qkv_norm_rope(qkv, self.q_norm, self.k_norm, cos, sin, hq, hkv, start_pos, pid)
         else:
             if qkv is not None:
                 q = qkv[..., : hq * hd].unflatten(-1, (hq, hd))

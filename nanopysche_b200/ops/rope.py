@@ -169,6 +169,75 @@ class _QKVRope(torch.autograd.Function):
         return out, None, None, None, None, None, None, None
 
 
+class _QKVNormRope(torch.autograd.Function):
+    """Split the fused QKV output, apply the per-head LayerNorms of q and k and rotate, one kernel each way."""
+
+    @staticmethod
+    def forward(ctx, qkv, gq, bq, gk, bk, eps, cos, sin, hq, hkv, pos_offset, pos_ids):
+        B, S, W = qkv.shape
+        hd, H = 128, hq + 2 * hkv
+        out = torch.empty((B, S, H, hd), device=qkv.device, dtype=qkv.dtype)
+        stats = torch.empty((B * S, hq + hkv, 2), device=qkv.device, dtype=torch.float32)
+        f = [t.detach().float().contiguous() for t in (gq, bq, gk, bk)]
+        pid = C.c_void_p(pos_ids.data_ptr() if pos_ids is not None else 0)
+        _lib.check(_lib.lib().np_qkv_norm_rope_fwd(
+            C.c_void_p(qkv.data_ptr()), C.c_longlong(qkv.stride(1)), hq, hkv, *[C.c_void_p(t.data_ptr()) for t in f],
+            C.c_float(eps), C.c_void_p(out.data_ptr()), C.c_void_p(stats.data_ptr()), C.c_void_p(cos.data_ptr()),
+            C.c_void_p(sin.data_ptr()), pid, C.c_longlong(B * S), S, int(pos_offset), C.c_void_p(_lib.stream())),
+            "qkv_norm_rope_fwd")
+        ctx.save_for_backward(qkv, stats, f[0], f[2], cos, sin, pos_ids if pos_ids is not None else cos.new_empty(0))
+        ctx.meta = (hq, hkv, pos_offset, pos_ids is not None, [t.dtype for t in (gq, bq, gk, bk)])
+        return out[:, :, :hq], out[:, :, hq:hq + hkv], out[:, :, hq + hkv:]
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        qkv, stats, gq, gk, cos, sin, pos_ids = ctx.saved_tensors
+        hq, hkv, pos_offset, has_ids, dtypes = ctx.meta
+        B, S, W = qkv.shape
+        hd = 128
+        fixed = []
+        for g, h in ((dq, hq), (dk, hkv), (dv, hkv)):
+            if g is None:
+                g = torch.zeros((B, S, h, hd), device=qkv.device, dtype=torch.bfloat16)
+            if g.stride(3) != 1 or g.stride(0) != S * g.stride(1) or g.stride(1) % 8 or g.stride(2) % 8:
+                g = g.contiguous()
+            fixed.append(g)
+        dq, dk, dv = fixed
+        lib = _lib.lib()
+        T = B * S
+        dqkv = torch.empty((B, S, W), device=qkv.device, dtype=qkv.dtype)
+        dparams = torch.empty((4, hd), device=qkv.device, dtype=torch.float32)
+        scratch = torch.empty((lib.np_qkv_norm_rope_parts(C.c_longlong(T)), 4 * hd), device=qkv.device,
+                              dtype=torch.float32)
+        _lib.check(lib.np_qkv_norm_rope_bwd(
+            C.c_void_p(dq.data_ptr()), C.c_longlong(dq.stride(1)), C.c_longlong(dq.stride(2)),
+            C.c_void_p(dk.data_ptr()), C.c_longlong(dk.stride(1)), C.c_longlong(dk.stride(2)),
+            C.c_void_p(dv.data_ptr()), C.c_longlong(dv.stride(1)), C.c_longlong(dv.stride(2)),
+            C.c_void_p(qkv.data_ptr()), C.c_longlong(qkv.stride(1)), hq, hkv, C.c_void_p(gq.data_ptr()),
+            C.c_void_p(gk.data_ptr()), C.c_void_p(stats.data_ptr()), C.c_void_p(dqkv.data_ptr()),
+            C.c_void_p(dparams.data_ptr()), C.c_void_p(scratch.data_ptr()), C.c_void_p(cos.data_ptr()),
+            C.c_void_p(sin.data_ptr()), C.c_void_p(pos_ids.data_ptr() if has_ids else 0), C.c_longlong(T), S,
+            int(pos_offset), 0, C.c_void_p(_lib.stream())), "qkv_norm_rope_bwd")
+        dgq, dbq, dgk, dbk = [dparams[i].to(dt) for i, dt in enumerate(dtypes)]
+        return dqkv, dgq, dbq, dgk, dbk, None, None, None, None, None, None, None
+
+
+def qkv_norm_rope_supported(qkv: torch.Tensor, cos, hq: int, hkv: int, hd: int) -> bool:
+    S = qkv.shape[1]
+    return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and hd == 128 and cos.shape[1] == 64 and
+            cos.dtype == torch.float32 and qkv.stride(2) == 1 and qkv.stride(1) % 8 == 0 and
+            qkv.stride(0) == S * qkv.stride(1) and (hq + hkv) * 8 <= 512 and (hq + hkv) * 8 + hkv * 16 <= 768)
+
+
+def qkv_norm_rope(qkv, q_norm, k_norm, cos, sin, hq: int, hkv: int, pos_offset: int = 0, pos_ids=None):
+    """``qkv [B, S, (hq+2*hkv)*128]`` -> LayerNorm'ed and rotated ``q``, ``k`` and ``v`` (views of one buffer);
+    ``q_norm`` / ``k_norm`` are the ``nn.LayerNorm(128)`` modules of the attention layer."""
+    if pos_ids is not None:
+        pos_ids = pos_ids.reshape(-1).to(torch.int32)
+    return _QKVNormRope.apply(qkv, q_norm.weight, q_norm.bias, k_norm.weight, k_norm.bias, float(q_norm.eps), cos, sin,
+                              hq, hkv, pos_offset, pos_ids)
+
+
 def qkv_rope(qkv: torch.Tensor, cos, sin, hq: int, hkv: int, hd: int, pos_offset: int = 0, pos_ids=None):
     """``qkv [B, S, (hq+2*hkv)*hd]`` -> rotated ``q [B,S,hq,hd]``, ``k [B,S,hkv,hd]`` and ``v`` (strided views of
     one buffer). Falls back to slicing + ``apply_rope`` off the kernel path."""

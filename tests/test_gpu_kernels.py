@@ -343,3 +343,41 @@ def test_flash_attention_strided_qkv_views():
     o, _ = A.flash_fwd(q, k, v, causal=True)
     o2, _ = A.flash_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal=True)
     assert torch.equal(o, o2)
+
+
+def test_qkv_layernorm_rope_fused_matches_unfused():
+    """Fused split + q/k LayerNorm + RoPE (forward and backward) against the unfused module math in fp32."""
+    from nanopysche_b200.models.attention import Attention
+    from nanopysche_b200.ops import rope as rope_ops
+
+    torch.manual_seed(0)
+    B, S, hq, hkv, hd = 2, 96, 4, 2, 128
+    att = Attention(d_model=hq * hd, n_heads=hq, n_kv_heads=hkv, qk_norm=True, device="cuda")
+    with torch.no_grad():
+        for ln in (att.q_norm, att.k_norm):
+            ln.weight.normal_(1.0, 0.2)
+            ln.bias.normal_(0.0, 0.2)
+    cos, sin = att.rope.half_tables(S + 5, torch.device("cuda"))
+    qkv = torch.randn(B, S, (hq + 2 * hkv) * hd, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    assert rope_ops.qkv_norm_rope_supported(qkv, cos, hq, hkv, hd)
+    q, k, v = rope_ops.qkv_norm_rope(qkv, att.q_norm, att.k_norm, cos, sin, hq, hkv, 5, None)
+    gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+    torch.autograd.backward([q, k, v], [gq, gk, gv])
+    got = [qkv.grad.clone(), att.q_norm.weight.grad.clone(), att.q_norm.bias.grad.clone(),
+           att.k_norm.weight.grad.clone(), att.k_norm.bias.grad.clone()]
+    qkv.grad = None
+    for ln in (att.q_norm, att.k_norm):
+        ln.weight.grad = ln.bias.grad = None
+    # reference: slice, LayerNorm in fp32, rotate with the reference rotation, all in fp32
+    x = qkv.detach().float().requires_grad_()
+    q0 = x[..., : hq * hd].unflatten(-1, (hq, hd))
+    k0 = x[..., hq * hd:(hq + hkv) * hd].unflatten(-1, (hkv, hd))
+    v0 = x[..., (hq + hkv) * hd:].unflatten(-1, (hkv, hd))
+    qr = rope_ops.apply_rope_ref(att.q_norm(q0), cos, sin, 5, None)
+    kr = rope_ops.apply_rope_ref(att.k_norm(k0), cos, sin, 5, None)
+    torch.autograd.backward([qr, kr, v0], [gq.float(), gk.float(), gv.float()])
+    assert (q.float() - qr).abs().max().item() < 5e-2 and (k.float() - kr).abs().max().item() < 5e-2
+    assert torch.equal(v, v0.detach().to(v.dtype))
+    ref = [x.grad, att.q_norm.weight.grad, att.q_norm.bias.grad, att.k_norm.weight.grad, att.k_norm.bias.grad]
+    for a, b in zip(got, ref):
+        assert ((a.float() - b.float()).norm() / b.float().norm()).item() < 1.5e-2
