@@ -6,7 +6,7 @@ roofline (``MEASURED_PEAKS.json`` at the repository root when present, else 6.65
 1.59 PFLOP/s). The same command lines are what the ``ncu`` captures under ``profiles/`` run.
 
 Cases: gemm (fwd / dgrad / wgrad layouts, optional cuBLAS comparison), swiglu (fused GEMM + SwiGLU),
-rmsnorm, adamw, xent, moe (one fused MoE layer forward + backward).
+rmsnorm, adamw, xent, moe (one fused MoE layer forward + backward), attention (flash forward / backward).
 """
 from __future__ import annotations
 
@@ -146,7 +146,37 @@ def case_moe(a):
             "tflops_upper_bound_rows": flops / med / 1e9}, None, None
 
 
-CASES = {"gemm": case_gemm, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "xent": case_xent,
+def case_attention(a):
+    """Flash attention forward and backward (``--batch --seq --heads --kv-heads``, head_dim 128, causal unless
+    ``--full``); ``--sdpa`` also times PyTorch SDPA on the same tensors. FLOPs: 4 B H S^2 hd (x 2.5 for backward),
+    halved under causal masking."""
+    from . import attention as A
+
+    B, S, Hq, Hkv = a.batch, a.seq, a.heads, a.kv_heads
+    qkv = torch.randn(B, S, (Hq + 2 * Hkv) * 128, device="cuda", dtype=torch.bfloat16)
+    q = qkv[..., : Hq * 128].unflatten(-1, (Hq, 128))
+    k = qkv[..., Hq * 128:(Hq + Hkv) * 128].unflatten(-1, (Hkv, 128))
+    v = qkv[..., (Hq + Hkv) * 128:].unflatten(-1, (Hkv, 128))
+    g = torch.randn(B, S, Hq, 128, device="cuda", dtype=torch.bfloat16)
+    causal = not a.full
+    o, lse = A.flash_fwd(q, k, v, causal=causal)
+    fwd, _ = timeit(lambda: A.flash_fwd(q, k, v, causal=causal), a.iters)
+    bwd, _ = timeit(lambda: A.flash_bwd(q, k, v, o, g, lse, causal=causal), a.iters)
+    fl = 4.0 * B * Hq * S * S * 128 * (0.5 if causal else 1.0)
+    res = {"case": "attention", "B": B, "S": S, "Hq": Hq, "Hkv": Hkv, "causal": causal, "fwd_ms": fwd, "bwd_ms": bwd,
+           "ms": fwd, "tflops": fl / fwd / 1e9, "bwd_tflops": 2.5 * fl / bwd / 1e9}
+    if a.sdpa:
+        qs, ks, vs = [t.detach().clone().requires_grad_() for t in (q, k, v)]
+        os_ = torch.nn.functional.scaled_dot_product_attention(
+            qs.transpose(1, 2), ks.transpose(1, 2), vs.transpose(1, 2), is_causal=causal, enable_gqa=Hq != Hkv)
+        f2, _ = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(
+            qs.transpose(1, 2), ks.transpose(1, 2), vs.transpose(1, 2), is_causal=causal, enable_gqa=Hq != Hkv), a.iters)
+        b2, _ = timeit(lambda: torch.autograd.grad(os_, (qs, ks, vs), g.transpose(1, 2), retain_graph=True), a.iters)
+        res["sdpa_fwd_ms"], res["sdpa_bwd_ms"] = f2, b2
+    return res, fl, None
+
+
+CASES = {"attention": case_attention, "gemm": case_gemm, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "xent": case_xent,
          "moe": case_moe}
 
 
@@ -165,6 +195,12 @@ def main(argv=None):
     ap.add_argument("--topk", type=int, default=2)
     ap.add_argument("--capacity", type=float, default=None)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--full", action="store_true", help="attention without the causal mask")
+    ap.add_argument("--sdpa", action="store_true", help="also time PyTorch SDPA")
     a = ap.parse_args(argv)
     hbm, tf, src = peaks()
     res, flops, nbytes = CASES[a.case](a)

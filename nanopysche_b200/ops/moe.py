@@ -325,7 +325,11 @@ class _FusedMoE(torch.autograd.Function):
                             push_epoch=e1)
         out = torch.empty((T, D), device=dev, dtype=torch.bfloat16)
         rt.combine(rt.ret_y[layer], slot_pos, weights, out, sent, e1)
-        ctx.save_for_backward(x2, weights, indices32, slot_pos, counts_kept, sent, gu, w1, w3, w2)
+        # the bf16 path keeps the activation h for the w2 weight gradient (57 MB per layer at the 1B shapes: cheap next
+        # to re-reading the pre-activations); the fp8 path recomputes it from them
+        ctx.has_h = not rt.fp8
+        ctx.save_for_backward(x2, weights, indices32, slot_pos, counts_kept, sent, gu, w1, w3, w2,
+                              *([h] if ctx.has_h else []))
         ctx.rt, ctx.layer = rt, layer
         ctx.x_shape = x.shape
         if stats_mod is not None:
@@ -335,7 +339,7 @@ class _FusedMoE(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        x2, weights, indices32, slot_pos, counts_kept, sent, gu, w1, w3, w2 = ctx.saved_tensors
+        x2, weights, indices32, slot_pos, counts_kept, sent, gu, w1, w3, w2 = ctx.saved_tensors[:10]
         rt, layer = ctx.rt, ctx.layer
         T, D, K, H = rt.T, rt.D, rt.K, rt.H
         dev = dout.device
@@ -349,7 +353,7 @@ class _FusedMoE(torch.autograd.Function):
         rt.dispatch(do2, indices32, slot_pos, counts_kept, weights, rt.p_recv_g, e2)
         # dH = dY @ w2^T  (w2 [H, D] per expert is K-major for this contraction)
         dh = rt.grouped_gemm(rt.recv_g, w2, N=H, K=D, b_mn=False, group_stride_b=H, wait_epoch=e2)
-        hh = glu(gu)  # recompute the activation from the saved pre-activations
+        hh = ctx.saved_tensors[10] if ctx.has_h else glu(gu)
         dw2 = rt.grouped_wgrad(hh, rt.recv_g, w2, M=H, N=D)
         del hh
         dgu = glu_bwd(gu, dh)
