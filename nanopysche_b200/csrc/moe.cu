@@ -315,6 +315,27 @@ __global__ void __launch_bounds__(256) router_dgate_kernel(const float* __restri
   }
 }
 
+// dx[t, :] = sum_e dl[t, e] * Wg[e, :] in bf16: the router's contribution to the gradient of its input (a
+// [T, E] x [E, D] product with E of 8 to 64: one thread per 8 output columns, the gate rows come from L1).
+__global__ void __launch_bounds__(256) router_dx_kernel(const float* __restrict__ dl, const float* __restrict__ wg,
+                                                        __nv_bfloat16* __restrict__ dx, int T, int D, int E) {
+  const int vec_per_row = D >> 3;
+  const long long total = (long long)T * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / vec_per_row), d = (int)(i % vec_per_row) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int e = 0; e < E; ++e) {
+      const float g = __ldg(dl + (size_t)t * E + e);
+      const float4 w0 = __ldg(reinterpret_cast<const float4*>(wg + (size_t)e * D + d));
+      const float4 w1 = __ldg(reinterpret_cast<const float4*>(wg + (size_t)e * D + d + 4));
+      acc[0] += g * w0.x; acc[1] += g * w0.y; acc[2] += g * w0.z; acc[3] += g * w0.w;
+      acc[4] += g * w1.x; acc[5] += g * w1.y; acc[6] += g * w1.z; acc[7] += g * w1.w;
+    }
+    *reinterpret_cast<uint4*>(dx + (size_t)t * D + d) = pack8(acc);
+  }
+}
+
 __global__ void colsum2_kernel(const float* __restrict__ partial, float* __restrict__ out, int parts,
                                long long cols, int accumulate) {
   const long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -768,6 +789,15 @@ NP_API int np_router_dgate(const float* dl, const void* x, float* dwg, float* db
   const long long cols = (long long)E * D;
   colsum2_kernel<<<(int)((cols + 63) / 64), 64, 0, s>>>(scratch, dwg, parts, cols, accumulate);
   if (dbias) colsum_narrow_kernel<<<1, 1024, 0, s>>>(dl, dbias, T, E, accumulate);
+  CHECK_LAUNCH();
+}
+
+NP_API int np_router_dx(const float* dl, const float* wg, void* dx, int T, int D, int E, void* stream) {
+  if (D % 8) return 1;
+  if (T <= 0) return 0;
+  long long blocks = ((long long)T * (D / 8) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  router_dx_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(dl, wg, (__nv_bfloat16*)dx, T, D, E);
   CHECK_LAUNCH();
 }
 

@@ -74,7 +74,11 @@ class _Router(torch.autograd.Function):
         dgw = torch.empty_like(gate_w)
         dgb = torch.empty(E, device=x2.device, dtype=torch.float32)
         _lib.call("router_dgate", dl, x2, dgw, dgb, scratch, T, D, E, 0)
-        dx = (dl @ gate_w).to(x2.dtype)
+        if x2.dtype == torch.bfloat16 and gate_w.dtype == torch.float32 and gate_w.is_contiguous():
+            dx = torch.empty_like(x2)
+            _lib.call("router_dx", dl, gate_w, dx, T, D, E)
+        else:
+            dx = (dl @ gate_w.float()).to(x2.dtype)
         return dx, dgw, dgb, None, None, None, None
 
 
