@@ -49,6 +49,27 @@ __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int kk) {
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int kk) {
   return np::make_smem_desc(tile + kk * 2048, CHUNK_BYTES, 1024);
 }
+// Sources that are still arriving in this GPU's memory (a peer is pushing them): flag[idx[s]] reaches the epoch
+// once source s is complete. The TMA producer checks it before its first load from the source.
+struct SrcFlags {
+  const int* flags;     // nullptr: every source is ready at launch
+  int idx[MAX_SRC];
+  int own;                 // flag index guarding the kernel's resident operand (Q / dO or K / V), -1: none
+  int epoch;
+  const int* epoch_base;   // optional device counter added to `epoch` (keeps epochs valid under graph replay)
+  unsigned long long limit_ns;
+};
+__device__ __forceinline__ bool src_ready(const SrcFlags& f, int s, int kid) {
+  if (!f.flags) return true;
+  const int want = f.epoch + (f.epoch_base ? *f.epoch_base : 0);
+  return np::wait_flag_ge(f.flags + f.idx[s], want, f.limit_ns, kid, 200 + s);
+}
+__device__ __forceinline__ bool own_ready(const SrcFlags& f, int kid) {
+  if (!f.flags || f.own < 0) return true;
+  const int want = f.epoch + (f.epoch_base ? *f.epoch_base : 0);
+  return np::wait_flag_ge(f.flags + f.own, want, f.limit_ns, kid, 250);
+}
+
 struct FwdParams {
   __nv_bfloat16* O; long long o_sb, o_ss, o_sh;   // output strides (elements): batch, seq, head
   float* lse;                                      // [B, Hq, Sq]
@@ -58,6 +79,7 @@ struct FwdParams {
   int n_src;                                       // number of KV sources (1 without context parallelism)
   int src_blocks;                                  // 128-row KV blocks per source
   int src_len;                                     // valid KV rows per source
+  SrcFlags fl;                                     // arrival flags of the KV sources (context parallelism)
   const int* q_blk_pos;                            // [Sq/128] global position of each local Q block (nullptr: i*128 + q_off)
   const int* k_blk_pos;                            // [n_src * src_blocks] global position of each KV block (nullptr: j*128)
   int q_off;
@@ -180,12 +202,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (warp == 0) {
     if (lane == 0) {
+      if (!own_ready(p.fl, KID_ATTN)) *abort_flag = 1;
       np::mbar_expect_tx(B_(FB_Q), TILE_BYTES);
       load_tile(sQ, &tmQ, B_(FB_Q), h, qb * BQ, b);
-      int i = 0;
+      int i = 0, last_src = -1;
       for (int j = next_vis(0); j < total_blocks && !*abort_flag; j = next_vis(j + 1), ++i) {
         const int ks = i % F_KST, vs = i % F_VST;
         const int src = j / p.src_blocks, jb = j - src * p.src_blocks;
+        if (src != last_src) {
+          if (!src_ready(p.fl, src, KID_ATTN)) { *abort_flag = 1; break; }
+          last_src = src;
+        }
         if (!np::mbar_wait(B_(FB_KE + ks), ((uint32_t)(i / F_KST) & 1u) ^ 1u, abort_flag, KID_ATTN, 1)) break;
         np::mbar_expect_tx(B_(FB_K + ks), TILE_BYTES);
         load_tile(sK0 + ks * TILE_BYTES, &tmK.m[src], B_(FB_K + ks), hkv, jb * BKV, b);
@@ -367,6 +394,16 @@ int make_tmap_4d(CUtensorMap* out, const void* base, long long B, long long S, l
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+void fill_flags(SrcFlags* f, const int* flags, const int* idx, int n_src, int epoch, const int* epoch_base,
+                unsigned long long limit_ns, int own) {
+  f->flags = flags;
+  f->own = own;
+  f->epoch = epoch;
+  f->epoch_base = epoch_base;
+  f->limit_ns = limit_ns ? limit_ns : NP_WAIT_LIMIT_NS;
+  for (int s = 0; s < MAX_SRC; ++s) f->idx[s] = (flags && idx && s < n_src) ? idx[s] : 0;
+}
+
 bool bind_ctx() {
   static thread_local bool bound = false;
   if (!bound) {
@@ -392,6 +429,9 @@ struct NpAttnFwdArgs {
   const int* q_blk_pos; const int* k_blk_pos;
   int split;       // unused (two softmax threads per row)
   int lse_heads;   // heads of the lse array when q / o are a head slice of larger tensors (0: Hq)
+  // KV sources that peers are still pushing into this GPU's memory: flags[flag_idx[s]] >= flag_epoch + *epoch_base
+  const int* src_flags; const int* flag_idx; int flag_epoch; const int* epoch_base; unsigned long long flag_limit_ns;
+  int flag_own;    // 1 + flag index that guards q itself (0: none)
 };
 
 NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
@@ -419,6 +459,8 @@ NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.n_src = a->n_src; p.src_len = a->src_len; p.src_blocks = (a->src_len + BKV - 1) / BKV;
   p.q_blk_pos = a->q_blk_pos; p.k_blk_pos = a->k_blk_pos; p.q_off = a->q_off;
+  fill_flags(&p.fl, a->src_flags, a->flag_idx, a->n_src, a->flag_epoch, a->epoch_base, a->flag_limit_ns,
+             a->flag_own - 1);
   constexpr int NS = 2;   // softmax threads per row
   constexpr int SMEM = (1 + F_KST + F_VST) * TILE_BYTES + 8 * FB_COUNT + 8 + 16 + 2 * NS * 128 * 4 + 16;
   static_assert(SMEM <= 227 * 1024, "shared memory budget");
@@ -455,6 +497,7 @@ struct PtrList {
 };
 
 struct BwdParams {
+  SrcFlags fl;                     // arrival flags of the looped sources
   int B, Sq, Hq, Hkv, causal;      // Sq: rows of the (local or per-source) Q tensor
   int lse_H;                       // heads of the lse / delta arrays (>= Hq for a head slice)
   float scale, scale_log2;
@@ -535,13 +578,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {
+      if (!own_ready(p.fl, KID_ATTN_DQ)) *abort_flag = 1;
       np::mbar_expect_tx(B_(QB_QDO), 2 * TILE_BYTES);
       load_tile(sQ, &tmQ, B_(QB_QDO), h, qb * BQ, b);
       load_tile(sdO, &tmdO, B_(QB_QDO), h, qb * BQ, b);
-      int i = 0;
+      int i = 0, last_src = -1;
       for (int j = next_vis(0); j < total_blocks && !*abort_flag; j = next_vis(j + 1), ++i) {
         const int ks = i % Q_KST, vs = i % Q_VST;
         const int src = j / p.src_blocks, jb = j - src * p.src_blocks;
+        if (src != last_src) {
+          if (!src_ready(p.fl, src, KID_ATTN_DQ)) { *abort_flag = 1; break; }
+          last_src = src;
+        }
         if (!np::mbar_wait(B_(QB_KE + ks), ((uint32_t)(i / Q_KST) & 1u) ^ 1u, abort_flag, KID_ATTN_DQ, 1)) break;
         np::mbar_expect_tx(B_(QB_K + ks), TILE_BYTES);
         load_tile(sK0 + ks * TILE_BYTES, &tmK.m[src], B_(QB_K + ks), hkv, jb * BKV, b);
@@ -601,13 +649,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int row = qb * BQ + r;
     const int q_pos = q_pos0 + r;
     float lse2 = INFINITY, dlt = 0.f;
+    bool ok = own_ready(p.fl, KID_ATTN_DQ);   // lse / delta belong to the same arriving shard as Q / dO
+    if (!ok) *abort_flag = 1;
     if (row < p.Sq) {
       const size_t idx = ((size_t)b * p.lse_H + h) * p.Sq + row;
       const float l = p.lse[idx];
       lse2 = (l == -INFINITY) ? INFINITY : l * LOG2E;
       dlt = p.delta[idx];
     }
-    bool ok = true;
     int nvis = 0;
     for (int j = next_vis(0); j < total_blocks; j = next_vis(j + 1), ++nvis) {
       const int i = nvis, st = i & 1;
@@ -743,13 +792,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
 
   if (warp == 0) {
     if (lane == 0) {
+      if (!own_ready(p.fl, KID_ATTN_DKV)) *abort_flag = 1;
       np::mbar_expect_tx(B_(KB_KV), 2 * TILE_BYTES);
       load_tile(sK, &tmK, B_(KB_KV), hkv, jb * BKV, b);
       load_tile(sV, &tmV, B_(KB_KV), hkv, jb * BKV, b);
-      int i = 0;
+      int i = 0, last_src = -1;
       for (int c = next_vis(0); c < total && !*abort_flag; c = next_vis(c + 1), ++i) {
         const int qs = i % K_QST, ds = i % K_DOST;
         const int qi = c % p.src_blocks, h = hkv * n_rep + (c / p.src_blocks) % n_rep, src = c / (p.src_blocks * n_rep);
+        if (src != last_src) {
+          if (!src_ready(p.fl, src, KID_ATTN_DKV)) { *abort_flag = 1; break; }
+          last_src = src;
+        }
         if (!np::mbar_wait(B_(KB_QE + qs), ((uint32_t)(i / K_QST) & 1u) ^ 1u, abort_flag, KID_ATTN_DKV, 1)) break;
         np::mbar_expect_tx(B_(KB_Q + qs), TILE_BYTES);
         load_tile(sQ0 + qs * TILE_BYTES, &tmQ.m[src], B_(KB_Q + qs), h, qi * BQ, b);
@@ -815,12 +869,16 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int k_pos = k_pos0 + r;
     bool ok = true;
-    int nvis = 0;
+    int nvis = 0, last_src = -1;
     // every thread runs every iteration: the named barriers need all of them
     for (int c = next_vis(0); c < total; c = next_vis(c + 1), ++nvis) {
       const int i = nvis, st = i & 1;
       const int qi = c % p.src_blocks, h = hkv * n_rep + (c / p.src_blocks) % n_rep, src = c / (p.src_blocks * n_rep);
       const int q_pos0 = q_pos0_of(src, qi);
+      if (src != last_src) {   // lse / delta of a source are read below: it has to be complete
+        if (ok && !src_ready(p.fl, src, KID_ATTN_DKV)) { *abort_flag = 1; ok = false; }
+        last_src = src;
+      }
       {  // stage this Q block's log-sum-exp (threads 0-127) and delta (threads 128-255), one column each
         const int qrow = qi * BQ + (t256 & 127);
         float val = (t256 < 128) ? INFINITY : 0.f;
@@ -949,6 +1007,12 @@ struct NpAttnBwdArgs {
   const int* k_blk_pos_local; const int* q_blk_pos_all;         // for dKV: local KV blocks vs all Q blocks
   int split;                                                    // softmax threads per row: 2 (default) or 4
   int lse_heads;                                                // heads of the lse / delta arrays (0: Hq)
+  // sources still arriving (as in NpAttnFwdArgs); which = 1: the flags guard the KV sources of the dQ kernel,
+  // 2: the Q / dO / lse / delta sources of the dK/dV kernel, 3: both
+  const int* src_flags; const int* flag_idx; int flag_epoch; const int* epoch_base; unsigned long long flag_limit_ns;
+  int flag_which;
+  int skip;       // 1: no dQ kernel, 2: no dK/dV kernel
+  int flag_own;   // 1 + flag index that guards the resident operands (q, d_o, lse, delta / k, v), 0: none
 };
 
 NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
@@ -1007,17 +1071,21 @@ NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
   BwdParams pq = p;
   pq.src_blocks = kblocks; pq.src_len = a->Sk;
   pq.q_blk_pos = a->q_blk_pos_local; pq.k_blk_pos = a->k_blk_pos_all;
+  fill_flags(&pq.fl, (a->flag_which & 1) ? a->src_flags : nullptr, a->flag_idx, a->n_src, a->flag_epoch, a->epoch_base,
+             a->flag_limit_ns, a->flag_own - 1);
   // dK, dV: local KV blocks against every source's Q blocks
   BwdParams pk = p;
   pk.src_blocks = qblocks; pk.src_len = a->Sq;
   pk.q_blk_pos = a->q_blk_pos_all; pk.k_blk_pos = a->k_blk_pos_local;
+  fill_flags(&pk.fl, (a->flag_which & 2) ? a->src_flags : nullptr, a->flag_idx, a->n_src, a->flag_epoch, a->epoch_base,
+             a->flag_limit_ns, a->flag_own - 1);
   const dim3 gq(a->Hq * a->B, qblocks), gk(a->Hkv * a->B, kblocks);
   if (a->split == 4) {
-    attn_bwd_dq_kernel<4><<<gq, nthreads(4), SMEM_DQ, stream>>>(tmQ, tmdO, lK, lV, pq);
-    attn_bwd_dkv_kernel<4><<<gk, nthreads(4), SMEM_DKV, stream>>>(tmK, tmV, lQ, ldO, pk);
+    if (!(a->skip & 1)) attn_bwd_dq_kernel<4><<<gq, nthreads(4), SMEM_DQ, stream>>>(tmQ, tmdO, lK, lV, pq);
+    if (!(a->skip & 2)) attn_bwd_dkv_kernel<4><<<gk, nthreads(4), SMEM_DKV, stream>>>(tmK, tmV, lQ, ldO, pk);
   } else {
-    attn_bwd_dq_kernel<2><<<gq, nthreads(2), SMEM_DQ, stream>>>(tmQ, tmdO, lK, lV, pq);
-    attn_bwd_dkv_kernel<2><<<gk, nthreads(2), SMEM_DKV, stream>>>(tmK, tmV, lQ, ldO, pk);
+    if (!(a->skip & 1)) attn_bwd_dq_kernel<2><<<gq, nthreads(2), SMEM_DQ, stream>>>(tmQ, tmdO, lK, lV, pq);
+    if (!(a->skip & 2)) attn_bwd_dkv_kernel<2><<<gk, nthreads(2), SMEM_DKV, stream>>>(tmK, tmV, lQ, ldO, pk);
   }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 500 + (int)e;

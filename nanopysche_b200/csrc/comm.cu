@@ -108,6 +108,37 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(const uint4* __rest
   }
 }
 
+// All-to-all as peer stores: every row of `src` (row_vecs x 16 bytes) is cut into n equal slices and slice r of
+// every row is stored into rank r's buffer at [my_rank][row][slice]; with `set_flag` the last CTA releases
+// flag [my_rank] on every rank (several tensors can share one flag: only the last push sets it, stream order
+// makes the earlier ones complete first).
+__global__ void __launch_bounds__(256) a2a_push_kernel(const uint4* __restrict__ src, long long rows,
+                                                       long long row_vecs, PeerPtrs dst, PeerPtrs flags,
+                                                       int* __restrict__ ctr, int my_rank, int n, int epoch,
+                                                       const int* epoch_base, int set_flag) {
+  const long long slice_vecs = row_vecs / n;
+  const long long total = rows * row_vecs;
+  const long long base = (long long)my_rank * rows * slice_vecs;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / row_vecs, c = i - row * row_vecs;
+    const int r = (int)(c / slice_vecs);
+    reinterpret_cast<uint4*>(dst.p[r])[base + row * slice_vecs + (c - r * slice_vecs)] = src[i];
+  }
+  if (!set_flag) return;
+  const int ep = epoch + (epoch_base ? *epoch_base : 0);
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(ctr, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if ((int)threadIdx.x < n) np::st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + my_rank, ep);
+    if (threadIdx.x == 0) *ctr = 0;
+  }
+}
+
 // gshard[i] = scale * sum_r grads_r[lo + i]; partial[b] = sum of gshard^2 over this CTA's slice.
 __global__ void __launch_bounds__(256) zero_reduce_kernel(PeerPtrs grads, int n, long long lo, long long cnt,
                                                           float scale, float* __restrict__ gshard,
@@ -240,6 +271,24 @@ NP_API int np_allgather_push(const void* src, void* const* gather_ptrs, long lon
   if (g > cap) g = cap;
   allgather_push_kernel<<<(int)g, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, d, vecs, (long long)my_rank * vecs,
                                                                   f, ctr, my_rank, n, epoch, epoch_base);
+  CHECK_LAUNCH();
+}
+
+// src: [rows, row_bytes] contiguous; dst_ptrs[r]: rank r's buffer of n x rows x (row_bytes / n) bytes; the slice of
+// this rank's rows lands at index my_rank. flag_ptrs / ctr as in np_allgather_push (used when set_flag != 0).
+NP_API int np_a2a_push(const void* src, long long rows, long long row_bytes, void* const* dst_ptrs,
+                       void* const* flag_ptrs, int* ctr, int my_rank, int n, int epoch, const int* epoch_base,
+                       int set_flag, int max_ctas, void* stream) {
+  if (n > MAX_PEERS || (row_bytes % (16 * n)) || (((uintptr_t)src) & 15)) return 1;
+  if (rows <= 0) return 0;
+  PeerPtrs d, f;
+  for (int i = 0; i < n; ++i) { d.p[i] = dst_ptrs[i]; f.p[i] = flag_ptrs ? flag_ptrs[i] : nullptr; }
+  const long long vecs = rows * (row_bytes >> 4);
+  long long g = (vecs + 255) / 256;
+  const int cap = max_ctas > 0 ? max_ctas : 148 * 2;
+  if (g > cap) g = cap;
+  a2a_push_kernel<<<(int)g, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, rows, row_bytes >> 4, d, f, ctr, my_rank, n,
+                                                            epoch, epoch_base, set_flag);
   CHECK_LAUNCH();
 }
 

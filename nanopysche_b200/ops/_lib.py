@@ -84,6 +84,8 @@ class AttnFwdArgs(C.Structure):
         ("scale", c_float),
         ("q_blk_pos", c_void_p), ("k_blk_pos", c_void_p),
         ("split", c_int), ("lse_heads", c_int),
+        ("src_flags", c_void_p), ("flag_idx", c_void_p), ("flag_epoch", c_int), ("epoch_base", c_void_p),
+        ("flag_limit_ns", c_ull), ("flag_own", c_int),
     ]
 
 
@@ -106,6 +108,8 @@ class AttnBwdArgs(C.Structure):
         ("q_blk_pos_local", c_void_p), ("k_blk_pos_all", c_void_p),
         ("k_blk_pos_local", c_void_p), ("q_blk_pos_all", c_void_p),
         ("split", c_int), ("lse_heads", c_int),
+        ("src_flags", c_void_p), ("flag_idx", c_void_p), ("flag_epoch", c_int), ("epoch_base", c_void_p),
+        ("flag_limit_ns", c_ull), ("flag_which", c_int), ("skip", c_int), ("flag_own", c_int),
     ]
 
 

@@ -72,6 +72,22 @@ def _strides3(t: torch.Tensor):
     return t.stride(0), t.stride(1), t.stride(2)
 
 
+def _set_flags(a, flags, keep: list):
+    """``flags``: None, or a dict ``flags`` (int32 tensor), ``idx`` (flag index per source), ``epoch``, ``epoch_base``
+    (device counter tensor) [, ``which``] naming sources that peers are still pushing into local memory."""
+    import ctypes as C
+
+    if not flags:
+        return
+    idx = (C.c_int * len(flags["idx"]))(*[int(i) for i in flags["idx"]])
+    keep.append(idx)
+    a.src_flags, a.flag_idx = flags["flags"].data_ptr(), C.cast(idx, C.c_void_p)
+    a.flag_epoch, a.epoch_base, a.flag_limit_ns = int(flags["epoch"]), flags["epoch_base"].data_ptr(), WAIT_LIMIT_NS
+    if hasattr(a, "flag_which"):
+        a.flag_which = int(flags.get("which", 3))
+    a.flag_own = int(flags.get("own", -1)) + 1
+
+
 def flash_supported(q: torch.Tensor, k: torch.Tensor) -> bool:
     """The tcgen05 kernels cover bf16, head_dim 128, 16-byte aligned strided ``[B, S, H, 128]`` views."""
     return (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and q.shape[-1] == 128
@@ -79,7 +95,8 @@ def flash_supported(q: torch.Tensor, k: torch.Tensor) -> bool:
             and all(s % 8 == 0 for s in q.stride()[:3]) and all(s % 8 == 0 for s in k.stride()[:3]))
 
 
-def flash_fwd(q, k_list, v_list, *, causal=True, scale=None, q_off=0, q_blk_pos=None, k_blk_pos=None, split=0):
+def flash_fwd(q, k_list, v_list, *, causal=True, scale=None, q_off=0, q_blk_pos=None, k_blk_pos=None, split=0,
+              flags=None):
     """Forward flash attention on the tcgen05 kernel. ``k_list`` / ``v_list`` are lists of equally shaped
     ``[B, Sk, Hkv, 128]`` KV sources (one entry without context parallelism; one per rank's shard - any of
     them may live in a peer's memory - with it). Returns ``(out [B,Sq,Hq,128] bf16, lse [B,Hq,Sq] fp32)``."""
@@ -108,6 +125,8 @@ def flash_fwd(q, k_list, v_list, *, causal=True, scale=None, q_off=0, q_blk_pos=
     a.q_blk_pos = q_blk_pos.data_ptr() if q_blk_pos is not None else None
     a.k_blk_pos = k_blk_pos.data_ptr() if k_blk_pos is not None else None
     a.split = split
+    keep = []
+    _set_flags(a, flags, keep)
     _lib.check(_lib.lib().np_attn_fwd(C.byref(a), C.c_void_p(_lib.stream())), "attn_fwd")
     return o, lse
 
@@ -120,6 +139,7 @@ def _ptr_array(items):
 
 
 def flash_bwd(q, k, v, o, d_o, lse, *, causal=True, scale=None, q_off=0, delta=None, sources=None, phase=3, split=0,
+              flags=None, skip=0, out=None,
               q_blk_pos_local=None, k_blk_pos_all=None, k_blk_pos_local=None, q_blk_pos_all=None):
     """Backward of ``flash_fwd``: returns ``(dq, dk, dv)`` in bf16 with the shapes of q / k / v.
 
@@ -135,9 +155,16 @@ def flash_bwd(q, k, v, o, d_o, lse, *, causal=True, scale=None, q_off=0, delta=N
         delta = torch.empty((B, Hq, Sq), device=q.device, dtype=torch.float32)
     if d_o.stride(3) != 1 or any(s % 8 for s in d_o.stride()[:3]):
         d_o = d_o.contiguous()
-    dq = torch.empty((B, Sq, Hq, hd), device=q.device, dtype=torch.bfloat16) if phase & 2 else None
-    dk = torch.empty((B, Sk, Hkv, hd), device=q.device, dtype=torch.bfloat16) if phase & 2 else None
-    dv = torch.empty_like(dk) if phase & 2 else None
+    # ``out``: optional (dq, dk, dv) destinations (tensors or raw device pointers, layouts of q / k); ``skip``:
+    # 1 = no dQ kernel, 2 = no dK/dV kernel
+    dq = dk = dv = None
+    if phase & 2:
+        if out is not None:
+            dq, dk, dv = out
+        else:
+            dq = torch.empty((B, Sq, Hq, hd), device=q.device, dtype=torch.bfloat16) if not skip & 1 else None
+            dk = torch.empty((B, Sk, Hkv, hd), device=q.device, dtype=torch.bfloat16) if not skip & 2 else None
+            dv = torch.empty_like(dk) if not skip & 2 else None
     a = _lib.AttnBwdArgs()
     a.q, a.k, a.v, a.o, a.d_o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr()
     a.q_sb, a.q_ss, a.q_sh = _strides3(q)
@@ -147,16 +174,24 @@ def flash_bwd(q, k, v, o, d_o, lse, *, causal=True, scale=None, q_off=0, delta=N
     a.do_sb, a.do_ss, a.do_sh = _strides3(d_o)
     a.lse, a.delta = lse.data_ptr(), delta.data_ptr()
     if phase & 2:
-        a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
-        a.dq_sb, a.dq_ss, a.dq_sh = _strides3(dq)
-        a.dk_sb, a.dk_ss, a.dk_sh = _strides3(dk)
-    src = sources or dict(k=[k], v=[v], q=[q], d_o=[d_o], lse=[lse], delta=[delta])
+        ptr = lambda t: None if t is None else (t.data_ptr() if isinstance(t, torch.Tensor) else int(t))  # noqa: E731
+        a.dq, a.dk, a.dv = ptr(dq), ptr(dk), ptr(dv)
+        a.dq_sb, a.dq_ss, a.dq_sh = _strides3(dq) if isinstance(dq, torch.Tensor) else (Sq * Hq * hd, Hq * hd, hd)
+        a.dk_sb, a.dk_ss, a.dk_sh = _strides3(dk) if isinstance(dk, torch.Tensor) else (Sk * Hkv * hd, Hkv * hd, hd)
+    # source lists: missing entries default to the local tensors, short lists are padded to the longest one
+    defaults = dict(k=k, v=v, q=q, d_o=d_o, lse=lse, delta=delta)
+    src = dict(sources) if sources else {}
+    n_src = max([len(src.get(nm) or []) for nm in defaults] + [1])
+    for nm, dflt in defaults.items():
+        lst = [dflt if t is None else t for t in (src.get(nm) or [dflt])]
+        src[nm] = lst + [lst[0]] * (n_src - len(lst))
     keep = [_ptr_array(src[n]) for n in ("k", "v", "q", "d_o", "lse", "delta")]
     a.k_src, a.v_src, a.q_src, a.do_src, a.lse_src, a.delta_src = [x[1] for x in keep]
     a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.causal, a.n_src, a.q_off, a.phase = \
-        B, Sq, Sk, Hq, Hkv, int(causal), len(src["k"]), q_off, phase
+        B, Sq, Sk, Hq, Hkv, int(causal), n_src, q_off, phase
     a.scale = scale or 1.0 / math.sqrt(hd)
-    a.split = split
+    a.split, a.skip = split, skip
+    _set_flags(a, flags, keep)
     for name, t in (("q_blk_pos_local", q_blk_pos_local), ("k_blk_pos_all", k_blk_pos_all),
                     ("k_blk_pos_local", k_blk_pos_local), ("q_blk_pos_all", q_blk_pos_all)):
         setattr(a, name, t.data_ptr() if t is not None else None)
@@ -165,7 +200,7 @@ def flash_bwd(q, k, v, o, d_o, lse, *, causal=True, scale=None, q_off=0, delta=N
 
 
 def flash_fwd_raw(q_ptr, k_ptrs, v_ptrs, o_ptr, lse_ptr, *, like_q, like_k, heads, lse_heads, causal=True, scale=None,
-                  q_blk_pos=None, k_blk_pos=None):
+                  q_blk_pos=None, k_blk_pos=None, like_o=None, flags=None):
     """``flash_fwd`` on raw device pointers (any of them may point into a peer's memory). The tensors have the
     shapes and strides of ``like_q`` / ``like_k`` except for the head count, which is ``heads = (Hq, Hkv)``: a launch
     can cover a head slice of larger buffers. The output and the log-sum-exp are stored through ``o_ptr`` /
@@ -176,7 +211,7 @@ def flash_fwd_raw(q_ptr, k_ptrs, v_ptrs, o_ptr, lse_ptr, *, like_q, like_k, head
     a = _lib.AttnFwdArgs()
     a.q, a.o, a.lse = int(q_ptr), int(o_ptr), int(lse_ptr)
     a.q_sb, a.q_ss, a.q_sh = _strides3(like_q)
-    a.o_sb, a.o_ss, a.o_sh = _strides3(like_q)
+    a.o_sb, a.o_ss, a.o_sh = _strides3(like_o if like_o is not None else like_q)
     a.k_sb, a.k_ss, a.k_sh = _strides3(like_k)
     kk, vv = _ptr_array(k_ptrs), _ptr_array(v_ptrs)
     a.k_ptrs, a.v_ptrs = kk[1], vv[1]
@@ -186,11 +221,13 @@ def flash_fwd_raw(q_ptr, k_ptrs, v_ptrs, o_ptr, lse_ptr, *, like_q, like_k, head
     a.q_blk_pos = q_blk_pos.data_ptr() if q_blk_pos is not None else None
     a.k_blk_pos = k_blk_pos.data_ptr() if k_blk_pos is not None else None
     a.lse_heads = lse_heads
+    keep = []
+    _set_flags(a, flags, keep)
     _lib.check(_lib.lib().np_attn_fwd(C.byref(a), C.c_void_p(_lib.stream())), "attn_fwd")
 
 
 def flash_bwd_raw(ptr, src, *, lse, delta, like_q, like_k, heads, lse_heads, causal=True, scale=None, blk_local=None,
-                  blk_all=None):
+                  blk_all=None, like_dq=None, like_dk=None, flags=None):
     """dQ and dK/dV kernels on raw device pointers. ``ptr``: dict ``q, d_o, k, v, dq, dk, dv`` of the tensors this
     launch owns (inputs of the layouts of ``like_q`` / ``like_k`` with ``heads = (Hq, Hkv)`` heads; the gradients
     are stored through ``dq / dk / dv``); ``src``: dict of per-rank pointer lists ``k, v, q, d_o, lse, delta``."""
@@ -203,9 +240,9 @@ def flash_bwd_raw(ptr, src, *, lse, delta, like_q, like_k, heads, lse_heads, cau
     a.lse, a.delta = int(lse), int(delta)
     a.q_sb, a.q_ss, a.q_sh = _strides3(like_q)
     a.do_sb, a.do_ss, a.do_sh = _strides3(like_q)
-    a.dq_sb, a.dq_ss, a.dq_sh = _strides3(like_q)
+    a.dq_sb, a.dq_ss, a.dq_sh = _strides3(like_dq if like_dq is not None else like_q)
     a.k_sb, a.k_ss, a.k_sh = _strides3(like_k)
-    a.dk_sb, a.dk_ss, a.dk_sh = _strides3(like_k)
+    a.dk_sb, a.dk_ss, a.dk_sh = _strides3(like_dk if like_dk is not None else like_k)
     keep = [_ptr_array(src[n]) for n in ("k", "v", "q", "d_o", "lse", "delta")]
     a.k_src, a.v_src, a.q_src, a.do_src, a.lse_src, a.delta_src = [x[1] for x in keep]
     a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.causal, a.n_src, a.q_off, a.phase = \
@@ -214,6 +251,7 @@ def flash_bwd_raw(ptr, src, *, lse, delta, like_q, like_k, heads, lse_heads, cau
     a.lse_heads = lse_heads
     a.q_blk_pos_local = a.k_blk_pos_local = blk_local.data_ptr() if blk_local is not None else None
     a.k_blk_pos_all = a.q_blk_pos_all = blk_all.data_ptr() if blk_all is not None else None
+    _set_flags(a, flags, keep)
     _lib.check(_lib.lib().np_attn_bwd(C.byref(a), C.c_void_p(_lib.stream())), "attn_bwd")
 
 
