@@ -40,6 +40,10 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
   float2 a = np::unpack_bf16(u.x), b = np::unpack_bf16(u.y), c = np::unpack_bf16(u.z), d = np::unpack_bf16(u.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
 }
+__device__ __forceinline__ void ld8f(const float* p, float* f) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
 __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
   float2 a = np::unpack_bf16(u.x), b = np::unpack_bf16(u.y), c = np::unpack_bf16(u.z), d = np::unpack_bf16(u.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
@@ -229,6 +233,74 @@ __global__ void __launch_bounds__(256) colsum_tall_kernel(const float* __restric
   }
 }
 
+// RMSNorm backward with one warp per row (cols == 256 * VPL <= 2048): no block-wide reduction per row, so all rows
+// of the grid are in flight at once. Every warp adds its dw contributions into a private shared-memory row
+// (deterministic: no atomics); the eight rows are summed into one partial per CTA at the end. The row is read
+// twice, the second time from L1, to keep the register count low enough for three CTAs per SM.
+template <int VPL>
+__global__ void __launch_bounds__(NT) rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                              const __nv_bfloat16* __restrict__ x,
+                                                              const float* __restrict__ w,
+                                                              const float* __restrict__ rstd,
+                                                              const __nv_bfloat16* __restrict__ dres,
+                                                              __nv_bfloat16* __restrict__ dx,
+                                                              float* __restrict__ dw_partial, int rows, int cols) {
+  extern __shared__ float s_dw[];   // [8 warps][cols]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* mine = s_dw + (size_t)warp * cols;
+  for (int i = lane; i < cols; i += 32) mine[i] = 0.f;
+  __syncwarp();
+  for (int r = blockIdx.x * 8 + warp; r < rows; r += gridDim.x * 8) {
+    const float rs = rstd[r];
+    const __nv_bfloat16* gy = dy + (size_t)r * cols;
+    const __nv_bfloat16* xr = x + (size_t)r * cols;
+    float dot = 0.f;
+#pragma unroll 2
+    for (int i = 0; i < VPL; ++i) {
+      const int c = (lane + 32 * i) * 8;
+      float g[8], xv[8], ww[8];
+      load8(gy + c, g);
+      load8(xr + c, xv);
+      ld8f(w + c, ww);
+      float4 a0 = *reinterpret_cast<float4*>(mine + c), a1 = *reinterpret_cast<float4*>(mine + c + 4);
+      float acc[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = xv[j] * rs;
+        acc[j] += g[j] * xh;
+        dot += g[j] * ww[j] * xh;
+      }
+      *reinterpret_cast<float4*>(mine + c) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(mine + c + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+    dot = np::warp_sum(dot) / (float)cols;
+#pragma unroll 2
+    for (int i = 0; i < VPL; ++i) {
+      const int c = (lane + 32 * i) * 8;
+      float g[8], xv[8], ww[8], o[8];
+      load8(gy + c, g);
+      load8(xr + c, xv);
+      ld8f(w + c, ww);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rs * (g[j] * ww[j] - xv[j] * rs * dot);
+      if (dres) {
+        float t[8];
+        load8(dres + (size_t)r * cols + c, t);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += t[j];
+      }
+      store8(dx + (size_t)r * cols + c, o);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < cols; c += NT) {
+    float t = 0.f;
+#pragma unroll
+    for (int ww = 0; ww < 8; ++ww) t += s_dw[(size_t)ww * cols + c];
+    dw_partial[(size_t)blockIdx.x * cols + c] = t;
+  }
+}
+
 // ------------------------------------------------------------------ SwiGLU / GeGLU
 __device__ __forceinline__ float gelu_tanh_f(float x) {
   const float k = 0.7978845608028654f;
@@ -410,10 +482,6 @@ __device__ __forceinline__ float group8_sum(float v, unsigned mask) {
   v += __shfl_xor_sync(mask, v, 2);
   v += __shfl_xor_sync(mask, v, 4);
   return v;
-}
-__device__ __forceinline__ void ld8f(const float* p, float* f) {
-  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
 }
 
 __global__ void __launch_bounds__(256) qkv_norm_rope_fwd_kernel(
@@ -790,10 +858,22 @@ static void launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, co
                                cudaStream_t s) {
 #define RB(V) rmsnorm_bwd_kernel<V><<<grid, NT, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, \
                                                        (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, rows, cols)
-  if (cols <= NT * 8) RB(1);
+#define RBW(V) rmsnorm_bwd_warp_kernel<V><<<grid, NT, 8 * cols * sizeof(float), s>>>( \
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, \
+      rows, cols)
+  static bool attr_set = false;
+  if (!attr_set) {   // the warp-per-row kernels keep 8 x cols floats in shared memory (64 KB at 2048 columns)
+    cudaFuncSetAttribute(rmsnorm_bwd_warp_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2048 * 4);
+    cudaFuncSetAttribute(rmsnorm_bwd_warp_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 1024 * 4);
+    attr_set = true;
+  }
+  if (cols == 2048) RBW(8);
+  else if (cols == 1024) RBW(4);
+  else if (cols <= NT * 8) RB(1);
   else if (cols <= NT * 16) RB(2);
   else RB(4);
 #undef RB
+#undef RBW
   colsum_tall_kernel<<<(cols + 31) / 32, 256, 0, s>>>(scratch, dw, grid, cols, accumulate_dw);
 }
 

@@ -90,7 +90,7 @@ def test_linear_autograd_matches_torch():
     assert w2.grad is None and rel(w2.main_grad, 2 * wr.grad) < 1e-3
 
 
-@pytest.mark.parametrize("rows,cols", [(64, 256), (4096, 2048), (33, 4096), (7, 8192)])
+@pytest.mark.parametrize("rows,cols", [(64, 256), (4096, 2048), (300, 1024), (5, 2048), (33, 4096), (7, 8192)])
 def test_rmsnorm_fwd_bwd(rows, cols):
     from nanopysche_b200.ops.norm import rms_norm, rms_norm_ref
 
