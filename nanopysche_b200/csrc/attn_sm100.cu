@@ -60,7 +60,7 @@ struct SrcFlags {
   unsigned long long limit_ns;
 };
 __device__ __forceinline__ bool src_ready(const SrcFlags& f, int s, int kid) {
-  if (!f.flags) return true;
+  if (!f.flags || f.idx[s] < 0) return true;   // negative index: the source was produced by this GPU itself
   const int want = f.epoch + (f.epoch_base ? *f.epoch_base : 0);
   return np::wait_flag_ge(f.flags + f.idx[s], want, f.limit_ns, kid, 200 + s);
 }

@@ -53,6 +53,12 @@ struct GemmParams {
   const int* epoch_base;      // optional device counter added to `epoch` (keeps epochs valid under graph replay)
   const int* b_ready_flags;   // arrival flags of the B operand: flag i covers B rows [i * b_rows_per_flag, ...)
   int b_rows_per_flag;
+  // Rows of A (K-major) / B (K-major) that this GPU produced itself are read from their source tensor through a
+  // second tensor map, so nothing in this kernel waits for a copy made by another kernel of the same GPU.
+  int a_loc_lo, a_loc_hi;     // A rows [lo, hi) come from tmAloc (row index - lo)
+  int b_loc_lo, b_loc_hi;     // B rows [lo, hi) come from tmBloc
+  int b_local_flag;           // index into b_ready_flags that needs no wait (the local shard), -1: none
+  int m_rot, n_rot;           // tile order starts at this M / N block (the local shard first)
 };
 
 template <class F>
@@ -91,7 +97,8 @@ struct Tile {
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmAloc,
+                 const __grid_constant__ CUtensorMap tmBloc, const GemmParams p) {
   constexpr int A_BYTES = BM * BK * 2;
   constexpr int B_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -157,6 +164,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int within = r - band * per_band;
     tl.m_blk = first_m + within % gsize;
     tl.n_blk = within / gsize;
+    if (p.m_rot) tl.m_blk = (tl.m_blk + p.m_rot) % m_blocks;
+    if (p.n_rot) tl.n_blk = (tl.n_blk + p.n_rot) % n_blocks;
     return tl;
   };
   // rows of this M block that carry data (0 = nothing to do); waits for the arrival flag first.
@@ -164,7 +173,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (p.mode != 1) return BM;
     if (p.ready_flags) {
       const int fi = p.mblk_flag ? p.mblk_flag[tl.m_blk] : 0;
-      if (!np::wait_flag_ge(p.ready_flags + fi, epoch, p.flag_limit_ns, KID_GEMM, 100 + role)) {
+      if (fi >= 0 && !np::wait_flag_ge(p.ready_flags + fi, epoch, p.flag_limit_ns, KID_GEMM, 100 + role)) {
         *abort_flag = 1;
         return -1;
       }
@@ -193,7 +202,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!p.b_ready_flags) return true;
           const int f0 = (int)(r0 / p.b_rows_per_flag), f1 = (int)(r1 / p.b_rows_per_flag);
           for (int f = f0 > b_flag_hi ? f0 : b_flag_hi + 1; f <= f1; ++f)
-            if (!np::wait_flag_ge(p.b_ready_flags + f, epoch, p.flag_limit_ns, KID_GEMM, 110)) {
+            if (f != p.b_local_flag && !np::wait_flag_ge(p.b_ready_flags + f, epoch, p.flag_limit_ns, KID_GEMM, 110)) {
               *abort_flag = 1;
               return false;
             }
@@ -214,7 +223,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t sB = sA + A_BYTES;
           np::mbar_expect_tx(full_bar(stage), STAGE_BYTES);
           if (!p.a_mn) {
-            np::tma_load_2d(sA, &tmA, full_bar(stage), k0, m0);
+            if (m0 >= p.a_loc_lo && m0 < p.a_loc_hi) np::tma_load_2d(sA, &tmAloc, full_bar(stage), k0, m0 - p.a_loc_lo);
+            else np::tma_load_2d(sA, &tmA, full_bar(stage), k0, m0);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
@@ -224,6 +234,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (p.epilogue == 1) {
               np::tma_load_2d(sB, &tmB, full_bar(stage), k0, (int)brow);
               np::tma_load_2d(sB + (BN / 2) * BK * 2, &tmB2, full_bar(stage), k0, (int)brow);
+            } else if (brow >= p.b_loc_lo && brow < p.b_loc_hi) {
+              np::tma_load_2d(sB, &tmBloc, full_bar(stage), k0, (int)brow - p.b_loc_lo);
             } else {
               np::tma_load_2d(sB, &tmB, full_bar(stage), k0, (int)brow);
             }
@@ -508,11 +520,17 @@ struct NpGemmArgs {
   // B arriving in row shards (a sharded weight being all-gathered while the GEMM runs): the producer waits for
   // the flag of every shard a tile touches before it loads from it
   const int* b_ready_flags; int b_rows_per_flag;
+  // Local shard read in place (K-major operands only): A rows [a_loc_lo, a_loc_hi) from A_loc (row 0 = a_loc_lo),
+  // B rows [b_loc_lo, b_loc_hi) from B_loc; the block boundaries must be multiples of the tile size. b_local_flag:
+  // 1 + index of the B flag that needs no wait (0: none). m_rot / n_rot: first M / N block of the tile order.
+  const void* A_loc; long long lda_loc; int a_loc_lo, a_loc_hi;
+  const void* B_loc; long long ldb_loc; int b_loc_lo, b_loc_hi;
+  int b_local_flag, m_rot, n_rot;
 };
 
 template <int BN, int STAGES>
 static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
-  CUtensorMap tmA, tmB, tmB2;
+  CUtensorMap tmA, tmB, tmB2, tmAloc, tmBloc;
   int rc;
   if (!a.a_mn) rc = np_make_tmap_2d(&tmA, a.A, 2, (uint64_t)a.a_rows, (uint64_t)a.K, (uint64_t)a.lda, BK, BM);
   else rc = np_make_tmap_2d(&tmA, a.A, 2, (uint64_t)a.a_rows, (uint64_t)a.M, (uint64_t)a.lda, 64, BK);
@@ -526,7 +544,23 @@ static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
     rc = np_make_tmap_2d(&tmB2, a.B2, 2, (uint64_t)a.b_rows, (uint64_t)a.K, (uint64_t)a.ldb, BK, b_box_rows);
     if (rc) return 300 + rc;
   }
+  tmAloc = tmA;
+  tmBloc = tmB;
   GemmParams p{};
+  p.b_local_flag = a.b_local_flag - 1;
+  p.m_rot = a.m_rot; p.n_rot = a.n_rot;
+  if (a.A_loc && !a.a_mn && a.a_loc_hi > a.a_loc_lo && a.a_loc_lo % BM == 0) {
+    rc = np_make_tmap_2d(&tmAloc, a.A_loc, 2, (uint64_t)(a.a_loc_hi - a.a_loc_lo), (uint64_t)a.K, (uint64_t)a.lda_loc, BK, BM);
+    if (rc) return 600 + rc;
+    p.a_loc_lo = a.a_loc_lo; p.a_loc_hi = a.a_loc_hi;
+  }
+  if (a.B_loc && !a.b_mn && a.epilogue != 1 && a.b_loc_hi > a.b_loc_lo && a.b_loc_lo % b_box_rows == 0 &&
+      (a.b_loc_hi - a.b_loc_lo) % b_box_rows == 0) {
+    rc = np_make_tmap_2d(&tmBloc, a.B_loc, 2, (uint64_t)(a.b_loc_hi - a.b_loc_lo), (uint64_t)a.K, (uint64_t)a.ldb_loc, BK,
+                         b_box_rows);
+    if (rc) return 700 + rc;
+    p.b_loc_lo = a.b_loc_lo; p.b_loc_hi = a.b_loc_hi;
+  }
   p.C = a.C; p.C2 = a.C2; p.M = a.M; p.N = a.N; p.K = a.K; p.ldc = a.ldc; p.ldc2 = a.ldc2;
   p.a_mn = a.a_mn; p.b_mn = a.b_mn; p.out_f32 = a.out_f32; p.accumulate = a.accumulate;
   p.epilogue = a.epilogue; p.mode = a.mode; p.alpha = a.alpha;
@@ -559,7 +593,7 @@ static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
   int cap = a.max_ctas > 0 ? a.max_ctas : g_num_sms;
   int grid = (int)(tiles < cap ? tiles : cap);
   if (grid <= 0) return 0;
-  gemm_bf16_kernel<BN, STAGES><<<grid, 192, SMEM, stream>>>(tmA, tmB, tmB2, p);
+  gemm_bf16_kernel<BN, STAGES><<<grid, 192, SMEM, stream>>>(tmA, tmB, tmB2, tmAloc, tmBloc, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 500 + (int)e;
 }

@@ -41,6 +41,9 @@ class GemmArgs(C.Structure):
         ("bn", c_int), ("max_ctas", c_int),
         ("Cin", c_void_p), ("ldcin", c_ll), ("epoch_base", c_void_p),
         ("b_ready_flags", c_void_p), ("b_rows_per_flag", c_int),
+        ("A_loc", c_void_p), ("lda_loc", c_ll), ("a_loc_lo", c_int), ("a_loc_hi", c_int),
+        ("B_loc", c_void_p), ("ldb_loc", c_ll), ("b_loc_lo", c_int), ("b_loc_hi", c_int),
+        ("b_local_flag", c_int), ("m_rot", c_int), ("n_rot", c_int),
     ]
 
 

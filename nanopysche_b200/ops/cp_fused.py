@@ -102,24 +102,32 @@ class CPRuntime:
             # without the zig-zag layout a rank may never touch some source, so the flags alone do not keep a
             # fast rank from overwriting a buffer a slow one still reads
             self.heap.barrier(attn_ops.WAIT_LIMIT_NS)
-        self.stage[0].copy_(k)
-        self.stage[1].copy_(v)
         h = self.heap
         e = h.next_epoch()
+        # The push is an ordinary kernel on the same stream: it has left this GPU before the attention kernel starts,
+        # and what overlaps the attention is the *peers'* pushes, which arrive while the kernel works on the local
+        # shard (read from k / v directly) and on the sources that are already complete. Running the push next to the
+        # attention kernel on a second stream deadlocks once the attention grid exceeds one wave: the block
+        # scheduler issues the push's CTAs only after all attention CTAs have been issued, while the resident
+        # attention CTAs of every rank wait for each other's push.
+        self.stage[0].copy_(k)
+        self.stage[1].copy_(v)
         _lib.check(_lib.lib().np_allgather_push(
-            C.c_void_p(self.stage.data_ptr()), h.host_ptr_array(self.gather[par]), C.c_longlong(self.stage.numel() * 2),
-            h.host_ptr_array(self.flags[par]), C.c_void_p(self.ctr.data_ptr()), self.rank, self.cp, e,
-            C.c_void_p(h.epoch_base.data_ptr()), 64, C.c_void_p(_lib.stream())), "cp_gather_push")
+            C.c_void_p(self.stage.data_ptr()), h.host_ptr_array(self.gather[par]),
+            C.c_longlong(self.stage.numel() * 2), h.host_ptr_array(self.flags[par]), C.c_void_p(self.ctr.data_ptr()),
+            self.rank, self.cp, e, C.c_void_p(h.epoch_base.data_ptr()), 0, C.c_void_p(_lib.stream())),
+            "cp_gather_push")
         g = self.gather[par]
-        flags = dict(flags=self.flags[par], idx=self.order, epoch=e, epoch_base=h.epoch_base, which=1)
-        return [g[r, 0] for r in self.order], [g[r, 1] for r in self.order], flags
+        flags = dict(flags=self.flags[par], idx=[-1] + self.order[1:], epoch=e, epoch_base=h.epoch_base, which=1)
+        return [k] + [g[r, 0] for r in self.order[1:]], [v] + [g[r, 1] for r in self.order[1:]], flags
 
     # -- forward / backward ---------------------------------------------------------------------------
     def forward(self, q, k, v, causal: bool, scale: Optional[float]):
         self._ensure(q, k)
         ks, vs, flags = self._gather_kv(k, v, causal)
-        return attn_ops.flash_fwd(q, ks, vs, causal=causal, scale=scale, q_blk_pos=self.blk_local,
-                                  k_blk_pos=self.blk_all, flags=flags)
+        res = attn_ops.flash_fwd(q, ks, vs, causal=causal, scale=scale, q_blk_pos=self.blk_local,
+                                 k_blk_pos=self.blk_all, flags=flags)
+        return res
 
     def backward(self, q, k, v, o, d_o, lse, causal: bool, scale: Optional[float]):
         ks, vs, flags = self._gather_kv(k, v, causal)

@@ -51,6 +51,7 @@ class FSDPRuntime:
         self.sent = torch.ones(self.n, dtype=torch.int32, device=self.device)
         self._calls = 0
         self._tables: dict = {}
+
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
@@ -86,11 +87,13 @@ class FSDPRuntime:
         _lib.check(_lib.lib().np_allgather_push(
             C.c_void_p(w_shard.data_ptr()), h.host_ptr_array(self.gather[par]), C.c_longlong(ns * K * 2),
             h.host_ptr_array(self.ag_flags[par]), C.c_void_p(self.ctr.data_ptr()), self.rank, self.n, e,
-            C.c_void_p(h.epoch_base.data_ptr()), 32, C.c_void_p(_lib.stream())), "fsdp_gather_push")
+            C.c_void_p(h.epoch_base.data_ptr()), 0, C.c_void_p(_lib.stream())), "fsdp_gather_push")
         return self.gather[par][: ns * self.n * K].view(ns * self.n, K), self.ag_flags[par], e
 
-    def gemm_b_arriving(self, A, W_full, flags, epoch, rows_per_flag, *, b_mn: bool):
-        """``A @ W^T`` (``b_mn=False``) or ``A @ W`` (``b_mn=True``) while W's row shards are still arriving."""
+    def gemm_b_arriving(self, A, W_full, flags, epoch, rows_per_flag, *, b_mn: bool, w_local=None):
+        """``A @ W^T`` (``b_mn=False``) or ``A @ W`` (``b_mn=True``) while W's row shards are still arriving. With
+        ``w_local`` (this rank's shard, forward layout only) the own rows are read from it without a flag and their
+        tiles come first."""
         M, K = A.shape
         N = W_full.shape[1] if b_mn else W_full.shape[0]
         out = torch.empty((M, N), device=A.device, dtype=torch.bfloat16)
@@ -101,6 +104,12 @@ class FSDPRuntime:
         g.M, g.N, g.K = M, N, K
         g.b_mn, g.mode, g.alpha = int(b_mn), 0, 1.0
         g.b_ready_flags, g.b_rows_per_flag = flags.data_ptr(), rows_per_flag
+        if w_local is not None and not b_mn and rows_per_flag % 256 == 0:
+            g.B_loc, g.ldb_loc = w_local.data_ptr(), w_local.stride(0)
+            g.b_loc_lo, g.b_loc_hi = self.rank * rows_per_flag, (self.rank + 1) * rows_per_flag
+            g.b_local_flag = self.rank + 1
+            g.bn = 256
+            g.n_rot = self.rank * rows_per_flag // 256
         g.epoch, g.flag_limit_ns = epoch, WAIT_LIMIT_NS
         g.epoch_base = self.heap.epoch_base.data_ptr()
         _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "fsdp_gemm")
@@ -144,7 +153,7 @@ class _ShardedLinear(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         x2 = x2 if x2.is_contiguous() else x2.contiguous()
         full, flags, e = rt.gather_push(w_shard)
-        y = rt.gemm_b_arriving(x2, full, flags, e, w_shard.shape[0], b_mn=False)
+        y = rt.gemm_b_arriving(x2, full, flags, e, w_shard.shape[0], b_mn=False, w_local=w_shard)
         ctx.save_for_backward(x2, w_shard)
         ctx.rt, ctx.x_shape = rt, x.shape
         return y.view(*x.shape[:-1], full.shape[0])

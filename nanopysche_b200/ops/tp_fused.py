@@ -54,6 +54,10 @@ class TPRuntime:
         owner, local = r // self.Ms, r % self.Ms
         self.row_dst = (owner << 40) | (local * self.N + self.rank)
         self.mblk_owner = ((torch.arange(rows // 128, device=self.device) * 128) // self.Ms).to(torch.int32)
+        # for the all-gather -> GEMM: this rank's own rows are read in place (flag index -1 = no wait)
+        self.mblk_owner_remote = torch.where(self.mblk_owner == self.rank, torch.full_like(self.mblk_owner, -1),
+                                             self.mblk_owner)
+
         self.done_expected = torch.full((self.N,), self.Ms // 128, dtype=torch.int32, device=self.device)
         self.done_counters = torch.zeros(self.N, dtype=torch.int32, device=self.device)
         self.ctr = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -68,7 +72,11 @@ class TPRuntime:
 
     # -- building blocks -------------------------------------------------------------------------------
     def all_gather_push(self, x_shard: torch.Tensor) -> tuple:
-        """Push this rank's ``[Ms, cols]`` shard to every rank; returns (local gather view [M, cols], epoch)."""
+        """Push this rank's ``[Ms, cols]`` shard to every rank; returns (local gather view [M, cols], epoch).
+
+        The push is an ordinary kernel on the same stream; what the GEMM that follows overlaps is the *peers'* pushes:
+        it reads this rank's own rows straight from ``x_shard``, computes their tiles first and waits inside the
+        kernel for a peer's rows only when it reaches them."""
         Ms, cols = x_shard.shape
         assert Ms == self.Ms and cols <= self.max_cols and x_shard.is_contiguous()
         e = self.heap.next_epoch()
@@ -76,11 +84,12 @@ class TPRuntime:
         _lib.check(_lib.lib().np_allgather_push(
             C.c_void_p(x_shard.data_ptr()), h.host_ptr_array(self.gather), C.c_longlong(Ms * cols * 2),
             h.host_ptr_array(self.ag_flags), C.c_void_p(self.ctr.data_ptr()), self.rank, self.N, e,
-            C.c_void_p(h.epoch_base.data_ptr()), 32, C.c_void_p(_lib.stream())), "allgather_push")
+            C.c_void_p(h.epoch_base.data_ptr()), 0, C.c_void_p(_lib.stream())), "allgather_push")
         return self.gather[: self.M * cols].view(self.M, cols), e
 
-    def gemm_wait(self, A, B, *, b_mn: bool, epoch: int, out_dtype=torch.bfloat16):
-        """``A @ B^T`` where A is the gather buffer: each M block waits for its owner's arrival flag."""
+    def gemm_wait(self, A, B, *, b_mn: bool, epoch: int, out_dtype=torch.bfloat16, a_local=None):
+        """``A @ B^T`` where A is the gather buffer: each M block waits for its owner's arrival flag. With
+        ``a_local`` (this rank's shard) the own rows are read from it, need no flag and are computed first."""
         M, K = A.shape
         N = B.shape[1] if b_mn else B.shape[0]
         out = torch.empty((M, N), device=A.device, dtype=out_dtype)
@@ -91,6 +100,11 @@ class TPRuntime:
         g.M, g.N, g.K = M, N, K
         g.b_mn, g.mode, g.alpha = int(b_mn), 1, 1.0
         g.ready_flags, g.mblk_flag = self.ag_flags.data_ptr(), self.mblk_owner.data_ptr()
+        if a_local is not None:
+            g.mblk_flag = self.mblk_owner_remote.data_ptr()
+            g.A_loc, g.lda_loc = a_local.data_ptr(), a_local.stride(0)
+            g.a_loc_lo, g.a_loc_hi = self.rank * self.Ms, (self.rank + 1) * self.Ms
+            g.m_rot = self.rank * self.Ms // 128
         g.epoch, g.flag_limit_ns = epoch, WAIT_LIMIT_NS
         g.epoch_base = self.heap.epoch_base.data_ptr()
         _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "tp_gemm_wait")
@@ -132,7 +146,7 @@ class _AGLinear(torch.autograd.Function):
         xs = x_shard.reshape(-1, x_shard.shape[-1])
         xs = xs if xs.is_contiguous() else xs.contiguous()
         full, e = rt.all_gather_push(xs)
-        y = rt.gemm_wait(full, w, b_mn=False, epoch=e)
+        y = rt.gemm_wait(full, w, b_mn=False, epoch=e, a_local=xs)
         ctx.save_for_backward(full.clone(), w)  # the gather buffer is reused by the next layer
         ctx.rt = rt
         ctx.x_shape = x_shard.shape
@@ -166,7 +180,7 @@ class _LinearRS(torch.autograd.Function):
         dys = dy_shard.reshape(-1, dy_shard.shape[-1])
         dys = dys if dys.is_contiguous() else dys.contiguous()
         dy_full, e = rt.all_gather_push(dys)
-        dx = rt.gemm_wait(dy_full, w, b_mn=True, epoch=e)
+        dx = rt.gemm_wait(dy_full, w, b_mn=True, epoch=e, a_local=dys)
         dw = None
         if ctx.needs_input_grad[1] or hasattr(w, "main_grad"):
             dw = _wgrad_into(w, dy_full, x2)  # runs after the dgrad GEMM, which has seen every flag

@@ -83,7 +83,7 @@ def main(argv=None):
     # all-gather -> GEMM
     def ag_fused():
         g, e = rt.all_gather_push(x_shard)
-        rt.gemm_wait(g, w_col, b_mn=False, epoch=e)
+        rt.gemm_wait(g, w_col, b_mn=False, epoch=e, a_local=x_shard)
 
     def ag_base():
         dist.all_gather_into_tensor(full, x_shard)
@@ -111,7 +111,7 @@ def main(argv=None):
 
     def fsdp_fused():
         wf, flags, e = frt.gather_push(w_shard)
-        frt.gemm_b_arriving(x, wf, flags, e, w_shard.shape[0], b_mn=False)
+        frt.gemm_b_arriving(x, wf, flags, e, w_shard.shape[0], b_mn=False, w_local=w_shard)
 
     def fsdp_base():
         dist.all_gather_into_tensor(w_full, w_shard)
