@@ -70,6 +70,47 @@ __device__ __forceinline__ bool own_ready(const SrcFlags& f, int kid) {
   return np::wait_flag_ge(f.flags + f.own, want, f.limit_ns, kid, 250);
 }
 
+// All-gather of this rank's K|V shard issued by the attention kernel itself: chunks are taken from an atomic
+// counter by whichever CTAs run first (the grid may be several waves deep, so no chunk may be tied to a CTA that
+// has not started), stored into every peer's gather buffer, and the CTA that completes the last chunk releases
+// this rank's arrival flag on the peers. `ctr` ([2] ints) is zeroed by the host before the launch.
+struct PushArgs {
+  const uint4* src[2];      // K and V shards (contiguous)
+  long long vecs_each;      // 16-byte vectors per shard
+  uint4* dst[MAX_SRC];      // peer gather slots of this rank: K at [0, vecs_each), V behind it
+  int* flag[MAX_SRC];
+  int n;                    // peers to push to (0: no push)
+  int* ctr;
+  int epoch;
+  const int* epoch_base;
+};
+__device__ __forceinline__ void push_kv(const PushArgs& a) {
+  if (a.n <= 0) return;
+  __shared__ int s_chunk;
+  constexpr long long CH = 2048;   // vectors per chunk (32 KB)
+  const long long total = 2 * a.vecs_each;
+  const int nch = (int)((total + CH - 1) / CH);
+  for (;;) {
+    if (threadIdx.x == 0) s_chunk = atomicAdd(&a.ctr[0], 1);
+    __syncthreads();
+    const int c = s_chunk;
+    __syncthreads();
+    if (c >= nch) break;
+    const long long hi = (c + 1) * CH < total ? (c + 1) * CH : total;
+    for (long long i = c * CH + threadIdx.x; i < hi; i += blockDim.x) {
+      const uint4 v = i < a.vecs_each ? a.src[0][i] : a.src[1][i - a.vecs_each];
+      for (int r = 0; r < a.n; ++r) a.dst[r][i] = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(&a.ctr[1], 1) == nch - 1) {
+      __threadfence_system();
+      const int ep = a.epoch + (a.epoch_base ? *a.epoch_base : 0);
+      for (int r = 0; r < a.n; ++r) np::st_release_sys(a.flag[r], ep);
+    }
+  }
+}
+
 struct FwdParams {
   __nv_bfloat16* O; long long o_sb, o_ss, o_sh;   // output strides (elements): batch, seq, head
   float* lse;                                      // [B, Hq, Sq]
@@ -80,6 +121,7 @@ struct FwdParams {
   int src_blocks;                                  // 128-row KV blocks per source
   int src_len;                                     // valid KV rows per source
   SrcFlags fl;                                     // arrival flags of the KV sources (context parallelism)
+  PushArgs push;                                   // this rank's K|V shard, pushed by the kernel's first CTAs
   const int* q_blk_pos;                            // [Sq/128] global position of each local Q block (nullptr: i*128 + q_off)
   const int* k_blk_pos;                            // [n_src * src_blocks] global position of each KV block (nullptr: j*128)
   int q_off;
@@ -199,6 +241,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   np::tc_fence_after();
   const uint32_t tmem = *tmem_ptr_smem;
   const uint32_t tO = tmem + F_O;
+  push_kv(p.push);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -394,6 +437,18 @@ int make_tmap_4d(CUtensorMap* out, const void* base, long long B, long long S, l
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+template <class A>
+int fill_push(PushArgs* q, const A* a) {
+  q->n = 0;
+  if (!a->push_k || a->push_n <= 0) return 0;
+  if (a->push_n > MAX_SRC || (a->push_bytes & 15) || (((uintptr_t)a->push_k | (uintptr_t)a->push_v) & 15)) return 1;
+  q->src[0] = (const uint4*)a->push_k; q->src[1] = (const uint4*)a->push_v;
+  q->vecs_each = a->push_bytes >> 4;
+  q->n = a->push_n; q->ctr = a->push_ctr; q->epoch = a->flag_epoch; q->epoch_base = a->epoch_base;
+  for (int r = 0; r < a->push_n; ++r) { q->dst[r] = (uint4*)a->push_dst[r]; q->flag[r] = a->push_flag[r]; }
+  return 0;
+}
+
 void fill_flags(SrcFlags* f, const int* flags, const int* idx, int n_src, int epoch, const int* epoch_base,
                 unsigned long long limit_ns, int own) {
   f->flags = flags;
@@ -432,6 +487,10 @@ struct NpAttnFwdArgs {
   // KV sources that peers are still pushing into this GPU's memory: flags[flag_idx[s]] >= flag_epoch + *epoch_base
   const int* src_flags; const int* flag_idx; int flag_epoch; const int* epoch_base; unsigned long long flag_limit_ns;
   int flag_own;    // 1 + flag index that guards q itself (0: none)
+  // this rank's K|V shard pushed by the kernel itself: push_bytes of push_k then push_v to push_dst[r] (r < push_n),
+  // then *push_flag[r] = flag_epoch (+ *epoch_base); push_ctr: two local ints the caller zeroes before the launch
+  const void* push_k; const void* push_v; long long push_bytes; void* const* push_dst; int* const* push_flag;
+  int push_n; int* push_ctr;
 };
 
 NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
@@ -461,6 +520,7 @@ NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
   p.q_blk_pos = a->q_blk_pos; p.k_blk_pos = a->k_blk_pos; p.q_off = a->q_off;
   fill_flags(&p.fl, a->src_flags, a->flag_idx, a->n_src, a->flag_epoch, a->epoch_base, a->flag_limit_ns,
              a->flag_own - 1);
+  if (fill_push(&p.push, a)) return 1;
   constexpr int NS = 2;   // softmax threads per row
   constexpr int SMEM = (1 + F_KST + F_VST) * TILE_BYTES + 8 * FB_COUNT + 8 + 16 + 2 * NS * 128 * 4 + 16;
   static_assert(SMEM <= 227 * 1024, "shared memory budget");
@@ -498,6 +558,7 @@ struct PtrList {
 
 struct BwdParams {
   SrcFlags fl;                     // arrival flags of the looped sources
+  PushArgs push;                   // dQ kernel: this rank's K|V shard, pushed by the kernel's first CTAs
   int B, Sq, Hq, Hkv, causal;      // Sq: rows of the (local or per-source) Q tensor
   int lse_H;                       // heads of the lse / delta arrays (>= Hq for a head slice)
   float scale, scale_log2;
@@ -575,6 +636,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   np::tc_fence_after();
   const uint32_t tmem = *tmem_ptr_smem;
   const uint32_t tdP = tmem + 256, tdQ = tmem + 384;   // S buffers at columns 0 and 128
+  push_kv(p.push);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -1013,6 +1075,9 @@ struct NpAttnBwdArgs {
   int flag_which;
   int skip;       // 1: no dQ kernel, 2: no dK/dV kernel
   int flag_own;   // 1 + flag index that guards the resident operands (q, d_o, lse, delta / k, v), 0: none
+  // K|V shard pushed by the dQ kernel itself (as in NpAttnFwdArgs)
+  const void* push_k; const void* push_v; long long push_bytes; void* const* push_dst; int* const* push_flag;
+  int push_n; int* push_ctr;
 };
 
 NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
@@ -1073,6 +1138,7 @@ NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
   pq.q_blk_pos = a->q_blk_pos_local; pq.k_blk_pos = a->k_blk_pos_all;
   fill_flags(&pq.fl, (a->flag_which & 1) ? a->src_flags : nullptr, a->flag_idx, a->n_src, a->flag_epoch, a->epoch_base,
              a->flag_limit_ns, a->flag_own - 1);
+  if (fill_push(&pq.push, a)) return 1;
   // dK, dV: local KV blocks against every source's Q blocks
   BwdParams pk = p;
   pk.src_blocks = qblocks; pk.src_len = a->Sq;

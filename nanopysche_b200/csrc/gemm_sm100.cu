@@ -59,6 +59,12 @@ struct GemmParams {
   int b_loc_lo, b_loc_hi;     // B rows [lo, hi) come from tmBloc
   int b_local_flag;           // index into b_ready_flags that needs no wait (the local shard), -1: none
   int m_rot, n_rot;           // tile order starts at this M / N block (the local shard first)
+  // All-gather issued by this kernel itself: before the first tile every CTA stores its slice of `push_src` into
+  // the peers' gather buffers; the CTA that finishes last releases this rank's arrival flag on every peer. The
+  // grid is one resident wave, so the push never waits for a CTA that has not started.
+  const uint4* push_src; long long push_vecs;
+  uint4* push_dst[8]; int* push_flag[8]; int push_n;
+  int* push_ctr;
 };
 
 template <class F>
@@ -149,6 +155,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   np::tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (p.push_src) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < p.push_vecs;
+         i += (long long)gridDim.x * blockDim.x) {
+      const uint4 v = p.push_src[i];
+      for (int r = 0; r < p.push_n; ++r) p.push_dst[r][i] = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(p.push_ctr, 1) == (int)gridDim.x - 1) {
+      __threadfence_system();
+      for (int r = 0; r < p.push_n; ++r) np::st_release_sys(p.push_flag[r], epoch);
+      *p.push_ctr = 0;
+    }
+  }
 
   auto decode = [&](int t) {
     Tile tl;
@@ -526,6 +547,10 @@ struct NpGemmArgs {
   const void* A_loc; long long lda_loc; int a_loc_lo, a_loc_hi;
   const void* B_loc; long long ldb_loc; int b_loc_lo, b_loc_hi;
   int b_local_flag, m_rot, n_rot;
+  // all-gather pushed by the GEMM's own CTAs before their first tile: push_bytes of push_src to push_dst[r]
+  // (r < push_n <= 8; the destinations already point at this rank's slot), then *push_flag[r] = epoch (+ base);
+  // push_ctr: a zeroed local int
+  const void* push_src; long long push_bytes; void* const* push_dst; int* const* push_flag; int push_n; int* push_ctr;
 };
 
 template <int BN, int STAGES>
@@ -548,6 +573,12 @@ static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
   tmBloc = tmB;
   GemmParams p{};
   p.b_local_flag = a.b_local_flag - 1;
+  if (a.push_src && a.push_n > 0) {
+    if (a.push_n > 8 || (a.push_bytes & 15) || (((uintptr_t)a.push_src) & 15)) return 1;
+    p.push_src = (const uint4*)a.push_src; p.push_vecs = a.push_bytes >> 4; p.push_n = a.push_n;
+    p.push_ctr = a.push_ctr;
+    for (int r = 0; r < a.push_n; ++r) { p.push_dst[r] = (uint4*)a.push_dst[r]; p.push_flag[r] = a.push_flag[r]; }
+  }
   p.m_rot = a.m_rot; p.n_rot = a.n_rot;
   if (a.A_loc && !a.a_mn && a.a_loc_hi > a.a_loc_lo && a.a_loc_lo % BM == 0) {
     rc = np_make_tmap_2d(&tmAloc, a.A_loc, 2, (uint64_t)(a.a_loc_hi - a.a_loc_lo), (uint64_t)a.K, (uint64_t)a.lda_loc, BK, BM);

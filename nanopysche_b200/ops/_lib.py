@@ -44,6 +44,8 @@ class GemmArgs(C.Structure):
         ("A_loc", c_void_p), ("lda_loc", c_ll), ("a_loc_lo", c_int), ("a_loc_hi", c_int),
         ("B_loc", c_void_p), ("ldb_loc", c_ll), ("b_loc_lo", c_int), ("b_loc_hi", c_int),
         ("b_local_flag", c_int), ("m_rot", c_int), ("n_rot", c_int),
+        ("push_src", c_void_p), ("push_bytes", c_ll), ("push_dst", c_void_p), ("push_flag", c_void_p),
+        ("push_n", c_int), ("push_ctr", c_void_p),
     ]
 
 
@@ -89,6 +91,8 @@ class AttnFwdArgs(C.Structure):
         ("split", c_int), ("lse_heads", c_int),
         ("src_flags", c_void_p), ("flag_idx", c_void_p), ("flag_epoch", c_int), ("epoch_base", c_void_p),
         ("flag_limit_ns", c_ull), ("flag_own", c_int),
+        ("push_k", c_void_p), ("push_v", c_void_p), ("push_bytes", c_ll), ("push_dst", c_void_p),
+        ("push_flag", c_void_p), ("push_n", c_int), ("push_ctr", c_void_p),
     ]
 
 
@@ -113,6 +117,8 @@ class AttnBwdArgs(C.Structure):
         ("split", c_int), ("lse_heads", c_int),
         ("src_flags", c_void_p), ("flag_idx", c_void_p), ("flag_epoch", c_int), ("epoch_base", c_void_p),
         ("flag_limit_ns", c_ull), ("flag_which", c_int), ("skip", c_int), ("flag_own", c_int),
+        ("push_k", c_void_p), ("push_v", c_void_p), ("push_bytes", c_ll), ("push_dst", c_void_p),
+        ("push_flag", c_void_p), ("push_n", c_int), ("push_ctr", c_void_p),
     ]
 
 

@@ -86,6 +86,16 @@ def _set_flags(a, flags, keep: list):
     if hasattr(a, "flag_which"):
         a.flag_which = int(flags.get("which", 3))
     a.flag_own = int(flags.get("own", -1)) + 1
+    push = flags.get("push")
+    if push:   # dict k, v (contiguous shards), dst / flag (lists of peer addresses), ctr (zeroed [2] int32 tensor)
+        n = len(push["dst"])
+        dst = (C.c_void_p * n)(*[int(x) for x in push["dst"]])
+        flg = (C.c_void_p * n)(*[int(x) for x in push["flag"]])
+        keep += [dst, flg]
+        a.push_k, a.push_v = push["k"].data_ptr(), push["v"].data_ptr()
+        a.push_bytes, a.push_n = push["k"].numel() * push["k"].element_size(), n
+        a.push_dst, a.push_flag = C.cast(dst, C.c_void_p), C.cast(flg, C.c_void_p)
+        a.push_ctr = push["ctr"].data_ptr()
 
 
 def flash_supported(q: torch.Tensor, k: torch.Tensor) -> bool:

@@ -1,9 +1,9 @@
 """Context-parallel attention fused into the flash kernels over peer memory.
 
-Ring: every rank stores its K|V shard into all ranks' gather buffers (one push kernel, one arrival flag per
-source) and the attention kernel of each rank walks the KV blocks of *all* ranks in one launch; its TMA producer
-waits for a source's flag the first time it needs a tile of that source, so the remote shards arrive while the
-tensor cores work on the blocks that are already there. Every shard crosses NVLink once per pass (a first version
+Ring: ONE kernel per rank and pass. Its first CTAs store this rank's K|V shard into all peers' gather buffers (32 KB
+chunks taken from an atomic counter) and release one arrival flag per peer; then the kernel walks the KV blocks of
+*all* ranks - the local shard first, read in place - and its TMA producer waits for a source's flag the first time
+it needs a tile of that source, so the remote shards arrive while the tensor cores work on what is already there. Every shard crosses NVLink once per pass (a first version
 let each CTA pull its tiles straight from the peers' memory: correct, but each remote tile then crossed NVLink
 once per Q block - 2.6x slower than the NCCL path, measured on 2 GPUs). There is no ring of send/recv steps and
 no log-sum-exp merge between steps: one kernel sees the whole sequence. Causality is decided per 128-row block
@@ -78,8 +78,7 @@ class CPRuntime:
         self.gather = [h.alloc((self.cp, 2) + tuple(k.shape), bf) for _ in range(2)]     # [source][K|V][B,S,Hkv,hd]
         self.flags = [h.alloc((self.cp,), torch.int32) for _ in range(2)]
         self.slots = h.alloc((self.cp, 2) + tuple(k.shape), bf)                           # dK|dV partial per source
-        self.stage = torch.empty((2,) + tuple(k.shape), device=self.device, dtype=bf)
-        self.ctr = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.ctr = torch.zeros(2, dtype=torch.int32, device=self.device)
         self._block_positions(q.shape[1])
         self._shape = shape
         torch.cuda.synchronize()
@@ -92,10 +91,6 @@ class CPRuntime:
     def _gather_kv(self, k, v, causal):
         """Start the all-gather of this rank's K|V shard; returns the per-source K / V views (visiting order) and
         the flag descriptor the kernels wait on."""
-        import ctypes as C
-
-        from . import _lib
-
         par = self._calls & 1
         self._calls += 1
         if causal and not self.zigzag:
@@ -104,22 +99,21 @@ class CPRuntime:
             self.heap.barrier(attn_ops.WAIT_LIMIT_NS)
         h = self.heap
         e = h.next_epoch()
-        # The push is an ordinary kernel on the same stream: it has left this GPU before the attention kernel starts,
-        # and what overlaps the attention is the *peers'* pushes, which arrive while the kernel works on the local
-        # shard (read from k / v directly) and on the sources that are already complete. Running the push next to the
-        # attention kernel on a second stream deadlocks once the attention grid exceeds one wave: the block
-        # scheduler issues the push's CTAs only after all attention CTAs have been issued, while the resident
-        # attention CTAs of every rank wait for each other's push.
-        self.stage[0].copy_(k)
-        self.stage[1].copy_(v)
-        _lib.check(_lib.lib().np_allgather_push(
-            C.c_void_p(self.stage.data_ptr()), h.host_ptr_array(self.gather[par]),
-            C.c_longlong(self.stage.numel() * 2), h.host_ptr_array(self.flags[par]), C.c_void_p(self.ctr.data_ptr()),
-            self.rank, self.cp, e, C.c_void_p(h.epoch_base.data_ptr()), 0, C.c_void_p(_lib.stream())),
-            "cp_gather_push")
+        # The push is part of the attention kernel: its first CTAs take 32 KB chunks of k | v from an atomic counter,
+        # store them into the peers' gather buffers and the one that completes the last chunk releases this rank's
+        # flag; then every CTA computes, starting with the local shard (read from k / v in place) and waiting for a
+        # peer's flag only when it first needs that peer's tiles. (A separate push kernel on a second stream deadlocks
+        # once the attention grid exceeds one wave: the block scheduler issues its CTAs only after all attention CTAs
+        # have been issued, while the resident attention CTAs of every rank wait for each other's push.)
+        self.ctr.zero_()
+        nb = k.numel() * 2
+        peers = self.order[1:]
         g = self.gather[par]
-        flags = dict(flags=self.flags[par], idx=[-1] + self.order[1:], epoch=e, epoch_base=h.epoch_base, which=1)
-        return [k] + [g[r, 0] for r in self.order[1:]], [v] + [g[r, 1] for r in self.order[1:]], flags
+        push = dict(k=k, v=v, ctr=self.ctr,
+                    dst=[h.peer_ptr(g, r) + self.rank * 2 * nb for r in peers],
+                    flag=[h.peer_ptr(self.flags[par], r) + 4 * self.rank for r in peers])
+        flags = dict(flags=self.flags[par], idx=[-1] + peers, epoch=e, epoch_base=h.epoch_base, which=1, push=push)
+        return [k] + [g[r, 0] for r in peers], [v] + [g[r, 1] for r in peers], flags
 
     # -- forward / backward ---------------------------------------------------------------------------
     def forward(self, q, k, v, causal: bool, scale: Optional[float]):

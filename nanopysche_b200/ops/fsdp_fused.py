@@ -90,6 +90,41 @@ class FSDPRuntime:
             C.c_void_p(h.epoch_base.data_ptr()), 0, C.c_void_p(_lib.stream())), "fsdp_gather_push")
         return self.gather[par][: ns * self.n * K].view(ns * self.n, K), self.ag_flags[par], e
 
+    def ag_gemm(self, A: torch.Tensor, w_shard: torch.Tensor):
+        """``A @ all_gather(w_shard)^T`` as ONE kernel (shard rows a multiple of 256): the GEMM's CTAs first store
+        their slice of the shard into every rank's gather buffer and release this rank's flag, then compute the
+        output columns of the own shard (read in place) and a peer's columns once its flag has arrived."""
+        ns, K = w_shard.shape
+        assert ns % 256 == 0 and ns * self.n * K <= self.max_elems and w_shard.is_contiguous()
+        par = self._calls & 1
+        self._calls += 1
+        h = self.heap
+        e = h.next_epoch()
+        N = ns * self.n
+        full = self.gather[par][: N * K].view(N, K)
+        out = torch.empty((A.shape[0], N), device=A.device, dtype=torch.bfloat16)
+        nbytes = ns * K * 2
+        dst = (C.c_void_p * self.n)(*[h.peer_ptr(self.gather[par], r) + self.rank * nbytes for r in range(self.n)])
+        flg = (C.c_void_p * self.n)(*[h.peer_ptr(self.ag_flags[par], r) + 4 * self.rank for r in range(self.n)])
+        g = _lib.GemmArgs()
+        g.A, g.B, g.C = A.data_ptr(), full.data_ptr(), out.data_ptr()
+        g.lda, g.ldb, g.ldc = A.stride(0), K, N
+        g.a_rows, g.b_rows = A.shape[0], N
+        g.M, g.N, g.K = A.shape[0], N, K
+        g.mode, g.alpha, g.bn = 0, 1.0, 256
+        g.b_ready_flags, g.b_rows_per_flag = self.ag_flags[par].data_ptr(), ns
+        g.B_loc, g.ldb_loc = w_shard.data_ptr(), K
+        g.b_loc_lo, g.b_loc_hi = self.rank * ns, (self.rank + 1) * ns
+        g.b_local_flag = self.rank + 1
+        g.n_rot = self.rank * ns // 256
+        g.push_src, g.push_bytes, g.push_n = w_shard.data_ptr(), nbytes, self.n
+        g.push_dst, g.push_flag = C.cast(dst, C.c_void_p), C.cast(flg, C.c_void_p)
+        g.push_ctr = self.ctr.data_ptr()
+        g.epoch, g.flag_limit_ns = e, WAIT_LIMIT_NS
+        g.epoch_base = h.epoch_base.data_ptr()
+        _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "fsdp_ag_gemm")
+        return out
+
     def gemm_b_arriving(self, A, W_full, flags, epoch, rows_per_flag, *, b_mn: bool, w_local=None):
         """``A @ W^T`` (``b_mn=False``) or ``A @ W`` (``b_mn=True``) while W's row shards are still arriving. With
         ``w_local`` (this rank's shard, forward layout only) the own rows are read from it without a flag and their
@@ -152,11 +187,14 @@ class _ShardedLinear(torch.autograd.Function):
     def forward(ctx, x, w_shard, rt: FSDPRuntime):
         x2 = x.reshape(-1, x.shape[-1])
         x2 = x2 if x2.is_contiguous() else x2.contiguous()
-        full, flags, e = rt.gather_push(w_shard)
-        y = rt.gemm_b_arriving(x2, full, flags, e, w_shard.shape[0], b_mn=False, w_local=w_shard)
+        if w_shard.shape[0] % 256 == 0:
+            y = rt.ag_gemm(x2, w_shard)           # push + GEMM in one kernel
+        else:
+            full, flags, e = rt.gather_push(w_shard)
+            y = rt.gemm_b_arriving(x2, full, flags, e, w_shard.shape[0], b_mn=False, w_local=w_shard)
         ctx.save_for_backward(x2, w_shard)
         ctx.rt, ctx.x_shape = rt, x.shape
-        return y.view(*x.shape[:-1], full.shape[0])
+        return y.view(*x.shape[:-1], y.shape[-1])
 
     @staticmethod
     def backward(ctx, dy):

@@ -1,9 +1,9 @@
 """Fused tensor-parallel linears over peer memory (Megatron sequence-parallel layout).
 
-``ag_linear``  : ``y[M, Nl] = all_gather(x_shard)[M, K] @ w[Nl, K]^T`` - every rank stores its row shard
-                 into all ranks' gather buffers (one push kernel) and the tcgen05 GEMM starts on each
-                 128-row block as soon as the flag of the rank that owns those rows arrives, so the
-                 transfer overlaps the math block by block.
+``ag_linear``  : ``y[M, Nl] = all_gather(x_shard)[M, K] @ w[Nl, K]^T`` as one kernel - the CTAs of the tcgen05 GEMM
+                 first store their slice of this rank's row shard into every rank's gather buffer and release
+                 the rank's flag, then compute this rank's own row blocks (read in place) and move on to a peer's
+                 128-row blocks as soon as that peer's flag has arrived, so the transfer overlaps the math.
 ``linear_rs``  : ``y_shard[M/tp, N] = reduce_scatter(x[M, Kl] @ w[N, Kl]^T)`` - the GEMM epilogue stores
                  every output row straight from TMEM into the owning rank's slot buffer and releases
                  that rank's flag when its blocks are done; the owner sums the ``tp`` partial rows.
@@ -87,6 +87,39 @@ class TPRuntime:
             C.c_void_p(h.epoch_base.data_ptr()), 0, C.c_void_p(_lib.stream())), "allgather_push")
         return self.gather[: self.M * cols].view(self.M, cols), e
 
+    def ag_gemm(self, x_shard: torch.Tensor, B: torch.Tensor, *, b_mn: bool):
+        """``all_gather(x_shard) @ B^T`` (``@ B`` with ``b_mn``) as ONE kernel: the GEMM's CTAs first store their slice
+        of ``x_shard`` into every rank's gather buffer and release this rank's flag, then compute - this rank's own
+        row blocks first (read from ``x_shard``), a peer's blocks when its flag has arrived. Returns
+        ``(y [M, N], gathered x [M, K])``."""
+        Ms, cols = x_shard.shape
+        assert Ms == self.Ms and cols <= self.max_cols and x_shard.is_contiguous()
+        h = self.heap
+        e = h.next_epoch()
+        full = self.gather[: self.M * cols].view(self.M, cols)
+        N = B.shape[1] if b_mn else B.shape[0]
+        out = torch.empty((self.M, N), device=x_shard.device, dtype=torch.bfloat16)
+        nbytes = Ms * cols * 2
+        dst = (C.c_void_p * self.N)(*[h.peer_ptr(self.gather, r) + self.rank * nbytes for r in range(self.N)])
+        flg = (C.c_void_p * self.N)(*[h.peer_ptr(self.ag_flags, r) + 4 * self.rank for r in range(self.N)])
+        g = _lib.GemmArgs()
+        g.A, g.B, g.C = full.data_ptr(), B.data_ptr(), out.data_ptr()
+        g.lda, g.ldb, g.ldc = cols, B.stride(0), N
+        g.a_rows, g.b_rows = self.M, B.shape[0]
+        g.M, g.N, g.K = self.M, N, cols
+        g.b_mn, g.mode, g.alpha = int(b_mn), 1, 1.0
+        g.ready_flags, g.mblk_flag = self.ag_flags.data_ptr(), self.mblk_owner_remote.data_ptr()
+        g.A_loc, g.lda_loc = x_shard.data_ptr(), cols
+        g.a_loc_lo, g.a_loc_hi = self.rank * Ms, (self.rank + 1) * Ms
+        g.m_rot = self.rank * Ms // 128
+        g.push_src, g.push_bytes, g.push_n = x_shard.data_ptr(), nbytes, self.N
+        g.push_dst, g.push_flag = C.cast(dst, C.c_void_p), C.cast(flg, C.c_void_p)
+        g.push_ctr = self.ctr.data_ptr()
+        g.epoch, g.flag_limit_ns = e, WAIT_LIMIT_NS
+        g.epoch_base = h.epoch_base.data_ptr()
+        _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "tp_ag_gemm")
+        return out, full
+
     def gemm_wait(self, A, B, *, b_mn: bool, epoch: int, out_dtype=torch.bfloat16, a_local=None):
         """``A @ B^T`` where A is the gather buffer: each M block waits for its owner's arrival flag. With
         ``a_local`` (this rank's shard) the own rows are read from it, need no flag and are computed first."""
@@ -145,8 +178,7 @@ class _AGLinear(torch.autograd.Function):
     def forward(ctx, x_shard, w, rt: TPRuntime):
         xs = x_shard.reshape(-1, x_shard.shape[-1])
         xs = xs if xs.is_contiguous() else xs.contiguous()
-        full, e = rt.all_gather_push(xs)
-        y = rt.gemm_wait(full, w, b_mn=False, epoch=e, a_local=xs)
+        y, full = rt.ag_gemm(xs, w, b_mn=False)
         ctx.save_for_backward(full.clone(), w)  # the gather buffer is reused by the next layer
         ctx.rt = rt
         ctx.x_shape = x_shard.shape
@@ -179,8 +211,7 @@ class _LinearRS(torch.autograd.Function):
         rt = ctx.rt
         dys = dy_shard.reshape(-1, dy_shard.shape[-1])
         dys = dys if dys.is_contiguous() else dys.contiguous()
-        dy_full, e = rt.all_gather_push(dys)
-        dx = rt.gemm_wait(dy_full, w, b_mn=True, epoch=e, a_local=dys)
+        dx, dy_full = rt.ag_gemm(dys, w, b_mn=True)
         dw = None
         if ctx.needs_input_grad[1] or hasattr(w, "main_grad"):
             dw = _wgrad_into(w, dy_full, x2)  # runs after the dgrad GEMM, which has seen every flag

@@ -82,8 +82,7 @@ def main(argv=None):
 
     # all-gather -> GEMM
     def ag_fused():
-        g, e = rt.all_gather_push(x_shard)
-        rt.gemm_wait(g, w_col, b_mn=False, epoch=e, a_local=x_shard)
+        rt.ag_gemm(x_shard, w_col, b_mn=False)
 
     def ag_base():
         dist.all_gather_into_tensor(full, x_shard)
@@ -110,8 +109,7 @@ def main(argv=None):
     w_full = torch.empty(F, D, device=dev, dtype=bf)
 
     def fsdp_fused():
-        wf, flags, e = frt.gather_push(w_shard)
-        frt.gemm_b_arriving(x, wf, flags, e, w_shard.shape[0], b_mn=False, w_local=w_shard)
+        frt.ag_gemm(x, w_shard)
 
     def fsdp_base():
         dist.all_gather_into_tensor(w_full, w_shard)
