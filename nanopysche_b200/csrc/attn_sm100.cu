@@ -84,16 +84,17 @@ struct PushArgs {
   int epoch;
   const int* epoch_base;
 };
-__device__ __forceinline__ void push_kv(const PushArgs& a) {
+// `s_chunk`: one int of the kernel's dynamic shared memory (a static __shared__ variable here would move the
+// dynamic region off its 1024-byte boundary and past the size the launch asked for).
+__device__ __forceinline__ void push_kv(const PushArgs& a, volatile int* s_chunk) {
   if (a.n <= 0) return;
-  __shared__ int s_chunk;
   constexpr long long CH = 2048;   // vectors per chunk (32 KB)
   const long long total = 2 * a.vecs_each;
   const int nch = (int)((total + CH - 1) / CH);
   for (;;) {
-    if (threadIdx.x == 0) s_chunk = atomicAdd(&a.ctr[0], 1);
+    if (threadIdx.x == 0) *s_chunk = atomicAdd(&a.ctr[0], 1);
     __syncthreads();
-    const int c = s_chunk;
+    const int c = *s_chunk;
     __syncthreads();
     if (c >= nch) break;
     const long long hi = (c + 1) * CH < total ? (c + 1) * CH : total;
@@ -241,7 +242,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   np::tc_fence_after();
   const uint32_t tmem = *tmem_ptr_smem;
   const uint32_t tO = tmem + F_O;
-  push_kv(p.push);
+  push_kv(p.push, reinterpret_cast<volatile int*>(tail + 8));
 
   if (warp == 0) {
     if (lane == 0) {
@@ -636,7 +637,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   np::tc_fence_after();
   const uint32_t tmem = *tmem_ptr_smem;
   const uint32_t tdP = tmem + 256, tdQ = tmem + 384;   // S buffers at columns 0 and 128
-  push_kv(p.push);
+  push_kv(p.push, reinterpret_cast<volatile int*>(tail + 12));
 
   if (warp == 0) {
     if (lane == 0) {
