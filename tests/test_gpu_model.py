@@ -163,3 +163,22 @@ def test_fused_moe_fp8_flow_path():
     assert rel(y, yr) < 0.08 and rel(xa.grad, xb.grad) < 0.08
     for n in ("w1", "w2", "w3"):
         assert rel(getattr(fused, n).grad, getattr(ref, n).grad) < 0.08, n
+
+
+def test_cli_train_and_bench_on_gpu(tmp_path, capsys):
+    """The user-facing entry points on a GPU: a few optimizer steps of a small GQA + MoE model (head_dim 128, so the
+    flash-attention, fused-MoE and arena paths all run) and the forward benchmark, through ``cli.main``."""
+    from nanopysche_b200 import cli
+    from nanopysche_b200.ops import _lib
+
+    args = ["--model", "125m", "--use-moe", "--num-experts", "4", "--top-k", "2", "--batch-size", "2", "--seq-len", "256",
+            "--device", "cuda"]
+    l0 = _lib.LAUNCHES
+    rc = cli.main(["train", *args, "--max-steps", "3", "--save-dir", str(tmp_path / "ck"), "--log-interval", "1"])
+    assert rc in (0, None)
+    assert _lib.LAUNCHES > l0, "the CUDA kernels were not used"
+    _lib.check_status("cli train")
+    rc = cli.main(["bench", *args, "--warmup", "1", "--iters", "2"])
+    assert rc in (0, None)
+    out = capsys.readouterr().out
+    assert "tokens/s" in out or "tok/s" in out.lower()
