@@ -139,6 +139,23 @@ __global__ void __launch_bounds__(256) a2a_push_kernel(const uint4* __restrict__
   }
 }
 
+// out[i] = sum_r src_r[off + i] over bf16 buffers that live on the n ranks (peer loads, fp32 accumulation): the
+// reduction half of a reduce-scatter whose partial results were written locally by each rank's GEMM.
+__global__ void __launch_bounds__(256) rs_reduce_bf16_kernel(PeerPtrs src, int n, long long off_vecs, long long vecs,
+                                                             uint4* __restrict__ out) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < vecs;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < n; ++r) {
+      const uint4 u = reinterpret_cast<const uint4*>(src.p[r])[off_vecs + i];
+      const float2 a = np::unpack_bf16(u.x), b = np::unpack_bf16(u.y), c = np::unpack_bf16(u.z), d = np::unpack_bf16(u.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    out[i] = make_uint4(np::pack_bf16(acc[0], acc[1]), np::pack_bf16(acc[2], acc[3]), np::pack_bf16(acc[4], acc[5]),
+                        np::pack_bf16(acc[6], acc[7]));
+  }
+}
+
 // gshard[i] = scale * sum_r grads_r[lo + i]; partial[b] = sum of gshard^2 over this CTA's slice.
 __global__ void __launch_bounds__(256) zero_reduce_kernel(PeerPtrs grads, int n, long long lo, long long cnt,
                                                           float scale, float* __restrict__ gshard,
@@ -289,6 +306,18 @@ NP_API int np_a2a_push(const void* src, long long rows, long long row_bytes, voi
   if (g > cap) g = cap;
   a2a_push_kernel<<<(int)g, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, rows, row_bytes >> 4, d, f, ctr, my_rank, n,
                                                             epoch, epoch_base, set_flag);
+  CHECK_LAUNCH();
+}
+
+// out[count] (bf16) = sum over the n ranks of their bf16 buffer at element offset `off` (off, count multiples of 8).
+NP_API int np_rs_reduce_bf16(void* const* src_ptrs, int n, long long off, long long count, void* out, void* stream) {
+  if (n > MAX_PEERS || (off & 7) || (count & 7)) return 1;
+  if (count <= 0) return 0;
+  PeerPtrs s;
+  for (int i = 0; i < n; ++i) s.p[i] = src_ptrs[i];
+  long long g = ((count >> 3) + 255) / 256;
+  if (g > 148 * 8) g = 148 * 8;
+  rs_reduce_bf16_kernel<<<(int)g, 256, 0, (cudaStream_t)stream>>>(s, n, off >> 3, count >> 3, (uint4*)out);
   CHECK_LAUNCH();
 }
 

@@ -8,9 +8,8 @@ Each rank owns ``N/n`` rows of a weight ``[N, K]``.
               on the wire (parameter all-gather fused into the first consuming GEMM).
 * dgrad     : the shards are gathered again (the buffer is shared by all layers) and ``dx = dy W`` waits per
               K-slice of B in the same way.
-* wgrad     : ``dW = dy^T x`` is computed for all ``N`` rows and every output row is stored straight from TMEM
-              into the owning rank's slot buffer (GEMM -> reduce-scatter); the owner sums the ``n`` partials
-              into the gradient of its shard.
+* wgrad     : ``dW = dy^T x`` is computed for all ``N`` rows into this rank's symmetric buffer; after a device
+              barrier every rank sums its row shard over all ranks' buffers with peer loads (reduce-scatter).
 
 Replaces ``fully_shard`` (reference: distributed/fsdp.py:18-83: NCCL all-gather before every layer forward and
 backward, NCCL reduce-scatter after backward).
@@ -24,6 +23,7 @@ import torch.distributed as dist
 
 from . import _lib
 from .attention import WAIT_LIMIT_NS
+from .gemm import gemm
 
 
 class FSDPRuntime:
@@ -37,10 +37,12 @@ class FSDPRuntime:
         self.rank = dist.get_rank(group)
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.max_elems = max_weight_elems
-        self.heap = SymmetricHeap(3 * max_weight_elems * 2 + (1 << 20), group, self.device)
+        self.heap = SymmetricHeap(4 * max_weight_elems * 2 + (1 << 20), group, self.device)
         h = self.heap
         self.gather = [h.alloc((max_weight_elems,), torch.bfloat16) for _ in range(2)]
         self.slots = h.alloc((max_weight_elems,), torch.bfloat16)
+        self.partial = [self.slots, h.alloc((max_weight_elems,), torch.bfloat16)]   # wgrad partials, by call parity
+        self._rs_calls = 0
         self.ag_flags = [h.alloc((self.n,), torch.int32) for _ in range(2)]
         self.rs_flags = h.alloc((self.n,), torch.int32)
         self.p_slots = h.ptr_array(self.slots)
@@ -151,34 +153,22 @@ class FSDPRuntime:
         return out
 
     def wgrad_reduce_scatter(self, dy, x):
-        """``reduce_scatter(dy^T x)`` over the weight rows: this rank's ``[N/n, K]`` fp32 gradient shard."""
+        """``reduce_scatter(dy^T x)`` over the weight rows: this rank's ``[N/n, K]`` gradient shard. The wgrad GEMM
+        writes the full partial ``[N, K]`` into this rank's symmetric buffer; after a device barrier every rank sums
+        its row shard over all ranks' buffers with peer loads."""
         T, N = dy.shape
         K = x.shape[1]
         assert N * K <= self.max_elems
-        tb = self._rs_tables(N)
-        e = self.heap.next_epoch()
-        self.done_counters.zero_()
-        g = _lib.GemmArgs()
-        g.A, g.B = dy.data_ptr(), x.data_ptr()
-        g.lda, g.ldb, g.ldc = dy.stride(0), x.stride(0), K
-        g.a_rows, g.b_rows = T, T
-        g.M, g.N, g.K = N, K, T
-        g.a_mn, g.b_mn, g.mode, g.alpha = 1, 1, 0, 1.0
-        g.row_dst, g.peer_base = tb["row_dst"].data_ptr(), self.p_slots.data_ptr()
-        g.mblk_flag = tb["mblk_owner"].data_ptr()
-        g.done_counters, g.done_expected = self.done_counters.data_ptr(), tb["done_expected"].data_ptr()
-        g.done_flag_ptr, g.epoch = self.p_done_flag.data_ptr(), e
-        g.epoch_base = self.heap.epoch_base.data_ptr()
-        _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "fsdp_wgrad_rs")
+        buf = self.partial[self._rs_calls & 1]
+        self._rs_calls += 1
+        part = buf[: N * K].view(N, K)
+        gemm(dy, x, a_mn=True, b_mn=True, out=part)
+        self.heap.barrier(WAIT_LIMIT_NS)
         ns = N // self.n
         out = torch.empty((ns, K), device=dy.device, dtype=torch.bfloat16)
-        c = _lib.CombineArgs()
-        c.rows, c.slot_pos, c.out = self.slots.data_ptr(), tb["slot_pos"].data_ptr(), out.data_ptr()
-        c.T, c.K, c.D, c.E = ns, self.n, K, 1
-        c.flags, c.sent_to_peer = self.rs_flags.data_ptr(), self.sent.data_ptr()
-        c.n_ranks, c.epoch, c.limit_ns = self.n, e, WAIT_LIMIT_NS
-        c.epoch_base = self.heap.epoch_base.data_ptr()
-        _lib.check(_lib.lib().np_ep_combine(C.byref(c), C.c_void_p(_lib.stream())), "fsdp_reduce")
+        _lib.check(_lib.lib().np_rs_reduce_bf16(
+            self.heap.host_ptr_array(buf), self.n, C.c_longlong(self.rank * ns * K), C.c_longlong(ns * K),
+            C.c_void_p(out.data_ptr()), C.c_void_p(_lib.stream())), "fsdp_rs_reduce")
         return out
 
 

@@ -101,6 +101,8 @@ def main(argv=None):
 
     report("tp_gemm_rs", _time(lambda: rt.gemm_reduce_scatter(h, w_row, b_mn=False), a.iters, dev),
            _time(rs_base, a.iters, dev), 2.0 * M * Fl * D, (n - 1) * (M // n) * D * 2)
+    report("tp_gemm_rs_push_epilogue", _time(lambda: rt.gemm_reduce_scatter_push(h, w_row, b_mn=False), a.iters, dev),
+           _time(rs_base, a.iters, dev), 2.0 * M * Fl * D, (n - 1) * (M // n) * D * 2)
 
     # FSDP: all-gather(weight) -> GEMM
     frt = FSDPRuntime(dist.group.WORLD, max_weight_elems=F * D)
