@@ -4,9 +4,10 @@
                  first store their slice of this rank's row shard into every rank's gather buffer and release
                  the rank's flag, then compute this rank's own row blocks (read in place) and move on to a peer's
                  128-row blocks as soon as that peer's flag has arrived, so the transfer overlaps the math.
-``linear_rs``  : ``y_shard[M/tp, N] = reduce_scatter(x[M, Kl] @ w[N, Kl]^T)`` - the GEMM epilogue stores
-                 every output row straight from TMEM into the owning rank's slot buffer and releases
-                 that rank's flag when its blocks are done; the owner sums the ``tp`` partial rows.
+``linear_rs``  : ``y_shard[M/tp, N] = reduce_scatter(x[M, Kl] @ w[N, Kl]^T)`` - the GEMM writes its partial product
+                 into this rank's symmetric buffer, a device barrier follows, and every rank adds its row shard
+                 over all ranks' buffers with coalesced peer loads (storing rows to the peer from the GEMM epilogue
+                 was measured slower: 16-byte pieces make poor NVLink packets).
 Backward passes are the conjugates (``ag_linear`` <-> ``linear_rs``) plus local wgrad GEMMs.
 
 They replace ``differentiable_all_reduce`` after the row-parallel projections of the reference
