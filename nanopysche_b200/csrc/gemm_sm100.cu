@@ -12,6 +12,7 @@
 //
 // Replaces the cuBLAS calls behind nn.Linear / torch.bmm in the reference
 // (model/attention.py:141-143,189; model/feed_forward.py:75; model/moe.py:1520-1538).
+#include <cstdlib>
 #include "common.cuh"
 
 __device__ int g_np_status[8];
@@ -65,7 +66,25 @@ struct GemmParams {
   const uint4* push_src; long long push_vecs;
   uint4* push_dst[8]; int* push_flag[8]; int push_n;
   int* push_ctr;
+  bool st32;                  // output rows and column chunks are 32-byte aligned: use 32-byte stores
 };
+
+// 64 bytes (32 bf16 packed in 16 registers) to a row: two 32-byte stores when the address allows it (a full sector
+// per request - what a row pushed to a peer over NVLink is made of), else four 16-byte stores.
+__device__ __forceinline__ void store64(void* dst, const uint32_t* o, bool st32) {
+  if (st32) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                 "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
+                 : "memory");
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"((char*)dst + 32), "r"(o[8]), "r"(o[9]),
+                 "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15])
+                 : "memory");
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+  }
+}
 
 template <class F>
 __device__ __forceinline__ void for_each_k(const GemmParams& p, int g, F&& f) {
@@ -432,6 +451,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             __nv_bfloat16* dst = (__nv_bfloat16*)crow + col;
             if (full) {
+              uint32_t pk[16];
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 float f[8];
@@ -443,9 +463,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                   f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
                   f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
                 }
-                reinterpret_cast<uint4*>(dst)[i] = make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]),
-                                                              np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
+                pk[4 * i] = np::pack_bf16(f[0], f[1]); pk[4 * i + 1] = np::pack_bf16(f[2], f[3]);
+                pk[4 * i + 2] = np::pack_bf16(f[4], f[5]); pk[4 * i + 3] = np::pack_bf16(f[6], f[7]);
               }
+              store64(dst, pk, p.st32);
             } else {
               _Pragma("unroll") for (int i = 0; i < 32; ++i) if (col + i < p.N) {
                 float v = __uint_as_float(r[i]) * p.alpha;
@@ -573,6 +594,11 @@ static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
   tmBloc = tmB;
   GemmParams p{};
   p.b_local_flag = a.b_local_flag - 1;
+  // 32-byte stores need every (row, 32-column chunk) address 32-byte aligned; destinations behind peer_base are
+  // allocations of the symmetric heap (256-byte aligned)
+  static const bool st32_on = !(getenv("NPB200_ST32") != nullptr && getenv("NPB200_ST32")[0] == '0');
+  p.st32 = st32_on && !a.out_f32 && a.epilogue != 1 && (a.ldc % 16 == 0) && (a.group_stride_c % 16 == 0) &&
+           (a.row_dst || (((uintptr_t)a.C) % 32 == 0));
   if (a.push_src && a.push_n > 0) {
     if (a.push_n > 8 || (a.push_bytes & 15) || (((uintptr_t)a.push_src) & 15)) return 1;
     p.push_src = (const uint4*)a.push_src; p.push_vecs = a.push_bytes >> 4; p.push_n = a.push_n;
