@@ -4,7 +4,9 @@
 ``(silu(x w1^T) * (x w3^T)) w2`` either in bf16 (fewer than ``fp8_gemm_threshold`` tokens per expert:
 quantisation overhead is not amortised) or with e4m3 operands (1x128 activation scales x 128x128 weight
 scales): quantise once on entry, SwiGLU and re-quantisation fused, weights quantised once per
-optimizer step and cached.
+optimizer step and cached. With the ``mxfp8`` recipe the operands are e4m3 with one power-of-two scale per 1x32
+block along the contraction and the grouped GEMMs run on the block-scaled tensor-core instruction
+(``nanopysche_b200/csrc/gemm_mxfp8_sm100.cu``).
 """
 from __future__ import annotations
 
@@ -54,6 +56,36 @@ class FP8FlowMoECompute:
             self._wq_version = ver
         return self._wq_cache
 
+    def _mx_weights(self):
+        """1x32-scaled e4m3 copies of the expert weights, K-major for their GEMM: w1, w3 ``[E*H, D]`` quantised
+        along D, w2 transposed per expert to ``[E*D, H]`` and quantised along H. Cached per weight version."""
+        from nanopysche_b200.ops.gemm_mxfp8 import mx_quantize
+
+        ver = ("mx",) + tuple(w._version for w in (self.w1, self.w2, self.w3))
+        if self._wq_cache is None or self._wq_version != ver:
+            E, H, D = self.num_experts, self.hidden, self.d_model
+            bf = lambda t: t.detach().to(torch.bfloat16).contiguous()
+            w2t = self.w2.detach().reshape(E, H, D).transpose(1, 2).reshape(E * D, H)
+            self._wq_cache = (*mx_quantize(bf(self.w1.reshape(E * H, D))), *mx_quantize(bf(self.w3.reshape(E * H, D))),
+                              *mx_quantize(bf(w2t)))
+            self._wq_version = ver
+        return self._wq_cache
+
+    def _mx_forward(self, xp: torch.Tensor, padded: torch.Tensor) -> torch.Tensor:
+        """Expert MLP over rows grouped per expert in multiples of 128 (``padded [E]`` rows per expert)."""
+        from nanopysche_b200.ops.gemm_mxfp8 import gemm_mxfp8, mx_quantize
+
+        H, D, E = self.hidden, self.d_model, padded.numel()
+        blocks = xp.shape[0] // 128
+        grp = torch.repeat_interleave(torch.arange(E, device=xp.device, dtype=torch.int32), padded // 128,
+                                      output_size=blocks)
+        w1q, s1, w3q, s3, w2q, s2 = self._mx_weights()
+        xq, sx = mx_quantize(xp.to(torch.bfloat16))
+        g = gemm_mxfp8(xq, sx, w1q, s1, mblk_group=grp, rows_per_group=H)
+        u = gemm_mxfp8(xq, sx, w3q, s3, mblk_group=grp, rows_per_group=H)
+        hq, sh = mx_quantize((F.silu(g.float()) * u.float()).to(torch.bfloat16))
+        return gemm_mxfp8(hq, sh, w2q, s2, mblk_group=grp, rows_per_group=D, out_dtype=xp.dtype)
+
     def use_fp8(self, tokens_per_expert: float) -> bool:
         c = self.config
         return bool(c.enabled and c.fp8_recipe.active and tokens_per_expert >= self.fp8_gemm_threshold and
@@ -72,6 +104,13 @@ class FP8FlowMoECompute:
         if self.use_fp8(n / max(E, 1)):
             self.last_path = "fp8"
             xp, row_map, padded = ops.fused_permute_pad(x, idx, E, 128)
+            if self.config.fp8_recipe.recipe_type == FP8RecipeType.MXFP8:
+                self.last_path = "mxfp8"
+                y = self._mx_forward(xp, padded)
+                if torch.is_grad_enabled() and (x.requires_grad or self.w1.requires_grad):
+                    y_ref = self._bf16(xp, padded)
+                    y = y_ref + (y - y_ref).detach()
+                return ops.fused_unpermute_unpad(y, row_map, weights)
             xq, xs = ops.quantize_to_fp8(xp)
             w1q, s1, w3q, s3, w2q, s2 = self._quantised_weights()
             g = ops.fp8_grouped_gemm(xq, xs, w1q, s1, padded)

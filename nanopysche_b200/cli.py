@@ -63,6 +63,8 @@ def build_parser() -> argparse.ArgumentParser:
     common.add_argument("--cp-size", type=int, default=1)
     common.add_argument("--ep-size", type=int, default=1)
     common.add_argument("--fsdp", action="store_true")
+    common.add_argument("--fsdp-backend", choices=["auto", "torch", "arena", "sharded"], default="auto",
+                        help="sharded: linear weights sharded by rows, gathered inside their GEMMs (CUDA)")
     common.add_argument("--ac-mode", choices=["full", "selected_blocks"], default=None)
     common.add_argument("--ulysses", action="store_true", help="Ulysses instead of ring attention under CP")
     t = sub.add_parser("train", parents=[common], help="Train a model")
@@ -207,7 +209,8 @@ def _maybe_parallelize_model(model, args, device):
         cp_config=ContextParallelConfig(args.cp_size, ring=not args.ulysses, ulysses=args.ulysses)
         if args.cp_size > 1 else None,
         pp_config=PipelineParallelConfig(args.pp_size) if args.pp_size > 1 else None,
-        dp_config=DataParallelConfig(param_dtype=_resolve_dtype(args)) if args.fsdp else None,
+        dp_config=DataParallelConfig(param_dtype=_resolve_dtype(args),
+                                     backend=getattr(args, "fsdp_backend", "auto")) if args.fsdp else None,
         moe_fp8_recipe=args.fp8_recipe, moe_fp8_gemm_threshold=args.fp8_gemm_threshold,
         compile_model=getattr(args, "compile", False), ac_mode=args.ac_mode) if mesh is not None or args.ac_mode \
         else model

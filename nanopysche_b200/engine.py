@@ -45,6 +45,9 @@ def prepare_training(model: nn.Module, *, tokens_per_rank: Optional[int] = None,
     if rt is not None:
         opt.post_step_hooks.append(rt.end_step)
     opt.post_step_hooks.append(_cp_end_step)
+    fs = getattr(model, "_fsdp_linear_runtime", None)
+    if fs is not None:
+        opt.post_step_hooks.append(fs.end_step)
     return opt, arena
 
 

@@ -138,6 +138,18 @@ class Fp8GemmArgs(C.Structure):
     ]
 
 
+class MxGemmArgs(C.Structure):
+    """Mirror of ``NpMxGemmArgs`` in csrc/gemm_mxfp8_sm100.cu."""
+
+    _fields_ = [
+        ("A", c_void_p), ("B", c_void_p), ("C", c_void_p), ("sfa", c_void_p), ("sfb", c_void_p),
+        ("lda", c_ll), ("ldb", c_ll), ("ldc", c_ll), ("a_rows", c_ll), ("b_rows", c_ll),
+        ("M", c_int), ("N", c_int), ("K", c_int), ("out_f32", c_int), ("mode", c_int),
+        ("mblk_group", c_void_p), ("mblk_rows", c_void_p), ("group_stride_b", c_ll),
+        ("max_ctas", c_int),
+    ]
+
+
 class KernelError(RuntimeError):
     """A kernel launch failed or a kernel reported a device-side status (timeout, bounds)."""
 
@@ -172,6 +184,8 @@ def lib():
     _LIB.np_ep_dispatch.argtypes = [C.POINTER(DispatchArgs), c_void_p]
     _LIB.np_ep_combine.argtypes = [C.POINTER(CombineArgs), c_void_p]
     _LIB.np_gemm_fp8_block.argtypes = [C.POINTER(Fp8GemmArgs), c_void_p]
+    _LIB.np_gemm_mxfp8.argtypes = [C.POINTER(MxGemmArgs), c_void_p]
+    _LIB.np_mx_quant.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p]
     _LIB.np_attn_fwd.argtypes = [C.POINTER(AttnFwdArgs), c_void_p]
     _LIB.np_attn_bwd.argtypes = [C.POINTER(AttnBwdArgs), c_void_p]
     _LIB.np_status_read.argtypes = [C.POINTER(c_int)]

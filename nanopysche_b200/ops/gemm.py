@@ -140,6 +140,12 @@ class _Linear(torch.autograd.Function):
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ w.T (+ bias)``; tcgen05 kernels for bf16 CUDA tensors, ``F.linear`` otherwise."""
     if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        rt = getattr(w, "_fsdp_rt", None)
+        if rt is not None:  # row-sharded weight: all-gather inside the GEMM, reduce-scattered weight gradient
+            from .fsdp_fused import sharded_linear
+
+            y = sharded_linear(x, w, rt)
+            return y if bias is None else y + bias
         y = _Linear.apply(x, w)
         return y if bias is None else y + bias
     return torch.nn.functional.linear(x, w, bias)

@@ -1,0 +1,147 @@
+"""MXFP8 GEMM op (csrc/gemm_mxfp8_sm100.cu) with its PyTorch reference.
+
+MXFP8: e4m3 values with one shared power-of-two scale (an e8m0 exponent byte, value ``2^(b - 127)``) per block of
+32 consecutive elements along the contraction dimension. ``mx_quantize(x)`` returns ``(q, sf)`` with ``q`` the e4m3
+tensor ``[rows, K]`` and ``sf`` the exponent bytes in the chunk layout the tensor core reads (``sf_index``);
+``gemm_mxfp8(aq, sfa, bq, sfb)`` computes ``dequant(a) @ dequant(b)^T`` with the scaling done by the block-scaled
+tcgen05 MMA. With ``mblk_group`` (one group id per 128-row block of ``aq``) block ``i`` uses rows
+``[g * rows_per_group, (g + 1) * rows_per_group)`` of ``bq``: the grouped (per-expert) form.
+
+Stands where the reference's ``mxfp8`` recipe hands linears to torchao's MX tensors (cli.py:28-186, fp8 recipe
+flag; fp8/recipes.py of the reference).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+SF_CHUNK = 512  # bytes: 128 rows x 4 blocks of 32
+
+
+def sf_index(rows: int, K: int, device=None) -> torch.Tensor:
+    """Byte offset of the scale of (row r, 32-block j) in the chunked buffer, as an int64 ``[rows, K/32]`` tensor:
+    chunk ``(r // 128) * (K // 128) + j // 4``, inside it ``(r % 32) * 16 + ((r % 128) // 32) * 4 + j % 4``."""
+    r = torch.arange(rows, device=device).view(-1, 1)
+    j = torch.arange(K // 32, device=device).view(1, -1)
+    chunk = (r // 128) * (K // 128) + j // 4
+    return chunk * SF_CHUNK + (r % 32) * 16 + ((r % 128) // 32) * 4 + (j % 4)
+
+
+def sf_bytes(rows: int, K: int) -> int:
+    return ((rows + 127) // 128) * (K // 128) * SF_CHUNK
+
+
+def mx_quantize_ref(x: torch.Tensor):
+    """PyTorch statement of the quantiser: per 1x32 block ``e = ceil(log2(amax / 448))`` clamped to [-127, 127]."""
+    rows, K = x.shape
+    xf = x.float().view(rows, K // 32, 32)
+    am = xf.abs().amax(-1)
+    mant, ex = torch.frexp(am / 448.0)
+    e = torch.where(mant == 0.5, ex - 1, ex)
+    e = torch.where(am > 0, e, torch.full_like(e, -127)).clamp(-127, 127)
+    q = (xf * torch.exp2(-e.float()).unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn).view(rows, K)
+    sf = torch.full((sf_bytes(rows, K),), 127, dtype=torch.uint8, device=x.device)
+    sf[sf_index(rows, K, x.device).reshape(-1)] = (e + 127).to(torch.uint8).reshape(-1)
+    return q, sf
+
+
+def mx_quantize(x: torch.Tensor):
+    """bf16 ``[rows, K]`` (K a multiple of 128, unit column stride) -> ``(e4m3 [rows, K], uint8 scale chunks)``."""
+    if not x.is_cuda:
+        return mx_quantize_ref(x)
+    rows, K = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and K % 128 == 0
+    q = torch.empty((rows, K), device=x.device, dtype=torch.float8_e4m3fn)
+    sf = torch.full((sf_bytes(rows, K),), 127, dtype=torch.uint8, device=x.device)
+    _lib.check(_lib.lib().np_mx_quant(C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)), C.c_void_p(q.data_ptr()),
+                                      C.c_longlong(K), C.c_void_p(sf.data_ptr()), rows, K,
+                                      C.c_void_p(_lib.stream())), "mx_quant")
+    return q, sf
+
+
+def mx_dequantize(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
+    rows, K = q.shape
+    e = sf[sf_index(rows, K, q.device).reshape(-1)].view(rows, K // 32).float() - 127.0
+    return (q.float().view(rows, K // 32, 32) * torch.exp2(e).unsqueeze(-1)).view(rows, K)
+
+
+def gemm_mxfp8_ref(aq, sfa, bq, sfb, mblk_group=None, rows_per_group: int = 0, out_dtype=torch.bfloat16):
+    a, b = mx_dequantize(aq, sfa), mx_dequantize(bq, sfb)
+    if mblk_group is None:
+        return (a @ b.t()).to(out_dtype)
+    N = rows_per_group
+    out = torch.zeros((a.shape[0], N), device=aq.device, dtype=torch.float32)
+    for i, g in enumerate(mblk_group.tolist()):
+        if g >= 0:
+            out[i * 128:(i + 1) * 128] = a[i * 128:(i + 1) * 128] @ b[g * N:(g + 1) * N].t()
+    return out.to(out_dtype)
+
+
+def gemm_mxfp8(aq: torch.Tensor, sfa: torch.Tensor, bq: torch.Tensor, sfb: torch.Tensor, *,
+               out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+               mblk_group: Optional[torch.Tensor] = None, mblk_rows: Optional[torch.Tensor] = None,
+               rows_per_group: int = 0) -> torch.Tensor:
+    if not aq.is_cuda:
+        return gemm_mxfp8_ref(aq, sfa, bq, sfb, mblk_group, rows_per_group, out_dtype)
+    M, K = aq.shape
+    N = rows_per_group if mblk_group is not None else bq.shape[0]
+    assert K % 128 == 0 and N % 128 == 0 and bq.shape[0] % 128 == 0 and aq.stride(1) == 1 and bq.stride(1) == 1
+    assert sfa.numel() >= sf_bytes(M, K) and sfb.numel() >= sf_bytes(bq.shape[0], K)
+    if out is None:
+        out = torch.empty((M, N), device=aq.device, dtype=out_dtype)
+    a = _lib.MxGemmArgs()
+    a.A, a.B, a.C, a.sfa, a.sfb = aq.data_ptr(), bq.data_ptr(), out.data_ptr(), sfa.data_ptr(), sfb.data_ptr()
+    a.lda, a.ldb, a.ldc = aq.stride(0), bq.stride(0), out.stride(0)
+    a.a_rows, a.b_rows = aq.shape[0], bq.shape[0]
+    a.M, a.N, a.K = M, N, K
+    a.out_f32 = int(out.dtype == torch.float32)
+    if mblk_group is not None:
+        a.mode, a.mblk_group, a.group_stride_b = 1, mblk_group.data_ptr(), rows_per_group
+        a.mblk_rows = mblk_rows.data_ptr() if mblk_rows is not None else None
+    _lib.check(_lib.lib().np_gemm_mxfp8(C.byref(a), C.c_void_p(_lib.stream())), "gemm_mxfp8")
+    return out
+
+
+class _MXLinear(torch.autograd.Function):
+    """Forward through the MXFP8 GEMM (activations and weight quantised per 1x32 block along the contraction);
+    both backward GEMMs in bf16 on the unquantised tensors."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        from .gemm import gemm
+
+        x2 = x.reshape(-1, x.shape[-1])
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        xq, sx = mx_quantize(x2)
+        wq, sw = mx_quantize(w if w.is_contiguous() else w.contiguous())
+        y = gemm_mxfp8(xq, sx, wq, sw)
+        ctx.save_for_backward(x2, w)
+        ctx.x_shape = x.shape
+        ctx.gemm = gemm
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .gemm import _wgrad_into
+
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+        dx = ctx.gemm(dy2, w, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dw = _wgrad_into(w, dy2, x2) if (ctx.needs_input_grad[1] or hasattr(w, "main_grad")) else None
+        return dx, dw
+
+
+def mx_linear_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 2 and
+            w.shape[1] % 128 == 0 and w.shape[0] % 128 == 0)
+
+
+def mx_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` with the forward GEMM in MXFP8."""
+    y = _MXLinear.apply(x, w)
+    return y if bias is None else y + bias

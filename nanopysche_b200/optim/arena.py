@@ -182,6 +182,9 @@ class ParamArena:
         if self.device.type != "cuda":
             return
         for m in self.model.modules():
+            if any(hasattr(p, "_fsdp_rt") for p in m.parameters(recurse=False)) or \
+                    any(hasattr(l.weight, "_fsdp_rt") for l in m.children() if isinstance(l, nn.Linear)):
+                continue  # row-sharded weights are gathered one by one inside their GEMMs
             if isinstance(m, Attention) and m.w_q.bias is None and m.w_q.weight.dtype == torch.bfloat16:
                 m._fused_qkv = self._fused_view([m.w_q.weight, m.w_k.weight, m.w_v.weight])
             elif isinstance(m, FeedForward) and m.w1.bias is None and m.w1.weight.dtype == torch.bfloat16:

@@ -8,6 +8,10 @@ Two sharding back ends sit behind the reference's hook names:
 * the flat parameter arena (``optim/arena.py``) shards optimizer state and gradients over the
   data-parallel group (ZeRO-2 layout) and runs reduce-scatter + AdamW + all-gather as one sm_100a
   kernel over peer memory (``ops/zero.py``); ``parallelize_model`` picks it on CUDA.
+* ``fully_shard_linears`` (``backend="sharded"``) additionally shards the bf16 weights of the linear layers by rows
+  (ZeRO-3 layout): the all-gather of a weight runs inside the GEMM that consumes it and the weight gradient comes
+  back reduce-scattered (``ops/fsdp_fused.py``); everything that is not such a weight stays with the arena's ZeRO
+  step.
 """
 from __future__ import annotations
 
@@ -44,7 +48,9 @@ class DataParallelConfig:
     reduce_dtype: torch.dtype = torch.float32
     wrapping_strategy: TransformerDataParallelWrappingStrategy = TransformerDataParallelWrappingStrategy.full
     prefetch_factor: int = 0
-    backend: str = "auto"  # "auto" | "torch" (fully_shard) | "arena" (flat ZeRO arena, CUDA)
+    # "auto" | "torch" (fully_shard) | "arena" (flat ZeRO arena, CUDA) | "sharded" (arena + row-sharded linear
+    # weights gathered inside their GEMMs, CUDA)
+    backend: str = "auto"
 
 
 def _mesh_ok(mesh) -> bool:
@@ -104,3 +110,66 @@ def apply_activation_checkpointing(model: nn.Module, mode: str = "full", block_i
 def apply_generic_fsdp(model: nn.Module, dp_mesh=None, dp_config: Optional[DataParallelConfig] = None):
     cfg = dp_config or DataParallelConfig()
     return shard_module(model, dp_mesh, mp_policy=MixedPrecision(cfg.param_dtype, cfg.reduce_dtype))
+
+
+def fully_shard_linears(model: nn.Module, group, *, device=None, skip=()):
+    """Shard the weight of every eligible ``nn.Linear`` by rows over ``group`` (ZeRO-3 layout for the GEMM weights).
+
+    Eligible: bf16 CUDA weight without bias, not tied to an embedding, rows divisible into shards of a multiple of
+    128 rows. ``lin.weight`` becomes this rank's ``[rows / n, in]`` shard, tagged with the shared ``FSDPRuntime``
+    (``_fsdp_rt``) so ``ops.gemm.linear`` runs it as all-gather-inside-GEMM with a reduce-scattered weight
+    gradient, and with ``_ep_sharded`` so the parameter arena treats it as rank-local (no second gradient
+    reduction; its squared norm is summed over the ranks). Returns the runtime, or ``None`` when nothing qualified.
+
+    Plays the role of ``fully_shard`` on the transformer blocks (reference: distributed/fsdp.py:18-83)."""
+    import torch.distributed as dist
+
+    from ..ops.fsdp_fused import FSDPRuntime
+
+    n = dist.get_world_size(group)
+    if n <= 1:
+        return None
+    rank = dist.get_rank(group)
+    tied = {id(m.weight) for m in model.modules() if isinstance(m, nn.Embedding)}
+    todo = []
+    for name, m in model.named_modules():
+        if not isinstance(m, nn.Linear) or m.bias is not None or name in skip:
+            continue
+        w = m.weight
+        if id(w) in tied or not w.is_cuda or w.dtype != torch.bfloat16 or getattr(w, "_ep_sharded", False):
+            continue
+        if not FSDPRuntime.supported(w.shape[0], n) or w.shape[1] % 64:
+            continue
+        todo.append((name, m))
+    if not todo:
+        return None
+    rt = FSDPRuntime(group, max(m.weight.numel() for _, m in todo), device=device or todo[0][1].weight.device)
+    for name, m in todo:
+        full = m.weight.data
+        ns = full.shape[0] // n
+        shard = nn.Parameter(full[rank * ns:(rank + 1) * ns].clone())
+        shard._fsdp_rt = rt
+        shard._fsdp_full_rows = full.shape[0]
+        shard._ep_sharded = True
+        m.weight = shard
+    model._fsdp_linear_runtime = rt
+    model._fsdp_sharded_linears = [name for name, _ in todo]
+    return rt
+
+
+def gather_sharded_linears(model: nn.Module) -> dict:
+    """``{module name: full bf16 weight}`` of the linears sharded by ``fully_shard_linears`` (NCCL all-gather; for
+    checkpoints and evaluation outside the sharded path)."""
+    import torch.distributed as dist
+
+    rt = getattr(model, "_fsdp_linear_runtime", None)
+    out = {}
+    if rt is None:
+        return out
+    mods = dict(model.named_modules())
+    for name in model._fsdp_sharded_linears:
+        w = mods[name].weight.data
+        full = torch.empty((w.shape[0] * rt.n, w.shape[1]), device=w.device, dtype=w.dtype)
+        dist.all_gather_into_tensor(full, w.contiguous(), group=rt.group)
+        out[name] = full
+    return out

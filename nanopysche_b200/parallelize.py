@@ -69,6 +69,13 @@ def parallelize_model(model: nn.Module, *, world_mesh, device: Optional[torch.de
         backend = getattr(dp_config, "backend", "auto")
         use_arena = backend == "arena" or (backend == "auto" and device is not None and
                                            torch.device(device).type == "cuda")
+        if backend == "sharded" and device is not None and torch.device(device).type == "cuda":
+            from .parallel.fsdp import fully_shard_linears
+
+            grp = dp_mesh.get_group() if hasattr(dp_mesh, "get_group") else dp_mesh
+            if grp is not None:
+                fully_shard_linears(model, grp, device=device)
+            use_arena = True
         if use_arena:
             # sharded optimizer state + fused reduce-scatter/AdamW/all-gather: set up by engine.prepare_training
             model._dp_mesh_for_arena = dp_mesh

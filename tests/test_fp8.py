@@ -102,6 +102,27 @@ def test_flow_moe_compute_threshold_switch_and_grads():
     assert off.last_path == "bf16"
 
 
+def test_flow_moe_compute_mxfp8_recipe():
+    """1x32 power-of-two scaled expert GEMMs (grouped form) against the per-row fp32 expert MLP."""
+    torch.manual_seed(5)
+    E, H, D = 3, 128, 256
+    w1, w2, w3 = (torch.nn.Parameter(torch.randn(E * H, D) * 0.1) for _ in range(3))
+    comp = fm.FP8FlowMoECompute(fm.FP8FlowMoEConfig(True, fm.FP8RecipeConfig(True, "mxfp8")), D, H, E,
+                                fp8_gemm_threshold=16)
+    assert comp.config.fp8_recipe.block_size == 32
+    comp.set_weights(w1, w2, w3)
+    x = torch.randn(300, D, requires_grad=True)
+    idx = torch.randint(0, E, (300,))
+    wts = torch.rand(300)
+    y = comp(x, wts, idx, 0, E)
+    assert comp.last_path == "mxfp8"
+    ref = torch.stack([(F.silu(x[i] @ w1[idx[i] * H:(idx[i] + 1) * H].t()) * (x[i] @ w3[idx[i] * H:(idx[i] + 1) * H].t()))
+                       @ w2[idx[i] * H:(idx[i] + 1) * H] for i in range(300)]) * wts.view(-1, 1)
+    assert ((y - ref).norm() / ref.norm()).item() < 0.08
+    y.sum().backward()
+    assert x.grad is not None and w2.grad is not None
+
+
 def test_moe_layer_with_flow_moe_recipe_and_fp8_linear():
     from nanopysche_b200.fp8.training import FP8Config, Float8Linear, apply_fp8, precompute_fp8_dynamic_scales
     from nanopysche_b200.models.moe import MoEBase

@@ -303,6 +303,55 @@ def test_fp8_block_gemm_grouped():
     assert rel(out, ref) < 1e-4
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (200, 256, 384), (4096, 2816, 2048)])
+def test_mxfp8_quantiser_and_gemm(M, N, K):
+    """1x32 e8m0-scaled e4m3: the quantiser against its PyTorch statement (bit exact) and the block-scaled tcgen05
+    GEMM against the fp32 product of the dequantised operands; scales vary per row and per 32-block."""
+    from nanopysche_b200.ops.gemm_mxfp8 import gemm_mxfp8, gemm_mxfp8_ref, mx_quantize, mx_quantize_ref
+
+    torch.manual_seed(14)
+    sc = lambda r: torch.exp2(torch.randint(-8, 9, (r, K // 32), device="cuda").float()).repeat_interleave(32, 1)
+    x = (torch.randn(M, K, device="cuda") * sc(M)).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05 * sc(N)).bfloat16()
+    xq, xs = mx_quantize(x)
+    wq, ws = mx_quantize(w)
+    xq_r, xs_r = mx_quantize_ref(x)
+    assert torch.equal(xq.view(torch.uint8), xq_r.view(torch.uint8)) and torch.equal(xs, xs_r)
+    got = gemm_mxfp8(xq, xs, wq, ws, out_dtype=torch.float32)
+    assert rel(got, gemm_mxfp8_ref(xq, xs, wq, ws, out_dtype=torch.float32)) < 1e-4
+    assert rel(got, x.float() @ w.float().t()) < 0.06
+    assert rel(gemm_mxfp8(xq, xs, wq, ws), got) < 5e-3  # bf16 output
+
+
+def test_mxfp8_gemm_grouped_and_linear():
+    from nanopysche_b200.ops.gemm_mxfp8 import gemm_mxfp8, gemm_mxfp8_ref, mx_linear, mx_quantize
+
+    torch.manual_seed(15)
+    E, N, K, blocks = 4, 256, 512, 6
+    x = torch.randn(blocks * 128, K, device="cuda").bfloat16()
+    w = (torch.randn(E * N, K, device="cuda") * 0.05).bfloat16()
+    grp = torch.tensor([0, 3, 1, 3, 2, 1], dtype=torch.int32, device="cuda")
+    rows = torch.tensor([128, 128, 77, 0, 128, 128], dtype=torch.int32, device="cuda")
+    xq, xs = mx_quantize(x)
+    wq, ws = mx_quantize(w)
+    out = torch.zeros(blocks * 128, N, device="cuda", dtype=torch.float32)
+    gemm_mxfp8(xq, xs, wq, ws, out=out, mblk_group=grp, mblk_rows=rows, rows_per_group=N)
+    ref = gemm_mxfp8_ref(xq, xs, wq, ws, grp, N, torch.float32)
+    ref[2 * 128 + 77:3 * 128] = 0
+    ref[3 * 128:4 * 128] = 0
+    assert rel(out, ref) < 1e-4
+    # linear with MXFP8 forward and bf16 backward
+    xl = torch.randn(4, 96, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    wl = (torch.randn(N, K, device="cuda") * 0.05).bfloat16().requires_grad_()
+    y = mx_linear(xl, wl)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf = xl.detach().float().requires_grad_(), wl.detach().float().requires_grad_()
+    yr = xf @ wf.t()
+    yr.backward(g.float())
+    assert rel(y, yr) < 0.06 and rel(xl.grad, xf.grad) < 1e-2 and rel(wl.grad, wf.grad) < 1e-2
+
+
 @pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,causal", [
     (1, 128, 128, 1, 1, False), (2, 512, 512, 4, 2, True), (1, 200, 200, 2, 2, True),
     (1, 128, 384, 2, 1, True), (1, 384, 256, 2, 2, False), (1, 1, 300, 4, 2, True)])

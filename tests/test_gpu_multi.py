@@ -266,3 +266,61 @@ def _fsdp_fused_worker(rank, world):
 def test_fused_fully_sharded_linear_two_gpus():
     _need2()
     assert all(run_distributed(_fsdp_fused_worker, 2, backend="nccl"))
+
+
+def _fsdp_model_worker(rank, world):
+    import copy
+
+    import torch.distributed as dist
+
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.engine import prepare_training
+    from nanopysche_b200.ops import _lib
+    from nanopysche_b200.parallel.fsdp import fully_shard_linears, gather_sharded_linears
+
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    cfg = TransformerConfig(vocab_size=1024, d_model=512, n_layers=2, n_heads=4, n_kv_heads=2, ffn_hidden=1024,
+                            max_seq_len=128, qk_norm=False)
+    model = cfg.build(dtype=torch.bfloat16, init_device=str(dev))
+    ref = copy.deepcopy(model).float()
+    rt = fully_shard_linears(model, dist.group.WORLD, device=dev)
+    assert rt is not None and len(model._fsdp_sharded_linears) >= 2 * 7
+    w_q = model.blocks["0"].attention.w_q.weight
+    assert w_q.shape == (256, 512) and w_q._fsdp_rt is rt
+    model._needs_grad_sync = True
+    opt, arena = prepare_training(model, dp_group=dist.group.WORLD, lr=1e-2, max_grad_norm=1.0)
+    assert any(not r.replicated for r in arena.regions.values())
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.0)
+    opt.param_groups[0]["weight_decay"] = 0.0
+    torch.manual_seed(5 + rank)
+    losses, rlosses = [], []
+    for _ in range(3):
+        ids = torch.randint(0, 1024, (2, 128), device=dev)
+        loss = model(ids, labels=ids)["loss"]
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        rl = ref(ids, labels=ids)["loss"]
+        rl.backward()
+        for p in ref.parameters():
+            dist.all_reduce(p.grad)
+            p.grad.div_(world)
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+        ropt.step()
+        ropt.zero_grad()
+        losses.append(float(loss))
+        rlosses.append(float(rl))
+    torch.cuda.synchronize()
+    _lib.check_status("fsdp_model")
+    assert all(abs(a - b) < 0.05 * abs(b) + 0.05 for a, b in zip(losses, rlosses)), (losses, rlosses)
+    full = gather_sharded_linears(model)
+    for name in ("blocks.0.attention.w_q", "blocks.1.feed_forward.w2"):
+        assert rel(full[name], ref.get_submodule(name).weight) < 3e-2, name
+    dist.barrier()
+    return True
+
+
+def test_fully_sharded_model_two_gpus():
+    _need2()
+    assert all(run_distributed(_fsdp_model_worker, 2, backend="nccl"))
