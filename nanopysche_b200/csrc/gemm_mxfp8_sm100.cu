@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const __nv_bfloat16* __re
     int e = -127;
     if (am > 0.f) {
       int ex;
-      const float mant = frexpf(am * (1.f / 448.f), &ex);   // am / 448 = mant * 2^ex, mant in [0.5, 1)
+      const float mant = frexpf(__fdiv_rn(am, 448.f), &ex);    // am / 448 = mant * 2^ex, mant in [0.5, 1)
       e = (mant == 0.5f) ? ex - 1 : ex;                     // ceil(log2(am / 448))
       e = max(-127, min(127, e));
     }

@@ -336,6 +336,39 @@ __global__ void __launch_bounds__(256) router_dx_kernel(const float* __restrict_
   }
 }
 
+// Same product for E <= 8 with D = 8 * blockDim.x: a thread keeps its 8 columns of all gate rows in registers and
+// walks TOK tokens, so the only memory traffic per token is the [E] gradient row (broadcast) and one 16-byte store.
+template <int TOK>
+__global__ void __launch_bounds__(256) router_dx_reg_kernel(const float* __restrict__ dl, const float* __restrict__ wg,
+                                                            __nv_bfloat16* __restrict__ dx, int T, int D, int E) {
+  const int d = threadIdx.x * 8;
+  float w[8][8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
+    if (e < E) {
+      w0 = __ldg(reinterpret_cast<const float4*>(wg + (size_t)e * D + d));
+      w1 = __ldg(reinterpret_cast<const float4*>(wg + (size_t)e * D + d + 4));
+    }
+    w[e][0] = w0.x; w[e][1] = w0.y; w[e][2] = w0.z; w[e][3] = w0.w;
+    w[e][4] = w1.x; w[e][5] = w1.y; w[e][6] = w1.z; w[e][7] = w1.w;
+  }
+  const int t0 = blockIdx.x * TOK;
+#pragma unroll 4
+  for (int i = 0; i < TOK; ++i) {
+    const int t = t0 + i;
+    if (t >= T) break;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float g = e < E ? __ldg(dl + (size_t)t * E + e) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += g * w[e][j];
+    }
+    *reinterpret_cast<uint4*>(dx + (size_t)t * D + d) = pack8(acc);
+  }
+}
+
 __global__ void colsum2_kernel(const float* __restrict__ partial, float* __restrict__ out, int parts,
                                long long cols, int accumulate) {
   const long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -795,8 +828,13 @@ NP_API int np_router_dgate(const float* dl, const void* x, float* dwg, float* db
 NP_API int np_router_dx(const float* dl, const float* wg, void* dx, int T, int D, int E, void* stream) {
   if (D % 8) return 1;
   if (T <= 0) return 0;
-  long long blocks = ((long long)T * (D / 8) + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (E <= 8 && D % 8 == 0 && D / 8 <= 256 && D / 8 >= 32) {
+    constexpr int TOK = 8;
+    router_dx_reg_kernel<TOK><<<(unsigned)((T + TOK - 1) / TOK), D / 8, 0, (cudaStream_t)stream>>>(
+        dl, wg, (__nv_bfloat16*)dx, T, D, E);
+    CHECK_LAUNCH();
+  }
+  const long long blocks = ((long long)T * (D / 8) + 255) / 256;
   router_dx_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(dl, wg, (__nv_bfloat16*)dx, T, D, E);
   CHECK_LAUNCH();
 }

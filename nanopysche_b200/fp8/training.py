@@ -1,10 +1,13 @@
 """FP8 training for dense Linear layers (reference: fp8/training.py:54-137, which delegates to
 torchao's ``convert_to_float8_training``).
 
-Here ``apply_fp8`` swaps eligible ``nn.Linear`` modules for ``Float8Linear``: e4m3 forward operands
-with dynamic blockwise scales (1x128 activations, 128x128 weights), gradients in bf16 (the
-reference's e5m2 backward dtype is accepted and recorded). The quantise-dequantise pair is applied
-around the GEMM, so the numerics are those of fp8 operands with fp32 accumulation on every device.
+Here ``apply_fp8`` swaps eligible ``nn.Linear`` modules for ``Float8Linear`` and tags their weights with the
+recipe (``weight._fp8_recipe``): e4m3 forward operands with dynamic scales - ``blockwise`` (1x128 activations,
+128x128 weights, fp32 scales) or ``mxfp8`` (1x32 blocks, power-of-two scales) - and gradients in bf16 (the
+reference's e5m2 backward dtype is accepted and recorded). On bf16 CUDA tensors ``ops.gemm.linear`` sends a tagged
+weight to the fp8 tcgen05 GEMM of its recipe (``csrc/gemm_fp8_sm100.cu``, ``csrc/gemm_mxfp8_sm100.cu``), whether
+the layer is called as a module or its weight is used by a fused block; elsewhere the quantise-dequantise pair
+is applied around the GEMM, which gives the numerics of fp8 operands with fp32 accumulation on every device.
 """
 from __future__ import annotations
 
@@ -46,12 +49,31 @@ class _QDQ(torch.autograd.Function):
         return g, None
 
 
+class _QDQmx(torch.autograd.Function):
+    """MXFP8 quantise-dequantise (1x32 blocks along the last dimension) with a straight-through gradient."""
+
+    @staticmethod
+    def forward(ctx, x):
+        from ..ops.gemm_mxfp8 import mx_dequantize, mx_quantize_ref
+
+        q, s = mx_quantize_ref(x.reshape(-1, x.shape[-1]))
+        return mx_dequantize(q, s).to(x.dtype).reshape(x.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g
+
+
 class Float8Linear(nn.Linear):
     def forward(self, x):
         if x.shape[-1] % 128 or self.weight.shape[0] % 128:
             return super().forward(x)
         from ..ops.gemm import linear
 
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
+            return linear(x, self.weight, self.bias)  # dispatches on the weight's recipe tag
+        if getattr(self.weight, "_fp8_recipe", None) == "mxfp8":
+            return nn.functional.linear(_QDQmx.apply(x), _QDQmx.apply(self.weight), self.bias)
         return linear(_QDQ.apply(x, False), _QDQ.apply(self.weight, True), self.bias)
 
 
@@ -71,6 +93,7 @@ def apply_fp8(model: nn.Module, config: Optional[FP8Config] = None,
             if module_filter is not None and not module_filter(child, fqn):
                 continue
             child.__class__ = Float8Linear
+            child.weight._fp8_recipe = "mxfp8" if cfg.recipe_name == "mxfp8" else "blockwise"
     model._fp8_config = cfg
     return model
 

@@ -146,6 +146,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
 
             y = sharded_linear(x, w, rt)
             return y if bias is None else y + bias
+        rec = getattr(w, "_fp8_recipe", None)
+        if rec is not None:  # weight tagged by fp8.training.apply_fp8: forward GEMM on e4m3 operands
+            if rec == "mxfp8":
+                from .gemm_mxfp8 import mx_linear, mx_linear_supported
+
+                if mx_linear_supported(x, w):
+                    return mx_linear(x, w, bias)
+            else:
+                from .gemm_fp8 import fp8_block_linear, fp8_block_linear_supported
+
+                if fp8_block_linear_supported(x, w):
+                    return fp8_block_linear(x, w, bias)
         y = _Linear.apply(x, w)
         return y if bias is None else y + bias
     return torch.nn.functional.linear(x, w, bias)

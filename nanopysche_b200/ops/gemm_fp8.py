@@ -63,3 +63,41 @@ def gemm_fp8_block(aq: torch.Tensor, sa: torch.Tensor, bq: torch.Tensor, sb: tor
         setattr(a, k, v)
     _lib.check(_lib.lib().np_gemm_fp8_block(C.byref(a), C.c_void_p(_lib.stream())), "gemm_fp8_block")
     return out
+
+
+class _Fp8BlockLinear(torch.autograd.Function):
+    """Forward GEMM on e4m3 operands (1x128 activation scales, 128x128 weight scales); backward GEMMs in bf16."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        from fp8_flow_moe import ops as fops
+
+        x2 = x.reshape(-1, x.shape[-1])
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        xq, xs = fops.quantize_to_fp8(x2)
+        wq, ws = fops.quantize_weight_blockwise(w if w.is_contiguous() else w.contiguous())
+        y = gemm_fp8_block(xq, xs.contiguous(), wq, ws.contiguous())
+        ctx.save_for_backward(x2, w)
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .gemm import _wgrad_into, gemm
+
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+        dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dw = _wgrad_into(w, dy2, x2) if (ctx.needs_input_grad[1] or hasattr(w, "main_grad")) else None
+        return dx, dw
+
+
+def fp8_block_linear_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 2 and
+            w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0)
+
+
+def fp8_block_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    y = _Fp8BlockLinear.apply(x, w)
+    return y if bias is None else y + bias

@@ -176,7 +176,35 @@ def case_attention(a):
     return res, fl, None
 
 
-CASES = {"attention": case_attention, "gemm": case_gemm, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "xent": case_xent,
+def case_mxfp8(a):
+    """MXFP8 GEMM (operands quantised beforehand), the quantiser alone, and the block-scaled 1x128 kernel."""
+    from .gemm_mxfp8 import gemm_mxfp8, mx_quantize
+
+    M, N, K = a.m, a.n, a.k
+    A, B = torch.randn(M, K, device="cuda").bfloat16(), torch.randn(N, K, device="cuda").bfloat16()
+    aq, sa = mx_quantize(A)
+    bq, sb = mx_quantize(B)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    med, best = timeit(lambda: gemm_mxfp8(aq, sa, bq, sb, out=out), a.iters)
+    qmed, _ = timeit(lambda: mx_quantize(A), a.iters)
+    flops = 2.0 * M * N * K
+    res = {"case": "mxfp8", "M": M, "N": N, "K": K, "ms": med, "ms_best": best, "tflops": flops / med / 1e9,
+           "quant_ms": qmed, "quant_gbs": M * K * 3.03 / qmed / 1e6}
+    if a.cublas:
+        from fp8_flow_moe import ops as fops
+
+        from .gemm_fp8 import gemm_fp8_block
+
+        xq, xs = fops.quantize_to_fp8(A)
+        wq, ws = fops.quantize_weight_blockwise(B)
+        m2, _ = timeit(lambda: gemm_fp8_block(xq, xs, wq, ws, out=out), a.iters)
+        res["block128_ms"], res["block128_tflops"] = m2, flops / m2 / 1e9
+        m3, _ = timeit(lambda: torch.matmul(A, B.t()), a.iters)
+        res["cublas_bf16_ms"], res["cublas_bf16_tflops"] = m3, flops / m3 / 1e9
+    return res, flops, None
+
+
+CASES = {"mxfp8": case_mxfp8, "attention": case_attention, "gemm": case_gemm, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "xent": case_xent,
          "moe": case_moe}
 
 

@@ -172,6 +172,9 @@ class ParamArena:
         w.main_grad = r.grads[off0:end].view(rows, cols)
         w._main_grad_dirty = False
         w._covers = list(plist)
+        recipes = {getattr(p, "_fp8_recipe", None) for p in plist}
+        if len(recipes) == 1 and None not in recipes:  # all covered weights share an fp8 recipe
+            w._fp8_recipe = recipes.pop()
         self.fused.append(w)
         return w
 

@@ -142,6 +142,15 @@ def test_moe_layer_with_flow_moe_recipe_and_fp8_linear():
     out = net(x)
     out.sum().backward()
     assert ((out - full).norm() / full.norm()).item() < 0.1 and net[0].weight.grad is not None
+    assert net[0].weight._fp8_recipe == "blockwise"
+    net_mx = torch.nn.Sequential(torch.nn.Linear(128, 256), torch.nn.ReLU(), torch.nn.Linear(256, 128))
+    net_mx.load_state_dict({k: v for k, v in net.state_dict().items()})
+    apply_fp8(net_mx, FP8Config(enabled=True, recipe_name="mxfp8"))
+    assert net_mx[2].weight._fp8_recipe == "mxfp8"
+    out_mx = net_mx(x)
+    out_mx.sum().backward()
+    assert ((out_mx - full).norm() / full.norm()).item() < 0.1 and net_mx[2].weight.grad is not None
+    assert not torch.equal(out_mx, out)
 
 
 @pytest.mark.gpu

@@ -352,6 +352,25 @@ def test_mxfp8_gemm_grouped_and_linear():
     assert rel(y, yr) < 0.06 and rel(xl.grad, xf.grad) < 1e-2 and rel(wl.grad, wf.grad) < 1e-2
 
 
+@pytest.mark.parametrize("recipe", ["blockwise", "mxfp8"])
+def test_fp8_recipe_tag_routes_linear_to_the_fp8_gemm(recipe):
+    from nanopysche_b200.ops.gemm import linear
+
+    torch.manual_seed(16)
+    x = torch.randn(3, 100, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(384, 512, device="cuda") * 0.05).bfloat16().requires_grad_()
+    plain = linear(x, w)
+    w._fp8_recipe = recipe
+    y = linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = xf @ wf.t()
+    yr.backward(g.float())
+    assert 1e-3 < rel(y, yr) < 0.06 and not torch.equal(y, plain)   # fp8 operands, not the bf16 GEMM
+    assert rel(x.grad, xf.grad) < 1e-2 and rel(w.grad, wf.grad) < 1e-2
+
+
 @pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,causal", [
     (1, 128, 128, 1, 1, False), (2, 512, 512, 4, 2, True), (1, 200, 200, 2, 2, True),
     (1, 128, 384, 2, 1, True), (1, 384, 256, 2, 2, False), (1, 1, 300, 4, 2, True)])
