@@ -289,34 +289,41 @@ def _fsdp_model_worker(rank, world):
     w_q = model.blocks["0"].attention.w_q.weight
     assert w_q.shape == (256, 512) and w_q._fsdp_rt is rt
     model._needs_grad_sync = True
-    opt, arena = prepare_training(model, dp_group=dist.group.WORLD, lr=1e-2, max_grad_norm=1.0)
+    opt, arena = prepare_training(model, dp_group=dist.group.WORLD, lr=1e-3, max_grad_norm=1.0)
     assert any(not r.replicated for r in arena.regions.values())
-    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.0)
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.0)
     opt.param_groups[0]["weight_decay"] = 0.0
     torch.manual_seed(5 + rank)
     losses, rlosses = [], []
-    for _ in range(3):
+    for it in range(3):
         ids = torch.randint(0, 1024, (2, 128), device=dev)
         loss = model(ids, labels=ids)["loss"]
         loss.backward()
-        opt.step()
-        opt.zero_grad()
         rl = ref(ids, labels=ids)["loss"]
         rl.backward()
         for p in ref.parameters():
             dist.all_reduce(p.grad)
             p.grad.div_(world)
-        torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+        if it == 0:  # the shard's gradient is the sum over the ranks' batches of the rows this rank owns
+            for name in ("blocks.0.attention.w_q", "blocks.1.feed_forward.w2", "lm_head"):
+                g = model.get_submodule(name).weight.main_grad / world
+                ns = g.shape[0]
+                gr = ref.get_submodule(name).weight.grad[rank * ns:(rank + 1) * ns]
+                assert rel(g, gr) < 3e-2, (name, rel(g, gr))
+        opt.step()
+        opt.zero_grad()
+        gn = torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+        assert abs(float(opt.last_grad_norm) - float(gn)) < 0.03 * float(gn), (float(opt.last_grad_norm), float(gn))
         ropt.step()
         ropt.zero_grad()
-        losses.append(float(loss))
-        rlosses.append(float(rl))
+        losses.append(float(loss.detach()))
+        rlosses.append(float(rl.detach()))
     torch.cuda.synchronize()
     _lib.check_status("fsdp_model")
-    assert all(abs(a - b) < 0.05 * abs(b) + 0.05 for a, b in zip(losses, rlosses)), (losses, rlosses)
+    assert all(abs(a - b) < 0.02 * abs(b) + 0.02 for a, b in zip(losses, rlosses)), (losses, rlosses)
     full = gather_sharded_linears(model)
     for name in ("blocks.0.attention.w_q", "blocks.1.feed_forward.w2"):
-        assert rel(full[name], ref.get_submodule(name).weight) < 3e-2, name
+        assert rel(full[name], ref.get_submodule(name).weight) < 3e-2, (name, rel(full[name], ref.get_submodule(name).weight))
     dist.barrier()
     return True
 
