@@ -9,10 +9,14 @@
 // chunk is one 512-byte bulk copy into shared memory and one tcgen05.cp (32 lanes x 128 bit, replicated to the four
 // lane quarters) into tensor memory.
 //
-// CTA roles: warp 0 lane 0 issues the copies (TMA tiles of A and B, bulk copies of the two scale chunks) into a
-// 6-stage ring; warp 1 lane 0 copies the scales of a stage into TMEM and issues four K = 32 MMAs whose instruction
-// descriptors select byte 0..3 of the scale words; warps 2-5 drain one of two 128-column accumulators (tcgen05.ld)
-// while the next tile accumulates into the other. Accumulation over the whole K stays in TMEM - no per-block
+// CTA roles: warp 0 lane 0 issues the copies (TMA tiles of A and B, bulk copies of the scale chunks) into a
+// 5-stage ring; warp 1 lane 0 copies the scales of a stage into TMEM and issues four K = 32 MMAs whose instruction
+// descriptors select byte 0..3 of the scale words; warps 2-5 drain one of two 192-column accumulators (tcgen05.ld)
+// while the next tile accumulates into the other. The tile is 128 x 192: two 192-column fp32 accumulators plus the
+// scale columns fit the 512 TMEM columns (two 256-column ones would leave none for the scales), and the operand
+// bytes per FLOP that cross from L2 drop by a fifth against a 128 x 128 tile. A 192-row B tile starts at row 0 or
+// 64 of a 128-row scale chunk, so both chunks it touches are copied and the MMA's B-scale address is offset by
+// (row % 128) / 32 columns. Accumulation over the whole K stays in TMEM - no per-block
 // promotion in registers as in the 1x128 / 128x128 kernel of gemm_fp8_sm100.cu. Row-grouped mode (one B row offset
 // per 128-row block of A) serves grouped expert GEMMs. Every wait is bounded and reports through the status word.
 //
@@ -23,12 +27,14 @@
 namespace {
 
 constexpr int BM = 128;
-constexpr int BN = 128;
-constexpr int BK = 128;   // four MMAs of K = 32; one scale chunk per operand
-constexpr int STAGES = 6;
+constexpr int BN = 192;   // 1.5 scale chunks of B per tile: a tile starts at row 0 or 64 of a 128-row chunk
+constexpr int BK = 128;   // four MMAs of K = 32; one scale chunk of A and two of B per stage
+constexpr int STAGES = 5;
 constexpr int KID_MX = 3;
 constexpr int SF_BYTES = 512;
-constexpr int TMEM_COLS = 512;            // 2 x 128 accumulator columns + 8 scale columns per stage
+constexpr int SF_SMEM = 2048;             // A chunk + two B chunks, padded so that stages stay 1024-byte aligned
+constexpr int SF_COLS = 12;               // TMEM columns per stage: 4 for A, 8 for the two B chunks
+constexpr int TMEM_COLS = 512;            // 2 x 192 accumulator columns + 12 scale columns per stage
 constexpr int SF_COL0 = 2 * BN;
 
 struct MxParams {
@@ -40,6 +46,7 @@ struct MxParams {
   int out_f32;
   int mode;                    // 0 dense, 1 row-grouped
   const int* mblk_group; const int* mblk_rows; long long group_stride_b;
+  long long b_chunks;          // 128-row scale chunks of B
 };
 
 __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
@@ -78,7 +85,8 @@ __host__ __device__ constexpr uint32_t make_idesc_mx(int m, int n, int a_sf, int
 
 __global__ void __launch_bounds__(192, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const MxParams p) {
-  constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;
+  constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES + SF_SMEM;
+  constexpr int TX_BYTES = A_BYTES + B_BYTES + 3 * SF_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (np::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
@@ -131,17 +139,22 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (tile_rows(m_blk) == 0) continue;
         const long long brow = b_row0(m_blk, n_blk);
         const uint8_t* sfa = p.sfa + (size_t)m_blk * nkb * SF_BYTES;
-        const uint8_t* sfb = p.sfb + (size_t)(brow / BN) * nkb * SF_BYTES;
+        // the two 128-row scale chunks of B that cover rows [brow, brow + 192); past the last chunk the last one is
+        // read again (those output columns lie beyond N and are never stored)
+        const long long c0 = brow / 128, c1 = (c0 + 1 < p.b_chunks) ? c0 + 1 : p.b_chunks - 1;
+        const uint8_t* sfb0 = p.sfb + (size_t)c0 * nkb * SF_BYTES;
+        const uint8_t* sfb1 = p.sfb + (size_t)c1 * nkb * SF_BYTES;
         bool ok = true;
         for (int kb = 0; kb < nkb && ok; ++kb) {
           ok = np::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, KID_MX, 1);
           if (!ok) break;
           const uint32_t sA = smem_base + stage * STAGE_BYTES, sB = sA + A_BYTES, sSF = sB + B_BYTES;
-          np::mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          np::mbar_expect_tx(full_bar(stage), TX_BYTES);
           np::tma_load_2d(sA, &tmA, full_bar(stage), kb * BK, m_blk * BM);
           np::tma_load_2d(sB, &tmB, full_bar(stage), kb * BK, (int)brow);
           bulk_load(sSF, sfa + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
-          bulk_load(sSF + SF_BYTES, sfb + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
+          bulk_load(sSF + SF_BYTES, sfb0 + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
+          bulk_load(sSF + 2 * SF_BYTES, sfb1 + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
@@ -153,8 +166,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
-        const int m_blk = t % m_blocks;
+        const int m_blk = t % m_blocks, n_blk = t / m_blocks;
         if (tile_rows(m_blk) == 0) continue;
+        // B scales of the tile's first row sit in column (row % 128) / 32 of the first chunk's four columns
+        const uint32_t sfb_off = (uint32_t)((b_row0(m_blk, n_blk) % 128) / 32);
         bool ok = np::mbar_wait(aempty_bar(acc), acc_phase ^ 1u, abort_flag, KID_MX, 2);
         if (!ok) break;
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
@@ -163,15 +178,16 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (!ok) break;
           np::tc_fence_after();
           const uint32_t sA = smem_base + stage * STAGE_BYTES, sB = sA + A_BYTES, sSF = sB + B_BYTES;
-          const uint32_t t_sfa = tmem_base + (uint32_t)(SF_COL0 + stage * 8), t_sfb = t_sfa + 4;
+          const uint32_t t_sfa = tmem_base + (uint32_t)(SF_COL0 + stage * SF_COLS), t_sfb = t_sfa + 4;
           tmem_cp_32x128b_x4(t_sfa, desc_noswizzle(sSF, 16, 128));
           tmem_cp_32x128b_x4(t_sfb, desc_noswizzle(sSF + SF_BYTES, 16, 128));
+          tmem_cp_32x128b_x4(t_sfb + 4, desc_noswizzle(sSF + 2 * SF_BYTES, 16, 128));
 #pragma unroll
           for (int kk = 0; kk < BK / 32; ++kk) {
             const uint64_t ad = np::make_smem_desc(sA + kk * 32, 16, 1024);
             const uint64_t bd = np::make_smem_desc(sB + kk * 32, 16, 1024);
             np::tc_fence_after();
-            tc_mma_mxf8(tmem_d, ad, bd, make_idesc_mx(BM, BN, kk, kk), t_sfa, t_sfb, (kb | kk) ? 1u : 0u);
+            tc_mma_mxf8(tmem_d, ad, bd, make_idesc_mx(BM, BN, kk, kk), t_sfa, t_sfb + sfb_off, (kb | kk) ? 1u : 0u);
           }
           np::tc_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -306,7 +322,7 @@ struct NpMxGemmArgs {
 NP_API int np_gemm_mxfp8(const NpMxGemmArgs* args, void* stream) {
   const NpMxGemmArgs& a = *args;
   if (a.M <= 0 || a.N <= 0) return 0;
-  if (a.K % 128 || a.N % 128 || (a.lda % 16) || (a.ldb % 16) || (((uintptr_t)a.A) & 15) || (((uintptr_t)a.B) & 15) ||
+  if (a.K % 128 || a.N % 8 || a.b_rows % 128 || (a.lda % 16) || (a.ldb % 16) || (((uintptr_t)a.A) & 15) || (((uintptr_t)a.B) & 15) ||
       (((uintptr_t)a.sfa) & 15) || (((uintptr_t)a.sfb) & 15) || (a.group_stride_b % 128))
     return 1;
   static thread_local bool ctx_bound = false;
@@ -325,7 +341,8 @@ NP_API int np_gemm_mxfp8(const NpMxGemmArgs* args, void* stream) {
   p.C = a.C; p.sfa = (const uint8_t*)a.sfa; p.sfb = (const uint8_t*)a.sfb;
   p.M = a.M; p.N = a.N; p.K = a.K; p.ldc = a.ldc; p.out_f32 = a.out_f32;
   p.mode = a.mode; p.mblk_group = a.mblk_group; p.mblk_rows = a.mblk_rows; p.group_stride_b = a.group_stride_b;
-  constexpr int SMEM = STAGES * (BM * BK + BN * BK + 2 * SF_BYTES) + 1024 + 256;
+  p.b_chunks = a.b_rows / 128;
+  constexpr int SMEM = STAGES * (BM * BK + BN * BK + SF_SMEM) + 1024 + 256;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -335,7 +352,7 @@ NP_API int np_gemm_mxfp8(const NpMxGemmArgs* args, void* stream) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const long long tiles = (long long)((a.M + BM - 1) / BM) * (a.N / BN);
+  const long long tiles = (long long)((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
   const int cap = a.max_ctas > 0 ? a.max_ctas : sms;
   const int grid = (int)(tiles < cap ? tiles : cap);
   gemm_mxfp8_kernel<<<grid, 192, SMEM, (cudaStream_t)stream>>>(tmA, tmB, p);
