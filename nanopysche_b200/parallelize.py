@@ -69,6 +69,10 @@ def parallelize_model(model: nn.Module, *, world_mesh, device: Optional[torch.de
         backend = getattr(dp_config, "backend", "auto")
         use_arena = backend == "arena" or (backend == "auto" and device is not None and
                                            torch.device(device).type == "cuda")
+        if backend == "sharded" and tp_config is not None and tp_config.degree > 1:
+            # the fused tensor-parallel linears read their weights directly (ops/tp_fused.py)
+            log.warning("  row-sharded linears are not combined with tensor parallelism: using the arena's ZeRO step")
+            backend = "arena"
         if backend == "sharded" and device is not None and torch.device(device).type == "cuda":
             from .parallel.fsdp import fully_shard_linears
 
