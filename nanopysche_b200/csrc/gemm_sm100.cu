@@ -67,6 +67,7 @@ struct GemmParams {
   uint4* push_dst[8]; int* push_flag[8]; int push_n;
   int* push_ctr;
   bool st32;                  // output rows and column chunks are 32-byte aligned: use 32-byte stores
+  const float* bias;          // optional [N] fp32 added to every output row (plain epilogue)
 };
 
 // 64 bytes (32 bf16 packed in 16 registers) to a row: two 32-byte stores when the address allows it (a full sector
@@ -428,6 +429,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int col = n0 + c * 32;
           if (!row_ok || col >= p.N) continue;
           const bool full = col + 32 <= p.N;
+          if (p.bias) {  // the same 32 values for every row of the warp: broadcast loads
+            const float inv_alpha = 1.f / p.alpha;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float b = (col + i < p.N) ? __ldg(p.bias + col + i) : 0.f;
+              r[i] = __float_as_uint(fmaf(b, inv_alpha, __uint_as_float(r[i])));
+            }
+          }
           if (p.out_f32) {
             float* dst = (float*)crow + col;
             if (full) {
@@ -572,6 +581,7 @@ struct NpGemmArgs {
   // (r < push_n <= 8; the destinations already point at this rank's slot), then *push_flag[r] = epoch (+ base);
   // push_ctr: a zeroed local int
   const void* push_src; long long push_bytes; void* const* push_dst; int* const* push_flag; int push_n; int* push_ctr;
+  const float* bias;  // optional [N] fp32 bias added in the plain epilogue (alpha != 0)
 };
 
 template <int BN, int STAGES>
@@ -619,6 +629,7 @@ static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
     p.b_loc_lo = a.b_loc_lo; p.b_loc_hi = a.b_loc_hi;
   }
   p.C = a.C; p.C2 = a.C2; p.M = a.M; p.N = a.N; p.K = a.K; p.ldc = a.ldc; p.ldc2 = a.ldc2;
+  p.bias = (a.epilogue == 0 && a.alpha != 0.f) ? a.bias : nullptr;
   p.a_mn = a.a_mn; p.b_mn = a.b_mn; p.out_f32 = a.out_f32; p.accumulate = a.accumulate;
   p.epilogue = a.epilogue; p.mode = a.mode; p.alpha = a.alpha;
   p.mblk_group = a.mblk_group; p.mblk_rows = a.mblk_rows; p.group_stride_b = a.group_stride_b;

@@ -46,6 +46,7 @@ class GemmArgs(C.Structure):
         ("b_local_flag", c_int), ("m_rot", c_int), ("n_rot", c_int),
         ("push_src", c_void_p), ("push_bytes", c_ll), ("push_dst", c_void_p), ("push_flag", c_void_p),
         ("push_n", c_int), ("push_ctr", c_void_p),
+        ("bias", c_void_p),
     ]
 
 

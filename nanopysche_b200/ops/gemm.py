@@ -40,11 +40,23 @@ def gemm_ref(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, accumula
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None, accumulate: bool = False,
-         alpha: float = 1.0, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
-    """``out[M, N] (+)= alpha * A @ B^T`` in the operand layouts described in the module docstring."""
+         alpha: float = 1.0, bn: int = 0, max_ctas: int = 0, bias: torch.Tensor | None = None,
+         residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[M, N] (+)= alpha * A @ B^T (+ bias) (+ residual)`` in the operand layouts described in the module
+    docstring. ``bias [N]`` (fp32) and ``residual [M, N]`` (dtype of ``out``) are added in the GEMM's epilogue."""
     if not _use_kernel(a):
-        return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, out=out, out_dtype=out_dtype, accumulate=accumulate,
-                        alpha=alpha)
+        if bias is None and residual is None:
+            return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, out=out, out_dtype=out_dtype, accumulate=accumulate,
+                            alpha=alpha)
+        y = gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32, alpha=alpha)
+        if bias is not None:
+            y = y + bias.float()
+        if residual is not None:
+            y = y + residual.float()
+        if out is None:
+            return y.to(out_dtype or a.dtype)
+        out.copy_((y + out.float()) if accumulate else y)
+        return out
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "kernel path is bf16"
     assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
@@ -64,6 +76,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     args.accumulate = int(accumulate)
     args.alpha = alpha
     args.bn, args.max_ctas = bn, max_ctas
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous()
+        args.bias = bias.data_ptr()
+    if residual is not None:
+        assert not accumulate and residual.shape == (M, N) and residual.dtype == out.dtype and residual.stride(1) == 1
+        args.accumulate, args.Cin, args.ldcin = 1, residual.data_ptr(), residual.stride(0)
     rc = _lib.lib().np_gemm_bf16(C.byref(args), C.c_void_p(_lib.stream()))
     if rc != 0:
         raise _lib.KernelError(
@@ -137,6 +155,30 @@ class _Linear(torch.autograd.Function):
         return dx, dw
 
 
+class _LinearBias(torch.autograd.Function):
+    """``x @ w.T + bias`` with the bias added in the GEMM's epilogue."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        ctx.save_for_backward(x, w)
+        ctx.bias_dtype = bias.dtype
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w, bias=bias.detach().float().contiguous())
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = gemm(dy2, w, b_mn=True).reshape(x.shape) if ctx.needs_input_grad[0] else None
+        dw = _wgrad_into(w, dy2, x2) if (ctx.needs_input_grad[1] or hasattr(w, "main_grad")) else None
+        db = dy2.float().sum(0).to(ctx.bias_dtype) if ctx.needs_input_grad[2] else None
+        return dx, dw, db
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ w.T (+ bias)``; tcgen05 kernels for bf16 CUDA tensors, ``F.linear`` otherwise."""
     if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
@@ -158,6 +200,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
 
                 if fp8_block_linear_supported(x, w):
                     return fp8_block_linear(x, w, bias)
-        y = _Linear.apply(x, w)
-        return y if bias is None else y + bias
+        if bias is not None:
+            return _LinearBias.apply(x, w, bias)
+        return _Linear.apply(x, w)
     return torch.nn.functional.linear(x, w, bias)

@@ -352,6 +352,31 @@ def test_mxfp8_gemm_grouped_and_linear():
     assert rel(y, yr) < 0.06 and rel(xl.grad, xf.grad) < 1e-2 and rel(wl.grad, wf.grad) < 1e-2
 
 
+@pytest.mark.parametrize("M,N,K,f32", [(300, 200, 192, False), (1024, 768, 512, True)])
+def test_gemm_bias_and_residual_epilogue(M, N, K, f32):
+    """Bias (per output column) and residual (same shape as the output) added in the GEMM's epilogue."""
+    from nanopysche_b200.ops.gemm import gemm, linear
+
+    torch.manual_seed(17)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    dt = torch.float32 if f32 else torch.bfloat16
+    res = torch.randn(M, N, device="cuda").to(dt)
+    ref = a.float() @ b.float().t()
+    assert rel(gemm(a, b, bias=bias, out_dtype=dt), ref + bias) < 6e-3
+    assert rel(gemm(a, b, residual=res, out_dtype=dt), ref + res.float()) < 6e-3
+    assert rel(gemm(a, b, bias=bias, residual=res, out_dtype=dt, alpha=0.5), 0.5 * ref + bias + res.float()) < 6e-3
+    x = a.view(2, M // 2, K).clone().requires_grad_()
+    w = b.clone().requires_grad_()
+    bb = bias.bfloat16().requires_grad_()
+    y = linear(x, w, bb)
+    g = torch.randn_like(y)
+    y.backward(g)
+    assert rel(y, ref.view(2, M // 2, N) + bb.float()) < 6e-3
+    assert rel(bb.grad, g.float().sum((0, 1))) < 6e-3 and rel(w.grad, g.float().view(M, N).t() @ a.float()) < 6e-3
+
+
 @pytest.mark.parametrize("recipe", ["blockwise", "mxfp8"])
 def test_fp8_recipe_tag_routes_linear_to_the_fp8_gemm(recipe):
     from nanopysche_b200.ops.gemm import linear
