@@ -111,6 +111,85 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __
   }
 }
 
+// RMSNorm forward with an e4m3 output for an fp8 GEMM that follows: the normalised row (rounded to bf16 first, so the
+// result equals quantising the bf16 output of the plain kernel) is quantised per 1x128 block with an fp32 scale
+// amax / 448; y (bf16) is optional. cols must be a multiple of 128: a block is the 16 consecutive threads of a
+// half-warp, 8 elements each.
+template <int MAXV>
+__global__ void __launch_bounds__(NT) rmsnorm_quant_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ res,
+                                                               const float* __restrict__ w,
+                                                               __nv_bfloat16* __restrict__ y,
+                                                               __nv_bfloat16* __restrict__ h_out,
+                                                               float* __restrict__ rstd, uint8_t* __restrict__ q,
+                                                               float* __restrict__ scales, int rows, int cols,
+                                                               float eps) {
+  __shared__ float red[32];
+  const int nvec = cols >> 3, bpr = cols >> 7;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const __nv_bfloat16* xr = x + (size_t)r * cols;
+    float v[MAXV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = threadIdx.x + i * NT;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+      if (c < nvec) {
+        load8(xr + c * 8, v[i]);
+        if (res) {
+          float t[8];
+          load8(res + (size_t)r * cols + c * 8, t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] += t[j];
+        }
+        if (h_out) {
+          store8(h_out + (size_t)r * cols + c * 8, v[i]);
+          if (res) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16(v[i][j]));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+      }
+    }
+    ss = block_sum(ss, red);
+    const float rs = rsqrtf(ss / (float)cols + eps);
+    if (threadIdx.x == 0 && rstd) rstd[r] = rs;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = threadIdx.x + i * NT;
+      const bool ok = c < nvec;       // whole half-warps are in or out (cols % 128 == 0): the shuffles stay converged
+      float o[8];
+      float am = 0.f;
+      const int cc = ok ? c : 0;
+      const float4 w0 = *reinterpret_cast<const float4*>(w + cc * 8);
+      const float4 w1 = *reinterpret_cast<const float4*>(w + cc * 8 + 4);
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = __bfloat162float(__float2bfloat16(v[i][j] * rs * wv[j]));
+        am = fmaxf(am, fabsf(o[j]));
+      }
+#pragma unroll
+      for (int d = 8; d > 0; d >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, d));
+      const float scale = fmaxf(am, 1e-12f) / 448.f, inv = 1.f / scale;
+      if (ok) {
+        if (y) store8(y + (size_t)r * cols + c * 8, o);
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          lo |= (uint32_t)__nv_cvt_float_to_fp8(o[j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+          hi |= (uint32_t)__nv_cvt_float_to_fp8(o[4 + j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+        }
+        *reinterpret_cast<uint2*>(q + (size_t)r * cols + c * 8) = make_uint2(lo, hi);
+        if ((threadIdx.x & 15) == 0) scales[(size_t)r * bpr + (c >> 4)] = scale;
+      }
+    }
+  }
+}
+
 // dx = rs * (w*dy - xhat * mean(w*dy*xhat)) [+ dres]; per-CTA partial dw into scratch[grid, cols].
 template <int MAXV>
 __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
@@ -849,6 +928,23 @@ NP_API int np_rmsnorm_fwd(const void* x, const void* res, const float* w, void* 
   else
     rmsnorm_fwd_kernel<4><<<grid, NT, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, w,
                                               (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, rows, cols, eps);
+  CHECK_LAUNCH();
+}
+
+// RMSNorm (+ residual) with an e4m3 + 1x128-scale output (q [rows, cols] bytes, scales [rows, cols / 128] fp32);
+// y may be null when only the quantised output is wanted. cols a multiple of 128.
+NP_API int np_rmsnorm_quant_fwd(const void* x, const void* res, const float* w, void* y, void* h_out, float* rstd,
+                                void* q, float* scales, int rows, int cols, float eps, void* stream) {
+  if (cols % 128 || cols > NT * 8 * 4) return 1;
+  const int grid = rows < GRID_CAP ? rows : GRID_CAP;
+  if (grid <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+#define RQ(V) rmsnorm_quant_fwd_kernel<V><<<grid, NT, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, w, \
+      (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, (uint8_t*)q, scales, rows, cols, eps)
+  if (cols <= NT * 8) RQ(1);
+  else if (cols <= NT * 16) RQ(2);
+  else RQ(4);
+#undef RQ
   CHECK_LAUNCH();
 }
 

@@ -80,3 +80,38 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual:
     if _kernel_ok(x, weight) and (residual is None or (residual.dtype == x.dtype and residual.is_cuda)):
         return _RMSNorm.apply(x, weight, residual, eps)
     return rms_norm_ref(x, weight, eps, residual)
+
+
+def rms_norm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual: torch.Tensor | None = None,
+                   return_bf16: bool = False):
+    """RMSNorm whose output is already quantised for an fp8 GEMM: ``(q e4m3 [rows, D], scales fp32 [rows, D / 128])``
+    with 1x128 blocks and ``scale = amax / 448`` - bit-identical to quantising the bf16 result of ``rms_norm``, in
+    one pass over the row. Also returns ``x + residual`` when a residual is given and the bf16 output when
+    ``return_bf16``. Forward only (inference, or the recompute half of a checkpointed block)."""
+    D = x.shape[-1]
+    x2 = x.reshape(-1, D)
+    if not (_kernel_ok(x, weight) and D % 128 == 0):
+        from fp8_flow_moe import ops as fops
+
+        out = rms_norm_ref(x2, weight, eps, None if residual is None else residual.reshape(-1, D))
+        y, h = (out if residual is not None else (out, None))
+        q, s = fops.quantize_to_fp8(y)
+        res = [q, s]
+    else:
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        r2 = None
+        if residual is not None:
+            r2 = residual.reshape(-1, D)
+            r2 = r2 if r2.is_contiguous() else r2.contiguous()
+        rows = x2.shape[0]
+        q = torch.empty((rows, D), device=x.device, dtype=torch.float8_e4m3fn)
+        s = torch.empty((rows, D // 128), device=x.device, dtype=torch.float32)
+        y = torch.empty_like(x2) if return_bf16 else None
+        h = torch.empty_like(x2) if residual is not None else None
+        _lib.call("rmsnorm_quant_fwd", x2, r2, weight, y, h, None, q, s, rows, D, float(eps))
+        res = [q, s]
+    if residual is not None:
+        res.append(h.view(x.shape))
+    if return_bf16:
+        res.append(y.view(x.shape))
+    return tuple(res)

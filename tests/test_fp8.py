@@ -175,3 +175,14 @@ def test_fp8_kernels_match_torch_reference():
     hq, hs = ops.fused_silu_multiply_quantize(g, u)
     ref = F.silu(g.float()) * u.float()
     assert ((ops.dequantize_from_fp8(hq, hs, dtype=torch.float32) - ref).norm() / ref.norm()).item() < 0.04
+
+
+def test_rmsnorm_with_fp8_output_cpu_path():
+    from nanopysche_b200.ops.norm import rms_norm_quant, rms_norm_ref
+
+    torch.manual_seed(6)
+    x, res, w = torch.randn(10, 256), torch.randn(10, 256), torch.rand(256) + 0.5
+    q, s, h, y = rms_norm_quant(x, w, 1e-6, res, return_bf16=True)
+    y_ref, h_ref = rms_norm_ref(x, w, 1e-6, res)
+    assert torch.equal(h, h_ref) and torch.equal(y, y_ref) and q.shape == (10, 256) and s.shape == (10, 2)
+    assert ((ops.dequantize_from_fp8(q, s, dtype=torch.float32) - y_ref).norm() / y_ref.norm()).item() < 0.04

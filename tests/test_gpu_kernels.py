@@ -352,6 +352,29 @@ def test_mxfp8_gemm_grouped_and_linear():
     assert rel(y, yr) < 0.06 and rel(xl.grad, xf.grad) < 1e-2 and rel(wl.grad, wf.grad) < 1e-2
 
 
+@pytest.mark.parametrize("rows,D,with_res", [(300, 256, False), (4096, 2048, True), (77, 4096, True)])
+def test_rmsnorm_with_fp8_output(rows, D, with_res):
+    """RMSNorm (+ residual) writing e4m3 + 1x128 scales: equal, bit for bit, to quantising the plain kernel's output."""
+    from fp8_flow_moe import ops as fops
+    from nanopysche_b200.ops.norm import rms_norm, rms_norm_quant
+
+    torch.manual_seed(18)
+    x = (torch.randn(rows, D, device="cuda") * 2).bfloat16()
+    res = torch.randn(rows, D, device="cuda").bfloat16() if with_res else None
+    w = torch.rand(D, device="cuda") + 0.5
+    out = rms_norm(x, w, 1e-6, res)
+    y, h = out if with_res else (out, None)
+    q_ref, s_ref = fops.quantize_to_fp8(y)
+    got = rms_norm_quant(x, w, 1e-6, res, return_bf16=True)
+    q, s = got[0], got[1]
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8)) and torch.equal(s, s_ref.view_as(s))
+    assert torch.equal(got[-1], y)
+    if with_res:
+        assert torch.equal(got[2], h)
+    deq = fops.dequantize_from_fp8(q, s, dtype=torch.float32)
+    assert rel(deq, y) < 0.04
+
+
 @pytest.mark.parametrize("M,N,K,f32", [(300, 200, 192, False), (1024, 768, 512, True)])
 def test_gemm_bias_and_residual_epilogue(M, N, K, f32):
     """Bias (per output column) and residual (same shape as the output) added in the GEMM's epilogue."""
