@@ -140,9 +140,16 @@ def case_moe(a):
         x.grad = None
 
     med, best = timeit(run, a.iters)
+
+    def fwd():
+        with torch.no_grad():
+            moe(x)
+
+    fmed, _ = timeit(fwd, a.iters)
     kept = T * K if a.capacity is None else min(T * K, E * int(a.capacity * T / E))
     flops = 3.0 * kept * 6.0 * D * H
     return {"case": "moe", "T": T, "D": D, "H": H, "E": E, "K": K, "capacity": a.capacity, "ms": med,
+            "fwd_ms": fmed, "fwd_tokens_per_s": T / fmed * 1e3,
             "tflops_upper_bound_rows": flops / med / 1e9}, None, None
 
 
