@@ -71,21 +71,6 @@ class FP8FlowMoECompute:
             self._wq_version = ver
         return self._wq_cache
 
-    def _mx_forward(self, xp: torch.Tensor, padded: torch.Tensor) -> torch.Tensor:
-        """Expert MLP over rows grouped per expert in multiples of 128 (``padded [E]`` rows per expert)."""
-        from nanopysche_b200.ops.gemm_mxfp8 import gemm_mxfp8, mx_quantize
-
-        H, D, E = self.hidden, self.d_model, padded.numel()
-        blocks = xp.shape[0] // 128
-        grp = torch.repeat_interleave(torch.arange(E, device=xp.device, dtype=torch.int32), padded // 128,
-                                      output_size=blocks)
-        w1q, s1, w3q, s3, w2q, s2 = self._mx_weights()
-        xq, sx = mx_quantize(xp.to(torch.bfloat16))
-        g = gemm_mxfp8(xq, sx, w1q, s1, mblk_group=grp, rows_per_group=H)
-        u = gemm_mxfp8(xq, sx, w3q, s3, mblk_group=grp, rows_per_group=H)
-        hq, sh = mx_quantize((F.silu(g.float()) * u.float()).to(torch.bfloat16))
-        return gemm_mxfp8(hq, sh, w2q, s2, mblk_group=grp, rows_per_group=D, out_dtype=xp.dtype)
-
     def use_fp8(self, tokens_per_expert: float) -> bool:
         c = self.config
         return bool(c.enabled and c.fp8_recipe.active and tokens_per_expert >= self.fp8_gemm_threshold and
@@ -105,11 +90,10 @@ class FP8FlowMoECompute:
             self.last_path = "fp8"
             xp, row_map, padded = ops.fused_permute_pad(x, idx, E, 128)
             if self.config.fp8_recipe.recipe_type == FP8RecipeType.MXFP8:
+                from nanopysche_b200.ops.gemm_mxfp8 import mx_expert_mlp
+
                 self.last_path = "mxfp8"
-                y = self._mx_forward(xp, padded)
-                if torch.is_grad_enabled() and (x.requires_grad or self.w1.requires_grad):
-                    y_ref = self._bf16(xp, padded)
-                    y = y_ref + (y - y_ref).detach()
+                y = mx_expert_mlp(xp, self.w1, self.w3, self.w2, padded.tolist(), self._mx_weights())
                 return ops.fused_unpermute_unpad(y, row_map, weights)
             xq, xs = ops.quantize_to_fp8(xp)
             w1q, s1, w3q, s3, w2q, s2 = self._quantised_weights()

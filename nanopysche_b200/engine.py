@@ -45,6 +45,14 @@ def prepare_training(model: nn.Module, *, tokens_per_rank: Optional[int] = None,
     if rt is not None:
         opt.post_step_hooks.append(rt.end_step)
     opt.post_step_hooks.append(_cp_end_step)
+    if any(m._fp8_flow_moe is not None for m in moes):
+        # the fused AdamW writes the weights from a kernel (no autograd version bump): drop the quantised copies
+        def _drop_quantised_weights():
+            for m in moes:
+                if m._fp8_flow_moe is not None:
+                    m._fp8_flow_moe._wq_cache = None
+
+        opt.post_step_hooks.append(_drop_quantised_weights)
     fs = getattr(model, "_fsdp_linear_runtime", None)
     if fs is not None:
         opt.post_step_hooks.append(fs.end_step)

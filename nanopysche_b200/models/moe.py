@@ -519,6 +519,10 @@ class MoEBase(nn.Module):
 
     def _can_fuse(self, x) -> bool:
         rt = self._fused_runtime
+        f = self._fp8_flow_moe
+        if f is not None and self.fp8_recipe == "mxfp8" and rt is not None and \
+                f.use_fp8(x.numel() // x.shape[-1] * self.top_k / max(self.num_experts, 1)):
+            return False  # the MXFP8 expert GEMMs live in the modular path (FP8FlowMoECompute)
         return (rt is not None and x.is_cuda and x.dtype == torch.bfloat16 and self.w1.dtype == torch.bfloat16
                 and self.shared_expert is None and self.router.config.normalize_expert_weights is None
                 and not (self.router.routing_replay and self.router._replay_mask is not None))

@@ -145,3 +145,66 @@ def mx_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     """``x @ w.T (+ bias)`` with the forward GEMM in MXFP8."""
     y = _MXLinear.apply(x, w)
     return y if bias is None else y + bias
+
+
+class _MXExpertMLP(torch.autograd.Function):
+    """``(silu(x w1_e^T) * (x w3_e^T)) w2_e`` over rows grouped per expert in multiples of 128: the three forward
+    GEMMs in MXFP8 (grouped form), the backward GEMMs in bf16 per expert on the unquantised tensors."""
+
+    @staticmethod
+    def forward(ctx, xp, w1, w3, w2, counts, quantised):
+        w1q, s1, w3q, s3, w2q, s2 = quantised
+        E = len(counts)
+        H, D = w1.shape[0] // E, w1.shape[1]
+        blocks = xp.shape[0] // 128
+        grp = torch.repeat_interleave(torch.arange(E, device=xp.device, dtype=torch.int32),
+                                      torch.tensor([c // 128 for c in counts], device=xp.device),
+                                      output_size=blocks)
+        xb = xp.to(torch.bfloat16)
+        xq, sx = mx_quantize(xb)
+        g = gemm_mxfp8(xq, sx, w1q, s1, mblk_group=grp, rows_per_group=H)
+        u = gemm_mxfp8(xq, sx, w3q, s3, mblk_group=grp, rows_per_group=H)
+        h = (torch.nn.functional.silu(g.float()) * u.float()).to(torch.bfloat16)
+        hq, sh = mx_quantize(h)
+        y = gemm_mxfp8(hq, sh, w2q, s2, mblk_group=grp, rows_per_group=D, out_dtype=xp.dtype)
+        ctx.save_for_backward(xb, g, u, w1, w3, w2)
+        ctx.counts, ctx.x_dtype = counts, xp.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .gemm import gemm
+
+        xb, g, u, w1, w3, w2 = ctx.saved_tensors
+        counts = ctx.counts
+        E = len(counts)
+        H, D = w1.shape[0] // E, w1.shape[1]
+        dyb = dy.to(torch.bfloat16)
+        dyb = dyb if dyb.is_contiguous() else dyb.contiguous()
+        dx = torch.zeros_like(xb)
+        dw1, dw3, dw2 = (torch.zeros(w.shape, device=w.device, dtype=torch.bfloat16) for w in (w1, w3, w2))
+        wb = [w.detach().to(torch.bfloat16) for w in (w1, w3, w2)]
+        start = 0
+        for e, c in enumerate(counts):
+            if c:
+                r = slice(start, start + c)
+                we1, we3, we2 = (w[e * H:(e + 1) * H] for w in wb)
+                gf, uf = g[r].float(), u[r].float()
+                sg = torch.sigmoid(gf)
+                dh = gemm(dyb[r], we2).float()                                   # [c, H] = dy w2_e^T
+                he = (gf * sg * uf).to(torch.bfloat16)
+                dg = (dh * uf * (sg * (1 + gf * (1 - sg)))).to(torch.bfloat16)
+                du = (dh * gf * sg).to(torch.bfloat16)
+                dx[r] = gemm(dg, we1, b_mn=True) + gemm(du, we3, b_mn=True)     # [c, D]
+                dw2[e * H:(e + 1) * H] = gemm(he, dyb[r], a_mn=True, b_mn=True)  # [H, D] = h^T dy
+                dw1[e * H:(e + 1) * H] = gemm(dg, xb[r], a_mn=True, b_mn=True)
+                dw3[e * H:(e + 1) * H] = gemm(du, xb[r], a_mn=True, b_mn=True)
+            start += c
+        return dx.to(ctx.x_dtype), dw1.to(w1.dtype), dw3.to(w3.dtype), dw2.to(w2.dtype), None, None
+
+
+def mx_expert_mlp(xp: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor, counts, quantised):
+    """Expert MLP over ``xp [P, D]`` whose rows are grouped per expert (``counts``: rows per expert, multiples of
+    128); ``w1, w3, w2: [E*H, D]``; ``quantised``: the six tensors of ``mx_quantize`` on w1, w3 and on w2 transposed
+    per expert to ``[E*D, H]``."""
+    return _MXExpertMLP.apply(xp, w1, w3, w2, list(counts), tuple(quantised))

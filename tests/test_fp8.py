@@ -119,8 +119,14 @@ def test_flow_moe_compute_mxfp8_recipe():
     ref = torch.stack([(F.silu(x[i] @ w1[idx[i] * H:(idx[i] + 1) * H].t()) * (x[i] @ w3[idx[i] * H:(idx[i] + 1) * H].t()))
                        @ w2[idx[i] * H:(idx[i] + 1) * H] for i in range(300)]) * wts.view(-1, 1)
     assert ((y - ref).norm() / ref.norm()).item() < 0.08
-    y.sum().backward()
-    assert x.grad is not None and w2.grad is not None
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    got = [t.grad.clone() for t in (x, w1, w2, w3)]
+    for t in (x, w1, w2, w3):
+        t.grad = None
+    ref.backward(gy)
+    for a, t, name in zip(got, (x, w1, w2, w3), ("x", "w1", "w2", "w3")):   # bf16 backward on the saved fp8 forward
+        assert ((a - t.grad).norm() / t.grad.norm()).item() < 0.08, name
 
 
 def test_moe_layer_with_flow_moe_recipe_and_fp8_linear():

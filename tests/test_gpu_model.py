@@ -165,6 +165,36 @@ def test_fused_moe_fp8_flow_path():
         assert rel(getattr(fused, n).grad, getattr(ref, n).grad) < 0.08, n
 
 
+def test_moe_layer_mxfp8_recipe_on_gpu():
+    """``mxfp8`` recipe with the fused runtime present: the layer leaves the fused path for the modular one whose
+    expert GEMMs run on the block-scaled tcgen05 kernel (forward MXFP8, backward bf16)."""
+    from nanopysche_b200.models.moe import MoEBase
+    from nanopysche_b200.ops import _lib
+    from nanopysche_b200.ops.moe import build_runtime
+
+    torch.manual_seed(1)
+    B, S, D, H, E, K = 2, 256, 256, 256, 4, 2
+    moe = MoEBase(d_model=D, hidden_size=H, num_experts=E, top_k=K, dtype=torch.bfloat16, device="cuda", init_std=0.05,
+                  fp8_flow_moe=True, fp8_recipe="mxfp8", fp8_gemm_threshold=64)
+    ref = MoEBase(d_model=D, hidden_size=H, num_experts=E, top_k=K, dtype=torch.float32, device="cuda", init_std=0.05)
+    ref.load_state_dict({k: v.float() for k, v in moe.state_dict().items()})
+    build_runtime([moe], tokens=B * S, device=torch.device("cuda"))
+    x = torch.randn(B, S, D, device="cuda").bfloat16()
+    assert not moe._can_fuse(x)
+    xa = x.clone().requires_grad_(True)
+    y = moe(xa)
+    assert moe._fp8_flow_moe.last_path == "mxfp8"
+    gy = torch.randn_like(y)
+    (y * gy).sum().backward()
+    xb = x.float().requires_grad_(True)
+    yr = ref(xb)
+    (yr * gy.float()).sum().backward()
+    _lib.check_status("mxfp8 moe")
+    assert rel(y, yr) < 0.08 and rel(xa.grad, xb.grad) < 0.08
+    for n in ("w1", "w2", "w3"):
+        assert rel(getattr(moe, n).grad, getattr(ref, n).grad) < 0.08, n
+
+
 def test_cli_train_and_bench_on_gpu(tmp_path, capsys):
     """The user-facing entry points on a GPU: a few optimizer steps of a small GQA + MoE model (head_dim 128, so the
     flash-attention, fused-MoE and arena paths all run) and the forward benchmark, through ``cli.main``."""
