@@ -185,7 +185,11 @@ def run_ours(args, rank, local, world):
                    "global_batch": c["batch_per_gpu"] * world, "seq_len": c["seq_len"], "parallelism": f"ep{world}",
                    "step": "forward+backward+clip+AdamW (fp32 masters)" + ("" if args.no_graph else ", replayed as one CUDA graph"),
                    "l2": "per-step working set (>5 GB of weights, gradients and activations) exceeds the 126 MB L2",
-                   "capacity": "int(1.25*T/E) per expert, whole-token drop in index order (reference rule)"},
+                   "capacity": "int(1.25*T/E) per expert, whole-token drop in index order (reference rule)",
+                   "dp_sync": ("none (one rank)" if world == 1 else
+                               "in-switch reduction and multicast stores (multimem over NVLS)"
+                               if arena is not None and any(r.mc_grads for r in arena.regions.values())
+                               else "reduce-scatter / all-gather by peer loads and stores")},
         "clocks": clocks,
         "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": host[0].numel() * host[0].element_size(), "d2h_bytes_per_step": 4},

@@ -218,6 +218,76 @@ __global__ void __launch_bounds__(256) zero_adamw_bcast_kernel(float* __restrict
   }
 }
 
+// The same two kernels through an NVLink multicast mapping of the gradient / weight arenas (NVLS): one
+// multimem.ld_reduce returns the sum over all ranks, formed inside the switch, so a rank receives its shard once
+// instead of once per peer; one multimem.st delivers the updated bf16 weights to every rank.
+__device__ __forceinline__ float4 mc_ld_reduce_f32x4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void mc_st_bf16x4(void* mc, uint32_t a, uint32_t b) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.bf16x2 [%0], {%1, %2};" ::"l"(mc), "r"(a), "r"(b) : "memory");
+}
+
+__global__ void __launch_bounds__(256) zero_reduce_mc_kernel(const float* __restrict__ mc_grads, long long lo,
+                                                             long long cnt, float scale, float* __restrict__ gshard,
+                                                             float* __restrict__ partial) {
+  __shared__ float red[32];
+  float ss = 0.f;
+  const long long nvec = cnt >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = mc_ld_reduce_f32x4(mc_grads + lo + 4 * i);
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    reinterpret_cast<float4*>(gshard)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  ss = np::warp_sum(ss);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = ss;
+  __syncthreads();
+  if (w == 0) {
+    float t = l < 8 ? red[l] : 0.f;
+    t = np::warp_sum(t);
+    if (l == 0) partial[blockIdx.x] = t;
+  }
+}
+
+__global__ void __launch_bounds__(256) zero_adamw_bcast_mc_kernel(float* __restrict__ p, const float* __restrict__ g,
+                                                                  float* __restrict__ m, float* __restrict__ v,
+                                                                  __nv_bfloat16* __restrict__ mc_w16, long long lo,
+                                                                  long long cnt, float lr, float b1, float b2, float eps,
+                                                                  float wd, float bc1, float bc2,
+                                                                  const float* __restrict__ gscale,
+                                                                  const float* __restrict__ hyper) {
+  const float gs = gscale ? gscale[0] : 1.f;
+  if (hyper) { lr = hyper[0]; bc1 = hyper[1]; bc2 = hyper[2]; }
+  const long long nvec = cnt >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 pp = reinterpret_cast<float4*>(p)[i];
+    const float4 gg = reinterpret_cast<const float4*>(g)[i];
+    float4 mm = reinterpret_cast<float4*>(m)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    float* P = &pp.x; const float* G = &gg.x; float* M = &mm.x; float* V = &vv.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gr = G[j] * gs;
+      M[j] = b1 * M[j] + (1.f - b1) * gr;
+      V[j] = b2 * V[j] + (1.f - b2) * gr * gr;
+      P[j] = P[j] * (1.f - lr * wd) - lr * (M[j] / bc1) / (sqrtf(V[j] / bc2) + eps);
+    }
+    reinterpret_cast<float4*>(p)[i] = pp;
+    reinterpret_cast<float4*>(m)[i] = mm;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    mc_st_bf16x4(mc_w16 + lo + 4 * i, np::pack_bf16(pp.x, pp.y), np::pack_bf16(pp.z, pp.w));
+  }
+}
+
 }  // namespace
 
 #define CHECK_LAUNCH() do { cudaError_t e_ = cudaGetLastError(); return e_ == cudaSuccess ? 0 : 500 + (int)e_; } while (0)
@@ -343,5 +413,25 @@ NP_API int np_zero_adamw_bcast(float* p, const float* g, float* m, float* v, voi
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
   zero_adamw_bcast_kernel<<<148 * 4, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, w, n, lo, cnt, lr, b1, b2, eps, wd,
                                                                     bc1, bc2, gscale, hyper);
+  CHECK_LAUNCH();
+}
+
+// NVLS forms of np_zero_reduce / np_zero_adamw_bcast: mc_grads / mc_w16 are the multicast addresses of the
+// gradient / weight arenas (memory of every rank bound to one NVLink multicast object at the same offsets).
+NP_API int np_zero_reduce_mc(const float* mc_grads, long long lo, long long cnt, float scale, float* gshard,
+                             float* partial, void* stream) {
+  if ((lo & 3) || (cnt & 3) || (((uintptr_t)mc_grads) & 15)) return 1;
+  zero_reduce_mc_kernel<<<np_zero_parts(), 256, 0, (cudaStream_t)stream>>>(mc_grads, lo, cnt, scale, gshard, partial);
+  CHECK_LAUNCH();
+}
+
+NP_API int np_zero_adamw_bcast_mc(float* p, const float* g, float* m, float* v, void* mc_w16, long long lo,
+                                  long long cnt, float lr, float b1, float b2, float eps, float wd, int step,
+                                  const float* gscale, const float* hyper, void* stream) {
+  if ((lo & 3) || (cnt & 3) || (((uintptr_t)mc_w16) & 15)) return 1;
+  if (cnt <= 0) return 0;
+  const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  zero_adamw_bcast_mc_kernel<<<148 * 4, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, (__nv_bfloat16*)mc_w16, lo, cnt, lr,
+                                                                       b1, b2, eps, wd, bc1, bc2, gscale, hyper);
   CHECK_LAUNCH();
 }

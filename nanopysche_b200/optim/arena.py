@@ -50,6 +50,9 @@ class _Region:
     lo: int = 0                              # owned shard [lo, lo+cnt) under ZeRO
     cnt: int = 0
     gshard: Optional[torch.Tensor] = None
+    mc_weights: int = 0                      # NVLink multicast addresses of the weight / gradient arenas (0: none)
+    mc_grads: int = 0
+    _mc_keep: Optional[tuple] = None         # symmetric-memory handles, kept alive with the region
 
 
 class ParamArena:
@@ -112,8 +115,20 @@ class ParamArena:
         symm = self.zero and r.replicated and r.dtype == torch.bfloat16
         total = self._padded(r.numel) if symm else (r.numel + 3) // 4 * 4
         if symm:
-            r.weights = self.heap.alloc((total,), r.dtype)
-            r.grads = self.heap.alloc((total,), torch.float32)
+            from ..parallel.symm import nvls_alloc
+
+            # NVLS: both arenas in multicast-bound memory, so that the gradient reduction happens inside the switch
+            # and one store delivers the new weights to every rank; otherwise plain peer loads / stores
+            mw = nvls_alloc(total, r.dtype, self.dp_group, dev)
+            mg = nvls_alloc(total, torch.float32, self.dp_group, dev) if mw is not None else None
+            if mw is not None and mg is not None:
+                r.weights, r.mc_weights, r._mc_keep = mw[0], mw[1], (mw[2], mg[2])
+                r.grads, r.mc_grads = mg[0], mg[1]
+                r.weights.zero_()
+                r.grads.zero_()
+            else:
+                r.weights = self.heap.alloc((total,), r.dtype)
+                r.grads = self.heap.alloc((total,), torch.float32)
             r.cnt = total // self.world
             r.lo = self.rank * r.cnt
         else:
@@ -285,7 +300,12 @@ class ArenaAdamW(torch.optim.Optimizer):
         extra = None
         for i, r in enumerate(a.regions.values()):
             part = self._partial[i * stride:(i + 1) * stride]
-            if a.zero and r.replicated and r.dtype == torch.bfloat16:
+            if a.zero and r.replicated and r.dtype == torch.bfloat16 and r.mc_grads:
+                _lib.check(_lib.lib().np_zero_reduce_mc(C.c_void_p(r.mc_grads), C.c_longlong(r.lo), C.c_longlong(r.cnt),
+                                                        C.c_float(inv), C.c_void_p(r.gshard.data_ptr()),
+                                                        C.c_void_p(part.data_ptr()), C.c_void_p(_lib.stream())),
+                           "zero_reduce_mc")
+            elif a.zero and r.replicated and r.dtype == torch.bfloat16:
                 ptrs = a.heap.host_ptr_array(r.grads)
                 _lib.check(_lib.lib().np_zero_reduce(ptrs, N, C.c_longlong(r.lo), C.c_longlong(r.cnt),
                                                      C.c_float(inv), C.c_void_p(r.gshard.data_ptr()),
@@ -316,7 +336,14 @@ class ArenaAdamW(torch.optim.Optimizer):
         torch.mul(self._coef[:1], inv, out=self._coef_local)  # coefficient for gradients not yet divided
         for r in a.regions.values():
             wdr = wd if r.decay else 0.0
-            if a.zero and r.replicated and r.dtype == torch.bfloat16:
+            if a.zero and r.replicated and r.dtype == torch.bfloat16 and r.mc_weights:
+                _lib.check(_lib.lib().np_zero_adamw_bcast_mc(
+                    C.c_void_p(r.master.data_ptr()), C.c_void_p(r.gshard.data_ptr()), C.c_void_p(r.m.data_ptr()),
+                    C.c_void_p(r.v.data_ptr()), C.c_void_p(r.mc_weights), C.c_longlong(r.lo), C.c_longlong(r.cnt),
+                    C.c_float(lr), C.c_float(b1), C.c_float(b2), C.c_float(eps), C.c_float(wdr), self.step_count,
+                    C.c_void_p(self._coef.data_ptr()), C.c_void_p(self._hyper.data_ptr()),
+                    C.c_void_p(_lib.stream())), "zero_adamw_bcast_mc")
+            elif a.zero and r.replicated and r.dtype == torch.bfloat16:
                 ptrs = a.heap.host_ptr_array(r.weights)
                 _lib.check(_lib.lib().np_zero_adamw_bcast(
                     C.c_void_p(r.master.data_ptr()), C.c_void_p(r.gshard.data_ptr()), C.c_void_p(r.m.data_ptr()),
