@@ -424,6 +424,264 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Forward with two Q tiles per CTA (plain single-source case: no arrival flags, no push, positions j * 128).
+//
+// One CTA owns 256 query rows of a (head, batch): tile 0 = rows [0, 128), tile 1 = rows [128, 256). Warps 2-5 are
+// the softmax group of tile 0 and warps 6-9 that of tile 1, one thread per row and all 128 score columns of a KV
+// block per thread, so no row exchange is needed. Both tiles share every K and V block, which halves the K/V
+// traffic per query row, and the MMA warp interleaves them:  P V of tile 0, S of tile 0 for the next block,
+// P V of tile 1, S of tile 1 ...  While one group is in its exp2 phase (which saturates the special-function
+// unit) the other group's maximum / rescale phases and the tensor pipe run. TMEM: S of tile t at columns [128 t,
+// 128 t + 128), O of tile t at [256 + 128 t, ...); P (bf16 pairs, 64 columns) overwrites the S it came from, which
+// is safe because a thread loads its whole row of S before it stores P, and S of the next block is only issued
+// after the P V that read P.
+enum { G_Q = 0, G_K = 1, G_KE = 4, G_V = 7, G_VE = 9, G_S = 11, G_P = 13, G_O = 15, G_COUNT = 17 };
+constexpr int G_KST = 3, G_VST = 2;   // Q0, Q1, three K stages, two V stages: seven 32 KB tiles
+
+__global__ void __launch_bounds__(320, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_al[];
+  const uint32_t base = np::smem_u32(smem_al);
+  if (base & 1023u) {
+    if (threadIdx.x == 0) np::report(NP_ERR_BAD_ARG, KID_ATTN, (int)(base & 1023u));
+    return;
+  }
+  const uint32_t sQ = base, sK0 = base + 2 * TILE_BYTES, sV0 = sK0 + G_KST * TILE_BYTES;
+  const uint32_t bar = sV0 + G_VST * TILE_BYTES;
+  auto B_ = [&](int i) { return bar + 8u * i; };
+  uint8_t* tail = smem_al + (2 + G_KST + G_VST) * TILE_BYTES + 8 * G_COUNT + 8;
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb2 = (p.Sq + 2 * BQ - 1) / (2 * BQ);
+  const int qb2 = nqb2 - 1 - (int)blockIdx.y;             // heaviest (most visible KV blocks) first
+  const int h = blockIdx.x % p.Hq, b = blockIdx.x / p.Hq;
+  const int hkv = h / (p.Hq / p.Hkv);
+  const int row0 = qb2 * 2 * BQ;                          // first query row of tile 0
+  // number of KV blocks tile t has to look at: the blocks form a prefix of the source
+  auto nvis = [&](int t) -> int {
+    if (row0 + t * BQ >= p.Sq) return 0;                  // tile past the end of the sequence
+    if (!p.causal) return p.src_blocks;
+    const int last = row0 + t * BQ + p.q_off + BQ - 1;    // position of the tile's last row
+    if (last < 0) return 0;
+    const int n = last / BKV + 1;
+    return n < p.src_blocks ? n : p.src_blocks;
+  };
+  const int nv0 = nvis(0), nv1 = nvis(1);
+  const int nv = nv0 > nv1 ? nv0 : nv1;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < G_COUNT; ++i) np::mbar_init(B_(i), (i == G_P || i == G_P + 1) ? 4 : 1);
+    *abort_flag = 0;
+    np::mbar_fence_init();
+  }
+  if (warp == 1) {
+    np::tmem_alloc(np::smem_u32((const void*)tmem_ptr_smem), 512);
+    np::tmem_relinquish();
+  }
+  np::tc_fence_before();
+  __syncthreads();
+  np::tc_fence_after();
+  const uint32_t tmem = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      np::mbar_expect_tx(B_(G_Q), 2 * TILE_BYTES);
+      load_tile(sQ, &tmQ, B_(G_Q), h, row0, b);
+      load_tile(sQ + TILE_BYTES, &tmQ, B_(G_Q), h, row0 + BQ, b);   // rows past the end read as zero
+      for (int i = 0; i < nv && !*abort_flag; ++i) {
+        const int ks = i % G_KST, vs = i % G_VST;
+        if (!np::mbar_wait(B_(G_KE + ks), ((uint32_t)(i / G_KST) & 1u) ^ 1u, abort_flag, KID_ATTN, 21)) break;
+        np::mbar_expect_tx(B_(G_K + ks), TILE_BYTES);
+        load_tile(sK0 + ks * TILE_BYTES, &tmK, B_(G_K + ks), hkv, i * BKV, b);
+        if (!np::mbar_wait(B_(G_VE + vs), ((uint32_t)(i / G_VST) & 1u) ^ 1u, abort_flag, KID_ATTN, 22)) break;
+        np::mbar_expect_tx(B_(G_V + vs), TILE_BYTES);
+        load_tile(sV0 + vs * TILE_BYTES, &tmV, B_(G_V + vs), hkv, i * BKV, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_qk = np::make_idesc(128, 128, 1, 1, 0, 0);
+      const uint32_t idesc_pv = np::make_idesc(128, 128, 1, 1, 0, 1);
+      bool ok = np::mbar_wait(B_(G_Q), 0, abort_flag, KID_ATTN, 23);
+      // S of tile t for block i (the K stage must have landed; the caller has waited for it)
+      auto issue_s = [&](int t, int i) {
+        const int ks = i % G_KST;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          np::tc_mma_f16(tmem + t * 128, desc_kmajor(sQ + t * TILE_BYTES, kk), desc_kmajor(sK0 + ks * TILE_BYTES, kk),
+                         idesc_qk, kk > 0);
+        np::tc_commit(B_(G_S + t));
+      };
+      auto wait_k = [&](int i) {
+        const bool w = np::mbar_wait(B_(G_K + i % G_KST), (uint32_t)(i / G_KST) & 1u, abort_flag, KID_ATTN, 24);
+        np::tc_fence_after();
+        return w;
+      };
+      auto issue_pv = [&](int t, int i) {
+        const int vs = i % G_VST;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tc_mma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, desc_mnmajor(sV0 + vs * TILE_BYTES, kk), idesc_pv,
+                        (i > 0) || (kk > 0));
+        np::tc_commit(B_(G_O + t));
+      };
+      if (ok && nv > 0) {
+        ok = wait_k(0);
+        if (ok) {
+          if (nv0 > 0) issue_s(0, 0);
+          if (nv1 > 0) issue_s(1, 0);
+          np::tc_commit(B_(G_KE + 0));
+        }
+      }
+      for (int i = 0; i < nv && ok && !*abort_flag; ++i) {
+        const int vs = i % G_VST;
+        bool have_k = false;
+        ok = np::mbar_wait(B_(G_V + vs), (uint32_t)(i / G_VST) & 1u, abort_flag, KID_ATTN, 25);
+        if (ok && i < nv0) {
+          ok = np::mbar_wait(B_(G_P + 0), (uint32_t)i & 1u, abort_flag, KID_ATTN, 26);   // P of tile 0 stored, O rescaled
+          if (!ok) break;
+          np::tc_fence_after();
+          issue_pv(0, i);
+          if (i + 1 < nv0) {
+            ok = wait_k(i + 1);
+            if (!ok) break;
+            have_k = true;
+            issue_s(0, i + 1);
+          }
+        }
+        if (ok && i < nv1) {
+          ok = np::mbar_wait(B_(G_P + 1), (uint32_t)i & 1u, abort_flag, KID_ATTN, 27);
+          if (!ok) break;
+          np::tc_fence_after();
+          issue_pv(1, i);
+        }
+        if (!ok) break;
+        np::tc_commit(B_(G_VE + vs));
+        if (i + 1 < nv) {
+          if (i + 1 < nv1) {
+            if (!have_k) ok = wait_k(i + 1);
+            if (!ok) break;
+            issue_s(1, i + 1);
+          }
+          np::tc_commit(B_(G_KE + (i + 1) % G_KST));
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax groups: one thread per query row
+    const int t = (warp - 2) >> 2;                        // tile of this warp's group
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem + t * 128 + lane_off, tO = tmem + 256 + t * 128 + lane_off;
+    const int row = row0 + t * BQ + r;
+    const int q_pos = row + p.q_off;
+    const int q_pos_first = row0 + t * BQ + p.q_off;
+    const int my_nv = t == 0 ? nv0 : nv1;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int i = 0; i < my_nv; ++i) {
+      const int kp0 = i * BKV;
+      const int valid_cols = p.src_len - kp0;
+      const bool need_mask = (p.causal && kp0 + BKV - 1 > q_pos_first) || valid_cols < BKV;
+      ok = ok && !*abort_flag && warp_wait(B_(G_S + t), (uint32_t)i & 1u, abort_flag, KID_ATTN, 28);
+      if (!ok) break;
+      np::tc_fence_after();
+      uint32_t s[128];
+      tmem_ld_cols<128>(tS, s);
+      if (need_mask) {
+#pragma unroll
+        for (int e = 0; e < 128; ++e)
+          if (e >= valid_cols || (p.causal && kp0 + e > q_pos)) s[e] = 0xff800000u;
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int e = 0; e < 128; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(s[e]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+      const bool grow = mx > m + RESCALE_LOG2 || (m == -INFINITY && mx > -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m, mx);
+        const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m - m_new);
+        if (i > 0) {
+          ok = warp_wait(B_(G_O + t), (uint32_t)(i - 1) & 1u, abort_flag, KID_ATTN, 29);   // P V of block i-1 is done
+          if (!ok) break;
+          np::tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld_cols<32>(tO + c * 32, o);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st_cols<32>(tO + c * 32, o);
+          }
+        }
+        l *= alpha;
+        m = m_new;
+      }
+      const float m_use = (m == -INFINITY) ? 0.f : m;
+      float rs[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {                      // 32 scores -> 16 packed columns of P, over the S they came from
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const float p0 = ex2(fmaf(__uint_as_float(s[c * 32 + e]), p.scale_log2, -m_use));
+          const float p1 = ex2(fmaf(__uint_as_float(s[c * 32 + e + 1]), p.scale_log2, -m_use));
+          rs[e & 2] += p0;
+          rs[(e & 2) + 1] += p1;
+          pk[e >> 1] = np::pack_bf16(p0, p1);
+        }
+        tmem_st16(tS + c * 16, pk);
+      }
+      l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
+      tmem_st_wait();
+      np::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) np::mbar_arrive(B_(G_P + t));
+    }
+    ok = ok && !*abort_flag;
+    if (ok && my_nv > 0) ok = warp_wait(B_(G_O + t), (uint32_t)(my_nv - 1) & 1u, abort_flag, KID_ATTN, 30);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && row0 + t * BQ < p.Sq) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = p.O + (size_t)b * p.o_sb + (size_t)row * p.o_ss + (size_t)h * p.o_sh;
+      if (my_nv > 0) np::tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        if (my_nv > 0) {
+          tmem_ld_cols<32>(tO + c * 32, o);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = 0u;
+        }
+        if (row < p.Sq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[8 * g + e]) * inv;
+            reinterpret_cast<uint4*>(dst + c * 32)[g] = make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]),
+                                                                   np::pack_bf16(f[4], f[5]), np::pack_bf16(f[6], f[7]));
+          }
+        }
+      }
+      if (p.lse && row < p.Sq)
+        p.lse[((size_t)b * p.lse_H + h) * p.Sq + row] = l > 0.f ? (m * 0.6931471805599453f + logf(l)) : -INFINITY;
+    }
+  }
+  np::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    np::tc_fence_after();
+    np::tmem_dealloc(tmem, 512);
+  }
+}
+
 int make_tmap_4d(CUtensorMap* out, const void* base, long long B, long long S, long long H, long long sb, long long ss,
                  long long sh) {
   NpEncodeTiledFn enc = np_get_encode_tiled();
@@ -522,6 +780,23 @@ NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
   fill_flags(&p.fl, a->src_flags, a->flag_idx, a->n_src, a->flag_epoch, a->epoch_base, a->flag_limit_ns,
              a->flag_own - 1);
   if (fill_push(&p.push, a)) return 1;
+  // Plain single-source case with more than one Q block: two Q tiles per CTA (attn_fwd2_kernel)
+  static const bool fwd2_on = [] { const char* e = getenv("NPB200_ATTN_FWD2"); return !(e && e[0] == '0'); }();
+  if (fwd2_on && a->n_src == 1 && !a->src_flags && !a->push_k && !a->q_blk_pos && !a->k_blk_pos && a->flag_own == 0 &&
+      a->Sq > BQ) {
+    constexpr int SMEM2 = (2 + G_KST + G_VST) * TILE_BYTES + 8 * G_COUNT + 8 + 16;
+    static_assert(SMEM2 <= 227 * 1024, "shared memory budget");
+    static bool attr2_set = false;
+    if (!attr2_set) {
+      cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2);
+      if (e != cudaSuccess) return 400 + (int)e;
+      attr2_set = true;
+    }
+    dim3 grid2(a->Hq * a->B, (a->Sq + 2 * BQ - 1) / (2 * BQ));
+    attn_fwd2_kernel<<<grid2, 320, SMEM2, (cudaStream_t)stream>>>(tmQ, tmK.m[0], tmV.m[0], p);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : 500 + (int)e;
+  }
   constexpr int NS = 2;   // softmax threads per row
   constexpr int SMEM = (1 + F_KST + F_VST) * TILE_BYTES + 8 * FB_COUNT + 8 + 16 + 2 * NS * 128 * 4 + 16;
   static_assert(SMEM <= 227 * 1024, "shared memory budget");
