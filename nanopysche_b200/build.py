@@ -50,7 +50,8 @@ def _newest_header_mtime() -> float:
 
 
 def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> tuple[str, int, str]:
-    cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    extra = os.environ.get("NPB200_NVCC_EXTRA", "").split()   # e.g. -DNP_ATTN_PROF for a development build
+    cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
     proc = subprocess.run(cmd, capture_output=True, text=True)

@@ -437,6 +437,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // is safe because a thread loads its whole row of S before it stores P, and S of the next block is only issued
 // after the P V that read P.
 enum { G_Q = 0, G_K = 1, G_KE = 4, G_V = 7, G_VE = 9, G_S = 11, G_P = 13, G_O = 15, G_COUNT = 17 };
+#ifdef NP_ATTN_PROF   // development build only: cycles per softmax phase, summed over (lane 0 of) all warps
+__device__ unsigned long long g_fwd2_prof[8];
+#define PROF_T(v) const long long v = clock64()
+#define PROF_ADD(i, a, b) do { if (lane == 0) atomicAdd(&g_fwd2_prof[i], (unsigned long long)((b) - (a))); } while (0)
+#else
+#define PROF_T(v) do {} while (0)
+#define PROF_ADD(i, a, b) do {} while (0)
+#endif
 constexpr int G_KST = 3, G_VST = 2;   // Q0, Q1, three K stages, two V stages: seven 32 KB tiles
 
 __global__ void __launch_bounds__(320, 1)
@@ -588,11 +596,14 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int kp0 = i * BKV;
       const int valid_cols = p.src_len - kp0;
       const bool need_mask = (p.causal && kp0 + BKV - 1 > q_pos_first) || valid_cols < BKV;
+      PROF_T(c0);
       ok = ok && !*abort_flag && warp_wait(B_(G_S + t), (uint32_t)i & 1u, abort_flag, KID_ATTN, 28);
       if (!ok) break;
       np::tc_fence_after();
+      PROF_T(c1);
       uint32_t s[128];
       tmem_ld_cols<128>(tS, s);
+      PROF_T(c2);
       if (need_mask) {
 #pragma unroll
         for (int e = 0; e < 128; ++e)
@@ -622,6 +633,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         l *= alpha;
         m = m_new;
       }
+      PROF_T(c3);
       const float m_use = (m == -INFINITY) ? 0.f : m;
       float rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -638,10 +650,14 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_st16(tS + c * 16, pk);
       }
       l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
+      PROF_T(c4);
       tmem_st_wait();
       np::tc_fence_before();
       __syncwarp();
       if (lane == 0) np::mbar_arrive(B_(G_P + t));
+      PROF_T(c5);
+      PROF_ADD(0, c0, c1); PROF_ADD(1, c1, c2); PROF_ADD(2, c2, c3); PROF_ADD(3, c3, c4); PROF_ADD(4, c4, c5);
+      PROF_ADD(5, c0, c0 + 1);
     }
     ok = ok && !*abort_flag;
     if (ok && my_nv > 0) ok = warp_wait(B_(G_O + t), (uint32_t)(my_nv - 1) & 1u, abort_flag, KID_ATTN, 30);
@@ -751,6 +767,14 @@ struct NpAttnFwdArgs {
   const void* push_k; const void* push_v; long long push_bytes; void* const* push_dst; int* const* push_flag;
   int push_n; int* push_ctr;
 };
+
+#ifdef NP_ATTN_PROF
+NP_API int np_attn_prof_read(unsigned long long* out8, int reset) {
+  cudaMemcpyFromSymbol(out8, g_fwd2_prof, sizeof(unsigned long long) * 8);
+  if (reset) { unsigned long long z[8] = {0}; cudaMemcpyToSymbol(g_fwd2_prof, z, sizeof(z)); }
+  return 0;
+}
+#endif
 
 NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
   if (a->B <= 0 || a->Sq <= 0 || a->src_len <= 0) return 0;
