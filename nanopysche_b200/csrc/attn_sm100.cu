@@ -155,6 +155,28 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x on the FMA pipe (degree-4 polynomial on the fraction, exponent patched in with integer adds; relative error
+// about 4e-5, 0 below 2^-125): used for a share of the scores so that the special-function unit is not the only
+// pipe the exp2 phase runs on
+__device__ __forceinline__ float ex2_poly(float x) {
+  const bool tiny = x < -125.f;              // masked scores (-inf) must give exactly 0
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;            // 1.5 * 2^23: the integer part lands in the low mantissa bits
+  const float f = x - (t - 12582912.f);      // [-0.5, 0.5]
+  float p = fmaf(f, 0.0096181291f, 0.0555041087f);
+  p = fmaf(p, f, 0.2402265070f);
+  p = fmaf(p, f, 0.6931471806f);
+  p = fmaf(p, f, 1.0f);
+  return tiny ? 0.f : __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+#ifndef NP_FWD2_POLY
+#define NP_FWD2_POLY 0   // 1: every fourth score of the two-Q-tile forward goes through ex2_poly (measured: 1.4x slower)
+#endif
 // mbarrier wait whose outcome is the same for every lane of the warp, so that the .sync.aligned tensor-memory
 // instructions that follow are never reached by part of a warp
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int kid, int where) {
@@ -611,7 +633,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int e = 0; e < 128; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(s[e]));
+      for (int e = 0; e < 128; e += 8) {      // three-input maxima: 64 instructions for the 128 scores
+        mx4[0] = fmax3(mx4[0], __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
+        mx4[1] = fmax3(mx4[1], __uint_as_float(s[e + 2]), __uint_as_float(s[e + 3]));
+        mx4[2] = fmax3(mx4[2], __uint_as_float(s[e + 4]), __uint_as_float(s[e + 5]));
+        mx4[3] = fmax3(mx4[3], __uint_as_float(s[e + 6]), __uint_as_float(s[e + 7]));
+      }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       const bool grow = mx > m + RESCALE_LOG2 || (m == -INFINITY && mx > -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
@@ -641,8 +668,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(s[c * 32 + e]), p.scale_log2, -m_use));
-          const float p1 = ex2(fmaf(__uint_as_float(s[c * 32 + e + 1]), p.scale_log2, -m_use));
+          const float x0 = fmaf(__uint_as_float(s[c * 32 + e]), p.scale_log2, -m_use);
+          const float x1 = fmaf(__uint_as_float(s[c * 32 + e + 1]), p.scale_log2, -m_use);
+          const float p0 = ex2(x0);
+          const float p1 = (NP_FWD2_POLY && (e & 2)) ? ex2_poly(x1) : ex2(x1);
           rs[e & 2] += p0;
           rs[(e & 2) + 1] += p1;
           pk[e >> 1] = np::pack_bf16(p0, p1);
