@@ -343,3 +343,16 @@ def _fsdp_worker(rank, world):
 
 def test_fsdp_matches_unsharded_loss():
     assert all(run_distributed(_fsdp_worker, 2))
+
+
+def test_nvls_allocation_is_opt_in(monkeypatch):
+    """The multicast (NVLS) arenas are only asked for with NPB200_NVLS=1; otherwise the data-parallel step keeps the
+    peer-load kernels and nothing is allocated."""
+    import torch
+
+    from nanopysche_b200.parallel.symm import nvls_alloc
+
+    monkeypatch.delenv("NPB200_NVLS", raising=False)
+    assert nvls_alloc(1024, torch.float32, object(), torch.device("cpu")) is None
+    monkeypatch.setenv("NPB200_NVLS", "1")
+    assert nvls_alloc(1024, torch.float32, None, torch.device("cpu")) is None   # no group: nothing to share with
