@@ -1106,6 +1106,42 @@ NP_API int np_sumsq(const float* x, long long n, float* partial, void* stream) {
   sumsq_kernel<<<np_sumsq_parts(), NT, 0, (cudaStream_t)stream>>>(x, n, partial);
   CHECK_LAUNCH();
 }
+// Embedding backward straight into the fp32 gradient arena: grad[ids[t], :] += dy[t, :]. One thread per four
+// columns of a token row, one 16-byte vector reduction each; rows of ids outside [0, V) are skipped.
+namespace {
+__global__ void __launch_bounds__(256) embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                            const long long* __restrict__ ids, float* __restrict__ grad,
+                                                            long long T, int D, long long V) {
+  const int vec_per_row = D >> 2;
+  const long long total = T * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vec_per_row;
+    const int d = (int)(i - t * vec_per_row) * 4;
+    const long long row = ids[t];
+    if (row < 0 || row >= V) continue;
+    const uint2 u = *reinterpret_cast<const uint2*>(dy + t * D + d);
+    const float2 a = np::unpack_bf16(u.x), b = np::unpack_bf16(u.y);
+    atomicAdd(reinterpret_cast<float4*>(grad + row * D + d), make_float4(a.x, a.y, b.x, b.y));
+  }
+}
+}  // namespace
+
+NP_API int np_embedding_bwd(const void* dy, const long long* ids, float* grad, long long T, int D, long long V,
+                            int zero_first, void* stream) {
+  if (T <= 0) return 0;
+  if (D % 4 || (((uintptr_t)dy) & 7) || (((uintptr_t)grad) & 15)) return 1;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (zero_first) {
+    cudaError_t e = cudaMemsetAsync(grad, 0, (size_t)V * D * sizeof(float), s);
+    if (e != cudaSuccess) return 400 + (int)e;
+  }
+  long long blocks = (T * (D / 4) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  embedding_bwd_kernel<<<(int)blocks, 256, 0, s>>>((const __nv_bfloat16*)dy, ids, grad, T, D, V);
+  CHECK_LAUNCH();
+}
+
 NP_API int np_clip_coef(const float* partial, int parts, const float* extra_sq, float max_norm, float* out2,
                         void* stream) {
   clip_coef_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(partial, parts, extra_sq, max_norm, out2);

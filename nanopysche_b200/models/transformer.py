@@ -19,6 +19,7 @@ from typing import Dict, Optional
 import torch
 import torch.nn as nn
 
+from ..ops import embedding as embedding_ops
 from ..ops import gemm as gemm_ops
 from ..ops import xent as xent_ops
 from .attention import Attention
@@ -188,7 +189,12 @@ class Transformer(nn.Module):
                 labels_shifted: bool = False, return_logits: bool = True, **kwargs):
         """Returns ``{"logits", "loss", "aux_loss"}`` (a stage without a head returns hidden states)."""
         if self.embeddings is not None and not input_ids.is_floating_point():
-            x = self.embeddings(input_ids)
+            emb = self.embeddings
+            if type(emb) is nn.Embedding and emb.padding_idx is None and emb.max_norm is None and \
+                    not self._fsdp_enabled and hasattr(emb.weight, "main_grad"):
+                x = embedding_ops.embedding(input_ids, emb.weight)   # backward adds into the gradient arena
+            else:
+                x = emb(input_ids)
             if self.embedding_norm is not None:
                 x = self.embedding_norm(x)
         else:

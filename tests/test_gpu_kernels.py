@@ -352,6 +352,31 @@ def test_mxfp8_gemm_grouped_and_linear():
     assert rel(y, yr) < 0.06 and rel(xl.grad, xf.grad) < 1e-2 and rel(wl.grad, wf.grad) < 1e-2
 
 
+def test_embedding_backward_into_the_gradient_arena():
+    """grad[ids[t]] += dy[t] by vector reductions into an fp32 ``main_grad``: overwrite on the first use of a step,
+    accumulate afterwards (tied weights); fp32 index_add as the oracle."""
+    from nanopysche_b200.ops.embedding import embedding
+
+    torch.manual_seed(19)
+    V, D = 1000, 512
+    w = torch.randn(V, D, device="cuda").bfloat16().requires_grad_()
+    w.main_grad = torch.full((V, D), 7.0, device="cuda")          # stale values that the first use must overwrite
+    w._main_grad_dirty = False
+    ids = torch.randint(0, V, (3, 700), device="cuda")
+    ids[0, :50] = 5                                                # many tokens on one row
+    y = embedding(ids, w)
+    assert torch.equal(y, w.detach()[ids])
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref = torch.zeros(V, D, device="cuda").index_add_(0, ids.reshape(-1), g.float().reshape(-1, D))
+    assert w.grad is None and w._main_grad_dirty and rel(w.main_grad, ref) < 1e-5
+    embedding(ids, w).backward(g)                                  # second use in the same step accumulates
+    assert rel(w.main_grad, 2 * ref) < 1e-5
+    w2 = w.detach().clone().requires_grad_()                       # no arena: dense gradient through autograd
+    embedding(ids, w2).backward(g)
+    assert rel(w2.grad, ref) < 1e-2
+
+
 @pytest.mark.parametrize("rows,D,with_res", [(300, 256, False), (4096, 2048, True), (77, 4096, True)])
 def test_rmsnorm_with_fp8_output(rows, D, with_res):
     """RMSNorm (+ residual) writing e4m3 + 1x128 scales: equal, bit for bit, to quantising the plain kernel's output."""
