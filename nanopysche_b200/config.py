@@ -5,7 +5,8 @@
 ``ExperimentConfig.build()`` assemble model, optimizer, scheduler and the runtime training config.
 ``TrainingConfig.build`` forwards the schedule fields and ``log_interval`` that the reference drops,
 and ``TransformerConfig`` can place MoE layers (``moe_interval`` / ``moe_offset`` / expert hidden
-size / capacity factor) and use GQA, which the BASELINE-style 1B / 7B configurations need.
+size / capacity factor / DeepSeek-V3 bias rate / shared expert / jitter) and use GQA, which the 1B
+and 7B mixture-of-experts configurations (GQA trunks, MoE in every or every other layer) need.
 """
 from __future__ import annotations
 
@@ -170,6 +171,10 @@ class TransformerConfig(Config):
     moe_hidden: Optional[int] = None
     moe_capacity_factor: Optional[float] = None
     moe_keep_dense_ffn: bool = False
+    moe_bias_gamma: Optional[float] = None      # DeepSeek-V3 auxiliary-loss-free balancing: bias update rate
+    moe_shared_expert: bool = False
+    moe_jitter_eps: Optional[float] = None
+    moe_z_loss: Optional[float] = None
     rope_scaling_factor: float = 1.0
     rope_scaling_type: str = "piecewise"
     dtype: str = "float32"
@@ -202,7 +207,9 @@ class TransformerConfig(Config):
                            hidden=self.moe_hidden or ffn, interval=self.moe_interval, offset=self.moe_offset,
                            capacity_factor=self.moe_capacity_factor, keep_dense_ffn=self.moe_keep_dense_ffn,
                            fp8_flow_moe=self.fp8_flow_moe, fp8_recipe=self.fp8_recipe,
-                           fp8_gemm_threshold=self.fp8_gemm_threshold, dtype=dtype)
+                           fp8_gemm_threshold=self.fp8_gemm_threshold, dtype=dtype,
+                           bias_gamma=self.moe_bias_gamma, shared_expert=self.moe_shared_expert,
+                           jitter_eps=self.moe_jitter_eps, z_loss_multiplier=self.moe_z_loss)
         if self.init_std is not None:
             model.init_weights(std=self.init_std)
         return model

@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(const uint4* __rest
                                                              long long vecs, long long dst_off_vecs, PeerPtrs flags,
                                                              int* __restrict__ ctr, int my_rank, int n, int epoch,
                                                              const int* epoch_base) {
+  np::CommSpan span(n > 1);
   const int ep = epoch + (epoch_base ? *epoch_base : 0);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < vecs;
        i += (long long)gridDim.x * blockDim.x) {
@@ -116,6 +117,7 @@ __global__ void __launch_bounds__(256) a2a_push_kernel(const uint4* __restrict__
                                                        long long row_vecs, PeerPtrs dst, PeerPtrs flags,
                                                        int* __restrict__ ctr, int my_rank, int n, int epoch,
                                                        const int* epoch_base, int set_flag) {
+  np::CommSpan span(n > 1);
   const long long slice_vecs = row_vecs / n;
   const long long total = rows * row_vecs;
   const long long base = (long long)my_rank * rows * slice_vecs;
@@ -143,6 +145,7 @@ __global__ void __launch_bounds__(256) a2a_push_kernel(const uint4* __restrict__
 // reduction half of a reduce-scatter whose partial results were written locally by each rank's GEMM.
 __global__ void __launch_bounds__(256) rs_reduce_bf16_kernel(PeerPtrs src, int n, long long off_vecs, long long vecs,
                                                              uint4* __restrict__ out) {
+  np::CommSpan span(n > 1);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < vecs;
        i += (long long)gridDim.x * blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -161,6 +164,7 @@ __global__ void __launch_bounds__(256) zero_reduce_kernel(PeerPtrs grads, int n,
                                                           float scale, float* __restrict__ gshard,
                                                           float* __restrict__ partial) {
   __shared__ float red[32];
+  np::CommSpan span(n > 1);
   float ss = 0.f;
   const long long nvec = cnt >> 2;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
@@ -192,6 +196,7 @@ __global__ void __launch_bounds__(256) zero_adamw_bcast_kernel(float* __restrict
                                                                float lr, float b1, float b2, float eps, float wd,
                                                                float bc1, float bc2, const float* __restrict__ gscale,
                                                                const float* __restrict__ hyper) {
+  np::CommSpan span(n > 1);
   const float gs = gscale ? gscale[0] : 1.f;
   if (hyper) { lr = hyper[0]; bc1 = hyper[1]; bc2 = hyper[2]; }
   const long long nvec = cnt >> 2;
@@ -237,6 +242,7 @@ __global__ void __launch_bounds__(256) zero_reduce_mc_kernel(const float* __rest
                                                              long long cnt, float scale, float* __restrict__ gshard,
                                                              float* __restrict__ partial) {
   __shared__ float red[32];
+  np::CommSpan span(true);
   float ss = 0.f;
   const long long nvec = cnt >> 2;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
@@ -264,6 +270,7 @@ __global__ void __launch_bounds__(256) zero_adamw_bcast_mc_kernel(float* __restr
                                                                   float wd, float bc1, float bc2,
                                                                   const float* __restrict__ gscale,
                                                                   const float* __restrict__ hyper) {
+  np::CommSpan span(true);
   const float gs = gscale ? gscale[0] : 1.f;
   if (hyper) { lr = hyper[0]; bc1 = hyper[1]; bc2 = hyper[2]; }
   const long long nvec = cnt >> 2;

@@ -27,6 +27,14 @@ enum NpStatus : int {
 // One per library instance; kernels only ever write a non-zero code (first writer wins).
 extern __device__ int g_np_status[8];
 
+// Communication-time accounting, per SM: the total length of the union of the intervals during which a thread
+// on that SM was polling a flag that had not been raised yet, or a CTA of a kernel that only moves data between
+// GPUs was running. The host reads the mean over the SMs per step as "exposed communication time": SM time that
+// no tensor-core or elementwise work could use. Two arrays of NP_MAX_SMS entries (np_wait_stats_read).
+#define NP_MAX_SMS 192
+extern __device__ unsigned long long g_np_wait_end[NP_MAX_SMS];  // end (globaltimer) of the last counted interval
+extern __device__ unsigned long long g_np_wait_ns[NP_MAX_SMS];   // accumulated union length in ns
+
 #ifndef NP_WAIT_LIMIT_NS
 #define NP_WAIT_LIMIT_NS 2000000000ull  // 2 s
 #endif
@@ -38,6 +46,28 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+
+// Add [t0, t1) to this SM's communication time, counting only the part not already covered by an earlier
+// interval (several CTAs of one SM usually wait at the same time).
+__device__ __forceinline__ void account_interval(uint64_t t0, uint64_t t1) {
+  unsigned sm;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+  if (sm >= NP_MAX_SMS || t1 <= t0) return;
+  const unsigned long long old = atomicMax(&g_np_wait_end[sm], (unsigned long long)t1);
+  const unsigned long long from = old > t0 ? old : (unsigned long long)t0;
+  if (t1 > from) atomicAdd(&g_np_wait_ns[sm], (unsigned long long)t1 - from);
+}
+// Counts the lifetime of thread 0 of a CTA as communication time (kernels whose only job is a transfer).
+struct CommSpan {
+  uint64_t t0;
+  bool on;
+  __device__ __forceinline__ explicit CommSpan(bool enable) : t0(0), on(enable && threadIdx.x == 0) {
+    if (on) t0 = globaltimer_ns();
+  }
+  __device__ __forceinline__ ~CommSpan() {
+    if (on) account_interval(t0, globaltimer_ns());
+  }
+};
 
 __device__ __forceinline__ void report(int code, int kernel_id, int detail) {
   if (atomicCAS(&g_np_status[0], 0, code) == 0) {
@@ -124,7 +154,10 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int want, uint64_t
   if (ld_acquire_sys(flag) >= want) return true;
   uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
-    if (ld_acquire_sys(flag) >= want) return true;
+    if (ld_acquire_sys(flag) >= want) {
+      account_interval(t0, globaltimer_ns());
+      return true;
+    }
     if ((it & 63u) == 0u) {
       if (globaltimer_ns() - t0 > limit_ns) {
         report(NP_ERR_FLAG_TIMEOUT, kernel_id, detail);

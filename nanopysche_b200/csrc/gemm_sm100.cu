@@ -16,6 +16,8 @@
 #include "common.cuh"
 
 __device__ int g_np_status[8];
+__device__ unsigned long long g_np_wait_end[NP_MAX_SMS];
+__device__ unsigned long long g_np_wait_ns[NP_MAX_SMS];
 
 namespace {
 
@@ -691,6 +693,18 @@ NP_API int np_gemm_bf16(const NpGemmArgs* args, void* stream) {
 NP_API int np_status_read(int* out8) {
   return (int)cudaMemcpyFromSymbol(out8, g_np_status, sizeof(int) * 8);
 }
+// Per-SM communication time in ns accumulated since the last reset (see account_interval): copies NP_MAX_SMS
+// values into `out_ns` and, when `reset` is set, zeroes the counters. Synchronises the device.
+NP_API int np_wait_stats_read(unsigned long long* out_ns, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out_ns, g_np_wait_ns, sizeof(unsigned long long) * NP_MAX_SMS);
+  if (e != cudaSuccess) return (int)e;
+  if (reset) {
+    static const unsigned long long z[NP_MAX_SMS] = {0};
+    e = cudaMemcpyToSymbol(g_np_wait_ns, z, sizeof(z));
+  }
+  return (int)e;
+}
+NP_API int np_wait_stats_slots() { return NP_MAX_SMS; }
 NP_API int np_status_clear() {
   int z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   return (int)cudaMemcpyToSymbol(g_np_status, z, sizeof(z));

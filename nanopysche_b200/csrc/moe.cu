@@ -569,6 +569,7 @@ struct DispatchParams {
 };
 
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(const DispatchParams p) {
+  np::CommSpan span(p.n_ranks > 1);
   const int lane = threadIdx.x & 31;
   const int warp_g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;

@@ -43,6 +43,8 @@ def prepare_training(model: nn.Module, *, tokens_per_rank: Optional[int] = None,
     opt = ArenaAdamW(arena, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, max_grad_norm=max_grad_norm)
     rt = getattr(moes[0], "_fused_runtime", None) if moes else None
     if rt is not None:
+        if rt.score_bias_all is not None:
+            opt.post_step_hooks.append(rt.update_router_bias)
         opt.post_step_hooks.append(rt.end_step)
     opt.post_step_hooks.append(_cp_end_step)
     if any(m._fp8_flow_moe is not None for m in moes):

@@ -18,6 +18,7 @@ from typing import Optional, Tuple
 import torch
 import torch.nn as nn
 
+from ..ops import _lib
 from ..ops import attention as attn_ops
 from ..ops import gemm as gemm_ops
 from ..ops import rope as rope_ops
@@ -62,7 +63,7 @@ class Attention(nn.Module):
         B, S, _ = x.shape
         hq, hkv, hd = self._local_heads, self._local_kv_heads, self.head_dim
         fused = self._fused_qkv
-        if fused is not None and x.is_cuda and x.dtype == fused.dtype and self.w_q.bias is None:
+        if fused is not None and _lib.on(x) and x.dtype == fused.dtype and self.w_q.bias is None:
             qkv = gemm_ops.linear(x, fused)  # [B, S, (hq + 2 hkv) * hd]
             q = qkv[..., : hq * hd].unflatten(-1, (hq, hd))
             k = qkv[..., hq * hd:(hq + hkv) * hd].unflatten(-1, (hkv, hd))
@@ -80,7 +81,7 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, *, causal: bool = True, attn_mask: Optional[torch.Tensor] = None,
                 kv_cache: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, start_pos: int = 0,
                 position_ids: Optional[torch.Tensor] = None, return_kv: bool = False, **_):
-        rt = self._tp_rt if (self._tp_rt is not None and x.is_cuda and x.dtype == torch.bfloat16) else None
+        rt = self._tp_rt if (self._tp_rt is not None and _lib.on(x) and x.dtype == torch.bfloat16) else None
         hq, hkv, hd = self._local_heads, self._local_kv_heads, self.head_dim
         qkv = None  # fused projection output [B, S, (hq + 2 hkv) * hd] when one GEMM produced all three
         if rt is not None:
@@ -95,7 +96,7 @@ class Attention(nn.Module):
             B, S, _ = x.shape
             x = copy_to_tp_region(x, self._tp_group, self._tp_size)
             fused = self._fused_qkv
-            if fused is not None and x.is_cuda and x.dtype == fused.dtype and self.w_q.bias is None:
+            if fused is not None and _lib.on(x) and x.dtype == fused.dtype and self.w_q.bias is None:
                 qkv = gemm_ops.linear(x, fused)
         if position_ids is None and self._cp_module is not None:
             position_ids = self._cp_module.local_positions(S, x.device)

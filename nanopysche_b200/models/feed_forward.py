@@ -14,6 +14,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops import _lib
 from ..ops import activation as act_ops
 from ..ops import gemm as gemm_ops
 from .tp_utils import copy_to_tp_region, differentiable_all_reduce
@@ -44,7 +45,7 @@ class FeedForward(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         act = self.activation.value
-        if self._tp_rt is not None and x.is_cuda and x.dtype == torch.bfloat16 and self.w1.bias is None:
+        if self._tp_rt is not None and _lib.on(x) and x.dtype == torch.bfloat16 and self.w1.bias is None:
             from ..ops import tp_fused
 
             rt = self._tp_rt
@@ -53,9 +54,9 @@ class FeedForward(nn.Module):
             return tp_fused.linear_rs(h, self.w2.weight, rt).view(*x.shape[:-1], -1)
         x = copy_to_tp_region(x, self._tp_group, self._tp_size)
         fused = self._fused_w13
-        if fused is not None and x.is_cuda and x.dtype == fused.dtype and self.w1.bias is None:
+        if fused is not None and _lib.on(x) and x.dtype == fused.dtype and self.w1.bias is None:
             h = act_ops.glu(gemm_ops.linear(x, fused), act)
-        elif x.is_cuda and x.dtype == torch.bfloat16 and self.w1.bias is None:
+        elif _lib.on(x) and x.dtype == torch.bfloat16 and self.w1.bias is None:
             gu = torch.cat([gemm_ops.linear(x, self.w1.weight), gemm_ops.linear(x, self.w3.weight)], dim=-1)
             h = act_ops.glu(gu, act)
         else:

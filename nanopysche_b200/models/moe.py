@@ -27,6 +27,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops import _lib
 from .ep_runtime import AdaptiveSMAllocator, CoupledEPScheduler, EPScheduleDecision, RoutingPrefetcher  # noqa: F401
 
 
@@ -126,7 +127,7 @@ class MoERouter(nn.Module):
         if cfg.jitter_eps is not None and self.training:
             x = x + torch.randn_like(x) * cfg.jitter_eps
         replay = self.routing_replay and self._replay_mask is not None and self.training
-        if x.is_cuda and x.dtype == torch.bfloat16 and not replay and cfg.normalize_expert_weights is None:
+        if _lib.on(x) and x.dtype == torch.bfloat16 and not replay and cfg.normalize_expert_weights is None:
             from ..ops import moe as moe_ops
 
             w, idx, aux, counts = moe_ops.route(x, self)
@@ -160,8 +161,8 @@ class MoERouter(nn.Module):
     @torch.no_grad()
     def post_batch(self, group=None) -> None:
         """DeepSeek-V3 bias update, once per step: ``bias += sign * gamma * (load_fraction - 1/E)``."""
-        if self.score_bias is None:
-            return
+        if self.score_bias is None or getattr(self, "_device_side_update", False):
+            return  # no bias, or the fused runtime updates all layers on the device (ops.moe.update_router_bias)
         if dist.is_available() and dist.is_initialized():
             packed = torch.cat([self._tokens_per_expert_this_batch, self._total_tokens_this_batch.reshape(1)])
             dist.all_reduce(packed, group=group)
@@ -523,8 +524,18 @@ class MoEBase(nn.Module):
         if f is not None and self.fp8_recipe == "mxfp8" and rt is not None and \
                 f.use_fp8(x.numel() // x.shape[-1] * self.top_k / max(self.num_experts, 1)):
             return False  # the MXFP8 expert GEMMs live in the modular path (FP8FlowMoECompute)
-        return (rt is not None and x.is_cuda and x.dtype == torch.bfloat16 and self.w1.dtype == torch.bfloat16
-                and self.shared_expert is None and self.router.config.normalize_expert_weights is None
+        if rt is not None and self.adaptive_capacity:
+            # the symmetric receive regions are sized for one capacity; a capacity factor that moves needs the
+            # modular path (say so once instead of silently running the slow path)
+            if not getattr(self, "_warned_adaptive", False):
+                import warnings
+
+                warnings.warn("MoEBase: adaptive_capacity is on, the fused expert-parallel kernels are bypassed "
+                              "(their receive buffers are sized for a fixed capacity factor)")
+                self._warned_adaptive = True
+            return False
+        return (rt is not None and _lib.on(x) and x.dtype == torch.bfloat16 and self.w1.dtype == torch.bfloat16
+                and self.router.config.normalize_expert_weights is None
                 and not (self.router.routing_replay and self.router._replay_mask is not None))
 
     # -- parallel / fp8 hooks -------------------------------------------------------------------------

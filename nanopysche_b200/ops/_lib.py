@@ -198,6 +198,21 @@ def available() -> bool:
     return torch.cuda.is_available()
 
 
+PLAIN = False  # True: every op takes its PyTorch statement even on CUDA tensors (the plain library-call arm)
+
+
+def set_plain(flag: bool) -> None:
+    """Route all ops to their PyTorch reference (cuBLAS / SDPA / ATen) regardless of device. Used by the plain
+    baseline arm of the benchmarks, which runs the same model through library calls and NCCL collectives."""
+    global PLAIN
+    PLAIN = bool(flag)
+
+
+def on(t: torch.Tensor) -> bool:
+    """True when ``t`` should go through the sm_100a kernels."""
+    return t.is_cuda and not PLAIN
+
+
 def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -230,6 +245,21 @@ def check_status(where: str = "") -> None:
         raise KernelError(
             f"device status {st[0]} ({STATUS_NAMES.get(st[0], '?')}) kernel={st[1]} block={st[2]} "
             f"detail={st[3]} {where}")
+
+
+def wait_stats(reset: bool = False) -> dict | None:
+    """Communication time the kernels accounted since the last reset: ``exposed_ms`` is the mean over the SMs of
+    the time an SM spent polling a flag a peer had not raised yet or running a transfer-only kernel (dispatch
+    pushes, gradient reduce-scatter loads, weight all-gather stores, barriers). Synchronises the device."""
+    if not torch.cuda.is_available():
+        return None
+    n = lib().np_wait_stats_slots()
+    buf = (c_ull * n)()
+    if lib().np_wait_stats_read(buf, int(reset)) != 0:
+        return None
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    vals = list(buf)[:min(sms, n)]
+    return {"exposed_ms": sum(vals) / max(len(vals), 1) / 1e6, "max_sm_ms": max(vals) / 1e6 if vals else 0.0}
 
 
 def call(name: str, *args) -> None:

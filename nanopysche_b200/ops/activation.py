@@ -45,7 +45,7 @@ class _GLU(torch.autograd.Function):
 
 def glu_bwd(gu: torch.Tensor, dh: torch.Tensor, act: str = "silu") -> torch.Tensor:
     """Gradient of ``glu`` w.r.t. the ``[gate | up]`` buffer (used by the fused GEMM+SwiGLU path)."""
-    if gu.is_cuda and gu.dtype == torch.bfloat16:
+    if _lib.on(gu) and gu.dtype == torch.bfloat16:
         Fh = gu.shape[-1] // 2
         gu2, dh2 = gu.reshape(-1, 2 * Fh), dh.reshape(-1, Fh).contiguous()
         dgu = torch.empty_like(gu2)
@@ -61,6 +61,6 @@ def glu_bwd(gu: torch.Tensor, dh: torch.Tensor, act: str = "silu") -> torch.Tens
 
 def glu(gu: torch.Tensor, act: str = "silu") -> torch.Tensor:
     """``act(gate) * up`` for ``gu = [gate | up]`` along the last dim."""
-    if gu.is_cuda and gu.dtype == torch.bfloat16 and (gu.shape[-1] // 2) % 8 == 0:
+    if _lib.on(gu) and gu.dtype == torch.bfloat16 and (gu.shape[-1] // 2) % 8 == 0:
         return _GLU.apply(gu, ACT_IDS[act])
     return glu_ref(gu, act)

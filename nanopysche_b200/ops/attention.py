@@ -100,7 +100,7 @@ def _set_flags(a, flags, keep: list):
 
 def flash_supported(q: torch.Tensor, k: torch.Tensor) -> bool:
     """The tcgen05 kernels cover bf16, head_dim 128, 16-byte aligned strided ``[B, S, H, 128]`` views."""
-    return (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and q.shape[-1] == 128
+    return (_lib.on(q) and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and q.shape[-1] == 128
             and k.shape[-1] == 128 and q.stride(-1) == 1 and k.stride(-1) == 1 and _lib.available()
             and all(s % 8 == 0 for s in q.stride()[:3]) and all(s % 8 == 0 for s in k.stride()[:3]))
 

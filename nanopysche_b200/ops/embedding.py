@@ -29,7 +29,7 @@ class _Embedding(torch.autograd.Function):
         D = w.shape[1]
         dy2 = dy.reshape(-1, D)
         mg = getattr(w, "main_grad", None)
-        if mg is not None and dy2.is_cuda and dy2.dtype == torch.bfloat16 and mg.dtype == torch.float32 and D % 4 == 0 \
+        if mg is not None and _lib.on(dy2) and dy2.dtype == torch.bfloat16 and mg.dtype == torch.float32 and D % 4 == 0 \
                 and ids.dtype == torch.int64:
             dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
             flat = ids.reshape(-1)

@@ -20,7 +20,7 @@ from . import _lib
 
 
 def _use_kernel(t: torch.Tensor) -> bool:
-    return t.is_cuda
+    return _lib.on(t)
 
 
 def gemm_ref(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, accumulate=False, alpha=1.0):
@@ -181,7 +181,7 @@ class _LinearBias(torch.autograd.Function):
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ w.T (+ bias)``; tcgen05 kernels for bf16 CUDA tensors, ``F.linear`` otherwise."""
-    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+    if _lib.on(x) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         rt = getattr(w, "_fsdp_rt", None)
         if rt is not None:  # row-sharded weight: all-gather inside the GEMM, reduce-scattered weight gradient
             from .fsdp_fused import sharded_linear

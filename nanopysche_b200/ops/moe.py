@@ -160,6 +160,12 @@ class FusedMoERuntime:
         self.dispatch_ctr = torch.zeros(1, device=self.device, dtype=torch.int32)
         self.layer_of: dict[int, int] = {}
         self.max_ctas_dispatch = max_ctas_dispatch
+        # DeepSeek-V3 auxiliary-loss-free balancing, kept on the device: per-layer assignment counts of the step and
+        # one [layers, experts] tensor that every router's ``score_bias`` is a row of (``bind_router_bias``)
+        h.reserve_allreduce(max(64, n_layers * num_experts))
+        self.bias_counts = torch.zeros((n_layers, num_experts), device=self.device, dtype=torch.float32)
+        self.score_bias_all: Optional[torch.Tensor] = None
+        self.bias_coef = 0.0
         if self.N > 1:
             torch.cuda.synchronize()
             dist.barrier(group=group)
@@ -173,6 +179,31 @@ class FusedMoERuntime:
 
     def next_epoch(self) -> int:
         return self.heap.next_epoch()
+
+    def bind_router_bias(self, moe_modules):
+        """Make the routers' ``score_bias`` buffers rows of one tensor so that the per-step update of all layers
+        (reference: model/moe.py:293-321, there a host-side loop with two world all-reduces per layer that nothing
+        calls) is a handful of small launches with no host synchronisation, capturable in the step's graph."""
+        cfg = moe_modules[0].router.config
+        self.score_bias_all = torch.zeros((self.L, self.E), device=self.device, dtype=torch.float32)
+        self.bias_coef = float(cfg.bias_update_sign) * float(cfg.bias_gamma)
+        for m in moe_modules:
+            row = self.score_bias_all[self.layer_index(m)]
+            row.copy_(m.router.score_bias)
+            m.router.score_bias = row
+            m.router._device_side_update = True
+
+    def update_router_bias(self):
+        """``bias += sign * gamma * (load fraction - 1/E)`` for every layer from this step's counts, summed over the
+        expert-parallel ranks through peer memory. Runs once per optimizer step, before ``end_step``."""
+        if self.score_bias_all is None:
+            return
+        c = self.bias_counts
+        if self.N > 1:
+            self.heap.all_reduce_(c.view(-1))
+        tot = c.sum(dim=1, keepdim=True).clamp_min_(1.0)
+        self.score_bias_all.add_((c / tot).sub_(1.0 / self.E), alpha=self.bias_coef)
+        c.zero_()
 
     def end_step(self):
         self.heap.end_step()
@@ -287,7 +318,7 @@ class FusedMoERuntime:
 # ------------------------------------------------------------------------------------------------ the layer
 class _FusedMoE(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weights, indices32, w1, w3, w2, rt: FusedMoERuntime, layer: int, stats_mod):
+    def forward(ctx, x, weights, indices32, w1, w3, w2, rt: FusedMoERuntime, layer: int, stats_mod, shared=None):
         T, D, K, H = rt.T, rt.D, rt.K, rt.H
         dev = x.device
         x2 = x.reshape(T, D)
@@ -328,12 +359,18 @@ class _FusedMoE(torch.autograd.Function):
             rt.grouped_gemm(h, w2, N=D, K=H, b_mn=True, group_stride_b=H, push_ptrs=rt.p_ret_y[layer],
                             push_epoch=e1)
         out = torch.empty((T, D), device=dev, dtype=torch.bfloat16)
-        rt.combine(rt.ret_y[layer], slot_pos, weights, out, sent, e1)
+        add1 = None
+        if shared is not None:
+            # the shared expert's output joins in the combine pass; a token dropped by the capacity rule gets no
+            # MoE output at all, shared expert included (reference: model/moe.py:1383-1390)
+            add1 = shared.reshape(T, D) * keep.to(shared.dtype).unsqueeze(1)
+        rt.combine(rt.ret_y[layer], slot_pos, weights, out, sent, e1, add1=add1)
+        ctx.has_shared = shared is not None
         # the bf16 path keeps the activation h for the w2 weight gradient (57 MB per layer at the 1B shapes: cheap next
         # to re-reading the pre-activations); the fp8 path recomputes it from them
         ctx.has_h = not rt.fp8
         ctx.save_for_backward(x2, weights, indices32, slot_pos, counts_kept, sent, gu, w1, w3, w2,
-                              *([h] if ctx.has_h else []))
+                              *([h] if ctx.has_h else []), *([keep] if ctx.has_shared else []))
         ctx.rt, ctx.layer = rt, layer
         ctx.x_shape = x.shape
         if stats_mod is not None:
@@ -376,7 +413,11 @@ class _FusedMoE(torch.autograd.Function):
         rt.grouped_gemm(du, w3, N=D, K=H, b_mn=True, group_stride_b=H, push_ptrs=rt.p_ret_g, push_epoch=e2, Cin=part)
         dx = torch.empty((T, D), device=dev, dtype=torch.bfloat16)
         rt.combine(rt.ret_g, slot_pos, None, dx, sent, e2)
-        return dx.view(ctx.x_shape), dweights, None, dw1, dw3, dw2, None, None, None
+        dshared = None
+        if ctx.has_shared:
+            keep = ctx.saved_tensors[-1]
+            dshared = (do2 * keep.to(do2.dtype).unsqueeze(1)).view(ctx.x_shape)
+        return dx.view(ctx.x_shape), dweights, None, dw1, dw3, dw2, None, None, None, dshared
 
 
 def build_runtime(moe_modules, *, tokens: int, group=None, device=None) -> FusedMoERuntime:
@@ -394,6 +435,9 @@ def build_runtime(moe_modules, *, tokens: int, group=None, device=None) -> Fused
                          device=device, fp8=fp8)
     for m in moe_modules:
         m._fused_runtime = rt
+        rt.layer_index(m)
+    if m0.router.score_bias is not None:
+        rt.bind_router_bias(moe_modules)
     return rt
 
 
@@ -405,11 +449,19 @@ def fused_moe_forward(mod, x: torch.Tensor) -> torch.Tensor:
             rt.capacity:
         raise _lib.KernelError(f"fused MoE runtime was built for {rt.T} tokens / capacity {rt.capacity}; got "
                                f"{B * S} tokens (rebuild the runtime or call the layer with a matching batch)")
-    w, idx, aux, counts = route(x, mod.router)
+    cfg = mod.router.config
+    xr = x
+    if cfg.jitter_eps is not None and mod.training:   # routing noise, as in MoERouter.forward
+        xr = x + torch.randn_like(x) * cfg.jitter_eps
+    w, idx, aux, counts = route(xr, mod.router)
     mod.router.last_counts = counts
-    if mod.router.score_bias is not None:
-        mod.router._update_expert_counts(idx, counts)
-    mod._aux_loss = aux
     layer = rt.layer_index(mod)
+    if mod.router.score_bias is not None:
+        if rt.score_bias_all is not None:
+            rt.bias_counts[layer].add_(counts)
+        else:
+            mod.router._update_expert_counts(idx, counts)
+    mod._aux_loss = aux
+    shared = mod.shared_expert(x) if mod.shared_expert is not None else None
     return _FusedMoE.apply(x, w.reshape(B * S, -1), idx.reshape(B * S, -1).to(torch.int32), mod.w1, mod.w3, mod.w2, rt,
-                           layer, mod)
+                           layer, mod, shared)

@@ -20,7 +20,7 @@ def rms_norm_ref(x, weight, eps=1e-6, residual=None):
 
 
 def _kernel_ok(x, weight):
-    return x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.float32 and \
+    return _lib.on(x) and x.dtype == torch.bfloat16 and weight.dtype == torch.float32 and \
         x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192
 
 

@@ -113,7 +113,7 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos_offset
                pos_ids: torch.Tensor | None = None) -> torch.Tensor:
     """Rotate ``x [B, S, H, hd]`` (a possibly strided view with contiguous heads) by its positions."""
     B, S, H, hd = x.shape
-    ok = (x.is_cuda and x.dtype == torch.bfloat16 and hd % 8 == 0 and (2 * cos.shape[1]) % 16 == 0 and
+    ok = (_lib.on(x) and x.dtype == torch.bfloat16 and hd % 8 == 0 and (2 * cos.shape[1]) % 16 == 0 and
           x.stride(3) == 1 and x.stride(2) == hd and x.stride(1) % 8 == 0 and x.stride(0) == S * x.stride(1) and
           cos.dtype == torch.float32)
     if ok:
@@ -224,7 +224,7 @@ class _QKVNormRope(torch.autograd.Function):
 
 def qkv_norm_rope_supported(qkv: torch.Tensor, cos, hq: int, hkv: int, hd: int) -> bool:
     S = qkv.shape[1]
-    return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and hd == 128 and cos.shape[1] == 64 and
+    return (_lib.on(qkv) and qkv.dtype == torch.bfloat16 and hd == 128 and cos.shape[1] == 64 and
             cos.dtype == torch.float32 and qkv.stride(2) == 1 and qkv.stride(1) % 8 == 0 and
             qkv.stride(0) == S * qkv.stride(1) and (hq + hkv) * 8 <= 512 and (hq + hkv) * 8 + hkv * 16 <= 768)
 
@@ -242,7 +242,7 @@ def qkv_rope(qkv: torch.Tensor, cos, sin, hq: int, hkv: int, hd: int, pos_offset
     """``qkv [B, S, (hq+2*hkv)*hd]`` -> rotated ``q [B,S,hq,hd]``, ``k [B,S,hkv,hd]`` and ``v`` (strided views of
     one buffer). Falls back to slicing + ``apply_rope`` off the kernel path."""
     B, S, W = qkv.shape
-    ok = (qkv.is_cuda and qkv.dtype == torch.bfloat16 and hd % 8 == 0 and (2 * cos.shape[1]) % 16 == 0 and
+    ok = (_lib.on(qkv) and qkv.dtype == torch.bfloat16 and hd % 8 == 0 and (2 * cos.shape[1]) % 16 == 0 and
           qkv.stride(2) == 1 and qkv.stride(1) % 8 == 0 and qkv.stride(0) == S * qkv.stride(1) and
           cos.dtype == torch.float32)
     if ok:

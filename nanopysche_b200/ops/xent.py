@@ -38,6 +38,6 @@ class _Xent(torch.autograd.Function):
 
 def cross_entropy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
     """Mean token cross-entropy of ``logits [rows, V]`` against ``labels [rows]``."""
-    if logits.is_cuda and logits.dtype == torch.bfloat16 and logits.stride(1) == 1 and logits.stride(0) % 8 == 0:
+    if _lib.on(logits) and logits.dtype == torch.bfloat16 and logits.stride(1) == 1 and logits.stride(0) % 8 == 0:
         return _Xent.apply(logits, labels.contiguous().long(), ignore_index)
     return F.cross_entropy(logits.float(), labels.long(), ignore_index=ignore_index)

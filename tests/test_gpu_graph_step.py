@@ -1,0 +1,109 @@
+"""The whole-step CUDA graph (``engine.GraphedTrainStep``) against the same step launched eagerly and
+against the fp32 PyTorch path of the same model (``torch.optim.AdamW`` + ``clip_grad_norm_``), at the
+layer widths of the headline benchmark (GPU only).
+
+The step being checked is the reference's training step (train/trainer.py:251-339): forward, loss plus
+auxiliary loss, backward, gradient clipping at 1.0, AdamW, learning-rate schedule.
+"""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+STEPS = 12
+PRE = 2   # steps taken before the schedule starts (the graph's own eager warm-up); lr is 0 there
+
+
+def _config():
+    from nanopysche_b200.config import TransformerConfig
+
+    # two layers of the benchmark's shapes: d 2048, 16 query / 8 KV heads of 128, 8 experts x 2816, top-2, cf 1.25
+    return TransformerConfig(vocab_size=32000, d_model=2048, n_layers=2, n_heads=16, n_kv_heads=8, ffn_hidden=5632,
+                             rope_base=10000.0, max_seq_len=512, qk_norm=False, use_moe=True, num_experts=8,
+                             moe_top_k=2, moe_interval=1, moe_offset=0, moe_hidden=2816, moe_capacity_factor=1.25)
+
+
+def _build(seed=0):
+    torch.manual_seed(seed)
+    model = _config().build(dtype=torch.bfloat16, init_device="cuda")
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2:
+                p.normal_(0.0, 0.02)
+    return model
+
+
+def _schedule(opt):
+    from nanopysche_b200.train.scheduler import CosineWithWarmup
+
+    return CosineWithWarmup(opt, warmup_steps=3, max_steps=1000)
+
+
+def _run_fused(model, ids, graphed: bool):
+    from nanopysche_b200.engine import GraphedTrainStep, prepare_training
+    from nanopysche_b200.ops import _lib
+
+    opt, _ = prepare_training(model, tokens_per_rank=ids.numel(), lr=3e-4, weight_decay=0.1, max_grad_norm=1.0)
+    sched = _schedule(opt)
+    losses = []
+    if graphed:
+        g = GraphedTrainStep(model, opt, ids, warmup=PRE).capture()
+        for _ in range(STEPS):
+            losses.append(g.step(ids).item())
+            sched.step()
+    else:
+        for i in range(PRE + STEPS):
+            out = model(ids, labels=ids)
+            (out["loss"] + out["aux_loss"]).backward()
+            opt.step()
+            opt.zero_grad()
+            if i >= PRE:
+                sched.step()
+                losses.append(out["loss"].item())
+    torch.cuda.synchronize()
+    _lib.check_status("graph step test")
+    return losses
+
+
+def _run_torch_fp32(model, ids):
+    # the arena applies no weight decay to norms, biases and router gates: same grouping here
+    from nanopysche_b200.optim.adamw import is_no_decay
+
+    decay = [p for n, p in model.named_parameters() if not is_no_decay(n, p)]
+    no_decay = [p for n, p in model.named_parameters() if is_no_decay(n, p)]
+    opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": no_decay, "weight_decay": 0.0}],
+                            lr=3e-4, betas=(0.9, 0.95), eps=1e-8)
+    sched = _schedule(opt)
+    losses = []
+    for i in range(PRE + STEPS):
+        out = model(ids, labels=ids)
+        (out["loss"] + out["aux_loss"]).backward()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        opt.step()
+        opt.zero_grad()
+        if i >= PRE:
+            sched.step()
+            losses.append(out["loss"].item())
+    return losses
+
+
+def test_graphed_step_matches_eager_and_fp32_pytorch():
+    base = _build()
+    torch.manual_seed(1)
+    ids = torch.randint(0, 32000, (2, 512), device="cuda")
+    ref = copy.deepcopy(base).float()
+    eager_model = copy.deepcopy(base)
+    l_graph = _run_fused(base, ids, graphed=True)
+    l_eager = _run_fused(eager_model, ids, graphed=False)
+    l_ref = _run_torch_fp32(ref, ids)
+    print("graph ", [round(x, 4) for x in l_graph])
+    print("eager ", [round(x, 4) for x in l_eager])
+    print("fp32  ", [round(x, 4) for x in l_ref])
+    assert all(x == x and x < 20 for x in l_graph), l_graph
+    for a, b in zip(l_graph, l_eager):   # same kernels, same order: only atomics-order noise is allowed
+        assert abs(a - b) <= 2e-2 * abs(b), (l_graph, l_eager)
+    for a, b in zip(l_graph, l_ref):     # bf16 compute against fp32
+        assert abs(a - b) <= 3e-2 * abs(b), (l_graph, l_ref)
+    assert l_graph[0] < 10.6 and l_graph[-1] < l_graph[0] - 0.5, l_graph   # starts near ln(V), memorises the batch

@@ -21,18 +21,19 @@ def _status_clean():
     _lib.check_status("after test")
 
 
-@pytest.mark.parametrize("capacity", [1.25, None])
-def test_fused_moe_matches_generic_path(capacity):
+@pytest.mark.parametrize("capacity,shared", [(1.25, False), (None, False), (1.25, True)])
+def test_fused_moe_matches_generic_path(capacity, shared):
     from nanopysche_b200.models.moe import MoEBase
     from nanopysche_b200.ops.moe import build_runtime
 
     torch.manual_seed(0)
     B, S, D, H, E, K = 2, 256, 256, 256, 4, 2
     fused = MoEBase(d_model=D, hidden_size=H, num_experts=E, top_k=K, capacity_factor=capacity, dtype=torch.bfloat16,
-                    device="cuda", init_std=0.05)
+                    device="cuda", init_std=0.05, shared_expert=shared)
     fused.router.cuda()
     ref = copy.deepcopy(fused).float()
     build_runtime([fused], tokens=B * S, device=torch.device("cuda"))
+    assert fused._can_fuse(torch.empty(1, 1, D, device="cuda", dtype=torch.bfloat16))
     x = (torch.randn(B, S, D, device="cuda")).bfloat16()
     xa = x.clone().requires_grad_(True)
     y = fused(xa)
@@ -49,6 +50,8 @@ def test_fused_moe_matches_generic_path(capacity):
     for n in ("w1", "w2", "w3"):
         assert rel(getattr(fused, n).grad, getattr(ref, n).grad) < 3e-2, n
     assert rel(fused.router.gate.weight.grad, ref.router.gate.weight.grad) < 5e-2
+    if shared:
+        assert rel(fused.shared_expert.ffn.w2.weight.grad, ref.shared_expert.ffn.w2.weight.grad) < 3e-2
 
 
 def test_flagship_block_matches_fp32_reference_and_trains():
