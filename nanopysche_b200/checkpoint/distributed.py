@@ -59,23 +59,26 @@ class CheckpointMetadata:
 
 
 class PinnedMemoryStager:
-    """Device -> host staging through reusable pinned buffers (plain ``.cpu()`` without CUDA)."""
+    """Device -> host staging through pinned bounce buffers (plain ``.cpu()`` without CUDA).
+
+    Every tensor of a state dict gets a pinned buffer of its own, keyed by its (nested) name and reused by later
+    saves of the same model, so the asynchronous copies of one save never share a destination: tensors of equal
+    shape (every layer's ``w_q``) must not alias. ``pool_size`` bounds how many *different* shapes may reuse a
+    name's buffer before it is reallocated (a name whose shape changes gets a new buffer)."""
 
     def __init__(self, pool_size: int = 2, enabled: bool = True):
         self.enabled = enabled and torch.cuda.is_available()
         self.pool_size = pool_size
-        self._pool: Dict[tuple, List[torch.Tensor]] = {}
+        self._pool: Dict[str, torch.Tensor] = {}
 
-    def _buffer(self, t: torch.Tensor) -> torch.Tensor:
-        key = (tuple(t.shape), t.dtype)
-        bufs = self._pool.setdefault(key, [])
-        if len(bufs) < self.pool_size:
-            bufs.append(torch.empty(t.shape, dtype=t.dtype, pin_memory=True))
-        buf = bufs.pop(0)
-        bufs.append(buf)
+    def _buffer(self, name: str, t: torch.Tensor) -> torch.Tensor:
+        buf = self._pool.get(name)
+        if buf is None or buf.shape != t.shape or buf.dtype != t.dtype:
+            buf = torch.empty(t.shape, dtype=t.dtype, pin_memory=self.enabled)
+            self._pool[name] = buf
         return buf
 
-    def stage_state_dict(self, sd: Dict[str, Any]) -> Dict[str, Any]:
+    def stage_state_dict(self, sd: Dict[str, Any], _prefix: str = "") -> Dict[str, Any]:
         out: Dict[str, Any] = {}
         used_cuda = False
         for k, v in sd.items():
@@ -84,16 +87,18 @@ class PinnedMemoryStager:
                 if hasattr(v, "full_tensor"):
                     v = v.to_local()
                 if v.is_cuda and self.enabled:
-                    out[k] = self._buffer(v).copy_(v, non_blocking=True)
+                    out[k] = self._buffer(f"{_prefix}{k}", v).copy_(v, non_blocking=True)
                     used_cuda = True
                 else:
                     out[k] = v.cpu()
             elif isinstance(v, dict):
-                out[k] = self.stage_state_dict(v)
+                out[k] = self.stage_state_dict(v, f"{_prefix}{k}.")
             else:
                 out[k] = v
         if used_cuda:
             torch.cuda.synchronize()
+            # hand out copies: the bounce buffers are overwritten by the next save while a background writer or the
+            # incremental checkpointer may still hold this one
             out = {k: (v.clone() if torch.is_tensor(v) and v.is_pinned() else v) for k, v in out.items()}
         return out
 
@@ -286,13 +291,25 @@ class DistributedCheckpointer:
         return full[-1][2] if full else None
 
     def _cleanup_checkpoints(self):
+        """Keep the last ``keep_last_n`` durable checkpoints and everything they need to be restored: the full
+        base of a retained delta and every earlier delta on the same base (``load`` replays the whole chain,
+        since a delta holds only the keys that changed since that key was last written)."""
         keep = self.config.keep_last_n
         if keep is None or keep <= 0:
             return
         cps = [x for x in self._checkpoints() if not x[3].get("ephemeral")]
-        needed = {x[3].get("base_checkpoint") for x in cps[-keep:] if x[3].get("incremental")}
+        retained = cps[-keep:]
+        needed = set()
+        for st, _, _, meta in retained:
+            base = meta.get("base_checkpoint")
+            if not (meta.get("incremental") and base):
+                continue
+            needed.add(base)
+            for st2, _, p2, m2 in cps:
+                if m2.get("incremental") and m2.get("base_checkpoint") == base and st2 < st:
+                    needed.add(os.path.basename(p2))
         for _, _, path, _ in cps[:-keep]:
-            if os.path.basename(path) in needed or path in needed:
+            if os.path.basename(path) in needed:
                 continue
             shutil.rmtree(path, ignore_errors=True)
 

@@ -27,11 +27,19 @@ def prepare_training(model: nn.Module, *, tokens_per_rank: Optional[int] = None,
     """Returns ``(optimizer, arena | None)``. ``dp_group``: ranks holding replicas of the non-expert
     parameters (their gradients are averaged); ``ep_group``: ranks the experts are spread over."""
     p0 = next(model.parameters())
+    if dp_group is not None and dist.is_initialized() and dist.get_world_size(dp_group) <= 1:
+        dp_group = None
     if p0.device.type != "cuda":
         opt = torch.optim.AdamW(model.parameters(), lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         return opt, None
-    if dp_group is None and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1 and \
+    if dp_group is None and hasattr(model, "_replica_group"):
+        dp_group = model._replica_group   # set by parallelize_model: the ranks holding the same parameters (dp x ep x cp)
+    elif dp_group is None and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1 and \
             getattr(model, "_needs_grad_sync", False):
+        if getattr(model, "_tp_enabled", False) or getattr(model, "_pp_enabled", False):
+            raise ValueError("prepare_training: the model is tensor- or pipeline-parallel; pass dp_group= (the ranks "
+                             "that hold replicas of this rank's parameters) - averaging over the whole world would "
+                             "mix different shards")
         dp_group = dist.group.WORLD
     arena = ParamArena(model, dp_group=dp_group, device=p0.device)
     moes = moe_layers(model)

@@ -179,6 +179,10 @@ class Attention(nn.Module):
         self.w_out.weight = nn.Parameter(self.w_out.weight.data[:, rank * n_in:(rank + 1) * n_in].clone())
         self.w_out.in_features = n_in
         self._fused_qkv = None
+        for lin in (self.w_q, self.w_k, self.w_v, self.w_out):   # shards differ between TP peers: never averaged
+            lin.weight._tp_sharded = group                       # over them, and their norms add up over them
+            if lin.bias is not None and lin is not self.w_out:
+                lin.bias._tp_sharded = group
 
     def apply_cp(self, cp_mesh, *, ring=None, uly=None, **_):
         """Route attention through the context-parallel module (ring by default, Ulysses if ``uly``)."""

@@ -86,4 +86,8 @@ class FeedForward(nn.Module):
             lin.out_features = n
         self.w2.weight = nn.Parameter(self.w2.weight.data[:, rank * n:(rank + 1) * n].clone())
         self.w2.in_features = n
+        for lin in (self.w1, self.w3, self.w2):
+            lin.weight._tp_sharded = group
+            if lin.bias is not None and lin is not self.w2:
+                lin.bias._tp_sharded = group
         self._fused_w13 = None

@@ -55,6 +55,7 @@ class _RowParallelLinear(nn.Module):
         super().__init__()
         n = lin.in_features // tp
         self.weight = nn.Parameter(lin.weight.data[:, rank * n:(rank + 1) * n].clone())
+        self.weight._tp_sharded = group
         self.bias = lin.bias
         self.group, self.tp, self.rank, self.n = group, tp, rank, n
 
@@ -72,6 +73,9 @@ class _ColParallelLinear(nn.Module):
         n = lin.out_features // tp
         self.weight = nn.Parameter(lin.weight.data[rank * n:(rank + 1) * n].clone())
         self.bias = None if lin.bias is None else nn.Parameter(lin.bias.data[rank * n:(rank + 1) * n].clone())
+        self.weight._tp_sharded = group
+        if self.bias is not None:
+            self.bias._tp_sharded = group
         self.group, self.tp = group, tp
 
     def forward(self, x):

@@ -50,6 +50,7 @@ class _Region:
     lo: int = 0                              # owned shard [lo, lo+cnt) under ZeRO
     cnt: int = 0
     gshard: Optional[torch.Tensor] = None
+    tp_group: Optional[object] = None        # tensor-parallel group these parameters are shards over (None: whole)
     mc_weights: int = 0                      # NVLink multicast addresses of the weight / gradient arenas (0: none)
     mc_grads: int = 0
     _mc_keep: Optional[tuple] = None         # symmetric-memory handles, kept alive with the region
@@ -73,9 +74,11 @@ class ParamArena:
                 continue
             seen.add(id(p))
             sharded = bool(getattr(p, "_ep_sharded", False))
+            tpg = getattr(p, "_tp_sharded", None)
             decay = not is_no_decay(n, p)
-            key = f"{str(p.dtype).split('.')[-1]}_{'local' if sharded else 'repl'}_{'decay' if decay else 'nodecay'}"
-            r = self.regions.setdefault(key, _Region(key, p.dtype, decay, not sharded))
+            key = f"{str(p.dtype).split('.')[-1]}_{'local' if sharded else 'repl'}_{'decay' if decay else 'nodecay'}" \
+                  f"{'_tp' if tpg is not None else ''}"
+            r = self.regions.setdefault(key, _Region(key, p.dtype, decay, not sharded, tp_group=tpg))
             off = (r.numel + ALIGN - 1) // ALIGN * ALIGN if not self._adjacent_ok(r, p) else r.numel
             r.params.append(p)
             r.names.append(n)
@@ -261,6 +264,7 @@ class ArenaAdamW(torch.optim.Optimizer):
         self._hyper_host = torch.zeros(3, dtype=torch.float32).pin_memory() if self._cuda else torch.zeros(3)
         self.post_step_hooks = []  # callables run at the end of every step (e.g. epoch bookkeeping)
         self._tot = torch.zeros(1, device=dev, dtype=torch.float32)
+        self._tot2 = torch.zeros(2, device=dev, dtype=torch.float32)
         self._coef = torch.ones(2, device=dev, dtype=torch.float32)   # [clip coefficient, grad norm]
         self._coef_local = torch.ones(1, device=dev, dtype=torch.float32)
         self.last_grad_norm: Optional[torch.Tensor] = None
@@ -322,7 +326,22 @@ class ArenaAdamW(torch.optim.Optimizer):
                 # once per rank in the global sum below
                 s = inv * inv / (N if (N > 1 and r.replicated) else 1)
                 part.mul_(s)
-        if N > 1:
+        tp_idx = [i for i, r in enumerate(a.regions.values()) if r.tp_group is not None]
+        if tp_idx:
+            # squared norms of tensor-parallel shards add up over the TP group; everything else is identical on the
+            # TP peers and counts once: [rest, shards] -> data-parallel sum of both -> TP sum of the second
+            P = self._partial.view(len(a.regions), stride)
+            self._tot2[1] = P[tp_idx].sum()
+            self._tot2[0] = P.sum() - self._tot2[1]
+            if N > 1:
+                if a.zero:
+                    a.heap.all_reduce_(self._tot2)
+                else:
+                    dist.all_reduce(self._tot2, group=a.dp_group)
+            dist.all_reduce(self._tot2[1:], group=next(r.tp_group for r in a.regions.values() if r.tp_group is not None))
+            self._partial.zero_()
+            self._partial[:1].copy_(self._tot2.sum(dim=0, keepdim=True))
+        elif N > 1:
             torch.sum(self._partial, dim=0, keepdim=True, out=self._tot)
             if a.zero:
                 a.heap.all_reduce_(self._tot)
@@ -369,15 +388,19 @@ class ArenaAdamW(torch.optim.Optimizer):
         a = self.arena
         N = a.world
         inv = 1.0 / (self.grad_divisor * (N if N > 1 else 1))
-        sq = torch.zeros((), dtype=torch.float32, device=a.device)
+        sq = torch.zeros(2, dtype=torch.float32, device=a.device)   # [whole parameters, tensor-parallel shards]
+        tpg = None
         for r in a.regions.values():
             if N > 1 and r.replicated:
                 dist.all_reduce(r.grads, group=a.dp_group)
             s = (r.grads.float() * inv).pow(2).sum()
-            sq += s / (N if (N > 1 and r.replicated) else 1)
+            sq[1 if r.tp_group is not None else 0] += s / (N if (N > 1 and r.replicated) else 1)
+            tpg = r.tp_group if r.tp_group is not None else tpg
         if N > 1:
             dist.all_reduce(sq, group=a.dp_group)
-        norm = sq.sqrt()
+        if tpg is not None:
+            dist.all_reduce(sq[1:], group=tpg)
+        norm = sq.sum().sqrt()
         for hook in self.post_step_hooks:
             hook()
         coef = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0) if self.max_grad_norm else torch.ones(())

@@ -143,6 +143,28 @@ def get_ep_mesh(world_mesh: Optional[DeviceMesh] = None):
     return None
 
 
+def get_replica_group(world_mesh: Optional[DeviceMesh] = None):
+    """Process group of the ranks that hold the *same* (non-expert) parameters as this rank and see different
+    tokens: the product of the dp (or dp_replicate x dp_shard), ep and cp dims. Gradients of replicated parameters
+    are averaged over exactly this group; tensor- and pipeline-parallel peers hold other shards / stages and stay
+    out. ``None`` when that product is 1; the world group when it is the whole world. Collective over the mesh."""
+    mesh = world_mesh or _WORLD_MESH
+    if mesh is None:
+        return None
+    rep = [n for n in _names(mesh) if n in (MeshDimName.dp, MeshDimName.dp_replicate, MeshDimName.dp_shard,
+                                             MeshDimName.ep, MeshDimName.cp)]
+    size = 1
+    for n in rep:
+        size *= mesh[n].size()
+    if size <= 1:
+        return None
+    if size == mesh.size():
+        return dist.group.WORLD
+    if len(rep) == 1:
+        return mesh[rep[0]].get_group()
+    return mesh[tuple(rep)]._flatten("replica").get_group()
+
+
 def data_parallel_coords(world_mesh: Optional[DeviceMesh] = None) -> tuple[int, int]:
     """(index, count) of this rank among the ranks that read *different* batches: dp x ep.
     EP peers process different tokens for the dense layers, so they count as data-parallel here."""

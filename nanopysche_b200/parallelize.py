@@ -19,7 +19,8 @@ from .models.parallel_adapter import ensure_parallel_hooks
 from .models.protocol import warn_unsupported_parallelism
 from .parallel.context_parallel import ContextParallelConfig
 from .parallel.fsdp import DataParallelConfig, apply_activation_checkpointing, apply_generic_fsdp
-from .parallel.mesh import (MeshDimName, get_cp_mesh, get_dp_model_mesh, get_ep_mesh, get_pp_mesh, get_tp_mesh)
+from .parallel.mesh import (MeshDimName, get_cp_mesh, get_dp_model_mesh, get_ep_mesh, get_pp_mesh, get_replica_group,
+                            get_tp_mesh)
 from .parallel.tensor_parallel import TensorParallelConfig
 
 log = logging.getLogger(__name__)
@@ -83,11 +84,17 @@ def parallelize_model(model: nn.Module, *, world_mesh, device: Optional[torch.de
         if use_arena:
             # sharded optimizer state + fused reduce-scatter/AdamW/all-gather: set up by engine.prepare_training
             model._dp_mesh_for_arena = dp_mesh
+            model._replica_group = get_replica_group(world_mesh)   # read by engine.prepare_training
             model._needs_grad_sync = True
         elif hasattr(model, "apply_fsdp"):
             model.apply_fsdp(dp_mesh=dp_mesh, param_dtype=dp_config.param_dtype, reduce_dtype=dp_config.reduce_dtype)
         else:
             apply_generic_fsdp(model, dp_mesh, dp_config)
+    if world_mesh is not None and not hasattr(model, "_replica_group"):
+        # un-sharded data parallelism: gradients are averaged over the ranks that hold the same parameters
+        model._replica_group = get_replica_group(world_mesh)
+        if model._replica_group is not None and not getattr(model, "_fsdp_enabled", False):
+            model._needs_grad_sync = True
     if device is not None and getattr(model, "_init_on_parallelize", False) and hasattr(model, "init_weights"):
         model.init_weights(device=device, world_mesh=world_mesh)
     return model

@@ -74,7 +74,7 @@ class TrainingConfig:
 class Trainer:
     def __init__(self, config: TrainingConfig, model: nn.Module, optimizer: torch.optim.Optimizer,
                  scheduler=None, data_loader=None, callbacks: Optional[List[Callback]] = None, checkpointer=None,
-                 hang_detector=None, heartbeat=None, device: Optional[torch.device] = None):
+                 hang_detector=None, heartbeat=None, device: Optional[torch.device] = None, status_reader=None):
         self.config = config
         self.model = model
         self.optimizer = optimizer
@@ -90,8 +90,17 @@ class Trainer:
         self._compressor = None
         self._best_val_loss = float("inf")
         self._stop_reason: Optional[str] = None
+        self.emergency_checkpoint_dir: Optional[str] = None
         self._data_iter = None
         self._setup_distributed(device)
+        # reads the kernels' device status words ((code, kernel, block, detail, ...); code 0 = ok). The fused kernels
+        # bound every wait on a peer and record a code instead of hanging; the trainer looks at it wherever it
+        # synchronises with the device anyway (metric flush, checkpoint)
+        self._status_reader = status_reader
+        if status_reader is None and self.device.type == "cuda":
+            from ..ops import _lib
+
+            self._status_reader = _lib.status
         if config.enable_hang_detection and self.hang_detector is None:
             from ..fault_tolerance.hang_detection import HangDetector
 
@@ -116,6 +125,7 @@ class Trainer:
             p = next(self.model.parameters(), None)
             self.device = p.device if p is not None else torch.device("cpu")
         self._arena_opt = type(self.optimizer).__name__ == "ArenaAdamW"
+        self._reducer = None           # parallel.ddp.BucketedGradReducer, built on first use
         self._pp_schedule = None       # built on the first step when the model is one stage of a pipeline
 
     @property
@@ -131,8 +141,43 @@ class Trainer:
         v = self._metrics.get(name)
         return float(v) if v is not None else None
 
+    def check_device_status(self, where: str = "") -> None:
+        """Raise if a kernel of an earlier step gave up on a bounded wait (a peer that stopped answering) or failed a
+        device-side check. ``CommTimeoutError`` for timeouts, ``KernelError`` otherwise; ``fit()`` then runs the
+        ``on_error`` callbacks and writes an emergency checkpoint of this rank's state."""
+        if self._status_reader is None:
+            return
+        st = tuple(self._status_reader())
+        if not st or st[0] == 0:
+            return
+        from ..fault_tolerance.hang_detection import CommTimeoutError
+        from ..ops import _lib
+
+        if self.device.type == "cuda":
+            _lib.lib().np_status_clear()
+        msg = (f"device status {st[0]} ({_lib.STATUS_NAMES.get(st[0], '?')}) kernel={st[1] if len(st) > 1 else '?'} "
+               f"block={st[2] if len(st) > 2 else '?'} detail={st[3] if len(st) > 3 else '?'} at step {self.step} {where}")
+        if st[0] in (1, 2):
+            raise CommTimeoutError(msg)
+        raise _lib.KernelError(msg)
+
+    def _emergency_checkpoint(self) -> Optional[str]:
+        """This rank's model / optimizer state written without any collective (peers may be gone):
+        ``<save_dir>/emergency_step_{step:06d}/rank_{rank:04d}_{model,optimizer}.pt``."""
+        try:
+            d = os.path.join(self.config.save_dir, f"emergency_step_{self.step:06d}")
+            os.makedirs(d, exist_ok=True)
+            torch.save({k: v.detach().cpu() for k, v in self.model.state_dict().items()},
+                       os.path.join(d, f"rank_{self.rank:04d}_model.pt"))
+            torch.save(self.optimizer.state_dict(), os.path.join(d, f"rank_{self.rank:04d}_optimizer.pt"))
+            return d
+        except Exception as e:  # noqa: BLE001
+            log.error("emergency checkpoint failed: %s", e)
+            return None
+
     def _flush_metrics(self) -> Dict[str, float]:
         """Average the buffered metrics over all ranks (every rank must call this)."""
+        self.check_device_status("(metric flush)")
         names = sorted(self._metrics)
         vals = torch.tensor([float(self._metrics[n]) for n in names], dtype=torch.float64)
         if self.world_size > 1 and dist.is_initialized():
@@ -182,6 +227,10 @@ class Trainer:
                     cb.on_error(self, e)
                 except Exception:  # noqa: BLE001
                     pass
+            from ..fault_tolerance.hang_detection import CommTimeoutError
+
+            if isinstance(e, CommTimeoutError):
+                self.emergency_checkpoint_dir = self._emergency_checkpoint()
             raise
         finally:
             if self.hang_detector is not None:
@@ -243,15 +292,24 @@ class Trainer:
         if c.save_interval and self.step % c.save_interval == 0 and self.step > 0:
             self._save_checkpoint()
 
+    def _grad_reducer(self):
+        """Bucketed, backward-overlapped all-reduce over the ranks that hold the same parameters (``parallel/ddp.py``);
+        built lazily for un-sharded data parallelism without the parameter arena."""
+        if self._reducer is None and self.world_size > 1 and not getattr(self.model, "_fsdp_enabled", False) and \
+                getattr(self.model, "_needs_grad_sync", False) and not self._arena_opt:
+            from ..parallel.ddp import BucketedGradReducer
+
+            group = getattr(self.model, "_replica_group", dist.group.WORLD)
+            if group is not None:
+                params = [p for p in self.model.parameters() if not getattr(p, "_ep_sharded", False)]
+                self._reducer = BucketedGradReducer(params, group=group)
+        return self._reducer
+
     def _sync_replicated_grads(self):
-        """Plain data parallelism for un-sharded models: average gradients over the world."""
-        if self.world_size <= 1 or getattr(self.model, "_fsdp_enabled", False) or \
-                not getattr(self.model, "_needs_grad_sync", False):
-            return
-        for p in self.model.parameters():
-            if p.grad is not None and not getattr(p, "_ep_sharded", False):
-                dist.all_reduce(p.grad)
-                p.grad.div_(self.world_size)
+        """Plain data parallelism for un-sharded models: finish the bucketed all-reduce started during backward."""
+        r = self._grad_reducer()
+        if r is not None:
+            r.finish()
 
     def _post_batch_hooks(self):
         for m in self.model.modules():
@@ -304,7 +362,10 @@ class Trainer:
         self.model.train()
         autocast_on = self.device.type == "cuda" and c.dtype in (torch.bfloat16, torch.float16) and \
             next(self.model.parameters()).dtype == torch.float32
-        for input_ids, labels in batches:
+        reducer = self._grad_reducer()
+        for bi, (input_ids, labels) in enumerate(batches):
+            if reducer is not None:
+                reducer.enabled = bi == accum - 1   # gradients accumulate locally; reduce on the last micro-batch
             input_ids = input_ids.to(self.device, non_blocking=True)
             labels = labels.to(self.device, non_blocking=True)
             kw = {}
@@ -343,6 +404,7 @@ class Trainer:
 
     # ------------------------------------------------------------------ checkpoints
     def _save_checkpoint(self, is_best: bool = False):
+        self.check_device_status("(before checkpoint)")
         if self.checkpointer is not None:
             self.checkpointer.save(self.step, self.model, self.optimizer, scheduler=self.scheduler,
                                    extra={"tokens_seen": self.tokens_seen, "best_val_loss": self._best_val_loss})

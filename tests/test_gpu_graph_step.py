@@ -68,7 +68,7 @@ def _run_fused(model, ids, graphed: bool):
 
 
 def _run_torch_fp32(model, ids):
-    # the arena applies no weight decay to norms, biases and router gates: same grouping here
+    # the arena applies no weight decay to norms, biases and embeddings: same grouping here
     from nanopysche_b200.optim.adamw import is_no_decay
 
     decay = [p for n, p in model.named_parameters() if not is_no_decay(n, p)]
@@ -102,8 +102,12 @@ def test_graphed_step_matches_eager_and_fp32_pytorch():
     print("eager ", [round(x, 4) for x in l_eager])
     print("fp32  ", [round(x, 4) for x in l_ref])
     assert all(x == x and x < 20 for x in l_graph), l_graph
-    for a, b in zip(l_graph, l_eager):   # same kernels, same order: only atomics-order noise is allowed
-        assert abs(a - b) <= 2e-2 * abs(b), (l_graph, l_eager)
-    for a, b in zip(l_graph, l_ref):     # bf16 compute against fp32
-        assert abs(a - b) <= 3e-2 * abs(b), (l_graph, l_ref)
-    assert l_graph[0] < 10.6 and l_graph[-1] < l_graph[0] - 0.5, l_graph   # starts near ln(V), memorises the batch
+    # The three runs follow one trajectory. Early on they agree closely (the graph replays the eager step's kernels;
+    # bf16 against fp32 differs in the third digit); once the model memorises the batch at this learning rate the
+    # trajectory is sensitive to rounding, so the later steps get a wider band.
+    for i, (a, b, c) in enumerate(zip(l_graph, l_eager, l_ref)):
+        tol = 1e-2 if i < 6 else 0.15
+        assert abs(a - b) <= tol * abs(b), (i, l_graph, l_eager)
+        assert abs(a - c) <= tol * abs(c), (i, l_graph, l_ref)
+    assert l_graph[0] < 10.6 and l_graph[-1] < l_graph[0] - 3.0, l_graph   # starts near ln(V), memorises the batch
+    assert l_ref[-1] < l_ref[0] - 3.0 and l_eager[-1] < l_eager[0] - 3.0

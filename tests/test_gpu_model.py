@@ -141,6 +141,51 @@ def test_bounded_wait_reports_instead_of_hanging():
     assert (torch.ones(4, device="cuda") * 2).sum().item() == 8.0
 
 
+def test_trainer_surfaces_a_timed_out_device_wait(tmp_path):
+    """The same flag that nothing sets, launched from a callback in the middle of ``Trainer.fit()``: the trainer reads
+    the status word at its next metric flush and raises ``CommTimeoutError`` (emergency checkpoint written)."""
+    import ctypes as C
+
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.engine import prepare_training
+    from nanopysche_b200.fault_tolerance.hang_detection import CommTimeoutError
+    from nanopysche_b200.ops import _lib
+    from nanopysche_b200.train.callbacks.base import Callback
+    from nanopysche_b200.train.trainer import Trainer, TrainingConfig
+
+    torch.manual_seed(0)
+    cfg = TransformerConfig(vocab_size=512, d_model=256, n_layers=1, n_heads=2, n_kv_heads=2, ffn_hidden=512,
+                            max_seq_len=128, qk_norm=False)
+    model = cfg.build(dtype=torch.bfloat16, init_device="cuda")
+    opt, _ = prepare_training(model, tokens_per_rank=2 * 128, lr=1e-3)
+    keep = []
+
+    class StuckPeer(Callback):
+        def post_step(self, t):
+            if t.step != 2:
+                return
+            T, K, D = 8, 2, 256
+            a = _lib.CombineArgs()
+            bufs = [torch.zeros(T * K, D, device="cuda", dtype=torch.bfloat16),
+                    torch.zeros(T, K, device="cuda", dtype=torch.int32),
+                    torch.zeros(T, D, device="cuda", dtype=torch.bfloat16),
+                    torch.zeros(1, device="cuda", dtype=torch.int32), torch.ones(1, device="cuda", dtype=torch.int32)]
+            keep.extend(bufs)
+            a.rows, a.slot_pos, a.out = bufs[0].data_ptr(), bufs[1].data_ptr(), bufs[2].data_ptr()
+            a.T, a.K, a.D, a.E = T, K, D, 1
+            a.flags, a.sent_to_peer, a.n_ranks, a.epoch, a.limit_ns = bufs[3].data_ptr(), bufs[4].data_ptr(), 1, 5, \
+                200_000_000
+            _lib.check(_lib.lib().np_ep_combine(C.byref(a), C.c_void_p(_lib.stream())), "ep_combine")
+
+    tc = TrainingConfig(global_batch_size=2 * 128, micro_batch_size=2, sequence_length=128, max_steps=6,
+                        log_interval=1, save_interval=0, save_dir=str(tmp_path), vocab_size=512)
+    tr = Trainer(tc, model, opt, None, None, [StuckPeer()])
+    with pytest.raises(CommTimeoutError):
+        tr.fit()
+    assert tr.step == 2 and tr.emergency_checkpoint_dir is not None
+    assert (torch.ones(4, device="cuda") * 2).sum().item() == 8.0   # the context is still usable
+
+
 def test_fused_moe_fp8_flow_path():
     """FP8-Flow-MoE recipe on the fused path: e4m3 dispatch + block-scaled fp8 expert GEMMs in forward,
     bf16 gradients; compared with the fp32 generic layer at fp8 tolerance."""
@@ -215,3 +260,28 @@ def test_cli_train_and_bench_on_gpu(tmp_path, capsys):
     assert rc in (0, None)
     out = capsys.readouterr().out
     assert "tokens/s" in out or "tok/s" in out.lower()
+
+
+def test_checkpoint_round_trip_on_gpu_with_equal_layer_shapes(tmp_path):
+    """Pinned staging must not alias tensors of equal shape and dtype: save a three-layer model whose layers all
+    have the same shapes from the GPU, load it into a fresh model, compare every tensor."""
+    from nanopysche_b200.checkpoint.distributed import CheckpointConfig, DistributedCheckpointer
+    from nanopysche_b200.config import TransformerConfig
+
+    def build(seed):
+        torch.manual_seed(seed)
+        cfg = TransformerConfig(vocab_size=256, d_model=128, n_layers=3, n_heads=2, n_kv_heads=2, ffn_hidden=256,
+                                max_seq_len=64, qk_norm=False)
+        return cfg.build(dtype=torch.bfloat16, init_device="cuda")
+
+    m = build(0)
+    with torch.no_grad():
+        for i, blk in enumerate(m.blocks.values()):
+            blk.attention.w_q.weight.fill_(float(i + 1))
+    ck = DistributedCheckpointer(CheckpointConfig(save_dir=str(tmp_path), pinned_memory=True))
+    assert ck.stager.enabled
+    ck.save(3, m)
+    m2 = build(1)
+    ck.load(model=m2)
+    for k, v in m.state_dict().items():
+        assert torch.equal(m2.state_dict()[k], v), k

@@ -356,3 +356,82 @@ def test_nvls_allocation_is_opt_in(monkeypatch):
     assert nvls_alloc(1024, torch.float32, object(), torch.device("cpu")) is None
     monkeypatch.setenv("NPB200_NVLS", "1")
     assert nvls_alloc(1024, torch.float32, None, torch.device("cpu")) is None   # no group: nothing to share with
+
+
+def _tp_dp_arena_worker(rank, world):
+    """tp 2 x dp 2 through parallelize_model + prepare_training's group choice: after one clipped AdamW step every
+    rank's shards equal the matching slices of an unsharded model stepped on the whole batch."""
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.optim.arena import ArenaAdamW, ParamArena
+    from nanopysche_b200.parallel.fsdp import DataParallelConfig
+    from nanopysche_b200.parallel.mesh import build_world_mesh
+    from nanopysche_b200.parallel.tensor_parallel import TensorParallelConfig
+    from nanopysche_b200.parallelize import parallelize_model
+
+    torch.manual_seed(0)
+    cfg = TransformerConfig(vocab_size=64, d_model=32, n_layers=2, n_heads=4, n_kv_heads=2, ffn_hidden=64,
+                            max_seq_len=16, qk_norm=False)
+    full = cfg.build()
+    model = copy.deepcopy(full)
+    mesh = build_world_mesh(tp_size=2, device_type="cpu", replace=True)
+    model = parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"), tp_config=TensorParallelConfig(2),
+                              dp_config=DataParallelConfig(backend="arena"))
+    grp = model._replica_group
+    assert grp is not None and dist.get_world_size(grp) == 2
+    assert getattr(model.blocks["0"].attention.w_q.weight, "_tp_sharded", None) is not None
+    tp_rank, dp_rank = rank % 2, rank // 2
+    torch.manual_seed(1)
+    ids = torch.randint(0, 64, (4, 16))
+    mine = ids[dp_rank * 2:(dp_rank + 1) * 2]
+    arena = ParamArena(model, dp_group=grp, device=torch.device("cpu"))
+    opt = ArenaAdamW(arena, lr=1e-2, weight_decay=0.1, max_grad_norm=0.05)
+    out = model(mine, labels=mine)
+    out["loss"].backward()
+    opt.step()
+    # oracle: the unsharded model on the whole batch (one rank, same optimizer code path)
+    a0 = ParamArena(full, device=torch.device("cpu"))
+    o0 = ArenaAdamW(a0, lr=1e-2, weight_decay=0.1, max_grad_norm=0.05)
+    full(ids, labels=ids)["loss"].backward()
+    o0.step()
+    assert abs(float(opt.last_grad_norm) - float(o0.last_grad_norm)) < 1e-4 * float(o0.last_grad_norm) + 1e-6, \
+        (float(opt.last_grad_norm), float(o0.last_grad_norm))
+    ref = dict(full.named_parameters())
+    for name, p in model.named_parameters():
+        r = ref[name]
+        if name.endswith(("w_q.weight", "w_k.weight", "w_v.weight", "w1.weight", "w3.weight")):
+            n = r.shape[0] // 2
+            r = r[tp_rank * n:(tp_rank + 1) * n]
+        elif name.endswith(("w_out.weight", "w2.weight")):
+            n = r.shape[1] // 2
+            r = r[:, tp_rank * n:(tp_rank + 1) * n]
+        assert torch.allclose(p, r, atol=2e-5, rtol=1e-4), (name, (p - r).abs().max())
+    return True
+
+
+def test_arena_step_with_tensor_parallel_and_data_parallel():
+    assert all(run_distributed(_tp_dp_arena_worker, 4))
+
+
+def _ddp_worker(rank, world):
+    from nanopysche_b200.parallel.ddp import BucketedGradReducer
+
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Tanh(), torch.nn.Linear(16, 4))
+    ref = copy.deepcopy(net)
+    red = BucketedGradReducer(net.parameters(), group=dist.group.WORLD, bucket_bytes=300)   # several buckets
+    assert len(red.buckets) >= 2
+    torch.manual_seed(5)
+    x = torch.randn(4 * world, 8)
+    for step in range(2):   # buckets are reusable
+        net.zero_grad()
+        ref.zero_grad()
+        net(x[rank * 4:(rank + 1) * 4]).pow(2).mean().backward()
+        red.finish()
+        ref(x).pow(2).mean().backward()
+        for a, b in zip(net.parameters(), ref.parameters()):
+            assert torch.allclose(a.grad, b.grad, atol=1e-6), (a.grad - b.grad).abs().max()
+    return True
+
+
+def test_bucketed_grad_reducer_matches_full_batch():
+    assert all(run_distributed(_ddp_worker, 2))

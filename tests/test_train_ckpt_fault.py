@@ -88,6 +88,32 @@ def test_trainer_synthetic_batches_and_error_hook():
     assert "on_error" in rec.events and rec.events[-1] == "close" and tr.step == 1
 
 
+def test_trainer_raises_comm_timeout_from_the_device_status_word(tmp_path):
+    """A stubbed status reader stands in for a kernel whose bounded wait ran out (code 2: flag wait): the trainer
+    sees it at the next metric flush, raises CommTimeoutError, runs on_error and writes an emergency checkpoint."""
+    from nanopysche_b200.fault_tolerance.hang_detection import CommTimeoutError
+
+    m = tiny_model()
+    opt = torch.optim.SGD(m.parameters(), lr=0.1)
+    rec = Recorder()
+    calls = {"n": 0}
+
+    def reader():
+        calls["n"] += 1
+        return (2, 11, 3, 250, 0, 0, 0, 0) if calls["n"] >= 3 else (0,) * 8
+
+    tc = TrainingConfig(global_batch_size=32, micro_batch_size=2, sequence_length=16, max_steps=8, log_interval=1,
+                        save_interval=0, save_dir=str(tmp_path), dtype=torch.float32, vocab_size=64)
+    tr = Trainer(tc, m, opt, None, None, [rec], status_reader=reader)
+    with pytest.raises(CommTimeoutError, match="flag wait timed out"):
+        tr.fit()
+    assert tr.step == 3 and "on_error" in rec.events and rec.events[-1] == "close"
+    d = tr.emergency_checkpoint_dir
+    assert d is not None and os.path.isfile(os.path.join(d, "rank_0000_model.pt"))
+    sd = torch.load(os.path.join(d, "rank_0000_model.pt"), weights_only=False)
+    assert torch.equal(sd["lm_head.weight"], m.lm_head.weight.detach())
+
+
 def test_dataset_and_loader_iterator_protocol():
     tokens = np.arange(1000, dtype=np.uint16)
     ds = DistributedDataset(tokens, 10)
@@ -219,6 +245,38 @@ def test_incremental_checkpoint_chain(tmp_path):
     inc = IncrementalCheckpointer(0.01, 3)
     assert inc.should_save_full(0) and not inc.should_save_full(1) and inc.should_save_full(3)
     assert len(IncrementalCheckpointer._hash(torch.randn(100))) == 16
+
+
+def test_retention_keeps_the_deltas_a_kept_checkpoint_needs(tmp_path):
+    """keep_last_n = 2 with deltas: the delta of step 2 carries a change that steps 3 and 4 do not repeat, so it
+    must survive the clean-up for step 4 to restore."""
+    m = tiny_model()
+    ck = DistributedCheckpointer(CheckpointConfig(save_dir=str(tmp_path), incremental=True, keep_last_n=2,
+                                                  full_save_interval=10, incremental_threshold=0.01))
+    ck.save(1, m)
+    with torch.no_grad():
+        m.lm_head.weight.mul_(2.0)
+    ck.save(2, m)
+    with torch.no_grad():
+        m.embeddings.weight.mul_(3.0)
+    ck.save(3, m)
+    ck.save(4, m)
+    assert os.path.isdir(tmp_path / "step_000001") and os.path.isdir(tmp_path / "step_000002")
+    m2 = tiny_model()
+    meta = ck.load(model=m2)
+    assert meta["step"] == 4
+    for k, v in m.state_dict().items():
+        assert torch.equal(m2.state_dict()[k], v), k
+
+
+def test_stager_gives_every_tensor_its_own_buffer():
+    st = PinnedMemoryStager(enabled=False)
+    sd = {f"l{i}.w": torch.full((4, 4), float(i)) for i in range(5)}
+    out = st.stage_state_dict(sd)
+    assert [float(out[f"l{i}.w"][0, 0]) for i in range(5)] == [0.0, 1.0, 2.0, 3.0, 4.0]
+    st._buffer("a", torch.zeros(3))
+    assert st._buffer("a", torch.zeros(3)) is st._buffer("a", torch.ones(3))          # reused across saves
+    assert st._buffer("a", torch.zeros(3)) is not st._buffer("b", torch.zeros(3))    # never shared between names
 
 
 def test_async_save_and_helpers(tmp_path):
