@@ -1,4 +1,4 @@
-"""Context-parallel attention benchmark: ``torchrun --nproc-per-node N -m nanopysche_b200.parallel.cp_bench``.
+"""Context-parallel attention benchmark: ``torchrun --nproc-per-node N -m benchmarks.cp_bench``.
 
 Times forward + backward of attention over a sequence sharded over the ``N`` ranks (zig-zag layout) for
 
@@ -34,9 +34,9 @@ def main(argv=None):
     torch.cuda.set_device(local)
     dist.init_process_group("nccl")
     rank, world = dist.get_rank(), dist.get_world_size()
-    from ..ops import _lib
-    from ..ops.microbench import peaks
-    from .context_parallel import RingAttention
+    from nanopysche_b200.ops import _lib
+    from benchmarks.microbench import peaks
+    from nanopysche_b200.parallel.context_parallel import RingAttention
 
     dev = torch.device("cuda", local)
     S = a.seq // world

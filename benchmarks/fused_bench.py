@@ -1,5 +1,5 @@
 """Fused compute+collective linears against their NCCL baselines:
-``torchrun --nproc-per-node N -m nanopysche_b200.parallel.fused_bench [--tokens 4096 --d-model 2048 --ffn 5632]``.
+``torchrun --nproc-per-node N -m benchmarks.fused_bench [--tokens 4096 --d-model 2048 --ffn 5632]``.
 
 Variants (forward only, CUDA events on every rank, max over ranks, median of ``--iters``):
 
@@ -55,10 +55,10 @@ def main(argv=None):
     dist.init_process_group("nccl")
     rank, n = dist.get_rank(), dist.get_world_size()
     dev = torch.device("cuda", local)
-    from ..ops import _lib, tp_fused
-    from ..ops.fsdp_fused import FSDPRuntime
-    from ..ops.gemm import gemm
-    from ..ops.microbench import peaks
+    from nanopysche_b200.ops import _lib, tp_fused
+    from nanopysche_b200.ops.fsdp_fused import FSDPRuntime
+    from nanopysche_b200.ops.gemm import gemm
+    from benchmarks.microbench import peaks
 
     _, tf, src = peaks()
     M, D, F = a.tokens, a.d_model, a.ffn

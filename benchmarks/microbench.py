@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: ``python -m nanopysche_b200.ops.microbench <case> [options]``.
+"""Kernel micro-benchmarks: ``python -m benchmarks.microbench <case> [options]`` (from the repository root).
 
 Each case times one in-tree kernel with CUDA events after warm-up, flushing L2 between iterations
 (a 512 MB write), and prints one JSON line with the achieved rate and its fraction of the measured
@@ -6,7 +6,8 @@ roofline (``MEASURED_PEAKS.json`` at the repository root when present, else 6.65
 1.59 PFLOP/s). The same command lines are what the ``ncu`` captures under ``profiles/`` run.
 
 Cases: gemm (fwd / dgrad / wgrad layouts, optional cuBLAS comparison), swiglu (fused GEMM + SwiGLU),
-rmsnorm, adamw, xent, moe (one fused MoE layer forward + backward), attention (flash forward / backward).
+rmsnorm, adamw, xent, moe (one fused MoE layer forward + backward), attention (flash forward / backward), mxfp8,
+flow (the FP8-Flow-MoE grouped expert GEMMs against the bf16 grouped GEMM at the same shapes).
 """
 from __future__ import annotations
 
@@ -19,7 +20,7 @@ import torch
 
 
 def peaks():
-    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    p = Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
         return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
@@ -46,7 +47,7 @@ def timeit(fn, iters: int, warmup: int = 3, flush: bool = True):
 
 
 def case_gemm(a):
-    from .gemm import gemm
+    from nanopysche_b200.ops.gemm import gemm
 
     M, N, K = a.m, a.n, a.k
     dev = "cuda"
@@ -71,7 +72,7 @@ def case_gemm(a):
 
 
 def case_swiglu(a):
-    from .gemm import gemm_swiglu
+    from nanopysche_b200.ops.gemm import gemm_swiglu
 
     x = torch.randn(a.m, a.k, device="cuda").bfloat16()
     w1 = torch.randn(a.n, a.k, device="cuda").bfloat16()
@@ -82,7 +83,7 @@ def case_swiglu(a):
 
 
 def case_rmsnorm(a):
-    from .norm import rms_norm
+    from nanopysche_b200.ops.norm import rms_norm
 
     x = torch.randn(a.m, a.n, device="cuda").bfloat16()
     r = torch.randn(a.m, a.n, device="cuda").bfloat16()
@@ -93,7 +94,7 @@ def case_rmsnorm(a):
 
 
 def case_adamw(a):
-    from . import _lib
+    from nanopysche_b200.ops import _lib
 
     n = a.m * a.n
     p, g = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
@@ -106,7 +107,7 @@ def case_adamw(a):
 
 
 def case_xent(a):
-    from .xent import cross_entropy
+    from nanopysche_b200.ops.xent import cross_entropy
 
     logits = torch.randn(a.m, a.n, device="cuda").bfloat16().requires_grad_(True)
     labels = torch.randint(0, a.n, (a.m,), device="cuda")
@@ -121,8 +122,8 @@ def case_xent(a):
 
 
 def case_moe(a):
-    from ..models.moe import MoEBase
-    from .moe import build_runtime
+    from nanopysche_b200.models.moe import MoEBase
+    from nanopysche_b200.ops.moe import build_runtime
 
     T, D, H, E, K = a.m, a.k, a.n, a.experts, a.topk
     moe = MoEBase(d_model=D, hidden_size=H, num_experts=E, top_k=K, capacity_factor=a.capacity, dtype=torch.bfloat16,
@@ -157,7 +158,7 @@ def case_attention(a):
     """Flash attention forward and backward (``--batch --seq --heads --kv-heads``, head_dim 128, causal unless
     ``--full``); ``--sdpa`` also times PyTorch SDPA on the same tensors. FLOPs: 4 B H S^2 hd (x 2.5 for backward),
     halved under causal masking."""
-    from . import attention as A
+    from nanopysche_b200.ops import attention as A
 
     B, S, Hq, Hkv = a.batch, a.seq, a.heads, a.kv_heads
     qkv = torch.randn(B, S, (Hq + 2 * Hkv) * 128, device="cuda", dtype=torch.bfloat16)
@@ -185,7 +186,7 @@ def case_attention(a):
 
 def case_mxfp8(a):
     """MXFP8 GEMM (operands quantised beforehand), the quantiser alone, and the block-scaled 1x128 kernel."""
-    from .gemm_mxfp8 import gemm_mxfp8, mx_quantize
+    from nanopysche_b200.ops.gemm_mxfp8 import gemm_mxfp8, mx_quantize
 
     M, N, K = a.m, a.n, a.k
     A, B = torch.randn(M, K, device="cuda").bfloat16(), torch.randn(N, K, device="cuda").bfloat16()
@@ -200,7 +201,7 @@ def case_mxfp8(a):
     if a.cublas:
         from fp8_flow_moe import ops as fops
 
-        from .gemm_fp8 import gemm_fp8_block
+        from nanopysche_b200.ops.gemm_fp8 import gemm_fp8_block
 
         xq, xs = fops.quantize_to_fp8(A)
         wq, ws = fops.quantize_weight_blockwise(B)
@@ -211,7 +212,68 @@ def case_mxfp8(a):
     return res, flops, None
 
 
-CASES = {"mxfp8": case_mxfp8, "attention": case_attention, "gemm": case_gemm, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "xent": case_xent,
+def case_flow(a):
+    """Grouped expert GEMMs of one MoE layer at ``--m`` rows per expert, ``--experts`` local experts, d_model
+    ``--k``, expert hidden ``--n``: gate|up (``[rows, 2H] = x @ [w1; w3]^T``) and down (``[rows, D] = h @ w2``) on
+    the block-scaled e4m3 path (1x128 / 128x128 power-of-two scales) and on the bf16 tcgen05 path, plus the
+    quantisers the fp8 path adds (SwiGLU + re-quantise per forward, weights once per optimizer step)."""
+    from nanopysche_b200.ops import _lib
+    from nanopysche_b200.ops import gemm_mxfp8 as mx
+    import ctypes as C
+
+    E, R, D, H = a.experts, a.m, a.k, a.n
+    rows = E * R
+    dev = "cuda"
+    x = torch.randn(rows, D, device=dev).bfloat16()
+    w1, w3, w2 = (torch.randn(E * H, D, device=dev).bfloat16() * 0.02 for _ in range(3))
+    grp = torch.arange(E, device=dev, dtype=torch.int32).repeat_interleave(R // 128)
+    mrows = torch.full((rows // 128,), 128, device=dev, dtype=torch.int32)
+    xq, xs = mx.flow_quantize_act(x)
+    w13q = torch.empty((E * 2 * H, D), device=dev, dtype=torch.float8_e4m3fn)
+    s13 = torch.zeros(mx.sf_bytes(E * 2 * H, D), device=dev, dtype=torch.uint8)
+    mx.flow_quantize_weight(w1, E, out=(w13q, s13), out_rows=2 * H, out_row0=0)
+    mx.flow_quantize_weight(w3, E, out=(w13q, s13), out_rows=2 * H, out_row0=H)
+    w2q, s2 = mx.flow_quantize_weight(w2, E, transpose=True)
+    gu = torch.empty(rows, 2 * H, device=dev, dtype=torch.bfloat16)
+    y = torch.empty(rows, D, device=dev, dtype=torch.bfloat16)
+    t_gu, _ = timeit(lambda: mx.gemm_mxfp8(xq, xs, w13q, s13, out=gu, mblk_group=grp, mblk_rows=mrows,
+                                           rows_per_group=2 * H), a.iters)
+    hq, hs = mx.flow_quantize_act(gu, swiglu=True)
+    t_q, _ = timeit(lambda: mx.flow_quantize_act(gu, swiglu=True, out=(hq, hs)), a.iters)
+    t_dn, _ = timeit(lambda: mx.gemm_mxfp8(hq, hs, w2q, s2, out=y, mblk_group=grp, mblk_rows=mrows, rows_per_group=D),
+                     a.iters)
+    t_wq, _ = timeit(lambda: (mx.flow_quantize_weight(w1, E, out=(w13q, s13), out_rows=2 * H, out_row0=0),
+                              mx.flow_quantize_weight(w3, E, out=(w13q, s13), out_rows=2 * H, out_row0=H),
+                              mx.flow_quantize_weight(w2, E, transpose=True, out=(w2q, s2))), a.iters)
+
+    def bf16_grouped(A, B, N, K, b_mn, out, B2=None, C2=None):
+        g = _lib.GemmArgs()
+        g.A, g.B, g.C = A.data_ptr(), B.data_ptr(), out.data_ptr()
+        g.lda, g.ldb, g.ldc = A.stride(0), B.stride(0), out.stride(0)
+        g.a_rows, g.b_rows, g.M, g.N, g.K = A.shape[0], B.shape[0], rows, N, K
+        g.b_mn, g.mode, g.alpha = int(b_mn), 1, 1.0
+        g.mblk_group, g.mblk_rows, g.group_stride_b = grp.data_ptr(), mrows.data_ptr(), H
+        if B2 is not None:
+            g.B2, g.epilogue, g.C2, g.ldc2 = B2.data_ptr(), 1, C2.data_ptr(), C2.stride(0)
+        _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "grouped_gemm")
+
+    h = torch.empty(rows, H, device=dev, dtype=torch.bfloat16)
+    b_gu, _ = timeit(lambda: bf16_grouped(x, w1, H, D, False, h, B2=w3, C2=gu), a.iters)
+    b_dn, _ = timeit(lambda: bf16_grouped(h, w2, D, H, True, y), a.iters)
+    f_gu, f_dn = 2.0 * rows * 2 * H * D, 2.0 * rows * D * H
+    res = {"case": "flow", "rows_per_expert": R, "experts": E, "D": D, "H": H,
+           "fp8_gate_up_ms": t_gu, "fp8_gate_up_tflops": f_gu / t_gu / 1e9,
+           "fp8_down_ms": t_dn, "fp8_down_tflops": f_dn / t_dn / 1e9,
+           "swiglu_quant_ms": t_q, "weight_quant_ms_per_step": t_wq,
+           "bf16_gate_up_swiglu_ms": b_gu, "bf16_gate_up_tflops": f_gu / b_gu / 1e9,
+           "bf16_down_ms": b_dn, "bf16_down_tflops": f_dn / b_dn / 1e9,
+           "gemm_speedup_gate_up": b_gu / t_gu, "gemm_speedup_down": b_dn / t_dn,
+           "forward_speedup_with_quant": (b_gu + b_dn) / (t_gu + t_q + t_dn),
+           "ms": t_gu + t_dn, "tflops": (f_gu + f_dn) / (t_gu + t_dn) / 1e9}
+    return res, f_gu + f_dn, None
+
+
+CASES = {"flow": case_flow, "mxfp8": case_mxfp8, "attention": case_attention, "gemm": case_gemm, "swiglu": case_swiglu, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "xent": case_xent,
          "moe": case_moe}
 
 
@@ -243,7 +305,7 @@ def main(argv=None):
         res["frac_of_" + src + "_bf16_peak"] = res.get("tflops", 0.0) / tf
     if nbytes:
         res["frac_of_" + src + "_hbm"] = res["gbs"] / hbm
-    from . import _lib
+    from nanopysche_b200.ops import _lib
 
     res["status"] = list(_lib.status())
     print(json.dumps(res))

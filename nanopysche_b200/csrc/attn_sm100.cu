@@ -839,7 +839,8 @@ NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
       a->Sq > BQ) {
     constexpr int SMEM2 = (2 + G_KST + G_VST) * TILE_BYTES + 8 * G_COUNT + 8 + 16;
     static_assert(SMEM2 <= 227 * 1024, "shared memory budget");
-    static bool attr2_set = false;
+    static NpPerDeviceOnce attr2_once;
+    bool& attr2_set = *attr2_once.slot();
     if (!attr2_set) {
       cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2);
       if (e != cudaSuccess) return 400 + (int)e;
@@ -853,7 +854,8 @@ NP_API int np_attn_fwd(const NpAttnFwdArgs* a, void* stream) {
   constexpr int NS = 2;   // softmax threads per row
   constexpr int SMEM = (1 + F_KST + F_VST) * TILE_BYTES + 8 * FB_COUNT + 8 + 16 + 2 * NS * 128 * 4 + 16;
   static_assert(SMEM <= 227 * 1024, "shared memory budget");
-  static bool attr_set = false;
+  static NpPerDeviceOnce attr_once;
+  bool& attr_set = *attr_once.slot();
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return 400 + (int)e;
@@ -1452,7 +1454,8 @@ NP_API int np_attn_bwd(const NpAttnBwdArgs* a, void* stream_) {
   constexpr int SMEM_DQ = BWD_TILES * TILE_BYTES + 8 * QB_COUNT + 16 + 16;
   constexpr int SMEM_DKV = BWD_TILES * TILE_BYTES + 8 * KB_COUNT + 16 + 2048 + 16;
   static_assert(SMEM_DKV <= 227 * 1024, "shared memory budget");
-  static bool attr_set = false;
+  static NpPerDeviceOnce attr_once;
+  bool& attr_set = *attr_once.slot();
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DQ);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd_dq_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DQ);

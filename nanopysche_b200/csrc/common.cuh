@@ -288,6 +288,16 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x))
 }  // namespace np
 
 // ------------------------------------------------------------------ host helpers
+// "Done once" guard for settings CUDA keeps per device (cudaFuncSetAttribute): a process that drives several
+// GPUs has to repeat them on each one, so the flag is per device ordinal, not per process.
+struct NpPerDeviceOnce {
+  bool done[64] = {};
+  bool* slot() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return &done[dev & 63];
+  }
+};
 typedef CUresult (*NpEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                     const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                     const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,

@@ -948,8 +948,9 @@ NP_API int np_rmsnorm_quant_fwd(const void* x, const void* res, const float* w, 
   CHECK_LAUNCH();
 }
 
-// The backward kernel followed by the column sum of its partials.
-static void launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* dres,
+// The backward kernel followed by the column sum of its partials. Returns 0, or 400 + the CUDA error of the
+// shared-memory attribute call (made once per device).
+static int launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* dres,
                                void* dx, float* dw, float* scratch, int rows, int cols, int accumulate_dw, int grid,
                                cudaStream_t s) {
 #define RB(V) rmsnorm_bwd_kernel<V><<<grid, NT, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, \
@@ -957,10 +958,13 @@ static void launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, co
 #define RBW(V) rmsnorm_bwd_warp_kernel<V><<<grid, NT, 8 * cols * sizeof(float), s>>>( \
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, \
       rows, cols)
-  static bool attr_set = false;
+  static NpPerDeviceOnce attr_once;
+  bool& attr_set = *attr_once.slot();
   if (!attr_set) {   // the warp-per-row kernels keep 8 x cols floats in shared memory (64 KB at 2048 columns)
-    cudaFuncSetAttribute(rmsnorm_bwd_warp_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2048 * 4);
-    cudaFuncSetAttribute(rmsnorm_bwd_warp_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 1024 * 4);
+    cudaError_t ea = cudaFuncSetAttribute(rmsnorm_bwd_warp_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2048 * 4);
+    if (ea == cudaSuccess)
+      ea = cudaFuncSetAttribute(rmsnorm_bwd_warp_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 1024 * 4);
+    if (ea != cudaSuccess) return 400 + (int)ea;
     attr_set = true;
   }
   if (cols == 2048) RBW(8);
@@ -971,6 +975,7 @@ static void launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, co
 #undef RB
 #undef RBW
   colsum_tall_kernel<<<(cols + 31) / 32, 256, 0, s>>>(scratch, dw, grid, cols, accumulate_dw);
+  return 0;
 }
 
 // Number of partial rows np_rmsnorm_bwd writes into its scratch for a given row count.
@@ -986,7 +991,9 @@ NP_API int np_rmsnorm_bwd(const void* dy, const void* x, const float* w, const f
   if (cols % 8 || cols > NT * 8 * 4) return 1;
   if (rows <= 0) return 0;
   const int grid = np_rmsnorm_bwd_parts(rows);
-  launch_rmsnorm_bwd(dy, x, w, rstd, dres, dx, dw, scratch, rows, cols, accumulate_dw, grid, (cudaStream_t)stream);
+  const int rc_attr = launch_rmsnorm_bwd(dy, x, w, rstd, dres, dx, dw, scratch, rows, cols, accumulate_dw, grid,
+                                         (cudaStream_t)stream);
+  if (rc_attr) return rc_attr;
   CHECK_LAUNCH();
 }
 
@@ -1184,6 +1191,8 @@ NP_API int np_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float* w,
   float* scratch = g_noalloc_ptr[dev];
   const int grid = np_rmsnorm_bwd_parts(rows);  // <= NP_NOALLOC_MAX_PARTS
   // every partial row [0, grid) x [0, cols) is written by the first kernel, so the column sum reads nothing stale
-  launch_rmsnorm_bwd(dy, x, w, rstd, dres, dx, dw, scratch, rows, cols, accumulate_dw, grid, (cudaStream_t)stream);
+  const int rc_attr = launch_rmsnorm_bwd(dy, x, w, rstd, dres, dx, dw, scratch, rows, cols, accumulate_dw, grid,
+                                         (cudaStream_t)stream);
+  if (rc_attr) return rc_attr;
   CHECK_LAUNCH();
 }

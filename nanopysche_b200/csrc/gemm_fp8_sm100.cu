@@ -278,7 +278,8 @@ NP_API int np_gemm_fp8_block(const NpFp8GemmArgs* args, void* stream) {
   p.row_dst = a.row_dst; p.peer_base = a.peer_base;
   p.done_counters = a.done_counters; p.done_expected = a.done_expected; p.done_flag_ptr = a.done_flag_ptr;
   constexpr int SMEM = STAGES * (BM * BK + BN * BK) + 1024 + 256;
-  static bool attr_set = false;
+  static NpPerDeviceOnce attr_once;
+  bool& attr_set = *attr_once.slot();
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return 400 + (int)e;

@@ -646,7 +646,8 @@ static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
   p.b_ready_flags = a.b_ready_flags; p.b_rows_per_flag = a.b_rows_per_flag;
 
   constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
-  static bool attr_set = false;
+  static NpPerDeviceOnce attr_once;
+  bool& attr_set = *attr_once.slot();
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return 400 + (int)e;

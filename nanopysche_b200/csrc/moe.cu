@@ -632,8 +632,21 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const DispatchParams p
         for (int j = 0; j < 8; ++j) am = fmaxf(am, fabsf(f[j]));
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-        const float scale = fmaxf(am, 1e-12f) / 448.f;
-        const float inv = 1.f / scale;
+        float scale, inv;
+        int e2 = -127;
+        if (p.quant == 2) {   // power-of-two scale (UE8M0): ceil(log2(am / 448))
+          if (am > 0.f) {
+            int ex;
+            const float mant = frexpf(__fdiv_rn(am, 448.f), &ex);
+            e2 = (mant == 0.5f) ? ex - 1 : ex;
+            e2 = max(-127, min(127, e2));
+          }
+          inv = exp2f((float)-e2);
+          scale = 0.f;
+        } else {
+          scale = fmaxf(am, 1e-12f) / 448.f;
+          inv = 1.f / scale;
+        }
         uint32_t lo = 0, hi = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -641,7 +654,17 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const DispatchParams p
           hi |= (uint32_t)__nv_cvt_float_to_fp8(f[4 + j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * j);
         }
         dst[v] = make_uint2(lo, hi);
-        if ((lane & 15) == 0) sdst[v >> 4] = scale;
+        if ((lane & 15) == 0) {
+          if (p.quant == 2) {
+            // exponent byte, four times, in the 512-byte chunk layout the block-scaled MMA reads (gemm_mxfp8_sm100.cu)
+            const int r = (int)(row & 127), kb = v >> 4, nkb = p.D >> 7;
+            uint8_t* sfb = reinterpret_cast<uint8_t*>(p.peer_scales[peer]);
+            *reinterpret_cast<uint32_t*>(sfb + ((row >> 7) * nkb + kb) * 512 + (r & 31) * 16 + (r >> 5) * 4) =
+                (uint32_t)(e2 + 127) * 0x01010101u;
+          } else {
+            sdst[v >> 4] = scale;
+          }
+        }
       }
     }
     if (p.write_meta && lane == 0) p.peer_row_dst[peer][row] = ret;
@@ -846,7 +869,8 @@ NP_API int np_capacity_scan(const int* indices, int T, int E, int K, int capacit
   if (T <= 0) return 0;
   const size_t smem = (size_t)T * K * 4 + (size_t)((T + 3) / 4) * 4;
   const int use_smem = smem <= 200 * 1024;
-  static bool attr_set = false;
+  static NpPerDeviceOnce attr_once;
+  bool& attr_set = *attr_once.slot();
   if (use_smem && !attr_set) {
     cudaError_t e = cudaFuncSetAttribute(capacity_scan_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e == cudaSuccess)

@@ -204,7 +204,8 @@ NP_API int np_transpose_1x128(const void* q, const float* s, void* qt, float* st
   if (M % 128 || N % 128) return 1;
   if (M <= 0 || N <= 0) return 0;
   constexpr int SMEM = 128 * 129 * 4;
-  static bool attr_set = false;
+  static NpPerDeviceOnce attr_once;
+  bool& attr_set = *attr_once.slot();
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(transpose_1x128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return 400 + (int)e;

@@ -44,9 +44,19 @@ class FaultTolerantCheckpointer:
             return None
         self.wait()
         rank, _ = self._rank_world()
-        cpu = lambda sd: {k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in sd.items()}  # noqa: E731
+        def cpu(obj):
+            """Deep copy to host memory: the background writer must not see tensors that later steps update (an
+            optimizer's state dict hands out its live moment buffers)."""
+            if torch.is_tensor(obj):
+                return obj.detach().to("cpu", copy=True)
+            if isinstance(obj, dict):
+                return {k: cpu(v) for k, v in obj.items()}
+            if isinstance(obj, (list, tuple)):
+                return type(obj)(cpu(v) for v in obj)
+            return obj
+
         msd = cpu(model.state_dict())
-        osd = optimizer.state_dict() if optimizer is not None else None
+        osd = cpu(optimizer.state_dict()) if optimizer is not None else None
         step_dir = os.path.join(self.save_dir, f"step_{step:06d}")
         tmp = os.path.join(self.save_dir, f".tmp_step_{step:06d}")
 
@@ -85,20 +95,34 @@ class FaultTolerantCheckpointer:
             self._thread.join()
             self._thread = None
 
-    def find_latest_checkpoint(self) -> Optional[str]:
+    def _loadable_steps(self) -> list:
+        """Steps (newest first) whose metadata and this rank's model shard both load."""
         rank, _ = self._rank_world()
+        out = []
         for d in sorted((d for d in os.listdir(self.save_dir) if d.startswith("step_")), reverse=True):
             p = os.path.join(self.save_dir, d)
             if not os.path.isfile(os.path.join(p, "metadata.json")):
                 continue
             try:
                 with open(os.path.join(p, "metadata.json")) as f:
-                    json.load(f)
+                    step = int(json.load(f)["step"])
                 torch.load(os.path.join(p, f"rank_{rank:04d}_model.pt"), map_location="cpu", weights_only=False)
             except Exception:  # noqa: BLE001  corrupt shard: fall back to the previous checkpoint
                 continue
-            return p
-        return None
+            out.append((step, p))
+        return out
+
+    def find_latest_checkpoint(self) -> Optional[str]:
+        """Newest checkpoint that EVERY rank can load: each rank lists the steps whose own shard is intact and the
+        ranks agree on the newest common one, so a truncated shard on one rank moves all ranks back together."""
+        mine = self._loadable_steps()
+        _, world = self._rank_world()
+        if world > 1:
+            lists = [None] * world
+            dist.all_gather_object(lists, [s for s, _ in mine])
+            common = set(lists[0]).intersection(*map(set, lists[1:]))
+            mine = [(s, p) for s, p in mine if s in common]
+        return mine[0][1] if mine else None
 
     def resume(self, model, optimizer=None, scheduler=None) -> int:
         self.wait()

@@ -148,6 +148,10 @@ class MxGemmArgs(C.Structure):
         ("M", c_int), ("N", c_int), ("K", c_int), ("out_f32", c_int), ("mode", c_int),
         ("mblk_group", c_void_p), ("mblk_rows", c_void_p), ("group_stride_b", c_ll),
         ("max_ctas", c_int),
+        ("ready_flags", c_void_p), ("mblk_flag", c_void_p), ("epoch", c_int), ("epoch_base", c_void_p),
+        ("flag_limit_ns", c_ull),
+        ("row_dst", c_void_p), ("peer_base", c_void_p),
+        ("done_counters", c_void_p), ("done_expected", c_void_p), ("done_flag_ptr", c_void_p),
     ]
 
 
@@ -187,6 +191,10 @@ def lib():
     _LIB.np_gemm_fp8_block.argtypes = [C.POINTER(Fp8GemmArgs), c_void_p]
     _LIB.np_gemm_mxfp8.argtypes = [C.POINTER(MxGemmArgs), c_void_p]
     _LIB.np_mx_quant.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p]
+    _LIB.np_flow_quant_act.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_void_p]
+    _LIB.np_mx_dequant.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p]
+    _LIB.np_flow_quant_weight.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                           c_void_p]
     _LIB.np_attn_fwd.argtypes = [C.POINTER(AttnFwdArgs), c_void_p]
     _LIB.np_attn_bwd.argtypes = [C.POINTER(AttnBwdArgs), c_void_p]
     _LIB.np_status_read.argtypes = [C.POINTER(c_int)]

@@ -63,6 +63,102 @@ def mx_quantize(x: torch.Tensor):
     return q, sf
 
 
+def mx_dequantize_bf16(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
+    """e4m3 ``[rows, K]`` + chunked exponent bytes -> bf16 (one kernel on CUDA)."""
+    rows, K = q.shape
+    if not q.is_cuda:
+        return mx_dequantize(q, sf).to(torch.bfloat16)
+    assert q.stride(1) == 1 and K % 128 == 0
+    out = torch.empty((rows, K), device=q.device, dtype=torch.bfloat16)
+    _lib.check(_lib.lib().np_mx_dequant(C.c_void_p(q.data_ptr()), C.c_longlong(q.stride(0)), C.c_void_p(sf.data_ptr()),
+                                        C.c_void_p(out.data_ptr()), C.c_longlong(K), rows, K,
+                                        C.c_void_p(_lib.stream())), "mx_dequant")
+    return out
+
+
+# ------------------------------------------------------------------------------------ 128-wide power-of-two blocks
+def _pow2_exp(am: torch.Tensor) -> torch.Tensor:
+    mant, ex = torch.frexp(am / 448.0)
+    e = torch.where(mant == 0.5, ex - 1, ex)
+    return torch.where(am > 0, e, torch.full_like(e, -127)).clamp(-127, 127)
+
+
+def flow_quantize_act_ref(x: torch.Tensor, swiglu: bool = False):
+    """PyTorch statement of ``flow_quantize_act``: one power-of-two scale per 1x128 block, stored as four equal
+    exponent bytes (the four 1x32 hardware blocks it spans)."""
+    xf = x.float()
+    if swiglu:
+        g, u = xf.chunk(2, dim=-1)
+        xf = torch.nn.functional.silu(g) * u
+    rows, K = xf.shape
+    xb = xf.view(rows, K // 128, 128)
+    e = _pow2_exp(xb.abs().amax(-1))
+    q = (xb * torch.exp2(-e.float()).unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn).view(rows, K)
+    sf = torch.zeros((sf_bytes(rows, K),), dtype=torch.uint8, device=x.device)
+    sf[sf_index(rows, K, x.device).reshape(-1)] = (e + 127).to(torch.uint8).repeat_interleave(4, dim=1).reshape(-1)
+    return q, sf
+
+
+def flow_quantize_act(x: torch.Tensor, swiglu: bool = False, out=None):
+    """bf16 ``[rows, K]`` -> ``(e4m3 [rows, K], exponent chunks)`` with 1x128 power-of-two scales (FP8-Flow-MoE
+    activations in the form the block-scaled tensor-core MMA consumes). ``swiglu``: ``x`` is ``[rows, 2K]`` =
+    ``[gate | up]`` and ``silu(gate) * up`` is what gets quantised (the reference's ``fused_swiglu_quantize``)."""
+    if not x.is_cuda:
+        return flow_quantize_act_ref(x, swiglu)
+    rows = x.shape[0]
+    K = x.shape[1] // 2 if swiglu else x.shape[1]
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and K % 128 == 0
+    if out is None:
+        q = torch.empty((rows, K), device=x.device, dtype=torch.float8_e4m3fn)
+        sf = torch.zeros((sf_bytes(rows, K),), dtype=torch.uint8, device=x.device)
+    else:
+        q, sf = out
+    _lib.check(_lib.lib().np_flow_quant_act(C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)),
+                                            C.c_void_p(q.data_ptr()), C.c_longlong(q.stride(0)),
+                                            C.c_void_p(sf.data_ptr()), rows, K, int(swiglu),
+                                            C.c_void_p(_lib.stream())), "flow_quant_act")
+    return q, sf
+
+
+def flow_quantize_weight_ref(w: torch.Tensor, experts: int = 1, transpose: bool = False):
+    R, Cc = w.shape[0] // experts, w.shape[1]
+    wf = w.float().view(experts, R, Cc)
+    if transpose:
+        wf = wf.transpose(1, 2).contiguous()
+        R, Cc = Cc, R
+    blk = wf.view(experts, R // 128, 128, Cc // 128, 128)
+    e = _pow2_exp(blk.abs().amax(dim=(2, 4)))                                   # [E, R/128, C/128]
+    q = (blk * torch.exp2(-e.float())[:, :, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+    q = q.view(experts * R, Cc)
+    sf = (e + 127).to(torch.uint8).reshape(-1, 1).expand(-1, SF_CHUNK).reshape(-1).contiguous()
+    return q, sf
+
+
+def flow_quantize_weight(w: torch.Tensor, experts: int = 1, transpose: bool = False, out=None, out_rows: int = 0,
+                         out_row0: int = 0):
+    """``experts`` stacked ``[R, C]`` bf16 matrices -> e4m3 with one power-of-two scale per 128x128 block
+    (FP8-Flow-MoE weights); ``transpose`` writes every matrix as ``[C, R]`` so that a GEMM can contract over R.
+    With ``out=(q, sf)``, ``out_rows`` and ``out_row0`` expert ``e`` is written to rows ``e * out_rows + out_row0`` of a
+    larger output (several weights stacked per expert)."""
+    if not w.is_cuda:
+        assert out is None
+        return flow_quantize_weight_ref(w, experts, transpose)
+    assert w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[0] % experts == 0
+    R, Cc = w.shape[0] // experts, w.shape[1]
+    assert R % 128 == 0 and Cc % 128 == 0
+    oshape = (experts * Cc, R) if transpose else (experts * R, Cc)
+    if out is None:
+        q = torch.empty(oshape, device=w.device, dtype=torch.float8_e4m3fn)
+        sf = torch.empty((sf_bytes(oshape[0], oshape[1]),), dtype=torch.uint8, device=w.device)
+    else:
+        q, sf = out
+    _lib.check(_lib.lib().np_flow_quant_weight(C.c_void_p(w.data_ptr()), C.c_void_p(q.data_ptr()),
+                                               C.c_void_p(sf.data_ptr()), experts, R, Cc, int(transpose),
+                                               int(out_rows), int(out_row0), C.c_void_p(_lib.stream())),
+               "flow_quant_weight")
+    return q, sf
+
+
 def mx_dequantize(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
     rows, K = q.shape
     e = sf[sf_index(rows, K, q.device).reshape(-1)].view(rows, K // 32).float() - 127.0
@@ -84,24 +180,30 @@ def gemm_mxfp8_ref(aq, sfa, bq, sfb, mblk_group=None, rows_per_group: int = 0, o
 def gemm_mxfp8(aq: torch.Tensor, sfa: torch.Tensor, bq: torch.Tensor, sfb: torch.Tensor, *,
                out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
                mblk_group: Optional[torch.Tensor] = None, mblk_rows: Optional[torch.Tensor] = None,
-               rows_per_group: int = 0) -> torch.Tensor:
+               rows_per_group: int = 0, fill: Optional[dict] = None) -> torch.Tensor:
+    """``fill``: extra ``MxGemmArgs`` fields (arrival-flag wait, per-row destination table and completion counters of
+    the fused expert-parallel path; with ``row_dst`` the output goes to peer buffers and ``out`` may be None)."""
     if not aq.is_cuda:
         return gemm_mxfp8_ref(aq, sfa, bq, sfb, mblk_group, rows_per_group, out_dtype)
     M, K = aq.shape
     N = rows_per_group if mblk_group is not None else bq.shape[0]
     assert K % 128 == 0 and N % 128 == 0 and bq.shape[0] % 128 == 0 and aq.stride(1) == 1 and bq.stride(1) == 1
     assert sfa.numel() >= sf_bytes(M, K) and sfb.numel() >= sf_bytes(bq.shape[0], K)
-    if out is None:
+    push = bool(fill and fill.get("row_dst"))
+    if out is None and not push:
         out = torch.empty((M, N), device=aq.device, dtype=out_dtype)
     a = _lib.MxGemmArgs()
-    a.A, a.B, a.C, a.sfa, a.sfb = aq.data_ptr(), bq.data_ptr(), out.data_ptr(), sfa.data_ptr(), sfb.data_ptr()
-    a.lda, a.ldb, a.ldc = aq.stride(0), bq.stride(0), out.stride(0)
+    a.A, a.B, a.sfa, a.sfb = aq.data_ptr(), bq.data_ptr(), sfa.data_ptr(), sfb.data_ptr()
+    a.C = out.data_ptr() if out is not None else None
+    a.lda, a.ldb, a.ldc = aq.stride(0), bq.stride(0), (out.stride(0) if out is not None else N)
     a.a_rows, a.b_rows = aq.shape[0], bq.shape[0]
     a.M, a.N, a.K = M, N, K
-    a.out_f32 = int(out.dtype == torch.float32)
+    a.out_f32 = int(out is not None and out.dtype == torch.float32)
     if mblk_group is not None:
         a.mode, a.mblk_group, a.group_stride_b = 1, mblk_group.data_ptr(), rows_per_group
         a.mblk_rows = mblk_rows.data_ptr() if mblk_rows is not None else None
+    for k, v in (fill or {}).items():
+        setattr(a, k, v)
     _lib.check(_lib.lib().np_gemm_mxfp8(C.byref(a), C.c_void_p(_lib.stream())), "gemm_mxfp8")
     return out
 

@@ -121,9 +121,9 @@ class FusedMoERuntime:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         row_bytes = self.rows_total * d_model * 2
         slot_bytes = tokens * top_k * d_model * 2
-        self.fp8 = bool(fp8) and d_model % 256 == 0 and hidden % 128 == 0
+        self.fp8 = bool(fp8) and d_model % 256 == 0 and hidden % 128 == 0   # 128-wide scale blocks on both GEMMs
         need = n_layers * (row_bytes + slot_bytes) + row_bytes + slot_bytes + self.rows_total * 8 + (1 << 20)
-        if self.fp8:  # e4m3 rows + 1x128 scales per layer instead of... in addition to the bf16 buffers
+        if self.fp8:  # e4m3 rows + their exponent chunks (512 bytes per 128 rows x 128 columns) per layer
             need += n_layers * (self.rows_total * d_model + self.rows_total * (d_model // 128) * 4 + 8192)
         self.heap = SymmetricHeap(need, group, self.device)
         h = self.heap
@@ -132,7 +132,8 @@ class FusedMoERuntime:
         self.recv_xq = self.recv_xs = self.p_recv_xq = self.p_recv_xs = None
         if self.fp8:
             self.recv_xq = [h.alloc((self.rows_total, d_model), torch.uint8) for _ in range(n_layers)]
-            self.recv_xs = [h.alloc((self.rows_total, d_model // 128), torch.float32) for _ in range(n_layers)]
+            # exponent bytes of the 1x128 blocks in the chunk layout of the block-scaled MMA: 4 bytes per row and block
+            self.recv_xs = [h.alloc((self.rows_total * (d_model // 128) * 4,), torch.uint8) for _ in range(n_layers)]
             self.p_recv_xq = [h.ptr_array(t) for t in self.recv_xq]
             self.p_recv_xs = [h.ptr_array(t) for t in self.recv_xs]
         self.recv_g = h.alloc((self.rows_total, d_model), torch.bfloat16)
@@ -160,6 +161,8 @@ class FusedMoERuntime:
         self.dispatch_ctr = torch.zeros(1, device=self.device, dtype=torch.int32)
         self.layer_of: dict[int, int] = {}
         self.max_ctas_dispatch = max_ctas_dispatch
+        self._wq: dict[int, tuple] = {}        # per layer: quantised expert weights (buffers reused every step)
+        self._wq_valid: set[int] = set()       # layers whose quantised weights match the current bf16 weights
         # DeepSeek-V3 auxiliary-loss-free balancing, kept on the device: per-layer assignment counts of the step and
         # one [layers, experts] tensor that every router's ``score_bias`` is a row of (``bind_router_bias``)
         h.reserve_allreduce(max(64, n_layers * num_experts))
@@ -207,6 +210,28 @@ class FusedMoERuntime:
 
     def end_step(self):
         self.heap.end_step()
+        self._wq_valid.clear()   # the optimizer has written new weights
+
+    def quantised_weights(self, layer: int, w1, w3, w2):
+        """e4m3 copies of a layer's expert weights with 128x128 power-of-two block scales, made once per optimizer
+        step (every forward of a gradient-accumulation step reuses them): ``[gate; up]`` stacked per expert for a
+        single gate|up GEMM, and the down projection transposed per expert to ``[D, H]``."""
+        from .gemm_mxfp8 import flow_quantize_weight, sf_bytes
+
+        E_l, H, D = self.E_local, self.H, self.D
+        if layer not in self._wq:
+            dev = self.device
+            self._wq[layer] = (torch.empty((E_l * 2 * H, D), device=dev, dtype=torch.float8_e4m3fn),
+                               torch.empty((sf_bytes(E_l * 2 * H, D),), device=dev, dtype=torch.uint8),
+                               torch.empty((E_l * D, H), device=dev, dtype=torch.float8_e4m3fn),
+                               torch.empty((sf_bytes(E_l * D, H),), device=dev, dtype=torch.uint8))
+        w13q, s13, w2q, s2 = self._wq[layer]
+        if layer not in self._wq_valid:
+            flow_quantize_weight(w1.detach(), E_l, out=(w13q, s13), out_rows=2 * H, out_row0=0)
+            flow_quantize_weight(w3.detach(), E_l, out=(w13q, s13), out_rows=2 * H, out_row0=H)
+            flow_quantize_weight(w2.detach(), E_l, transpose=True, out=(w2q, s2))
+            self._wq_valid.add(layer)
+        return w13q, s13, w2q, s2
 
     # -- kernels -------------------------------------------------------------------------------------
     def dispatch(self, x2, indices, slot_pos, counts_kept, scale, p_rows, epoch, p_scales=None):
@@ -216,7 +241,7 @@ class FusedMoERuntime:
         a.slot_scale = scale.data_ptr() if scale is not None else None
         a.T, a.K, a.D, a.E, a.E_local, a.n_ranks, a.my_rank = self.T, self.K, self.D, self.E, self.E_local, self.N, \
             self.rank
-        a.region_rows, a.quant = self.R, int(p_scales is not None)
+        a.region_rows, a.quant = self.R, (2 if p_scales is not None else 0)   # 2: e4m3 + power-of-two 1x128 scales
         a.peer_rows, a.peer_scales = p_rows.data_ptr(), (p_scales.data_ptr() if p_scales is not None else None)
         a.peer_row_dst, a.peer_mblk_rows = self.p_row_dst.data_ptr(), self.p_mblk_rows.data_ptr()
         a.peer_src_blocks, a.peer_flags = self.p_src_blocks.data_ptr(), self.p_dispatch_flags.data_ptr()
@@ -277,9 +302,10 @@ class FusedMoERuntime:
         _lib.check(_lib.lib().np_gemm_bf16(C.byref(g), C.c_void_p(_lib.stream())), "grouped_gemm")
         return out
 
-    def grouped_gemm_fp8(self, aq, sa, bq, sb, *, N, out=None, wait_epoch=0, push_ptrs=None, push_epoch=0):
-        """Row-grouped block-scaled fp8 GEMM over the receive-buffer layout (B K-major, N rows per expert)."""
-        from .gemm_fp8 import gemm_fp8_block
+    def grouped_gemm_fp8(self, aq, sfa, bq, sfb, *, N, out=None, wait_epoch=0, push_ptrs=None, push_epoch=0):
+        """Row-grouped e4m3 GEMM over the receive-buffer layout on the block-scaled tensor-core path (B K-major,
+        ``N`` rows per expert; scales as exponent chunks)."""
+        from .gemm_mxfp8 import gemm_mxfp8
 
         fill = {"mblk_flag": self.mblk_flag.data_ptr(), "epoch_base": self.heap.epoch_base.data_ptr()}
         if wait_epoch:
@@ -289,8 +315,8 @@ class FusedMoERuntime:
             fill.update(row_dst=self.row_dst.data_ptr(), peer_base=push_ptrs.data_ptr(),
                         done_counters=self.done_counters.data_ptr(), done_expected=self.src_blocks.data_ptr(),
                         done_flag_ptr=self.p_done_flag.data_ptr(), epoch=push_epoch)
-        return gemm_fp8_block(aq, sa, bq, sb, out=out, mblk_group=self.mblk_group, mblk_rows=self.mblk_rows,
-                              rows_per_group=N, fill=fill)
+        return gemm_mxfp8(aq, sfa, bq, sfb, out=out, mblk_group=self.mblk_group, mblk_rows=self.mblk_rows,
+                          rows_per_group=N, fill=fill)
 
     def grouped_wgrad(self, A, Bm, w: torch.Tensor, *, M, N):
         """dW[g] (+)= A[rows of g]^T @ B[rows of g] for every local expert g (mode 2), into ``main_grad``
@@ -333,21 +359,18 @@ class _FusedMoE(torch.autograd.Function):
         e1 = rt.next_epoch()
         gu = torch.empty((rt.rows_total, 2 * H), device=dev, dtype=torch.bfloat16)
         if rt.fp8:
-            # FP8-Flow-MoE forward: rows travel as e4m3 + 1x128 scales, both expert GEMMs run on the fp8
-            # tensor-core path with fp32 per-block scaling, SwiGLU and re-quantisation are one kernel
-            from fp8_flow_moe import ops as fops
+            # FP8-Flow-MoE forward: rows travel as e4m3 with 1x128 power-of-two scales (quantised inside the dispatch
+            # kernel), the expert weights are e4m3 with 128x128 scales (made once per optimizer step), both expert
+            # GEMMs run on the block-scaled tcgen05 path with the scaling done by the tensor core: one gate|up GEMM,
+            # SwiGLU + re-quantisation in one pass, and the down GEMM pushing rows back to their sources
+            from .gemm_mxfp8 import flow_quantize_act
 
-            E_l = rt.E_local
-            w1q, s1 = fops.quantize_weight_blockwise(w1.detach())
-            w3q, s3 = fops.quantize_weight_blockwise(w3.detach())
-            w2t = w2.detach().view(E_l, H, D).transpose(1, 2).contiguous().view(E_l * D, H)
-            w2q, s2 = fops.quantize_weight_blockwise(w2t)
+            w13q, s13, w2q, s2 = rt.quantised_weights(layer, w1, w3, w2)
             rt.dispatch(x2, indices32, slot_pos, counts_kept, None, rt.p_recv_xq[layer], e1,
                         p_scales=rt.p_recv_xs[layer])
             xq, xs = rt.recv_xq[layer].view(torch.float8_e4m3fn), rt.recv_xs[layer]
-            rt.grouped_gemm_fp8(xq, xs, w1q, s1, N=H, out=gu[:, :H], wait_epoch=e1)
-            rt.grouped_gemm_fp8(xq, xs, w3q, s3, N=H, out=gu[:, H:], wait_epoch=e1)
-            hq, hs = fops.fused_silu_multiply_quantize(gu[:, :H], gu[:, H:])
+            rt.grouped_gemm_fp8(xq, xs, w13q, s13, N=2 * H, out=gu, wait_epoch=e1)
+            hq, hs = flow_quantize_act(gu, swiglu=True)
             rt.grouped_gemm_fp8(hq, hs, w2q, s2, N=D, push_ptrs=rt.p_ret_y[layer], push_epoch=e1)
         else:
             rt.dispatch(x2, indices32, slot_pos, counts_kept, None, rt.p_recv_x[layer], e1)
@@ -401,9 +424,9 @@ class _FusedMoE(torch.autograd.Function):
         del dh
         dg, du = dgu[:, :H], dgu[:, H:]
         if rt.fp8:  # the rows arrived as e4m3: dequantise once for the (bf16) weight-gradient GEMMs
-            from fp8_flow_moe import ops as fops
+            from .gemm_mxfp8 import mx_dequantize_bf16
 
-            xr = fops.dequantize_from_fp8(rt.recv_xq[layer].view(torch.float8_e4m3fn), rt.recv_xs[layer])
+            xr = mx_dequantize_bf16(rt.recv_xq[layer].view(torch.float8_e4m3fn), rt.recv_xs[layer])
         else:
             xr = rt.recv_x[layer]
         dw1 = rt.grouped_wgrad(dg, xr, w1, M=H, N=D)

@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 import torch
 
+import torch.distributed as dist
 from conftest import run_distributed
 from nanopysche_b200.checkpoint.distributed import (CheckpointConfig, DistributedCheckpointer,
                                                     IncrementalCheckpointer, PinnedMemoryStager, PlanCache)
@@ -396,3 +397,24 @@ def test_profiler_callback_window(tmp_path):
                         save_interval=0, dtype=torch.float32, vocab_size=64)
     Trainer(tc, m, opt, None, None, [prof]).fit()
     assert any(f.endswith(".chrome_trace.json.gz") for f in os.listdir(tmp_path))
+
+
+def _ft_resume_worker(rank, world, save_dir):
+    """Rank 1's newest shard is truncated: both ranks must fall back to the older step together."""
+    from nanopysche_b200.fault_tolerance.checkpoint import FaultTolerantCheckpointer
+
+    m = tiny_model()
+    ck = FaultTolerantCheckpointer(save_dir, save_interval=1, keep_last_n=5)
+    ck.save(1, m, force=True)
+    ck.save(2, m, force=True)
+    dist.barrier()
+    if rank == 1:
+        with open(os.path.join(save_dir, "step_000002", "rank_0001_model.pt"), "wb") as f:
+            f.write(b"trunc")
+    dist.barrier()
+    step = ck.resume(tiny_model())
+    return step
+
+
+def test_fault_tolerant_resume_agrees_across_ranks(tmp_path):
+    assert run_distributed(_ft_resume_worker, 2, str(tmp_path)) == [1, 1]
