@@ -57,6 +57,9 @@ def build_parser() -> argparse.ArgumentParser:
     common.add_argument("--capacity-factor", type=float, default=None)
     common.add_argument("--moe-keep-dense-ffn", action="store_true")
     common.add_argument("--tp-size", type=int, default=1)
+    common.add_argument("--async-tp", action="store_true",
+                        help="tensor parallelism with the all-gather / reduce-scatter fused into the GEMM kernels "
+                             "(sequence-parallel layout over NVLink peer memory)")
     common.add_argument("--pp-size", type=int, default=1)
     common.add_argument("--pp-schedule", default="1F1B", help="GPipe | 1F1B | ZBVZeroBubble | Interleaved1F1B | ...")
     common.add_argument("--pp-microbatches", type=int, default=0, help="microbatches per step (0: one per PP rank)")
@@ -205,10 +208,14 @@ def _maybe_parallelize_model(model, args, device):
                                 ep_size=args.ep_size, device_type=device.type, replace=True)
     model = parallelize_model(
         model, world_mesh=mesh, device=device,
-        tp_config=TensorParallelConfig(args.tp_size) if args.tp_size > 1 else None,
+        tp_config=TensorParallelConfig(args.tp_size, enable_async=getattr(args, "async_tp", False),
+                                       sequence_parallel=getattr(args, "async_tp", False))
+        if args.tp_size > 1 else None,
         cp_config=ContextParallelConfig(args.cp_size, ring=not args.ulysses, ulysses=args.ulysses)
         if args.cp_size > 1 else None,
-        pp_config=PipelineParallelConfig(args.pp_size) if args.pp_size > 1 else None,
+        pp_config=PipelineParallelConfig(args.pp_size, schedule=getattr(args, "pp_schedule", "1F1B"),
+                                         num_microbatches=getattr(args, "pp_microbatches", 0) or None)
+        if args.pp_size > 1 else None,
         dp_config=DataParallelConfig(param_dtype=_resolve_dtype(args),
                                      backend=getattr(args, "fsdp_backend", "auto")) if args.fsdp else None,
         moe_fp8_recipe=args.fp8_recipe, moe_fp8_gemm_threshold=args.fp8_gemm_threshold,
@@ -221,12 +228,17 @@ def _build_optimizer_and_scheduler(model, args, tokens_per_rank: int, max_steps:
     from .engine import prepare_training
     from .train.scheduler import CosineWithWarmup
 
-    if getattr(model, "_pp_enabled", False):
-        # a pipeline stage clips by the norm over all stages (trainer), so it takes the plain optimizer
-        opt = torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.1, betas=(0.9, 0.95))
-        return opt, CosineWithWarmup(opt, warmup_steps=min(10, max(max_steps // 10, 1)), max_steps=max_steps)
+    pp = getattr(model, "_pp_enabled", False)
+    if pp:
+        # tokens per forward call of a stage: one pipeline microbatch
+        m = getattr(args, "pp_microbatches", 0) or args.pp_size
+        tokens_per_rank = tokens_per_rank // max(m, 1)
     opt, arena = prepare_training(model, tokens_per_rank=tokens_per_rank, lr=args.lr, weight_decay=0.1,
                                   betas=(0.9, 0.95))
+    if pp and arena is not None:
+        # the fused optimizer clips by the norm over all pipeline stages: one extra scalar all-reduce on the PP group
+        opt.norm_groups = [model._pp_group]
+        opt.norm_copies = 2.0 if getattr(model, "is_dualpipe", False) else 1.0
     sched = CosineWithWarmup(opt, warmup_steps=min(10, max(max_steps // 10, 1)), max_steps=max_steps)
     return opt, sched
 
@@ -247,6 +259,8 @@ def cmd_train(args) -> int:
     model, f_opt, f_sched = build_model(ctx, factory_spec=args.model_factory)
     model = model.to(device)
     model, mesh = _maybe_parallelize_model(model, args, device)
+    if getattr(args, "compile", False) and mesh is None and hasattr(model, "apply_compile"):
+        model.apply_compile()
     dp = max(world // (args.tp_size * args.pp_size * args.cp_size), 1)
     if f_opt is None:
         opt, sched = _build_optimizer_and_scheduler(model, args, args.batch_size * args.seq_len // args.cp_size,

@@ -195,11 +195,13 @@ __global__ void __launch_bounds__(256) zero_adamw_bcast_kernel(float* __restrict
                                                                PeerPtrs w16, int n, long long lo, long long cnt,
                                                                float lr, float b1, float b2, float eps, float wd,
                                                                float bc1, float bc2, const float* __restrict__ gscale,
-                                                               const float* __restrict__ hyper) {
+                                                               const float* __restrict__ hyper, long long slice,
+                                                               long long bstride) {
   np::CommSpan span(n > 1);
   const float gs = gscale ? gscale[0] : 1.f;
   if (hyper) { lr = hyper[0]; bc1 = hyper[1]; bc2 = hyper[2]; }
   const long long nvec = cnt >> 2;
+  const long long svec = slice >> 2;   // bucketed layout: shard element 4i lives at flat (4i / slice) * bstride + lo + 4i % slice
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
     float4 pp = reinterpret_cast<float4*>(p)[i];
@@ -218,8 +220,111 @@ __global__ void __launch_bounds__(256) zero_adamw_bcast_kernel(float* __restrict
     reinterpret_cast<float4*>(m)[i] = mm;
     reinterpret_cast<float4*>(v)[i] = vv;
     const uint2 packed = make_uint2(np::pack_bf16(pp.x, pp.y), np::pack_bf16(pp.z, pp.w));
+    const long long fv = svec > 0 ? (i / svec) * (bstride >> 2) + (i % svec) : i;   // position in float4 units after lo
     for (int r = 0; r < n; ++r)
-      reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(w16.p[r]) + lo)[i] = packed;
+      reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(w16.p[r]) + lo)[fv] = packed;
+  }
+}
+
+// Copy-engine form of the overlapped reduce-scatter. bucket_sync_kernel (one warp) announces "bucket b is final on
+// this rank" to every rank and waits for everyone's announcement; the host then queues one cudaMemcpyAsync per peer
+// (peer gradient slice -> local staging), which the copy engines move over NVLink without occupying an SM, so the
+// tensor-core kernels of the backward pass keep all SMs to themselves. After the backward pass
+// zero_reduce_staged_kernel sums the local slice and the staged peer slices at HBM speed.
+__global__ void bucket_sync_kernel(PeerPtrs flags, int flag_off, int my_rank, int n, int epoch,
+                                   const int* __restrict__ epoch_base, unsigned long long limit_ns) {
+  const int t = threadIdx.x;
+  const int ep = epoch + (epoch_base ? *epoch_base : 0);
+  if (t < n) {
+    __threadfence_system();
+    np::st_release_sys(reinterpret_cast<int*>(flags.p[t]) + flag_off + my_rank, ep);
+    np::wait_flag_ge(reinterpret_cast<int*>(flags.p[my_rank]) + flag_off + t, ep, limit_ns, KID_BARRIER, 300 + t);
+  }
+}
+
+// gshard[i] = scale * (local[flat(i)] + sum over the staged peer copies of element i), i over this rank's compact
+// shard (slices of `slice` elements, slice k at flat offset lo + k * bstride in the local gradient buffer; the staged
+// copies already use the compact order, `cnt` elements per peer). partial[block] = sum of squares of the CTA's part.
+__global__ void __launch_bounds__(256) zero_reduce_staged_kernel(const float* __restrict__ local, long long lo,
+                                                                 long long slice, long long bstride,
+                                                                 const float* __restrict__ staged, int n_staged,
+                                                                 long long cnt, float scale, float* __restrict__ gshard,
+                                                                 float* __restrict__ partial) {
+  __shared__ float red[32];
+  float ss = 0.f;
+  const long long nvec = cnt >> 2, svec = slice >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long fv = (i / svec) * (bstride >> 2) + (i % svec);
+    float4 acc = reinterpret_cast<const float4*>(local + lo)[fv];
+    for (int k = 0; k < n_staged; ++k) {
+      const float4 g = reinterpret_cast<const float4*>(staged + (size_t)k * cnt)[i];
+      acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+    }
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    reinterpret_cast<float4*>(gshard)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  ss = np::warp_sum(ss);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = ss;
+  __syncthreads();
+  if (w == 0) {
+    float t = l < 8 ? red[l] : 0.f;
+    t = np::warp_sum(t);
+    if (l == 0) partial[blockIdx.x] = t;
+  }
+}
+
+// One bucket of the overlapped gradient reduce-scatter. Launched on a side stream as soon as this rank's backward
+// pass has produced every gradient of the bucket: release "bucket b is final on rank r" on every rank, wait (bounded)
+// until all n ranks have said so, then sum this rank's slice of the bucket over all ranks' gradient buffers (peer
+// loads), scale it, store it into the compact shard buffer and add its sum of squares to *sumsq. A few CTAs are
+// enough: the transfer only has to finish before the end of the backward pass it runs under.
+constexpr int KID_ZERO_BUCKET = 21;
+__global__ void __launch_bounds__(256) zero_reduce_bucket_kernel(PeerPtrs grads, PeerPtrs flags, int flag_off,
+                                                                 int my_rank, int n, int epoch,
+                                                                 const int* __restrict__ epoch_base,
+                                                                 unsigned long long limit_ns, long long lo,
+                                                                 long long cnt, float scale, float* __restrict__ gshard,
+                                                                 float* __restrict__ sumsq) {
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  np::CommSpan span(n > 1);
+  const int ep = epoch + (epoch_base ? *epoch_base : 0);
+  if (blockIdx.x == 0 && (int)threadIdx.x < n) {
+    __threadfence_system();
+    np::st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + flag_off + my_rank, ep);
+  }
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < n &&
+      !np::wait_flag_ge(reinterpret_cast<int*>(flags.p[my_rank]) + flag_off + threadIdx.x, ep, limit_ns, KID_ZERO_BUCKET,
+                        threadIdx.x))
+    s_ok = 0;
+  __syncthreads();
+  if (!s_ok) return;
+  float ss = 0.f;
+  const long long nvec = cnt >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < n; ++r) {
+      const float4 g = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo)[i];
+      acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+    }
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    reinterpret_cast<float4*>(gshard)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  ss = np::warp_sum(ss);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = ss;
+  __syncthreads();
+  if (w == 0) {
+    float t = l < 8 ? red[l] : 0.f;
+    t = np::warp_sum(t);
+    if (l == 0) atomicAdd(sumsq, t);
   }
 }
 
@@ -410,16 +515,62 @@ NP_API int np_zero_reduce(void* const* grad_ptrs, int n, long long lo, long long
   CHECK_LAUNCH();
 }
 
+// Overlapped form of np_zero_reduce for one bucket (see zero_reduce_bucket_kernel). flag_ptrs[r]: rank r's bucket
+// flag array (n ints per bucket); lo: flat element offset of this rank's slice of the bucket; cnt: slice length;
+// gshard: destination inside the compact shard buffer; sumsq: one float that the kernel adds to.
+NP_API int np_zero_reduce_bucket(void* const* grad_ptrs, void* const* flag_ptrs, int bucket, int my_rank, int n,
+                                 int epoch, const int* epoch_base, unsigned long long limit_ns, long long lo,
+                                 long long cnt, float scale, float* gshard, float* sumsq, int ctas, void* stream) {
+  if (n > MAX_PEERS || (lo & 3) || (cnt & 3) || ctas <= 0) return 1;
+  PeerPtrs g, f;
+  for (int i = 0; i < n; ++i) { g.p[i] = grad_ptrs[i]; f.p[i] = flag_ptrs[i]; }
+  zero_reduce_bucket_kernel<<<ctas, 256, 0, (cudaStream_t)stream>>>(g, f, bucket * n, my_rank, n, epoch, epoch_base,
+                                                                   limit_ns ? limit_ns : NP_WAIT_LIMIT_NS, lo, cnt,
+                                                                   scale, gshard, sumsq);
+  CHECK_LAUNCH();
+}
+
+NP_API int np_bucket_sync(void* const* flag_ptrs, int bucket, int my_rank, int n, int epoch, const int* epoch_base,
+                          unsigned long long limit_ns, void* stream) {
+  if (n > MAX_PEERS || n > 32) return 1;
+  PeerPtrs f;
+  for (int i = 0; i < n; ++i) f.p[i] = flag_ptrs[i];
+  bucket_sync_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, bucket * n, my_rank, n, epoch, epoch_base,
+                                                         limit_ns ? limit_ns : NP_WAIT_LIMIT_NS);
+  CHECK_LAUNCH();
+}
+
+// Stream-ordered copy between any two device addresses of the unified address space (a peer's buffer mapped through
+// CUDA IPC included): one plain cudaMemcpyAsync, executed by a copy engine.
+NP_API int np_memcpy_async(void* dst, const void* src, unsigned long long bytes, void* stream) {
+  if (bytes == 0) return 0;
+  cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, (cudaStream_t)stream);
+  return e == cudaSuccess ? 0 : 500 + (int)e;
+}
+
+// partial: fp32 [np_zero_parts()]; see zero_reduce_staged_kernel.
+NP_API int np_zero_reduce_staged(const float* local, long long lo, long long slice, long long bstride,
+                                 const float* staged, int n_staged, long long cnt, float scale, float* gshard,
+                                 float* partial, void* stream) {
+  if ((lo & 3) || (cnt & 3) || (slice & 3) || (bstride & 3) || slice <= 0) return 1;
+  zero_reduce_staged_kernel<<<np_zero_parts(), 256, 0, (cudaStream_t)stream>>>(local, lo, slice, bstride, staged,
+                                                                              n_staged, cnt, scale, gshard, partial);
+  CHECK_LAUNCH();
+}
+
+// slice > 0: the shard is `cnt / slice` slices of `slice` elements, slice k at flat offset lo + k * bstride (the
+// bucketed layout of the overlapped reduce-scatter); slice == 0: one contiguous range [lo, lo + cnt).
 NP_API int np_zero_adamw_bcast(float* p, const float* g, float* m, float* v, void* const* w16_ptrs, int n,
                                long long lo, long long cnt, float lr, float b1, float b2, float eps, float wd,
-                               int step, const float* gscale, const float* hyper, void* stream) {
-  if (n > MAX_PEERS || (lo & 3) || (cnt & 3)) return 1;
+                               int step, const float* gscale, const float* hyper, long long slice, long long bstride,
+                               void* stream) {
+  if (n > MAX_PEERS || (lo & 3) || (cnt & 3) || (slice & 3) || (bstride & 3)) return 1;
   if (cnt <= 0) return 0;
   PeerPtrs w;
   for (int i = 0; i < n; ++i) w.p[i] = w16_ptrs[i];
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
   zero_adamw_bcast_kernel<<<148 * 4, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, w, n, lo, cnt, lr, b1, b2, eps, wd,
-                                                                    bc1, bc2, gscale, hyper);
+                                                                    bc1, bc2, gscale, hyper, slice, bstride);
   CHECK_LAUNCH();
 }
 

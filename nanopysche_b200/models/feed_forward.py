@@ -60,9 +60,9 @@ class FeedForward(nn.Module):
             gu = torch.cat([gemm_ops.linear(x, self.w1.weight), gemm_ops.linear(x, self.w3.weight)], dim=-1)
             h = act_ops.glu(gu, act)
         else:
-            g = F.linear(x, self.w1.weight, self.w1.bias)
+            g = gemm_ops.linear(x, self.w1.weight, self.w1.bias)
             a = F.silu(g) if act == "silu" else F.gelu(g, approximate="tanh")
-            h = a * F.linear(x, self.w3.weight, self.w3.bias)
+            h = a * gemm_ops.linear(x, self.w3.weight, self.w3.bias)
         out = gemm_ops.linear(h, self.w2.weight, None)
         out = differentiable_all_reduce(out, self._tp_group, self._tp_size)
         if self.w2.bias is not None:

@@ -372,7 +372,14 @@ class Transformer(nn.Module):
         self._fsdp_enabled = True
 
     def apply_compile(self):
-        """Kept for interface parity: the hot path is hand-written kernels, nothing is traced."""
+        """Kept for interface parity: the hot path is hand-written kernels, nothing is traced. Says so once, so that
+        ``--compile`` is not mistaken for a speed-up."""
+        if not self._compile_enabled:
+            import logging
+
+            logging.getLogger(__name__).warning(
+                "apply_compile / --compile is a no-op here: the blocks already run as hand-written sm_100a kernels "
+                "(and as plain PyTorch ops on CPU); nothing is traced or compiled")
         self._compile_enabled = True
 
     def apply_activation_checkpointing(self, mode: str = "full", block_interval: Optional[int] = None):

@@ -28,7 +28,8 @@ class _Embedding(torch.autograd.Function):
         w = ctx.weight
         D = w.shape[1]
         dy2 = dy.reshape(-1, D)
-        mg = getattr(w, "main_grad", None)
+        # a weight whose gradient is partial per tensor-parallel rank goes through autograd so that its reduce hook runs
+        mg = None if getattr(w, "_tp_partial", False) else getattr(w, "main_grad", None)
         if mg is not None and _lib.on(dy2) and dy2.dtype == torch.bfloat16 and mg.dtype == torch.float32 and D % 4 == 0 \
                 and ids.dtype == torch.int64:
             dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
@@ -37,6 +38,9 @@ class _Embedding(torch.autograd.Function):
             first = not getattr(w, "_main_grad_dirty", False)
             _lib.call("embedding_bwd", dy2, flat, mg, _lib.LL(flat.numel()), D, _lib.LL(w.shape[0]), int(first))
             w._main_grad_dirty = True
+            cb = getattr(w, "_grad_ready_cb", None)   # the arena's overlapped gradient reduction
+            if cb is not None:
+                cb(w)
             return None, None
         g = torch.zeros(w.shape, device=dy2.device, dtype=torch.float32)
         g.index_add_(0, ids.reshape(-1), dy2.float())

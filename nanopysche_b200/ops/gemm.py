@@ -120,15 +120,57 @@ def gemm_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *, sa
     return h, gu
 
 
+# Zero-bubble pipeline schedules split a backward pass into B (input gradients, on the critical path between
+# stages) and W (weight gradients, moved into what would be bubbles). While ``_DEFER`` is a list, every weight-gradient
+# GEMM is queued there instead of run; ``run_deferred_wgrads`` executes a queue later. ``SPLIT_MODE`` makes ``linear``
+# take its autograd function on every device (CPU included), so that all linear weight gradients are deferrable.
+_DEFER: "list | None" = None
+SPLIT_MODE = False
+
+
+class defer_wgrad:
+    """Context manager: weight-gradient GEMMs issued inside are appended to ``queue`` as ``(w, dy, x)``."""
+
+    def __init__(self, queue: list):
+        self.queue, self._prev = queue, None
+
+    def __enter__(self):
+        global _DEFER
+        self._prev, _DEFER = _DEFER, self.queue
+        return self.queue
+
+    def __exit__(self, *exc):
+        global _DEFER
+        _DEFER = self._prev
+        return False
+
+
+def run_deferred_wgrads(queue: list) -> None:
+    """The W step: run the queued weight-gradient GEMMs (into ``main_grad`` when the weight has one, else into
+    ``.grad``) and release the saved activations."""
+    while queue:
+        w, dy2, x2 = queue.pop(0)
+        g = _wgrad_into(w, dy2, x2)
+        if g is not None:
+            g = g.to(w.dtype)
+            w.grad = g if w.grad is None else w.grad + g
+
+
 def _wgrad_into(w: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor):
     """dW[N, K] = dy^T x, accumulated into ``w.main_grad`` when present; returns the autograd grad."""
+    if _DEFER is not None:
+        _DEFER.append((w, dy2, x2))
+        return None
     mg = getattr(w, "main_grad", None)
     if mg is not None:
         first = not getattr(w, "_main_grad_dirty", False)
         gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=not first)
         w._main_grad_dirty = True
-        for q in getattr(w, "_covers", ()):  # a fused view stands for several parameters
+        for q in getattr(w, "_covers", None) or (w,):  # a fused view stands for several parameters
             q._main_grad_dirty = True
+            cb = getattr(q, "_grad_ready_cb", None)      # the arena's overlapped gradient reduction (optim/arena.py)
+            if cb is not None:
+                cb(q)
         return None
     return gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype if w.is_cuda else None)
 
@@ -181,6 +223,10 @@ class _LinearBias(torch.autograd.Function):
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ w.T (+ bias)``; tcgen05 kernels for bf16 CUDA tensors, ``F.linear`` otherwise."""
+    if SPLIT_MODE and not (_lib.on(x) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+        # same math through the autograd function whose weight gradient can be deferred
+        xx = x if x.dtype == w.dtype else x.to(w.dtype)
+        return _Linear.apply(xx, w) if bias is None else _LinearBias.apply(xx, w, bias)
     if _lib.on(x) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         rt = getattr(w, "_fsdp_rt", None)
         if rt is not None:  # row-sharded weight: all-gather inside the GEMM, reduce-scattered weight gradient

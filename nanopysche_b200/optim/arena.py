@@ -51,13 +51,25 @@ class _Region:
     cnt: int = 0
     gshard: Optional[torch.Tensor] = None
     tp_group: Optional[object] = None        # tensor-parallel group these parameters are shards over (None: whole)
+    # overlapped reduce-scatter (ZeRO regions): the flat buffer is cut into equal buckets, rank r owns slice r of every
+    # bucket; master / m / v / gshard hold the owned slices back to back in bucket order
+    bucket: int = 0                          # elements per bucket (0: one contiguous shard, no overlap)
+    slice: int = 0                           # bucket // world
+    n_buckets: int = 0
+    pending: Optional[List[int]] = None      # per bucket: parameters whose gradient is still to come this step
+    need: Optional[List[int]] = None         # per bucket: number of parameters overlapping it
+    launched: Optional[List[bool]] = None
+    flags: Optional[torch.Tensor] = None     # symmetric int32 [n_buckets * world]
+    sumsq: Optional[torch.Tensor] = None     # one float: sum of squares of the reduced shard, filled by the buckets
+    staged: Optional[torch.Tensor] = None    # copy mode: [(world - 1) * cnt] peer slices in the compact shard order
     mc_weights: int = 0                      # NVLink multicast addresses of the weight / gradient arenas (0: none)
     mc_grads: int = 0
     _mc_keep: Optional[tuple] = None         # symmetric-memory handles, kept alive with the region
 
 
 class ParamArena:
-    def __init__(self, model: nn.Module, *, dp_group=None, device=None, use_symmetric: Optional[bool] = None):
+    def __init__(self, model: nn.Module, *, dp_group=None, device=None, use_symmetric: Optional[bool] = None,
+                 bucket_elems: Optional[int] = None):
         params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
         assert params, "model has no trainable parameters"
         self.model = model
@@ -67,6 +79,22 @@ class ParamArena:
         self.rank = dist.get_rank(dp_group) if self.world > 1 else 0
         cuda = self.device.type == "cuda"
         self.zero = self.world > 1 and cuda if use_symmetric is None else bool(use_symmetric)
+        import os as _os
+
+        if bucket_elems is None:
+            bucket_elems = int(_os.environ.get("NPB200_ZERO_BUCKET", str(16 << 20)))
+        q = 4 * self.world * ALIGN
+        self.bucket_elems = 0 if (bucket_elems <= 0 or _os.environ.get("NPB200_NVLS", "0") == "1") else \
+            (bucket_elems + q - 1) // q * q
+        self.reduce_ctas = int(_os.environ.get("NPB200_ZERO_CTAS", "32"))   # CTAs of one overlapped bucket reduction
+        # "copy": peers' slices are fetched by the copy engines (cudaMemcpyAsync over NVLink) into a staging buffer
+        # while the backward pass runs and summed by one kernel afterwards: no SM is taken from the GEMMs. "kernel":
+        # a small kernel per bucket pulls and sums (measured slower: its CTAs share SMs with the persistent GEMMs)
+        self.reduce_mode = _os.environ.get("NPB200_ZERO_MODE", "copy")
+        self.reduce_enabled = True      # False while earlier micro-batches of an accumulation step run
+        self._late_write = False
+        self._side: Optional[torch.cuda.Stream] = torch.cuda.Stream(device=self.device) if (self.zero and cuda) else None
+        self._epoch = 0
         self.regions: Dict[str, _Region] = {}
         seen = set()
         for n, p in params:
@@ -85,6 +113,7 @@ class ParamArena:
             r.offsets.append(off)
             r.numel = off + p.numel()
         self.heap = None
+        self.grad_inv = 1.0 / max(self.world, 1)   # scale of the reduced gradients (set by the optimizer every step)
         if self.zero:
             from ..parallel.symm import SymmetricHeap
 
@@ -92,7 +121,7 @@ class ParamArena:
             for r in self.regions.values():
                 if r.replicated and r.dtype == torch.bfloat16:
                     pad = self._padded(r.numel)
-                    need += pad * 2 + pad * 4 + 8192
+                    need += pad * 2 + pad * 4 + 8192 + 4 * self.world * (pad // max(self.bucket_elems, 1) + 2)
             f32_elems = sum(r.numel for r in self.regions.values() if r.replicated and r.dtype == torch.float32)
             self._ar_max = max(f32_elems + 64, 4096)
             self.heap = SymmetricHeap(need + 2 * self.world * self._ar_max * 4 + (1 << 20), dp_group, self.device)
@@ -110,7 +139,7 @@ class ParamArena:
         return r.numel % ALIGN == 0
 
     def _padded(self, n: int) -> int:
-        q = 4 * self.world * ALIGN
+        q = self.bucket_elems if (self.zero and self.bucket_elems) else 4 * self.world * ALIGN
         return (n + q - 1) // q * q
 
     def _materialise(self, r: _Region):
@@ -134,6 +163,14 @@ class ParamArena:
                 r.grads = self.heap.alloc((total,), torch.float32)
             r.cnt = total // self.world
             r.lo = self.rank * r.cnt
+            if self.bucket_elems and not r.mc_grads:
+                r.bucket, r.slice, r.n_buckets = self.bucket_elems, self.bucket_elems // self.world, \
+                    total // self.bucket_elems
+                r.lo = self.rank * r.slice
+                r.flags = self.heap.alloc((r.n_buckets * self.world,), torch.int32)
+                r.sumsq = torch.zeros(1, device=dev, dtype=torch.float32)
+                if self.reduce_mode == "copy":
+                    r.staged = torch.empty((self.world - 1) * r.cnt, device=dev, dtype=torch.float32)
         else:
             r.weights = torch.zeros(total, device=dev, dtype=r.dtype)
             r.grads = torch.zeros(total, device=dev, dtype=torch.float32)
@@ -146,11 +183,17 @@ class ParamArena:
                 p.main_grad = r.grads[off:off + p.numel()].view(p.shape)
                 p._main_grad_dirty = False
         if r.dtype != torch.float32:
-            r.master = r.weights[r.lo:r.lo + r.cnt].float()
+            r.master = self.owned(r, r.weights).float()
         r.m = torch.zeros(r.cnt, device=dev, dtype=torch.float32)
         r.v = torch.zeros(r.cnt, device=dev, dtype=torch.float32)
         if symm:
             r.gshard = torch.empty(r.cnt, device=dev, dtype=torch.float32)
+
+    def owned(self, r: _Region, flat: torch.Tensor) -> torch.Tensor:
+        """This rank's part of a flat region buffer, in the order master / m / v / gshard hold it."""
+        if r.bucket:
+            return flat.view(r.n_buckets, self.world, r.slice)[:, self.rank].reshape(-1)
+        return flat[r.lo:r.lo + r.cnt]
 
     def _install_hooks(self):
         def hook(p):
@@ -162,10 +205,102 @@ class ParamArena:
                 p.main_grad.copy_(p.grad)
                 p._main_grad_dirty = True
             p.grad = None
+            cb = getattr(p, "_grad_ready_cb", None)
+            if cb is not None:
+                cb(p)
 
         for r in self.regions.values():
             for p in r.params:
                 p.register_post_accumulate_grad_hook(hook)
+            if r.bucket:
+                # which buckets each parameter overlaps; a bucket is reduced as soon as all of them have their gradient
+                r.need = [0] * r.n_buckets
+                for p, off in zip(r.params, r.offsets):
+                    bs = list(range(off // r.bucket, (off + p.numel() - 1) // r.bucket + 1))
+                    p._arena_buckets = (r, bs)
+                    p._grad_ready_cb = self._param_ready
+                    for b in bs:
+                        r.need[b] += 1
+                r.pending = list(r.need)
+                r.launched = [False] * r.n_buckets
+
+    # ------------------------------------------------------------------ overlapped gradient reduction
+    def _param_ready(self, p):
+        """Called when a parameter's gradient for this backward pass has been written (wgrad GEMM epilogue,
+        embedding backward kernel or the autograd hook above)."""
+        if not self.reduce_enabled:
+            return
+        if getattr(p, "_arena_counted", False):
+            if any(p._arena_buckets[0].launched[b] for b in p._arena_buckets[1]):
+                self._late_write = True      # a second backward wrote after the bucket went out: redone in step()
+            return
+        p._arena_counted = True
+        r, bs = p._arena_buckets
+        for b in bs:
+            r.pending[b] -= 1
+            if r.pending[b] == 0 and not r.launched[b]:
+                self._launch_bucket(r, b)
+
+    def _launch_bucket(self, r: _Region, b: int, inv: Optional[float] = None):
+        import ctypes as C
+
+        if not any(x for rr in self.regions.values() if rr.bucket for x in rr.launched):
+            self._epoch = self.heap.next_epoch()      # one epoch per step for every bucket flag
+        main = torch.cuda.current_stream()
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            lo = b * r.bucket + self.rank * r.slice
+            if r.staged is not None:
+                lib, st = _lib.lib(), C.c_void_p(_lib.stream())
+                _lib.check(lib.np_bucket_sync(self.heap.host_ptr_array(r.flags), b, self.rank, self.world, self._epoch,
+                                              C.c_void_p(self.heap.epoch_base.data_ptr()), C.c_ulonglong(0), st),
+                           "bucket_sync")
+                k = 0
+                for peer in range(self.world):
+                    if peer == self.rank:
+                        continue
+                    src = self.heap.peer_ptr(r.grads, peer) + lo * 4
+                    dstp = r.staged.data_ptr() + (k * r.cnt + b * r.slice) * 4
+                    _lib.check(lib.np_memcpy_async(C.c_void_p(dstp), C.c_void_p(src), C.c_ulonglong(r.slice * 4), st),
+                               "memcpy_async")
+                    k += 1
+                r.launched[b] = True
+                return
+            dst = r.gshard[b * r.slice:(b + 1) * r.slice]
+            _lib.check(_lib.lib().np_zero_reduce_bucket(
+                self.heap.host_ptr_array(r.grads), self.heap.host_ptr_array(r.flags), b, self.rank, self.world,
+                self._epoch, C.c_void_p(self.heap.epoch_base.data_ptr()), C.c_ulonglong(0), C.c_longlong(lo),
+                C.c_longlong(r.slice), C.c_float(self.grad_inv if inv is None else inv), C.c_void_p(dst.data_ptr()),
+                C.c_void_p(r.sumsq.data_ptr()), self.reduce_ctas, C.c_void_p(_lib.stream())), "zero_reduce_bucket")
+        r.launched[b] = True
+
+    def finish_buckets(self):
+        """Launch whatever has not gone out yet (parameters without a gradient this step were just zeroed), redo
+        everything if a later backward pass wrote into a bucket that had already been reduced, and make the current
+        stream wait for the side stream."""
+        regs = [r for r in self.regions.values() if r.bucket]
+        if not regs:
+            return
+        if self._late_write:
+            if self._side is not None:
+                torch.cuda.current_stream().wait_stream(self._side)
+            for r in regs:
+                r.sumsq.zero_()
+                r.launched = [False] * r.n_buckets
+            self._late_write = False
+        for r in regs:
+            for b in range(r.n_buckets):
+                if not r.launched[b]:
+                    self._launch_bucket(r, b)
+        torch.cuda.current_stream().wait_stream(self._side)
+
+    def reset_buckets(self):
+        for r in self.regions.values():
+            if r.bucket:
+                r.pending = list(r.need)
+                r.launched = [False] * r.n_buckets
+                for p in r.params:
+                    p._arena_counted = False
 
     def _region_of(self, p) -> Optional[tuple]:
         for r in self.regions.values():
@@ -220,6 +355,7 @@ class ParamArena:
                 p.grad = None
         for w in self.fused:
             w._main_grad_dirty = False
+        self.reset_buckets()
 
     def finalize_grads(self):
         """Zero the gradient of any parameter that received none this step."""
@@ -251,6 +387,13 @@ class ArenaAdamW(torch.optim.Optimizer):
         self.max_grad_norm = max_grad_norm
         self.grad_divisor = grad_divisor
         self.step_count = 0
+        # process groups over which the squared gradient norm is additionally summed before clipping (pipeline stages
+        # hold disjoint parameters: the PP group), and how many ranks of those groups hold every parameter (DualPipe: 2)
+        self.norm_groups: list = []
+        self.norm_copies: float = 1.0
+        # second stream of the two-stream parameter update (created here: not inside a graph capture)
+        self._side2: Optional[torch.cuda.Stream] = torch.cuda.Stream(device=arena.device) \
+            if (arena.zero and arena.device.type == "cuda") else None
         dev = arena.device
         self._cuda = dev.type == "cuda"
         nreg = len(arena.regions)
@@ -268,6 +411,17 @@ class ArenaAdamW(torch.optim.Optimizer):
         self._coef = torch.ones(2, device=dev, dtype=torch.float32)   # [clip coefficient, grad norm]
         self._coef_local = torch.ones(1, device=dev, dtype=torch.float32)
         self.last_grad_norm: Optional[torch.Tensor] = None
+
+    @property
+    def grad_divisor(self) -> float:
+        return self._grad_divisor
+
+    @grad_divisor.setter
+    def grad_divisor(self, v: float):
+        # the overlapped bucket reductions run during the backward pass, before step(): they read the scale here
+        self._grad_divisor = float(v)
+        a = self.arena
+        a.grad_inv = 1.0 / (self._grad_divisor * (a.world if a.world > 1 else 1))
 
     def zero_grad(self, set_to_none: bool = True):
         self.arena.zero_grad()
@@ -299,12 +453,26 @@ class ArenaAdamW(torch.optim.Optimizer):
         inv = 1.0 / (self.grad_divisor * (N if N > 1 else 1))
         stride = self._partial.numel() // len(a.regions)
         self._partial.zero_()
-        if a.zero:
+        bucketed = a.zero and any(r.bucket for r in a.regions.values())
+        if bucketed:
+            # the reduce-scatter of every bucket was launched on the side stream while the backward pass ran (each
+            # waits on per-bucket flags of all ranks): send the stragglers and join
+            a.finish_buckets()
+        if a.zero and any(r.replicated and r.dtype == torch.bfloat16 and not r.bucket for r in a.regions.values()):
             a.heap.barrier()  # every rank's backward has finished writing its gradient buffers
         extra = None
         for i, r in enumerate(a.regions.values()):
             part = self._partial[i * stride:(i + 1) * stride]
-            if a.zero and r.replicated and r.dtype == torch.bfloat16 and r.mc_grads:
+            if r.bucket and r.staged is not None:
+                _lib.check(_lib.lib().np_zero_reduce_staged(
+                    C.c_void_p(r.grads.data_ptr()), C.c_longlong(r.lo), C.c_longlong(r.slice), C.c_longlong(r.bucket),
+                    C.c_void_p(r.staged.data_ptr()), N - 1, C.c_longlong(r.cnt), C.c_float(inv),
+                    C.c_void_p(r.gshard.data_ptr()), C.c_void_p(part.data_ptr()), C.c_void_p(_lib.stream())),
+                    "zero_reduce_staged")
+            elif r.bucket:
+                part[:1].copy_(r.sumsq)
+                r.sumsq.zero_()
+            elif a.zero and r.replicated and r.dtype == torch.bfloat16 and r.mc_grads:
                 _lib.check(_lib.lib().np_zero_reduce_mc(C.c_void_p(r.mc_grads), C.c_longlong(r.lo), C.c_longlong(r.cnt),
                                                         C.c_float(inv), C.c_void_p(r.gshard.data_ptr()),
                                                         C.c_void_p(part.data_ptr()), C.c_void_p(_lib.stream())),
@@ -349,12 +517,40 @@ class ArenaAdamW(torch.optim.Optimizer):
                 dist.all_reduce(self._tot, group=a.dp_group)
             self._partial.zero_()
             self._partial[:1].copy_(self._tot)
+        if self.norm_groups:
+            torch.sum(self._partial, dim=0, keepdim=True, out=self._tot)
+            for g in self.norm_groups:
+                dist.all_reduce(self._tot, group=g)
+            self._partial.zero_()
+            self._partial[:1].copy_(self._tot / self.norm_copies)
         _lib.call("clip_coef", self._partial, self._partial.numel(), extra,
                   float(self.max_grad_norm or 0.0), self._coef)
         self.last_grad_norm = self._coef[1]
         torch.mul(self._coef[:1], inv, out=self._coef_local)  # coefficient for gradients not yet divided
+        main = torch.cuda.current_stream() if self._cuda else None
+        two_stream = a.zero and any(not (r.replicated and r.dtype == torch.bfloat16) and r.weights.numel() > (1 << 24)
+                                    for r in a.regions.values())
+        if two_stream:
+            # the sharded update ends in peer stores of the new weights (NVLink-bound), the update of the local (expert)
+            # regions is HBM-bound: run the first on a side stream under the second
+            self._side2.wait_stream(main)
         for r in a.regions.values():
             wdr = wd if r.decay else 0.0
+            zero_region = a.zero and r.replicated and r.dtype == torch.bfloat16
+            with torch.cuda.stream(self._side2 if (two_stream and zero_region) else main):
+                self._update_region(r, lr, b1, b2, eps, wdr, N)
+        if two_stream:
+            main.wait_stream(self._side2)
+        if a.zero:
+            a.heap.barrier()  # all ranks' weight stores have landed before the next forward reads them
+            a.heap.end_step()
+        for hook in self.post_step_hooks:
+            hook()
+        return None
+
+    def _update_region(self, r, lr, b1, b2, eps, wdr, N):
+        a = self.arena
+        if True:
             if a.zero and r.replicated and r.dtype == torch.bfloat16 and r.mc_weights:
                 _lib.check(_lib.lib().np_zero_adamw_bcast_mc(
                     C.c_void_p(r.master.data_ptr()), C.c_void_p(r.gshard.data_ptr()), C.c_void_p(r.m.data_ptr()),
@@ -369,6 +565,7 @@ class ArenaAdamW(torch.optim.Optimizer):
                     C.c_void_p(r.v.data_ptr()), ptrs, N, C.c_longlong(r.lo), C.c_longlong(r.cnt), C.c_float(lr),
                     C.c_float(b1), C.c_float(b2), C.c_float(eps), C.c_float(wdr), self.step_count,
                     C.c_void_p(self._coef.data_ptr()), C.c_void_p(self._hyper.data_ptr()),
+                    C.c_longlong(r.slice if r.bucket else 0), C.c_longlong(r.bucket),
                     C.c_void_p(_lib.stream())), "zero_adamw_bcast")
             elif r.dtype == torch.float32:
                 _lib.call("adamw", r.weights, r.grads, r.m, r.v, None, _lib.LL(r.weights.numel()), float(lr),
@@ -376,12 +573,6 @@ class ArenaAdamW(torch.optim.Optimizer):
             else:
                 _lib.call("adamw", r.master, r.grads, r.m, r.v, r.weights, _lib.LL(r.weights.numel()), float(lr),
                           float(b1), float(b2), float(eps), float(wdr), self.step_count, self._coef_local, self._hyper)
-        if a.zero:
-            a.heap.barrier()  # all ranks' weight stores have landed before the next forward reads them
-            a.heap.end_step()
-        for hook in self.post_step_hooks:
-            hook()
-        return None
 
     def _step_reference(self, lr, b1, b2, eps, wd):
         """CPU path: same math with torch ops (also the oracle of the kernels)."""
@@ -400,7 +591,10 @@ class ArenaAdamW(torch.optim.Optimizer):
             dist.all_reduce(sq, group=a.dp_group)
         if tpg is not None:
             dist.all_reduce(sq[1:], group=tpg)
-        norm = sq.sum().sqrt()
+        tot = sq.sum()
+        for g in self.norm_groups:
+            dist.all_reduce(tot, group=g)
+        norm = (tot / self.norm_copies).sqrt()
         for hook in self.post_step_hooks:
             hook()
         coef = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0) if self.max_grad_norm else torch.ones(())
@@ -422,7 +616,7 @@ class ArenaAdamW(torch.optim.Optimizer):
         a = self.arena
         return {"step": self.step_count, "param_groups": [{k: v for k, v in g.items() if k != "params"}
                                                           for g in self.param_groups],
-                "regions": {k: {"master": r.master, "m": r.m, "v": r.v, "lo": r.lo, "cnt": r.cnt}
+                "regions": {k: {"master": r.master, "m": r.m, "v": r.v, "lo": r.lo, "cnt": r.cnt, "bucket": r.bucket}
                             for k, r in a.regions.items()}}
 
     def load_state_dict(self, sd):

@@ -28,15 +28,19 @@ class _Bucket:
         self.numel = n
         self.flat: Optional[torch.Tensor] = None
         self.pending = len(params)
+        self.seen = set()
         self.work = None
 
 
 class BucketedGradReducer:
     def __init__(self, params: Iterable[torch.nn.Parameter], group=None, bucket_bytes: int = 64 << 20,
-                 average: bool = True):
+                 average: bool = True, divisor: Optional[float] = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.average = average
+        # what the summed gradients are divided by: the group size, or less when some ranks of the group hold shares
+        # of one sample's gradient that must add up (context parallelism)
+        self.divisor = float(divisor) if divisor else float(self.world)
         self.enabled = True          # the trainer switches this off for all but the last micro-batch of a step
         self.buckets: List[_Bucket] = []
         self._of = {}
@@ -65,6 +69,7 @@ class BucketedGradReducer:
         if b.flat is None:
             b.flat = torch.zeros(b.numel, dtype=p.grad.dtype, device=p.grad.device)
         b.flat[off:off + p.numel()].copy_(p.grad.reshape(-1))
+        b.seen.add(id(p))
         b.pending -= 1
         if b.pending == 0:
             b.work = dist.all_reduce(b.flat, group=self.group, async_op=True)
@@ -75,21 +80,31 @@ class BucketedGradReducer:
         if self.world <= 1:
             return
         for b in self.buckets:
-            if b.work is None and b.pending < len(b.params):   # some parameters of the bucket had no gradient
-                if b.flat is not None:
-                    for p, off in zip(b.params, b.offsets):
-                        if p.grad is None:
-                            b.flat[off:off + p.numel()].zero_()
-                    b.work = dist.all_reduce(b.flat, group=self.group, async_op=True)
+            if b.work is None:
+                # not every parameter came through the hook: it had no gradient this step, or its gradient was set
+                # outside autograd (weight gradients deferred by a zero-bubble schedule); every rank sends the bucket
+                ref = next((p for p in b.params if p.grad is not None), None)
+                if b.flat is None:
+                    b.flat = torch.zeros(b.numel, dtype=ref.grad.dtype if ref is not None else b.params[0].dtype,
+                                         device=b.params[0].device)
+                for p, off in zip(b.params, b.offsets):
+                    if id(p) in b.seen:
+                        continue
+                    if p.grad is None:
+                        b.flat[off:off + p.numel()].zero_()
+                    else:
+                        b.flat[off:off + p.numel()].copy_(p.grad.reshape(-1))
+                b.work = dist.all_reduce(b.flat, group=self.group, async_op=True)
         for b in self.buckets:
             if b.work is not None:
                 b.work.wait()
                 if self.average:
-                    b.flat.div_(self.world)
+                    b.flat.div_(self.divisor)
                 for p, off in zip(b.params, b.offsets):
                     if p.grad is not None:
                         p.grad.copy_(b.flat[off:off + p.numel()].view_as(p.grad))
             b.work, b.pending = None, len(b.params)
+            b.seen.clear()
 
     def remove(self):
         for h in self._handles:

@@ -4,9 +4,16 @@ clipping across stages (reference: distributed/pipeline_runtime.py:55-534).
 The reference wraps ``torch.distributed.pipelining`` and a sequential DualPipe placeholder; neither
 is wired to its Trainer. Here one executor runs any per-rank action list produced by
 ``pipeline_parallel`` (GPipe, 1F1B, Zero-Bubble with B/W split, DualPipe with two stage copies per
-rank): activations and gradients move with non-blocking ``batch_isend_irecv`` pairs on the PP
-group, receives are posted one action ahead so the transfer overlaps the previous action's compute
-(on a GPU the NCCL p2p kernels run on NCCL's own stream).
+rank). Activations and gradients move with non-blocking ``batch_isend_irecv`` on the PP group:
+
+* every incoming channel (peer, activation | gradient) is a FIFO in the *sender's* order, derived from the sender's
+  action list, and the executor keeps ``prefetch`` receives of each channel posted ahead of the action that consumes
+  them, so a transfer runs under the compute of earlier actions (NCCL matches point-to-point messages by order, not
+  by tag, so receives must be posted in the order the peer sends);
+* activations and gradients use separate communicators, chosen by the parity of the sender's rank, so a receive
+  that is posted early never sits in front of this rank's own sends on one NCCL stream;
+* a zero-bubble B action runs the backward pass with every weight-gradient GEMM deferred (``ops.gemm.defer_wgrad``)
+  and the W action runs them later.
 """
 from __future__ import annotations
 
@@ -72,6 +79,10 @@ class PipelineParallelConfig:
         return 1 if PipelineScheduleType(self.schedule).is_single_stage else 2
 
     def num_stages(self) -> int:
+        """Number of distinct model stages. DualPipe keeps ``degree`` stages and gives every rank two of them (its own
+        and its mirror's copy); the other two-stage schedules cut the model into ``2 * degree`` stages."""
+        if PipelineScheduleType(self.schedule) == PipelineScheduleType.dualpipe:
+            return self.degree
         return self.degree * self.stages_per_rank()
 
     def get_split_points(self, n_layers: int) -> List[int]:
@@ -83,8 +94,9 @@ class PipelineParallelConfig:
         n, spr = self.degree, self.stages_per_rank()
         if spr == 1:
             return [pp_rank]
-        if PipelineScheduleType(self.schedule) in (PipelineScheduleType.zbv_zero_bubble,
-                                                   PipelineScheduleType.dualpipe) or \
+        if PipelineScheduleType(self.schedule) == PipelineScheduleType.dualpipe:
+            return [pp_rank, n - 1 - pp_rank]       # direction 0: stage r; direction 1: the mirror rank's stage
+        if PipelineScheduleType(self.schedule) == PipelineScheduleType.zbv_zero_bubble or \
                 self.style == PipelineSplitStyle.v:
             return [pp_rank, self.num_stages() - 1 - pp_rank]
         return [pp_rank + s * n for s in range(spr)]
@@ -108,8 +120,77 @@ def split_model(model: nn.Module, pp_mesh, pp_config: PipelineParallelConfig, *,
         if device is not None:
             m = m.to(device)
         m._stage_id = sid
+        m._direction = len(stages)
         stages.append(m)
     return stages
+
+
+class PipelineStages(nn.Module):
+    """The stage modules one rank owns under a schedule with more than one stage per rank (interleaved, zero-bubble
+    V, DualPipe). Behaves like a model for optimizers, checkpoints and the ``apply_*`` hooks; ``Trainer`` hands
+    ``.stages`` to ``PipelineSchedule``. Under DualPipe the second entry is a *copy* of the mirror rank's stage: its
+    gradients are summed with that rank's after every step (``sync_twin_grads``) and both copies take the same update."""
+
+    def __init__(self, stages: Sequence[nn.Module], pp_group, pp_config: "PipelineParallelConfig"):
+        super().__init__()
+        self.stages = nn.ModuleList(stages)
+        self._pp_enabled = True
+        self._pp_group = pp_group
+        self._pp_config = pp_config
+        self.d_model = getattr(stages[0], "d_model", None)
+        self.vocab_size = getattr(stages[0], "vocab_size", None)
+
+    def forward(self, *a, **k):
+        raise RuntimeError("a PipelineStages container is run by PipelineSchedule (Trainer does that), not called")
+
+    def __getattr__(self, name):
+        if name.startswith("apply_"):
+            stages = super().__getattr__("stages")
+
+            def fan_out(*a, **k):
+                for st in stages:
+                    if hasattr(st, name):
+                        getattr(st, name)(*a, **k)
+            return fan_out
+        return super().__getattr__(name)
+
+    @property
+    def is_dualpipe(self) -> bool:
+        return PipelineScheduleType(self._pp_config.schedule) == PipelineScheduleType.dualpipe
+
+
+def sync_twin_grads(stages: Sequence[nn.Module], group, grad_of=None) -> None:
+    """DualPipe: rank r holds stage r (direction 0) and a copy of stage p-1-r (direction 1); the mirror rank p-1-r
+    holds the same two stages the other way round. Every stage therefore has one half of its gradient on each of the
+    two ranks: exchange and add, so that both copies see the full gradient. One flat send + receive per rank."""
+    p, r = dist.get_world_size(group), dist.get_rank(group)
+    partner = p - 1 - r
+    grad_of = grad_of or (lambda q: q.grad)
+    order = sorted(stages, key=lambda st: st._stage_id)            # both ranks hold stages {r, p-1-r}: same order
+    if partner == r:                                                # odd p, middle rank: both copies are local
+        a, b = stages
+        for (_, qa), (_, qb) in zip(a.named_parameters(), b.named_parameters()):
+            ga, gb = grad_of(qa), grad_of(qb)
+            if ga is not None and gb is not None:
+                tot = ga + gb
+                ga.copy_(tot)
+                gb.copy_(tot)
+        return
+    grads = [grad_of(q) for st in order for q in st.parameters()]
+    grads = [g for g in grads if g is not None]
+    if not grads:
+        return
+    flat = torch.cat([g.reshape(-1).float() for g in grads])
+    other = torch.empty_like(flat)
+    peer = dist.get_global_rank(group, partner)
+    for w in dist.batch_isend_irecv([dist.P2POp(dist.isend, flat, peer, group=group),
+                                     dist.P2POp(dist.irecv, other, peer, group=group)]):
+        w.wait()
+    flat += other
+    off = 0
+    for g in grads:
+        g.copy_(flat[off:off + g.numel()].view_as(g))
+        off += g.numel()
 
 
 # ------------------------------------------------------------------ executor
@@ -158,13 +239,22 @@ class PipelineSchedule:
         else:  # Interleaved1F1B, LoopedBFS
             gen = InterleavedSchedule(self.p, self.m, v=2, placement="loop")
         self.generator = gen
-        self.actions: List[Action] = gen.generate_schedule()[self.rank]
+        self.all_actions: List[List[Action]] = gen.generate_schedule()
+        self.actions: List[Action] = self.all_actions[self.rank]
+        self.prefetch = 2   # receives of every incoming channel kept posted ahead of their use
+        self.split_w = any(a.type == ScheduleType.BWD_WEIGHT for a in self.actions)
+        if self.split_w:
+            from ..ops import gemm as gemm_ops
+
+            gemm_ops.SPLIT_MODE = True   # every linear goes through the autograd function with deferrable wgrad
         self.total_stages = getattr(gen, "total_stages", 2 * self.p if self.dual else self.p)
         if self.dual:
             # direction 1 is a second copy of the pipeline: schedule stage p+s holds model stage s
             self.stage_of = {self.rank: self.stages[0], self.p + (self.p - 1 - self.rank): self.stages[-1]}
         else:
             self.stage_of = {getattr(s, "_stage_id", self.rank): s for s in self.stages}
+        self._chan_groups = self._make_channel_groups() if (self.group is not None and dist.is_initialized()) else {}
+        self.channels = self._incoming_channels()
 
     # -- helpers
     def _first(self, stage: int) -> bool:
@@ -179,11 +269,52 @@ class PipelineSchedule:
     def _global(self, r: int) -> int:
         return dist.get_global_rank(self.group, r) if self.group is not None else r
 
-    def _p2p(self, op, tensor, stage_peer: int, tag: int):
-        peer = self._global(self._rank_of(stage_peer))
-        return dist.batch_isend_irecv([dist.P2POp(op, tensor, peer, group=self.group, tag=tag)])
+    # -- point-to-point plumbing ---------------------------------------------------------------------------------
+    def _make_channel_groups(self):
+        """Four communicators over the PP group: (activation | gradient) x parity of the sender's PP rank.
+        ``new_group`` is collective over the whole job, so every rank creates the groups of every PP group."""
+        if self.group is None or self.p <= 1:
+            return {}
+        mine = [dist.get_global_rank(self.group, r) for r in range(self.p)]
+        every = [None] * dist.get_world_size()
+        dist.all_gather_object(every, mine)
+        out = {}
+        for ranks in sorted({tuple(x) for x in every}):
+            for kind in ("act", "grad"):
+                for parity in (0, 1):
+                    g = dist.new_group(list(ranks))
+                    if tuple(mine) == ranks:
+                        out[(kind, parity)] = g
+        return out
+
+    def _chan_group(self, kind: str, sender_rank: int):
+        return self._chan_groups.get((kind, sender_rank & 1), self.group)
+
+    def _sends_of(self, rank: int) -> List[tuple]:
+        """(kind, destination rank, label) of every message ``rank`` sends, in its action order."""
+        out = []
+        for a in self.all_actions[rank]:
+            if a.type == ScheduleType.FWD and not self._last(a.stage) and self._rank_of(a.stage + 1) != rank:
+                out.append(("act", self._rank_of(a.stage + 1), ("act", a.stage + 1, a.microbatch)))
+            elif a.type in (ScheduleType.BWD, ScheduleType.BWD_INPUT) and not self._first(a.stage) and \
+                    self._rank_of(a.stage - 1) != rank:
+                out.append(("grad", self._rank_of(a.stage - 1), ("grad", a.stage - 1, a.microbatch)))
+        return out
+
+    def _incoming_channels(self) -> Dict[tuple, List[tuple]]:
+        """{(peer, kind): labels in the order the peer sends them} for the messages addressed to this rank."""
+        ch: Dict[tuple, List[tuple]] = {}
+        for peer in range(self.p):
+            if peer == self.rank:
+                continue
+            for kind, dst, label in self._sends_of(peer):
+                if dst == self.rank:
+                    ch.setdefault((peer, kind), []).append(label)
+        return ch
 
     def step(self, inputs: torch.Tensor, target: Optional[torch.Tensor] = None, **kwargs):
+        from ..ops import gemm as gemm_ops
+
         m = self.m
         in_chunks = list(inputs.chunk(m, dim=0)) if inputs is not None else [None] * m
         tg_chunks = list(target.chunk(m, dim=0)) if target is not None else [None] * m
@@ -191,18 +322,53 @@ class PipelineSchedule:
         pending_send: list = []
         keepalive: list = []  # tensors of in-flight sends
         local_box: Dict[tuple, torch.Tensor] = {}  # hand-off between two stages of this rank
+        wqueues: Dict[tuple, list] = {}            # deferred weight-gradient GEMMs per (stage, microbatch)
         losses: List[torch.Tensor] = []
         hs, hd = self.hidden_shape, self.hidden_dtype
+        channels = {k: list(v) for k, v in self.channels.items()}
+        nxt = {k: 0 for k in channels}              # next message of the channel to post a receive for
+        posted: Dict[tuple, tuple] = {}              # label -> (buffer, works, channel)
+        outstanding = {k: 0 for k in channels}
 
-        def hidden_like(ref_mb: int):
-            nonlocal hs, hd
+        def post_next(ch):
+            peer, kind = ch
             if hs is None:
                 raise RuntimeError("hidden_shape is required on stages that receive activations")
-            return torch.empty(hs, dtype=hd, device=self._device())
+            label = channels[ch][nxt[ch]]
+            nxt[ch] += 1
+            buf = torch.empty(hs, dtype=hd, device=self._device())
+            tag = label[2] + (10000 if kind == "grad" else 0) + 100 * label[1]
+            works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, buf, self._global(peer),
+                                                       group=self._chan_group(kind, peer), tag=tag)])
+            posted[label] = (buf, works, ch)
+            outstanding[ch] += 1
+
+        def prefetch():
+            for ch in channels:
+                while outstanding[ch] < self.prefetch and nxt[ch] < len(channels[ch]):
+                    post_next(ch)
+
+        def receive(label, ch):
+            while label not in posted:      # post in the sender's order until this message's receive is out
+                post_next(ch)
+            buf, works, _ = posted.pop(label)
+            for w in works:
+                w.wait()
+            outstanding[ch] -= 1
+            return buf
+
+        def send(kind, tensor, dst_stage, label):
+            keepalive.append(tensor.detach().contiguous())
+            tag = label[2] + (10000 if kind == "grad" else 0) + 100 * label[1]
+            pending_send.extend(dist.batch_isend_irecv([dist.P2POp(
+                dist.isend, keepalive[-1], self._global(self._rank_of(dst_stage)),
+                group=self._chan_group(kind, self.rank), tag=tag)]))
 
         for a in self.actions:
             if a.type == ScheduleType.IDLE:
                 continue
+            if hs is not None:
+                prefetch()
             stage_mod = self.stage_of[a.stage]
             key = (a.stage, a.microbatch)
             if a.type == ScheduleType.FWD:
@@ -212,10 +378,8 @@ class PipelineSchedule:
                 elif self._rank_of(a.stage - 1) == self.rank:  # previous stage lives on this rank too
                     x = local_box.pop(("act", a.stage, a.microbatch)).requires_grad_(True)
                 else:
-                    buf = hidden_like(a.microbatch)
-                    for w in self._p2p(dist.irecv, buf, a.stage - 1, tag=a.microbatch):
-                        w.wait()
-                    x = buf.requires_grad_(True)
+                    x = receive(("act", a.stage, a.microbatch), (self._rank_of(a.stage - 1), "act"))
+                    x.requires_grad_(True)
                 mb.inp = x
                 if self._last(a.stage):
                     out = stage_mod(x, labels=tg_chunks[a.microbatch], **kwargs) if self.loss_fn is None else \
@@ -238,27 +402,31 @@ class PipelineSchedule:
                     if self._rank_of(a.stage + 1) == self.rank:
                         local_box[("act", a.stage + 1, a.microbatch)] = y.detach().clone()
                     else:
-                        keepalive.append(y.detach().contiguous())
-                        pending_send += self._p2p(dist.isend, keepalive[-1], a.stage + 1, tag=a.microbatch)
+                        send("act", y, a.stage + 1, ("act", a.stage + 1, a.microbatch))
             elif a.type in (ScheduleType.BWD, ScheduleType.BWD_INPUT):
                 mb = state[key]
                 if self._last(a.stage):
-                    mb.loss.backward()
+                    root, g = mb.loss, None
                 elif self._rank_of(a.stage + 1) == self.rank:
-                    mb.out.backward(local_box.pop(("grad", a.stage, a.microbatch)))
+                    root, g = mb.out, local_box.pop(("grad", a.stage, a.microbatch))
                 else:
-                    g = torch.empty_like(mb.out)
-                    for w in self._p2p(dist.irecv, g, a.stage + 1, tag=10000 + a.microbatch):
-                        w.wait()
-                    mb.out.backward(g)
+                    root, g = mb.out, receive(("grad", a.stage, a.microbatch), (self._rank_of(a.stage + 1), "grad"))
+                if a.type == ScheduleType.BWD_INPUT:
+                    # B: everything except the weight-gradient GEMMs, which wait in a queue for this pair's W action
+                    with gemm_ops.defer_wgrad(wqueues.setdefault(key, [])):
+                        root.backward(g)
+                else:
+                    root.backward(g)
                 if not self._first(a.stage) and mb.inp.grad is not None:
                     if self._rank_of(a.stage - 1) == self.rank:
                         local_box[("grad", a.stage - 1, a.microbatch)] = mb.inp.grad
                     else:
-                        keepalive.append(mb.inp.grad.contiguous())
-                        pending_send += self._p2p(dist.isend, keepalive[-1], a.stage - 1, tag=10000 + a.microbatch)
+                        send("grad", mb.inp.grad, a.stage - 1, ("grad", a.stage - 1, a.microbatch))
                 state.pop(key)
-            # BWD_WEIGHT: weight gradients were produced together with the input gradients above
+            elif a.type == ScheduleType.BWD_WEIGHT:
+                gemm_ops.run_deferred_wgrads(wqueues.pop(key, []))
+        for q in wqueues.values():      # a schedule without W actions for some pair: nothing may be left behind
+            gemm_ops.run_deferred_wgrads(q)
         for w in pending_send:
             w.wait()
         if losses:
@@ -283,8 +451,11 @@ class DualPipeScheduleRuntime(PipelineSchedule):
         super().__init__(stages, pp_mesh, cfg, **kw)
 
 
-def clip_grad_norm_pp(parameters, max_norm: float, pp_group=None, norm_type: float = 2.0) -> torch.Tensor:
-    """Clip by the global norm over all pipeline stages (one scalar all-reduce over the PP group)."""
+def clip_grad_norm_pp(parameters, max_norm: float, pp_group=None, norm_type: float = 2.0,
+                      copies: int = 1) -> torch.Tensor:
+    """Clip by the global norm over all pipeline stages (one scalar all-reduce over the PP group). ``copies``: how
+    many ranks hold each stage (2 under DualPipe, whose twin copies carry identical gradients after
+    ``sync_twin_grads``), so that every stage counts once."""
     params = [p for p in parameters if p.grad is not None]
     dev = params[0].device if params else torch.device("cpu")
     if norm_type == float("inf"):
@@ -296,7 +467,7 @@ def clip_grad_norm_pp(parameters, max_norm: float, pp_group=None, norm_type: flo
             if params else torch.zeros((), device=dev)
         if pp_group is not None:
             dist.all_reduce(total, op=dist.ReduceOp.SUM, group=pp_group)
-        total = total ** (1.0 / norm_type)
+        total = (total / max(copies, 1)) ** (1.0 / norm_type)
     coef = (max_norm / (total + 1e-6)).clamp(max=1.0)
     for p in params:
         p.grad.mul_(coef.to(p.grad.dtype))

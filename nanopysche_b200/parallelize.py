@@ -26,6 +26,26 @@ from .parallel.tensor_parallel import TensorParallelConfig
 log = logging.getLogger(__name__)
 
 
+_PP_SCHEDULE_NAMES = {"1f1b": "1F1B", "gpipe": "GPipe", "dualpipe": "DualPipe", "interleaved": "Interleaved1F1B",
+                      "interleaved1f1b": "Interleaved1F1B", "loopedbfs": "LoopedBFS", "zb": "InterleavedZeroBubble",
+                      "zero_bubble": "InterleavedZeroBubble", "zerobubble": "InterleavedZeroBubble",
+                      "interleavedzerobubble": "InterleavedZeroBubble", "zbv": "ZBVZeroBubble",
+                      "zbvzerobubble": "ZBVZeroBubble"}
+
+
+def runtime_pp_config(pp_config):
+    """Either of the two ``PipelineParallelConfig`` classes (the reference has both: distributed/pipeline_parallel.py
+    with a schedule *name*, distributed/pipeline_runtime.py with a schedule *type*) as the runtime one."""
+    from .parallel.pipeline_runtime import PipelineParallelConfig as RuntimeConfig
+    from .parallel.pipeline_runtime import PipelineScheduleType
+
+    if isinstance(pp_config, RuntimeConfig):
+        return pp_config
+    name = str(getattr(pp_config.schedule, "value", pp_config.schedule))
+    st = PipelineScheduleType(_PP_SCHEDULE_NAMES.get(name.lower(), name))
+    return RuntimeConfig(degree=pp_config.degree, schedule=st, num_microbatches=pp_config.num_microbatches)
+
+
 def parallelize_model(model: nn.Module, *, world_mesh, device: Optional[torch.device] = None,
                       max_sequence_length: Optional[int] = None, tp_config: Optional[TensorParallelConfig] = None,
                       cp_config: Optional[ContextParallelConfig] = None, pp_config=None,
@@ -39,7 +59,17 @@ def parallelize_model(model: nn.Module, *, world_mesh, device: Optional[torch.de
                                  ep=2 if ep_requested else 1, fsdp=dp_config is not None, compile=compile_model)
     if pp_config is not None and getattr(pp_config, "degree", 1) > 1:
         log.info("  Applying PP (degree=%d)", pp_config.degree)
-        model.apply_pp(get_pp_mesh(world_mesh))
+        rt_cfg = runtime_pp_config(pp_config)
+        pp_mesh = get_pp_mesh(world_mesh)
+        if rt_cfg.stages_per_rank() == 1 or not hasattr(model, "n_layers"):
+            model.apply_pp(pp_mesh)
+            model._pp_config = rt_cfg
+        else:
+            # interleaved / zero-bubble V / DualPipe: this rank runs two stages; the model becomes a container of them
+            from .parallel.pipeline_runtime import PipelineStages, split_model
+
+            group = pp_mesh.get_group() if hasattr(pp_mesh, "get_group") else pp_mesh
+            model = PipelineStages(split_model(model, pp_mesh, rt_cfg, device=device), group, rt_cfg)
     if fp8_config is not None and fp8_config.enabled:
         from .fp8.training import apply_fp8
 
@@ -52,8 +82,19 @@ def parallelize_model(model: nn.Module, *, world_mesh, device: Optional[torch.de
     if tp_config is not None and tp_config.degree > 1:
         log.info("  Applying TP (degree=%d)", tp_config.degree)
         tp_mesh = get_tp_mesh(world_mesh)
-        model.apply_tp(tp_mesh)
-        tp_config.maybe_enable_async_tp(tp_mesh)
+        # "async TP": the sequence-parallel layout with the all-gather inside the column-parallel GEMMs and the
+        # reduce-scatter behind the row-parallel ones (ops/tp_fused.py); needs CUDA peer memory and a model whose
+        # apply_tp knows the switch, otherwise the plain all-reduce form
+        fused = tp_config.maybe_enable_async_tp(tp_mesh) and device is not None and \
+            torch.device(device).type == "cuda"
+        try:
+            model.apply_tp(tp_mesh, fused=fused) if fused else model.apply_tp(tp_mesh)
+        except TypeError:
+            model.apply_tp(tp_mesh)
+            fused = False
+        if tp_config.enable_async and not fused:
+            log.warning("  async TP requested but not available here: tensor parallelism uses plain all-reduces")
+        model._tp_async = bool(fused)
     if ep_requested:
         log.info("  Applying EP")
         model.apply_ep(get_ep_mesh(world_mesh))

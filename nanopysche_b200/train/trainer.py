@@ -257,7 +257,6 @@ class Trainer:
             cb.pre_optim_step(self)
         if self._arena_opt:
             self.optimizer.max_grad_norm = c.max_grad_norm
-            self.optimizer.grad_divisor = float(c.gradient_accumulation_steps) / 1.0
             self.optimizer.step()
             grad_norm = self.optimizer.last_grad_norm
         else:
@@ -267,7 +266,8 @@ class Trainer:
                 if getattr(self.model, "_pp_enabled", False):
                     from ..parallel.pipeline_runtime import clip_grad_norm_pp
 
-                    grad_norm = clip_grad_norm_pp(params, c.max_grad_norm, getattr(self.model, "_pp_group", None))
+                    grad_norm = clip_grad_norm_pp(params, c.max_grad_norm, getattr(self.model, "_pp_group", None),
+                                                  copies=2 if getattr(self.model, "is_dualpipe", False) else 1)
                 elif params:
                     grad_norm = torch.nn.utils.clip_grad_norm_(params, c.max_grad_norm)
             self.optimizer.step()
@@ -302,7 +302,8 @@ class Trainer:
             group = getattr(self.model, "_replica_group", dist.group.WORLD)
             if group is not None:
                 params = [p for p in self.model.parameters() if not getattr(p, "_ep_sharded", False)]
-                self._reducer = BucketedGradReducer(params, group=group)
+                self._reducer = BucketedGradReducer(params, group=group,
+                                                    divisor=dist.get_world_size(group) / max(self.config.cp_size, 1))
         return self._reducer
 
     def _sync_replicated_grads(self):
@@ -325,16 +326,18 @@ class Trainer:
         c = self.config
         group = self.model._pp_group
         pp = dist.get_world_size(group)
+        stages = list(self.model.stages) if hasattr(self.model, "stages") else [self.model]
         if self._pp_schedule is None:
             m = c.pp_microbatches or pp
             assert c.micro_batch_size % m == 0, "micro_batch_size must be a multiple of the pipeline microbatch count"
-            cfg = PipelineParallelConfig(degree=pp, schedule=PipelineScheduleType(c.pp_schedule), num_microbatches=m)
-            assert cfg.stages_per_rank() == 1, \
-                "the trainer drives one stage per rank (GPipe, 1F1B); schedules with several stages per rank take " \
-                "split_model() + PipelineSchedule directly"
-            d_model = self.model.d_model
+            cfg = getattr(self.model, "_pp_config", None) or PipelineParallelConfig(
+                degree=pp, schedule=PipelineScheduleType(c.pp_schedule), num_microbatches=m)
+            assert cfg.stages_per_rank() == len(stages), \
+                f"schedule {cfg.schedule} needs {cfg.stages_per_rank()} stage(s) per rank, the model holds {len(stages)}: " \
+                "build it with parallelize_model(pp_config=...) or split_model() + PipelineStages"
+            d_model = stages[0].d_model
             dtype = next(self.model.parameters()).dtype
-            self._pp_schedule = PipelineSchedule([self.model], group, cfg, num_microbatches=m,
+            self._pp_schedule = PipelineSchedule(stages, group, cfg, num_microbatches=m,
                                                  hidden_shape=(c.micro_batch_size // m, c.sequence_length, d_model),
                                                  hidden_dtype=dtype)
         self.model.train()
@@ -346,11 +349,24 @@ class Trainer:
             if loss is not None:
                 total += loss.detach().float()
         total /= len(batches)
-        if len(batches) > 1:
+        if self._arena_opt:
+            self.optimizer.grad_divisor = float(len(batches))
+        elif len(batches) > 1:
             for p in self.model.parameters():
                 if p.grad is not None:
                     p.grad.div_(len(batches))
-        dist.broadcast(total, dist.get_global_rank(group, pp - 1), group=group)
+        if getattr(self.model, "is_dualpipe", False):
+            from ..parallel.pipeline_runtime import sync_twin_grads
+
+            sync_twin_grads(stages, group, grad_of=(lambda q: getattr(q, "main_grad", None)) if self._arena_opt
+                            else None)
+            # the loss lives on the last stage of each direction: ranks p-1 (even microbatches) and 0 (odd ones)
+            both = total.clone() if self._pp_schedule.rank in (0, pp - 1) else torch.zeros_like(total)
+            dist.all_reduce(both, group=group)
+            return both / (2 if pp > 1 else 1)
+        # the rank that holds the last stage (rank p-1 for loop placements, rank 0 for the V placement) has the loss
+        src = self._pp_schedule._rank_of(self._pp_schedule.total_stages - 1)
+        dist.broadcast(total, dist.get_global_rank(group, src), group=group)
         return total
 
     def _train_step(self, batches):
@@ -363,9 +379,17 @@ class Trainer:
         autocast_on = self.device.type == "cuda" and c.dtype in (torch.bfloat16, torch.float16) and \
             next(self.model.parameters()).dtype == torch.float32
         reducer = self._grad_reducer()
+        arena = getattr(self.optimizer, "arena", None) if self._arena_opt else None
+        if arena is not None:
+            # read by the bucket reductions launched during backward. Context-parallel ranks each hold their share of one
+            # sequence's gradient (the loss is already normalised by the global token count): those are summed, only
+            # the data-parallel replicas are averaged
+            self.optimizer.grad_divisor = float(accum) / max(self.config.cp_size, 1)
         for bi, (input_ids, labels) in enumerate(batches):
             if reducer is not None:
                 reducer.enabled = bi == accum - 1   # gradients accumulate locally; reduce on the last micro-batch
+            if arena is not None:
+                arena.reduce_enabled = bi == accum - 1
             input_ids = input_ids.to(self.device, non_blocking=True)
             labels = labels.to(self.device, non_blocking=True)
             kw = {}

@@ -1,6 +1,6 @@
-"""Multi-GPU checks (2 GPUs, NCCL + peer memory): symmetric heap, fused EP, sharded fused optimizer.
-Skipped when fewer than 2 GPUs are visible. NVLS is off in the child ranks and all in-tree kernels use
-plain peer loads / stores."""
+"""Multi-GPU checks (NCCL + peer memory): symmetric heap, fused EP, sharded fused optimizer, fused TP / CP / FSDP
+linears. Skipped when fewer than 2 GPUs are visible; the expert-parallel and data-parallel checks use as many of
+2 / 4 / 8 GPUs as there are. NVLS is off in the child ranks and all in-tree kernels use plain peer loads / stores."""
 import pytest
 import torch
 
@@ -12,6 +12,12 @@ pytestmark = pytest.mark.gpu
 def _need2():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
+
+
+def _world() -> int:
+    """The largest of 8 / 4 / 2 ranks the box has GPUs for."""
+    _need2()
+    return max(w for w in (2, 4, 8) if w <= torch.cuda.device_count())
 
 
 def rel(a, b):
@@ -63,7 +69,7 @@ def _ep_worker(rank, world):
 
     dev = torch.device("cuda", rank)
     torch.manual_seed(0)
-    B, S, D, H, E, K = 2, 256, 256, 256, 4, 2
+    B, S, D, H, E, K = 2, 256, 256, 256, 8, 2
     full = MoEBase(d_model=D, hidden_size=H, num_experts=E, top_k=K, capacity_factor=1.25, dtype=torch.bfloat16,
                    device=dev, init_std=0.05)
     ref = copy.deepcopy(full).float()
@@ -89,13 +95,14 @@ def _ep_worker(rank, world):
 
 
 def test_fused_expert_parallel_two_gpus():
-    _need2()
-    assert all(run_distributed(_ep_worker, 2, backend="nccl"))
+    assert all(run_distributed(_ep_worker, _world(), backend="nccl"))
 
 
-def _zero_worker(rank, world):
+def _zero_worker(rank, world, bucket, mode):
     import copy
+    import os
 
+    os.environ["NPB200_ZERO_MODE"] = mode
     import torch.distributed as dist
 
     from nanopysche_b200.config import TransformerConfig
@@ -109,8 +116,12 @@ def _zero_worker(rank, world):
     model = cfg.build(dtype=torch.bfloat16, init_device=str(dev))
     ref = copy.deepcopy(model).float()
     model._needs_grad_sync = True
+    if bucket:
+        os.environ["NPB200_ZERO_BUCKET"] = str(bucket)   # small buckets: several per region, some straddling layers
     opt, arena = prepare_training(model, dp_group=dist.group.WORLD, lr=1e-2, max_grad_norm=1.0)
     assert arena.zero
+    nb = max(r.n_buckets for r in arena.regions.values())
+    assert nb >= (4 if bucket else 1), nb
     ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.0)
     opt.param_groups[0]["weight_decay"] = 0.0
     torch.manual_seed(5 + rank)
@@ -129,16 +140,83 @@ def _zero_worker(rank, world):
     torch.cuda.synchronize()
     _lib.check_status("zero")
     w = model.blocks["0"].attention.w_q.weight
-    assert rel(w, ref.blocks["0"].attention.w_q.weight) < 2e-2
+    rp = dict(ref.named_parameters())
+    for n, p in model.named_parameters():   # bf16 against fp32 after three Adam steps at lr 1e-2
+        assert rel(p, rp[n]) < (2e-2 if "attention.w_q" in n else 8e-2), (n, rel(p, rp[n]))
     gathered = [torch.empty_like(w) for _ in range(world)]
     dist.all_gather(gathered, w.contiguous())
-    assert torch.equal(gathered[0], gathered[1])  # replicas stay bit-identical
+    assert all(torch.equal(gathered[0], g) for g in gathered[1:])  # replicas stay bit-identical
     return True
 
 
-def test_sharded_fused_optimizer_two_gpus():
-    _need2()
-    assert all(run_distributed(_zero_worker, 2, backend="nccl"))
+@pytest.mark.parametrize("bucket,mode", [(0, "copy"), (32768, "copy"), (32768, "kernel")])
+def test_sharded_fused_optimizer_two_gpus(bucket, mode):
+    """ZeRO step over N ranks equals the single-rank AdamW on the averaged gradients; with small buckets the
+    reduce-scatter of each bucket is launched from inside the backward pass on a side stream."""
+    assert all(run_distributed(_zero_worker, _world(), bucket, mode, backend="nccl"))
+
+
+def _model_ep_zero_worker(rank, world):
+    """The benchmark's structure at toy size: every FFN a MoE layer, experts spread over all ranks (fused dispatch /
+    combine over peer memory), the rest replicated with the sharded optimizer. Two steps must match one fp32 model
+    that sees all ranks' batches (dropless routing, so the result does not depend on how tokens are split)."""
+    import copy
+
+    import torch.distributed as dist
+
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.engine import prepare_training
+    from nanopysche_b200.models.moe import ExpertParallelConfig
+    from nanopysche_b200.ops import _lib
+    from nanopysche_b200.optim.adamw import is_no_decay
+
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    E, H = 8, 256
+    cfg = TransformerConfig(vocab_size=512, d_model=256, n_layers=2, n_heads=2, n_kv_heads=2, ffn_hidden=512,
+                            max_seq_len=128, qk_norm=False, rope_base=10000.0, use_moe=True, num_experts=E,
+                            moe_top_k=2, moe_interval=1, moe_offset=0, moe_hidden=H, moe_capacity_factor=None)
+    model = cfg.build(dtype=torch.bfloat16, init_device=str(dev))
+    ref = copy.deepcopy(model).float()
+    model.apply_ep(ExpertParallelConfig(ep_size=world, ep_group=dist.group.WORLD))
+    model._needs_grad_sync = True
+    opt, arena = prepare_training(model, tokens_per_rank=2 * 128, dp_group=dist.group.WORLD,
+                                  ep_group=dist.group.WORLD, lr=3e-3, weight_decay=0.1, max_grad_norm=1.0)
+    decay = [p for n, p in ref.named_parameters() if not is_no_decay(n, p)]
+    rest = [p for n, p in ref.named_parameters() if is_no_decay(n, p)]
+    ropt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": rest, "weight_decay": 0.0}], lr=3e-3,
+                             betas=(0.9, 0.95))
+    torch.manual_seed(7 + rank)
+    for _ in range(2):
+        ids = torch.randint(0, 512, (2, 128), device=dev)
+        allids = [torch.empty_like(ids) for _ in range(world)]
+        dist.all_gather(allids, ids)
+        out = model(ids, labels=ids)
+        out["loss"].backward()
+        opt.step()
+        opt.zero_grad()
+        outr = ref(torch.cat(allids), labels=torch.cat(allids))
+        outr["loss"].backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+        ropt.step()
+        ropt.zero_grad()
+        mean_loss = out["loss"].detach().float().clone()
+        dist.all_reduce(mean_loss)
+        assert abs(mean_loss.item() / world - outr["loss"].item()) < 2e-2 * outr["loss"].item()
+    torch.cuda.synchronize()
+    _lib.check_status("model ep+zero")
+    rp = dict(ref.named_parameters())
+    n_loc = E // world
+    for n, p in model.named_parameters():
+        r = rp[n]
+        if getattr(p, "_ep_sharded", False):
+            r = r[rank * n_loc * H:(rank + 1) * n_loc * H]
+        assert rel(p, r) < 3e-2, n
+    return True
+
+
+def test_model_expert_parallel_and_sharded_optimizer_match_one_rank():
+    assert all(run_distributed(_model_ep_zero_worker, _world(), backend="nccl", timeout=600))
 
 
 def _tp_fused_worker(rank, world):

@@ -39,8 +39,15 @@ def _pp_trainer_worker(rank, world, schedule):
         ref_losses.append(loss.item())
 
     mesh = build_world_mesh(pp_size=world, device_type="cpu", replace=True)
-    model = parallelize_model(model, world_mesh=mesh, pp_config=PipelineParallelConfig(world))
-    assert model._pp_enabled and len(model.blocks) == 4 // world
+    model = parallelize_model(model, world_mesh=mesh,
+                              pp_config=PipelineParallelConfig(world, schedule=schedule, num_microbatches=2))
+    multi = schedule not in ("1F1B", "GPipe")
+    assert model._pp_enabled
+    if multi:   # two stages per rank: interleaved / V placement cut the model in 2 * world, DualPipe keeps world stages twice
+        assert len(model.stages) == 2
+        assert sum(len(st.blocks) for st in model.stages) == (2 * (4 // world) if schedule == "DualPipe" else 4 // world)
+    else:
+        assert len(model.blocks) == 4 // world
     opt = torch.optim.AdamW(model.parameters(), lr=1e-2, weight_decay=0.0)
 
     class Loader:
@@ -75,11 +82,12 @@ def _pp_trainer_worker(rank, world, schedule):
         assert a == pytest.approx(b, rel=2e-4, abs=2e-5)
     # parameters of this stage followed the same trajectory as the single-process run
     for name, p in model.named_parameters():
-        assert torch.allclose(p, dict(ref.named_parameters())[name], atol=2e-4), name
+        rname = name.split(".", 2)[2] if name.startswith("stages.") else name
+        assert torch.allclose(p, dict(ref.named_parameters())[rname], atol=2e-4), name
     return True
 
 
-@pytest.mark.parametrize("schedule", ["1F1B", "GPipe"])
+@pytest.mark.parametrize("schedule", ["1F1B", "GPipe", "DualPipe", "ZBVZeroBubble", "InterleavedZeroBubble"])
 def test_trainer_runs_pipeline_stages(schedule):
     assert all(run_distributed(_pp_trainer_worker, 2, schedule))
 
