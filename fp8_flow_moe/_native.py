@@ -1,8 +1,9 @@
-"""Optional binding of the fp8 kernels in the in-tree sm_100a library (used when a GPU is present).
+"""Binding of this package's sm_100a kernels (used when a GPU is present).
 
-The package stays importable and fully functional without it: every operator has a PyTorch path.
-The library is looked up next to a sibling ``nanopysche_b200`` package or through
-``FP8_FLOW_MOE_LIB``.
+The package stays importable and fully functional without them: every operator has a PyTorch path. Lookup order:
+``FP8_FLOW_MOE_LIB``; the training framework's library when this package sits next to ``nanopysche_b200`` (it links
+the same sources, so one library is loaded per process); this package's own ``lib/libfp8flow.so``, built from
+``csrc/`` on first use when nvcc is there (``python -m fp8_flow_moe.build``).
 """
 from __future__ import annotations
 
@@ -73,10 +74,40 @@ class _Native:
         return qt, st
 
 
+    def expert_rank(self, indices, num_experts, pad_multiple):
+        n = indices.numel()
+        idx = indices.reshape(-1).to(torch.int64).contiguous()
+        row_map = torch.empty(n, device=idx.device, dtype=torch.int64)
+        padded = torch.empty(num_experts, device=idx.device, dtype=torch.int64)
+        self._check(self.lib.np_expert_rank(C.c_void_p(idx.data_ptr()), n, num_experts, pad_multiple,
+                                            C.c_void_p(row_map.data_ptr()), C.c_void_p(padded.data_ptr()),
+                                            self._stream()), "expert_rank")
+        return row_map, padded
+
+    def move_rows(self, x, out, row_map, weights, scatter):
+        w = weights.reshape(-1).float().contiguous() if weights is not None else None
+        self._check(self.lib.np_move_rows(C.c_void_p(x.data_ptr()), C.c_void_p(out.data_ptr()),
+                                          C.c_void_p(row_map.data_ptr()), C.c_void_p(w.data_ptr() if w is not None else 0),
+                                          C.c_longlong(row_map.numel()), C.c_longlong(x.shape[1] * x.element_size()),
+                                          int(scatter), self._stream()), "move_rows")
+        return out
+
+
 def native():
     global _NATIVE
     if _NATIVE is None:
-        cand = os.environ.get("FP8_FLOW_MOE_LIB") or str(
-            Path(__file__).resolve().parent.parent / "nanopysche_b200" / "lib" / "libnpb200.so")
+        here = Path(__file__).resolve().parent
+        cand = os.environ.get("FP8_FLOW_MOE_LIB")
+        if not cand:
+            sibling = here.parent / "nanopysche_b200" / "lib" / "libnpb200.so"
+            if sibling.exists():
+                cand = str(sibling)
+            else:
+                own = here / "lib" / "libfp8flow.so"
+                if not own.exists():
+                    from .build import build_extension
+
+                    build_extension()
+                cand = str(own)
         _NATIVE = _Native(C.CDLL(cand))
     return _NATIVE

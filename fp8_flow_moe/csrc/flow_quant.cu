@@ -7,7 +7,7 @@
 //   swiglu_quant     silu(gate) * up quantised in the same pass
 // Reference names: quantize_to_fp8 / dequantize_from_fp8 / scaling_aware_transpose /
 // fused_silu_multiply_quantize of the fp8_flow_moe package (fp8/__init__.py:8-22 of the reference).
-#include "common.cuh"
+#include "fp8_common.cuh"
 
 namespace {
 

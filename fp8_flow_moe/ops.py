@@ -23,14 +23,19 @@ FP8_DTYPE = torch.float8_e4m3fn
 
 def _kernels():
     """The ctypes kernel library if a GPU and the library are available, else None."""
-    if not torch.cuda.is_available():
-        return None
-    try:
-        from ._native import native
+    import os
 
-        return native()
-    except Exception:  # noqa: BLE001
+    if not torch.cuda.is_available() or os.environ.get("FP8_FLOW_MOE_NO_NATIVE", "0") == "1":
         return None
+    from ._native import native
+
+    try:
+        return native()
+    except Exception as e:  # noqa: BLE001
+        # on a GPU box the kernels are the product: say why they are missing instead of quietly running ATen ops
+        raise RuntimeError(f"fp8_flow_moe: a GPU is present but the kernel library could not be loaded or built ({e}); "
+                           "run `python -m fp8_flow_moe.build`, or set FP8_FLOW_MOE_NO_NATIVE=1 for the PyTorch "
+                           "path") from e
 
 
 def _pow2_ceil(s: torch.Tensor) -> torch.Tensor:
@@ -124,6 +129,14 @@ def fused_permute_pad(x: torch.Tensor, indices: torch.Tensor, num_experts: int, 
     each input row in the permuted tensor, tokens_per_expert [E] padded segment sizes)``.
     """
     n = x.shape[0]
+    k = _kernels()
+    if k is not None and x.is_cuda and n > 0 and x.is_contiguous() and (x.shape[1] * x.element_size()) % 16 == 0:
+        # counting-sort positions and the row scatter as kernels (no argsort); the output size depends on the data,
+        # so one scalar comes back to the host
+        row_map, padded = k.expert_rank(indices, num_experts, pad_multiple)
+        out = x.new_zeros((int(padded.sum().item()), x.shape[1]))
+        k.move_rows(x, out, row_map, None, scatter=True)
+        return out, row_map, padded
     order = torch.argsort(indices, stable=True)
     counts = torch.bincount(indices, minlength=num_experts)
     padded = (counts + pad_multiple - 1) // pad_multiple * pad_multiple
@@ -142,6 +155,11 @@ def fused_permute_pad(x: torch.Tensor, indices: torch.Tensor, num_experts: int, 
 def fused_unpermute_unpad(y: torch.Tensor, row_map: torch.Tensor, weights: Optional[torch.Tensor] = None
                           ) -> torch.Tensor:
     """Inverse of ``fused_permute_pad``: gather the original rows (optionally times a per-row weight)."""
+    k = _kernels()
+    if k is not None and y.is_cuda and y.is_contiguous() and (y.shape[1] * y.element_size()) % 16 == 0 and \
+            row_map.numel() > 0 and (weights is None or y.dtype == torch.bfloat16):
+        out = torch.empty((row_map.numel(), y.shape[1]), device=y.device, dtype=y.dtype)
+        return k.move_rows(y, out, row_map.to(torch.int64).contiguous(), weights, scatter=False)
     out = y[row_map]
     return out if weights is None else out * weights.reshape(-1, 1).to(out.dtype)
 

@@ -40,18 +40,21 @@ def find_nvcc() -> str | None:
     return None
 
 
+FP8_CSRC = PKG_DIR.parent / "fp8_flow_moe" / "csrc"   # the stand-alone fp8_flow_moe package's kernels, linked in too
+
+
 def sources() -> list[Path]:
-    return sorted(CSRC.glob("*.cu"))
+    return sorted(CSRC.glob("*.cu")) + (sorted(FP8_CSRC.glob("*.cu")) if FP8_CSRC.is_dir() else [])
 
 
 def _newest_header_mtime() -> float:
-    hs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
+    hs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + (list(FP8_CSRC.glob("*.cuh")) if FP8_CSRC.is_dir() else [])
     return max((h.stat().st_mtime for h in hs), default=0.0)
 
 
 def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> tuple[str, int, str]:
     extra = os.environ.get("NPB200_NVCC_EXTRA", "").split()   # e.g. -DNP_ATTN_PROF for a development build
-    cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(src.parent), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
     proc = subprocess.run(cmd, capture_output=True, text=True)

@@ -276,58 +276,6 @@ __global__ void __launch_bounds__(256) zero_reduce_staged_kernel(const float* __
   }
 }
 
-// One bucket of the overlapped gradient reduce-scatter. Launched on a side stream as soon as this rank's backward
-// pass has produced every gradient of the bucket: release "bucket b is final on rank r" on every rank, wait (bounded)
-// until all n ranks have said so, then sum this rank's slice of the bucket over all ranks' gradient buffers (peer
-// loads), scale it, store it into the compact shard buffer and add its sum of squares to *sumsq. A few CTAs are
-// enough: the transfer only has to finish before the end of the backward pass it runs under.
-constexpr int KID_ZERO_BUCKET = 21;
-__global__ void __launch_bounds__(256) zero_reduce_bucket_kernel(PeerPtrs grads, PeerPtrs flags, int flag_off,
-                                                                 int my_rank, int n, int epoch,
-                                                                 const int* __restrict__ epoch_base,
-                                                                 unsigned long long limit_ns, long long lo,
-                                                                 long long cnt, float scale, float* __restrict__ gshard,
-                                                                 float* __restrict__ sumsq) {
-  __shared__ float red[32];
-  __shared__ int s_ok;
-  np::CommSpan span(n > 1);
-  const int ep = epoch + (epoch_base ? *epoch_base : 0);
-  if (blockIdx.x == 0 && (int)threadIdx.x < n) {
-    __threadfence_system();
-    np::st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + flag_off + my_rank, ep);
-  }
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  if ((int)threadIdx.x < n &&
-      !np::wait_flag_ge(reinterpret_cast<int*>(flags.p[my_rank]) + flag_off + threadIdx.x, ep, limit_ns, KID_ZERO_BUCKET,
-                        threadIdx.x))
-    s_ok = 0;
-  __syncthreads();
-  if (!s_ok) return;
-  float ss = 0.f;
-  const long long nvec = cnt >> 2;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
-       i += (long long)gridDim.x * blockDim.x) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < n; ++r) {
-      const float4 g = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo)[i];
-      acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
-    }
-    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-    reinterpret_cast<float4*>(gshard)[i] = acc;
-    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
-  }
-  ss = np::warp_sum(ss);
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  if (l == 0) red[w] = ss;
-  __syncthreads();
-  if (w == 0) {
-    float t = l < 8 ? red[l] : 0.f;
-    t = np::warp_sum(t);
-    if (l == 0) atomicAdd(sumsq, t);
-  }
-}
-
 // The same two kernels through an NVLink multicast mapping of the gradient / weight arenas (NVLS): one
 // multimem.ld_reduce returns the sum over all ranks, formed inside the switch, so a rank receives its shard once
 // instead of once per peer; one multimem.st delivers the updated bf16 weights to every rank.
@@ -512,21 +460,6 @@ NP_API int np_zero_reduce(void* const* grad_ptrs, int n, long long lo, long long
   PeerPtrs g;
   for (int i = 0; i < n; ++i) g.p[i] = grad_ptrs[i];
   zero_reduce_kernel<<<np_zero_parts(), 256, 0, (cudaStream_t)stream>>>(g, n, lo, cnt, scale, gshard, partial);
-  CHECK_LAUNCH();
-}
-
-// Overlapped form of np_zero_reduce for one bucket (see zero_reduce_bucket_kernel). flag_ptrs[r]: rank r's bucket
-// flag array (n ints per bucket); lo: flat element offset of this rank's slice of the bucket; cnt: slice length;
-// gshard: destination inside the compact shard buffer; sumsq: one float that the kernel adds to.
-NP_API int np_zero_reduce_bucket(void* const* grad_ptrs, void* const* flag_ptrs, int bucket, int my_rank, int n,
-                                 int epoch, const int* epoch_base, unsigned long long limit_ns, long long lo,
-                                 long long cnt, float scale, float* gshard, float* sumsq, int ctas, void* stream) {
-  if (n > MAX_PEERS || (lo & 3) || (cnt & 3) || ctas <= 0) return 1;
-  PeerPtrs g, f;
-  for (int i = 0; i < n; ++i) { g.p[i] = grad_ptrs[i]; f.p[i] = flag_ptrs[i]; }
-  zero_reduce_bucket_kernel<<<ctas, 256, 0, (cudaStream_t)stream>>>(g, f, bucket * n, my_rank, n, epoch, epoch_base,
-                                                                   limit_ns ? limit_ns : NP_WAIT_LIMIT_NS, lo, cnt,
-                                                                   scale, gshard, sumsq);
   CHECK_LAUNCH();
 }
 

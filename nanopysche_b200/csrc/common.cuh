@@ -290,6 +290,8 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x))
 // ------------------------------------------------------------------ host helpers
 // "Done once" guard for settings CUDA keeps per device (cudaFuncSetAttribute): a process that drives several
 // GPUs has to repeat them on each one, so the flag is per device ordinal, not per process.
+#ifndef NP_PER_DEVICE_ONCE_DEFINED
+#define NP_PER_DEVICE_ONCE_DEFINED
 struct NpPerDeviceOnce {
   bool done[64] = {};
   bool* slot() {
@@ -298,6 +300,7 @@ struct NpPerDeviceOnce {
     return &done[dev & 63];
   }
 };
+#endif
 typedef CUresult (*NpEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                     const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                     const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,

@@ -28,6 +28,7 @@ WAIT_LIMIT_NS = int(float(os.environ.get("NPB200_WAIT_LIMIT_MS", "10000")) * 1e6
 # Single-device attention runs on the tcgen05 flash kernels whenever they cover the case; NPB200_SDPA=1 routes it
 # through PyTorch SDPA instead.
 USE_FLASH = os.environ.get("NPB200_SDPA", "0") != "1"
+PAD_SMALL_HEADS = os.environ.get("NPB200_PAD_SMALL_HEADS", "1") == "1"   # head_dim < 128 on the flash kernels, padded
 
 
 def attention_ref(q, k, v, causal=True, q_pos=None, k_pos=None, scale=None):
@@ -296,6 +297,16 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
     Hq, Hkv = q.shape[2], k.shape[2]
     if USE_FLASH and attn_mask is None and flash_supported(q, k) and (not causal or q.shape[1] <= k.shape[1]):
         return flash_attention(q, k, v, causal=causal, scale=scale)
+    hd = q.shape[-1]
+    if USE_FLASH and PAD_SMALL_HEADS and attn_mask is None and _lib.on(q) and q.dtype == torch.bfloat16 and \
+            k.dtype == torch.bfloat16 and hd < 128 and hd % 8 == 0 and (not causal or q.shape[1] <= k.shape[1]):
+        # head dims below 128 (the 125m / 350m / 1b presets have 64): zero-pad the head dimension so the tcgen05
+        # kernels apply. The padded columns add nothing to q.k and come out of P.V as zeros; the price is the work
+        # of the padding (twice the FLOPs and traffic at 64). ``NPB200_SDPA=1`` picks PyTorch's library kernel instead.
+        pad = (0, 128 - hd)
+        o = flash_attention(F.pad(q, pad), F.pad(k, pad), F.pad(v, pad), causal=causal,
+                            scale=scale if scale is not None else 1.0 / math.sqrt(hd))
+        return o[..., :hd]
     qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
     is_causal = causal and attn_mask is None and q.shape[1] == k.shape[1]
     if causal and not is_causal and attn_mask is None:

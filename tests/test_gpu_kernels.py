@@ -565,3 +565,28 @@ def test_flow_moe_power_of_two_block_quantisers_and_gemm():
     exact = torch.cat([x[i * 128:(i + 1) * 128].float() @ stacked.view(E, 2 * H, K)[g].float().t()
                        for i, g in enumerate(grp.tolist())])
     assert rel(got, exact) < 0.06
+
+
+def test_attention_head_dim_64_runs_on_the_flash_kernels_padded():
+    """head_dim 64 (the 125m / 350m / 1b presets): ``ops.attention.attention`` zero-pads the head dimension to 128
+    and runs the tcgen05 kernels; output and gradients match fp32 SDPA."""
+    from nanopysche_b200.ops import _lib
+    from nanopysche_b200.ops.attention import attention
+
+    torch.manual_seed(0)
+    B, S, Hq, Hkv, hd = 2, 384, 4, 2, 64
+    q = torch.randn(B, S, Hq, hd, device="cuda").bfloat16().requires_grad_(True)
+    k = torch.randn(B, S, Hkv, hd, device="cuda").bfloat16().requires_grad_(True)
+    v = torch.randn(B, S, Hkv, hd, device="cuda").bfloat16().requires_grad_(True)
+    l0 = _lib.LAUNCHES
+    o = attention(q, k, v, causal=True)
+    assert _lib.LAUNCHES > l0 and o.shape == (B, S, Hq, hd)
+    g = torch.randn_like(o)
+    o.backward(g)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    of = torch.nn.functional.scaled_dot_product_attention(qf.transpose(1, 2), kf.transpose(1, 2), vf.transpose(1, 2),
+                                                          is_causal=True, enable_gqa=True).transpose(1, 2)
+    of.backward(g.float())
+    assert rel(o, of) < 2e-2
+    for a, b in ((q, qf), (k, kf), (v, vf)):
+        assert rel(a.grad, b.grad) < 3e-2

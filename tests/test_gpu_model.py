@@ -244,8 +244,9 @@ def test_moe_layer_mxfp8_recipe_on_gpu():
 
 
 def test_cli_train_and_bench_on_gpu(tmp_path, capsys):
-    """The user-facing entry points on a GPU: a few optimizer steps of a small GQA + MoE model (head_dim 128, so the
-    flash-attention, fused-MoE and arena paths all run) and the forward benchmark, through ``cli.main``."""
+    """The user-facing entry points on a GPU: a few optimizer steps of the 125m preset with MoE layers (12 heads of
+    dim 64: attention runs on the flash kernels with the head dimension zero-padded to 128; fused-MoE and arena
+    paths) and the forward benchmark, through ``cli.main``."""
     from nanopysche_b200 import cli
     from nanopysche_b200.ops import _lib
 
