@@ -121,6 +121,44 @@ def fused_swiglu_quantize(gate_up: torch.Tensor, block_size: int = FP8_BLOCK_SIZ
     return fused_silu_multiply_quantize(g.contiguous(), u.contiguous(), block_size)
 
 
+class _ScatterRows(torch.autograd.Function):
+    """``out[row_map[i]] = x[i]`` into ``total`` zero rows (kernel); backward gathers."""
+
+    @staticmethod
+    def forward(ctx, x, row_map, total):
+        ctx.save_for_backward(row_map)
+        out = x.new_zeros((total, x.shape[1]))
+        return _kernels().move_rows(x, out, row_map, None, scatter=True)
+
+    @staticmethod
+    def backward(ctx, g):
+        (row_map,) = ctx.saved_tensors
+        g = g if g.is_contiguous() else g.contiguous()
+        dx = torch.empty((row_map.numel(), g.shape[1]), device=g.device, dtype=g.dtype)
+        return _kernels().move_rows(g, dx, row_map, None, scatter=False), None, None
+
+
+class _GatherRows(torch.autograd.Function):
+    """``out[i] = y[row_map[i]] * w[i]`` (kernel); backward scatters ``g * w`` and reduces ``<g, y>`` per row."""
+
+    @staticmethod
+    def forward(ctx, y, row_map, weights):
+        ctx.save_for_backward(y, row_map, weights if weights is not None else y.new_empty(0))
+        ctx.has_w = weights is not None
+        out = torch.empty((row_map.numel(), y.shape[1]), device=y.device, dtype=y.dtype)
+        return _kernels().move_rows(y, out, row_map, weights, scatter=False)
+
+    @staticmethod
+    def backward(ctx, g):
+        y, row_map, w = ctx.saved_tensors
+        g = g if g.is_contiguous() else g.contiguous()
+        gw = g * w.reshape(-1, 1).to(g.dtype) if ctx.has_w else g
+        dy = _kernels().move_rows(gw.contiguous(), y.new_zeros(y.shape), row_map, None, scatter=True)
+        dw = (g.float() * y[row_map].float()).sum(-1).reshape(w.shape).to(w.dtype) if ctx.has_w and \
+            ctx.needs_input_grad[2] else None
+        return dy, None, dw
+
+
 def fused_permute_pad(x: torch.Tensor, indices: torch.Tensor, num_experts: int, pad_multiple: int = FP8_BLOCK_SIZE
                       ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Sort rows by expert and pad every expert segment to a multiple of ``pad_multiple``.
@@ -134,9 +172,7 @@ def fused_permute_pad(x: torch.Tensor, indices: torch.Tensor, num_experts: int, 
         # counting-sort positions and the row scatter as kernels (no argsort); the output size depends on the data,
         # so one scalar comes back to the host
         row_map, padded = k.expert_rank(indices, num_experts, pad_multiple)
-        out = x.new_zeros((int(padded.sum().item()), x.shape[1]))
-        k.move_rows(x, out, row_map, None, scatter=True)
-        return out, row_map, padded
+        return _ScatterRows.apply(x, row_map, int(padded.sum().item())), row_map, padded
     order = torch.argsort(indices, stable=True)
     counts = torch.bincount(indices, minlength=num_experts)
     padded = (counts + pad_multiple - 1) // pad_multiple * pad_multiple
@@ -158,8 +194,7 @@ def fused_unpermute_unpad(y: torch.Tensor, row_map: torch.Tensor, weights: Optio
     k = _kernels()
     if k is not None and y.is_cuda and y.is_contiguous() and (y.shape[1] * y.element_size()) % 16 == 0 and \
             row_map.numel() > 0 and (weights is None or y.dtype == torch.bfloat16):
-        out = torch.empty((row_map.numel(), y.shape[1]), device=y.device, dtype=y.dtype)
-        return k.move_rows(y, out, row_map.to(torch.int64).contiguous(), weights, scatter=False)
+        return _GatherRows.apply(y, row_map.to(torch.int64).contiguous(), weights)
     out = y[row_map]
     return out if weights is None else out * weights.reshape(-1, 1).to(out.dtype)
 

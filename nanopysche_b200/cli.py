@@ -66,6 +66,9 @@ def build_parser() -> argparse.ArgumentParser:
     common.add_argument("--cp-size", type=int, default=1)
     common.add_argument("--ep-size", type=int, default=1)
     common.add_argument("--fsdp", action="store_true")
+    common.add_argument("--dp-replicate", type=int, default=1,
+                        help="hybrid sharding (HSDP): number of replicas of the sharded state; the data-parallel "
+                             "ranks split into dp_replicate x dp_shard")
     common.add_argument("--fsdp-backend", choices=["auto", "torch", "arena", "sharded"], default="auto",
                         help="sharded: linear weights sharded by rows, gathered inside their GEMMs (CUDA)")
     common.add_argument("--ac-mode", choices=["full", "selected_blocks"], default=None)
@@ -204,8 +207,14 @@ def _maybe_parallelize_model(model, args, device):
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             os.environ.setdefault("MASTER_PORT", "29533")
             dist.init_process_group("gloo" if device.type == "cpu" else "nccl", rank=0, world_size=1)
+        rep = max(getattr(args, "dp_replicate", 1), 1)
+        hsdp = {}
+        if rep > 1:
+            dp_total = world // (args.tp_size * args.pp_size * args.cp_size * args.ep_size)
+            assert dp_total % rep == 0, "--dp-replicate must divide the data-parallel size"
+            hsdp = dict(dp_replicate=rep, dp_shard=dp_total // rep)
         mesh = build_world_mesh(tp_size=args.tp_size, pp_size=args.pp_size, cp_size=args.cp_size,
-                                ep_size=args.ep_size, device_type=device.type, replace=True)
+                                ep_size=args.ep_size, device_type=device.type, replace=True, **hsdp)
     model = parallelize_model(
         model, world_mesh=mesh, device=device,
         tp_config=TensorParallelConfig(args.tp_size, enable_async=getattr(args, "async_tp", False),

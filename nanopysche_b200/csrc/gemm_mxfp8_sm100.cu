@@ -385,7 +385,8 @@ __device__ __forceinline__ void load8_bf16(const __nv_bfloat16* p, float* f) {
 // quantised value is silu(gate) * up (the expert MLP's hidden activation), else the input itself.
 __global__ void __launch_bounds__(256) flow_quant_act_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                                              uint8_t* __restrict__ q, long long ldq,
-                                                             uint8_t* __restrict__ sf, int rows, int K, int swiglu) {
+                                                             uint8_t* __restrict__ sf, int rows, int K, int swiglu,
+                                                             __nv_bfloat16* __restrict__ h_out, long long ldh) {
   const int nkb = K >> 7;
   const long long total = (long long)rows * nkb;
   const int lane = threadIdx.x & 31, half = lane >> 4, l16 = lane & 15;
@@ -405,6 +406,10 @@ __global__ void __launch_bounds__(256) flow_quant_act_kernel(const __nv_bfloat16
         load8_bf16(src + K, u);
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = np::silu_f(f[j]) * u[j];
+        if (h_out)   // the unquantised activation too (the weight gradient of the down projection wants it)
+          *reinterpret_cast<uint4*>(h_out + row * ldh + kb * 128 + l16 * 8) =
+              make_uint4(np::pack_bf16(f[0], f[1]), np::pack_bf16(f[2], f[3]), np::pack_bf16(f[4], f[5]),
+                         np::pack_bf16(f[6], f[7]));
       }
     }
     float am = 0.f;
@@ -589,16 +594,18 @@ NP_API int np_mx_quant(const void* x, long long ldx, void* q, long long ldq, voi
 }
 
 // bf16 [rows, K] (or, with `swiglu`, [rows, 2K] = [gate | up] quantising silu(gate) * up) -> e4m3 [rows, K] with one
-// power-of-two scale per 1x128 block, exponent bytes in the chunk layout. K a multiple of 128.
+// power-of-two scale per 1x128 block, exponent bytes in the chunk layout. K a multiple of 128. With `swiglu`, `h_out`
+// (optional, row stride ldh elements) also receives silu(gate) * up in bf16.
 NP_API int np_flow_quant_act(const void* x, long long ldx, void* q, long long ldq, void* sf, int rows, int K,
-                             int swiglu, void* stream) {
+                             int swiglu, void* h_out, long long ldh, void* stream) {
   if (rows <= 0) return 0;
   if (K % 128 || (ldx % 8) || (ldq % 8) || (((uintptr_t)x) & 15) || (((uintptr_t)q) & 7) || (((uintptr_t)sf) & 3)) return 1;
   const long long total = (long long)rows * (K / 128);
   long long blocks = (total + 15) / 16;   // 8 warps x 2 blocks per CTA iteration
   if (blocks > 148 * 128) blocks = 148 * 128;
   flow_quant_act_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq,
-                                                                        (uint8_t*)sf, rows, K, swiglu);
+                                                                        (uint8_t*)sf, rows, K, swiglu,
+                                                                        (__nv_bfloat16*)h_out, ldh);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 500 + (int)e;
 }

@@ -22,10 +22,13 @@ def moe_layers(model: nn.Module) -> list:
 
 
 def prepare_training(model: nn.Module, *, tokens_per_rank: Optional[int] = None, dp_group=None, ep_group=None,
+                     replicate_group=None,
                      lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1,
                      max_grad_norm: Optional[float] = 1.0, fused_moe: bool = True):
     """Returns ``(optimizer, arena | None)``. ``dp_group``: ranks holding replicas of the non-expert
-    parameters (their gradients are averaged); ``ep_group``: ranks the experts are spread over."""
+    parameters (their gradients are averaged; optimizer state is sharded over them); ``ep_group``: ranks the
+    experts are spread over; ``replicate_group``: under hybrid sharding (HSDP) the ranks that hold the same
+    optimizer shard (``dp_group`` is then the shard group)."""
     p0 = next(model.parameters())
     if dp_group is not None and dist.is_initialized() and dist.get_world_size(dp_group) <= 1:
         dp_group = None
@@ -41,7 +44,9 @@ def prepare_training(model: nn.Module, *, tokens_per_rank: Optional[int] = None,
                              "that hold replicas of this rank's parameters) - averaging over the whole world would "
                              "mix different shards")
         dp_group = dist.group.WORLD
-    arena = ParamArena(model, dp_group=dp_group, device=p0.device)
+    if replicate_group is None:
+        replicate_group = getattr(model, "_replicate_group", None)   # HSDP: set by parallelize_model
+    arena = ParamArena(model, dp_group=dp_group, device=p0.device, replicate_group=replicate_group)
     moes = moe_layers(model)
     if moes and fused_moe and tokens_per_rank:
         from .ops.moe import build_runtime

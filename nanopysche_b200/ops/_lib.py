@@ -191,7 +191,8 @@ def lib():
     _LIB.np_gemm_fp8_block.argtypes = [C.POINTER(Fp8GemmArgs), c_void_p]
     _LIB.np_gemm_mxfp8.argtypes = [C.POINTER(MxGemmArgs), c_void_p]
     _LIB.np_mx_quant.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p]
-    _LIB.np_flow_quant_act.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_void_p]
+    _LIB.np_flow_quant_act.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_void_p, c_ll,
+                                        c_void_p]
     _LIB.np_mx_dequant.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p]
     _LIB.np_flow_quant_weight.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_void_p]

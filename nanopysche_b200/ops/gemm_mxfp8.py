@@ -99,12 +99,17 @@ def flow_quantize_act_ref(x: torch.Tensor, swiglu: bool = False):
     return q, sf
 
 
-def flow_quantize_act(x: torch.Tensor, swiglu: bool = False, out=None):
+def flow_quantize_act(x: torch.Tensor, swiglu: bool = False, out=None, h_out: Optional[torch.Tensor] = None):
     """bf16 ``[rows, K]`` -> ``(e4m3 [rows, K], exponent chunks)`` with 1x128 power-of-two scales (FP8-Flow-MoE
     activations in the form the block-scaled tensor-core MMA consumes). ``swiglu``: ``x`` is ``[rows, 2K]`` =
-    ``[gate | up]`` and ``silu(gate) * up`` is what gets quantised (the reference's ``fused_swiglu_quantize``)."""
+    ``[gate | up]`` and ``silu(gate) * up`` is what gets quantised (the reference's ``fused_swiglu_quantize``);
+    ``h_out`` (bf16 ``[rows, K]``) then also receives the unquantised product."""
     if not x.is_cuda:
-        return flow_quantize_act_ref(x, swiglu)
+        q, sf = flow_quantize_act_ref(x, swiglu)
+        if h_out is not None:
+            g, u = x.float().chunk(2, dim=-1)
+            h_out.copy_((torch.nn.functional.silu(g) * u).to(h_out.dtype))
+        return q, sf
     rows = x.shape[0]
     K = x.shape[1] // 2 if swiglu else x.shape[1]
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and K % 128 == 0
@@ -116,6 +121,8 @@ def flow_quantize_act(x: torch.Tensor, swiglu: bool = False, out=None):
     _lib.check(_lib.lib().np_flow_quant_act(C.c_void_p(x.data_ptr()), C.c_longlong(x.stride(0)),
                                             C.c_void_p(q.data_ptr()), C.c_longlong(q.stride(0)),
                                             C.c_void_p(sf.data_ptr()), rows, K, int(swiglu),
+                                            C.c_void_p(h_out.data_ptr() if h_out is not None else 0),
+                                            C.c_longlong(h_out.stride(0) if h_out is not None else 0),
                                             C.c_void_p(_lib.stream())), "flow_quant_act")
     return q, sf
 

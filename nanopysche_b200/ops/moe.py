@@ -370,7 +370,8 @@ class _FusedMoE(torch.autograd.Function):
                         p_scales=rt.p_recv_xs[layer])
             xq, xs = rt.recv_xq[layer].view(torch.float8_e4m3fn), rt.recv_xs[layer]
             rt.grouped_gemm_fp8(xq, xs, w13q, s13, N=2 * H, out=gu, wait_epoch=e1)
-            hq, hs = flow_quantize_act(gu, swiglu=True)
+            h = torch.empty((rt.rows_total, H), device=dev, dtype=torch.bfloat16)
+            hq, hs = flow_quantize_act(gu, swiglu=True, h_out=h)
             rt.grouped_gemm_fp8(hq, hs, w2q, s2, N=D, push_ptrs=rt.p_ret_y[layer], push_epoch=e1)
         else:
             rt.dispatch(x2, indices32, slot_pos, counts_kept, None, rt.p_recv_x[layer], e1)
@@ -389,9 +390,9 @@ class _FusedMoE(torch.autograd.Function):
             add1 = shared.reshape(T, D) * keep.to(shared.dtype).unsqueeze(1)
         rt.combine(rt.ret_y[layer], slot_pos, weights, out, sent, e1, add1=add1)
         ctx.has_shared = shared is not None
-        # the bf16 path keeps the activation h for the w2 weight gradient (57 MB per layer at the 1B shapes: cheap next
-        # to re-reading the pre-activations); the fp8 path recomputes it from them
-        ctx.has_h = not rt.fp8
+        # the activation h is kept for the w2 weight gradient (57 MB per layer at the 1B shapes: cheap next to
+        # re-reading the pre-activations)
+        ctx.has_h = True
         ctx.save_for_backward(x2, weights, indices32, slot_pos, counts_kept, sent, gu, w1, w3, w2,
                               *([h] if ctx.has_h else []), *([keep] if ctx.has_shared else []))
         ctx.rt, ctx.layer = rt, layer

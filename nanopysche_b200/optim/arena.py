@@ -68,7 +68,7 @@ class _Region:
 
 class ParamArena:
     def __init__(self, model: nn.Module, *, dp_group=None, device=None, use_symmetric: Optional[bool] = None,
-                 bucket_elems: Optional[int] = None):
+                 bucket_elems: Optional[int] = None, replicate_group=None):
         params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
         assert params, "model has no trainable parameters"
         self.model = model
@@ -76,6 +76,11 @@ class ParamArena:
         self.dp_group = dp_group
         self.world = dist.get_world_size(dp_group) if (dp_group is not None and dist.is_initialized()) else 1
         self.rank = dist.get_rank(dp_group) if self.world > 1 else 0
+        # hybrid sharding (HSDP): optimizer state and gradients are sharded over ``dp_group`` and every shard is
+        # replicated over ``replicate_group``; reduced gradient shards are summed across the replicas before the update
+        self.replicate_group = replicate_group
+        self.rep_world = dist.get_world_size(replicate_group) if (replicate_group is not None and
+                                                                  dist.is_initialized()) else 1
         cuda = self.device.type == "cuda"
         self.zero = self.world > 1 and cuda if use_symmetric is None else bool(use_symmetric)
         import os as _os
@@ -111,7 +116,8 @@ class ParamArena:
             r.offsets.append(off)
             r.numel = off + p.numel()
         self.heap = None
-        self.grad_inv = 1.0 / max(self.world, 1)   # scale of the reduced gradients (set by the optimizer every step)
+        # scale of the reduced gradients (set by the optimizer every step)
+        self.grad_inv = 1.0 / (max(self.world, 1) * max(self.rep_world, 1))
         if self.zero:
             from ..parallel.symm import SymmetricHeap
 
@@ -407,7 +413,7 @@ class ArenaAdamW(torch.optim.Optimizer):
         # the overlapped bucket reductions run during the backward pass, before step(): they read the scale here
         self._grad_divisor = float(v)
         a = self.arena
-        a.grad_inv = 1.0 / (self._grad_divisor * (a.world if a.world > 1 else 1))
+        a.grad_inv = 1.0 / (self._grad_divisor * (a.world if a.world > 1 else 1) * max(a.rep_world, 1))
 
     def zero_grad(self, set_to_none: bool = True):
         self.arena.zero_grad()
@@ -436,7 +442,8 @@ class ArenaAdamW(torch.optim.Optimizer):
         if not self._cuda:
             return self._step_reference(lr, b1, b2, eps, wd)
         N = a.world
-        inv = 1.0 / (self.grad_divisor * (N if N > 1 else 1))
+        R = a.rep_world
+        inv = 1.0 / (self.grad_divisor * (N if N > 1 else 1) * R)
         stride = self._partial.numel() // len(a.regions)
         self._partial.zero_()
         bucketed = a.zero and any(r.bucket for r in a.regions.values())
@@ -455,6 +462,10 @@ class ArenaAdamW(torch.optim.Optimizer):
                     C.c_void_p(r.staged.data_ptr()), N - 1, C.c_longlong(r.cnt), C.c_float(inv),
                     C.c_void_p(r.gshard.data_ptr()), C.c_void_p(part.data_ptr()), C.c_void_p(_lib.stream())),
                     "zero_reduce_staged")
+                if R > 1:   # HSDP: sum the shard over the replicas, then take its norm
+                    dist.all_reduce(r.gshard, group=a.replicate_group)
+                    part.zero_()
+                    _lib.call("sumsq", r.gshard, _lib.LL(r.gshard.numel()), part)
             elif a.zero and r.replicated and r.dtype == torch.bfloat16 and r.mc_grads:
                 _lib.check(_lib.lib().np_zero_reduce_mc(C.c_void_p(r.mc_grads), C.c_longlong(r.lo), C.c_longlong(r.cnt),
                                                         C.c_float(inv), C.c_void_p(r.gshard.data_ptr()),
@@ -466,12 +477,18 @@ class ArenaAdamW(torch.optim.Optimizer):
                                                      C.c_float(inv), C.c_void_p(r.gshard.data_ptr()),
                                                      C.c_void_p(part.data_ptr()), C.c_void_p(_lib.stream())),
                            "zero_reduce")
+                if R > 1:
+                    dist.all_reduce(r.gshard, group=a.replicate_group)
+                    part.zero_()
+                    _lib.call("sumsq", r.gshard, _lib.LL(r.gshard.numel()), part)
             else:
                 if N > 1 and r.replicated:  # small fp32 region: all-reduce through peer memory (NCCL otherwise)
                     if a.zero:
                         a.heap.all_reduce_(r.grads)
                     else:
                         dist.all_reduce(r.grads, group=a.dp_group)
+                if R > 1 and r.replicated:
+                    dist.all_reduce(r.grads, group=a.replicate_group)
                 _lib.call("sumsq", r.grads, _lib.LL(r.grads.numel()), part)
                 # scale of these gradients relative to the final ones: inv; replicated ones are counted
                 # once per rank in the global sum below
@@ -561,12 +578,14 @@ class ArenaAdamW(torch.optim.Optimizer):
         """CPU path: same math with torch ops (also the oracle of the kernels)."""
         a = self.arena
         N = a.world
-        inv = 1.0 / (self.grad_divisor * (N if N > 1 else 1))
+        inv = 1.0 / (self.grad_divisor * (N if N > 1 else 1) * a.rep_world)
         sq = torch.zeros(2, dtype=torch.float32, device=a.device)   # [whole parameters, tensor-parallel shards]
         tpg = None
         for r in a.regions.values():
             if N > 1 and r.replicated:
                 dist.all_reduce(r.grads, group=a.dp_group)
+            if a.rep_world > 1 and r.replicated:
+                dist.all_reduce(r.grads, group=a.replicate_group)
             s = (r.grads.float() * inv).pow(2).sum()
             sq[1 if r.tp_group is not None else 0] += s / (N if (N > 1 and r.replicated) else 1)
             tpg = r.tp_group if r.tp_group is not None else tpg

@@ -143,6 +143,27 @@ def get_ep_mesh(world_mesh: Optional[DeviceMesh] = None):
     return None
 
 
+def get_hsdp_groups(world_mesh: Optional[DeviceMesh] = None):
+    """``(shard_group, replicate_group)`` when the mesh has ``dp_replicate`` and ``dp_shard`` dims (hybrid sharding):
+    state is sharded over dp_shard (x ep x cp) and replicated over dp_replicate. ``(None, None)`` otherwise."""
+    mesh = world_mesh or _WORLD_MESH
+    if mesh is None:
+        return None, None
+    names = _names(mesh)
+    if MeshDimName.dp_replicate not in names or MeshDimName.dp_shard not in names:
+        return None, None
+    if mesh[MeshDimName.dp_replicate].size() <= 1:
+        return None, None
+    inner = [n for n in names if n in (MeshDimName.dp_shard, MeshDimName.ep, MeshDimName.cp) and mesh[n].size() > 1]
+    if not inner:
+        shard = None
+    elif len(inner) == 1:
+        shard = mesh[inner[0]].get_group()
+    else:
+        shard = mesh[tuple(inner)]._flatten("hsdp_shard").get_group()
+    return shard, mesh[MeshDimName.dp_replicate].get_group()
+
+
 def get_replica_group(world_mesh: Optional[DeviceMesh] = None):
     """Process group of the ranks that hold the *same* (non-expert) parameters as this rank and see different
     tokens: the product of the dp (or dp_replicate x dp_shard), ep and cp dims. Gradients of replicated parameters

@@ -19,8 +19,8 @@ from .models.parallel_adapter import ensure_parallel_hooks
 from .models.protocol import warn_unsupported_parallelism
 from .parallel.context_parallel import ContextParallelConfig
 from .parallel.fsdp import DataParallelConfig, apply_activation_checkpointing, apply_generic_fsdp
-from .parallel.mesh import (MeshDimName, get_cp_mesh, get_dp_model_mesh, get_ep_mesh, get_pp_mesh, get_replica_group,
-                            get_tp_mesh)
+from .parallel.mesh import (MeshDimName, get_cp_mesh, get_dp_model_mesh, get_ep_mesh, get_hsdp_groups, get_pp_mesh,
+                            get_replica_group, get_tp_mesh)
 from .parallel.tensor_parallel import TensorParallelConfig
 
 log = logging.getLogger(__name__)
@@ -125,7 +125,11 @@ def parallelize_model(model: nn.Module, *, world_mesh, device: Optional[torch.de
         if use_arena:
             # sharded optimizer state + fused reduce-scatter/AdamW/all-gather: set up by engine.prepare_training
             model._dp_mesh_for_arena = dp_mesh
-            model._replica_group = get_replica_group(world_mesh)   # read by engine.prepare_training
+            shard_g, rep_g = get_hsdp_groups(world_mesh)
+            if rep_g is not None:      # HSDP: shard over dp_shard, replicate over dp_replicate
+                model._replica_group, model._replicate_group = shard_g, rep_g
+            else:
+                model._replica_group = get_replica_group(world_mesh)   # read by engine.prepare_training
             model._needs_grad_sync = True
         elif hasattr(model, "apply_fsdp"):
             model.apply_fsdp(dp_mesh=dp_mesh, param_dtype=dp_config.param_dtype, reduce_dtype=dp_config.reduce_dtype)

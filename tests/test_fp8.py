@@ -192,3 +192,30 @@ def test_rmsnorm_with_fp8_output_cpu_path():
     y_ref, h_ref = rms_norm_ref(x, w, 1e-6, res)
     assert torch.equal(h, h_ref) and torch.equal(y, y_ref) and q.shape == (10, 256) and s.shape == (10, 2)
     assert ((ops.dequantize_from_fp8(q, s, dtype=torch.float32) - y_ref).norm() / y_ref.norm()).item() < 0.04
+
+
+@pytest.mark.gpu
+def test_permute_pad_kernels_match_the_sorting_statement_and_differentiate():
+    """``fused_permute_pad`` / ``fused_unpermute_unpad`` on the GPU (counting-sort positions + row kernels) against the
+    argsort statement of the same functions on CPU tensors, values and gradients."""
+    torch.manual_seed(3)
+    n, D, E = 777, 256, 5
+    x = torch.randn(n, D, device="cuda").bfloat16()
+    idx = torch.randint(0, E, (n,), device="cuda")
+    idx[idx == 3] = 2                                    # an expert with no rows
+    w = torch.rand(n, device="cuda")
+    xa = x.clone().requires_grad_(True)
+    wa = w.clone().requires_grad_(True)
+    out, row_map, padded = ops.fused_permute_pad(xa, idx, E, 128)
+    back = ops.fused_unpermute_unpad(out * 2.0, row_map, wa)
+    back.float().pow(2).sum().backward()
+    xc = x.cpu().float().requires_grad_(True)
+    wc = w.cpu().clone().requires_grad_(True)
+    out_c, map_c, pad_c = ops.fused_permute_pad(xc, idx.cpu(), E, 128)
+    back_c = ops.fused_unpermute_unpad(out_c * 2.0, map_c, wc)
+    back_c.pow(2).sum().backward()
+    assert torch.equal(row_map.cpu(), map_c) and torch.equal(padded.cpu(), pad_c)
+    assert torch.equal(out.float().cpu(), out_c.detach().bfloat16().float())
+    assert ((back.float().cpu() - back_c.detach()).norm() / back_c.detach().norm()).item() < 1e-2
+    assert ((xa.grad.float().cpu() - xc.grad).norm() / xc.grad.norm()).item() < 2e-2
+    assert ((wa.grad.cpu() - wc.grad).norm() / wc.grad.norm()).item() < 2e-2

@@ -435,3 +435,58 @@ def _ddp_worker(rank, world):
 
 def test_bucketed_grad_reducer_matches_full_batch():
     assert all(run_distributed(_ddp_worker, 2))
+
+
+def _hsdp_worker(rank, world, backend):
+    """dp_replicate 2 x dp_shard 2 on four ranks, both back ends: PyTorch FSDP2 over the 2-D mesh and the parameter
+    arena (shard over dp_shard, sum over dp_replicate). One step equals the unsharded model on the whole batch."""
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.optim.arena import ArenaAdamW, ParamArena
+    from nanopysche_b200.parallel.fsdp import DataParallelConfig, DataParallelType
+    from nanopysche_b200.parallel.mesh import ParallelDims
+    from nanopysche_b200.parallelize import parallelize_model
+
+    torch.manual_seed(0)
+    cfg = TransformerConfig(vocab_size=64, d_model=32, n_layers=2, n_heads=4, n_kv_heads=2, ffn_hidden=64,
+                            max_seq_len=16, qk_norm=False)
+    full = cfg.build()
+    model = copy.deepcopy(full)
+    dims = ParallelDims(dp_shard=2, dp_replicate=2)
+    mesh = dims.build_mesh("cpu")
+    assert tuple(mesh.mesh_dim_names) == ("pp", "dp_replicate", "dp_shard")
+    torch.manual_seed(1)
+    ids = torch.randint(0, 64, (8, 16))
+    mine = ids[rank * 2:(rank + 1) * 2]
+    model = parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"),
+                              dp_config=DataParallelConfig(name=DataParallelType.hsdp, backend=backend))
+    if backend == "torch":
+        assert model._fsdp_enabled
+        loss = model(mine, labels=mine)["loss"]
+        loss.backward()
+        ref_loss = full(ids, labels=ids)["loss"]
+        ref_loss.backward()
+        tot = loss.detach().clone()
+        dist.all_reduce(tot)
+        assert abs(tot.item() / world - ref_loss.item()) < 1e-5
+        g = model.blocks["0"].attention.w_q.weight.grad.full_tensor()   # sharded over dp_shard, averaged over all
+        assert torch.allclose(g, full.blocks["0"].attention.w_q.weight.grad, atol=1e-5)
+        return True
+    assert model._replicate_group is not None and dist.get_world_size(model._replica_group) == 2
+    arena = ParamArena(model, dp_group=model._replica_group, replicate_group=model._replicate_group,
+                       device=torch.device("cpu"))
+    opt = ArenaAdamW(arena, lr=1e-2, max_grad_norm=0.05)
+    model(mine, labels=mine)["loss"].backward()
+    opt.step()
+    a0 = ParamArena(full, device=torch.device("cpu"))
+    o0 = ArenaAdamW(a0, lr=1e-2, max_grad_norm=0.05)
+    full(ids, labels=ids)["loss"].backward()
+    o0.step()
+    assert abs(float(opt.last_grad_norm) - float(o0.last_grad_norm)) < 1e-4 * float(o0.last_grad_norm) + 1e-6
+    for (n, p), q in zip(model.named_parameters(), full.parameters()):
+        assert torch.allclose(p, q, atol=2e-5, rtol=1e-4), n
+    return True
+
+
+@pytest.mark.parametrize("backend", ["torch", "arena"])
+def test_hybrid_sharded_data_parallel_four_ranks(backend):
+    assert all(run_distributed(_hsdp_worker, 4, backend))
