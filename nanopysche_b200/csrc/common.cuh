@@ -135,6 +135,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+}  // namespace np
+// Debug-bounds build: compile with -DNP_DEBUG (NPB200_NVCC_EXTRA=-DNP_DEBUG python -m nanopysche_b200.build --force).
+// compute-sanitizer is not always available; these index predicates record (code 4, kernel id, block, offending
+// value) in the status word and skip the access instead of trapping, so that a wrong index shows up as a readable
+// status after the launch. In a normal build they compile to nothing.
+#ifdef NP_DEBUG
+#define NP_DBG_SKIP_UNLESS(cond, kid, detail) \
+  if (!(cond)) {                              \
+    np::report(NP_ERR_BOUNDS, kid, (int)(detail)); \
+    continue;                                 \
+  }
+#else
+#define NP_DBG_SKIP_UNLESS(cond, kid, detail)
+#endif
+namespace np {
 // ------------------------------------------------------------------ global flags
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;

@@ -1126,6 +1126,7 @@ __global__ void __launch_bounds__(256) embedding_bwd_kernel(const __nv_bfloat16*
     const long long t = i / vec_per_row;
     const int d = (int)(i - t * vec_per_row) * 4;
     const long long row = ids[t];
+    NP_DBG_SKIP_UNLESS(row >= 0 && row < V, 40, row)   // a token id outside the vocabulary (debug build: reported)
     if (row < 0 || row >= V) continue;
     const uint2 u = *reinterpret_cast<const uint2*>(dy + t * D + d);
     const float2 a = np::unpack_bf16(u.x), b = np::unpack_bf16(u.y);

@@ -585,6 +585,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const DispatchParams p
       pos = p.slot_pos[it];
       if (pos < 0) continue;
       e = p.indices[it];
+      NP_DBG_SKIP_UNLESS(e >= 0 && e < p.E, KID_DISPATCH, e)
       src = p.x + (size_t)(it / p.K) * p.D;
       if (p.slot_scale) sc = p.slot_scale[it];
       ret = ((long long)p.my_rank << 40) | (long long)it;
@@ -739,6 +740,7 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const CombineParams p) 
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int k = 0; k < p.K; ++k) {
       if (p.slot_pos[(size_t)t * p.K + k] < 0) continue;
+      NP_DBG_SKIP_UNLESS(p.slot_pos[(size_t)t * p.K + k] < (1 << 24), KID_COMBINE, p.slot_pos[(size_t)t * p.K + k])
       float f[8];
       load8(p.rows + ((size_t)t * p.K + k) * p.D + d, f);
       const float w = p.weights ? p.weights[(size_t)t * p.K + k] : 1.f;

@@ -19,6 +19,7 @@ from typing import Dict, Optional
 import torch
 import torch.nn as nn
 
+from ..ops import _lib
 from ..ops import embedding as embedding_ops
 from ..ops import gemm as gemm_ops
 from ..ops import xent as xent_ops
@@ -204,8 +205,9 @@ class Transformer(nn.Module):
             B0, S0, D0 = x.shape
             tp_rt = self._ensure_tp_runtime(B0, S0, x.device)
             x = x.reshape(B0 * S0, D0)[tp_rt.rank * tp_rt.Ms:(tp_rt.rank + 1) * tp_rt.Ms].unsqueeze(0)
-        for blk in self.blocks.values():
-            x = blk(x, **kwargs)
+        for name, blk in self.blocks.items():
+            with _lib.nvtx_range("block." + name):
+                x = blk(x, **kwargs)
         if tp_rt is not None:
             from ..ops.tp_fused import gather_rows_replicated
 

@@ -230,6 +230,28 @@ def ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+NVTX = os.environ.get("NPB200_NVTX", "0") == "1"   # wrap library calls and model blocks in NVTX ranges
+
+
+class nvtx_range:
+    """``with nvtx_range("name"):`` pushes an NVTX range when ``NPB200_NVTX=1`` (profilers show the fused kernels and
+    the blocks of the model by name); free otherwise."""
+
+    __slots__ = ("name",)
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if NVTX:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if NVTX:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 LAUNCHES = 0  # number of successful calls into the kernel library (each launches >= 1 kernel)
 
 
@@ -289,6 +311,13 @@ def call(name: str, *args) -> None:
         else:
             conv.append(a)
     conv.append(c_void_p(stream()))
+    if NVTX:
+        torch.cuda.nvtx.range_push("np_" + name)
+        try:
+            check(fn(*conv), name)
+        finally:
+            torch.cuda.nvtx.range_pop()
+        return
     check(fn(*conv), name)
 
 

@@ -487,5 +487,6 @@ def fused_moe_forward(mod, x: torch.Tensor) -> torch.Tensor:
             mod.router._update_expert_counts(idx, counts)
     mod._aux_loss = aux
     shared = mod.shared_expert(x) if mod.shared_expert is not None else None
-    return _FusedMoE.apply(x, w.reshape(B * S, -1), idx.reshape(B * S, -1).to(torch.int32), mod.w1, mod.w3, mod.w2, rt,
-                           layer, mod, shared)
+    with _lib.nvtx_range("fused_moe"):
+        return _FusedMoE.apply(x, w.reshape(B * S, -1), idx.reshape(B * S, -1).to(torch.int32), mod.w1, mod.w3,
+                               mod.w2, rt, layer, mod, shared)

@@ -433,6 +433,10 @@ class ArenaAdamW(torch.optim.Optimizer):
 
     @torch.no_grad()
     def step(self, closure=None, _hyper_ready: bool = False):
+        with _lib.nvtx_range("optimizer.step"):
+            return self._step(_hyper_ready)
+
+    def _step(self, _hyper_ready: bool = False):
         a = self.arena
         a.finalize_grads()
         if not _hyper_ready:

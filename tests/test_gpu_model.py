@@ -286,3 +286,33 @@ def test_checkpoint_round_trip_on_gpu_with_equal_layer_shapes(tmp_path):
     ck.load(model=m2)
     for k, v in m.state_dict().items():
         assert torch.equal(m2.state_dict()[k], v), k
+
+
+def test_same_seed_gives_the_same_first_loss_bit_for_bit_and_the_same_trajectory():
+    """Determinism: forward pass and loss have a fixed reduction order, so two runs from one seed agree bit for bit on
+    the first loss; the following steps go through gradients accumulated with atomics (embedding rows, router
+    statistics) and agree to rounding."""
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.engine import prepare_training
+
+    def run():
+        torch.manual_seed(11)
+        cfg = TransformerConfig(vocab_size=1024, d_model=256, n_layers=2, n_heads=2, n_kv_heads=1, ffn_hidden=512,
+                                rope_base=10000.0, max_seq_len=256, qk_norm=False, use_moe=True, num_experts=4,
+                                moe_top_k=2, moe_interval=1, moe_hidden=256, moe_capacity_factor=1.25)
+        model = cfg.build(dtype=torch.bfloat16, init_device="cuda")
+        opt, _ = prepare_training(model, tokens_per_rank=2 * 256, lr=1e-3)
+        ids = torch.randint(0, 1024, (2, 256), device="cuda")
+        out = []
+        for _ in range(4):
+            o = model(ids, labels=ids)
+            (o["loss"] + o["aux_loss"]).backward()
+            opt.step()
+            opt.zero_grad()
+            out.append(o["loss"].item())
+        return out
+
+    a, b = run(), run()
+    assert a[0] == b[0], (a, b)
+    for x, y in zip(a, b):
+        assert abs(x - y) <= 2e-3 * abs(x), (a, b)

@@ -193,10 +193,17 @@ def _model_ep_zero_worker(rank, world):
         dist.all_gather(allids, ids)
         out = model(ids, labels=ids)
         out["loss"].backward()
-        opt.step()
-        opt.zero_grad()
         outr = ref(torch.cat(allids), labels=torch.cat(allids))
         outr["loss"].backward()
+        # expert gradients: every rank's tokens reach the local experts, each rank's loss is its own mean, so the
+        # local gradient is `world` times the gradient of the global mean
+        rpar = dict(ref.named_parameters())
+        for n_, g_ in arena.named_main_grads():
+            if ".moe.w" in n_:
+                lo = rank * (E // world) * H
+                assert rel(g_ / world, rpar[n_].grad[lo:lo + (E // world) * H]) < 4e-2, n_
+        opt.step()
+        opt.zero_grad()
         torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
         ropt.step()
         ropt.zero_grad()
@@ -209,9 +216,11 @@ def _model_ep_zero_worker(rank, world):
     n_loc = E // world
     for n, p in model.named_parameters():
         r = rp[n]
+        tol = 3e-2
         if getattr(p, "_ep_sharded", False):
             r = r[rank * n_loc * H:(rank + 1) * n_loc * H]
-        assert rel(p, r) < 3e-2, n
+            tol = 0.2   # N(0, 0.01) weights after two Adam steps of 3e-3: a sign flip of a near-zero gradient is 30 %
+        assert rel(p, r) < tol, (n, rel(p, r))
     return True
 
 
