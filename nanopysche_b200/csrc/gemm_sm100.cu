@@ -122,14 +122,23 @@ struct Tile {
   int g, m_blk, n_blk;
 };
 
-template <int BN, int STAGES>
+// MT = 1: one 128 x BN accumulator per tile, double-buffered in tensor memory (the epilogue of a tile runs under the
+// MMAs of the next). MT = 2: a 256 x BN tile as two 128-row halves that share every B tile; per FLOP a third fewer
+// operand bytes cross from L2 into shared memory, which is what bounds the 128 x 256 tile (the L2 -> SM fabric
+// delivers about 16 TB/s, the 128 x 256 tile asks for 11.4 bytes per kFLOP). The two accumulators fill all 512
+// tensor-memory columns, so they are single-buffered: MMA issue pauses while a tile drains.
+template <int BN, int STAGES, int MT>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmAloc,
                  const __grid_constant__ CUtensorMap tmBloc, const GemmParams p) {
-  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int TM = BM * MT;                 // rows of a tile
+  constexpr int A_HALF = BM * BK * 2;         // one 128-row half of the A tile
+  constexpr int A_BYTES = TM * BK * 2;
   constexpr int B_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int NACC = MT == 1 ? 2 : 1;       // accumulator buffers in tensor memory
+  static_assert(MT * BN * NACC <= 512, "tensor memory holds 512 columns");
   constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
 
   extern __shared__ uint8_t smem_raw[];
@@ -148,7 +157,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int epoch = p.epoch + (p.epoch_base ? *p.epoch_base : 0);
 
-  const int m_blocks = (p.M + BM - 1) / BM;
+  const int m_blocks = (p.M + TM - 1) / TM;
   const int bn_out = (p.epilogue == 1) ? BN / 2 : BN;  // output columns per tile
   const int n_blocks = (p.N + bn_out - 1) / bn_out;
   const int groups = (p.mode == 2) ? p.num_groups : 1;
@@ -213,7 +222,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   };
   // rows of this M block that carry data (0 = nothing to do); waits for the arrival flag first.
   auto tile_rows = [&](const Tile& tl, int role) -> int {
-    if (p.mode != 1) return BM;
+    if (p.mode != 1 || MT != 1) return TM;   // the row-grouped form (per-128-row-block tables) runs with MT = 1
     if (p.ready_flags) {
       const int fi = p.mblk_flag ? p.mblk_flag[tl.m_blk] : 0;
       if (fi >= 0 && !np::wait_flag_ge(p.ready_flags + fi, epoch, p.flag_limit_ns, KID_GEMM, 100 + role)) {
@@ -234,7 +243,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int rows = tile_rows(tl, 0);
         if (rows < 0) break;
         if (rows == 0) continue;
-        const int m0 = tl.m_blk * BM;
+        const int m0 = tl.m_blk * TM;
         const int n0 = tl.n_blk * bn_out;
         long long goff = 0;  // row offset of this tile's group inside the stacked B tensor
         if (p.mode == 1 && p.mblk_group) goff = (long long)p.mblk_group[tl.m_blk] * p.group_stride_b;
@@ -266,11 +275,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t sB = sA + A_BYTES;
           np::mbar_expect_tx(full_bar(stage), STAGE_BYTES);
           if (!p.a_mn) {
-            if (m0 >= p.a_loc_lo && m0 < p.a_loc_hi) np::tma_load_2d(sA, &tmAloc, full_bar(stage), k0, m0 - p.a_loc_lo);
-            else np::tma_load_2d(sA, &tmA, full_bar(stage), k0, m0);
+            if (MT == 1 && m0 >= p.a_loc_lo && m0 < p.a_loc_hi) {
+              np::tma_load_2d(sA, &tmAloc, full_bar(stage), k0, m0 - p.a_loc_lo);
+            } else {
+#pragma unroll
+              for (int h = 0; h < MT; ++h) np::tma_load_2d(sA + h * A_HALF, &tmA, full_bar(stage), k0, m0 + h * BM);
+            }
           } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c)
+            for (int c = 0; c < TM / 64; ++c)
               np::tma_load_2d(sA + c * (64 * BK * 2), &tmA, full_bar(stage), m0 + c * 64, k0);
           }
           if (!p.b_mn) {
@@ -309,7 +322,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (count_k(p, tl.g) == 0) continue;
         if (!np::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, KID_GEMM, 2)) break;
         np::tc_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * MT * BN);
         uint32_t accum = 0;
         for_each_k(p, tl.g, [&](int) -> bool {
           if (!np::mbar_wait(full_bar(stage), phase, abort_flag, KID_GEMM, 3)) return false;
@@ -318,11 +331,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t sB = sA + A_BYTES;
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
-            const uint64_t ad = p.a_mn ? np::make_smem_desc(sA + kk * 2048, 64 * BK * 2, 1024)
-                                       : np::make_smem_desc(sA + kk * 32, 16, 1024);
             const uint64_t bd = p.b_mn ? np::make_smem_desc(sB + kk * 2048, 64 * BK * 2, 1024)
                                        : np::make_smem_desc(sB + kk * 32, 16, 1024);
-            np::tc_mma_f16(tmem_d, ad, bd, idesc, accum);
+#pragma unroll
+            for (int h = 0; h < MT; ++h) {   // both halves read the same B tile
+              const uint32_t sAh = sA + h * A_HALF;
+              const uint64_t ad = p.a_mn ? np::make_smem_desc(sAh + kk * 2048, 64 * BK * 2, 1024)
+                                         : np::make_smem_desc(sAh + kk * 32, 16, 1024);
+              np::tc_mma_f16(tmem_d + (uint32_t)(h * BN), ad, bd, idesc, accum);
+            }
             accum = 1;
           }
           np::tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
@@ -330,7 +347,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           return true;
         });
         np::tc_commit(tfull_bar(acc));
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        if (++acc == NACC) { acc = 0; acc_phase ^= 1u; }
       }
       if (*abort_flag) __nanosleep(1000000);
     }
@@ -345,8 +362,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (rows < 0) break;
       if (rows == 0) continue;
       const int nk = count_k(p, tl.g);
-      const int row = tl.m_blk * BM + quarter * 32 + lane;
       const int n0 = tl.n_blk * bn_out;
+      bool have_acc = nk > 0;
+      if (have_acc) {
+        if (!np::mbar_wait(tfull_bar(acc), acc_phase, abort_flag, KID_GEMM, 4)) break;
+        np::tc_fence_after();
+      }
+#pragma unroll 1
+      for (int h = 0; h < MT; ++h) {   // the 128-row halves of the tile, one accumulator each
+      const int row = tl.m_blk * TM + h * BM + quarter * 32 + lane;
       bool row_ok = row < p.M;
       char* crow;
       if (p.row_dst) {
@@ -360,12 +384,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       const char* cin_row = p.Cin ? (const char*)p.Cin + ((size_t)tl.g * p.group_stride_c + (size_t)row * p.ldcin) * (p.out_f32 ? 4 : 2)
                                   : nullptr;
-      bool have_acc = nk > 0;
-      if (have_acc) {
-        if (!np::mbar_wait(tfull_bar(acc), acc_phase, abort_flag, KID_GEMM, 4)) break;
-        np::tc_fence_after();
-      }
-      const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t taddr = tmem_base + (uint32_t)((acc * MT + h) * BN) + ((uint32_t)(quarter * 32) << 16);
       if (p.epilogue == 1) {
         // gate = columns [0, BN/2), up = columns [BN/2, BN); out = silu(gate) * up
 #pragma unroll 1
@@ -488,11 +507,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
+      }   // halves
       if (have_acc) {
         np::tc_fence_before();
         __syncwarp();
         if (lane == 0) np::mbar_arrive(tempty_bar(acc));
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        if (++acc == NACC) { acc = 0; acc_phase ^= 1u; }
       }
       if (p.done_counters) {
         // all rows of this tile are stored (possibly into peer memory): publish, then count the
@@ -584,10 +604,12 @@ struct NpGemmArgs {
   // push_ctr: a zeroed local int
   const void* push_src; long long push_bytes; void* const* push_dst; int* const* push_flag; int push_n; int* push_ctr;
   const float* bias;  // optional [N] fp32 bias added in the plain epilogue (alpha != 0)
+  int mt;             // rows of a tile in units of 128: 0 = choose, 1, or 2 (256 x 256 tiles, dense and K-grouped forms)
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MT>
 static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
+  constexpr int TM = BM * MT;
   CUtensorMap tmA, tmB, tmB2, tmAloc, tmBloc;
   int rc;
   if (!a.a_mn) rc = np_make_tmap_2d(&tmA, a.A, 2, (uint64_t)a.a_rows, (uint64_t)a.K, (uint64_t)a.lda, BK, BM);
@@ -645,11 +667,12 @@ static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
   p.epoch_base = a.epoch_base;
   p.b_ready_flags = a.b_ready_flags; p.b_rows_per_flag = a.b_rows_per_flag;
 
-  constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  constexpr int SMEM = STAGES * (TM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  static_assert(SMEM <= 227 * 1024, "shared memory budget");
   static NpPerDeviceOnce attr_once;
   bool& attr_set = *attr_once.slot();
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return 400 + (int)e;
     attr_set = true;
   }
@@ -659,12 +682,12 @@ static int launch_gemm(const NpGemmArgs& a, cudaStream_t stream) {
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const int bn_out = a.epilogue == 1 ? BN / 2 : BN;
-  const int m_blocks = (a.M + BM - 1) / BM, n_blocks = (a.N + bn_out - 1) / bn_out;
+  const int m_blocks = (a.M + TM - 1) / TM, n_blocks = (a.N + bn_out - 1) / bn_out;
   const long long tiles = (long long)m_blocks * n_blocks * (a.mode == 2 ? a.num_groups : 1);
   int cap = a.max_ctas > 0 ? a.max_ctas : g_num_sms;
   int grid = (int)(tiles < cap ? tiles : cap);
   if (grid <= 0) return 0;
-  gemm_bf16_kernel<BN, STAGES><<<grid, 192, SMEM, stream>>>(tmA, tmB, tmB2, tmAloc, tmBloc, p);
+  gemm_bf16_kernel<BN, STAGES, MT><<<grid, 192, SMEM, stream>>>(tmA, tmB, tmB2, tmAloc, tmBloc, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 500 + (int)e;
 }
@@ -687,8 +710,34 @@ NP_API int np_gemm_bf16(const NpGemmArgs* args, void* stream) {
   int bn = a.bn;
   if (a.epilogue == 1) bn = 256;
   if (bn == 0) bn = (a.N >= 256 && (a.N % 256 == 0 || a.N >= 2048)) ? 256 : 128;
-  if (bn == 256) return launch_gemm<256, 4>(a, (cudaStream_t)stream);
-  return launch_gemm<128, 6>(a, (cudaStream_t)stream);
+  if (bn == 256) {
+    // 256 x 256 tiles where the form allows (no per-128-row-block tables, flags or pushes) and the problem has
+    // enough of them to occupy the SMs; NPB200_GEMM_MT=1 keeps the 128-row tiles
+    static const int mt_env = getenv("NPB200_GEMM_MT") ? atoi(getenv("NPB200_GEMM_MT")) : 0;
+    int mt = a.mt ? a.mt : mt_env;
+    const bool plain = a.mode != 1 && !a.row_dst && !a.ready_flags && !a.b_ready_flags && !a.push_src && !a.A_loc &&
+                       !a.B_loc && !a.done_counters && a.m_rot == 0 && a.n_rot == 0;
+    if (mt == 0) {
+      // A 256-row tile costs about 1.68 tiles of 128 rows (measured on B200: 8192^3 1354 -> 1610 TFLOP/s, 4096 x 32000
+      // x 2048 1282 -> 1444, 4096 x 2048 x 5632 1037 -> 1264), so it wins unless its coarser grain wastes the last wave
+      const int bn_out = a.epilogue == 1 ? 128 : 256;
+      const long long groups = a.mode == 2 ? a.num_groups : 1;
+      const long long nb = (a.N + bn_out - 1) / bn_out;
+      const long long tiles1 = (long long)((a.M + 127) / 128) * nb * groups;
+      const long long tiles2 = (long long)((a.M + 255) / 256) * nb * groups;
+      if (g_num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+      }
+      const int sms = a.max_ctas > 0 ? a.max_ctas : (g_num_sms > 0 ? g_num_sms : 148);
+      const long long w1 = (tiles1 + sms - 1) / sms, w2 = (tiles2 + sms - 1) / sms;
+      mt = (plain && a.M >= 256 && 1.68 * (double)w2 < (double)w1) ? 2 : 1;
+    }
+    if (mt == 2 && plain) return launch_gemm<256, 3, 2>(a, (cudaStream_t)stream);
+    return launch_gemm<256, 4, 1>(a, (cudaStream_t)stream);
+  }
+  return launch_gemm<128, 6, 1>(a, (cudaStream_t)stream);
 }
 
 NP_API int np_status_read(int* out8) {

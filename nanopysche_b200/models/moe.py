@@ -263,8 +263,35 @@ class SymmetricMemoryDispatcher(NcclAllToAllDispatcher):
 
 
 class DeepEPDispatcher(SymmetricMemoryDispatcher):
-    """The reference's optional DeepEP backend (model/moe.py:501-617) maps onto the in-tree
-    symmetric-memory kernels; ``deep_ep`` itself is not used."""
+    """The reference's optional DeepEP backend (model/moe.py:501-617) mapped onto the in-tree symmetric-memory
+    kernels; ``deep_ep`` itself is not used. Its three knobs configure the fused runtime that
+    ``ops.moe.build_runtime`` creates for the layers holding this dispatcher:
+
+    * ``num_sms``: CTAs the dispatch kernel may occupy (the rest of the GPU keeps running the dense branch of a hybrid
+      block or the previous GEMM's tail); ``None`` with ``adaptive=True`` asks ``AdaptiveSMAllocator`` for the
+      roofline split of the layer's shapes, ``None`` otherwise means all SMs;
+    * ``use_fp8_dispatch``: rows travel as e4m3 with 1x128 scales and feed the e4m3 expert GEMMs, regardless of the
+      tokens-per-expert threshold of the FP8-Flow-MoE switch;
+    * ``async_with_compute_stream``: kept for signature parity. The fused kernels always run in stream order with the
+      compute kernels and overlap through their arrival flags, which is what the option asks DeepEP for.
+    """
+
+    def __init__(self, num_sms: Optional[int] = None, use_fp8_dispatch: bool = False,
+                 async_with_compute_stream: bool = True, adaptive: bool = False):
+        self.num_sms = num_sms
+        self.use_fp8_dispatch = use_fp8_dispatch
+        self.async_with_compute_stream = async_with_compute_stream
+        self.adaptive = adaptive
+
+    def dispatch_ctas(self, *, tokens: int, d_model: int, hidden: int, num_experts: int, top_k: int,
+                      fp8: bool = False) -> int:
+        """CTA budget of the dispatch kernel (0 = no limit)."""
+        if self.num_sms:
+            return int(self.num_sms)
+        if not self.adaptive:
+            return 0
+        return AdaptiveSMAllocator().compute_optimal_sms(tokens, d_model, hidden, num_experts, top_k,
+                                                        num_bytes_per_elem=1 if fp8 else 2)
 
 
 def get_best_dispatcher() -> TokenDispatcher:

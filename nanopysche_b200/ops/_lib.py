@@ -47,6 +47,7 @@ class GemmArgs(C.Structure):
         ("push_src", c_void_p), ("push_bytes", c_ll), ("push_dst", c_void_p), ("push_flag", c_void_p),
         ("push_n", c_int), ("push_ctr", c_void_p),
         ("bias", c_void_p),
+        ("mt", c_int),
     ]
 
 

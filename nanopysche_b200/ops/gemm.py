@@ -41,7 +41,7 @@ def gemm_ref(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, accumula
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None, accumulate: bool = False,
          alpha: float = 1.0, bn: int = 0, max_ctas: int = 0, bias: torch.Tensor | None = None,
-         residual: torch.Tensor | None = None) -> torch.Tensor:
+         residual: torch.Tensor | None = None, mt: int = 0) -> torch.Tensor:
     """``out[M, N] (+)= alpha * A @ B^T (+ bias) (+ residual)`` in the operand layouts described in the module
     docstring. ``bias [N]`` (fp32) and ``residual [M, N]`` (dtype of ``out``) are added in the GEMM's epilogue."""
     if not _use_kernel(a):
@@ -75,7 +75,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     assert out.dtype in (torch.float32, torch.bfloat16)
     args.accumulate = int(accumulate)
     args.alpha = alpha
-    args.bn, args.max_ctas = bn, max_ctas
+    args.bn, args.max_ctas, args.mt = bn, max_ctas, mt   # mt: 0 = choose; 2 = 256-row tiles (dense / K-grouped forms)
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous()
         args.bias = bias.data_ptr()

@@ -452,11 +452,18 @@ def build_runtime(moe_modules, *, tokens: int, group=None, device=None) -> Fused
     world = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
     # FP8-Flow-MoE switch: fp8 expert GEMMs once the expected tokens per expert reach the threshold
     per_expert = tokens * m0.top_k * world / m0.num_experts
+    # ("fp8 grouped GEMM above N tokens per expert and bf16 below": strictly above)
     fp8 = bool(m0.fp8_flow_moe_enabled and m0.fp8_recipe in ("blockwise", "flow_moe") and
-               per_expert >= m0.fp8_gemm_threshold)
+               per_expert > m0.fp8_gemm_threshold)
+    disp = getattr(m0.ep, "dispatcher", None)
+    max_ctas = 0
+    if hasattr(disp, "dispatch_ctas"):      # DeepEPDispatcher knobs: SM budget of the dispatch kernel, e4m3 on the wire
+        fp8 = fp8 or bool(getattr(disp, "use_fp8_dispatch", False))
+        max_ctas = disp.dispatch_ctas(tokens=tokens, d_model=m0.d_model, hidden=m0.hidden_size,
+                                      num_experts=m0.num_experts, top_k=m0.top_k, fp8=fp8)
     rt = FusedMoERuntime(tokens=tokens, d_model=m0.d_model, hidden=m0.hidden_size, num_experts=m0.num_experts,
                          top_k=m0.top_k, n_layers=len(moe_modules), capacity_factor=m0.capacity_factor, group=group,
-                         device=device, fp8=fp8)
+                         device=device, fp8=fp8, max_ctas_dispatch=max_ctas)
     for m in moe_modules:
         m._fused_runtime = rt
         rt.layer_index(m)

@@ -200,6 +200,7 @@ class _MB:
     out: Optional[torch.Tensor] = None
     loss: Optional[torch.Tensor] = None
     grad_in: Optional[torch.Tensor] = None
+    aux: Optional[torch.Tensor] = None   # auxiliary (router) loss of a stage that is not the last one
 
 
 class PipelineSchedule:
@@ -389,14 +390,16 @@ class PipelineSchedule:
                         loss = self.loss_fn(y, tg_chunks[a.microbatch])
                     else:
                         loss = out["loss"]
-                        if isinstance(out, dict) and out.get("aux_loss") is not None:
-                            loss = loss + out["aux_loss"]
+                    losses.append(loss.detach())     # what is reported: the cross-entropy, as in the non-pipelined step
+                    if self.loss_fn is None and isinstance(out, dict) and out.get("aux_loss") is not None:
+                        loss = loss + out["aux_loss"]
                     mb.loss = loss / m
-                    losses.append(loss.detach())
                 else:
                     out = stage_mod(x, **kwargs)
                     y = out["hidden_states"] if isinstance(out, dict) else out
                     mb.out = y
+                    if isinstance(out, dict) and out.get("aux_loss") is not None and out["aux_loss"].requires_grad:
+                        mb.aux = out["aux_loss"] / m   # back-propagated locally together with the incoming gradient
                     if hs is None:
                         hs, hd = tuple(y.shape), y.dtype
                     if self._rank_of(a.stage + 1) == self.rank:
@@ -411,12 +414,16 @@ class PipelineSchedule:
                     root, g = mb.out, local_box.pop(("grad", a.stage, a.microbatch))
                 else:
                     root, g = mb.out, receive(("grad", a.stage, a.microbatch), (self._rank_of(a.stage + 1), "grad"))
+                roots, gouts = [root], [g]
+                if mb.aux is not None:
+                    roots.append(mb.aux)
+                    gouts.append(torch.ones_like(mb.aux))
                 if a.type == ScheduleType.BWD_INPUT:
                     # B: everything except the weight-gradient GEMMs, which wait in a queue for this pair's W action
                     with gemm_ops.defer_wgrad(wqueues.setdefault(key, [])):
-                        root.backward(g)
+                        torch.autograd.backward(roots, gouts)
                 else:
-                    root.backward(g)
+                    torch.autograd.backward(roots, gouts)
                 if not self._first(a.stage) and mb.inp.grad is not None:
                     if self._rank_of(a.stage - 1) == self.rank:
                         local_box[("grad", a.stage - 1, a.microbatch)] = mb.inp.grad
@@ -452,19 +459,42 @@ class DualPipeScheduleRuntime(PipelineSchedule):
 
 
 def clip_grad_norm_pp(parameters, max_norm: float, pp_group=None, norm_type: float = 2.0,
-                      copies: int = 1) -> torch.Tensor:
+                      copies: int = 1, ep_group=None) -> torch.Tensor:
     """Clip by the global norm over all pipeline stages (one scalar all-reduce over the PP group). ``copies``: how
     many ranks hold each stage (2 under DualPipe, whose twin copies carry identical gradients after
-    ``sync_twin_grads``), so that every stage counts once."""
+    ``sync_twin_grads``), so that every stage counts once. Composed with other dimensions every parameter still counts
+    once: tensor-parallel shards (``_tp_sharded`` = their TP group) add up over that group, expert shards
+    (``_ep_sharded``) over ``ep_group``, everything else is identical on those peers."""
     params = [p for p in parameters if p.grad is not None]
     dev = params[0].device if params else torch.device("cpu")
     if norm_type == float("inf"):
         total = torch.stack([p.grad.detach().abs().max() for p in params]).max() if params else torch.zeros((), device=dev)
-        if pp_group is not None:
-            dist.all_reduce(total, op=dist.ReduceOp.MAX, group=pp_group)
+        groups = {id(g): g for g in [pp_group, ep_group, *[getattr(p, "_tp_sharded", None) for p in params]]
+                  if g is not None}
+        for g in groups.values():
+            dist.all_reduce(total, op=dist.ReduceOp.MAX, group=g)
     else:
-        total = torch.stack([p.grad.detach().float().norm(norm_type) ** norm_type for p in params]).sum() \
-            if params else torch.zeros((), device=dev)
+        def sq(ps):
+            return torch.stack([p.grad.detach().float().norm(norm_type) ** norm_type for p in ps]).sum() \
+                if ps else torch.zeros((), device=dev)
+
+        tp_groups = {}
+        for p in params:
+            g = getattr(p, "_tp_sharded", None)
+            if g is not None:
+                tp_groups.setdefault(id(g), (g, []))[1].append(p)
+        ep_params = [p for p in params if getattr(p, "_ep_sharded", False) and getattr(p, "_tp_sharded", None) is None]
+        rest = [p for p in params if getattr(p, "_tp_sharded", None) is None and not getattr(p, "_ep_sharded", False)]
+        total = sq(rest)
+        for g, ps in tp_groups.values():
+            part = sq(ps)
+            dist.all_reduce(part, group=g)
+            total = total + part
+        if ep_params or ep_group is not None:
+            part = sq(ep_params)
+            if ep_group is not None:
+                dist.all_reduce(part, group=ep_group)
+            total = total + part
         if pp_group is not None:
             dist.all_reduce(total, op=dist.ReduceOp.SUM, group=pp_group)
         total = (total / max(copies, 1)) ** (1.0 / norm_type)

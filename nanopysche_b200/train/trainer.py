@@ -266,8 +266,11 @@ class Trainer:
                 if getattr(self.model, "_pp_enabled", False):
                     from ..parallel.pipeline_runtime import clip_grad_norm_pp
 
+                    ep_group = next((m.ep.ep_group for m in self.model.modules()
+                                     if hasattr(m, "ep") and getattr(m.ep, "ep_size", 1) > 1), None)
                     grad_norm = clip_grad_norm_pp(params, c.max_grad_norm, getattr(self.model, "_pp_group", None),
-                                                  copies=2 if getattr(self.model, "is_dualpipe", False) else 1)
+                                                  copies=2 if getattr(self.model, "is_dualpipe", False) else 1,
+                                                  ep_group=ep_group)
                 elif params:
                     grad_norm = torch.nn.utils.clip_grad_norm_(params, c.max_grad_norm)
             self.optimizer.step()
@@ -342,6 +345,9 @@ class Trainer:
                                                  hidden_dtype=dtype)
         self.model.train()
         total = torch.zeros((), device=self.device)
+        reducer = self._grad_reducer()
+        if reducer is not None:
+            reducer.enabled = False   # many backward passes per step: the buckets go out once, in finish()
         for input_ids, labels in batches:
             input_ids = input_ids.to(self.device, non_blocking=True)
             labels = labels.to(self.device, non_blocking=True)

@@ -590,3 +590,22 @@ def test_attention_head_dim_64_runs_on_the_flash_kernels_padded():
     assert rel(o, of) < 2e-2
     for a, b in ((q, qf), (k, kf), (v, vf)):
         assert rel(a.grad, b.grad) < 3e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 128), (600, 520, 200), (4096, 2048, 2048), (1000, 32000, 256)])
+def test_gemm_256_row_tiles_all_layouts(M, N, K):
+    """The 256 x 256 tile form (two 128-row halves sharing every B tile, single-buffered accumulators), forced on,
+    against fp32 matmul: forward, dgrad and wgrad operand layouts, fp32 accumulate, ragged edges."""
+    from nanopysche_b200.ops.gemm import gemm
+
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    ref = a.float() @ b.float().t()
+    assert rel(gemm(a, b, bn=256, mt=2), ref) < 1e-2
+    assert rel(gemm(a, b.t().contiguous(), b_mn=True, bn=256, mt=2), ref) < 1e-2                    # dgrad layout
+    at, bt = a.t().contiguous(), b.t().contiguous()
+    out = torch.full((M, N), 0.5, device="cuda")
+    gemm(at, bt, a_mn=True, b_mn=True, out=out, accumulate=True, bn=256, mt=2)                     # wgrad layout, +=
+    assert rel(out, ref + 0.5) < 1e-2
+    assert rel(gemm(a, b, bn=256, mt=2), gemm(a, b, bn=256, mt=1)) < 1e-5                          # same numbers as 128-row tiles

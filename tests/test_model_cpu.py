@@ -273,3 +273,18 @@ def test_125m_cpu_ten_adamw_steps_loss_decreases():
         opt.zero_grad()
         losses.append(out["loss"].item())
     assert losses[-1] < losses[0] - 0.5 and all(math.isfinite(l) for l in losses)
+
+
+def test_deepep_dispatcher_knobs_map_onto_the_fused_runtime_settings():
+    """``DeepEPDispatcher(num_sms=, use_fp8_dispatch=, adaptive=)``: explicit SM budget, roofline budget from
+    ``AdaptiveSMAllocator`` (communication share of the layer's time on a 148-SM part), none by default."""
+    from nanopysche_b200.models.moe import DeepEPDispatcher, ExpertParallelConfig
+
+    shapes = dict(tokens=4096, d_model=2048, hidden=2816, num_experts=8, top_k=2)
+    assert DeepEPDispatcher().dispatch_ctas(**shapes) == 0
+    assert DeepEPDispatcher(num_sms=24).dispatch_ctas(**shapes) == 24
+    a = DeepEPDispatcher(adaptive=True).dispatch_ctas(**shapes)
+    b = DeepEPDispatcher(adaptive=True).dispatch_ctas(**shapes, fp8=True)
+    assert 4 <= b <= a <= 144      # e4m3 rows halve the bytes on the wire, so fewer SMs go to the dispatch
+    cfg = ExpertParallelConfig(ep_size=1, dispatcher=DeepEPDispatcher(use_fp8_dispatch=True))
+    assert cfg.dispatcher.use_fp8_dispatch and cfg.dispatcher.async_with_compute_stream

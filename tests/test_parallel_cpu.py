@@ -275,7 +275,10 @@ def test_stage_layer_ranges():
     assert stage_layer_ranges(10, 4) == [(0, 2), (2, 5), (5, 8), (8, 10)]  # remainder goes to stages 1..
     assert stage_layer_ranges(6, 3, [1, 3]) == [(0, 1), (1, 3), (3, 6)]
     c = PipelineParallelConfig(degree=4, schedule=PipelineScheduleType.dualpipe)
-    assert c.stages_per_rank() == 2 and c.stage_ids_this_rank(1) == [1, 6]
+    # DualPipe: four model stages, every rank holds its own and a copy of its mirror rank's
+    assert c.stages_per_rank() == 2 and c.num_stages() == 4 and c.stage_ids_this_rank(1) == [1, 2]
+    cv = PipelineParallelConfig(degree=4, schedule=PipelineScheduleType.zbv_zero_bubble)
+    assert cv.num_stages() == 8 and cv.stage_ids_this_rank(1) == [1, 6]
     c2 = PipelineParallelConfig(degree=4, schedule=PipelineScheduleType.interleaved_1F1B)
     assert c2.stage_ids_this_rank(1) == [1, 5]
 

@@ -130,3 +130,79 @@ def _pp_tp_worker(rank, world):
 
 def test_pipeline_times_tensor_parallel_four_ranks():
     assert all(run_distributed(_pp_tp_worker, 4))
+
+
+def _hybrid_cfg():
+    from nanopysche_b200.config import TransformerConfig
+
+    # dense FFN on even layers, 4-expert top-2 MoE on odd ones (the layout of the 7B hybrid configuration, toy-sized)
+    return TransformerConfig(d_model=32, n_layers=4, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=16,
+                             ffn_hidden=64, qk_norm=False, use_moe=True, num_experts=4, moe_top_k=2, moe_interval=2,
+                             moe_offset=1, moe_hidden=32, moe_capacity_factor=None)
+
+
+def _pp_tp_ep_worker(rank, world):
+    """PP 2 (DualPipe) x EP 2 x TP 2 on eight ranks through parallelize_model + Trainer.fit: the loss (averaged over
+    the expert-parallel ranks, which read different batches) follows the single-process model on all batches, and so
+    do the parameters of the stages this rank holds."""
+    from nanopysche_b200.parallel.mesh import build_world_mesh, get_ep_mesh
+    from nanopysche_b200.parallel.pipeline_parallel import PipelineParallelConfig
+    from nanopysche_b200.parallel.tensor_parallel import TensorParallelConfig
+    from nanopysche_b200.parallelize import parallelize_model
+    from nanopysche_b200.train.trainer import Trainer, TrainingConfig
+
+    torch.manual_seed(0)
+    model = _hybrid_cfg().build()
+    ref = _hybrid_cfg().build()
+    ref.load_state_dict(model.state_dict())
+    mesh = build_world_mesh(pp_size=2, ep_size=2, tp_size=2, device_type="cpu", replace=True)
+    assert tuple(mesh.mesh_dim_names) == ("pp", "dp", "ep", "tp")
+    ep_rank = get_ep_mesh(mesh).get_local_rank()
+    torch.manual_seed(1)
+    all_batches = [[torch.randint(0, 64, (4, 8)) for _ in range(2)] for _ in range(2)]   # [ep rank][step]
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.0)
+    ref_losses = []
+    for step in range(2):
+        ids = torch.cat([all_batches[e][step] for e in range(2)])
+        out = ref(ids, labels=ids)
+        (out["loss"] + out["aux_loss"]).backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+        ropt.step()
+        ropt.zero_grad()
+        ref_losses.append(out["loss"].item())
+
+    model = parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"),
+                              pp_config=PipelineParallelConfig(2, schedule="DualPipe", num_microbatches=2),
+                              tp_config=TensorParallelConfig(2))
+    assert model.is_dualpipe and len(model.stages) == 2 and model._replica_group is not None
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2, weight_decay=0.0)
+    mine = all_batches[ep_rank]
+
+    class Loader:
+        def __iter__(self):
+            return iter([(b, b.clone()) for b in mine])
+
+    tc = TrainingConfig(global_batch_size=4 * 8, micro_batch_size=4, sequence_length=8, max_steps=2, dtype=torch.float32,
+                        log_interval=0, save_interval=0, vocab_size=64, pp_schedule="DualPipe", pp_microbatches=2)
+    tr = Trainer(tc, model, opt, data_loader=Loader(), device=torch.device("cpu"))
+    got, orig = [], tr._train_step
+
+    def spy(b):
+        out = orig(b)
+        got.append(out.detach().clone())
+        return out
+
+    tr._train_step = spy
+    tr.fit()
+    return [float(x) for x in got], ref_losses, ep_rank
+
+
+def test_dualpipe_times_expert_parallel_times_tensor_parallel_eight_ranks():
+    res = run_distributed(_pp_tp_ep_worker, 8, timeout=600)
+    ref_losses = res[0][1]
+    for step in range(2):
+        by_ep = {}
+        for losses, _, ep in res:
+            by_ep.setdefault(ep, losses[step])
+        mean = sum(by_ep.values()) / len(by_ep)
+        assert mean == pytest.approx(ref_losses[step], rel=5e-3), (step, by_ep, ref_losses)
