@@ -4,6 +4,11 @@ Random-sign chunk-sum projection of the flat gradient to ``compression_rank`` nu
 feedback; only the projected vector is all-reduced. The projection is one segmented reduction
 (``reshape + sum``) instead of the reference's Python loop over chunks, and the shared random signs
 come from a private generator (the reference reseeds the global RNG in its constructor).
+
+Error feedback keeps the residual ``(gradient + previous residual) - reconstruction`` for the next step. The
+reference's ``decompress`` subtracts the reconstruction from the old buffer without adding the gradient
+(optim/diko.py:112-113), so its buffer never sees what the projection dropped; a ``decompress`` call that was not
+preceded by ``compress`` keeps that behaviour.
 """
 from __future__ import annotations
 
@@ -21,6 +26,7 @@ class DiLoCoCompressor:
         gen = torch.Generator(device="cpu").manual_seed(seed)
         self._random_diag = torch.randn(self.total_params, generator=gen).to(self.device)
         self.error_buffer = torch.zeros(self.total_params, device=self.device)
+        self._pending = None      # gradient + residual of the compress() call that a decompress() has not yet closed
 
     def _chunks(self, n: int):
         chunk = max(1, n // self.compression_rank)
@@ -48,12 +54,17 @@ class DiLoCoCompressor:
 
     def compress(self, gradients: torch.Tensor):
         g = gradients + self.error_buffer[: gradients.shape[0]]
+        self._pending = g
         compressed = self._fast_project(g)
         return compressed, compressed.abs().max().clamp(min=1e-8)
 
     def decompress(self, compressed: torch.Tensor, scale: torch.Tensor, N: int) -> torch.Tensor:
         rec = self._fast_reconstruct(compressed, N)
-        self.error_buffer[:N] = self.error_buffer[:N] - rec
+        if self._pending is not None and self._pending.shape[0] == N:
+            self.error_buffer[:N] = self._pending - rec
+        else:
+            self.error_buffer[:N] = self.error_buffer[:N] - rec
+        self._pending = None
         return rec
 
     def all_reduce_gradients(self, gradients: torch.Tensor) -> torch.Tensor:

@@ -50,6 +50,7 @@ class TrainingConfig:
     dp_world_size: int = 1
     enable_hang_detection: bool = False
     enable_gradient_compression: bool = False
+    compression_rank: int = 256
     vocab_size: int = 32000
     cp_size: int = 1
     pp_schedule: str = "1F1B"          # pipeline schedule when the model is a pipeline stage
@@ -106,9 +107,17 @@ class Trainer:
 
             self.hang_detector = HangDetector()
         if config.enable_gradient_compression:
+            # replaces the data-parallel gradient all-reduce (the reference constructs the compressor but never calls
+            # it, train/trainer.py:112-119; here it is the gradient synchronisation of the un-sharded path)
             from ..optim.diko import DiLoCoCompressor
 
-            self._compressor = DiLoCoCompressor(list(model.parameters()), compression_rank=256)
+            if self._arena_opt or getattr(model, "_fsdp_enabled", False):
+                raise ValueError("enable_gradient_compression needs un-sharded data parallelism: the parameter arena "
+                                 "and FSDP reduce-scatter full-precision gradients into shards")
+            self._compressed_params = [p for p in model.parameters()
+                                       if p.requires_grad and not getattr(p, "_ep_sharded", False)]
+            self._compressor = DiLoCoCompressor(self._compressed_params, compression_rank=config.compression_rank,
+                                                group=getattr(model, "_replica_group", None))
 
     # ------------------------------------------------------------------ setup
     def _setup_distributed(self, device=None):
@@ -299,7 +308,7 @@ class Trainer:
         """Bucketed, backward-overlapped all-reduce over the ranks that hold the same parameters (``parallel/ddp.py``);
         built lazily for un-sharded data parallelism without the parameter arena."""
         if self._reducer is None and self.world_size > 1 and not getattr(self.model, "_fsdp_enabled", False) and \
-                getattr(self.model, "_needs_grad_sync", False) and not self._arena_opt:
+                getattr(self.model, "_needs_grad_sync", False) and not self._arena_opt and self._compressor is None:
             from ..parallel.ddp import BucketedGradReducer
 
             group = getattr(self.model, "_replica_group", dist.group.WORLD)
@@ -310,7 +319,21 @@ class Trainer:
         return self._reducer
 
     def _sync_replicated_grads(self):
-        """Plain data parallelism for un-sharded models: finish the bucketed all-reduce started during backward."""
+        """Plain data parallelism for un-sharded models: finish the bucketed all-reduce started during backward, or,
+        with gradient compression on, all-reduce the random projection of the flat gradient (error feedback keeps what
+        the projection lost for the next step)."""
+        if self._compressor is not None:
+            if self.world_size > 1:
+                ps = [p for p in self._compressed_params if p.grad is not None]
+                if ps:
+                    flat = torch.cat([p.grad.reshape(-1).float() for p in ps])
+                    rec = self._compressor.all_reduce_gradients(flat)
+                    off = 0
+                    for p in ps:
+                        n = p.numel()
+                        p.grad.copy_(rec[off:off + n].view_as(p.grad))
+                        off += n
+            return
         r = self._grad_reducer()
         if r is not None:
             r.finish()

@@ -181,7 +181,7 @@ def test_diloco_compressor_roundtrip_and_error_feedback():
     comp, scale = c.compress(g)
     assert comp.shape == (16,)
     rec = c.decompress(comp, scale, 1000)
-    assert rec.shape == (1000,) and torch.allclose(c.error_buffer, -rec)
+    assert rec.shape == (1000,) and torch.allclose(c.error_buffer, g - rec)   # the residual is carried over
     out = c.all_reduce_gradients(g)
     assert out.shape == (1000,)
     sd = c.compress_state_dict({"a": torch.randn(10, 50), "b": torch.randn(500)})
@@ -418,3 +418,48 @@ def _ft_resume_worker(rank, world, save_dir):
 
 def test_fault_tolerant_resume_agrees_across_ranks(tmp_path):
     assert run_distributed(_ft_resume_worker, 2, str(tmp_path)) == [1, 1]
+
+
+def _compressed_dp_worker(rank, world):
+    torch.manual_seed(0)
+    m = tiny_model()
+    m._replica_group = dist.group.WORLD
+    opt = torch.optim.SGD(m.parameters(), lr=1e-2)
+    tc = TrainingConfig(global_batch_size=2 * 16 * world, micro_batch_size=2, sequence_length=16, max_steps=3,
+                        log_interval=0, save_interval=0, dtype=torch.float32, vocab_size=64, dp_world_size=world,
+                        enable_gradient_compression=True, compression_rank=64)
+    tr = Trainer(tc, m, opt, None, None, [])
+    sent = []
+    orig = dist.all_reduce
+
+    def spy(t, *a, **k):
+        sent.append(t.numel())
+        return orig(t, *a, **k)
+
+    dist.all_reduce = spy
+    try:
+        torch.manual_seed(100 + rank)       # every rank trains on its own batches
+        tr.fit()
+    finally:
+        dist.all_reduce = orig
+    assert 64 in sent and max(sent) <= 64, sent       # only the projection crosses the ranks
+    assert tr._compressor.error_buffer.abs().sum() > 0
+    flat = torch.cat([p.detach().reshape(-1) for p in m.parameters()])
+    both = [torch.zeros_like(flat) for _ in range(world)]
+    dist.all_gather(both, flat)
+    assert torch.equal(both[0], both[1])               # identical updates: the replicas stay in step
+    return True
+
+
+def test_trainer_applies_gradient_compression_across_replicas():
+    assert all(run_distributed(_compressed_dp_worker, 2))
+
+
+def test_gradient_compression_refuses_sharded_optimizers():
+    m = tiny_model()
+    arena = ParamArena(m, device=torch.device("cpu"))
+    opt = ArenaAdamW(arena, lr=1e-3)
+    tc = TrainingConfig(global_batch_size=32, micro_batch_size=2, sequence_length=16, max_steps=1,
+                        dtype=torch.float32, vocab_size=64, enable_gradient_compression=True)
+    with pytest.raises(ValueError, match="un-sharded"):
+        Trainer(tc, m, opt, None, None, [])
