@@ -242,6 +242,9 @@ def _build_optimizer_and_scheduler(model, args, tokens_per_rank: int, max_steps:
         # tokens per forward call of a stage: one pipeline microbatch
         m = getattr(args, "pp_microbatches", 0) or args.pp_size
         tokens_per_rank = tokens_per_rank // max(m, 1)
+    if any(getattr(mod, "_tp_fused", False) for mod in model.modules()):
+        # fused tensor parallelism keeps activations as row shards between blocks: a MoE layer sees 1 / tp of the rows
+        tokens_per_rank = tokens_per_rank // max(getattr(args, "tp_size", 1), 1)
     opt, arena = prepare_training(model, tokens_per_rank=tokens_per_rank, lr=args.lr, weight_decay=0.1,
                                   betas=(0.9, 0.95))
     if pp and arena is not None:
@@ -286,6 +289,12 @@ def cmd_train(args) -> int:
     callbacks = [SpeedMonitorCallback(device=device), StabilityMonitorCallback(), ConsoleLoggerCallback(log_interval=1)]
     if device.type == "cuda":
         callbacks.insert(1, GPUMemoryMonitorCallback(device))
+    from .train.callbacks import ThroughputSummaryCallback
+
+    callbacks.append(ThroughputSummaryCallback(
+        warmup_steps=min(5, max(args.max_steps // 3, 1)),
+        label={"model": args.model, "tp": args.tp_size, "pp": args.pp_size, "cp": args.cp_size, "ep": args.ep_size,
+               "batch": args.batch_size, "seq": args.seq_len}))
     if args.wandb:
         callbacks.append(WandBCallback(project=args.wandb_project, config=vars(args)))
     if args.val_interval and val_loader is not None:

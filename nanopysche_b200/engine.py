@@ -35,6 +35,11 @@ def prepare_training(model: nn.Module, *, tokens_per_rank: Optional[int] = None,
     if p0.device.type != "cuda":
         opt = torch.optim.AdamW(model.parameters(), lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         return opt, None
+    if any(type(p).__name__ == "DTensor" for p in model.parameters()):
+        # wrapped by torch's FSDP2 (``--fsdp-backend torch``): the parameters are sharded DTensors that the flat arena
+        # cannot alias; the library's fused AdamW steps the shards
+        opt = torch.optim.AdamW(model.parameters(), lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, fused=True)
+        return opt, None
     if dp_group is None and hasattr(model, "_replica_group"):
         dp_group = model._replica_group   # set by parallelize_model: the ranks holding the same parameters (dp x ep x cp)
     elif dp_group is None and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1 and \

@@ -201,7 +201,10 @@ class Transformer(nn.Module):
         else:
             x = input_ids  # hidden states from the previous pipeline stage
         tp_rt = None
-        if getattr(self, "_tp_fused", False) and x.is_cuda and x.dtype == torch.bfloat16 and self._is_first_stage:
+        # every pipeline stage takes its row shard of the (replicated) hidden states it receives and hands the next
+        # stage replicated rows again: the slice's backward leaves the other ranks' rows zero and the gather's backward
+        # of the previous stage takes exactly this rank's rows, so the partial gradients never need a reduction
+        if getattr(self, "_tp_fused", False) and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3:
             B0, S0, D0 = x.shape
             tp_rt = self._ensure_tp_runtime(B0, S0, x.device)
             x = x.reshape(B0 * S0, D0)[tp_rt.rank * tp_rt.Ms:(tp_rt.rank + 1) * tp_rt.Ms].unsqueeze(0)

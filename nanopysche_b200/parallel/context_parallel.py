@@ -175,13 +175,28 @@ class RingAttention(nn.Module):
     (zig-zag layout when ``use_zigzag``); the output has q's shape.
     """
 
-    def __init__(self, group=None, *, use_ulysses: bool = False, use_zigzag: bool = True, fused: bool = True):
+    def __init__(self, group=None, *, use_ulysses: bool = False, use_zigzag: bool = True,
+                 fused: Optional[bool] = None):
         super().__init__()
         self.group = group
         self.use_ulysses = use_ulysses
         self.use_zigzag = use_zigzag
-        self.fused = fused          # ring attention as one kernel over the peers' memory when the case allows it
+        # One kernel over the peers' memory when the case allows it. ``None`` picks by measurement (B200, total sequence
+        # 16384 - 32768, forward + backward): the fused ring always; fused Ulysses on 2 GPUs (3.63 ms against 3.99 ms
+        # for all-to-alls around the local kernels), the all-to-all form on 4 and 8 (6.49 against 8.33 ms, 3.86
+        # against 13.66 ms: every CTA of the fused form then gathers its rows from up to 7 peers one tile at a time).
+        self._fused_arg = fused
         self._fused_rt = None
+
+    @property
+    def fused(self) -> bool:
+        if self._fused_arg is not None:
+            return bool(self._fused_arg)
+        return (not self.use_ulysses) or self.cp <= 2
+
+    @fused.setter
+    def fused(self, value):
+        self._fused_arg = value
 
     @property
     def cp(self) -> int:

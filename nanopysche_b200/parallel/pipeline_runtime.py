@@ -286,6 +286,17 @@ class PipelineSchedule:
                     g = dist.new_group(list(ranks))
                     if tuple(mine) == ranks:
                         out[(kind, parity)] = g
+        # Create the NCCL communicators now, in the same order on every rank. Creation is collective and blocking and
+        # would otherwise happen at each group's first send or receive, which the ranks of a pipeline reach in different
+        # orders (rank 0 first posts a receive on a gradient channel, rank 1 on an activation channel): each would
+        # then wait inside the creation of a communicator that its peer has not reached yet. The point-to-point
+        # operations below are issued through ``batch_isend_irecv``, which uses the group's collective communicator,
+        # so one small all-reduce per group is enough.
+        if out and dist.get_backend(self.group) == "nccl":
+            warm = torch.zeros(1, device=self._device())
+            for key in sorted(out):
+                dist.all_reduce(warm, group=out[key])
+            torch.cuda.synchronize(warm.device)
         return out
 
     def _chan_group(self, kind: str, sender_rank: int):

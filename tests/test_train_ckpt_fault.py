@@ -463,3 +463,56 @@ def test_gradient_compression_refuses_sharded_optimizers():
                         dtype=torch.float32, vocab_size=64, enable_gradient_compression=True)
     with pytest.raises(ValueError, match="un-sharded"):
         Trainer(tc, m, opt, None, None, [])
+
+
+def test_speed_monitor_reads_device_time_one_step_late_and_normalises_per_device(monkeypatch):
+    """With a (faked) CUDA device the step time comes from event pairs read one step later, and the per-device
+    figures divide by the world size / replica count instead of charging the global batch to one device."""
+    import nanopysche_b200.train.callbacks.speed_monitor as sm
+
+    clock = {"t": 0.0}
+
+    class FakeEvent:
+        def __init__(self, enable_timing=False):
+            self.t = None
+
+        def record(self):
+            self.t = clock["t"]
+
+        def query(self):
+            return False                      # never complete "yet": only older steps are read, after synchronize()
+
+        def synchronize(self):
+            pass
+
+        def elapsed_time(self, other):
+            return (other.t - self.t) * 1e3
+
+    monkeypatch.setattr(sm.torch.cuda, "Event", FakeEvent)
+    monkeypatch.setattr(sm.torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(sm, "_get_device_peak_flops", lambda d: 1e15)
+
+    class T:
+        device = torch.device("cuda", 0)
+        world_size = 8
+        tokens_per_step = 8 * 4096
+        model = torch.nn.Linear(10, 10, bias=False)     # 100 parameters
+        config = type("C", (), {"dp_world_size": 8, "cp_size": 1, "global_batch_size": 8 * 4096})()
+
+        def __init__(self):
+            self.m = {}
+
+        def record_metric(self, k, v):
+            self.m[k] = v
+
+    t, cb = T(), SpeedMonitorCallback()
+    for step in range(3):
+        cb.pre_load_batch(t)
+        cb.pre_step(t, None)
+        clock["t"] += 0.5                    # the device takes 0.5 s per step; the host returns at once
+        cb.post_step(t)
+    # step 3 reports the device time of step 2
+    assert abs(t.m["throughput/device/BPS"] - 2.0) < 1e-6
+    assert abs(t.m["throughput/device/TPS"] - 4096 / 0.5) < 1e-3
+    assert abs(t.m["throughput/device/flopsPS"] - 6 * 100 * 4096 / 0.5) < 1e-3
+    assert t.m["throughput/total tokens"] == 3 * 8 * 4096
