@@ -10,8 +10,9 @@ rank). Activations and gradients move with non-blocking ``batch_isend_irecv`` on
   action list, and the executor keeps ``prefetch`` receives of each channel posted ahead of the action that consumes
   them, so a transfer runs under the compute of earlier actions (NCCL matches point-to-point messages by order, not
   by tag, so receives must be posted in the order the peer sends);
-* activations and gradients use separate communicators, chosen by the parity of the sender's rank, so a receive
-  that is posted early never sits in front of this rank's own sends on one NCCL stream;
+* every directed channel (activation | gradient, sender, receiver) has its own two-rank communicator, so a receive
+  that is posted early never sits in front of another channel's operations on one NCCL stream
+  (``pipeline_sim`` replays every schedule under NCCL's ordering rules on the host);
 * a zero-bubble B action runs the backward pass with every weight-gradient GEMM deferred (``ops.gemm.defer_wgrad``)
   and the W action runs them later.
 """
@@ -194,6 +195,40 @@ def sync_twin_grads(stages: Sequence[nn.Module], group, grad_of=None) -> None:
 
 
 # ------------------------------------------------------------------ executor
+class _P2PTransport:
+    """How the executor moves a message: ``batch_isend_irecv`` on the channel's communicator. The executor talks to
+    this object only, so the same ``step()`` can be replayed against a recording transport
+    (``pipeline_sim.RecordingTransport``) that checks the order of operations under NCCL's rules without a GPU."""
+
+    def __init__(self, sched: "PipelineSchedule"):
+        self.s = sched
+
+    def post_recv(self, kind: str, peer: int, label: tuple, shape, dtype, device):
+        buf = torch.empty(shape, dtype=dtype, device=device)
+        tag = label[2] + (10000 if kind == "grad" else 0) + 100 * label[1]
+        works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, buf, self.s._global(peer),
+                                                   group=self.s._chan_group(kind, peer, self.s.rank), tag=tag)])
+        return buf, works
+
+    def wait_recv(self, handle):
+        buf, works = handle
+        for w in works:
+            w.wait()
+        return buf
+
+    def send(self, kind: str, dst_rank: int, tensor: torch.Tensor, label: tuple):
+        tag = label[2] + (10000 if kind == "grad" else 0) + 100 * label[1]
+        return dist.batch_isend_irecv([dist.P2POp(dist.isend, tensor, self.s._global(dst_rank),
+                                                  group=self.s._chan_group(kind, self.s.rank, dst_rank), tag=tag)])
+
+    def wait_sends(self, works):
+        for w in works:
+            w.wait()
+
+    def compute(self, action) -> None:   # marks where an action's kernels are issued (used by the recorder)
+        pass
+
+
 @dataclass
 class _MB:
     inp: Optional[torch.Tensor] = None
@@ -215,12 +250,19 @@ class PipelineSchedule:
 
     def __init__(self, stages: Sequence[nn.Module], pp_mesh, pp_config: PipelineParallelConfig, *,
                  num_microbatches: Optional[int] = None, loss_fn: Optional[Callable] = None,
-                 hidden_shape: Optional[Sequence[int]] = None, hidden_dtype: Optional[torch.dtype] = None):
+                 hidden_shape: Optional[Sequence[int]] = None, hidden_dtype: Optional[torch.dtype] = None,
+                 transport=None, placement: Optional[tuple] = None):
+        """``transport`` / ``placement=(p, rank)``: run this rank's program without a process group, against a
+        transport that records instead of sending (``pipeline_sim``)."""
         self.stages = list(stages)
         self.group = pp_mesh.get_group() if hasattr(pp_mesh, "get_group") else pp_mesh
         self.cfg = pp_config
-        self.p = dist.get_world_size(self.group) if self.group is not None else 1
-        self.rank = dist.get_rank(self.group) if self.group is not None else 0
+        if placement is not None:
+            self.p, self.rank = placement
+        else:
+            self.p = dist.get_world_size(self.group) if self.group is not None else 1
+            self.rank = dist.get_rank(self.group) if self.group is not None else 0
+        self.transport = transport if transport is not None else _P2PTransport(self)
         self.m = num_microbatches or pp_config.num_microbatches or self.p
         self.loss_fn = loss_fn
         self.hidden_shape = tuple(hidden_shape) if hidden_shape is not None else None
@@ -254,7 +296,8 @@ class PipelineSchedule:
             self.stage_of = {self.rank: self.stages[0], self.p + (self.p - 1 - self.rank): self.stages[-1]}
         else:
             self.stage_of = {getattr(s, "_stage_id", self.rank): s for s in self.stages}
-        self._chan_groups = self._make_channel_groups() if (self.group is not None and dist.is_initialized()) else {}
+        self._chan_groups = self._make_channel_groups() if (self.group is not None and dist.is_initialized() and
+                                                            placement is None) else {}
         self.channels = self._incoming_channels()
 
     # -- helpers
@@ -272,26 +315,34 @@ class PipelineSchedule:
 
     # -- point-to-point plumbing ---------------------------------------------------------------------------------
     def _make_channel_groups(self):
-        """Four communicators over the PP group: (activation | gradient) x parity of the sender's PP rank.
-        ``new_group`` is collective over the whole job, so every rank creates the groups of every PP group."""
+        """One two-rank communicator per directed channel (activation | gradient, sender, receiver) that the schedule
+        uses. On NCCL all operations of a communicator run on one stream per rank in issue order and complete only
+        when the peer's matching operation has reached the head of its stream, so a communicator shared by two
+        channels lets a receive that was posted early hold back an unrelated send behind it; replaying the schedules
+        under those rules (``pipeline_sim``) shows DualPipe on three or more ranks, the V placement on four and the
+        looped placements on an odd number of ranks standing still with communicators shared by sender parity. With
+        one communicator per directed channel each stream carries one FIFO whose two ends agree on the order, and
+        only a cyclic schedule could block. ``new_group`` is collective over the whole job, so every rank creates the
+        groups of every pipeline group, in one order."""
         if self.group is None or self.p <= 1:
             return {}
         mine = [dist.get_global_rank(self.group, r) for r in range(self.p)]
         every = [None] * dist.get_world_size()
         dist.all_gather_object(every, mine)
+        keys = sorted({self._chan_key(kind, r, dst) for r in range(self.p) for kind, dst, _ in self._sends_of(r)})
         out = {}
         for ranks in sorted({tuple(x) for x in every}):
-            for kind in ("act", "grad"):
-                for parity in (0, 1):
-                    g = dist.new_group(list(ranks))
-                    if tuple(mine) == ranks:
-                        out[(kind, parity)] = g
-        # Create the NCCL communicators now, in the same order on every rank. Creation is collective and blocking and
-        # would otherwise happen at each group's first send or receive, which the ranks of a pipeline reach in different
-        # orders (rank 0 first posts a receive on a gradient channel, rank 1 on an activation channel): each would
-        # then wait inside the creation of a communicator that its peer has not reached yet. The point-to-point
-        # operations below are issued through ``batch_isend_irecv``, which uses the group's collective communicator,
-        # so one small all-reduce per group is enough.
+            for key in keys:
+                _, a, b = key
+                g = dist.new_group(sorted((ranks[a], ranks[b])))
+                if tuple(mine) == ranks and self.rank in (a, b):
+                    out[key] = g
+        # Create the NCCL communicators now, in the same (sorted) order on every rank. Creation is collective and
+        # blocking and would otherwise happen at each group's first send or receive, which the ranks of a pipeline
+        # reach in different orders: each would wait inside the creation of a communicator that its peer has not
+        # reached yet. In one global order the smallest unfinished key can always complete, so this cannot block.
+        # The point-to-point operations are issued through ``batch_isend_irecv``, which uses the group's collective
+        # communicator, so one small all-reduce per group creates the communicator they use.
         if out and dist.get_backend(self.group) == "nccl":
             warm = torch.zeros(1, device=self._device())
             for key in sorted(out):
@@ -299,8 +350,13 @@ class PipelineSchedule:
             torch.cuda.synchronize(warm.device)
         return out
 
-    def _chan_group(self, kind: str, sender_rank: int):
-        return self._chan_groups.get((kind, sender_rank & 1), self.group)
+    @staticmethod
+    def _chan_key(kind: str, sender_rank: int, receiver_rank: int) -> tuple:
+        """Which communicator carries the messages of ``kind`` from ``sender_rank`` to ``receiver_rank``."""
+        return (kind, sender_rank, receiver_rank)
+
+    def _chan_group(self, kind: str, sender_rank: int, receiver_rank: int):
+        return self._chan_groups.get(self._chan_key(kind, sender_rank, receiver_rank), self.group)
 
     def _sends_of(self, rank: int) -> List[tuple]:
         """(kind, destination rank, label) of every message ``rank`` sends, in its action order."""
@@ -348,11 +404,7 @@ class PipelineSchedule:
                 raise RuntimeError("hidden_shape is required on stages that receive activations")
             label = channels[ch][nxt[ch]]
             nxt[ch] += 1
-            buf = torch.empty(hs, dtype=hd, device=self._device())
-            tag = label[2] + (10000 if kind == "grad" else 0) + 100 * label[1]
-            works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, buf, self._global(peer),
-                                                       group=self._chan_group(kind, peer), tag=tag)])
-            posted[label] = (buf, works, ch)
+            posted[label] = (self.transport.post_recv(kind, peer, label, hs, hd, self._device()), ch)
             outstanding[ch] += 1
 
         def prefetch():
@@ -363,18 +415,14 @@ class PipelineSchedule:
         def receive(label, ch):
             while label not in posted:      # post in the sender's order until this message's receive is out
                 post_next(ch)
-            buf, works, _ = posted.pop(label)
-            for w in works:
-                w.wait()
+            handle, _ = posted.pop(label)
+            buf = self.transport.wait_recv(handle)
             outstanding[ch] -= 1
             return buf
 
         def send(kind, tensor, dst_stage, label):
             keepalive.append(tensor.detach().contiguous())
-            tag = label[2] + (10000 if kind == "grad" else 0) + 100 * label[1]
-            pending_send.extend(dist.batch_isend_irecv([dist.P2POp(
-                dist.isend, keepalive[-1], self._global(self._rank_of(dst_stage)),
-                group=self._chan_group(kind, self.rank), tag=tag)]))
+            pending_send.extend(self.transport.send(kind, self._rank_of(dst_stage), keepalive[-1], label))
 
         for a in self.actions:
             if a.type == ScheduleType.IDLE:
@@ -384,6 +432,7 @@ class PipelineSchedule:
             stage_mod = self.stage_of[a.stage]
             key = (a.stage, a.microbatch)
             if a.type == ScheduleType.FWD:
+                self.transport.compute(a)
                 mb = state.setdefault(key, _MB())
                 if self._first(a.stage):
                     x = in_chunks[a.microbatch]
@@ -419,6 +468,7 @@ class PipelineSchedule:
                         send("act", y, a.stage + 1, ("act", a.stage + 1, a.microbatch))
             elif a.type in (ScheduleType.BWD, ScheduleType.BWD_INPUT):
                 mb = state[key]
+                self.transport.compute(a)
                 if self._last(a.stage):
                     root, g = mb.loss, None
                 elif self._rank_of(a.stage + 1) == self.rank:
@@ -442,11 +492,11 @@ class PipelineSchedule:
                         send("grad", mb.inp.grad, a.stage - 1, ("grad", a.stage - 1, a.microbatch))
                 state.pop(key)
             elif a.type == ScheduleType.BWD_WEIGHT:
+                self.transport.compute(a)
                 gemm_ops.run_deferred_wgrads(wqueues.pop(key, []))
         for q in wqueues.values():      # a schedule without W actions for some pair: nothing may be left behind
             gemm_ops.run_deferred_wgrads(q)
-        for w in pending_send:
-            w.wait()
+        self.transport.wait_sends(pending_send)
         if losses:
             return torch.stack(losses).mean()
         return None
