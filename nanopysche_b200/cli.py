@@ -60,6 +60,9 @@ def build_parser() -> argparse.ArgumentParser:
     common.add_argument("--async-tp", action="store_true",
                         help="tensor parallelism with the all-gather / reduce-scatter fused into the GEMM kernels "
                              "(sequence-parallel layout over NVLink peer memory)")
+    common.add_argument("--sequence-parallel", action="store_true",
+                        help="Megatron sequence parallelism under --tp-size: activations between blocks are row shards, "
+                             "all-gather / reduce-scatter collectives around the GEMMs (--async-tp fuses them instead)")
     common.add_argument("--pp-size", type=int, default=1)
     common.add_argument("--pp-schedule", default="1F1B", help="GPipe | 1F1B | ZBVZeroBubble | Interleaved1F1B | ...")
     common.add_argument("--pp-microbatches", type=int, default=0, help="microbatches per step (0: one per PP rank)")
@@ -218,7 +221,8 @@ def _maybe_parallelize_model(model, args, device):
     model = parallelize_model(
         model, world_mesh=mesh, device=device,
         tp_config=TensorParallelConfig(args.tp_size, enable_async=getattr(args, "async_tp", False),
-                                       sequence_parallel=getattr(args, "async_tp", False))
+                                       sequence_parallel=getattr(args, "async_tp", False) or
+                                       getattr(args, "sequence_parallel", False))
         if args.tp_size > 1 else None,
         cp_config=ContextParallelConfig(args.cp_size, ring=not args.ulysses, ulysses=args.ulysses)
         if args.cp_size > 1 else None,

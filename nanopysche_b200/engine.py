@@ -51,7 +51,8 @@ def prepare_training(model: nn.Module, *, tokens_per_rank: Optional[int] = None,
         dp_group = dist.group.WORLD
     if replicate_group is None:
         replicate_group = getattr(model, "_replicate_group", None)   # HSDP: set by parallelize_model
-    arena = ParamArena(model, dp_group=dp_group, device=p0.device, replicate_group=replicate_group)
+    arena = ParamArena(model, dp_group=dp_group, device=p0.device, replicate_group=replicate_group,
+                       expert_replica_group=getattr(model, "_expert_replica_group", None))
     moes = moe_layers(model)
     if moes and fused_moe and tokens_per_rank:
         from .ops.moe import build_runtime

@@ -81,7 +81,9 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, *, causal: bool = True, attn_mask: Optional[torch.Tensor] = None,
                 kv_cache: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, start_pos: int = 0,
                 position_ids: Optional[torch.Tensor] = None, return_kv: bool = False, **_):
-        rt = self._tp_rt if (self._tp_rt is not None and _lib.on(x) and x.dtype == torch.bfloat16) else None
+        from ..ops.tp_fused import active as _sp_active
+
+        rt = self._tp_rt if _sp_active(self._tp_rt, x) else None
         hq, hkv, hd = self._local_heads, self._local_kv_heads, self.head_dim
         qkv = None  # fused projection output [B, S, (hq + 2 hkv) * hd] when one GEMM produced all three
         if rt is not None:

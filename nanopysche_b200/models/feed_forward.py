@@ -45,8 +45,9 @@ class FeedForward(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         act = self.activation.value
-        if self._tp_rt is not None and _lib.on(x) and x.dtype == torch.bfloat16 and self.w1.bias is None:
-            from ..ops import tp_fused
+        from ..ops import tp_fused
+
+        if tp_fused.active(self._tp_rt, x) and self.w1.bias is None:
 
             rt = self._tp_rt
             w13 = self._fused_w13 if self._fused_w13 is not None else torch.cat([self.w1.weight, self.w3.weight], 0)

@@ -117,9 +117,26 @@ class MoERouter(nn.Module):
         n_tok = logits.numel() // logits.shape[-1]
         counts = torch.zeros(self.num_experts, device=logits.device, dtype=torch.float32)
         counts.scatter_add_(0, indices.reshape(-1), torch.ones(indices.numel(), device=logits.device))
-        f = counts / n_tok
         P = F.softmax(logits.float(), dim=-1).reshape(-1, self.num_experts).mean(0)
+        sp = getattr(self, "_sp_group", None)
+        if sp is not None and dist.is_available() and dist.is_initialized() and dist.get_world_size(sp) > 1:
+            # sequence-parallel tensor parallelism: this rank routes 1 / tp of the rows. The loss is E * sum(f * P) over
+            # *all* rows: f (token fractions, no gradient) is summed over the group; P is a mean of per-rank means, so
+            # each rank contributes f_all * P_local / tp and the contributions add up over the group - in value after
+            # the all-reduce below, in gradient through the partial-gradient sum of the router's parameters.
+            n = dist.get_world_size(sp)
+            all_counts = counts.clone()
+            dist.all_reduce(all_counts, group=sp)
+            part = self.num_experts * ((all_counts / (n_tok * n)) * P).sum() / n
+            return self._sp_total(part), counts
+        f = counts / n_tok
         return self.num_experts * (f * P).sum(), counts
+
+    def _sp_total(self, part: torch.Tensor) -> torch.Tensor:
+        """Value: the sum of ``part`` over the sequence-parallel group; gradient: this rank's ``part`` only."""
+        tot = part.detach().clone()
+        dist.all_reduce(tot, group=self._sp_group)
+        return part + (tot - part.detach())
 
     def forward(self, x: torch.Tensor):
         """x: (B, S, D) or (T, D) -> (weights (..., K) fp32, indices (..., K) int64, aux_loss)."""
@@ -131,6 +148,12 @@ class MoERouter(nn.Module):
             from ..ops import moe as moe_ops
 
             w, idx, aux, counts = moe_ops.route(x, self)
+            sp = getattr(self, "_sp_group", None)
+            if sp is not None and dist.is_initialized() and dist.get_world_size(sp) > 1:
+                # the router kernels take their load statistics over this rank's rows: under sequence-parallel tensor
+                # parallelism the loss is then the mean of the ranks' own losses (Megatron's per-rank form) rather than
+                # the loss of the whole batch that the PyTorch path below computes
+                aux = self._sp_total(aux / dist.get_world_size(sp))
         else:
             logits = F.linear(x.float(), self.gate.weight, self.gate.bias)
             if self.score_bias is not None:
@@ -145,7 +168,11 @@ class MoERouter(nn.Module):
                 w = w / (w.norm(dim=-1, keepdim=True) + 1e-8)
             aux, counts = self._load_balancing_loss(logits, idx)
             if cfg.z_loss_multiplier is not None:
-                aux = aux + cfg.z_loss_multiplier * torch.logsumexp(logits.float(), dim=-1).square().mean()
+                z = cfg.z_loss_multiplier * torch.logsumexp(logits.float(), dim=-1).square().mean()
+                sp = getattr(self, "_sp_group", None)
+                if sp is not None and dist.is_initialized() and dist.get_world_size(sp) > 1:
+                    z = self._sp_total(z / dist.get_world_size(sp))    # mean over all rows = mean of the ranks' means
+                aux = aux + z
         self.last_counts = counts.detach()
         if self.score_bias is not None:
             self._update_expert_counts(idx, counts)

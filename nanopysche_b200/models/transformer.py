@@ -204,7 +204,8 @@ class Transformer(nn.Module):
         # every pipeline stage takes its row shard of the (replicated) hidden states it receives and hands the next
         # stage replicated rows again: the slice's backward leaves the other ranks' rows zero and the gather's backward
         # of the previous stage takes exactly this rank's rows, so the partial gradients never need a reduction
-        if getattr(self, "_tp_fused", False) and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3:
+        if getattr(self, "_tp_fused", False) and x.dim() == 3 and \
+                (getattr(self, "_tp_host", False) or (x.is_cuda and x.dtype == torch.bfloat16)):
             B0, S0, D0 = x.shape
             tp_rt = self._ensure_tp_runtime(B0, S0, x.device)
             x = x.reshape(B0 * S0, D0)[tp_rt.rank * tp_rt.Ms:(tp_rt.rank + 1) * tp_rt.Ms].unsqueeze(0)
@@ -261,36 +262,65 @@ class Transformer(nn.Module):
         return aux
 
     # ------------------------------------------------------------------ hooks
-    def apply_tp(self, tp_mesh, *, fused: bool = False, **kw):
+    def apply_tp(self, tp_mesh, *, fused: bool = False, sequence_parallel: bool = False, **kw):
         """Megatron TP over ``tp_mesh``. ``fused=True`` (CUDA, bf16) switches to the sequence-parallel
         layout with the all-gather fused into the column-parallel GEMMs and the reduce-scatter into the
-        row-parallel ones (``ops/tp_fused.py``); activations between blocks are then row shards."""
+        row-parallel ones (``ops/tp_fused.py``); activations between blocks are then row shards.
+        ``sequence_parallel=True`` is the same layout through library collectives (all-gather before the
+        column-parallel GEMMs, reduce-scatter behind the row-parallel ones; any device and dtype)."""
         for blk in self.blocks.values():
             blk.apply_tp(tp_mesh)
         self._tp_enabled = True
         self._tp_group = tp_mesh.get_group() if hasattr(tp_mesh, "get_group") else tp_mesh
-        self._tp_fused = bool(fused)
+        p0 = next(self.parameters(), None)
+        on_gpu = p0 is not None and p0.is_cuda and p0.dtype == torch.bfloat16
+        self._tp_host = bool(sequence_parallel and not fused) or bool(fused and not on_gpu)
+        fused = bool(fused or sequence_parallel)
+        self._tp_fused = fused
         self._tp_rt = None
         if fused:
             import torch.distributed as dist
 
             group = self._tp_group
 
-            def reduce_hook(p):
-                if p.grad is not None:
-                    dist.all_reduce(p.grad, group=group)
+            def reduce_hook(g):
+                # the gradient of one backward pass, before it is added to ``.grad``: summing the accumulated
+                # ``.grad`` instead would count earlier micro-batches once per later pass
+                g = g.contiguous().clone()
+                dist.all_reduce(g, group=group)
+                return g
 
             # parameters applied to row shards (or to this rank's heads only) see a partial gradient
             for name, p in self.named_parameters():
                 if "norm" in name or name.startswith("embeddings") or ".router." in name:
                     p._tp_partial = True
-                    p.register_post_accumulate_grad_hook(reduce_hook)
+                    p.register_hook(reduce_hook)
+
+            # A MoE layer is not tensor-parallel: under this layout each TP rank routes and computes its own rows, so
+            # the expert (and shared-expert) weights see a partial gradient as well. Their gradients may be written by
+            # kernels straight into the parameter arena, past any autograd hook, so the arena sums the regions of
+            # parameters carrying ``_sp_reduce_group``; without an arena the hook below does it. The router takes its
+            # load statistics over the whole TP group (``MoERouter._sp_group``).
+            def expert_hook(param):
+                def fn(g):
+                    return g if hasattr(param, "main_grad") else reduce_hook(g)
+                return fn
+
+            for m in self.modules():
+                if isinstance(m, MoEBase):
+                    m.router._sp_group = group
+                    for p in m.parameters():
+                        if not getattr(p, "_tp_partial", False):
+                            p._sp_reduce_group = group
+                            p.register_hook(expert_hook(p))
 
     def _ensure_tp_runtime(self, B: int, S: int, device):
         from ..models.attention import Attention
         from ..models.feed_forward import FeedForward
-        from ..ops.tp_fused import TPRuntime
+        from ..ops.tp_fused import HostTPRuntime, TPRuntime
 
+        if getattr(self, "_tp_host", False):
+            TPRuntime = HostTPRuntime   # noqa: N806 - same interface, library collectives
         if self._tp_rt is None or self._tp_rt.M != B * S:
             cols = self.d_model
             for m in self.modules():

@@ -27,8 +27,56 @@ from .gemm import _wgrad_into, gemm
 from .moe import WAIT_LIMIT_NS
 
 
+def active(rt, x: torch.Tensor) -> bool:
+    """Whether a layer holding runtime ``rt`` takes the sequence-parallel path for input ``x``."""
+    if rt is None:
+        return False
+    return bool(getattr(rt, "host", False)) or (_lib.on(x) and x.dtype == torch.bfloat16)
+
+
+class HostTPRuntime:
+    """The same sequence-parallel layout through library collectives: all-gather, then GEMM; GEMM, then
+    reduce-scatter (Megatron sequence parallelism, reference: distributed/tensor_parallel.py:32-120). It is what
+    ``apply_tp(sequence_parallel=True)`` uses where the fused kernels cannot run (CPU / gloo, dtypes other than bf16),
+    the NCCL arm the fused kernels are measured against, and the CPU test vehicle of everything around the kernels:
+    the row-shard hand-over between blocks and pipeline stages and the partial gradients of the replicated
+    parameters. Same interface as ``TPRuntime`` (``ag_gemm`` / ``gemm_reduce_scatter``)."""
+
+    host = True
+
+    def __init__(self, group, rows: int, max_cols: int = 0, device=None):
+        self.group = group
+        self.N = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.M = rows
+        assert rows % self.N == 0, "token count must be a multiple of the tensor-parallel degree"
+        self.Ms = rows // self.N
+        self.device = device
+        self.batch_shape: Optional[tuple] = None
+
+    def end_step(self):
+        pass
+
+    def ag_gemm(self, x_shard: torch.Tensor, B: torch.Tensor, *, b_mn: bool):
+        full = torch.empty((self.M, x_shard.shape[1]), device=x_shard.device, dtype=x_shard.dtype)
+        dist.all_gather_into_tensor(full, x_shard.contiguous(), group=self.group)
+        return gemm(full, B, b_mn=b_mn), full
+
+    def gemm_reduce_scatter(self, A: torch.Tensor, B: torch.Tensor, *, b_mn: bool) -> torch.Tensor:
+        part = gemm(A, B, b_mn=b_mn)
+        if dist.get_backend(self.group) == "gloo":     # gloo has no reduce-scatter: reduce everything, keep the shard
+            part = part.contiguous()
+            dist.all_reduce(part, group=self.group)
+            return part[self.rank * self.Ms:(self.rank + 1) * self.Ms].clone()
+        out = torch.empty((self.Ms, part.shape[1]), device=part.device, dtype=part.dtype)
+        dist.reduce_scatter_tensor(out, part.contiguous(), group=self.group)
+        return out
+
+
 class TPRuntime:
     """Symmetric buffers and flag tables for one tensor-parallel group (shared by all layers)."""
+
+    host = False
 
     def __init__(self, group, rows: int, max_cols: int, device=None):
         from ..parallel.symm import SymmetricHeap

@@ -51,6 +51,8 @@ class _Region:
     cnt: int = 0
     gshard: Optional[torch.Tensor] = None
     tp_group: Optional[object] = None        # tensor-parallel group these parameters are shards over (None: whole)
+    sp_group: Optional[object] = None        # group over which these parameters' gradients are partial sums (whole
+    #                                          parameters applied to row shards under sequence parallelism)
     # overlapped reduce-scatter (ZeRO regions): the flat buffer is cut into equal buckets, rank r owns slice r of every
     # bucket; master / m / v / gshard hold the owned slices back to back in bucket order
     bucket: int = 0                          # elements per bucket (0: one contiguous shard, no overlap)
@@ -68,7 +70,7 @@ class _Region:
 
 class ParamArena:
     def __init__(self, model: nn.Module, *, dp_group=None, device=None, use_symmetric: Optional[bool] = None,
-                 bucket_elems: Optional[int] = None, replicate_group=None):
+                 bucket_elems: Optional[int] = None, replicate_group=None, expert_replica_group=None):
         params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
         assert params, "model has no trainable parameters"
         self.model = model
@@ -81,6 +83,11 @@ class ParamArena:
         self.replicate_group = replicate_group
         self.rep_world = dist.get_world_size(replicate_group) if (replicate_group is not None and
                                                                   dist.is_initialized()) else 1
+        # ranks holding a copy of the same expert shard that see other tokens (ep_size below the data-parallel size):
+        # the gradients of the expert-sharded regions are summed over them before the update
+        self.expert_replica_group = expert_replica_group
+        self.expert_rep_world = dist.get_world_size(expert_replica_group) if (
+            expert_replica_group is not None and dist.is_initialized()) else 1
         cuda = self.device.type == "cuda"
         self.zero = self.world > 1 and cuda if use_symmetric is None else bool(use_symmetric)
         import os as _os
@@ -114,10 +121,11 @@ class ParamArena:
             seen.add(id(p))
             sharded = bool(getattr(p, "_ep_sharded", False))
             tpg = getattr(p, "_tp_sharded", None)
+            spg = getattr(p, "_sp_reduce_group", None)
             decay = not is_no_decay(n, p)
             key = f"{str(p.dtype).split('.')[-1]}_{'local' if sharded else 'repl'}_{'decay' if decay else 'nodecay'}" \
-                  f"{'_tp' if tpg is not None else ''}"
-            r = self.regions.setdefault(key, _Region(key, p.dtype, decay, not sharded, tp_group=tpg))
+                  f"{'_tp' if tpg is not None else ''}{'_sp' if spg is not None else ''}"
+            r = self.regions.setdefault(key, _Region(key, p.dtype, decay, not sharded, tp_group=tpg, sp_group=spg))
             off = (r.numel + ALIGN - 1) // ALIGN * ALIGN if not self._adjacent_ok(r, p) else r.numel
             r.params.append(p)
             r.names.append(n)
@@ -474,8 +482,11 @@ class ArenaAdamW(torch.optim.Optimizer):
                     C.c_void_p(r.staged.data_ptr()), N - 1, C.c_longlong(r.cnt), C.c_float(inv),
                     C.c_void_p(r.gshard.data_ptr()), C.c_void_p(part.data_ptr()), C.c_void_p(_lib.stream())),
                     "zero_reduce_staged")
-                if R > 1:   # HSDP: sum the shard over the replicas, then take its norm
-                    dist.all_reduce(r.gshard, group=a.replicate_group)
+                if R > 1 or r.sp_group is not None:   # HSDP: sum the shard over the replicas, then take its norm
+                    if R > 1:
+                        dist.all_reduce(r.gshard, group=a.replicate_group)
+                    if r.sp_group is not None:
+                        dist.all_reduce(r.gshard, group=r.sp_group)
                     part.zero_()
                     _lib.call("sumsq", r.gshard, _lib.LL(r.gshard.numel()), part)
             elif a.zero and r.replicated and r.dtype == torch.bfloat16 and r.mc_grads:
@@ -489,8 +500,11 @@ class ArenaAdamW(torch.optim.Optimizer):
                                                      C.c_float(inv), C.c_void_p(r.gshard.data_ptr()),
                                                      C.c_void_p(part.data_ptr()), C.c_void_p(_lib.stream())),
                            "zero_reduce")
-                if R > 1:
-                    dist.all_reduce(r.gshard, group=a.replicate_group)
+                if R > 1 or r.sp_group is not None:
+                    if R > 1:
+                        dist.all_reduce(r.gshard, group=a.replicate_group)
+                    if r.sp_group is not None:
+                        dist.all_reduce(r.gshard, group=r.sp_group)
                     part.zero_()
                     _lib.call("sumsq", r.gshard, _lib.LL(r.gshard.numel()), part)
             else:
@@ -501,10 +515,15 @@ class ArenaAdamW(torch.optim.Optimizer):
                         dist.all_reduce(r.grads, group=a.dp_group)
                 if R > 1 and r.replicated:
                     dist.all_reduce(r.grads, group=a.replicate_group)
+                ER = a.expert_rep_world if not r.replicated else 1
+                if ER > 1:   # copies of this expert shard on other data-parallel ranks
+                    dist.all_reduce(r.grads, group=a.expert_replica_group)
+                if r.sp_group is not None:
+                    dist.all_reduce(r.grads, group=r.sp_group)
                 _lib.call("sumsq", r.grads, _lib.LL(r.grads.numel()), part)
-                # scale of these gradients relative to the final ones: inv; replicated ones are counted
-                # once per rank in the global sum below
-                s = inv * inv / (N if (N > 1 and r.replicated) else 1)
+                # scale of these gradients relative to the final ones: inv; replicated ones (and the copies of an
+                # expert shard) are counted once per holder in the global sum below
+                s = inv * inv / (N if (N > 1 and r.replicated) else ER)
                 part.mul_(s)
         tp_idx = [i for i, r in enumerate(a.regions.values()) if r.tp_group is not None]
         if tp_idx:
@@ -598,8 +617,13 @@ class ArenaAdamW(torch.optim.Optimizer):
                 dist.all_reduce(r.grads, group=a.dp_group)
             if a.rep_world > 1 and r.replicated:
                 dist.all_reduce(r.grads, group=a.replicate_group)
+            ER = a.expert_rep_world if not r.replicated else 1
+            if ER > 1:
+                dist.all_reduce(r.grads, group=a.expert_replica_group)
+            if r.sp_group is not None:
+                dist.all_reduce(r.grads, group=r.sp_group)
             s = (r.grads.float() * inv).pow(2).sum()
-            sq[1 if r.tp_group is not None else 0] += s / (N if (N > 1 and r.replicated) else 1)
+            sq[1 if r.tp_group is not None else 0] += s / (N if (N > 1 and r.replicated) else ER)
             tpg = r.tp_group if r.tp_group is not None else tpg
         if N > 1:
             dist.all_reduce(sq, group=a.dp_group)

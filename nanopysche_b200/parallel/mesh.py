@@ -143,6 +143,30 @@ def get_ep_mesh(world_mesh: Optional[DeviceMesh] = None):
     return None
 
 
+def get_expert_replica_group(world_mesh: Optional[DeviceMesh] = None):
+    """Process group of the ranks that hold the *same expert shard* as this rank and see different tokens: the data-
+    parallel dims that expert parallelism does not use, times cp. With an explicit ep dim those are all dp dims (eight
+    ranks with ``ep_size=2`` keep four copies of every expert, whose gradients have to be summed); without one the
+    experts are spread over dp_shard (or dp) itself and only dp_replicate / cp are left. ``None`` when that product
+    is 1. Collective over the mesh."""
+    mesh = world_mesh or _WORLD_MESH
+    if mesh is None:
+        return None
+    names = _names(mesh)
+    dp_dims = [n for n in names if n in (MeshDimName.dp, MeshDimName.dp_replicate, MeshDimName.dp_shard)]
+    if MeshDimName.ep not in names:
+        for n in (MeshDimName.dp_shard, MeshDimName.dp):     # the dim get_ep_mesh hands to the experts
+            if n in dp_dims:
+                dp_dims.remove(n)
+                break
+    rep = [n for n in dp_dims + ([MeshDimName.cp] if MeshDimName.cp in names else []) if mesh[n].size() > 1]
+    if not rep:
+        return None
+    if len(rep) == 1:
+        return mesh[rep[0]].get_group()
+    return mesh[tuple(n for n in names if n in rep)]._flatten("expert_replica").get_group()
+
+
 def get_hsdp_groups(world_mesh: Optional[DeviceMesh] = None):
     """``(shard_group, replicate_group)`` when the mesh has ``dp_replicate`` and ``dp_shard`` dims (hybrid sharding):
     state is sharded over dp_shard (x ep x cp) and replicated over dp_replicate. ``(None, None)`` otherwise."""

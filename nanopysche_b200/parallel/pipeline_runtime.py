@@ -345,6 +345,9 @@ class PipelineSchedule:
         # communicator, so one small all-reduce per group creates the communicator they use.
         if out and dist.get_backend(self.group) == "nccl":
             warm = torch.zeros(1, device=self._device())
+            # the pipeline group itself first: ``sync_twin_grads`` uses it pairwise and the middle rank of an odd
+            # pipeline takes no part there, so its communicator must exist before
+            dist.all_reduce(warm, group=self.group)
             for key in sorted(out):
                 dist.all_reduce(warm, group=out[key])
             torch.cuda.synchronize(warm.device)

@@ -87,14 +87,24 @@ def parallelize_model(model: nn.Module, *, world_mesh, device: Optional[torch.de
         # apply_tp knows the switch, otherwise the plain all-reduce form
         fused = tp_config.maybe_enable_async_tp(tp_mesh) and device is not None and \
             torch.device(device).type == "cuda"
+        # without the fused kernels (CPU, or not asked for) ``sequence_parallel`` gives the same row-shard layout
+        # through all-gather / reduce-scatter collectives; async TP that cannot be fused falls back to it as well
+        seq_par = bool(getattr(tp_config, "sequence_parallel", False) or (tp_config.enable_async and not fused))
         try:
-            model.apply_tp(tp_mesh, fused=fused) if fused else model.apply_tp(tp_mesh)
+            if fused:
+                model.apply_tp(tp_mesh, fused=True)
+            elif seq_par:
+                model.apply_tp(tp_mesh, sequence_parallel=True)
+            else:
+                model.apply_tp(tp_mesh)
         except TypeError:
             model.apply_tp(tp_mesh)
-            fused = False
+            fused = seq_par = False
         if tp_config.enable_async and not fused:
-            log.warning("  async TP requested but not available here: tensor parallelism uses plain all-reduces")
+            log.warning("  async TP requested but the fused kernels are not available here: %s",
+                        "sequence parallelism through library collectives" if seq_par else "plain all-reduces")
         model._tp_async = bool(fused)
+        model._tp_sequence_parallel = bool(fused or seq_par)
     if ep_requested:
         log.info("  Applying EP")
         model.apply_ep(get_ep_mesh(world_mesh))
@@ -135,6 +145,11 @@ def parallelize_model(model: nn.Module, *, world_mesh, device: Optional[torch.de
             model.apply_fsdp(dp_mesh=dp_mesh, param_dtype=dp_config.param_dtype, reduce_dtype=dp_config.reduce_dtype)
         else:
             apply_generic_fsdp(model, dp_mesh, dp_config)
+    if world_mesh is not None and ep_requested:
+        # copies of one expert shard on ranks that read other batches (ep_size smaller than the data-parallel size)
+        from .parallel.mesh import get_expert_replica_group
+
+        model._expert_replica_group = get_expert_replica_group(world_mesh)
     if world_mesh is not None and not hasattr(model, "_replica_group"):
         # un-sharded data parallelism: gradients are averaged over the ranks that hold the same parameters
         model._replica_group = get_replica_group(world_mesh)

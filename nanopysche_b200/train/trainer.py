@@ -272,7 +272,11 @@ class Trainer:
             self._sync_replicated_grads()
             if c.max_grad_norm and c.max_grad_norm > 0:
                 params = [p for p in self.model.parameters() if p.grad is not None]
-                if getattr(self.model, "_pp_enabled", False):
+                sharded = any(getattr(p, "_ep_sharded", False) or getattr(p, "_tp_sharded", None) is not None
+                              for p in params) and dist.is_available() and dist.is_initialized()
+                if getattr(self.model, "_pp_enabled", False) or sharded:
+                    # one norm over every shard: tensor-parallel shards add up over their group, expert shards over the
+                    # expert-parallel group, pipeline stages over the pipeline group
                     from ..parallel.pipeline_runtime import clip_grad_norm_pp
 
                     ep_group = next((m.ep.ep_group for m in self.model.modules()
@@ -337,6 +341,32 @@ class Trainer:
         r = self._grad_reducer()
         if r is not None:
             r.finish()
+        self._sync_expert_replicas()
+
+    def _sync_expert_replicas(self):
+        """Expert shards are left out of the replica reduction above (every expert-parallel rank holds other experts).
+        An expert's gradient already collects the tokens of all expert-parallel peers, each with its own rank's
+        mean-loss scale; what is missing is (1) the sum over the copies of the same shard on other data-parallel ranks
+        (``ep_size`` below the data-parallel size) and (2) the division by the number of ranks that read different
+        batches, which the replicated parameters get from their averaging all-reduce."""
+        if not (dist.is_available() and dist.is_initialized()) or self._arena_opt:
+            return
+        ps = [p for p in self.model.parameters() if getattr(p, "_ep_sharded", False) and p.grad is not None]
+        if not ps:
+            return
+        group = getattr(self.model, "_expert_replica_group", None)
+        replica = getattr(self.model, "_replica_group", None)
+        n_data = (dist.get_world_size(replica) if replica is not None else 1) / max(self.config.cp_size, 1)
+        if group is not None and dist.get_world_size(group) > 1:
+            flat = torch.cat([p.grad.reshape(-1).float() for p in ps])
+            dist.all_reduce(flat, group=group)
+            off = 0
+            for p in ps:
+                p.grad.copy_(flat[off:off + p.numel()].view_as(p.grad))
+                off += p.numel()
+        if n_data > 1:
+            for p in ps:
+                p.grad.div_(n_data)
 
     def _post_batch_hooks(self):
         for m in self.model.modules():

@@ -92,9 +92,11 @@ def test_trainer_runs_pipeline_stages(schedule):
     assert all(run_distributed(_pp_trainer_worker, 2, schedule))
 
 
-def _pp_tp_worker(rank, world):
+def _pp_tp_worker(rank, world, seq_par=False):
     """pp=2 x tp=2 on four ranks: each pipeline stage is tensor-parallel; loss and a gradient of every stage
-    match the unsharded model."""
+    match the unsharded model. ``seq_par``: the sequence-parallel layout - every stage slices its row shard out of
+    the replicated hidden states it receives and gathers them again at its end, so the gradient it sends back is
+    non-zero on its own rows only, which is exactly what the previous stage's gather takes."""
     from nanopysche_b200.parallel.mesh import build_world_mesh, get_pp_mesh, get_tp_mesh
     from nanopysche_b200.parallel.pipeline_parallel import PipelineParallelConfig
     from nanopysche_b200.parallel.pipeline_runtime import PipelineParallelConfig as RuntimePPConfig
@@ -109,11 +111,13 @@ def _pp_tp_worker(rank, world):
     ref = model(x, labels=x)["loss"]
     ref.backward()
     g_ref = {i: model.blocks[str(i)].attention.w_out.weight.grad.clone() for i in range(4)}
+    n_ref = {i: model.blocks[str(i)].attention_norm.weight.grad.clone() for i in range(4)}
     model.zero_grad()
 
     mesh = build_world_mesh(pp_size=2, tp_size=2, device_type="cpu", replace=True)
     model = parallelize_model(model, world_mesh=mesh, pp_config=PipelineParallelConfig(2),
-                              tp_config=TensorParallelConfig(2))
+                              tp_config=TensorParallelConfig(2, sequence_parallel=seq_par))
+    assert bool(getattr(model, "_tp_fused", False)) == seq_par
     pp_group, tp_group = get_pp_mesh(mesh).get_group(), get_tp_mesh(mesh).get_group()
     pp_rank, tp_rank = dist.get_rank(pp_group), dist.get_rank(tp_group)
     sched = PipelineSchedule([model], pp_group, RuntimePPConfig(2, num_microbatches=2), num_microbatches=2,
@@ -125,11 +129,15 @@ def _pp_tp_worker(rank, world):
         w = model.blocks[str(i)].attention.w_out.weight          # row-parallel: input features sharded over tp
         cols = g_ref[i].shape[1] // 2
         assert torch.allclose(w.grad, g_ref[i][:, tp_rank * cols:(tp_rank + 1) * cols], atol=1e-5), i
+        if seq_par:   # replicated parameters applied to row shards: the hook sums the partial gradients over tp
+            n = model.blocks[str(i)].attention_norm.weight
+            assert torch.allclose(n.grad, n_ref[i], atol=1e-5), i
     return True
 
 
-def test_pipeline_times_tensor_parallel_four_ranks():
-    assert all(run_distributed(_pp_tp_worker, 4))
+@pytest.mark.parametrize("seq_par", [False, True])
+def test_pipeline_times_tensor_parallel_four_ranks(seq_par):
+    assert all(run_distributed(_pp_tp_worker, 4, seq_par))
 
 
 def _hybrid_cfg():
@@ -141,7 +149,7 @@ def _hybrid_cfg():
                              moe_offset=1, moe_hidden=32, moe_capacity_factor=None)
 
 
-def _pp_tp_ep_worker(rank, world):
+def _pp_tp_ep_worker(rank, world, seq_par=False):
     """PP 2 (DualPipe) x EP 2 x TP 2 on eight ranks through parallelize_model + Trainer.fit: the loss (averaged over
     the expert-parallel ranks, which read different batches) follows the single-process model on all batches, and so
     do the parameters of the stages this rank holds."""
@@ -173,7 +181,7 @@ def _pp_tp_ep_worker(rank, world):
 
     model = parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"),
                               pp_config=PipelineParallelConfig(2, schedule="DualPipe", num_microbatches=2),
-                              tp_config=TensorParallelConfig(2))
+                              tp_config=TensorParallelConfig(2, sequence_parallel=seq_par))
     assert model.is_dualpipe and len(model.stages) == 2 and model._replica_group is not None
     opt = torch.optim.AdamW(model.parameters(), lr=1e-2, weight_decay=0.0)
     mine = all_batches[ep_rank]
@@ -197,8 +205,11 @@ def _pp_tp_ep_worker(rank, world):
     return [float(x) for x in got], ref_losses, ep_rank
 
 
-def test_dualpipe_times_expert_parallel_times_tensor_parallel_eight_ranks():
-    res = run_distributed(_pp_tp_ep_worker, 8, timeout=600)
+@pytest.mark.parametrize("seq_par", [False, True])
+def test_dualpipe_times_expert_parallel_times_tensor_parallel_eight_ranks(seq_par):
+    """``seq_par``: the configuration of the 7B hybrid run with ``--async-tp`` - every stage works on row shards, so a
+    MoE layer routes this rank's half of the tokens and the router's gradient is partial over the TP group."""
+    res = run_distributed(_pp_tp_ep_worker, 8, seq_par, timeout=600)
     ref_losses = res[0][1]
     for step in range(2):
         by_ep = {}
@@ -206,3 +217,76 @@ def test_dualpipe_times_expert_parallel_times_tensor_parallel_eight_ranks():
             by_ep.setdefault(ep, losses[step])
         mean = sum(by_ep.values()) / len(by_ep)
         assert mean == pytest.approx(ref_losses[step], rel=5e-3), (step, by_ep, ref_losses)
+
+
+def _ep_dp_worker(rank, world, use_arena):
+    """ep_size 2 on four ranks: two data-parallel copies of every expert shard. Three Trainer steps follow the
+    single-process model that sees all four batches (expert gradients summed over the copies, every gradient scaled
+    by the number of ranks that read different batches, one clipping norm over all shards)."""
+    from nanopysche_b200.optim.arena import ArenaAdamW, ParamArena
+    from nanopysche_b200.parallel.mesh import build_world_mesh, get_expert_replica_group
+    from nanopysche_b200.parallelize import parallelize_model
+    from nanopysche_b200.train.trainer import Trainer, TrainingConfig
+
+    torch.manual_seed(0)
+    model = _hybrid_cfg().build()
+    ref = _hybrid_cfg().build()
+    ref.load_state_dict(model.state_dict())
+    mesh = build_world_mesh(ep_size=2, device_type="cpu", replace=True)
+    assert "ep" in mesh.mesh_dim_names and mesh["dp"].size() == 2
+    torch.manual_seed(1)
+    all_batches = [[torch.randint(0, 64, (2, 8)) for _ in range(3)] for _ in range(world)]   # [rank][step]
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.0)
+    ref_losses = []
+    for step in range(3):
+        ids = torch.cat([all_batches[r][step] for r in range(world)])
+        out = ref(ids, labels=ids)
+        (out["loss"] + out["aux_loss"]).backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
+        ropt.step()
+        ropt.zero_grad()
+        ref_losses.append(out["loss"].item())
+
+    model = parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"))
+    grp = get_expert_replica_group(mesh)
+    assert model._expert_replica_group is not None and dist.get_world_size(grp) == 2
+    if use_arena:
+        arena = ParamArena(model, dp_group=model._replica_group, device=torch.device("cpu"),
+                           expert_replica_group=model._expert_replica_group)
+        opt = ArenaAdamW(arena, lr=1e-2, weight_decay=0.0, max_grad_norm=0.5)
+    else:
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-2, weight_decay=0.0)
+    mine = all_batches[rank]
+
+    class Loader:
+        def __iter__(self):
+            return iter([(b, b.clone()) for b in mine])
+
+    tc = TrainingConfig(global_batch_size=world * 2 * 8, micro_batch_size=2, sequence_length=8, max_steps=3,
+                        dtype=torch.float32, log_interval=0, save_interval=0, vocab_size=64, dp_world_size=world,
+                        max_grad_norm=0.5)
+    tr = Trainer(tc, model, opt, data_loader=Loader(), device=torch.device("cpu"))
+    got, orig = [], tr._train_step
+
+    def spy(b):
+        out = orig(b)
+        got.append(out.detach().clone())
+        return out
+
+    tr._train_step = spy
+    tr.fit()
+    # replicas of one expert shard stay identical
+    w = model.blocks["1"].moe.w1.detach().clone()
+    both = [torch.zeros_like(w) for _ in range(2)]
+    dist.all_gather(both, w, group=grp)
+    assert torch.allclose(both[0], both[1], atol=1e-7)
+    return [float(x) for x in got], ref_losses
+
+
+@pytest.mark.parametrize("use_arena", [False, True])
+def test_expert_replicas_across_data_parallel_ranks(use_arena):
+    res = run_distributed(_ep_dp_worker, 4, use_arena, timeout=600)
+    ref_losses = res[0][1]
+    for step in range(3):
+        mean = sum(r[0][step] for r in res) / len(res)
+        assert mean == pytest.approx(ref_losses[step], rel=2e-3), (step, [r[0][step] for r in res], ref_losses)
