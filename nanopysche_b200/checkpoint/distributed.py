@@ -429,8 +429,12 @@ class DistributedCheckpointer:
             raise FileNotFoundError(f"no checkpoint found under {path or self.config.save_dir}")
         with open(os.path.join(path, "metadata.json")) as f:
             meta = json.load(f)
-        rank, _ = self._rank_world()
-        pre = os.path.join(path, f"rank_{rank:04d}_")
+        rank, world = self._rank_world()
+        saved_world = int(meta.get("world_size") or world)
+        # Resuming on another number of ranks (pure data parallelism): the replicated model is in every rank's file,
+        # the sharded optimizer state is put together from all of them (``load_state_dict_resharded``)
+        src_rank = rank if rank < saved_world else rank % saved_world
+        pre = os.path.join(path, f"rank_{src_rank:04d}_")
 
         def _load(p):
             return torch.load(p, map_location="cpu", weights_only=False)
@@ -439,15 +443,18 @@ class DistributedCheckpointer:
             sd: Dict[str, Any] = {}
             if meta.get("incremental") and meta.get("base_checkpoint"):
                 base = os.path.join(os.path.dirname(path), meta["base_checkpoint"])
-                sd.update(_load(os.path.join(base, f"rank_{rank:04d}_model.pt")))
+                sd.update(_load(os.path.join(base, f"rank_{src_rank:04d}_model.pt")))
                 # deltas between the base and this one, oldest first
                 for st, _, p, m in self._checkpoints_in(os.path.dirname(path)):
                     if m.get("incremental") and m.get("base_checkpoint") == meta["base_checkpoint"] and \
                             st < meta["step"]:
-                        sd.update(_load(os.path.join(p, f"rank_{rank:04d}_model.pt")))
+                        sd.update(_load(os.path.join(p, f"rank_{src_rank:04d}_model.pt")))
             sd.update(_load(pre + "model.pt"))
             model.load_state_dict(sd, strict=strict)
-        if optimizer is not None and os.path.exists(pre + "optimizer.pt"):
+        if optimizer is not None and saved_world != world and hasattr(optimizer, "load_state_dict_resharded"):
+            optimizer.load_state_dict_resharded(
+                [_load(os.path.join(path, f"rank_{i:04d}_optimizer.pt")) for i in range(saved_world)])
+        elif optimizer is not None and os.path.exists(pre + "optimizer.pt"):
             optimizer.load_state_dict(_load(pre + "optimizer.pt"))
         if scheduler is not None and os.path.exists(pre + "scheduler.pt"):
             scheduler.load_state_dict(_load(pre + "scheduler.pt"))

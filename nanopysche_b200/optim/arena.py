@@ -68,6 +68,24 @@ class _Region:
     _mc_keep: Optional[tuple] = None         # symmetric-memory handles, kept alive with the region
 
 
+def owned_slice(flat: torch.Tensor, world: int, rank: int, bucket: int) -> torch.Tensor:
+    """Rank ``rank``'s part of a flat region buffer of a ``world``-way sharded arena: one contiguous piece, or - with
+    the bucketed reduce-scatter - slice ``rank`` of every bucket, back to back."""
+    if bucket:
+        return flat.view(-1, world, bucket // world)[:, rank].reshape(-1)
+    cnt = flat.numel() // world
+    return flat[rank * cnt:(rank + 1) * cnt]
+
+
+def assemble_shards(shards: List[torch.Tensor], bucket: int) -> torch.Tensor:
+    """Inverse of ``owned_slice``: the flat buffer from the parts of all ranks (in rank order)."""
+    world = len(shards)
+    if bucket:
+        sl = bucket // world
+        return torch.stack([sh.view(-1, sl) for sh in shards], dim=1).reshape(-1)
+    return torch.cat(shards)
+
+
 class ParamArena:
     def __init__(self, model: nn.Module, *, dp_group=None, device=None, use_symmetric: Optional[bool] = None,
                  bucket_elems: Optional[int] = None, replicate_group=None, expert_replica_group=None):
@@ -655,7 +673,52 @@ class ArenaAdamW(torch.optim.Optimizer):
         return {"step": self.step_count, "param_groups": [{k: v for k, v in g.items() if k != "params"}
                                                           for g in self.param_groups],
                 "regions": {k: {"master": r.master, "m": r.m, "v": r.v, "lo": r.lo, "cnt": r.cnt, "bucket": r.bucket}
-                            for k, r in a.regions.items()}}
+                            for k, r in a.regions.items()},
+                # how the state above is cut, so that a run on another number of ranks can put it together again
+                "layout": {"world": a.world, "rank": a.rank,
+                           "regions": {k: {"numel": r.numel, "total": r.weights.numel(), "replicated": r.replicated,
+                                           "sharded": bool(r.cnt != r.weights.numel())}
+                                       for k, r in a.regions.items()}}}
+
+    def load_state_dict_resharded(self, by_rank: List[dict]):
+        """Restore from the optimizer states of *all* ranks of a run with another data-parallel size (``by_rank[i]``:
+        what rank i saved). Sharded regions are put together from every rank's part, cut to the parameters' length
+        (the padding depends on the old world size) and cut again the way this arena shards them. Expert-sharded
+        regions hold other experts on every rank: they can only be taken over when the expert placement is unchanged,
+        which a different world size rules out, so that case raises instead of loading the wrong experts."""
+        first = by_rank[0]
+        old = first.get("layout")
+        if old is None:
+            raise ValueError("this checkpoint predates the layout record needed for re-sharding")
+        assert len(by_rank) == old["world"], "need the optimizer state of every rank of the saved run"
+        self.step_count = first["step"]
+        for g, s in zip(self.param_groups, first["param_groups"]):
+            g.update(s)
+        a = self.arena
+        for k, r in a.regions.items():
+            lay = old["regions"].get(k)
+            if lay is None:
+                raise KeyError(f"region {k} is not in the checkpoint")
+            if not r.replicated and a.world != old["world"]:
+                raise ValueError(f"region {k} is expert-sharded: the expert placement of a {old['world']}-rank run "
+                                 f"cannot be mapped onto {a.world} ranks")
+            total_new = r.weights.numel()
+            for name in ("master", "m", "v"):
+                cur = getattr(r, name)
+                if cur is None:
+                    continue
+                parts = [sd["regions"][k][name] for sd in by_rank]
+                if any(p_ is None for p_ in parts):
+                    continue
+                if lay["sharded"]:
+                    full = assemble_shards([p_.reshape(-1) for p_ in parts], first["regions"][k]["bucket"])
+                else:
+                    full = parts[min(a.rank, len(parts) - 1)].reshape(-1) if not r.replicated else parts[0].reshape(-1)
+                full = full[:lay["numel"]]
+                flat = torch.zeros(total_new, dtype=cur.dtype)
+                flat[:full.numel()] = full.to(cur.dtype)
+                piece = owned_slice(flat, a.world, a.rank, r.bucket) if cur.numel() != total_new else flat
+                cur.copy_(piece.to(cur.device))
 
     def load_state_dict(self, sd):
         self.step_count = sd["step"]

@@ -516,3 +516,83 @@ def test_speed_monitor_reads_device_time_one_step_late_and_normalises_per_device
     assert abs(t.m["throughput/device/TPS"] - 4096 / 0.5) < 1e-3
     assert abs(t.m["throughput/device/flopsPS"] - 6 * 100 * 4096 / 0.5) < 1e-3
     assert t.m["throughput/total tokens"] == 3 * 8 * 4096
+
+
+def test_arena_optimizer_state_reshards_to_another_world_size(tmp_path):
+    """Elastic resume: the optimizer state of a 4-rank run with the bucketed shard layout (and of a 2-rank run with the
+    contiguous one) is put together and cut again for this process's layout; the shard helpers are inverse to each
+    other for every layout; an expert-sharded region refuses a changed world size."""
+    from nanopysche_b200.optim.arena import assemble_shards, owned_slice
+
+    flat = torch.arange(2 * 4 * 6, dtype=torch.float32)
+    for world, bucket in ((4, 24), (2, 0), (4, 0), (2, 12), (1, 0)):
+        parts = [owned_slice(flat, world, r, bucket) for r in range(world)]
+        assert sum(p.numel() for p in parts) == flat.numel()
+        assert torch.equal(assemble_shards(parts, bucket), flat)
+    assert torch.equal(owned_slice(flat, 4, 1, 24), torch.cat([flat[6:12], flat[30:36]]))   # slice 1 of both buckets
+
+    torch.manual_seed(0)
+    m = tiny_model()
+    arena = ParamArena(m, device=torch.device("cpu"))
+    opt = ArenaAdamW(arena, lr=1e-3)
+    want = {}
+    for k, r in arena.regions.items():
+        r.m.copy_(torch.randn_like(r.m))
+        r.v.copy_(torch.rand_like(r.v))
+        want[k] = (r.m.clone(), r.v.clone())
+    full_sd = opt.state_dict()
+    full_sd["step"] = 7
+
+    def fake_run(world, bucket_of):
+        """What the ranks of a ``world``-way sharded run would have saved for this optimizer state."""
+        out = []
+        for rank in range(world):
+            regs = {}
+            for k, r in arena.regions.items():
+                b = bucket_of(r)
+                total = (r.numel + max(b, 4 * world) - 1) // max(b, 4 * world) * max(b, 4 * world)
+                ent = {"master": None, "lo": 0, "cnt": total // world, "bucket": b}
+                for name in ("m", "v"):
+                    pad = torch.zeros(total)
+                    pad[:r.numel] = getattr(r, name)[:r.numel]
+                    ent[name] = owned_slice(pad, world, rank, b).clone()
+                regs[k] = ent
+            lay = {"world": world, "rank": rank,
+                   "regions": {k: {"numel": r.numel, "total": 0, "replicated": True, "sharded": True}
+                               for k, r in arena.regions.items()}}
+            out.append({"step": 7, "param_groups": full_sd["param_groups"], "regions": regs, "layout": lay})
+        return out
+
+    for world, bucket_of in ((4, lambda r: 64), (2, lambda r: 0)):
+        saved = fake_run(world, bucket_of)
+        for r in arena.regions.values():
+            r.m.zero_()
+            r.v.zero_()
+        opt.load_state_dict_resharded(saved)
+        assert opt.step_count == 7
+        for k, r in arena.regions.items():
+            assert torch.equal(r.m[:r.numel], want[k][0][:r.numel]) and torch.equal(r.v[:r.numel], want[k][1][:r.numel])
+
+    # through the checkpointer: a directory written by a 2-rank run, read by this single process
+    ck = DistributedCheckpointer(CheckpointConfig(save_dir=str(tmp_path), pinned_memory=False))
+    ck.save(7, m, opt)
+    step_dir = ck._find_latest_checkpoint()
+    meta_path = os.path.join(step_dir, "metadata.json")
+    meta = json.load(open(meta_path))
+    meta["world_size"] = 2
+    json.dump(meta, open(meta_path, "w"))
+    for rank, sd in enumerate(fake_run(2, lambda r: 0)):
+        torch.save(sd, os.path.join(step_dir, f"rank_{rank:04d}_optimizer.pt"))
+    bad = fake_run(2, lambda r: 0)
+    for r in arena.regions.values():
+        r.m.zero_()
+    ck.load(step_dir, m, opt)
+    for k, r in arena.regions.items():
+        assert torch.equal(r.m[:r.numel], want[k][0][:r.numel])
+
+    # expert-sharded regions cannot follow a changed world size
+    key = next(iter(arena.regions))
+    arena.regions[key].replicated = False
+    arena.world = 1
+    with pytest.raises(ValueError, match="expert-sharded"):
+        opt.load_state_dict_resharded(bad)
