@@ -435,7 +435,6 @@ class PipelineSchedule:
             stage_mod = self.stage_of[a.stage]
             key = (a.stage, a.microbatch)
             if a.type == ScheduleType.FWD:
-                self.transport.compute(a)
                 mb = state.setdefault(key, _MB())
                 if self._first(a.stage):
                     x = in_chunks[a.microbatch]
@@ -445,6 +444,7 @@ class PipelineSchedule:
                     x = receive(("act", a.stage, a.microbatch), (self._rank_of(a.stage - 1), "act"))
                     x.requires_grad_(True)
                 mb.inp = x
+                self.transport.compute(a)     # everything this action waits for has been waited for
                 if self._last(a.stage):
                     out = stage_mod(x, labels=tg_chunks[a.microbatch], **kwargs) if self.loss_fn is None else \
                         stage_mod(x, **kwargs)
@@ -471,7 +471,6 @@ class PipelineSchedule:
                         send("act", y, a.stage + 1, ("act", a.stage + 1, a.microbatch))
             elif a.type in (ScheduleType.BWD, ScheduleType.BWD_INPUT):
                 mb = state[key]
-                self.transport.compute(a)
                 if self._last(a.stage):
                     root, g = mb.loss, None
                 elif self._rank_of(a.stage + 1) == self.rank:
@@ -479,6 +478,7 @@ class PipelineSchedule:
                 else:
                     root, g = mb.out, receive(("grad", a.stage, a.microbatch), (self._rank_of(a.stage + 1), "grad"))
                 roots, gouts = [root], [g]
+                self.transport.compute(a)
                 if mb.aux is not None:
                     roots.append(mb.aux)
                     gouts.append(torch.ones_like(mb.aux))

@@ -38,6 +38,8 @@ class Op:
     deps: List[int] = field(default_factory=list)   # indices (into the rank's op list) that must finish first
     done: bool = False
     note: str = ""
+    action: str = ""                # compute ops: "FWD" | "BWD" | "BWD_INPUT" | "BWD_WEIGHT"
+    t_end: float = 0.0              # finish time in the timed replay
 
 
 class RecordingTransport:
@@ -80,7 +82,8 @@ class RecordingTransport:
         if self._last_compute is not None:
             deps.append(self._last_compute)
         self._waited = []
-        self.ops.append(Op("compute", ("compute",), deps=deps, note=f"{action.type.name} s{action.stage} mb{action.microbatch}"))
+        self.ops.append(Op("compute", ("compute",), deps=deps, action=action.type.name,
+                           note=f"{action.type.name} s{action.stage} mb{action.microbatch}"))
         self._last_compute = len(self.ops) - 1
 
 
@@ -118,10 +121,19 @@ def trace_rank(schedule, p: int, m: int, rank: int, prefetch: Optional[int] = No
         gemm_ops.SPLIT_MODE = split_mode
 
 
-def simulate(programs: List[List[Op]]) -> Tuple[bool, List[str]]:
+def simulate(programs: List[List[Op]], cost: Optional[Dict[str, float]] = None) -> Tuple[bool, List[str]]:
     """Advance all ranks' streams under NCCL's rules. Returns ``(finished, stuck)`` where ``stuck`` describes the head
-    of every stream that could not move."""
+    of every stream that could not move. With ``cost`` (durations per compute action name plus ``"p2p"``) every
+    operation also gets a finish time ``t_end``: it starts when its stream is free and its dependencies (and, for a
+    transfer, the peer's side) are ready."""
     n = len(programs)
+    cost = cost or {}
+    free: List[Dict[tuple, float]] = [dict() for _ in range(n)]
+
+    def t_ready(r, i):
+        op = programs[r][i]
+        return max([free[r].get(op.stream, 0.0)] + [programs[r][d].t_end for d in op.deps])
+
     streams: List[Dict[tuple, List[int]]] = []
     for ops in programs:
         by: Dict[tuple, List[int]] = {}
@@ -157,6 +169,8 @@ def simulate(programs: List[List[Op]]) -> Tuple[bool, List[str]]:
                     continue
                 op = programs[r][i]
                 if op.kind == "compute":
+                    op.t_end = t_ready(r, i) + cost.get(op.action, 0.0)
+                    free[r][k] = op.t_end
                     op.done = True
                     heads[r][k] += 1
                     progress = True
@@ -168,6 +182,9 @@ def simulate(programs: List[List[Op]]) -> Tuple[bool, List[str]]:
                     if programs[op.peer][j].label != op.label:     # NCCL matches by order: the labels must agree
                         return False, [f"rank {r} {op.kind} {op.label} met rank {op.peer} "
                                        f"{programs[op.peer][j].kind} {programs[op.peer][j].label}"]
+                    end = max(t_ready(r, i), t_ready(op.peer, j)) + cost.get("p2p", 0.0)
+                    op.t_end = programs[op.peer][j].t_end = end
+                    free[r][k] = free[op.peer][op.stream] = end
                     op.done = programs[op.peer][j].done = True
                     heads[r][k] += 1
                     heads[op.peer][op.stream] += 1
@@ -190,3 +207,21 @@ def check_schedule(schedule, p: int, m: int, prefetch: Optional[int] = None, cha
     send met the receive with its own label."""
     programs = [trace_rank(schedule, p, m, r, prefetch, chan_key) for r in range(p)]
     return simulate(programs)
+
+
+def timeline(schedule, p: int, m: int, *, t_fwd: float = 1.0, t_bwd: float = 2.0, t_bwd_input: Optional[float] = None,
+             t_bwd_weight: Optional[float] = None, t_p2p: float = 0.0, prefetch: Optional[int] = None) -> Dict[str, float]:
+    """Timed replay of one step: ``{"makespan", "bubble"}`` where ``bubble`` is the idle share of the compute streams
+    (1 - busy time / (p x makespan)). A full backward costs ``t_bwd``; schedules with a B / W split charge
+    ``t_bwd_input`` and ``t_bwd_weight`` (default: half of ``t_bwd`` each); a transfer occupies its two streams for
+    ``t_p2p``. For GPipe and 1F1B without transfer cost this gives the closed form (p - 1) / (m + p - 1)."""
+    bi = t_bwd / 2 if t_bwd_input is None else t_bwd_input
+    bw = t_bwd / 2 if t_bwd_weight is None else t_bwd_weight
+    cost = {"FWD": t_fwd, "BWD": t_bwd, "BWD_INPUT": bi, "BWD_WEIGHT": bw, "p2p": t_p2p}
+    programs = [trace_rank(schedule, p, m, r, prefetch) for r in range(p)]
+    ok, stuck = simulate(programs, cost)
+    if not ok:
+        raise RuntimeError(f"schedule does not complete: {stuck[:3]}")
+    makespan = max(op.t_end for ops in programs for op in ops)
+    busy = sum(cost.get(op.action, 0.0) for ops in programs for op in ops if op.kind == "compute")
+    return {"makespan": makespan, "bubble": 1.0 - busy / (p * makespan)}

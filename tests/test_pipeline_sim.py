@@ -44,3 +44,20 @@ def test_order_mismatch_is_reported():
     sends[0].label, sends[1].label = sends[1].label, sends[0].label
     ok, msg = simulate(progs)
     assert not ok and "met" in msg[0]
+
+
+def test_timed_replay_reproduces_closed_form_bubbles_and_ranks_schedules():
+    from nanopysche_b200.parallel.pipeline_sim import timeline
+
+    for p, m in ((4, 8), (4, 16), (8, 16)):
+        closed = (p - 1) / (m + p - 1)
+        for sch in ("GPipe", "1F1B"):
+            t = timeline(sch, p, m, t_fwd=1.0, t_bwd=2.0)
+            assert t["makespan"] == pytest.approx((m + p - 1) * 3.0)
+            assert t["bubble"] == pytest.approx(closed, abs=1e-9)
+        # two half-size stages per rank: compare at equal work per rank (half the cost per action)
+        zb = timeline("ZBVZeroBubble", p, m, t_fwd=0.5, t_bwd=1.0)
+        dual = timeline("DualPipe", p, m, t_fwd=1.0, t_bwd=2.0)
+        assert zb["bubble"] < 0.5 * closed and dual["bubble"] < 0.5 * closed
+    # a transfer cost lengthens the step of a schedule whose transfers are on the critical path
+    assert timeline("GPipe", 4, 8, t_p2p=0.25)["makespan"] > timeline("GPipe", 4, 8)["makespan"]
