@@ -135,51 +135,80 @@ class OneForwardOneBackwardSchedule(_Schedule):
 
 
 def _greedy(p: int, work: Dict[int, List[List[Action]]], stage_rank, last_stage_of, first_stage_of,
-            split_w: bool, costs=None) -> List[List[Action]]:
-    """List-scheduling simulator shared by Zero-Bubble and DualPipe: every rank holds one ordered
-    queue per (direction) of F and B actions; at each tick a rank runs the first *ready* action by
-    priority B > F (alternating directions), and fills idle ticks with pending W."""
-    done: set = set()
+                  split_w: bool, costs=None) -> List[List[Action]]:
+    """List scheduling shared by the interleaved, Zero-Bubble and DualPipe generators: every rank holds one ordered
+    queue of F and B actions per stage (or direction). It works with durations, not ticks: an unsplit backward costs
+    twice a forward, so a rank that has just finished a forward may find the gradient it waits for still one forward
+    away and should run another forward meanwhile, which a scheduler that advances every rank by one action per tick
+    cannot see (interleaved 1F1B at p = 4, m = 8: 18.6 % idle instead of 28.4 %). At each step the
+    action that can start earliest on any rank is placed (a ready backward before a ready forward, alternating between
+    a rank's queues); a rank with nothing startable at its clock runs a pending W if it has one, else idles until its
+    earliest head becomes ready."""
+    costs = costs or {F: 1.0, B: 2.0, BI: 1.0, W: 1.0}
+    finish: Dict[tuple, float] = {}
+    clock = [0.0] * p
     pending_w: List[List[Action]] = [[] for _ in range(p)]
     out: List[List[Action]] = [[] for _ in range(p)]
     queues = {r: [list(q) for q in work[r]] for r in range(p)}
     turn = [0] * p
+    INF = float("inf")
 
-    def ready(a: Action) -> bool:
+    def ready_time(a: Action) -> float:
+        """Earliest start allowed by the dependencies that are already placed; ``INF`` while one is not."""
+        deps = []
         if a.type == F:
-            return a.stage == first_stage_of(a) or ("F", a.microbatch, a.stage - 1) in done
-        nxt_ok = a.stage == last_stage_of(a) or ("B", a.microbatch, a.stage + 1) in done
-        return ("F", a.microbatch, a.stage) in done and nxt_ok
+            if a.stage != first_stage_of(a):
+                deps.append(("F", a.microbatch, a.stage - 1))
+        else:
+            deps.append(("F", a.microbatch, a.stage))
+            if a.stage != last_stage_of(a):
+                deps.append(("B", a.microbatch, a.stage + 1))
+        t = 0.0
+        for d in deps:
+            if d not in finish:
+                return INF
+            t = max(t, finish[d])
+        return t
 
     total = sum(len(q) for r in range(p) for q in queues[r])
     guard = 0
     while total > 0:
         guard += 1
-        if guard > 100000:
+        if guard > 1000000:
             raise RuntimeError("schedule generation did not converge")
-        fired = []
+        best = None   # (start, is_forward, queue distance, rank, queue index)
         for r in range(p):
-            cands = []
             for qi, q in enumerate(queues[r]):
-                if q and ready(q[0]):
-                    cands.append((0 if q[0].type != F else 1, (qi - turn[r]) % max(len(queues[r]), 1), qi))
-            if cands:
-                _, _, qi = min(cands)
-                a = queues[r][qi].pop(0)
-                turn[r] = (qi + 1) % len(queues[r])
-                fired.append((r, a))
-            elif pending_w[r]:
-                out[r].append(pending_w[r].pop(0))
-        for r, a in fired:
-            if a.type == F:
-                out[r].append(a)
-            else:
-                out[r].append(Action(BI if split_w else B, a.microbatch, a.stage))
-                if split_w:
-                    pending_w[r].append(Action(W, a.microbatch, a.stage))
-            total -= 1
-        for r, a in fired:  # results become visible to other ranks on the next tick
-            done.add(("F" if a.type == F else "B", a.microbatch, a.stage))
+                if not q:
+                    continue
+                rt = ready_time(q[0])
+                if rt == INF:
+                    continue
+                start = max(rt, clock[r])
+                key = (start, 1 if q[0].type == F else 0, (qi - turn[r]) % max(len(queues[r]), 1), r, qi)
+                if best is None or key < best:
+                    best = key
+        if best is None:
+            raise RuntimeError("no action can start: the queues do not form a valid pipeline")
+        start, _, _, r, qi = best
+        # fill the wait before `start` with deferred weight-gradient work (it needs nothing from other ranks)
+        while pending_w[r] and clock[r] + costs[W] <= start + 1e-9:
+            out[r].append(pending_w[r].pop(0))
+            clock[r] += costs[W]
+        start = max(start, clock[r])
+        a = queues[r][qi].pop(0)
+        turn[r] = (qi + 1) % len(queues[r])
+        if a.type == F:
+            out[r].append(a)
+            dur, tag = costs[F], "F"
+        else:
+            out[r].append(Action(BI if split_w else B, a.microbatch, a.stage))
+            dur, tag = (costs[BI] if split_w else costs[B]), "B"
+            if split_w:
+                pending_w[r].append(Action(W, a.microbatch, a.stage))
+        clock[r] = start + dur
+        finish[(tag, a.microbatch, a.stage)] = clock[r]
+        total -= 1
     for r in range(p):
         out[r] += pending_w[r]
     return out
