@@ -1,5 +1,5 @@
 """Fault tolerance: resumable checkpoints and hang detection."""
 from .checkpoint import FaultTolerantCheckpointer
-from .hang_detection import CommTimeoutError, HangDetector, HeartbeatCoordinator
+from .hang_detection import CommTimeoutError, HangDetector, HeartbeatCoordinator, PeerLeftError
 
-__all__ = ["FaultTolerantCheckpointer", "HangDetector", "HeartbeatCoordinator", "CommTimeoutError"]
+__all__ = ["FaultTolerantCheckpointer", "HangDetector", "HeartbeatCoordinator", "CommTimeoutError", "PeerLeftError"]

@@ -20,6 +20,11 @@ class CommTimeoutError(RuntimeError):
     """A bounded device-side or collective wait ran out."""
 
 
+class PeerLeftError(CommTimeoutError):
+    """A peer announced that it leaves the job (preemption, planned shrink): raised on the remaining ranks before they
+    launch the step the peer will no longer take part in."""
+
+
 class HangDetector:
     def __init__(self, timeout: float = 300.0, check_interval: float = 10.0, on_hang: Optional[Callable] = None,
                  abort_on_hang: bool = True):
@@ -117,6 +122,31 @@ class HeartbeatCoordinator:
     def heartbeat(self, step: Optional[int] = None):
         self._step = self._step + 1 if step is None else step
         self.store.set(f"{self.prefix}/{self.rank}", str(self._step))
+
+    # -- planned departure ----------------------------------------------------------------------------------------
+    # A rank leaves only between steps, with none of its kernels or collectives in flight, and says so one step ahead:
+    # it writes "I take part up to step k" into the store *before* it enters step k. Step k contains a collective that
+    # every rank takes part in, so by the time a peer has finished step k the note is visible to it; every remaining
+    # rank therefore finds it at the top of step k + 1, before launching anything that would wait for the departed
+    # rank, and all of them stop at the same step.
+    def announce_departure(self, last_step: int) -> None:
+        self.store.set(f"{self.prefix}/left/{self.rank}", str(int(last_step)))
+
+    def departed(self, step: int) -> List[int]:
+        """Ranks whose announced last step is below ``step`` (the step about to start)."""
+        gone = []
+        for r in range(self.world_size):
+            if r == self.rank:
+                continue
+            key = f"{self.prefix}/left/{r}"
+            try:
+                if hasattr(self.store, "check") and not self.store.check([key]):
+                    continue
+                if int(self.store.get(key).decode()) < step:
+                    gone.append(r)
+            except Exception:  # noqa: BLE001
+                continue
+        return gone
 
     def start(self):
         if self.rank != 0:

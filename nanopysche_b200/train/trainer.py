@@ -89,6 +89,7 @@ class Trainer:
         self.tokens_seen = 0
         self._metrics: Dict[str, Any] = {}
         self._compressor = None
+        self._leave_after: Optional[int] = None    # this rank's announced last step (leave_after_step)
         self._best_val_loss = float("inf")
         self._stop_reason: Optional[str] = None
         self.emergency_checkpoint_dir: Optional[str] = None
@@ -211,6 +212,27 @@ class Trainer:
     def request_stop(self, reason: str = "") -> None:
         self._stop_reason = reason or "stop requested"
 
+    def leave_after_step(self, last_step: Optional[int] = None) -> None:
+        """This rank leaves the job (preemption notice, planned shrink) after completing ``last_step`` (default: the
+        step that is about to run or running). Call it before that step's collectives start - from ``pre_step`` or
+        earlier; the peers find the note at the top of the following step and stop there with ``PeerLeftError``
+        (their ``on_error`` callbacks run and each writes its emergency checkpoint), this rank returns from ``fit()``
+        normally. Needs a ``heartbeat`` coordinator (its store carries the note)."""
+        if self.heartbeat is None:
+            raise RuntimeError("leave_after_step needs Trainer(heartbeat=HeartbeatCoordinator(...))")
+        self._leave_after = self.step + 1 if last_step is None else int(last_step)
+        self.heartbeat.announce_departure(self._leave_after)
+
+    def _check_peers_present(self) -> None:
+        if self.heartbeat is None or not hasattr(self.heartbeat, "departed"):
+            return
+        gone = self.heartbeat.departed(self.step + 1)
+        if gone:
+            from ..fault_tolerance.hang_detection import PeerLeftError
+
+            raise PeerLeftError(f"rank(s) {gone} left the job after step {self.step}: stopping before step "
+                                f"{self.step + 1} is launched")
+
     # ------------------------------------------------------------------ loop
     def fit(self):
         if self.hang_detector is not None:
@@ -221,12 +243,16 @@ class Trainer:
             cb.pre_train(self)
         try:
             while self.step < self.config.max_steps and self._stop_reason is None:
+                if self._leave_after is not None and self.step >= self._leave_after:
+                    self._stop_reason = f"left the job after step {self.step}"
+                    break
+                self._check_peers_present()
                 self._train_step_with_callbacks()
                 if self.hang_detector is not None:
                     self.hang_detector.heartbeat()
                 if self.heartbeat is not None:
                     self.heartbeat.heartbeat(self.step)
-            if self._metrics:
+            if self._metrics and self._leave_after is None:   # a collective: not for a rank that leaves alone
                 self._flush_metrics()
             for cb in self.callbacks:
                 cb.post_train(self)

@@ -596,3 +596,48 @@ def test_arena_optimizer_state_reshards_to_another_world_size(tmp_path):
     arena.world = 1
     with pytest.raises(ValueError, match="expert-sharded"):
         opt.load_state_dict_resharded(bad)
+
+
+def _departure_worker(rank, world, save_dir):
+    """Rank 2 announces in ``pre_step`` of its third step that this is its last one and returns from ``fit()`` after
+    it; ranks 0 and 1 find the note at the top of step four - before any collective that would wait for rank 2 -
+    raise ``PeerLeftError``, run ``on_error`` and write their emergency checkpoints. Nothing hangs: every collective
+    that was started had all three ranks in it."""
+    from nanopysche_b200.fault_tolerance import HeartbeatCoordinator, PeerLeftError
+
+    torch.manual_seed(0)
+    m = tiny_model()
+    m._replica_group = dist.group.WORLD
+    m._needs_grad_sync = True
+    opt = torch.optim.SGD(m.parameters(), lr=1e-2)
+    events = []
+
+    class Leaver(Callback):
+        def pre_step(self, trainer, batch):
+            if trainer.rank == 2 and trainer.step == 2:
+                trainer.leave_after_step()            # the step about to run (number 3) is the last one
+
+        def on_error(self, trainer, err):
+            events.append(type(err).__name__)
+
+    tc = TrainingConfig(global_batch_size=2 * 16 * world, micro_batch_size=2, sequence_length=16, max_steps=8,
+                        log_interval=0, save_interval=0, dtype=torch.float32, vocab_size=64, dp_world_size=world,
+                        save_dir=save_dir)
+    tr = Trainer(tc, m, opt, None, None, [Leaver()], heartbeat=HeartbeatCoordinator(check_interval=60.0))
+    err = None
+    try:
+        tr.fit()
+    except PeerLeftError as e:
+        err = str(e)
+    return rank, tr.step, err, events, tr.emergency_checkpoint_dir
+
+
+def test_planned_departure_stops_the_peers_before_the_next_step(tmp_path):
+    res = sorted(run_distributed(_departure_worker, 3, str(tmp_path)))
+    (r0, s0, e0, ev0, d0), (r1, s1, e1, ev1, d1), (r2, s2, e2, ev2, d2) = res
+    assert (s0, s1, s2) == (3, 3, 3)                      # everyone completed exactly three steps
+    assert e2 is None and ev2 == [] and d2 is None         # the leaver returned normally
+    for e, ev, d in ((e0, ev0, d0), (e1, ev1, d1)):
+        assert e is not None and "[2]" in e and ev == ["PeerLeftError"]
+        assert d is not None and os.path.isdir(d)
+    assert os.path.exists(os.path.join(d0, "rank_0000_model.pt")) and os.path.exists(os.path.join(d1, "rank_0001_model.pt"))
