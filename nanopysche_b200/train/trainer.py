@@ -180,6 +180,17 @@ class Trainer:
             torch.save({k: v.detach().cpu() for k, v in self.model.state_dict().items()},
                        os.path.join(d, f"rank_{self.rank:04d}_model.pt"))
             torch.save(self.optimizer.state_dict(), os.path.join(d, f"rank_{self.rank:04d}_optimizer.pt"))
+            # the same metadata from every rank (whoever writes last wins, the content is identical): makes the
+            # directory loadable by DistributedCheckpointer.load, also on another number of ranks
+            import json
+
+            meta = {"step": self.step, "world_size": self.world_size, "model_keys": list(self.model.state_dict().keys()),
+                    "config": {}, "extra": {"tokens_seen": self.tokens_seen, "emergency": True}, "ephemeral": False,
+                    "incremental": False, "base_checkpoint": None, "dataloader_state": None}
+            tmp = os.path.join(d, f".metadata.{self.rank}.tmp")
+            with open(tmp, "w") as f:
+                json.dump(meta, f)
+            os.replace(tmp, os.path.join(d, "metadata.json"))
             return d
         except Exception as e:  # noqa: BLE001
             log.error("emergency checkpoint failed: %s", e)
@@ -245,6 +256,9 @@ class Trainer:
             while self.step < self.config.max_steps and self._stop_reason is None:
                 if self._leave_after is not None and self.step >= self._leave_after:
                     self._stop_reason = f"left the job after step {self.step}"
+                    # this rank's state joins the peers' emergency checkpoints of the same step, so that a restart
+                    # on the remaining ranks finds every shard
+                    self.emergency_checkpoint_dir = self._emergency_checkpoint()
                     break
                 self._check_peers_present()
                 self._train_step_with_callbacks()

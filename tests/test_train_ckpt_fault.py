@@ -636,8 +636,18 @@ def test_planned_departure_stops_the_peers_before_the_next_step(tmp_path):
     res = sorted(run_distributed(_departure_worker, 3, str(tmp_path)))
     (r0, s0, e0, ev0, d0), (r1, s1, e1, ev1, d1), (r2, s2, e2, ev2, d2) = res
     assert (s0, s1, s2) == (3, 3, 3)                      # everyone completed exactly three steps
-    assert e2 is None and ev2 == [] and d2 is None         # the leaver returned normally
+    assert e2 is None and ev2 == [] and d2 == d0           # the leaver returned normally, its state saved with the others
     for e, ev, d in ((e0, ev0, d0), (e1, ev1, d1)):
         assert e is not None and "[2]" in e and ev == ["PeerLeftError"]
         assert d is not None and os.path.isdir(d)
     assert os.path.exists(os.path.join(d0, "rank_0000_model.pt")) and os.path.exists(os.path.join(d1, "rank_0001_model.pt"))
+    assert os.path.exists(os.path.join(d0, "rank_0002_optimizer.pt"))
+    # the directory loads like a regular checkpoint, here into a single process (another world size)
+    meta = json.load(open(os.path.join(d0, "metadata.json")))
+    assert meta["step"] == 3 and meta["world_size"] == 3
+    m = tiny_model()
+    opt = torch.optim.SGD(m.parameters(), lr=1e-2)
+    DistributedCheckpointer(CheckpointConfig(save_dir=str(tmp_path))).load(d0, m, opt, restore_rng=False)
+    saved = torch.load(os.path.join(d0, "rank_0000_model.pt"))
+    for k, v in m.state_dict().items():
+        assert torch.equal(v, saved[k]), k
