@@ -78,7 +78,19 @@ class PinnedMemoryStager:
             self._pool[name] = buf
         return buf
 
-    def stage_state_dict(self, sd: Dict[str, Any], _prefix: str = "") -> Dict[str, Any]:
+    def stage_tensor(self, tensor: torch.Tensor) -> torch.Tensor:
+        """One tensor to host memory (pinned when CUDA is present), a fresh buffer per call
+        (reference: checkpoint/distributed.py:120-132)."""
+        t = tensor.detach()
+        if not (t.is_cuda and self.enabled):
+            return t.cpu().clone()
+        out = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+        out.copy_(t, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return out
+
+    def stage_state_dict(self, state_dict: Dict[str, Any], _prefix: str = "") -> Dict[str, Any]:
+        sd = state_dict
         out: Dict[str, Any] = {}
         used_cuda = False
         for k, v in sd.items():
@@ -115,6 +127,7 @@ class PlanCache:
 
     def __init__(self):
         self._plans: Dict[str, SavePlan] = {}
+        self._last: Optional[SavePlan] = None
 
     @staticmethod
     def signature(sd: Dict[str, torch.Tensor]) -> str:
@@ -125,11 +138,24 @@ class PlanCache:
                 h.update(str(tuple(v.shape)).encode())
         return h.hexdigest()[:16]
 
+    # step-keyed interface of the reference (checkpoint/distributed.py:185-201): the most recent plan, regardless of step
+    def get_plan(self, step: Optional[int] = None) -> Optional[SavePlan]:
+        return self._last
+
+    def cache_plan(self, step: int, plan: SavePlan) -> None:
+        self._last = plan
+
+    def invalidate(self) -> None:
+        """Forget every plan (the model's structure changed)."""
+        self._plans.clear()
+        self._last = None
+
     def get(self, sd: Dict[str, torch.Tensor]) -> SavePlan:
         sig = self.signature(sd)
         if sig not in self._plans:
             sizes = {k: v.numel() * v.element_size() for k, v in sd.items() if torch.is_tensor(v)}
             self._plans[sig] = SavePlan(list(sd.keys()), sizes, sum(sizes.values()))
+        self._last = self._plans[sig]
         return self._plans[sig]
 
 
@@ -143,6 +169,13 @@ class IncrementalCheckpointer:
         self._hashes: Dict[str, str] = {}
         self._prev: Dict[str, torch.Tensor] = {}
 
+    def compute_param_hash(self, tensor: torch.Tensor) -> str:
+        """Sampled hash of a tensor (reference: checkpoint/distributed.py:227-241)."""
+        return self._hash(tensor)
+
+    def is_base_checkpoint_needed(self, save_count: int, full_interval: Optional[int] = None) -> bool:
+        return save_count % (full_interval or self.full_save_interval) == 0
+
     @staticmethod
     def _hash(t: torch.Tensor) -> str:
         f = t.detach().reshape(-1).float()
@@ -151,7 +184,8 @@ class IncrementalCheckpointer:
         sample = torch.cat([f[:4], f[-4:], f.sum().reshape(1), torch.tensor([float(f.numel())])])
         return hashlib.sha256(sample.cpu().numpy().tobytes()).hexdigest()[:16]
 
-    def compute_delta(self, sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    def compute_delta(self, state_dict: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        sd = state_dict
         delta = {}
         for k, v in sd.items():
             if not torch.is_tensor(v):
@@ -186,9 +220,32 @@ class DataloaderStateTracker:
         self.samples_seen = 0
         self.extra: Dict[str, Any] = {}
 
-    def update(self, batch_size: int = 1):
+    def update(self, batch_size: Optional[int] = None, **fields):
+        """``update()`` / ``update(batch_size)``: count one batch. ``update(key=value, ...)`` (the reference's form,
+        checkpoint/distributed.py:309-312: current file, shard index, loader RNG state, ...): keep the fields in
+        ``extra`` without counting; both together do both."""
+        if fields:
+            self.extra.update(fields)
+            if batch_size is None:
+                return
         self.batches_seen += 1
-        self.samples_seen += batch_size
+        self.samples_seen += 1 if batch_size is None else batch_size
+
+    def get_state(self) -> Dict[str, Any]:
+        import copy as _copy
+
+        return _copy.deepcopy(self.state_dict())
+
+    def save(self, path) -> None:
+        tmp = f"{path}.tmp"
+        with open(tmp, "w") as f:
+            json.dump(self.state_dict(), f)
+        os.replace(tmp, path)
+
+    def load(self, path) -> None:
+        if os.path.exists(path):
+            with open(path) as f:
+                self.load_state_dict(json.load(f))
 
     def new_epoch(self):
         self.epoch += 1

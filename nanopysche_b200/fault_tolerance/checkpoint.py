@@ -20,9 +20,15 @@ import torch.distributed as dist
 
 class FaultTolerantCheckpointer:
     def __init__(self, save_dir: str = "checkpoints", save_interval: int = 1000, keep_last_n: int = 3,
-                 async_save: bool = False):
+                 async_save: bool = False, max_stale_steps: Optional[int] = None):
+        """``max_stale_steps`` (reference: fault_tolerance/checkpoint.py, fourth positional argument there): checkpoints
+        more than this many steps behind the newest one are removed as well; a bool in the ``keep_last_n`` position is
+        read as the reference's ``async_save`` (its third positional argument)."""
+        if isinstance(keep_last_n, bool):
+            keep_last_n, async_save = 3, keep_last_n
         self.save_dir, self.save_interval, self.keep_last_n, self.async_save = save_dir, save_interval, keep_last_n, \
             async_save
+        self.max_stale_steps = max_stale_steps
         os.makedirs(save_dir, exist_ok=True)
         self._thread: Optional[threading.Thread] = None
 
@@ -39,7 +45,17 @@ class FaultTolerantCheckpointer:
     def should_save(self, step: int) -> bool:
         return step > 0 and step % self.save_interval == 0
 
-    def save(self, step: int, model, optimizer=None, extra: Optional[dict] = None, force: bool = False) -> Optional[str]:
+    def save(self, step, model=None, optimizer=None, extra: Optional[dict] = None, force: bool = False,
+             scheduler=None) -> Optional[str]:
+        """``save(step, model, optimizer)``; the reference's order ``save(model, optimizer, step, scheduler, extra)``
+        (fault_tolerance/checkpoint.py) is recognised by its first argument being a module."""
+        if isinstance(step, torch.nn.Module):
+            ref_model, ref_opt, ref_step = step, model, optimizer
+            if isinstance(extra, dict) or extra is None:
+                pass
+            elif scheduler is None:          # positional (model, optimizer, step, scheduler)
+                scheduler, extra = extra, None
+            step, model, optimizer = int(ref_step), ref_model, ref_opt
         if not force and not self.should_save(step):
             return None
         self.wait()
@@ -89,6 +105,13 @@ class FaultTolerantCheckpointer:
         done = sorted(d for d in os.listdir(self.save_dir) if d.startswith("step_"))
         for d in done[:-self.keep_last_n] if self.keep_last_n else []:
             shutil.rmtree(os.path.join(self.save_dir, d), ignore_errors=True)
+        if self.max_stale_steps is not None:
+            for d in done:
+                try:
+                    if step - int(d.split("_")[1]) > self.max_stale_steps:
+                        shutil.rmtree(os.path.join(self.save_dir, d), ignore_errors=True)
+                except ValueError:
+                    pass
 
     def wait(self):
         if self._thread is not None:

@@ -30,6 +30,12 @@ class FP8Config:
     ignored_modules: List[str] = field(default_factory=lambda: ["lm_head", "gate"])
     min_features: int = 128
 
+    def build_torchao_config(self):
+        """The reference hands its linears to torchao (fp8/training.py:78-90). Here the fp8 linears run on this
+        package's own block-scaled kernels and nothing is delegated, so there is no torchao object to build: ``None``,
+        which is also what the reference returns when torchao is not installed."""
+        return None
+
 
 class _QDQ(torch.autograd.Function):
     """Quantise-dequantise with a straight-through gradient."""

@@ -224,19 +224,27 @@ class _AllToAllSingle(torch.autograd.Function):
         return out, None, None, None
 
 
+class _CallableInt(int):
+    """An int that may also be called (returns itself)."""
+
+    def __call__(self) -> int:
+        return int(self)
+
+
 class TokenDispatcher:
     """Interface of an EP dispatcher.
 
-    ``dispatch(x (T,D), indices (T,K), weights (T,K), num_experts, ep_group, ep_size)`` returns
-    ``(local_x (n,D), local_weights (n,), local_indices (n,) local expert ids, meta)`` with rows sorted
-    by local expert; ``combine(expert_out (n,D), meta, x, weights, indices)`` returns ``(T, D)``: the
-    router-weighted sum of every token's K expert outputs.
+    ``dispatch(x (T,D), expert_indices (T,K), expert_weights (T,K), num_experts, ep_size, ep_rank, ep_group)`` - the
+    reference's signature (model/moe.py:335-345) - returns ``(local_x (n,D), local_weights (n,), local_indices (n,)
+    local expert ids, meta)`` with rows sorted by local expert; ``combine(expert_output (n,D), combine_metadata, x,
+    expert_weights, expert_indices, ep_size, ep_group)`` returns ``(T, D)``: the router-weighted sum of every token's K
+    expert outputs.
     """
 
-    def dispatch(self, x, indices, weights, num_experts, ep_group=None, ep_size=1):
+    def dispatch(self, x, expert_indices, expert_weights, num_experts, ep_size=1, ep_rank=None, ep_group=None):
         raise NotImplementedError
 
-    def combine(self, expert_output, meta, x, weights, indices):
+    def combine(self, expert_output, combine_metadata, x, expert_weights, expert_indices, ep_size=None, ep_group=None):
         raise NotImplementedError
 
 
@@ -244,7 +252,10 @@ class NcclAllToAllDispatcher(TokenDispatcher):
     """Plain-collective dispatcher: one counts all-to-all, rows and expert ids by
     ``all_to_all_single`` (NCCL on GPU, gloo on CPU). This is the un-fused baseline."""
 
-    def dispatch(self, x, indices, weights, num_experts, ep_group=None, ep_size=1):
+    def dispatch(self, x, expert_indices, expert_weights, num_experts, ep_size=1, ep_rank=None, ep_group=None):
+        indices, weights = expert_indices, expert_weights
+        if not isinstance(ep_size, int):       # the former order of this package: (..., num_experts, ep_group, ep_size)
+            ep_size, ep_group = (ep_rank if isinstance(ep_rank, int) else 1), ep_size
         T, K = indices.shape
         flat_e = indices.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
@@ -269,7 +280,8 @@ class NcclAllToAllDispatcher(TokenDispatcher):
                     ep_size=ep_size)
         return recv_rows[order2], w_out[order2], local_ids[order2], meta
 
-    def combine(self, expert_output, meta, x, weights, indices):
+    def combine(self, expert_output, combine_metadata, x, expert_weights, expert_indices, ep_size=None, ep_group=None):
+        meta, weights = combine_metadata, expert_weights
         T, K = meta["T"], meta["K"]
         if meta["ep_size"] > 1:
             unsorted = torch.empty_like(expert_output)
@@ -340,18 +352,38 @@ class ExpertParallelConfig:
 
     @property
     def ep_rank(self) -> int:
+        """This rank's index in the EP group; reads as a number and may be called (a method in the reference,
+        model/moe.py:660-663)."""
         if self.ep_size <= 1 or self.ep_group is None:
-            return 0
-        return dist.get_rank(self.ep_group)
+            return _CallableInt(0)
+        return _CallableInt(dist.get_rank(self.ep_group))
 
     def local_experts(self, num_experts: int) -> tuple[int, int]:
         n = num_experts // max(self.ep_size, 1)
         return self.ep_rank * n, (self.ep_rank + 1) * n
 
-    def dispatch(self, x, indices, weights, num_experts):
+    def _reference_style(self) -> bool:
+        """A dispatcher written against the reference's interface takes ``(x, expert_indices, expert_weights,
+        num_experts, ep_size, ep_rank, ep_group)`` and ``combine(..., ep_size, ep_group)`` (model/moe.py:335-357)."""
+        import inspect
+
+        try:
+            return "ep_rank" in inspect.signature(self.dispatcher.dispatch).parameters
+        except (TypeError, ValueError):
+            return False
+
+    def dispatch(self, x, expert_indices, expert_weights, num_experts):
+        indices, weights = expert_indices, expert_weights
+        if self._reference_style():
+            return self.dispatcher.dispatch(x, indices, weights, num_experts, self.ep_size, int(self.ep_rank),
+                                            self.ep_group)
+        # a dispatcher written for this package's earlier interface
         return self.dispatcher.dispatch(x, indices, weights, num_experts, self.ep_group, self.ep_size)
 
-    def combine(self, expert_output, meta, x, weights, indices):
+    def combine(self, expert_output, combine_metadata, x, expert_weights, expert_indices):
+        meta, weights, indices = combine_metadata, expert_weights, expert_indices
+        if self._reference_style():
+            return self.dispatcher.combine(expert_output, meta, x, weights, indices, self.ep_size, self.ep_group)
         return self.dispatcher.combine(expert_output, meta, x, weights, indices)
 
 
@@ -539,26 +571,27 @@ class MoEBase(nn.Module):
         self._aux_loss = aux
         return x_flat, w_flat, i_flat, aux, dropped, keep_mask
 
-    def dispatch(self, x_flat, i_flat, w_flat):
-        return self.ep.dispatch(x_flat, i_flat, w_flat, self.num_experts)
+    # parameter names as in the reference (model/moe.py), so that keyword calls written against it keep working
+    def dispatch(self, x_flat, indices_flat, weights_flat):
+        return self.ep.dispatch(x_flat, indices_flat, weights_flat, self.num_experts)
 
-    def local_compute(self, local_x, local_w, local_i):
+    def local_compute(self, local_x, local_weights, local_indices):
         if self._fp8_flow_moe is not None and local_x.shape[0] > 0:
-            return self._fp8_flow_moe(local_x, None, local_i, 0, self.num_local_experts)
-        return self._compute_experts_grouped_gemm(local_x, local_w, local_i)
+            return self._fp8_flow_moe(local_x, None, local_indices, 0, self.num_local_experts)
+        return self._compute_experts_grouped_gemm(local_x, local_weights, local_indices)
 
-    def combine(self, expert_out, combine_meta, x_flat, w_flat, i_flat):
-        out = self.ep.combine(expert_out, combine_meta, x_flat, w_flat, i_flat)
+    def combine(self, expert_output, combine_metadata, x_flat, weights_flat, indices_flat):
+        out = self.ep.combine(expert_output, combine_metadata, x_flat, weights_flat, indices_flat)
         if self.shared_expert is not None:
             out = out + self.shared_expert(x_flat)
         return out
 
-    def reassemble(self, moe_flat, *, dropped, keep_mask, B, S, D):
+    def reassemble(self, output, *, dropped, keep_mask, B, S, D):
         if keep_mask is not None:
-            full = moe_flat.new_zeros((B * S, D))
-            full[keep_mask] = moe_flat
-            moe_flat = full
-        return moe_flat.view(B, S, D)
+            full = output.new_zeros((B * S, D))
+            full[keep_mask] = output
+            output = full
+        return output.view(B, S, D)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         B, S, D = x.shape
@@ -610,8 +643,9 @@ class MoEBase(nn.Module):
         for p in (self.w1, self.w2, self.w3):
             p._ep_sharded = True  # gradients of expert shards are not averaged over the EP group
 
-    def apply_fp8_flow_moe(self, enabled: bool = True, fp8_recipe: str = "blockwise",
+    def apply_fp8_flow_moe(self, fp8_flow_moe: bool = True, fp8_recipe: str = "blockwise",
                            fp8_gemm_threshold: Optional[int] = None):
+        enabled = fp8_flow_moe
         self.fp8_flow_moe_enabled = enabled
         self.fp8_recipe = fp8_recipe
         if fp8_gemm_threshold is not None:

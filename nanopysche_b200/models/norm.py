@@ -12,10 +12,13 @@ from ..ops.norm import rms_norm
 
 
 class RMSNorm(nn.Module):
-    def __init__(self, size: int, eps: float = 1e-6, device=None, dtype=None):
+    def __init__(self, size: int, eps: float = 1e-6, device=None, dtype=None, full_precision: bool = True):
+        """``full_precision`` is accepted for the reference's signature (model/norm.py:26): the statistics are always
+        accumulated in fp32 here, in the kernel as on the PyTorch path, so the flag changes nothing."""
         super().__init__()
         self.size = size
         self.eps = eps
+        self.full_precision = True
         self.weight = nn.Parameter(torch.ones(size, device=device, dtype=torch.float32))
 
     def _apply(self, fn, recurse=True):  # keep the weight fp32 under .to(bf16) / .bfloat16()

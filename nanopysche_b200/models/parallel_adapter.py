@@ -47,7 +47,24 @@ def find_head(model: nn.Module):
 
 
 def _layers(stack):
-    return list(stack.values()) if isinstance(stack, nn.ModuleDict) else list(stack)
+    """Layers of a stack in execution order (a ``ModuleDict`` keyed by layer index is ordered numerically, so
+    ``"10"`` follows ``"9"``)."""
+    if isinstance(stack, nn.ModuleDict):
+        keys = sorted(stack.keys(), key=lambda k: (0, int(k)) if str(k).isdigit() else (1, str(k)))
+        return [stack[k] for k in keys]
+    return list(stack)
+
+
+def layer_count(model: nn.Module) -> int:
+    """Number of layers in the model's layer stack, 0 when none is found (reference: model/parallel_adapter.py:41-45)."""
+    _, stack = find_layer_stack(model)
+    return len(stack) if stack is not None else 0
+
+
+def iter_layers(model: nn.Module):
+    """The model's layers in execution order (reference: model/parallel_adapter.py:48-57)."""
+    _, stack = find_layer_stack(model)
+    return iter(_layers(stack)) if stack is not None else iter(())
 
 
 class _RowParallelLinear(nn.Module):

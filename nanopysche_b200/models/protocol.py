@@ -3,6 +3,8 @@ from __future__ import annotations
 
 import warnings
 
+from typing import Optional
+
 import torch.nn as nn
 
 PARALLEL_HOOKS = ("apply_pp", "apply_tp", "apply_cp", "apply_ep", "apply_fsdp", "apply_compile")
@@ -15,14 +17,20 @@ def has_hook(model: nn.Module, name: str) -> bool:
     return callable(getattr(model, name, None))
 
 
-def model_display_name(model: nn.Module) -> str:
-    return type(model).__name__
+def model_display_name(model: nn.Module, preset: Optional[str] = None) -> str:
+    """The preset's name when the model came from one, else the class name (reference: model/protocol.py:75-78)."""
+    return preset or type(model).__name__
 
 
 def unsupported_parallelism(model: nn.Module, *, tp: int = 1, pp: int = 1, cp: int = 1, ep: int = 1,
-                            fsdp: bool = False, compile: bool = False) -> list[str]:
-    """Names of the requested parallelism kinds the model has no hook for."""
-    wanted = {"tp": tp > 1, "pp": pp > 1, "cp": cp > 1, "ep": ep > 1, "fsdp": bool(fsdp), "compile": bool(compile)}
+                            fsdp: bool = False, compile: bool = False, compile_model: bool = False) -> list[str]:
+    """Names of the requested parallelism kinds the model has no hook for. Degrees (``tp=2``) or the reference's
+    booleans (``tp=True``, ``compile_model=True``; model/protocol.py) are both accepted."""
+    def on(v):
+        return v is True or (not isinstance(v, bool) and v > 1)
+
+    wanted = {"tp": on(tp), "pp": on(pp), "cp": on(cp), "ep": on(ep), "fsdp": bool(fsdp),
+              "compile": bool(compile or compile_model)}
     return [k for k, on in wanted.items() if on and not has_hook(model, _HOOK_OF[k])]
 
 

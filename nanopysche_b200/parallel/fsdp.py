@@ -77,12 +77,13 @@ def shard_module(module: nn.Module, dp_mesh=None, *, reshard_after_forward: bool
 class ActivationCheckpointing(nn.Module):
     """Recompute the wrapped module in backward (non-reentrant checkpoint)."""
 
-    def __init__(self, module: nn.Module):
+    def __init__(self, module: nn.Module, use_reentrant: bool = False):
         super().__init__()
         self.module = module
+        self.use_reentrant = use_reentrant
 
     def forward(self, *args, **kwargs):
-        return checkpoint(self.module, *args, use_reentrant=False, **kwargs)
+        return checkpoint(self.module, *args, use_reentrant=self.use_reentrant, **kwargs)
 
     def __getattr__(self, name):  # hooks (apply_tp, feed_forward, ...) resolve on the wrapped module
         try:
@@ -107,8 +108,15 @@ def apply_activation_checkpointing(model: nn.Module, mode: str = "full", block_i
     return model
 
 
-def apply_generic_fsdp(model: nn.Module, dp_mesh=None, dp_config: Optional[DataParallelConfig] = None):
+def apply_generic_fsdp(model: nn.Module, dp_mesh=None, dp_config: Optional[DataParallelConfig] = None, *,
+                       param_dtype: Optional[torch.dtype] = None, reduce_dtype: Optional[torch.dtype] = None):
+    """``param_dtype`` / ``reduce_dtype`` (the reference's keywords, distributed/fsdp.py) override the config's."""
     cfg = dp_config or DataParallelConfig()
+    if param_dtype is not None or reduce_dtype is not None:
+        import dataclasses as _dc
+
+        cfg = _dc.replace(cfg, **({"param_dtype": param_dtype} if param_dtype is not None else {}),
+                          **({"reduce_dtype": reduce_dtype} if reduce_dtype is not None else {}))
     return shard_module(model, dp_mesh, mp_policy=MixedPrecision(cfg.param_dtype, cfg.reduce_dtype))
 
 

@@ -93,9 +93,9 @@ def _sub(mesh: DeviceMesh, name: str) -> Optional[DeviceMesh]:
     return mesh[name] if name in _names(mesh) else None
 
 
-def get_dp_model_mesh(world_mesh: Optional[DeviceMesh] = None) -> Optional[DeviceMesh]:
+def get_dp_model_mesh(world_mesh: Optional[DeviceMesh] = None, device_mesh: Optional[DeviceMesh] = None) -> Optional[DeviceMesh]:
     """The mesh FSDP shards over: the dp dims (both of them under HSDP), never cp/tp/pp."""
-    mesh = world_mesh or _WORLD_MESH
+    mesh = world_mesh or device_mesh or _WORLD_MESH   # ``device_mesh``: the reference's name for the argument
     if mesh is None:
         return None
     names = _names(mesh)
@@ -104,9 +104,9 @@ def get_dp_model_mesh(world_mesh: Optional[DeviceMesh] = None) -> Optional[Devic
     return _sub(mesh, MeshDimName.dp)
 
 
-def get_dp_mesh(world_mesh: Optional[DeviceMesh] = None) -> Optional[DeviceMesh]:
+def get_dp_mesh(world_mesh: Optional[DeviceMesh] = None, device_mesh: Optional[DeviceMesh] = None) -> Optional[DeviceMesh]:
     """The mesh the data loader shards over (CP/TP peers of one dp index read the same batch)."""
-    mesh = world_mesh or _WORLD_MESH
+    mesh = world_mesh or device_mesh or _WORLD_MESH   # ``device_mesh``: the reference's name for the argument
     if mesh is None:
         return None
     names = _names(mesh)
@@ -117,24 +117,24 @@ def get_dp_mesh(world_mesh: Optional[DeviceMesh] = None) -> Optional[DeviceMesh]
     return None
 
 
-def get_tp_mesh(world_mesh: Optional[DeviceMesh] = None):
-    mesh = world_mesh or _WORLD_MESH
+def get_tp_mesh(world_mesh: Optional[DeviceMesh] = None, device_mesh: Optional[DeviceMesh] = None):
+    mesh = world_mesh or device_mesh or _WORLD_MESH   # ``device_mesh``: the reference's name for the argument
     return None if mesh is None else _sub(mesh, MeshDimName.tp)
 
 
-def get_cp_mesh(world_mesh: Optional[DeviceMesh] = None):
-    mesh = world_mesh or _WORLD_MESH
+def get_cp_mesh(world_mesh: Optional[DeviceMesh] = None, device_mesh: Optional[DeviceMesh] = None):
+    mesh = world_mesh or device_mesh or _WORLD_MESH   # ``device_mesh``: the reference's name for the argument
     return None if mesh is None else _sub(mesh, MeshDimName.cp)
 
 
-def get_pp_mesh(world_mesh: Optional[DeviceMesh] = None):
-    mesh = world_mesh or _WORLD_MESH
+def get_pp_mesh(world_mesh: Optional[DeviceMesh] = None, device_mesh: Optional[DeviceMesh] = None):
+    mesh = world_mesh or device_mesh or _WORLD_MESH   # ``device_mesh``: the reference's name for the argument
     return None if mesh is None else _sub(mesh, MeshDimName.pp)
 
 
-def get_ep_mesh(world_mesh: Optional[DeviceMesh] = None):
+def get_ep_mesh(world_mesh: Optional[DeviceMesh] = None, device_mesh: Optional[DeviceMesh] = None):
     """The ep dim; without one, experts are spread over dp_shard (then dp), as in the reference."""
-    mesh = world_mesh or _WORLD_MESH
+    mesh = world_mesh or device_mesh or _WORLD_MESH   # ``device_mesh``: the reference's name for the argument
     if mesh is None:
         return None
     for n in (MeshDimName.ep, MeshDimName.dp_shard, MeshDimName.dp):

@@ -50,10 +50,18 @@ class PipelineStage(nn.Module):
     """A contiguous slice of layers with p2p helpers (reference: distributed/pipeline_parallel.py:71-149).
     Sends/receives are non-blocking ``batch_isend_irecv`` pairs on the PP group."""
 
-    def __init__(self, layers: nn.Module, stage_id: int, num_stages: int, group=None):
+    def __init__(self, layers=None, stage_id=None, num_stages: Optional[int] = None, group=None, *,
+                 stage_idx: Optional[int] = None, loss_fn=None):
+        """``PipelineStage(layers, stage_id, num_stages)``; the reference's ``PipelineStage(stage_idx, num_stages, layers,
+        loss_fn)`` (distributed/pipeline_parallel.py) is recognised by its first argument being an int."""
         super().__init__()
+        if isinstance(layers, int) and not isinstance(layers, bool):      # reference order: (stage_idx, num_stages, layers)
+            layers, stage_id, num_stages = num_stages, layers, stage_id
+        if stage_idx is not None:
+            stage_id = stage_idx
         self.layers = layers
         self.stage_id, self.num_stages, self.group = stage_id, num_stages, group
+        self.loss_fn = loss_fn
 
     @property
     def is_first(self) -> bool:
@@ -77,17 +85,19 @@ class PipelineStage(nn.Module):
         n = dist.get_world_size(self.group)
         return dist.get_global_rank(self.group, (r + delta) % n) if self.group is not None else (r + delta) % n
 
-    def send_forward(self, t):
-        return dist.batch_isend_irecv([dist.P2POp(dist.isend, t.contiguous(), self._peer(+1), group=self.group)])
+    def send_forward(self, x):
+        return dist.batch_isend_irecv([dist.P2POp(dist.isend, x.contiguous(), self._peer(+1), group=self.group)])
 
-    def recv_forward(self, buf):
-        return dist.batch_isend_irecv([dist.P2POp(dist.irecv, buf, self._peer(-1), group=self.group)])
+    def recv_forward(self, x):
+        """``x``: the buffer to receive into."""
+        return dist.batch_isend_irecv([dist.P2POp(dist.irecv, x, self._peer(-1), group=self.group)])
 
-    def send_backward(self, t):
-        return dist.batch_isend_irecv([dist.P2POp(dist.isend, t.contiguous(), self._peer(-1), group=self.group)])
+    def send_backward(self, grad):
+        return dist.batch_isend_irecv([dist.P2POp(dist.isend, grad.contiguous(), self._peer(-1), group=self.group)])
 
-    def recv_backward(self, buf):
-        return dist.batch_isend_irecv([dist.P2POp(dist.irecv, buf, self._peer(+1), group=self.group)])
+    def recv_backward(self, grad):
+        """``grad``: the buffer to receive into."""
+        return dist.batch_isend_irecv([dist.P2POp(dist.irecv, grad, self._peer(+1), group=self.group)])
 
 
 # ------------------------------------------------------------------ generators
@@ -95,7 +105,14 @@ F, B, BI, W = ScheduleType.FWD, ScheduleType.BWD, ScheduleType.BWD_INPUT, Schedu
 
 
 class _Schedule:
-    def __init__(self, num_stages: int, num_microbatches: int):
+    def __init__(self, num_stages=None, num_microbatches: int = 1, *, stages=None):
+        """``num_stages``: the pipeline depth, or - the reference's form, ``GPipeSchedule(stages, num_microbatches)``
+        (distributed/pipeline_parallel.py) - the list of stage modules, of which only the length matters here."""
+        if stages is not None and num_stages is None:
+            num_stages = stages
+        if not isinstance(num_stages, int):
+            self.stages = list(num_stages)
+            num_stages = len(self.stages)
         self.num_stages = num_stages
         self.num_microbatches = num_microbatches
 

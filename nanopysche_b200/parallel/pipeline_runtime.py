@@ -68,6 +68,13 @@ def stage_layer_ranges(n_layers: int, num_stages: int, split_points: Optional[Se
     return out
 
 
+class _CallableInt(int):
+    """An int that may also be called (returns itself): lets one attribute serve as a property and as a method."""
+
+    def __call__(self) -> int:
+        return int(self)
+
+
 @dataclass
 class PipelineParallelConfig:
     degree: int = 1
@@ -76,8 +83,27 @@ class PipelineParallelConfig:
     num_microbatches: Optional[int] = None
     style: PipelineSplitStyle = PipelineSplitStyle.loop
 
-    def stages_per_rank(self) -> int:
-        return 1 if PipelineScheduleType(self.schedule).is_single_stage else 2
+    @property
+    def stages_per_rank(self) -> "_CallableInt":
+        """1 for GPipe / 1F1B, else 2. Reads as a number (the reference's property,
+        distributed/pipeline_runtime.py:97-99) and may also be called."""
+        return _CallableInt(1 if PipelineScheduleType(self.schedule).is_single_stage else 2)
+
+    @property
+    def is_single_stage(self) -> bool:
+        return PipelineScheduleType(self.schedule).is_single_stage
+
+    @property
+    def total_stages(self) -> int:
+        """``degree x stages_per_rank`` as in the reference (distributed/pipeline_runtime.py:101-103); the number of
+        *distinct* model stages, which is ``degree`` under DualPipe, is ``num_stages()``."""
+        return self.degree * int(self.stages_per_rank)
+
+    @property
+    def split_style(self) -> PipelineSplitStyle:
+        if PipelineScheduleType(self.schedule) == PipelineScheduleType.zbv_zero_bubble:
+            return PipelineSplitStyle.v
+        return PipelineSplitStyle(self.style)
 
     def num_stages(self) -> int:
         """Number of distinct model stages. DualPipe keeps ``degree`` stages and gives every rank two of them (its own
@@ -91,7 +117,9 @@ class PipelineParallelConfig:
             return list(self.split_points)
         return [hi for _, hi in stage_layer_ranges(n_layers, self.num_stages())[:-1]]
 
-    def stage_ids_this_rank(self, pp_rank: int) -> List[int]:
+    def stage_ids_this_rank(self, pp_rank: int, num_stages: Optional[int] = None) -> List[int]:
+        """``num_stages`` is accepted for the reference's signature (distributed/pipeline_runtime.py); the count
+        follows from the schedule and the degree."""
         n, spr = self.degree, self.stages_per_rank()
         if spr == 1:
             return [pp_rank]
@@ -103,11 +131,18 @@ class PipelineParallelConfig:
         return [pp_rank + s * n for s in range(spr)]
 
 
-def split_model(model: nn.Module, pp_mesh, pp_config: PipelineParallelConfig, *, device=None) -> List[nn.Module]:
+def split_model(model: nn.Module, pp_mesh=None, pp_config: Optional[PipelineParallelConfig] = None, *, device=None,
+                pp_rank: Optional[int] = None, pp_group=None) -> List[nn.Module]:
     """One module per stage owned by this rank: a deep copy of the model trimmed to the stage's
-    layers (embeddings only on the first stage, head only on the last)."""
+    layers (embeddings only on the first stage, head only on the last). ``pp_mesh``: the pipeline mesh or group;
+    the reference's keyword form ``split_model(model, pp_config=, pp_rank=, device=, pp_group=)``
+    (distributed/pipeline_runtime.py) works as well."""
+    assert pp_config is not None, "split_model needs pp_config"
+    if pp_mesh is None:
+        pp_mesh = pp_group
     group = pp_mesh.get_group() if hasattr(pp_mesh, "get_group") else pp_mesh
-    pp_rank = dist.get_rank(group) if group is not None else 0
+    if pp_rank is None:
+        pp_rank = dist.get_rank(group) if group is not None else 0
     n_stages = pp_config.num_stages()
     pts = pp_config.get_split_points(getattr(model, "n_layers", 0)) if hasattr(model, "n_layers") else None
     for mod in model.modules():  # graph tensors cached by a previous forward cannot be deep-copied
@@ -248,12 +283,20 @@ class PipelineSchedule:
     rank's action list and returns the mean loss on the rank holding the last stage (else ``None``).
     """
 
-    def __init__(self, stages: Sequence[nn.Module], pp_mesh, pp_config: PipelineParallelConfig, *,
+    def __init__(self, stages: Sequence[nn.Module], pp_mesh=None, pp_config: Optional[PipelineParallelConfig] = None, *,
                  num_microbatches: Optional[int] = None, loss_fn: Optional[Callable] = None,
                  hidden_shape: Optional[Sequence[int]] = None, hidden_dtype: Optional[torch.dtype] = None,
-                 transport=None, placement: Optional[tuple] = None):
+                 transport=None, placement: Optional[tuple] = None, stages_reverse: Optional[Sequence[nn.Module]] = None):
         """``transport`` / ``placement=(p, rank)``: run this rank's program without a process group, against a
-        transport that records instead of sending (``pipeline_sim``)."""
+        transport that records instead of sending (``pipeline_sim``). The reference's keyword form
+        ``PipelineSchedule(stages=, pp_config=, loss_fn=, num_microbatches=, stages_reverse=)``
+        (distributed/pipeline_runtime.py) works too: without ``pp_mesh`` the pipeline spans the default process group
+        and ``stages_reverse`` (DualPipe's second direction) is appended to ``stages``."""
+        assert pp_config is not None, "PipelineSchedule needs pp_config"
+        if stages_reverse:
+            stages = list(stages) + list(stages_reverse)
+        if pp_mesh is None and placement is None and dist.is_available() and dist.is_initialized():
+            pp_mesh = dist.group.WORLD
         self.stages = list(stages)
         self.group = pp_mesh.get_group() if hasattr(pp_mesh, "get_group") else pp_mesh
         self.cfg = pp_config
@@ -522,13 +565,33 @@ class DualPipeScheduleRuntime(PipelineSchedule):
         super().__init__(stages, pp_mesh, cfg, **kw)
 
 
-def clip_grad_norm_pp(parameters, max_norm: float, pp_group=None, norm_type: float = 2.0,
-                      copies: int = 1, ep_group=None) -> torch.Tensor:
+def clip_grad_norm_pp(parameters, max_norm=None, pp_group=None, norm_type: float = 2.0,
+                      copies: int = 1, ep_group=None, *, max_grad_norm: Optional[float] = None,
+                      model_parts=None) -> torch.Tensor:
     """Clip by the global norm over all pipeline stages (one scalar all-reduce over the PP group). ``copies``: how
     many ranks hold each stage (2 under DualPipe, whose twin copies carry identical gradients after
     ``sync_twin_grads``), so that every stage counts once. Composed with other dimensions every parameter still counts
     once: tensor-parallel shards (``_tp_sharded`` = their TP group) add up over that group, expert shards
     (``_ep_sharded``) over ``ep_group``, everything else is identical on those peers."""
+    if model_parts is not None:
+        parameters = model_parts
+    parameters = list(parameters)
+    if parameters and isinstance(parameters[0], nn.Module):
+        # the reference's form: clip_grad_norm_pp(model_parts, pp_group, max_grad_norm, norm_type)
+        # (distributed/pipeline_runtime.py): stage modules first, then the group, then the norm
+        if isinstance(pp_group, (int, float)) and not isinstance(pp_group, bool):
+            max_norm, pp_group = pp_group, max_norm          # positional: the group sits where max_norm is expected
+        elif max_norm is not None and not isinstance(max_norm, (int, float)):
+            max_norm, pp_group = None, max_norm              # group positional, the norm by keyword
+        seen, flat = set(), []
+        for mod in parameters:
+            for q in mod.parameters():
+                if id(q) not in seen:
+                    seen.add(id(q))
+                    flat.append(q)
+        parameters = flat
+    if max_grad_norm is not None:
+        max_norm = max_grad_norm
     params = [p for p in parameters if p.grad is not None]
     dev = params[0].device if params else torch.device("cpu")
     if norm_type == float("inf"):

@@ -9,6 +9,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+from typing import Optional
+
 import torch.nn as nn
 
 from ..models.tp_utils import gather_seq, scatter_seq
@@ -34,10 +36,15 @@ class SequenceParallel(nn.Module):
     exit (``gather_output``) or scatters on entry (``scatter_input``) over the TP group, along
     ``sequence_dim``; the conjugate collective runs in backward."""
 
-    def __init__(self, module: nn.Module, tp_group=None, tp_size: int = 1, *, sequence_dim: int = 1,
-                 gather_output: bool = True, scatter_input: bool = False):
+    def __init__(self, module: Optional[nn.Module] = None, tp_group=None, tp_size: int = 1, *, sequence_dim: int = 1,
+                 gather_output: bool = True, scatter_input: bool = False, use_local_output: bool = False,
+                 output_layouts=None):
+        """``use_local_output`` / ``output_layouts`` belong to the reference's DTensor style object
+        (distributed/tensor_parallel.py), which has no module argument; they are accepted so that its keyword form
+        constructs, and ``module`` may then be given later (``.module = ...``). Tensors here are plain local tensors."""
         super().__init__()
-        self.module = module
+        self.use_local_output, self.output_layouts = use_local_output, output_layouts
+        self.module = module if module is not None else nn.Identity()
         self.tp_group, self.tp_size = tp_group, tp_size
         self.sequence_dim = sequence_dim
         self.gather_output, self.scatter_input = gather_output, scatter_input

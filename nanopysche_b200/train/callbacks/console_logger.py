@@ -18,8 +18,10 @@ DEFAULT_LOG_PATTERNS = ["train/*", "optim/LR", "optim/total grad norm", "through
 
 
 class ConsoleLoggerCallback(Callback):
-    def __init__(self, patterns: Optional[Sequence[str]] = None, log_interval: int = 1):
-        self.patterns = list(patterns or DEFAULT_LOG_PATTERNS)
+    def __init__(self, patterns: Optional[Sequence[str]] = None, log_interval: int = 1,
+                 metrics_to_log: Optional[Sequence[str]] = None):
+        """``metrics_to_log``: the reference's name for the list of metric patterns (train/callbacks/console_logger.py)."""
+        self.patterns = list(patterns or metrics_to_log or DEFAULT_LOG_PATTERNS)
         self.log_interval = log_interval
         self._t0: Optional[float] = None
 

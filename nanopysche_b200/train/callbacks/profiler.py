@@ -18,7 +18,10 @@ class ProfilerCallback(Callback):
     def __init__(self, save_dir: str = "profiler", skip_first: int = 2, wait: int = 0, warmup: int = 1, active: int = 3,
                  repeat: int = 1, profile_ranks: Optional[str] = None, with_stack: bool = False,
                  profile_memory: bool = False, record_shapes: bool = False, with_flops: bool = False,
-                 row_limit: int = 20):
+                 row_limit: int = 20, output_dir: Optional[str] = None, enable_cuda_sync_events: bool = False):
+        """``output_dir`` / ``enable_cuda_sync_events``: the reference's names (train/callbacks/profiler.py); the latter
+        is accepted and ignored (the Kineto switch it set only adds synchronisation records to the trace)."""
+        save_dir = output_dir or save_dir
         self.save_dir = save_dir
         self.skip_first, self.wait, self.warmup, self.active, self.repeat = skip_first, wait, warmup, active, repeat
         self.profile_ranks = profile_ranks

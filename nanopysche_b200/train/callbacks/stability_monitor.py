@@ -3,15 +3,22 @@ a value further than ``threshold`` standard deviations from the rolling mean cou
 from __future__ import annotations
 
 from collections import deque
-from typing import Any
+from typing import Any, Optional
 
 from .base import Callback
 
 
 class StabilityMonitorCallback(Callback):
     def __init__(self, window_size: int = 128, threshold: float = 10.0,
-                 metrics: tuple = ("train/CE loss", "optim/total grad norm")):
-        self.window_size, self.threshold, self.metrics = window_size, threshold, metrics
+                 metrics: tuple = ("train/CE loss", "optim/total grad norm"), *,
+                 threshold_std: Optional[float] = None, metric_name: Optional[str] = None):
+        """``threshold_std`` / ``metric_name``: the reference's names (train/callbacks/stability_monitor.py) for the
+        threshold and for watching a single metric."""
+        if threshold_std is not None:
+            threshold = threshold_std
+        if metric_name is not None:
+            metrics = (metric_name,)
+        self.window_size, self.threshold, self.metrics = window_size, threshold, tuple(metrics)
         self._hist = {m: deque(maxlen=window_size) for m in metrics}
         self._total_spikes = 0
 

@@ -13,7 +13,9 @@ log = logging.getLogger(__name__)
 class WandBCallback(Callback):
     def __init__(self, project: str = "nanopsyche", name: Optional[str] = None, config: Optional[dict] = None,
                  entity: Optional[str] = None, tags: Optional[list] = None, cancel_tags: Optional[list] = None,
-                 cancel_check_interval: int = 25, enabled: bool = True):
+                 cancel_check_interval: int = 25, enabled: bool = True, group: Optional[str] = None,
+                 notes: Optional[str] = None):
+        self.group, self.notes = group, notes       # passed to wandb.init like the reference does
         self.project, self.name, self.config, self.entity, self.tags = project, name, config, entity, tags
         self.cancel_tags = cancel_tags or ["cancel", "canceled", "cancelled"]
         self.cancel_check_interval = cancel_check_interval
@@ -32,7 +34,7 @@ class WandBCallback(Callback):
             return
         self._wandb = wandb
         self._run = wandb.init(project=self.project, name=self.name, config=self.config, entity=self.entity,
-                               tags=self.tags)
+                               tags=self.tags, group=self.group, notes=self.notes)
 
     def log_metrics(self, metrics: Dict[str, Any], step: int, trainer: Any) -> None:
         if self._run is not None:

@@ -17,7 +17,13 @@ from torch.utils.data import DataLoader, Dataset, DistributedSampler, RandomSamp
 
 
 class DistributedDataset(Dataset):
-    def __init__(self, tokens, seq_len: int):
+    def __init__(self, tokens=None, seq_len: Optional[int] = None, *, data_source=None, sequence_length: Optional[int] = None):
+        """``tokens`` / ``seq_len``, or by the reference's names ``data_source`` / ``sequence_length``
+        (train/data.py, default length 2048)."""
+        tokens = tokens if tokens is not None else data_source
+        seq_len = seq_len if seq_len is not None else (sequence_length if sequence_length is not None else 2048)
+        if torch.is_tensor(tokens):
+            tokens = tokens.cpu().numpy()
         self.tokens = tokens
         self.seq_len = seq_len
         self.n = max((len(tokens) - 1) // seq_len, 0)

@@ -220,6 +220,17 @@ class Trainer:
                 cb.post_log_metrics(self)
         return out
 
+    def get_vocab_size(self) -> int:
+        """Vocabulary size for synthetic batches: the model's, else the configured one
+        (reference: train/trainer.py:361-367)."""
+        v = getattr(self.model, "vocab_size", None)
+        if v:
+            return int(v)
+        emb = getattr(self.model, "embeddings", None)
+        if emb is not None and hasattr(emb, "weight"):
+            return int(emb.weight.shape[0])
+        return int(getattr(self.config, "vocab_size", 32000) or 32000)
+
     def request_stop(self, reason: str = "") -> None:
         self._stop_reason = reason or "stop requested"
 

@@ -288,3 +288,19 @@ def test_deepep_dispatcher_knobs_map_onto_the_fused_runtime_settings():
     assert 4 <= b <= a <= 144      # e4m3 rows halve the bytes on the wire, so fewer SMs go to the dispatch
     cfg = ExpertParallelConfig(ep_size=1, dispatcher=DeepEPDispatcher(use_fp8_dispatch=True))
     assert cfg.dispatcher.use_fp8_dispatch and cfg.dispatcher.async_with_compute_stream
+
+
+def test_generic_adapter_layer_helpers():
+    import torch.nn as nn
+
+    from nanopysche_b200.models.parallel_adapter import iter_layers, layer_count
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = nn.ModuleDict({str(i): nn.Linear(2, 2 + i) for i in (0, 1, 2, 10, 9)})
+
+    m = M()
+    assert layer_count(m) == 5
+    assert [l.out_features for l in iter_layers(m)] == [2, 3, 4, 11, 12]      # numeric order: 9 before 10
+    assert layer_count(nn.Linear(2, 2)) == 0 and list(iter_layers(nn.Linear(2, 2))) == []

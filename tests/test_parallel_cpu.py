@@ -573,3 +573,42 @@ def _seq_parallel_moe_worker(rank, world):
 
 def test_moe_under_sequence_parallel_matches_unsharded():
     assert all(run_distributed(_seq_parallel_moe_worker, 2))
+
+
+def test_reference_call_forms_of_the_pipeline_and_mesh_api():
+    """The argument orders and keyword names of the reference are accepted next to this package's own."""
+    import torch.nn as nn
+
+    from nanopysche_b200.models.moe import ExpertParallelConfig, TokenDispatcher
+    from nanopysche_b200.parallel.pipeline_runtime import PipelineParallelConfig as RtCfg
+    from nanopysche_b200.parallel.pipeline_runtime import clip_grad_norm_pp
+
+    stages = [nn.Linear(2, 2) for _ in range(4)]
+    assert pp.GPipeSchedule(stages, 8).num_stages == 4 and pp.GPipeSchedule(4, 8).num_stages == 4
+    assert pp.OneForwardOneBackwardSchedule(stages=stages, num_microbatches=8).num_stages == 4
+    st = pp.PipelineStage(1, 4, nn.ModuleList([nn.Linear(2, 2)]), loss_fn=None)       # reference order
+    assert st.stage_id == 1 and st.num_stages == 4 and isinstance(st.layers, nn.ModuleList)
+    st = pp.PipelineStage(nn.ModuleList([nn.Linear(2, 2)]), 3, 4)
+    assert st.stage_id == 3 and st.is_last
+    assert RtCfg(4, schedule="1F1B").stage_ids_this_rank(2, 4) == [2]
+
+    parts = [nn.Linear(3, 3), nn.Linear(3, 3)]
+    for m in parts:
+        for q in m.parameters():
+            q.grad = torch.ones_like(q)
+    total = clip_grad_norm_pp(parts, None, 1.0)                  # (model_parts, pp_group, max_grad_norm)
+    assert total.item() == pytest.approx((2 * 12) ** 0.5)
+    assert sum(q.grad.pow(2).sum() for m in parts for q in m.parameters()).sqrt().item() == pytest.approx(1.0, rel=1e-4)
+
+    class RefStyle(TokenDispatcher):                              # a dispatcher written against the reference's ABC
+        def dispatch(self, x, expert_indices, expert_weights, num_experts, ep_size, ep_rank, ep_group):
+            return x, expert_weights, expert_indices, ("meta", ep_size, ep_rank)
+
+        def combine(self, expert_output, combine_metadata, x, expert_weights, expert_indices, ep_size, ep_group):
+            return expert_output + ep_size
+
+    ep = ExpertParallelConfig(ep_size=1, dispatcher=RefStyle())
+    x = torch.zeros(2, 3)
+    out = ep.dispatch(x, torch.zeros(2, 1, dtype=torch.long), torch.ones(2, 1), 4)
+    assert out[3] == ("meta", 1, 0) and ep.ep_rank == 0 and ep.ep_rank() == 0
+    assert torch.equal(ep.combine(x, out[3], x, out[1], out[2]), x + 1)

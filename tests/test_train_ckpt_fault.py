@@ -651,3 +651,51 @@ def test_planned_departure_stops_the_peers_before_the_next_step(tmp_path):
     saved = torch.load(os.path.join(d0, "rank_0000_model.pt"))
     for k, v in m.state_dict().items():
         assert torch.equal(v, saved[k]), k
+
+
+def test_reference_method_surface_of_checkpoint_and_pipeline_helpers(tmp_path):
+    """Methods a user of the reference may call on the helper classes (names and meaning as in
+    checkpoint/distributed.py and distributed/pipeline_runtime.py of the reference)."""
+    from nanopysche_b200.checkpoint.distributed import (DataloaderStateTracker, IncrementalCheckpointer, PlanCache,
+                                                        SavePlan)
+    from nanopysche_b200.fp8.training import FP8Config
+    from nanopysche_b200.parallel.pipeline_runtime import PipelineParallelConfig, PipelineSplitStyle
+
+    st = PinnedMemoryStager()
+    t = torch.arange(6.0).view(2, 3)
+    out = st.stage_tensor(t)
+    assert torch.equal(out, t) and out.data_ptr() != t.data_ptr()
+
+    pc = PlanCache()
+    assert pc.get_plan(1) is None
+    plan = pc.get({"a": torch.zeros(3)})
+    assert pc.get_plan(5) is plan
+    pc.cache_plan(7, SavePlan(["x"], {"x": 4}, 4))
+    assert pc.get_plan(7).keys == ["x"]
+    pc.invalidate()
+    assert pc.get_plan(7) is None
+
+    inc = IncrementalCheckpointer(full_save_interval=4)
+    assert inc.compute_param_hash(t) == inc.compute_param_hash(t.clone()) != inc.compute_param_hash(t + 1)
+    assert inc.is_base_checkpoint_needed(8) and not inc.is_base_checkpoint_needed(9) and inc.is_base_checkpoint_needed(9, 3)
+
+    tr = DataloaderStateTracker()
+    tr.update(4)
+    tr.update(current_file="shard_3.bin", global_step=11)          # the reference's keyword form: fields, no count
+    assert tr.get_state()["samples_seen"] == 4 and tr.get_state()["extra"]["current_file"] == "shard_3.bin"
+    p = os.path.join(str(tmp_path), "dl.json")
+    tr.save(p)
+    tr2 = DataloaderStateTracker()
+    tr2.load(p)
+    assert tr2.state_dict() == tr.state_dict()
+
+    cfg = PipelineParallelConfig(4, schedule="ZBVZeroBubble")
+    assert cfg.stages_per_rank == 2 and cfg.stages_per_rank() == 2 and cfg.total_stages == 8
+    assert not cfg.is_single_stage and cfg.split_style == PipelineSplitStyle.v
+    assert PipelineParallelConfig(2).is_single_stage and PipelineParallelConfig(2).total_stages == 2
+    assert FP8Config(enabled=True).build_torchao_config() is None
+
+    m = tiny_model()
+    tc = TrainingConfig(global_batch_size=32, micro_batch_size=2, sequence_length=16, max_steps=1, dtype=torch.float32,
+                        vocab_size=64)
+    assert Trainer(tc, m, torch.optim.SGD(m.parameters(), lr=0.1), None, None, []).get_vocab_size() == 64
