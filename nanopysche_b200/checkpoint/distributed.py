@@ -120,6 +120,11 @@ class SavePlan:
     keys: List[str] = field(default_factory=list)
     sizes: Dict[str, int] = field(default_factory=dict)
     total_bytes: int = 0
+    # fields of the reference's plan (checkpoint/distributed.py:163-169); every rank writes its own shard here, so the
+    # assignment is the identity and filled on request
+    rank_assignments: Dict[int, List[str]] = field(default_factory=dict)
+    created_at_step: int = -1
+    param_hashes: Dict[str, str] = field(default_factory=dict)
 
 
 class PlanCache:

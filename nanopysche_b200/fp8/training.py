@@ -29,6 +29,8 @@ class FP8Config:
     force_recompute_fp8_weight_in_bwd: bool = False
     ignored_modules: List[str] = field(default_factory=lambda: ["lm_head", "gate"])
     min_features: int = 128
+    cast_input_text: bool = True            # reference field (fp8/training.py:75): activations are always cast here
+    filter_fn: Optional[str] = None         # reference field (fp8/training.py:76): substring a module's name must contain
 
     def build_torchao_config(self):
         """The reference hands its linears to torchao (fp8/training.py:78-90). Here the fp8 linears run on this
@@ -97,6 +99,8 @@ def apply_fp8(model: nn.Module, config: Optional[FP8Config] = None,
                     cfg.min_features:
                 continue
             if module_filter is not None and not module_filter(child, fqn):
+                continue
+            if cfg.filter_fn and cfg.filter_fn not in fqn:
                 continue
             child.__class__ = Float8Linear
             child.weight._fp8_recipe = "mxfp8" if cfg.recipe_name == "mxfp8" else "blockwise"

@@ -421,6 +421,7 @@ class MoEConfig:
     adaptive_capacity_ema: float = 0.3
     routing_replay: bool = False
     shared_expert: bool = False
+    ep: Optional["ExpertParallelConfig"] = None      # expert-parallel placement (reference: model/moe.py:1209)
     fp8_flow_moe: bool = False
     fp8_recipe: str = "none"
     fp8_gemm_threshold: int = 1000000

@@ -34,6 +34,15 @@ class Action:
     microbatch: int = -1
     stage: int = -1
 
+    # the reference's field names (distributed/pipeline_parallel.py:62-68)
+    @property
+    def microbatch_idx(self) -> int:
+        return self.microbatch
+
+    @property
+    def stage_idx(self) -> int:
+        return self.stage
+
     def __repr__(self):
         tag = {"fwd": "F", "bwd": "B", "bwd_b": "Bi", "bwd_w": "W", "idle": "-"}[self.type.value]
         return f"{tag}{self.microbatch}@{self.stage}" if self.type != ScheduleType.IDLE else "-"
