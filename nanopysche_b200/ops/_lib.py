@@ -208,7 +208,8 @@ def available() -> bool:
     return torch.cuda.is_available()
 
 
-PLAIN = False  # True: every op takes its PyTorch statement even on CUDA tensors (the plain library-call arm)
+# True: every op takes its PyTorch statement even on CUDA tensors (the plain library-call arm); NPB200_PLAIN=1 sets it
+PLAIN = os.environ.get("NPB200_PLAIN", "0") == "1"
 
 
 def set_plain(flag: bool) -> None:
