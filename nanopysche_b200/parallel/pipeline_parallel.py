@@ -260,9 +260,11 @@ class InterleavedSchedule(_Schedule):
     ``split_w`` the backward is split into B and W and W fills idle slots."""
 
     def __init__(self, num_ranks: int, num_microbatches: int, v: int = 2, placement: str = "loop",
-                 split_w: bool = False):
+                 split_w: bool = False, order: str = "1f1b"):
+        """``order="bfs"``: looped breadth-first - every stage runs all its forwards before any backward (the GPipe
+        order per model chunk), which keeps the most activations alive and the fewest transfers in flight."""
         super().__init__(num_ranks, num_microbatches)
-        self.v, self.placement, self.split_w = v, placement, split_w
+        self.v, self.placement, self.split_w, self.order = v, placement, split_w, order
         self.total_stages = v * num_ranks
 
     def rank_of_stage(self, stage: int) -> int:
@@ -278,7 +280,11 @@ class InterleavedSchedule(_Schedule):
     def generate_schedule(self):
         p, m, S = self.num_stages, self.num_microbatches, self.total_stages
         mbs = list(range(m))
-        work = {r: [_one_f_one_b_queue(s, s, S, mbs) for s in self.stages_of_rank(r)] for r in range(p)}
+        if self.order == "bfs":
+            work = {r: [[Action(F, mb, s) for mb in mbs] + [Action(B, mb, s) for mb in mbs]
+                        for s in self.stages_of_rank(r)] for r in range(p)}
+        else:
+            work = {r: [_one_f_one_b_queue(s, s, S, mbs) for s in self.stages_of_rank(r)] for r in range(p)}
         return _greedy(p, work, self.rank_of_stage, lambda a: S - 1, lambda a: 0, split_w=self.split_w)
 
 

@@ -322,7 +322,9 @@ class PipelineSchedule:
             gen = InterleavedSchedule(self.p, self.m, v=2, placement="v", split_w=True)
         elif st == PipelineScheduleType.interleaved_zero_bubble:
             gen = InterleavedSchedule(self.p, self.m, v=2, placement="loop", split_w=True)
-        else:  # Interleaved1F1B, LoopedBFS
+        elif st == PipelineScheduleType.looped_bfs:
+            gen = InterleavedSchedule(self.p, self.m, v=2, placement="loop", order="bfs")
+        else:  # Interleaved1F1B
             gen = InterleavedSchedule(self.p, self.m, v=2, placement="loop")
         self.generator = gen
         self.all_actions: List[List[Action]] = gen.generate_schedule()

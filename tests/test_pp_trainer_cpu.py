@@ -87,7 +87,8 @@ def _pp_trainer_worker(rank, world, schedule):
     return True
 
 
-@pytest.mark.parametrize("schedule", ["1F1B", "GPipe", "DualPipe", "ZBVZeroBubble", "InterleavedZeroBubble"])
+@pytest.mark.parametrize("schedule", ["1F1B", "GPipe", "DualPipe", "ZBVZeroBubble", "InterleavedZeroBubble",
+                                      "Interleaved1F1B", "LoopedBFS"])
 def test_trainer_runs_pipeline_stages(schedule):
     assert all(run_distributed(_pp_trainer_worker, 2, schedule))
 
