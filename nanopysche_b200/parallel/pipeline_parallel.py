@@ -283,6 +283,26 @@ class InterleavedSchedule(_Schedule):
         if self.order == "bfs":
             work = {r: [[Action(F, mb, s) for mb in mbs] + [Action(B, mb, s) for mb in mbs]
                         for s in self.stages_of_rank(r)] for r in range(p)}
+        elif self.order == "1f1b" and self.placement == "loop" and not self.split_w and m % p == 0:
+            # The depth-first interleaved order (Narayanan et al. 2021): micro-batches advance in groups of p through
+            # chunk 0, chunk 1, ...; rank r warms up with 2 (p - r - 1) + (v - 1) p forwards, then alternates one
+            # forward and one backward. One fixed queue per rank; the list scheduler only checks that it is feasible.
+            v, total = self.v, m * self.v
+
+            def fwd(k, r):
+                return Action(F, (k // (p * v)) * p + k % p, ((k // p) % v) * p + r)
+
+            def bwd(k, r):
+                return Action(B, (k // (p * v)) * p + k % p, (v - 1 - (k // p) % v) * p + r)
+
+            work = {}
+            for r in range(p):
+                warm = min(2 * (p - r - 1) + (v - 1) * p, total)
+                q = [fwd(k, r) for k in range(warm)]
+                for i in range(total - warm):
+                    q += [fwd(warm + i, r), bwd(i, r)]
+                q += [bwd(i, r) for i in range(total - warm, total)]
+                work[r] = [q]
         else:
             work = {r: [_one_f_one_b_queue(s, s, S, mbs) for s in self.stages_of_rank(r)] for r in range(p)}
         return _greedy(p, work, self.rank_of_stage, lambda a: S - 1, lambda a: 0, split_w=self.split_w)
