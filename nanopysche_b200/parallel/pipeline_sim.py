@@ -225,3 +225,24 @@ def timeline(schedule, p: int, m: int, *, t_fwd: float = 1.0, t_bwd: float = 2.0
     makespan = max(op.t_end for ops in programs for op in ops)
     busy = sum(cost.get(op.action, 0.0) for ops in programs for op in ops if op.kind == "compute")
     return {"makespan": makespan, "bubble": 1.0 - busy / (p * makespan)}
+
+
+def recommend(p: int, m: int, *, t_fwd: float = 1.0, t_bwd: float = 2.0, t_p2p: float = 0.0,
+              schedules=("1F1B", "Interleaved1F1B", "LoopedBFS", "InterleavedZeroBubble", "ZBVZeroBubble", "DualPipe")):
+    """Schedules ranked by replayed step time for measured per-rank costs: ``t_fwd`` / ``t_bwd`` are the forward and
+    backward time of one micro-batch through *all* layers of a rank (a schedule with two chunks per rank is charged
+    half per action; DualPipe's two stage copies each hold a whole rank's share), ``t_p2p`` one activation transfer.
+    Returns ``[(name, makespan, bubble), ...]``, best first; a schedule that cannot run with these sizes (DualPipe and
+    an odd micro-batch count) is left out."""
+    out = []
+    for name in schedules:
+        st = PipelineScheduleType(name)
+        chunks = 1 if (st.is_single_stage or st == PipelineScheduleType.dualpipe) else 2
+        if st == PipelineScheduleType.dualpipe and m % 2:
+            continue
+        try:
+            t = timeline(name, p, m, t_fwd=t_fwd / chunks, t_bwd=t_bwd / chunks, t_p2p=t_p2p)
+        except Exception:  # noqa: BLE001  (sizes the generator refuses)
+            continue
+        out.append((name, t["makespan"], t["bubble"]))
+    return sorted(out, key=lambda x: x[1])

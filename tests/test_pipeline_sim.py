@@ -61,3 +61,13 @@ def test_timed_replay_reproduces_closed_form_bubbles_and_ranks_schedules():
         assert zb["bubble"] < 0.5 * closed and dual["bubble"] < 0.5 * closed
     # a transfer cost lengthens the step of a schedule whose transfers are on the critical path
     assert timeline("GPipe", 4, 8, t_p2p=0.25)["makespan"] > timeline("GPipe", 4, 8)["makespan"]
+
+
+def test_recommend_ranks_schedules_by_replayed_step_time():
+    from nanopysche_b200.parallel.pipeline_sim import recommend
+
+    ranked = recommend(4, 8, t_fwd=1.0, t_bwd=2.0, t_p2p=0.05)
+    names = [n for n, _, _ in ranked]
+    assert names[-1] == "1F1B" and names.index("DualPipe") < names.index("Interleaved1F1B") < names.index("1F1B")
+    assert all(a[1] <= b[1] for a, b in zip(ranked, ranked[1:]))
+    assert "DualPipe" not in [n for n, _, _ in recommend(3, 5)]
