@@ -147,16 +147,20 @@ class SymmetricHeap:
             C.c_void_p(_lib.stream())), "symm_allreduce")
         return t
 
-    def close(self):
+    def close(self, collective: bool = True):
+        """Unmap the peers' memory and free this rank's. ``collective=True`` brackets the unmapping with two barriers
+        so that no rank frees memory a peer still has mapped and in use; after a peer has left the job
+        (``PeerLeftError``, ``CommTimeoutError``) pass ``collective=False``: a barrier would wait for the departed
+        rank, and nothing of this heap is launched any more."""
         if self._ipc:
             lib = _lib.lib()
             torch.cuda.synchronize()
-            if dist.is_initialized():
+            if collective and dist.is_initialized():
                 dist.barrier(group=self.group)
             for r, p in enumerate(self.peer_ptrs):
                 if r != self.rank:
                     lib.np_symm_close(C.c_void_p(p))
-            if dist.is_initialized():
+            if collective and dist.is_initialized():
                 dist.barrier(group=self.group)
             lib.np_symm_free(C.c_void_p(self.local_ptr))
             self._ipc = False
