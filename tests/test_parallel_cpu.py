@@ -612,3 +612,55 @@ def test_reference_call_forms_of_the_pipeline_and_mesh_api():
     out = ep.dispatch(x, torch.zeros(2, 1, dtype=torch.long), torch.ones(2, 1), 4)
     assert out[3] == ("meta", 1, 0) and ep.ep_rank == 0 and ep.ep_rank() == 0
     assert torch.equal(ep.combine(x, out[3], x, out[1], out[2]), x + 1)
+
+
+def _seq_parallel_arena_worker(rank, world):
+    """Sequence-parallel TP (tp 2) of a MoE model with the parameter arena: the MoE weights' gradients reach the arena
+    past the autograd hooks' reduction (the hook leaves arena-managed parameters alone) and are summed over the TP
+    group by the arena step; after one clipped AdamW step every parameter (or shard) equals the unsharded model's."""
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.optim.arena import ArenaAdamW, ParamArena
+    from nanopysche_b200.parallel.mesh import build_world_mesh
+    from nanopysche_b200.parallel.tensor_parallel import TensorParallelConfig
+    from nanopysche_b200.parallelize import parallelize_model
+
+    torch.manual_seed(0)
+    cfg = TransformerConfig(d_model=32, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=16,
+                            ffn_hidden=64, qk_norm=False, use_moe=True, num_experts=4, moe_top_k=2, moe_interval=2,
+                            moe_offset=1, moe_hidden=32, moe_capacity_factor=None)
+    full = cfg.build()
+    model = copy.deepcopy(full)
+    mesh = build_world_mesh(tp_size=2, device_type="cpu", replace=True)
+    model = parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"),
+                              tp_config=TensorParallelConfig(2, sequence_parallel=True))
+    assert model._tp_sequence_parallel and not model._tp_async
+    ids = torch.randint(0, 64, (2, 16))
+    dist.broadcast(ids, 0)
+    arena = ParamArena(model, dp_group=None, device=torch.device("cpu"))
+    assert any(r.sp_group is not None for r in arena.regions.values())
+    opt = ArenaAdamW(arena, lr=1e-2, weight_decay=0.1, max_grad_norm=0.05)
+    out = model(ids, labels=ids)
+    (out["loss"] + out["aux_loss"]).backward()
+    opt.step()
+    a0 = ParamArena(full, device=torch.device("cpu"))
+    o0 = ArenaAdamW(a0, lr=1e-2, weight_decay=0.1, max_grad_norm=0.05)
+    o = full(ids, labels=ids)
+    (o["loss"] + o["aux_loss"]).backward()
+    o0.step()
+    assert abs(float(opt.last_grad_norm) - float(o0.last_grad_norm)) < 1e-4 * float(o0.last_grad_norm) + 1e-6, \
+        (float(opt.last_grad_norm), float(o0.last_grad_norm))
+    ref = dict(full.named_parameters())
+    for name, p in model.named_parameters():
+        r = ref[name]
+        if name.endswith(("w_q.weight", "w_k.weight", "w_v.weight", "w1.weight", "w3.weight")):
+            n = r.shape[0] // 2
+            r = r[rank * n:(rank + 1) * n]
+        elif name.endswith(("w_out.weight", "w2.weight")):
+            n = r.shape[1] // 2
+            r = r[:, rank * n:(rank + 1) * n]
+        assert torch.allclose(p, r, atol=2e-5, rtol=1e-4), (name, (p - r).abs().max())
+    return True
+
+
+def test_arena_step_under_sequence_parallel_with_moe():
+    assert all(run_distributed(_seq_parallel_arena_worker, 2))
