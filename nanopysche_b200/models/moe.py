@@ -118,24 +118,40 @@ class MoERouter(nn.Module):
         counts = torch.zeros(self.num_experts, device=logits.device, dtype=torch.float32)
         counts.scatter_add_(0, indices.reshape(-1), torch.ones(indices.numel(), device=logits.device))
         P = F.softmax(logits.float(), dim=-1).reshape(-1, self.num_experts).mean(0)
-        sp = getattr(self, "_sp_group", None)
-        if sp is not None and dist.is_available() and dist.is_initialized() and dist.get_world_size(sp) > 1:
-            # sequence-parallel tensor parallelism: this rank routes 1 / tp of the rows. The loss is E * sum(f * P) over
-            # *all* rows: f (token fractions, no gradient) is summed over the group; P is a mean of per-rank means, so
-            # each rank contributes f_all * P_local / tp and the contributions add up over the group - in value after
-            # the all-reduce below, in gradient through the partial-gradient sum of the router's parameters.
-            n = dist.get_world_size(sp)
+        n = self._token_shards()
+        if n > 1:
+            # The rows of one batch are spread over other ranks (sequence-parallel tensor parallelism: 1 / tp of the
+            # rows; context parallelism: 1 / cp of every sequence). The loss is E * sum(f * P) over *all* rows: f (token
+            # fractions, no gradient) is summed over those ranks; P is a mean of per-rank means, so each rank
+            # contributes f_all * P_local / n and the contributions add up - in value after the all-reduce below, in
+            # gradient through the sum of the partial gradients that these layouts form anyway.
             all_counts = counts.clone()
-            dist.all_reduce(all_counts, group=sp)
+            for g in self._token_shard_groups():
+                dist.all_reduce(all_counts, group=g)
             part = self.num_experts * ((all_counts / (n_tok * n)) * P).sum() / n
             return self._sp_total(part), counts
         f = counts / n_tok
         return self.num_experts * (f * P).sum(), counts
 
+    def _token_shard_groups(self) -> list:
+        """Groups over which the rows of one batch are spread: ``_sp_group`` (set by sequence-parallel TP) and
+        ``_cp_group`` (set by context parallelism). Summing over each in turn sums over their product."""
+        if not (dist.is_available() and dist.is_initialized()):
+            return []
+        return [g for g in (getattr(self, "_sp_group", None), getattr(self, "_cp_group", None))
+                if g is not None and dist.get_world_size(g) > 1]
+
+    def _token_shards(self) -> int:
+        n = 1
+        for g in self._token_shard_groups():
+            n *= dist.get_world_size(g)
+        return n
+
     def _sp_total(self, part: torch.Tensor) -> torch.Tensor:
-        """Value: the sum of ``part`` over the sequence-parallel group; gradient: this rank's ``part`` only."""
+        """Value: the sum of ``part`` over the ranks that share the batch's rows; gradient: this rank's ``part`` only."""
         tot = part.detach().clone()
-        dist.all_reduce(tot, group=self._sp_group)
+        for g in self._token_shard_groups():
+            dist.all_reduce(tot, group=g)
         return part + (tot - part.detach())
 
     def forward(self, x: torch.Tensor):
@@ -148,12 +164,13 @@ class MoERouter(nn.Module):
             from ..ops import moe as moe_ops
 
             w, idx, aux, counts = moe_ops.route(x, self)
-            sp = getattr(self, "_sp_group", None)
-            if sp is not None and dist.is_initialized() and dist.get_world_size(sp) > 1:
-                # the router kernels take their load statistics over this rank's rows: under sequence-parallel tensor
-                # parallelism the loss is then the mean of the ranks' own losses (Megatron's per-rank form) rather than
-                # the loss of the whole batch that the PyTorch path below computes
-                aux = self._sp_total(aux / dist.get_world_size(sp))
+            n = self._token_shards()
+            if n > 1:
+                # the router kernels take their load statistics over this rank's rows: with the batch's rows spread
+                # over other ranks (sequence-parallel TP, context parallelism) the loss is then the mean of the ranks'
+                # own losses (Megatron's per-rank form) rather than the loss of the whole batch that the PyTorch path
+                # below computes
+                aux = self._sp_total(aux / n)
         else:
             logits = F.linear(x.float(), self.gate.weight, self.gate.bias)
             if self.score_bias is not None:
@@ -169,9 +186,9 @@ class MoERouter(nn.Module):
             aux, counts = self._load_balancing_loss(logits, idx)
             if cfg.z_loss_multiplier is not None:
                 z = cfg.z_loss_multiplier * torch.logsumexp(logits.float(), dim=-1).square().mean()
-                sp = getattr(self, "_sp_group", None)
-                if sp is not None and dist.is_initialized() and dist.get_world_size(sp) > 1:
-                    z = self._sp_total(z / dist.get_world_size(sp))    # mean over all rows = mean of the ranks' means
+                n = self._token_shards()
+                if n > 1:
+                    z = self._sp_total(z / n)    # mean over all rows = mean of the ranks' means
                 aux = aux + z
         self.last_counts = counts.detach()
         if self.score_bias is not None:

@@ -339,6 +339,9 @@ class Transformer(nn.Module):
         for blk in self.blocks.values():
             blk.apply_cp(cp_mesh, ring=ring, uly=uly)
         self._cp_group = cp_mesh.get_group() if hasattr(cp_mesh, "get_group") else cp_mesh
+        for m in self.modules():     # a router sees 1 / cp of every sequence: its load statistics span the group
+            if isinstance(m, MoEBase):
+                m.router._cp_group = self._cp_group
 
     def replace_block_with_moe_hybrid(self, block_idx: int, moe: MoEBase, dense_ffn: Optional[FeedForward] = None):
         key = str(block_idx)

@@ -664,3 +664,41 @@ def _seq_parallel_arena_worker(rank, world):
 
 def test_arena_step_under_sequence_parallel_with_moe():
     assert all(run_distributed(_seq_parallel_arena_worker, 2))
+
+
+def _cp_moe_worker(rank, world):
+    """Context parallelism over a MoE model: every rank routes its share of each sequence; the load-balancing loss takes
+    its statistics over the whole sequence, so loss, auxiliary loss and all gradients (summed over the CP group) equal
+    the single-process model's. (With per-rank statistics every rank would add a full auxiliary loss and the router's
+    gradient would come out cp times too large.)"""
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.parallel.context_parallel import shard_batch_for_cp
+
+    torch.manual_seed(0)
+    cfg = TransformerConfig(d_model=32, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=64,
+                            ffn_hidden=64, qk_norm=False, use_moe=True, num_experts=4, moe_top_k=2, moe_interval=2,
+                            moe_offset=1, moe_hidden=32, moe_capacity_factor=None, moe_z_loss=1e-3)
+    m = cfg.build()
+    ref = copy.deepcopy(m)
+    x = torch.randint(0, 64, (2, 32))
+    dist.broadcast(x, 0)
+    o = ref(x, labels=x)
+    (o["loss"] + o["aux_loss"]).backward()
+    m.apply_cp(dist.group.WORLD)
+    ids, tgt = shard_batch_for_cp(x, x, world, rank)
+    out = m(ids, labels=tgt, labels_shifted=True)
+    (out["loss"] + out["aux_loss"]).backward()
+    assert out["loss"].item() == pytest.approx(o["loss"].item(), rel=1e-5)
+    assert out["aux_loss"].item() == pytest.approx(o["aux_loss"].item(), rel=1e-5)
+    rp = dict(ref.named_parameters())
+    for n, p in m.named_parameters():
+        if p.grad is None:
+            continue
+        g = p.grad.clone()
+        dist.all_reduce(g)
+        assert torch.allclose(g, rp[n].grad, atol=2e-5, rtol=1e-4), n
+    return True
+
+
+def test_context_parallel_with_moe_matches_single_process():
+    assert all(run_distributed(_cp_moe_worker, 2))
