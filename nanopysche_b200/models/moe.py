@@ -660,6 +660,31 @@ class MoEBase(nn.Module):
         self.expert_offset = lo
         for p in (self.w1, self.w2, self.w3):
             p._ep_sharded = True  # gradients of expert shards are not averaged over the EP group
+        if getattr(self.router, "_sp_group", None) is not None:
+            self.mark_rows_sharded(self.router._sp_group)     # the shards are new parameter objects: mark them again
+
+    def mark_rows_sharded(self, group) -> None:
+        """Sequence-parallel tensor parallelism hands this layer 1 / tp of the rows on every TP rank, and a MoE layer
+        is not tensor-parallel: every weight of it then sees a partial gradient that has to be summed over ``group``.
+        Gradients may be written by kernels straight into the parameter arena, past any autograd hook, so the arena
+        sums the regions of parameters carrying ``_sp_reduce_group``; without an arena the tensor hook does it (per
+        backward pass, before accumulation). The router also takes its load statistics over the group."""
+        self.router._sp_group = group
+
+        def hook_for(param):
+            def fn(g):
+                if hasattr(param, "main_grad"):
+                    return g
+                g = g.contiguous().clone()
+                dist.all_reduce(g, group=group)
+                return g
+            return fn
+
+        for p in self.parameters():
+            if getattr(p, "_tp_partial", False) or getattr(p, "_sp_reduce_group", None) is not None:
+                continue
+            p._sp_reduce_group = group
+            p.register_hook(hook_for(p))
 
     def apply_fp8_flow_moe(self, fp8_flow_moe: bool = True, fp8_recipe: str = "blockwise",
                            fp8_gemm_threshold: Optional[int] = None):

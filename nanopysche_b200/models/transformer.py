@@ -301,18 +301,9 @@ class Transformer(nn.Module):
             # kernels straight into the parameter arena, past any autograd hook, so the arena sums the regions of
             # parameters carrying ``_sp_reduce_group``; without an arena the hook below does it. The router takes its
             # load statistics over the whole TP group (``MoERouter._sp_group``).
-            def expert_hook(param):
-                def fn(g):
-                    return g if hasattr(param, "main_grad") else reduce_hook(g)
-                return fn
-
             for m in self.modules():
                 if isinstance(m, MoEBase):
-                    m.router._sp_group = group
-                    for p in m.parameters():
-                        if not getattr(p, "_tp_partial", False):
-                            p._sp_reduce_group = group
-                            p.register_hook(expert_hook(p))
+                    m.mark_rows_sharded(group)
 
     def _ensure_tp_runtime(self, B: int, S: int, device):
         from ..models.attention import Attention

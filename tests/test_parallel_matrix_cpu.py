@@ -1,0 +1,86 @@
+"""Compositions of the parallel dimensions through ``parallelize_model`` + ``Trainer`` on gloo ranks: one SGD step with
+learning rate 1 and no clipping turns every parameter's change into the gradient the framework applied, which must equal
+the gradient of the single-process model under the data-parallel objective (the mean over the ranks that read
+different batches of each rank's cross-entropy plus auxiliary loss) - for replicated parameters, tensor-parallel
+shards, expert shards and parameters applied to row shards alike."""
+import copy
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from conftest import run_distributed
+
+
+def _worker(rank, world, dims, moe, seq_par):
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.parallel.context_parallel import ContextParallelConfig
+    from nanopysche_b200.parallel.mesh import build_world_mesh, data_parallel_coords
+    from nanopysche_b200.parallel.tensor_parallel import TensorParallelConfig
+    from nanopysche_b200.parallelize import parallelize_model
+    from nanopysche_b200.train.trainer import Trainer, TrainingConfig
+
+    torch.manual_seed(0)
+    kw = dict(use_moe=True, num_experts=4, moe_top_k=2, moe_interval=2, moe_offset=1, moe_hidden=32,
+              moe_capacity_factor=None) if moe else {}
+    cfg = TransformerConfig(d_model=32, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=32,
+                            ffn_hidden=64, qk_norm=False, **kw)
+    model = cfg.build()
+    ref = copy.deepcopy(model)
+    mesh = build_world_mesh(device_type="cpu", replace=True, **dims)
+    idx, cnt = data_parallel_coords(mesh)
+    torch.manual_seed(1)
+    batches = [torch.randint(0, 64, (2, 16)) for _ in range(cnt)]
+    for b in batches:
+        o = ref(b, labels=b)
+        ((o["loss"] + (o["aux_loss"] if o.get("aux_loss") is not None else 0)) / cnt).backward()
+    tp, cp, ep = dims.get("tp_size", 1), dims.get("cp_size", 1), dims.get("ep_size", 1)
+    model = parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"),
+                              tp_config=TensorParallelConfig(tp, sequence_parallel=seq_par) if tp > 1 else None,
+                              cp_config=ContextParallelConfig(cp) if cp > 1 else None)
+    opt = torch.optim.SGD(model.parameters(), lr=1.0)
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    mine = batches[idx]
+
+    class Loader:
+        def __iter__(self):
+            return iter([(mine, mine.clone())])
+
+    tc = TrainingConfig(global_batch_size=cnt * 2 * 16, micro_batch_size=2, sequence_length=16, max_steps=1,
+                        dtype=torch.float32, log_interval=0, save_interval=0, vocab_size=64, dp_world_size=cnt,
+                        max_grad_norm=0.0, cp_size=cp)
+    Trainer(tc, model, opt, data_loader=Loader(), device=torch.device("cpu")).fit()
+    names = mesh.mesh_dim_names
+    tp_rank = mesh["tp"].get_local_rank() if "tp" in names else 0
+    ep_rank = mesh["ep"].get_local_rank() if "ep" in names else 0
+    rp = dict(ref.named_parameters())
+    bad = {}
+    for n, p in model.named_parameters():
+        g, r = before[n] - p.detach(), rp[n].grad
+        if tp > 1 and n.endswith(("w_q.weight", "w_k.weight", "w_v.weight", "w1.weight", "w3.weight")):
+            k = r.shape[0] // tp
+            r = r[tp_rank * k:(tp_rank + 1) * k]
+        elif tp > 1 and n.endswith(("w_out.weight", "w2.weight")):
+            k = r.shape[1] // tp
+            r = r[:, tp_rank * k:(tp_rank + 1) * k]
+        if getattr(p, "_ep_sharded", False):
+            k = r.shape[0] // ep
+            r = r[ep_rank * k:(ep_rank + 1) * k]
+        err = float((g - r).abs().max() / (r.abs().max() + 1e-12)) if g.shape == r.shape else float("inf")
+        if err > 2e-3:
+            bad[n] = err
+    return bad
+
+
+@pytest.mark.parametrize("world,dims,moe,seq_par", [
+    (2, dict(tp_size=2), True, True),
+    (4, dict(ep_size=2, tp_size=2), True, True),
+    (4, dict(ep_size=2, tp_size=2), True, False),
+    (4, dict(cp_size=2, ep_size=2), True, False),
+    (4, dict(cp_size=2, tp_size=2), True, True),
+    (4, dict(cp_size=2), False, False),
+], ids=["tp2sp-moe", "ep2xtp2sp-moe", "ep2xtp2-moe", "cp2xep2-moe", "cp2xtp2sp-moe", "dp2xcp2-dense"])
+def test_applied_gradients_match_single_process(world, dims, moe, seq_par):
+    res = run_distributed(_worker, world, dims, moe, seq_par, timeout=300)
+    bad = {k: v for r in res for k, v in r.items()}
+    assert not bad, bad
