@@ -158,7 +158,9 @@ def run_deferred_wgrads(queue: list) -> None:
 
 def _wgrad_into(w: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor):
     """dW[N, K] = dy^T x, accumulated into ``w.main_grad`` when present; returns the autograd grad."""
-    if _DEFER is not None:
+    if _DEFER is not None and (w.is_leaf or hasattr(w, "main_grad")):
+        # a weight that is itself computed (two parameters concatenated for one GEMM) has no ``.grad`` to fill later:
+        # its gradient has to go back through autograd now, so only leaves and arena views are deferred
         _DEFER.append((w, dy2, x2))
         return None
     mg = getattr(w, "main_grad", None)

@@ -434,6 +434,9 @@ class Trainer:
         group = self.model._pp_group
         pp = dist.get_world_size(group)
         stages = list(self.model.stages) if hasattr(self.model, "stages") else [self.model]
+        # context parallelism inside the stages: every CP rank runs the pipeline on its share of each sequence
+        cp_group = getattr(stages[0], "_cp_group", None)
+        cp = dist.get_world_size(cp_group) if cp_group is not None else 1
         if self._pp_schedule is None:
             m = c.pp_microbatches or pp
             assert c.micro_batch_size % m == 0, "micro_batch_size must be a multiple of the pipeline microbatch count"
@@ -445,7 +448,7 @@ class Trainer:
             d_model = stages[0].d_model
             dtype = next(self.model.parameters()).dtype
             self._pp_schedule = PipelineSchedule(stages, group, cfg, num_microbatches=m,
-                                                 hidden_shape=(c.micro_batch_size // m, c.sequence_length, d_model),
+                                                 hidden_shape=(c.micro_batch_size // m, c.sequence_length // cp, d_model),
                                                  hidden_dtype=dtype)
         self.model.train()
         total = torch.zeros((), device=self.device)
@@ -455,12 +458,18 @@ class Trainer:
         for input_ids, labels in batches:
             input_ids = input_ids.to(self.device, non_blocking=True)
             labels = labels.to(self.device, non_blocking=True)
-            loss = self._pp_schedule.step(input_ids, target=labels)
+            kw = {}
+            if cp > 1:
+                from ..parallel.context_parallel import shard_batch_for_cp
+
+                input_ids, labels = shard_batch_for_cp(input_ids, labels, cp, dist.get_rank(cp_group))
+                kw["labels_shifted"] = True
+            loss = self._pp_schedule.step(input_ids, target=labels, **kw)
             if loss is not None:
                 total += loss.detach().float()
         total /= len(batches)
         if self._arena_opt:
-            self.optimizer.grad_divisor = float(len(batches))
+            self.optimizer.grad_divisor = float(len(batches)) / cp     # CP ranks hold shares of one gradient: summed
         elif len(batches) > 1:
             for p in self.model.parameters():
                 if p.grad is not None:

@@ -84,3 +84,85 @@ def test_applied_gradients_match_single_process(world, dims, moe, seq_par):
     res = run_distributed(_worker, world, dims, moe, seq_par, timeout=300)
     bad = {k: v for r in res for k, v in r.items()}
     assert not bad, bad
+
+
+def _pp_worker(rank, world, dims, moe, seq_par, schedule):
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.parallel.mesh import build_world_mesh, data_parallel_coords
+    from nanopysche_b200.parallel.tensor_parallel import TensorParallelConfig
+    from nanopysche_b200.parallel.context_parallel import ContextParallelConfig
+    from nanopysche_b200.parallel.pipeline_parallel import PipelineParallelConfig
+    from nanopysche_b200.parallelize import parallelize_model
+    from nanopysche_b200.train.trainer import Trainer, TrainingConfig
+    torch.manual_seed(0)
+    kw = dict(use_moe=True, num_experts=4, moe_top_k=2, moe_interval=2, moe_offset=1, moe_hidden=32,
+              moe_capacity_factor=None) if moe else {}
+    cfg = TransformerConfig(d_model=32, n_layers=4, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=32,
+                            ffn_hidden=64, qk_norm=False, **kw)
+    model = cfg.build()
+    ref = copy.deepcopy(model)
+    mesh = build_world_mesh(device_type="cpu", replace=True, **dims)
+    idx, cnt = data_parallel_coords(mesh)
+    torch.manual_seed(1)
+    M = 2
+    batches = [torch.randint(0, 64, (4, 16)) for _ in range(cnt)]
+    for b in batches:
+        for mb in b.chunk(M):
+            o = ref(mb, labels=mb)
+            ((o["loss"] + (o["aux_loss"] if o.get("aux_loss") is not None else 0)) / (cnt * M)).backward()
+    tp, cp, ep, pp = dims.get("tp_size", 1), dims.get("cp_size", 1), dims.get("ep_size", 1), dims.get("pp_size", 1)
+    model = parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"),
+                              pp_config=PipelineParallelConfig(pp, schedule=schedule, num_microbatches=M),
+                              tp_config=TensorParallelConfig(tp, sequence_parallel=seq_par) if tp > 1 else None,
+                              cp_config=ContextParallelConfig(cp) if cp > 1 else None)
+    opt = torch.optim.SGD(model.parameters(), lr=1.0)
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    mine = batches[idx]
+    class Loader:
+        def __iter__(self):
+            return iter([(mine, mine.clone())])
+    tc = TrainingConfig(global_batch_size=cnt * 4 * 16, micro_batch_size=4, sequence_length=16, max_steps=1,
+                        dtype=torch.float32, log_interval=0, save_interval=0, vocab_size=64, dp_world_size=cnt,
+                        max_grad_norm=0.0, cp_size=cp, pp_schedule=schedule, pp_microbatches=M)
+    Trainer(tc, model, opt, data_loader=Loader(), device=torch.device("cpu")).fit()
+    names = mesh.mesh_dim_names
+    tp_rank = mesh["tp"].get_local_rank() if "tp" in names else 0
+    ep_rank = mesh["ep"].get_local_rank() if "ep" in names else 0
+    rp = dict(ref.named_parameters())
+    bad = {}
+    for n, p in model.named_parameters():
+        key = n.split(".", 2)[2] if n.startswith("stages.") else n
+        if key not in rp:
+            bad[n] = "missing"
+            continue
+        g, r = before[n] - p.detach(), rp[key].grad
+        if tp > 1 and key.endswith(("w_q.weight", "w_k.weight", "w_v.weight", "w1.weight", "w3.weight")):
+            k = r.shape[0] // tp
+            r = r[tp_rank * k:(tp_rank + 1) * k]
+        elif tp > 1 and key.endswith(("w_out.weight", "w2.weight")):
+            k = r.shape[1] // tp
+            r = r[:, tp_rank * k:(tp_rank + 1) * k]
+        if getattr(p, "_ep_sharded", False):
+            k = r.shape[0] // ep
+            r = r[ep_rank * k:(ep_rank + 1) * k]
+        if g.shape != r.shape:
+            bad[n] = "shape"
+            continue
+        e = float((g - r).abs().max() / (r.abs().max() + 1e-12))
+        if e > 2e-3:
+            bad[n] = round(e, 4)
+    return bad
+
+
+@pytest.mark.parametrize("world,dims,moe,seq_par,schedule", [
+    (4, dict(pp_size=2, cp_size=2), False, False, "1F1B"),
+    (4, dict(pp_size=2, ep_size=2), True, False, "1F1B"),
+    (4, dict(pp_size=2, tp_size=2), True, True, "DualPipe"),
+    (4, dict(pp_size=2, ep_size=2), True, False, "DualPipe"),
+], ids=["pp2xcp2-dense-1f1b", "pp2xep2-moe-1f1b", "pp2xtp2sp-moe-dualpipe", "pp2xep2-moe-dualpipe"])
+def test_applied_gradients_match_single_process_under_pipelines(world, dims, moe, seq_par, schedule):
+    """The same check with a pipeline in the composition: the reference objective is the mean over micro-batches (and
+    data-parallel ranks) of each micro-batch's loss, as the schedule computes it."""
+    res = run_distributed(_pp_worker, world, dims, moe, seq_par, schedule, timeout=300)
+    bad = {k: v for r in res for k, v in r.items()}
+    assert not bad, bad
