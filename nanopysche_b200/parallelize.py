@@ -141,10 +141,33 @@ def parallelize_model(model: nn.Module, *, world_mesh, device: Optional[torch.de
             else:
                 model._replica_group = get_replica_group(world_mesh)   # read by engine.prepare_training
             model._needs_grad_sync = True
-        elif hasattr(model, "apply_fsdp"):
-            model.apply_fsdp(dp_mesh=dp_mesh, param_dtype=dp_config.param_dtype, reduce_dtype=dp_config.reduce_dtype)
         else:
-            apply_generic_fsdp(model, dp_mesh, dp_config)
+            if getattr(model, "_tp_sequence_parallel", False):
+                raise NotImplementedError(
+                    "sequence-parallel tensor parallelism (sequence_parallel / --async-tp) is not combined with PyTorch "
+                    "FSDP2: FSDP2 replaces the parameters, which drops the hooks that sum the partial gradients of "
+                    "norms, embeddings and MoE weights over the TP group. Use the arena backend "
+                    "(DataParallelConfig(backend=\"arena\"), the default on CUDA)")
+            # FSDP2 shards (and averages gradients) over the dp dims only. Expert-parallel peers read other batches
+            # and context-parallel peers other parts of each sequence, so the gradients still have to be combined over
+            # those dims: Trainer._sync_fsdp_extra_dims does it after the backward pass
+            names_ = tuple(world_mesh.mesh_dim_names or ()) if world_mesh is not None else ()
+            extra = {}
+            if MeshDimName.ep in names_ and world_mesh[MeshDimName.ep].size() > 1:
+                extra["ep"] = world_mesh[MeshDimName.ep].get_group()
+            if MeshDimName.cp in names_ and world_mesh[MeshDimName.cp].size() > 1:
+                extra["cp"] = world_mesh[MeshDimName.cp].get_group()
+            if hasattr(model, "apply_fsdp"):
+                model.apply_fsdp(dp_mesh=dp_mesh, param_dtype=dp_config.param_dtype,
+                                 reduce_dtype=dp_config.reduce_dtype)
+            else:
+                apply_generic_fsdp(model, dp_mesh, dp_config)
+            model._fsdp_extra_dims = extra
+            model._fsdp_enabled = True
+            # the group the parameter shards are spread over (dp_shard under HSDP): squared gradient norms add up over it
+            shard_dim = next((n for n in (MeshDimName.dp_shard, MeshDimName.dp) if n in names_), None)
+            model._fsdp_shard_group = world_mesh[shard_dim].get_group() if (
+                shard_dim is not None and world_mesh[shard_dim].size() > 1) else None
     if world_mesh is not None and ep_requested:
         # copies of one expert shard on ranks that read other batches (ep_size smaller than the data-parallel size)
         from .parallel.mesh import get_expert_replica_group

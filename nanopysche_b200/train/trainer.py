@@ -335,6 +335,9 @@ class Trainer:
                     grad_norm = clip_grad_norm_pp(params, c.max_grad_norm, getattr(self.model, "_pp_group", None),
                                                   copies=2 if getattr(self.model, "is_dualpipe", False) else 1,
                                                   ep_group=ep_group)
+                elif params and getattr(self.model, "_fsdp_extra_dims", None) is not None and dist.is_initialized() and (
+                        self.model._fsdp_extra_dims.get("ep") is not None or getattr(self.model, "_tp_enabled", False)):
+                    grad_norm = self._clip_fsdp_sharded(params, c.max_grad_norm)
                 elif params:
                     grad_norm = torch.nn.utils.clip_grad_norm_(params, c.max_grad_norm)
             self.optimizer.step()
@@ -393,6 +396,80 @@ class Trainer:
         if r is not None:
             r.finish()
         self._sync_expert_replicas()
+        self._sync_fsdp_extra_dims()
+
+    def _clip_fsdp_sharded(self, params, max_norm: float):
+        """Global-norm clipping of a PyTorch-FSDP2 model that also holds tensor-parallel or expert shards. FSDP2 replaces
+        the parameter objects, so the shard marks are read off the modules: squared norms of the local gradient shards
+        add up over the FSDP shard group; those of tensor-parallel weights also over the TP group and those of expert
+        shards over the EP group, on whose ranks everything else is identical. (``clip_grad_norm_`` alone gives every
+        rank a norm with only its own TP / expert shards in it, and the replicas drift apart.)"""
+        from ..models.attention import Attention
+        from ..models.feed_forward import FeedForward
+        from ..models.moe import MoEBase
+
+        expert_ids, tp_ids, tp_group = set(), set(), None
+        for m in self.model.modules():
+            if isinstance(m, MoEBase) and getattr(m.ep, "ep_size", 1) > 1:
+                expert_ids |= {id(m.w1), id(m.w2), id(m.w3)}
+            elif isinstance(m, (Attention, FeedForward)) and getattr(m, "_tp_size", 1) > 1:
+                tp_group = m._tp_group
+                for lin in ((m.w_q, m.w_k, m.w_v, m.w_out) if isinstance(m, Attention) else (m.w1, m.w3, m.w2)):
+                    tp_ids.add(id(lin.weight))
+                    if lin.bias is not None and lin not in (getattr(m, "w_out", None), getattr(m, "w2", None)):
+                        tp_ids.add(id(lin.bias))      # column-parallel biases are shards; row-parallel ones are whole
+
+        def local(g):
+            return g._local_tensor if hasattr(g, "_local_tensor") else g
+
+        t = torch.zeros(3, device=self.device, dtype=torch.float32)      # [whole, expert shards, TP shards]
+        for p in params:
+            k = 1 if id(p) in expert_ids else (2 if id(p) in tp_ids else 0)
+            t[k] += local(p.grad).detach().float().pow(2).sum()
+        shard_group = getattr(self.model, "_fsdp_shard_group", None)
+        if shard_group is not None:
+            dist.all_reduce(t, group=shard_group)
+        ep_group = self.model._fsdp_extra_dims.get("ep")
+        if ep_group is not None:
+            dist.all_reduce(t[1:2], group=ep_group)
+        if tp_group is not None:
+            dist.all_reduce(t[2:], group=tp_group)
+        total = t.sum().sqrt()
+        coef = (max_norm / (total + 1e-6)).clamp(max=1.0)
+        for p in params:
+            local(p.grad).mul_(coef.to(local(p.grad).dtype))
+        return total
+
+    def _sync_fsdp_extra_dims(self):
+        """PyTorch FSDP2 reduce-scatters (averages) over the dp dims only. With expert parallelism the EP peers read
+        other batches: gradients of everything but the expert shards are averaged over the EP group as well, and an
+        expert shard's gradient - a sum over its EP sources, each scaled by its own rank's mean - is divided by the EP
+        size so that every parameter ends up with the gradient of the mean over all ranks that read different batches.
+        With context parallelism every gradient is a partial sum over the CP group and is summed there."""
+        extra = getattr(self.model, "_fsdp_extra_dims", None)
+        if not extra or not getattr(self.model, "_fsdp_enabled", False):
+            return
+        from ..models.moe import MoEBase
+
+        expert_ids = set()
+        for m in self.model.modules():
+            if isinstance(m, MoEBase) and getattr(m.ep, "ep_size", 1) > 1:
+                expert_ids |= {id(m.w1), id(m.w2), id(m.w3)}
+
+        def local(g):
+            return g._local_tensor if hasattr(g, "_local_tensor") else g
+
+        ep_group, cp_group = extra.get("ep"), extra.get("cp")
+        for p in self.model.parameters():
+            if p.grad is None:
+                continue
+            g = local(p.grad)
+            if ep_group is not None:
+                if id(p) not in expert_ids:
+                    dist.all_reduce(g, group=ep_group)
+                g.div_(dist.get_world_size(ep_group))
+            if cp_group is not None:
+                dist.all_reduce(g, group=cp_group)
 
     def _sync_expert_replicas(self):
         """Expert shards are left out of the replica reduction above (every expert-parallel rank holds other experts).

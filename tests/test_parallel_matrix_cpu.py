@@ -166,3 +166,108 @@ def test_applied_gradients_match_single_process_under_pipelines(world, dims, moe
     res = run_distributed(_pp_worker, world, dims, moe, seq_par, schedule, timeout=300)
     bad = {k: v for r in res for k, v in r.items()}
     assert not bad, bad
+
+
+def _fsdp_worker(rank, world, dims, moe, seq_par, hsdp, clip):
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.parallel.fsdp import DataParallelConfig
+    from nanopysche_b200.parallel.mesh import build_world_mesh, data_parallel_coords
+    from nanopysche_b200.parallel.tensor_parallel import TensorParallelConfig
+    from nanopysche_b200.parallelize import parallelize_model
+    from nanopysche_b200.parallel.context_parallel import ContextParallelConfig
+    from nanopysche_b200.train.trainer import Trainer, TrainingConfig
+    torch.manual_seed(0)
+    kw = dict(use_moe=True, num_experts=4, moe_top_k=2, moe_interval=2, moe_offset=1, moe_hidden=32,
+              moe_capacity_factor=None) if moe else {}
+    cfg = TransformerConfig(d_model=32, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=32,
+                            ffn_hidden=64, qk_norm=False, **kw)
+    model = cfg.build()
+    ref = copy.deepcopy(model)
+    mesh = build_world_mesh(device_type="cpu", replace=True, **dims, **hsdp)
+    idx, cnt = data_parallel_coords(mesh)
+    torch.manual_seed(1)
+    batches = [torch.randint(0, 64, (2, 16)) for _ in range(cnt)]
+    for b in batches:
+        o = ref(b, labels=b)
+        ((o["loss"] + (o["aux_loss"] if o.get("aux_loss") is not None else 0)) / cnt).backward()
+    tp, ep = dims.get("tp_size", 1), dims.get("ep_size", 1)
+    model = parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"),
+                              tp_config=TensorParallelConfig(tp, sequence_parallel=seq_par) if tp > 1 else None,
+                              cp_config=ContextParallelConfig(dims.get("cp_size", 1)) if dims.get("cp_size", 1) > 1 else None,
+                              dp_config=DataParallelConfig(backend="torch", param_dtype=torch.float32))
+    CLIP = clip
+    if CLIP:
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), CLIP)
+    opt = torch.optim.SGD(model.parameters(), lr=1.0)
+    def full(p):
+        return p.full_tensor() if hasattr(p, "full_tensor") else p
+    before = {n: full(p.detach()).clone() for n, p in model.named_parameters()}
+    mine = batches[idx]
+    class Loader:
+        def __iter__(self):
+            return iter([(mine, mine.clone())])
+    tc = TrainingConfig(global_batch_size=cnt * 2 * 16, micro_batch_size=2, sequence_length=16, max_steps=1,
+                        dtype=torch.float32, log_interval=0, save_interval=0, vocab_size=64, dp_world_size=cnt,
+                        max_grad_norm=CLIP, cp_size=dims.get("cp_size", 1))
+    Trainer(tc, model, opt, data_loader=Loader(), device=torch.device("cpu")).fit()
+    names = mesh.mesh_dim_names
+    tp_rank = mesh["tp"].get_local_rank() if "tp" in names else 0
+    ep_rank = mesh["ep"].get_local_rank() if "ep" in names else 0
+    rp = dict(ref.named_parameters())
+    bad = {}
+    for n, p in model.named_parameters():
+        g, r = before[n] - full(p.detach()), rp[n].grad
+        if tp > 1 and n.endswith(("w_q.weight", "w_k.weight", "w_v.weight", "w1.weight", "w3.weight")):
+            k = r.shape[0] // tp
+            r = r[tp_rank * k:(tp_rank + 1) * k]
+        elif tp > 1 and n.endswith(("w_out.weight", "w2.weight")):
+            k = r.shape[1] // tp
+            r = r[:, tp_rank * k:(tp_rank + 1) * k]
+        if ".moe.w" in n and ep > 1:
+            k = r.shape[0] // ep
+            r = r[ep_rank * k:(ep_rank + 1) * k]
+        if g.shape != r.shape:
+            bad[n] = ("shape", tuple(g.shape), tuple(r.shape))
+            continue
+        e = float((g - r).abs().max() / (r.abs().max() + 1e-12))
+        if e > 2e-3:
+            bad[n] = round(e, 4)
+    return bad
+
+
+@pytest.mark.parametrize("world,dims,moe,hsdp", [
+    (4, dict(tp_size=2), False, {}),
+    (4, dict(ep_size=2), True, {}),
+    (4, dict(cp_size=2), False, {}),
+    (4, {}, False, dict(dp_replicate=2, dp_shard=2)),
+], ids=["fsdp2xtp2", "fsdp2xep2-moe", "fsdp2xcp2", "hsdp2x2"])
+def test_applied_gradients_match_single_process_under_torch_fsdp2(world, dims, moe, hsdp):
+    """PyTorch FSDP2 (the reference's data-parallel mechanism) shards and averages over the dp dims only; the Trainer
+    combines the gradients over the EP / CP dims afterwards and clips with one norm over TP, expert and FSDP shards.
+    One clipped SGD step against the clipped single-process gradient."""
+    res = run_distributed(_fsdp_worker, world, dims, moe, False, hsdp, 0.05, timeout=300)
+    bad = {k: v for r in res for k, v in r.items()}
+    assert not bad, bad
+
+
+def _sp_fsdp_refusal_worker(rank, world):
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.parallel.fsdp import DataParallelConfig
+    from nanopysche_b200.parallel.mesh import build_world_mesh
+    from nanopysche_b200.parallel.tensor_parallel import TensorParallelConfig
+    from nanopysche_b200.parallelize import parallelize_model
+
+    model = TransformerConfig(d_model=32, n_layers=1, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=16,
+                              ffn_hidden=64, qk_norm=False).build()
+    mesh = build_world_mesh(tp_size=2, device_type="cpu", replace=True)
+    try:
+        parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"),
+                          tp_config=TensorParallelConfig(2, sequence_parallel=True),
+                          dp_config=DataParallelConfig(backend="torch"))
+    except NotImplementedError as e:
+        return "FSDP2" in str(e)
+    return False
+
+
+def test_sequence_parallel_with_torch_fsdp2_is_refused():
+    assert all(run_distributed(_sp_fsdp_refusal_worker, 2))
