@@ -148,12 +148,13 @@ class defer_wgrad:
 def run_deferred_wgrads(queue: list) -> None:
     """The W step: run the queued weight-gradient GEMMs (into ``main_grad`` when the weight has one, else into
     ``.grad``) and release the saved activations."""
-    while queue:
-        w, dy2, x2 = queue.pop(0)
-        g = _wgrad_into(w, dy2, x2)
-        if g is not None:
-            g = g.to(w.dtype)
-            w.grad = g if w.grad is None else w.grad + g
+    with torch.no_grad():      # like the backward pass these GEMMs were taken out of: nothing here is differentiated
+        while queue:
+            w, dy2, x2 = queue.pop(0)
+            g = _wgrad_into(w, dy2, x2)
+            if g is not None:
+                g = g.to(w.dtype)
+                w.grad = g if w.grad is None else w.grad + g
 
 
 def _wgrad_into(w: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor):

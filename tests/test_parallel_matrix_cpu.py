@@ -271,3 +271,94 @@ def _sp_fsdp_refusal_worker(rank, world):
 
 def test_sequence_parallel_with_torch_fsdp2_is_refused():
     assert all(run_distributed(_sp_fsdp_refusal_worker, 2))
+
+
+def _pp_arena_worker(rank, world, dims, moe, seq_par, schedule):
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.parallel.mesh import build_world_mesh, data_parallel_coords
+    from nanopysche_b200.parallel.tensor_parallel import TensorParallelConfig
+    from nanopysche_b200.parallel.context_parallel import ContextParallelConfig
+    from nanopysche_b200.parallel.pipeline_parallel import PipelineParallelConfig
+    from nanopysche_b200.parallelize import parallelize_model
+    from nanopysche_b200.train.trainer import Trainer, TrainingConfig
+    torch.manual_seed(0)
+    kw = dict(use_moe=True, num_experts=4, moe_top_k=2, moe_interval=2, moe_offset=1, moe_hidden=32,
+              moe_capacity_factor=None) if moe else {}
+    cfg = TransformerConfig(d_model=32, n_layers=4, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=32,
+                            ffn_hidden=64, qk_norm=False, **kw)
+    model = cfg.build()
+    ref = copy.deepcopy(model)
+    mesh = build_world_mesh(device_type="cpu", replace=True, **dims)
+    idx, cnt = data_parallel_coords(mesh)
+    torch.manual_seed(1)
+    M = 2
+    batches = [torch.randint(0, 64, (4, 16)) for _ in range(cnt)]
+    from nanopysche_b200.optim.arena import ArenaAdamW, ParamArena
+    a0 = ParamArena(ref, device=torch.device("cpu"))
+    o0 = ArenaAdamW(a0, lr=1e-2, weight_decay=0.1, max_grad_norm=0.05)
+    for b in batches:
+        for mb in b.chunk(M):
+            o = ref(mb, labels=mb)
+            ((o["loss"] + (o["aux_loss"] if o.get("aux_loss") is not None else 0)) / (cnt * M)).backward()
+    o0.step()
+    tp, cp, ep, pp = dims.get("tp_size", 1), dims.get("cp_size", 1), dims.get("ep_size", 1), dims.get("pp_size", 1)
+    model = parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"),
+                              pp_config=PipelineParallelConfig(pp, schedule=schedule, num_microbatches=M),
+                              tp_config=TensorParallelConfig(tp, sequence_parallel=seq_par) if tp > 1 else None,
+                              cp_config=ContextParallelConfig(cp) if cp > 1 else None)
+    arena = ParamArena(model, dp_group=getattr(model, "_replica_group", None), device=torch.device("cpu"),
+                       expert_replica_group=getattr(model, "_expert_replica_group", None))
+    opt = ArenaAdamW(arena, lr=1e-2, weight_decay=0.1, max_grad_norm=0.05)
+    opt.norm_groups = [model._pp_group]
+    opt.norm_copies = 2.0 if getattr(model, "is_dualpipe", False) else 1.0
+    mine = batches[idx]
+    class Loader:
+        def __iter__(self):
+            return iter([(mine, mine.clone())])
+    tc = TrainingConfig(global_batch_size=cnt * 4 * 16, micro_batch_size=4, sequence_length=16, max_steps=1,
+                        dtype=torch.float32, log_interval=0, save_interval=0, vocab_size=64, dp_world_size=cnt,
+                        max_grad_norm=0.05, cp_size=cp, pp_schedule=schedule, pp_microbatches=M)
+    Trainer(tc, model, opt, data_loader=Loader(), device=torch.device("cpu")).fit()
+    names = mesh.mesh_dim_names
+    tp_rank = mesh["tp"].get_local_rank() if "tp" in names else 0
+    ep_rank = mesh["ep"].get_local_rank() if "ep" in names else 0
+    rp = dict(ref.named_parameters())
+    bad = {}
+    gn = (float(opt.last_grad_norm), float(o0.last_grad_norm))
+    if abs(gn[0] - gn[1]) > 1e-3 * gn[1]:
+        bad["grad_norm"] = gn
+    for n, p in model.named_parameters():
+        key = n.split(".", 2)[2] if n.startswith("stages.") else n
+        if key not in rp:
+            bad[n] = "missing"
+            continue
+        g, r = p.detach(), rp[key].detach()
+        if tp > 1 and key.endswith(("w_q.weight", "w_k.weight", "w_v.weight", "w1.weight", "w3.weight")):
+            k = r.shape[0] // tp
+            r = r[tp_rank * k:(tp_rank + 1) * k]
+        elif tp > 1 and key.endswith(("w_out.weight", "w2.weight")):
+            k = r.shape[1] // tp
+            r = r[:, tp_rank * k:(tp_rank + 1) * k]
+        if getattr(p, "_ep_sharded", False):
+            k = r.shape[0] // ep
+            r = r[ep_rank * k:(ep_rank + 1) * k]
+        if g.shape != r.shape:
+            bad[n] = "shape"
+            continue
+        e = float((g - r).abs().max())
+        if e > 5e-5:
+            bad[n] = round(e, 6)
+    return bad
+
+
+@pytest.mark.parametrize("world,dims,moe,seq_par,schedule", [
+    (4, dict(pp_size=2), False, False, "ZBVZeroBubble"),
+    (4, dict(pp_size=2, tp_size=2), True, True, "DualPipe"),
+], ids=["pp2xdp2-dense-zbv-arena", "pp2xtp2sp-moe-dualpipe-arena"])
+def test_arena_optimizer_under_pipelines_matches_single_process(world, dims, moe, seq_par, schedule):
+    """The parameter arena (CPU reference path of the fused optimizer) behind pipeline schedules with deferred
+    weight-gradient GEMMs: clipping norm over all stages (``norm_groups``, DualPipe's twin copies counted once) and the
+    weights after one clipped AdamW step equal the single-process arena step."""
+    res = run_distributed(_pp_arena_worker, world, dims, moe, seq_par, schedule, timeout=300)
+    bad = {k: v for r in res for k, v in r.items()}
+    assert not bad, bad
