@@ -320,9 +320,22 @@ def _pp_worker(rank, world, schedule):
     return True
 
 
-@pytest.mark.parametrize("schedule", ["1F1B", "GPipe", "InterleavedZeroBubble", "Interleaved1F1B", "ZBVZeroBubble"])
-def test_pipeline_runtime_matches_single_process(schedule):
-    assert all(run_distributed(_pp_worker, 2, schedule))
+def _pp_worker_all(rank, world, schedules):
+    from nanopysche_b200.ops import gemm as gemm_ops
+
+    for sch in schedules:      # one pair of ranks for all schedules: spawning costs more than a schedule's step
+        try:
+            assert _pp_worker(rank, world, sch)
+        except AssertionError as e:
+            raise AssertionError(f"schedule {sch}: {e}") from e
+        gemm_ops.SPLIT_MODE = False
+        dist.barrier()
+    return True
+
+
+def test_pipeline_runtime_matches_single_process():
+    schedules = ["1F1B", "GPipe", "InterleavedZeroBubble", "Interleaved1F1B", "ZBVZeroBubble", "LoopedBFS"]
+    assert all(run_distributed(_pp_worker_all, 2, schedules, timeout=600))
 
 
 def _fsdp_worker(rank, world):
@@ -490,9 +503,15 @@ def _hsdp_worker(rank, world, backend):
     return True
 
 
-@pytest.mark.parametrize("backend", ["torch", "arena"])
-def test_hybrid_sharded_data_parallel_four_ranks(backend):
-    assert all(run_distributed(_hsdp_worker, 4, backend))
+def _hsdp_both(rank, world):
+    for backend in ("torch", "arena"):
+        assert _hsdp_worker(rank, world, backend), backend
+        dist.barrier()
+    return True
+
+
+def test_hybrid_sharded_data_parallel_four_ranks():
+    assert all(run_distributed(_hsdp_both, 4, timeout=600))
 
 
 def _seq_parallel_worker(rank, world):

@@ -72,18 +72,34 @@ def _worker(rank, world, dims, moe, seq_par):
     return bad
 
 
-@pytest.mark.parametrize("world,dims,moe,seq_par", [
-    (2, dict(tp_size=2), True, True),
-    (4, dict(ep_size=2, tp_size=2), True, True),
-    (4, dict(ep_size=2, tp_size=2), True, False),
-    (4, dict(cp_size=2, ep_size=2), True, False),
-    (4, dict(cp_size=2, tp_size=2), True, True),
-    (4, dict(cp_size=2), False, False),
-], ids=["tp2sp-moe", "ep2xtp2sp-moe", "ep2xtp2-moe", "cp2xep2-moe", "cp2xtp2sp-moe", "dp2xcp2-dense"])
-def test_applied_gradients_match_single_process(world, dims, moe, seq_par):
-    res = run_distributed(_worker, world, dims, moe, seq_par, timeout=300)
-    bad = {k: v for r in res for k, v in r.items()}
+def _many(rank, world, fn, cases):
+    """Run several compositions inside one set of ranks (each builds its own mesh): spawning ranks costs more than a
+    case does. Returns ``{case id: mismatches}`` for the cases that did not match."""
+    out = {}
+    for cid, args in cases:
+        bad = fn(rank, world, *args)
+        if bad:
+            out[cid] = bad
+        dist.barrier()
+    return out
+
+
+def _check(res):
+    bad = {}
+    for r in res:
+        for cid, b in r.items():
+            bad.setdefault(cid, {}).update(b)
     assert not bad, bad
+
+
+def test_applied_gradients_match_single_process():
+    cases = [("dp2xtp2sp-moe", (dict(tp_size=2), True, True)),
+             ("ep2xtp2sp-moe", (dict(ep_size=2, tp_size=2), True, True)),
+             ("ep2xtp2-moe", (dict(ep_size=2, tp_size=2), True, False)),
+             ("cp2xep2-moe", (dict(cp_size=2, ep_size=2), True, False)),
+             ("cp2xtp2sp-moe", (dict(cp_size=2, tp_size=2), True, True)),
+             ("dp2xcp2-dense", (dict(cp_size=2), False, False))]
+    _check(run_distributed(_many, 4, _worker, cases, timeout=600))
 
 
 def _pp_worker(rank, world, dims, moe, seq_par, schedule):
@@ -154,18 +170,14 @@ def _pp_worker(rank, world, dims, moe, seq_par, schedule):
     return bad
 
 
-@pytest.mark.parametrize("world,dims,moe,seq_par,schedule", [
-    (4, dict(pp_size=2, cp_size=2), False, False, "1F1B"),
-    (4, dict(pp_size=2, ep_size=2), True, False, "1F1B"),
-    (4, dict(pp_size=2, tp_size=2), True, True, "DualPipe"),
-    (4, dict(pp_size=2, ep_size=2), True, False, "DualPipe"),
-], ids=["pp2xcp2-dense-1f1b", "pp2xep2-moe-1f1b", "pp2xtp2sp-moe-dualpipe", "pp2xep2-moe-dualpipe"])
-def test_applied_gradients_match_single_process_under_pipelines(world, dims, moe, seq_par, schedule):
+def test_applied_gradients_match_single_process_under_pipelines():
     """The same check with a pipeline in the composition: the reference objective is the mean over micro-batches (and
     data-parallel ranks) of each micro-batch's loss, as the schedule computes it."""
-    res = run_distributed(_pp_worker, world, dims, moe, seq_par, schedule, timeout=300)
-    bad = {k: v for r in res for k, v in r.items()}
-    assert not bad, bad
+    cases = [("pp2xcp2-dense-1f1b", (dict(pp_size=2, cp_size=2), False, False, "1F1B")),
+             ("pp2xep2-moe-1f1b", (dict(pp_size=2, ep_size=2), True, False, "1F1B")),
+             ("pp2xtp2sp-moe-dualpipe", (dict(pp_size=2, tp_size=2), True, True, "DualPipe")),
+             ("pp2xep2-moe-dualpipe", (dict(pp_size=2, ep_size=2), True, False, "DualPipe"))]
+    _check(run_distributed(_many, 4, _pp_worker, cases, timeout=600))
 
 
 def _fsdp_worker(rank, world, dims, moe, seq_par, hsdp, clip):
@@ -235,19 +247,15 @@ def _fsdp_worker(rank, world, dims, moe, seq_par, hsdp, clip):
     return bad
 
 
-@pytest.mark.parametrize("world,dims,moe,hsdp", [
-    (4, dict(tp_size=2), False, {}),
-    (4, dict(ep_size=2), True, {}),
-    (4, dict(cp_size=2), False, {}),
-    (4, {}, False, dict(dp_replicate=2, dp_shard=2)),
-], ids=["fsdp2xtp2", "fsdp2xep2-moe", "fsdp2xcp2", "hsdp2x2"])
-def test_applied_gradients_match_single_process_under_torch_fsdp2(world, dims, moe, hsdp):
+def test_applied_gradients_match_single_process_under_torch_fsdp2():
     """PyTorch FSDP2 (the reference's data-parallel mechanism) shards and averages over the dp dims only; the Trainer
     combines the gradients over the EP / CP dims afterwards and clips with one norm over TP, expert and FSDP shards.
     One clipped SGD step against the clipped single-process gradient."""
-    res = run_distributed(_fsdp_worker, world, dims, moe, False, hsdp, 0.05, timeout=300)
-    bad = {k: v for r in res for k, v in r.items()}
-    assert not bad, bad
+    cases = [("fsdp2xtp2", (dict(tp_size=2), False, False, {}, 0.05)),
+             ("fsdp2xep2-moe", (dict(ep_size=2), True, False, {}, 0.05)),
+             ("fsdp2xcp2", (dict(cp_size=2), False, False, {}, 0.05)),
+             ("hsdp2x2", ({}, False, False, dict(dp_replicate=2, dp_shard=2), 0.05))]
+    _check(run_distributed(_many, 4, _fsdp_worker, cases, timeout=600))
 
 
 def _sp_fsdp_refusal_worker(rank, world):
@@ -351,14 +359,10 @@ def _pp_arena_worker(rank, world, dims, moe, seq_par, schedule):
     return bad
 
 
-@pytest.mark.parametrize("world,dims,moe,seq_par,schedule", [
-    (4, dict(pp_size=2), False, False, "ZBVZeroBubble"),
-    (4, dict(pp_size=2, tp_size=2), True, True, "DualPipe"),
-], ids=["pp2xdp2-dense-zbv-arena", "pp2xtp2sp-moe-dualpipe-arena"])
-def test_arena_optimizer_under_pipelines_matches_single_process(world, dims, moe, seq_par, schedule):
+def test_arena_optimizer_under_pipelines_matches_single_process():
     """The parameter arena (CPU reference path of the fused optimizer) behind pipeline schedules with deferred
     weight-gradient GEMMs: clipping norm over all stages (``norm_groups``, DualPipe's twin copies counted once) and the
     weights after one clipped AdamW step equal the single-process arena step."""
-    res = run_distributed(_pp_arena_worker, world, dims, moe, seq_par, schedule, timeout=300)
-    bad = {k: v for r in res for k, v in r.items()}
-    assert not bad, bad
+    cases = [("pp2xdp2-dense-zbv-arena", (dict(pp_size=2), False, False, "ZBVZeroBubble")),
+             ("pp2xtp2sp-moe-dualpipe-arena", (dict(pp_size=2, tp_size=2), True, True, "DualPipe"))]
+    _check(run_distributed(_many, 4, _pp_arena_worker, cases, timeout=600))

@@ -87,10 +87,23 @@ def _pp_trainer_worker(rank, world, schedule):
     return True
 
 
-@pytest.mark.parametrize("schedule", ["1F1B", "GPipe", "DualPipe", "ZBVZeroBubble", "InterleavedZeroBubble",
-                                      "Interleaved1F1B", "LoopedBFS"])
-def test_trainer_runs_pipeline_stages(schedule):
-    assert all(run_distributed(_pp_trainer_worker, 2, schedule))
+def _pp_trainer_all(rank, world, schedules):
+    """All schedules inside one pair of ranks (spawning ranks costs more than a schedule's three steps)."""
+    from nanopysche_b200.ops import gemm as gemm_ops
+
+    for sch in schedules:
+        try:
+            assert _pp_trainer_worker(rank, world, sch)
+        except AssertionError as e:
+            raise AssertionError(f"schedule {sch}: {e}") from e
+        gemm_ops.SPLIT_MODE = False        # set by schedules with a B / W split; the next schedule decides for itself
+        dist.barrier()
+    return True
+
+
+def test_trainer_runs_pipeline_stages():
+    schedules = ["1F1B", "GPipe", "DualPipe", "ZBVZeroBubble", "InterleavedZeroBubble", "Interleaved1F1B", "LoopedBFS"]
+    assert all(run_distributed(_pp_trainer_all, 2, schedules, timeout=600))
 
 
 def _pp_tp_worker(rank, world, seq_par=False):
@@ -206,18 +219,28 @@ def _pp_tp_ep_worker(rank, world, seq_par=False):
     return [float(x) for x in got], ref_losses, ep_rank
 
 
-@pytest.mark.parametrize("seq_par", [False, True])
-def test_dualpipe_times_expert_parallel_times_tensor_parallel_eight_ranks(seq_par):
-    """``seq_par``: the configuration of the 7B hybrid run with ``--async-tp`` - every stage works on row shards, so a
-    MoE layer routes this rank's half of the tokens and the router's gradient is partial over the TP group."""
-    res = run_distributed(_pp_tp_ep_worker, 8, seq_par, timeout=600)
-    ref_losses = res[0][1]
-    for step in range(2):
-        by_ep = {}
-        for losses, _, ep in res:
-            by_ep.setdefault(ep, losses[step])
-        mean = sum(by_ep.values()) / len(by_ep)
-        assert mean == pytest.approx(ref_losses[step], rel=5e-3), (step, by_ep, ref_losses)
+def _pp_tp_ep_both(rank, world):
+    out = []
+    for seq_par in (False, True):
+        out.append(_pp_tp_ep_worker(rank, world, seq_par))
+        dist.barrier()
+    return out
+
+
+def test_dualpipe_times_expert_parallel_times_tensor_parallel_eight_ranks():
+    """Both tensor-parallel layouts in one set of eight ranks. Sequence-parallel: the configuration of the 7B hybrid
+    run with ``--async-tp`` - every stage works on row shards, so a MoE layer routes this rank's half of the tokens and
+    the router's gradient is partial over the TP group."""
+    both = run_distributed(_pp_tp_ep_both, 8, timeout=600)
+    for variant in range(2):
+        res = [r[variant] for r in both]
+        ref_losses = res[0][1]
+        for step in range(2):
+            by_ep = {}
+            for losses, _, ep in res:
+                by_ep.setdefault(ep, losses[step])
+            mean = sum(by_ep.values()) / len(by_ep)
+            assert mean == pytest.approx(ref_losses[step], rel=5e-3), (variant, step, by_ep, ref_losses)
 
 
 def _ep_dp_worker(rank, world, use_arena):
@@ -284,10 +307,19 @@ def _ep_dp_worker(rank, world, use_arena):
     return [float(x) for x in got], ref_losses
 
 
-@pytest.mark.parametrize("use_arena", [False, True])
-def test_expert_replicas_across_data_parallel_ranks(use_arena):
-    res = run_distributed(_ep_dp_worker, 4, use_arena, timeout=600)
-    ref_losses = res[0][1]
-    for step in range(3):
-        mean = sum(r[0][step] for r in res) / len(res)
-        assert mean == pytest.approx(ref_losses[step], rel=2e-3), (step, [r[0][step] for r in res], ref_losses)
+def _ep_dp_both(rank, world):
+    out = []
+    for use_arena in (False, True):
+        out.append(_ep_dp_worker(rank, world, use_arena))
+        dist.barrier()
+    return out
+
+
+def test_expert_replicas_across_data_parallel_ranks():
+    both = run_distributed(_ep_dp_both, 4, timeout=600)
+    for variant in range(2):        # plain optimizer, parameter arena
+        res = [r[variant] for r in both]
+        ref_losses = res[0][1]
+        for step in range(3):
+            mean = sum(r[0][step] for r in res) / len(res)
+            assert mean == pytest.approx(ref_losses[step], rel=2e-3), (variant, step, [r[0][step] for r in res])
