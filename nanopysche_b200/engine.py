@@ -62,6 +62,11 @@ def prepare_training(model: nn.Module, *, tokens_per_rank: Optional[int] = None,
     opt = ArenaAdamW(arena, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, max_grad_norm=max_grad_norm)
     rt = getattr(moes[0], "_fused_runtime", None) if moes else None
     if rt is not None:
+        # ranks outside the expert-parallel group that hold the same layers and route other tokens: copies of the
+        # expert shards on other data-parallel ranks (incl. context-parallel peers) and, under sequence-parallel TP,
+        # the TP peers. Their load counts belong to the same DeepSeek-V3 bias update.
+        rt.extra_count_groups = [g for g in (getattr(model, "_expert_replica_group", None),
+                                             getattr(moes[0].router, "_sp_group", None)) if g is not None]
         if rt.score_bias_all is not None:
             opt.post_step_hooks.append(rt.update_router_bias)
         opt.post_step_hooks.append(rt.end_step)

@@ -203,13 +203,21 @@ class MoERouter(nn.Module):
         self._total_tokens_this_batch += indices.numel()
 
     @torch.no_grad()
-    def post_batch(self, group=None) -> None:
-        """DeepSeek-V3 bias update, once per step: ``bias += sign * gamma * (load_fraction - 1/E)``."""
+    def post_batch(self, group=None, *, groups=None) -> None:
+        """DeepSeek-V3 bias update, once per step: ``bias += sign * gamma * (load_fraction - 1/E)``. The token counts
+        are summed over ``group`` (default: all ranks) or, with ``groups`` given, over each group of that list in turn
+        (an empty list: no reduction). Only ranks that hold *this* layer and route other tokens belong there - the
+        replica group, plus the TP group under sequence parallelism; a reduction over all ranks of a pipelined job
+        would pair this layer's counts with another stage's layer."""
         if self.score_bias is None or getattr(self, "_device_side_update", False):
             return  # no bias, or the fused runtime updates all layers on the device (ops.moe.update_router_bias)
         if dist.is_available() and dist.is_initialized():
             packed = torch.cat([self._tokens_per_expert_this_batch, self._total_tokens_this_batch.reshape(1)])
-            dist.all_reduce(packed, group=group)
+            if groups is None:
+                dist.all_reduce(packed, group=group)
+            else:
+                for g in groups:
+                    dist.all_reduce(packed, group=g)
             self._tokens_per_expert_this_batch.copy_(packed[:-1])
             self._total_tokens_this_batch.copy_(packed[-1])
         total = self._total_tokens_this_batch.float().clamp_min(1.0)

@@ -168,6 +168,7 @@ class FusedMoERuntime:
         h.reserve_allreduce(max(64, n_layers * num_experts))
         self.bias_counts = torch.zeros((n_layers, num_experts), device=self.device, dtype=torch.float32)
         self.score_bias_all: Optional[torch.Tensor] = None
+        self.extra_count_groups: list = []   # process groups whose ranks' load counts join the bias update
         self.bias_coef = 0.0
         if self.N > 1:
             torch.cuda.synchronize()
@@ -204,6 +205,14 @@ class FusedMoERuntime:
         c = self.bias_counts
         if self.N > 1:
             self.heap.all_reduce_(c.view(-1))
+        # other ranks that hold the same layers and route other tokens (data-parallel copies of the expert shards,
+        # context-parallel peers, TP peers under sequence parallelism): set by engine.prepare_training, empty for
+        # expert parallelism over all ranks, where the step stays free of library collectives
+        if self.extra_count_groups:
+            import torch.distributed as dist
+
+            for g in self.extra_count_groups:
+                dist.all_reduce(c, group=g)
         tot = c.sum(dim=1, keepdim=True).clamp_min_(1.0)
         self.score_bias_all.add_((c / tot).sub_(1.0 / self.E), alpha=self.bias_coef)
         c.zero_()

@@ -229,6 +229,43 @@ def sync_twin_grads(stages: Sequence[nn.Module], group, grad_of=None) -> None:
         off += g.numel()
 
 
+def sync_twin_router_counts(stages: Sequence[nn.Module], group) -> None:
+    """DualPipe: the two copies of a stage each route half of the micro-batches, so the per-step load counts of their
+    routers (the input of the DeepSeek-V3 bias update) are halves as well. Exchange and add them with the mirror rank,
+    in stage order, so that both copies update their biases from the whole step and stay identical."""
+    p, r = dist.get_world_size(group), dist.get_rank(group)
+    partner = p - 1 - r
+    order = sorted(stages, key=lambda st: st._stage_id)
+
+    def counters(st):
+        out = []
+        for m in st.modules():
+            if hasattr(m, "_tokens_per_expert_this_batch") and getattr(m, "score_bias", None) is not None:
+                out += [m._tokens_per_expert_this_batch, m._total_tokens_this_batch]
+        return out
+
+    if partner == r:                       # odd p, middle rank: both copies are local
+        for a, b in zip(counters(stages[0]), counters(stages[1])):
+            tot = a + b
+            a.copy_(tot)
+            b.copy_(tot)
+        return
+    bufs = [c for st in order for c in counters(st)]
+    if not bufs:
+        return
+    flat = torch.cat([c.reshape(-1).to(torch.float64) for c in bufs])
+    other = torch.empty_like(flat)
+    peer = dist.get_global_rank(group, partner)
+    for w in dist.batch_isend_irecv([dist.P2POp(dist.isend, flat, peer, group=group),
+                                     dist.P2POp(dist.irecv, other, peer, group=group)]):
+        w.wait()
+    flat += other
+    off = 0
+    for c in bufs:
+        c.copy_(flat[off:off + c.numel()].view_as(c).to(c.dtype))
+        off += c.numel()
+
+
 # ------------------------------------------------------------------ executor
 class _P2PTransport:
     """How the executor moves a message: ``batch_isend_irecv`` on the channel's communicator. The executor talks to

@@ -497,9 +497,17 @@ class Trainer:
                 p.grad.div_(n_data)
 
     def _post_batch_hooks(self):
+        """Per-step router updates (DeepSeek-V3 bias). A model that went through ``parallelize_model`` says which ranks
+        hold the same layers and route other tokens (its replica group; under sequence-parallel TP also the TP group):
+        the load counts are summed over exactly those. Any other model keeps the plain all-rank sum."""
+        scoped = hasattr(self.model, "_replica_group") and dist.is_available() and dist.is_initialized()
+        rep = getattr(self.model, "_replica_group", None)
         for m in self.model.modules():
             if hasattr(m, "post_batch") and hasattr(m, "score_bias"):
-                m.post_batch()
+                if scoped:
+                    m.post_batch(groups=[g for g in (rep, getattr(m, "_sp_group", None)) if g is not None])
+                else:
+                    m.post_batch()
 
     def _pipeline_step(self, batches):
         """One optimizer step of a pipeline stage: every batch runs through this rank's action list of the
@@ -552,10 +560,11 @@ class Trainer:
                 if p.grad is not None:
                     p.grad.div_(len(batches))
         if getattr(self.model, "is_dualpipe", False):
-            from ..parallel.pipeline_runtime import sync_twin_grads
+            from ..parallel.pipeline_runtime import sync_twin_grads, sync_twin_router_counts
 
             sync_twin_grads(stages, group, grad_of=(lambda q: getattr(q, "main_grad", None)) if self._arena_opt
                             else None)
+            sync_twin_router_counts(stages, group)
             # the loss lives on the last stage of each direction: ranks p-1 (even microbatches) and 0 (odd ones)
             both = total.clone() if self._pp_schedule.rank in (0, pp - 1) else torch.zeros_like(total)
             dist.all_reduce(both, group=group)

@@ -22,7 +22,7 @@ def _worker(rank, world, dims, moe, seq_par):
 
     torch.manual_seed(0)
     kw = dict(use_moe=True, num_experts=4, moe_top_k=2, moe_interval=2, moe_offset=1, moe_hidden=32,
-              moe_capacity_factor=None) if moe else {}
+              moe_capacity_factor=None, moe_bias_gamma=1e-2) if moe else {}
     cfg = TransformerConfig(d_model=32, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=32,
                             ffn_hidden=64, qk_norm=False, **kw)
     model = cfg.build()
@@ -69,7 +69,26 @@ def _worker(rank, world, dims, moe, seq_par):
         err = float((g - r).abs().max() / (r.abs().max() + 1e-12)) if g.shape == r.shape else float("inf")
         if err > 2e-3:
             bad[n] = err
+    _ref_bias_update(ref)
+    _check_biases(model, ref, bad)
     return bad
+
+
+def _ref_bias_update(ref):
+    """The single-process model's DeepSeek-V3 bias update from the counts of everything it routed."""
+    for m in ref.modules():
+        if hasattr(m, "post_batch") and hasattr(m, "score_bias") and m.score_bias is not None:
+            m.post_batch(groups=[])
+
+
+def _check_biases(model, ref, bad):
+    rb = {n: b for n, b in ref.named_buffers() if n.endswith("score_bias")}
+    for n, b in model.named_buffers():
+        if n.endswith("score_bias"):
+            key = n.split(".", 2)[2] if n.startswith("stages.") else n
+            key = key.replace(".module.", ".")
+            if not torch.allclose(b, rb[key], atol=1e-7):
+                bad[n] = ("score_bias", float((b - rb[key]).abs().max()))
 
 
 def _many(rank, world, fn, cases):
@@ -112,7 +131,7 @@ def _pp_worker(rank, world, dims, moe, seq_par, schedule):
     from nanopysche_b200.train.trainer import Trainer, TrainingConfig
     torch.manual_seed(0)
     kw = dict(use_moe=True, num_experts=4, moe_top_k=2, moe_interval=2, moe_offset=1, moe_hidden=32,
-              moe_capacity_factor=None) if moe else {}
+              moe_capacity_factor=None, moe_bias_gamma=1e-2) if moe else {}
     cfg = TransformerConfig(d_model=32, n_layers=4, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=32,
                             ffn_hidden=64, qk_norm=False, **kw)
     model = cfg.build()
@@ -167,6 +186,8 @@ def _pp_worker(rank, world, dims, moe, seq_par, schedule):
         e = float((g - r).abs().max() / (r.abs().max() + 1e-12))
         if e > 2e-3:
             bad[n] = round(e, 4)
+    _ref_bias_update(ref)
+    _check_biases(model, ref, bad)
     return bad
 
 
@@ -190,7 +211,7 @@ def _fsdp_worker(rank, world, dims, moe, seq_par, hsdp, clip):
     from nanopysche_b200.train.trainer import Trainer, TrainingConfig
     torch.manual_seed(0)
     kw = dict(use_moe=True, num_experts=4, moe_top_k=2, moe_interval=2, moe_offset=1, moe_hidden=32,
-              moe_capacity_factor=None) if moe else {}
+              moe_capacity_factor=None, moe_bias_gamma=1e-2) if moe else {}
     cfg = TransformerConfig(d_model=32, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=32,
                             ffn_hidden=64, qk_norm=False, **kw)
     model = cfg.build()
@@ -244,6 +265,8 @@ def _fsdp_worker(rank, world, dims, moe, seq_par, hsdp, clip):
         e = float((g - r).abs().max() / (r.abs().max() + 1e-12))
         if e > 2e-3:
             bad[n] = round(e, 4)
+    _ref_bias_update(ref)
+    _check_biases(model, ref, bad)
     return bad
 
 
@@ -291,7 +314,7 @@ def _pp_arena_worker(rank, world, dims, moe, seq_par, schedule):
     from nanopysche_b200.train.trainer import Trainer, TrainingConfig
     torch.manual_seed(0)
     kw = dict(use_moe=True, num_experts=4, moe_top_k=2, moe_interval=2, moe_offset=1, moe_hidden=32,
-              moe_capacity_factor=None) if moe else {}
+              moe_capacity_factor=None, moe_bias_gamma=1e-2) if moe else {}
     cfg = TransformerConfig(d_model=32, n_layers=4, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=32,
                             ffn_hidden=64, qk_norm=False, **kw)
     model = cfg.build()
@@ -356,6 +379,8 @@ def _pp_arena_worker(rank, world, dims, moe, seq_par, schedule):
         e = float((g - r).abs().max())
         if e > 5e-5:
             bad[n] = round(e, 6)
+    _ref_bias_update(ref)
+    _check_biases(model, ref, bad)
     return bad
 
 
