@@ -142,17 +142,35 @@ def load_dataset(dataset_spec: Optional[str], batch_size: int, seq_len: int, spl
 
 @torch.no_grad()
 def compute_val_perplexity(model, val_loader, device, max_batches: int = 10) -> float:
+    """exp(mean loss) over up to ``max_batches`` validation batches, without gradients. A context-parallel model gets
+    its share of every sequence (its loss is already the mean over the whole sequence); a pipeline stage cannot
+    evaluate on its own, so under pipeline parallelism the result is ``nan`` with a warning."""
+    if getattr(model, "_pp_enabled", False):
+        import warnings
+
+        warnings.warn("validation perplexity is not computed under pipeline parallelism (a stage has no loss of its own)")
+        return float("nan")
+    cp_group = getattr(model, "_cp_group", None)
     model.eval()
     tot, n = 0.0, 0
     it = iter(val_loader)
-    for _ in range(max_batches):
-        try:
-            ids, labels = next(it)
-        except StopIteration:
-            break
-        out = model(ids.to(device), labels=labels.to(device))
-        tot += float(out["loss"])
-        n += 1
+    with torch.no_grad():
+        for _ in range(max_batches):
+            try:
+                ids, labels = next(it)
+            except StopIteration:
+                break
+            ids, labels, kw = ids.to(device), labels.to(device), {}
+            if cp_group is not None:
+                import torch.distributed as dist
+
+                from .parallel.context_parallel import shard_batch_for_cp
+
+                ids, labels = shard_batch_for_cp(ids, labels, dist.get_world_size(cp_group), dist.get_rank(cp_group))
+                kw["labels_shifted"] = True
+            out = model(ids, labels=labels, **kw)
+            tot += float(out["loss"])
+            n += 1
     model.train()
     return math.exp(min(tot / max(n, 1), 20.0))
 
