@@ -39,27 +39,50 @@ class DistributedDataset(Dataset):
 
 
 class DistributedDataLoader:
+    """Batches of ``(input_ids, labels)`` for this rank's data-parallel index. Which index that is - the position
+    among the ranks that read *different* batches (dp x ep of the world mesh; tensor-, context- and pipeline-parallel
+    peers read the same batch) - is resolved at the first batch, not at construction: the CLI builds its loaders before
+    the mesh exists. Without a mesh every rank is its own data-parallel index (plain DDP)."""
+
     def __init__(self, dataset: Dataset, batch_size: int, *, num_workers: int = 0, seed: int = 0,
                  dp_rank: Optional[int] = None, dp_world: Optional[int] = None, shuffle: bool = True,
                  pin_memory: Optional[bool] = None, drop_last: bool = True):
         self.dataset, self.batch_size, self.seed = dataset, batch_size, seed
         self.epoch = 0
-        if dp_world is None:
-            from ..parallel.mesh import data_parallel_coords
-
-            dp_rank, dp_world = data_parallel_coords()
-            if dp_world == 1 and torch.distributed.is_available() and torch.distributed.is_initialized():
-                dp_rank, dp_world = torch.distributed.get_rank(), torch.distributed.get_world_size()
-        if dp_world > 1:
-            self.sampler = DistributedSampler(dataset, num_replicas=dp_world, rank=dp_rank, shuffle=shuffle, seed=seed)
-        else:
-            gen = torch.Generator().manual_seed(seed)
-            self.sampler = RandomSampler(dataset, generator=gen) if shuffle else None
-        pin = torch.cuda.is_available() if pin_memory is None else pin_memory
-        self.loader = DataLoader(dataset, batch_size=batch_size, sampler=self.sampler, num_workers=num_workers,
-                                 pin_memory=pin, drop_last=drop_last, persistent_workers=num_workers > 0)
+        self._args = dict(num_workers=num_workers, dp_rank=dp_rank, dp_world=dp_world, shuffle=shuffle,
+                          pin_memory=pin_memory, drop_last=drop_last)
+        self.sampler = None
+        self._loader: Optional[DataLoader] = None
         self._it: Optional[Iterator] = None
         self.batches_served = 0
+
+    @property
+    def loader(self) -> DataLoader:
+        if self._loader is None:
+            a = self._args
+            dp_rank, dp_world = a["dp_rank"], a["dp_world"]
+            if dp_world is None:
+                from ..parallel.mesh import data_parallel_coords, get_world_mesh
+
+                if get_world_mesh() is not None:
+                    dp_rank, dp_world = data_parallel_coords()
+                elif torch.distributed.is_available() and torch.distributed.is_initialized():
+                    dp_rank, dp_world = torch.distributed.get_rank(), torch.distributed.get_world_size()
+                else:
+                    dp_rank, dp_world = 0, 1
+            self.dp_rank, self.dp_world = dp_rank, dp_world
+            if dp_world > 1:
+                self.sampler = DistributedSampler(self.dataset, num_replicas=dp_world, rank=dp_rank,
+                                                  shuffle=a["shuffle"], seed=self.seed)
+                self.sampler.set_epoch(self.epoch)
+            else:
+                gen = torch.Generator().manual_seed(self.seed)
+                self.sampler = RandomSampler(self.dataset, generator=gen) if a["shuffle"] else None
+            pin = torch.cuda.is_available() if a["pin_memory"] is None else a["pin_memory"]
+            self._loader = DataLoader(self.dataset, batch_size=self.batch_size, sampler=self.sampler,
+                                      num_workers=a["num_workers"], pin_memory=pin, drop_last=a["drop_last"],
+                                      persistent_workers=a["num_workers"] > 0)
+        return self._loader
 
     def set_epoch(self, epoch: int):
         self.epoch = epoch

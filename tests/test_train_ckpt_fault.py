@@ -699,3 +699,24 @@ def test_reference_method_surface_of_checkpoint_and_pipeline_helpers(tmp_path):
     tc = TrainingConfig(global_batch_size=32, micro_batch_size=2, sequence_length=16, max_steps=1, dtype=torch.float32,
                         vocab_size=64)
     assert Trainer(tc, m, torch.optim.SGD(m.parameters(), lr=0.1), None, None, []).get_vocab_size() == 64
+
+
+def _loader_coords_worker(rank, world):
+    """The loader is built before the mesh (as the CLI does) and resolves its data-parallel index at the first batch:
+    with dp 2 x tp 2 the tensor-parallel peers read the same rows, the data-parallel peers different ones."""
+    from nanopysche_b200.parallel.mesh import build_world_mesh
+
+    tokens = np.arange(64 * 17, dtype=np.int64)
+    loader = create_distributed_loader(tokens, 2, 16, shuffle=False)
+    mesh = build_world_mesh(tp_size=2, device_type="cpu", replace=True)
+    ids, _ = next(iter(loader))
+    assert (loader.dp_rank, loader.dp_world) == (mesh["dp"].get_local_rank(), 2)
+    first = [torch.zeros_like(ids[0]) for _ in range(world)]
+    dist.all_gather(first, ids[0].contiguous())
+    tp_peer, dp_peer = rank ^ 1, rank ^ 2
+    assert torch.equal(first[rank], first[tp_peer]) and not torch.equal(first[rank], first[dp_peer])
+    return True
+
+
+def test_loader_built_before_the_mesh_follows_the_mesh():
+    assert all(run_distributed(_loader_coords_worker, 4))
