@@ -355,13 +355,42 @@ def cmd_bench(args) -> int:
     if not args.forward_only:
         opt, _ = _build_optimizer_and_scheduler(model, args, args.batch_size * args.seq_len // args.cp_size, 1000)
     x = torch.randint(0, vocab, (args.batch_size, args.seq_len), device=device)
+    labels, fwd_kw = x, {}
+    cp_group = getattr(model, "_cp_group", None) or getattr(getattr(model, "stages", [None])[0], "_cp_group", None)
+    if cp_group is not None:           # every context-parallel rank works on its share of each sequence
+        import torch.distributed as dist
+
+        from .parallel.context_parallel import shard_batch_for_cp
+
+        x, labels = shard_batch_for_cp(x, x, dist.get_world_size(cp_group), dist.get_rank(cp_group))
+        fwd_kw["labels_shifted"] = True
+    sched = None
+    if getattr(model, "_pp_enabled", False):
+        # a pipeline stage is stepped by the schedule executor (forward and backward of all micro-batches)
+        import torch.distributed as dist
+
+        from .parallel.pipeline_runtime import PipelineSchedule
+
+        if args.forward_only:
+            raise SystemExit("bench --forward-only is not available with --pp-size > 1: a pipeline step is a full step")
+        stages = list(model.stages) if hasattr(model, "stages") else [model]
+        m = getattr(args, "pp_microbatches", 0) or args.pp_size
+        assert args.batch_size % m == 0, "--batch-size must be a multiple of the pipeline micro-batch count"
+        sched = PipelineSchedule(stages, model._pp_group, model._pp_config, num_microbatches=m,
+                                 hidden_shape=(args.batch_size // m, x.shape[1], stages[0].d_model),
+                                 hidden_dtype=next(model.parameters()).dtype)
 
     def step():
+        if sched is not None:
+            sched.step(x, target=labels, **fwd_kw)
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            return
         if args.forward_only:
             with torch.no_grad():
                 model(x)
             return
-        out = model(x, labels=x)
+        out = model(x, labels=labels, **fwd_kw)
         loss = out["loss"] if out.get("aux_loss") is None else out["loss"] + out["aux_loss"]
         loss.backward()
         opt.step()
