@@ -383,6 +383,12 @@ def cmd_bench(args) -> int:
     def step():
         if sched is not None:
             sched.step(x, target=labels, **fwd_kw)
+            if getattr(model, "is_dualpipe", False):      # the two copies of every stage exchange their gradient halves
+                from .parallel.pipeline_runtime import sync_twin_grads
+
+                arena_opt = type(opt).__name__ == "ArenaAdamW"
+                sync_twin_grads(list(model.stages), model._pp_group,
+                                grad_of=(lambda q: getattr(q, "main_grad", None)) if arena_opt else None)
             opt.step()
             opt.zero_grad(set_to_none=True)
             return
