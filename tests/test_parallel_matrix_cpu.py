@@ -4,6 +4,7 @@ the gradient of the single-process model under the data-parallel objective (the 
 different batches of each rank's cross-entropy plus auxiliary loss) - for replicated parameters, tensor-parallel
 shards, expert shards and parameters applied to row shards alike."""
 import copy
+import os
 
 import pytest
 import torch
@@ -391,3 +392,86 @@ def test_arena_optimizer_under_pipelines_matches_single_process():
     cases = [("pp2xdp2-dense-zbv-arena", (dict(pp_size=2), False, False, "ZBVZeroBubble")),
              ("pp2xtp2sp-moe-dualpipe-arena", (dict(pp_size=2, tp_size=2), True, True, "DualPipe"))]
     _check(run_distributed(_many, 4, _pp_arena_worker, cases, timeout=600))
+
+
+def _build_for_resume(dims, sp, schedule):
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.parallel.mesh import build_world_mesh
+    from nanopysche_b200.parallel.tensor_parallel import TensorParallelConfig
+    from nanopysche_b200.parallel.pipeline_parallel import PipelineParallelConfig
+    from nanopysche_b200.parallelize import parallelize_model
+    torch.manual_seed(0)
+    cfg = TransformerConfig(d_model=32, n_layers=4, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=32,
+                            ffn_hidden=64, qk_norm=False, use_moe=True, num_experts=4, moe_top_k=2, moe_interval=2,
+                            moe_offset=1, moe_hidden=32, moe_capacity_factor=None, moe_bias_gamma=1e-2)
+    model = cfg.build()
+    mesh = build_world_mesh(device_type="cpu", replace=True, **dims)
+    tp, pp = dims.get("tp_size", 1), dims.get("pp_size", 1)
+    model = parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"),
+                              pp_config=PipelineParallelConfig(pp, schedule=schedule, num_microbatches=2) if pp > 1 else None,
+                              tp_config=TensorParallelConfig(tp, sequence_parallel=sp) if tp > 1 else None)
+    return model, mesh
+
+
+def _resume_worker(rank, world, dims, sp, schedule, save_dir):
+    from nanopysche_b200.checkpoint.distributed import CheckpointConfig, DistributedCheckpointer
+    from nanopysche_b200.parallel.mesh import data_parallel_coords
+    from nanopysche_b200.train.trainer import Trainer, TrainingConfig
+    def run(model, mesh, steps, ck=None, resume=False, start_batches=0):
+        idx, cnt = data_parallel_coords(mesh)
+        torch.manual_seed(1)
+        allb = [[torch.randint(0, 64, (4, 16)) for _ in range(cnt)] for _ in range(4)]
+        mine = [allb[s][idx] for s in range(4)][start_batches:]
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+        class Loader:
+            def __iter__(self):
+                return iter([(b, b.clone()) for b in mine])
+        tc = TrainingConfig(global_batch_size=cnt * 4 * 16, micro_batch_size=4, sequence_length=16, max_steps=steps,
+                            dtype=torch.float32, log_interval=0, save_interval=0, vocab_size=64, dp_world_size=cnt,
+                            max_grad_norm=1.0, pp_schedule=schedule, pp_microbatches=2, save_dir=save_dir)
+        tr = Trainer(tc, model, opt, data_loader=Loader(), device=torch.device("cpu"), checkpointer=ck)
+        if resume:
+            tr.load_checkpoint(save_dir)
+        tr.fit()
+        return tr, opt
+    # uninterrupted: 3 steps
+    m1, mesh = _build_for_resume(dims, sp, schedule)
+    run(m1, mesh, 3)
+    # interrupted: 2 steps, save, rebuild, resume, 1 more step
+    m2, mesh = _build_for_resume(dims, sp, schedule)
+    ck = DistributedCheckpointer(CheckpointConfig(save_dir=save_dir, pinned_memory=False))
+    tr, opt = run(m2, mesh, 2, ck=ck)
+    ck.save(tr.step, m2, opt)
+    m3, mesh = _build_for_resume(dims, sp, schedule)
+    for p in m3.parameters():
+        p.data.add_(1.0)     # make sure the load does something
+    ck3 = DistributedCheckpointer(CheckpointConfig(save_dir=save_dir, pinned_memory=False))
+    tr3, _ = run(m3, mesh, 3, ck=ck3, resume=True, start_batches=2)
+    bad = {}
+    for (n, a), (_, b) in zip(m1.named_parameters(), m3.named_parameters()):
+        e = float((a.detach() - b.detach()).abs().max())
+        if e > 1e-5:
+            bad[n] = e
+    for (n, a), (_, b) in zip(m1.named_buffers(), m3.named_buffers()):
+        if n.endswith("score_bias") and float((a - b).abs().max()) > 1e-6:
+            bad[n] = "bias"
+    assert tr3.step == 3
+    return bad
+
+
+def _resume_cases(rank, world, root):
+    out = {}
+    for cid, dims, sp, sch in (("tp2sp-x-ep2", dict(tp_size=2, ep_size=2), True, "1F1B"),
+                               ("pp2-dualpipe-x-ep2", dict(pp_size=2, ep_size=2), False, "DualPipe")):
+        bad = _resume_worker(rank, world, dims, sp, sch, os.path.join(root, cid))
+        if bad:
+            out[cid] = bad
+        dist.barrier()
+    return out
+
+
+def test_resume_under_compositions_is_exact(tmp_path):
+    """Two steps, a checkpoint, a freshly built (and deliberately perturbed) model that resumes and takes the third
+    step: weights and router biases equal those of three uninterrupted steps - with tensor-parallel, expert and
+    sequence-parallel shards, and with DualPipe's two stage copies per rank."""
+    _check(run_distributed(_resume_cases, 4, str(tmp_path), timeout=600))
