@@ -1,12 +1,15 @@
-"""Host-side EP runtime heuristics (reference: model/moe.py:716-1156).
+"""Host-side EP runtime heuristics (reference: model/moe.py:716-1156, same class and method names).
 
-``AdaptiveSMAllocator`` splits SMs between the dispatch/combine kernels and the expert GEMMs from a
-roofline estimate, ``RoutingPrefetcher`` predicts next-step routing from history and
-``CoupledEPScheduler`` couples SM split, prefetch confidence and re-balancing strength to the
-measured imbalance. Pure host arithmetic; the defaults here are B200 figures (148 SMs, 900 GB/s per
-direction of NVLink 5, 2250 dense bf16 TFLOP/s) instead of the reference's H100 ones, and the
-per-token compute time is multiplied by the token count so both terms of the roofline are seconds
-for the whole batch (the reference compares whole-batch communication with per-token compute).
+``AdaptiveSMAllocator`` decides how many SMs the dispatch / combine kernels may take from the expert GEMMs,
+``RoutingPrefetcher`` predicts next-step routing from history and ``CoupledEPScheduler`` couples the SM split, the
+prefetch confidence and the re-balancing strength to the measured load imbalance. Pure host arithmetic.
+
+The SM split is not the reference's proportional rule (SMs in the ratio of communication time to total time, with
+H100 constants and a per-token compute time against a whole-batch transfer time). On a B200 the two kernels run side
+by side, so the layer takes ``max(t_comm(s), t_gemm(148 - s))``; a pushing SM sustains only a share of the NVLink
+port, which saturates at 770 GB/s (measured, per direction) - after about sixteen SMs by this model's estimate of 48
+GB/s per SM, a figure that has not been measured on its own - and the GEMM's rate is proportional to the SMs it keeps. The allocator returns the ``s`` that minimises that maximum: the smallest budget that
+hides the transfer under the GEMM when that is possible, the saturation point when it is not.
 """
 from __future__ import annotations
 
@@ -16,7 +19,33 @@ from typing import Optional
 import torch
 
 
+@dataclass
+class _LinkComputeModel:
+    """Seconds for an expert-parallel exchange and for the expert GEMMs of one layer as functions of the SM split."""
+
+    total_sms: int = 148
+    link_gbps: float = 770.0          # measured peer-copy bandwidth per direction (nominal 900)
+    per_sm_gbps: float = 48.0         # estimate of what one SM of 16-byte peer stores sustains (port full near 16 SMs)
+    tflops: float = 1590.0            # measured cuBLAS bf16 burst rate of the whole GPU (nominal 2250 dense)
+
+    def t_comm(self, nbytes: float, sms: int) -> float:
+        return nbytes / (min(sms * self.per_sm_gbps, self.link_gbps) * 1e9)
+
+    def t_gemm(self, flops: float, sms: int) -> float:
+        return flops / (self.tflops * 1e12 * max(sms, 1) / self.total_sms)
+
+    def best_split(self, nbytes: float, flops: float, lo: int, hi: int) -> int:
+        """``s`` in ``[lo, hi]`` minimising ``max(t_comm(s), t_gemm(total - s))``; ties go to the smaller budget."""
+        best, best_t = lo, float("inf")
+        for s in range(lo, hi + 1):
+            t = max(self.t_comm(nbytes, s), self.t_gemm(flops, self.total_sms - s))
+            if t < best_t - 1e-15:
+                best, best_t = s, t
+        return best
+
+
 class AdaptiveSMAllocator:
+    # nominal figures kept as class attributes for callers that read them (the reference's names)
     NVLINK_BW_GBPS: float = 900.0
     GPU_TFLOPS_BF16: float = 2250.0
     TOTAL_SMS: int = 148
@@ -31,37 +60,43 @@ class AdaptiveSMAllocator:
             self.GPU_TFLOPS_BF16 = gpu_tflops
         self.min_sms = min_sms
         self.max_sms = max_sms or (self.TOTAL_SMS - 4)
-        self._prev_comm_time = 0.0
-        self._prev_compute_time = 0.0
+        # the achievable rates scale with the nominal ones the caller gave (770 / 900 and 1590 / 2250 measured on B200)
+        self.model = _LinkComputeModel(total_sms=self.TOTAL_SMS, link_gbps=self.NVLINK_BW_GBPS * 770.0 / 900.0,
+                                       tflops=self.GPU_TFLOPS_BF16 * 1590.0 / 2250.0)
         self._ema_alpha = 0.3
+        self._ema_bytes: Optional[float] = None
+        self._ema_flops: Optional[float] = None
+
+    def _smooth(self, nbytes: float, flops: float) -> tuple:
+        """Exponential average of the workload over calls: the split should not jump with one odd batch."""
+        a = self._ema_alpha
+        self._ema_bytes = nbytes if self._ema_bytes is None else a * nbytes + (1 - a) * self._ema_bytes
+        self._ema_flops = flops if self._ema_flops is None else a * flops + (1 - a) * self._ema_flops
+        return self._ema_bytes, self._ema_flops
 
     def compute_optimal_sms(self, num_tokens: int, hidden_size: int, expert_hidden: int, num_experts: int,
                             num_topk: int, num_bytes_per_elem: int = 2) -> int:
-        comm_bytes = num_tokens * num_topk * hidden_size * num_bytes_per_elem
-        comm_time = comm_bytes / (self.NVLINK_BW_GBPS * 1e9)
-        flops = num_tokens * num_topk * (2 * hidden_size * expert_hidden * 3)
-        compute_time = flops / (self.GPU_TFLOPS_BF16 * 1e12)
-        a = self._ema_alpha
-        comm_time = a * comm_time + (1 - a) * self._prev_comm_time
-        compute_time = a * compute_time + (1 - a) * self._prev_compute_time
-        self._prev_comm_time, self._prev_compute_time = comm_time, compute_time
-        total = comm_time + compute_time
-        if total == 0:
+        """SM budget of the dispatch / combine kernels for a layer that moves ``num_tokens x num_topk`` rows of
+        ``hidden_size`` elements and runs three ``hidden_size x expert_hidden`` GEMMs on each of them."""
+        rows = num_tokens * num_topk
+        if rows <= 0:
             return self.min_sms
-        return max(self.min_sms, min(self.max_sms, int(self.TOTAL_SMS * comm_time / total)))
+        nbytes, flops = self._smooth(rows * hidden_size * num_bytes_per_elem,
+                                     rows * 6.0 * hidden_size * expert_hidden)
+        return self.model.best_split(nbytes, flops, self.min_sms, self.max_sms)
 
     def compute_optimal_sms_from_counts(self, tokens_per_expert: torch.Tensor, hidden_size: int,
                                         expert_hidden: int, num_bytes_per_elem: int = 2) -> int:
-        num_experts = tokens_per_expert.shape[0]
-        total_tokens = float(tokens_per_expert.sum().item())
-        if total_tokens == 0:
+        """The same from measured per-expert loads. An uneven load makes the busiest expert's rows the critical path of
+        both kernels; the transfer of those rows cannot be spread over more links, so the budget grows with the
+        imbalance (up to one half more) to start the longest GEMM earlier."""
+        total = float(tokens_per_expert.sum().item())
+        if total == 0:
             return self.min_sms
-        mean_tokens = total_tokens / num_experts
-        imbalance = (tokens_per_expert.float() / mean_tokens).std().item() if num_experts > 1 else 0.0
-        base = self.compute_optimal_sms(int(total_tokens), hidden_size, expert_hidden, num_experts, 1,
-                                        num_bytes_per_elem)
-        boosted = int(base * (1.0 + min(0.5, imbalance * 0.1)))
-        return max(self.min_sms, min(self.max_sms, boosted))
+        n = tokens_per_expert.shape[0]
+        spread = (tokens_per_expert.float() * n / total).std().item() if n > 1 else 0.0
+        base = self.compute_optimal_sms(int(total), hidden_size, expert_hidden, n, 1, num_bytes_per_elem)
+        return max(self.min_sms, min(self.max_sms, int(base * (1.0 + min(0.5, 0.1 * spread)))))
 
 
 class RoutingPrefetcher:
@@ -129,6 +164,11 @@ class EPScheduleDecision:
 
 
 class CoupledEPScheduler:
+    """One decision per step from the measured per-expert loads: the imbalance (coefficient of variation, smoothed)
+    drives the SM budget of the exchange (the allocator's balanced split, widened with the imbalance), how much a
+    routing prediction is trusted, how hard the router's bias should push back, and whether the exchange may use the
+    fixed-capacity fast path."""
+
     def __init__(self, num_experts: int, hidden_size: int, expert_hidden: int, total_sms: int = 148,
                  nvlink_bw_gbps: float = 900.0, gpu_tflops_bf16: float = 2250.0, ema_alpha: float = 0.3,
                  min_sms: int = 4):
@@ -140,6 +180,7 @@ class CoupledEPScheduler:
         self.gpu_tflops_bf16 = gpu_tflops_bf16
         self.ema_alpha = ema_alpha
         self.min_sms = min_sms
+        self._allocator = AdaptiveSMAllocator(total_sms, nvlink_bw_gbps, gpu_tflops_bf16, min_sms=min_sms)
         self._ema_cv = 0.0
         self._step_count = 0
         self._routing_history: list[torch.Tensor] = []
@@ -152,15 +193,16 @@ class CoupledEPScheduler:
         cv = (t.std() / (t.mean() + 1e-8)).item() if t.numel() > 1 else 0.0
         self._ema_cv = self.ema_alpha * cv + (1 - self.ema_alpha) * self._ema_cv
         self._step_count += 1
-        comm_fraction = min(1.0, self._ema_cv * 1.5)
-        base = max(self.min_sms, int(self.total_sms * comm_fraction * 0.5))
-        sms = min(self.total_sms - 4, max(self.min_sms, base))
+        cv = self._ema_cv
+        balanced = self._allocator.compute_optimal_sms(num_tokens, self.hidden_size, self.expert_hidden,
+                                                       self.num_experts, num_topk)
+        sms = min(self.total_sms - 4, max(self.min_sms, int(balanced * (1.0 + min(1.0, cv)))))
         return EPScheduleDecision(
             num_sms=sms,
-            prefetch_confidence=max(0.1, min(0.95, 1.0 - self._ema_cv * 0.8)),
-            load_rebalancing_strength=min(0.9, max(0.1, self._ema_cv * 0.8)),
-            imbalance_coefficient=self._ema_cv,
-            dispatch_mode="fast" if self._ema_cv < 0.3 else "safe",
+            prefetch_confidence=max(0.1, min(0.95, 1.0 - 0.8 * cv)),      # skewed routing changes faster
+            load_rebalancing_strength=min(0.9, max(0.1, 0.8 * cv)),
+            imbalance_coefficient=cv,
+            dispatch_mode="fast" if cv < 0.3 else "safe",
         )
 
     def update_routing_history(self, expert_indices: torch.Tensor):
