@@ -100,37 +100,56 @@ class AdaptiveSMAllocator:
 
 
 class RoutingPrefetcher:
+    """Predicts where a layer's tokens will be routed from where they went in the last few steps, so that a runtime
+    may start moving rows before the router has run (reference: model/moe.py ``RoutingPrefetcher``, same methods).
+
+    Per layer the last ``history_len`` index tensors sit in one ring buffer ``[history_len, tokens, K]``. A prediction
+    is each token position's expert with the largest *recency-weighted* vote (every step counts twice as much as the
+    one before it: routing drifts, so older steps together never outvote the newest one, they only decide between its
+    K experts); its confidence is that expert's share of the weighted votes, i.e. how long it has been chosen."""
+
     def __init__(self, num_experts: int, history_len: int = 4, confidence_threshold: float = 0.8,
                  max_prefetch_tokens: int = 4096):
         self.num_experts = num_experts
         self.history_len = history_len
         self.confidence_threshold = confidence_threshold
         self.max_prefetch_tokens = max_prefetch_tokens
-        self._routing_history: dict[int, list[torch.Tensor]] = {}
-        self._prefetch_cache: dict[int, torch.Tensor] = {}
+        self._ring: dict[int, torch.Tensor] = {}      # layer -> [history_len, tokens, K] int64
+        self._filled: dict[int, int] = {}             # layer -> number of steps recorded (saturates at history_len)
         self._hit_count = 0
         self._miss_count = 0
 
     def record_routing(self, layer_idx: int, expert_indices: torch.Tensor):
-        hist = self._routing_history.setdefault(layer_idx, [])
-        hist.append(expert_indices.detach().cpu())
-        if len(hist) > self.history_len:
-            hist.pop(0)
+        idx = expert_indices.detach().to("cpu", torch.int64)
+        flat = idx.reshape(-1, idx.shape[-1])
+        ring = self._ring.get(layer_idx)
+        if ring is None or ring.shape[1:] != flat.shape:       # first step, or the batch shape changed: start over
+            ring = torch.zeros((self.history_len, *flat.shape), dtype=torch.int64)
+            self._ring[layer_idx], self._filled[layer_idx] = ring, 0
+        ring.copy_(torch.roll(ring, shifts=-1, dims=0))         # oldest step out, newest into the last slot
+        ring[-1] = flat
+        self._filled[layer_idx] = min(self._filled[layer_idx] + 1, self.history_len)
+
+    def should_prefetch(self, layer_idx: int) -> bool:
+        return self._filled.get(layer_idx, 0) >= 2
 
     def predict_next_layer(self, layer_idx: int, current_indices: torch.Tensor):
-        history = self._routing_history.get(layer_idx, [])
-        if len(history) < 2:
+        """``(predicted (B, S, K), confident (B, S))`` or ``None`` before two steps are known. Every one of the K slots
+        carries the same predicted expert (the most voted one)."""
+        if not self.should_prefetch(layer_idx):
             return None
-        stacked = torch.stack(history[-self.history_len:], dim=0)  # (H, B, S, K)
         B, S, K = current_indices.shape
-        flat = stacked.reshape(stacked.shape[0], B * S, K).permute(1, 0, 2).reshape(B * S, -1).long()
-        counts = torch.zeros(B * S, self.num_experts, dtype=torch.float32)
-        counts.scatter_add_(1, flat, torch.ones_like(flat, dtype=torch.float32))
-        probs = counts / counts.sum(-1, keepdim=True).clamp(min=1)
-        confidence, predicted = probs.max(dim=-1)
-        predicted = predicted.reshape(B, S, 1).expand(B, S, K)
-        confident = confidence.reshape(B, S) >= self.confidence_threshold
-        return predicted, confident
+        n = self._filled[layer_idx]
+        ring = self._ring[layer_idx][-n:]
+        if ring.shape[1] != B * S:
+            return None
+        weights = (2.0 ** torch.arange(n, dtype=torch.float32)).view(n, 1, 1).expand(n, B * S, ring.shape[2])
+        votes = torch.zeros(B * S, self.num_experts)
+        votes.scatter_add_(1, ring.permute(1, 0, 2).reshape(B * S, -1), weights.permute(1, 0, 2).reshape(B * S, -1))
+        share, expert = (votes / votes.sum(-1, keepdim=True).clamp_min(1.0)).max(dim=-1)
+        # an expert chosen in every remembered step by one of K slots has a share of 1 / K: compare on that scale
+        confident = (share * K).clamp(max=1.0) >= self.confidence_threshold
+        return expert.view(B, S, 1).expand(B, S, K), confident.view(B, S)
 
     def record_outcome(self, predicted: torch.Tensor, actual: torch.Tensor, mask: Optional[torch.Tensor] = None):
         """Score a prediction against the routing that happened (feeds ``get_stats``)."""
@@ -140,14 +159,11 @@ class RoutingPrefetcher:
         self._hit_count += int(hit.sum())
         self._miss_count += int(hit.numel() - hit.sum())
 
-    def should_prefetch(self, layer_idx: int) -> bool:
-        return len(self._routing_history.get(layer_idx, [])) >= 2
-
     def get_stats(self) -> dict:
         total = self._hit_count + self._miss_count
         return {"hit_rate": self._hit_count / max(1, total), "total_predictions": total,
                 "hits": self._hit_count, "misses": self._miss_count,
-                "history_depth": {k: len(v) for k, v in self._routing_history.items()}}
+                "history_depth": dict(self._filled)}
 
     def reset_stats(self):
         self._hit_count = 0

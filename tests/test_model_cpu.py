@@ -304,3 +304,33 @@ def test_generic_adapter_layer_helpers():
     assert layer_count(m) == 5
     assert [l.out_features for l in iter_layers(m)] == [2, 3, 4, 11, 12]      # numeric order: 9 before 10
     assert layer_count(nn.Linear(2, 2)) == 0 and list(iter_layers(nn.Linear(2, 2))) == []
+
+
+def test_routing_prefetcher_votes_with_recency_and_scores_itself():
+    from nanopysche_b200.models.ep_runtime import AdaptiveSMAllocator, CoupledEPScheduler, RoutingPrefetcher
+
+    pf = RoutingPrefetcher(num_experts=4, history_len=3, confidence_threshold=0.8)
+    stable = torch.tensor([[[0, 1], [2, 3]]])                  # (B=1, S=2, K=2)
+    assert pf.predict_next_layer(0, stable) is None and not pf.should_prefetch(0)
+    pf.record_routing(0, stable)
+    pf.record_routing(0, stable)
+    pred, conf = pf.predict_next_layer(0, stable)
+    assert pred.shape == (1, 2, 2) and bool(conf.all())        # the same experts every step: confident
+    assert set(pred[0, 0].tolist()) <= {0, 1} and set(pred[0, 1].tolist()) <= {2, 3}
+    moved = torch.tensor([[[3, 2], [2, 3]]])                   # token 0 changes its experts in the newest step
+    pf.record_routing(0, moved)
+    pred, conf = pf.predict_next_layer(0, moved)
+    assert int(pred[0, 0, 0]) in (2, 3) and not bool(conf[0, 0]) and bool(conf[0, 1])    # the newest step outvotes
+    pf.record_outcome(pred, moved)
+    st = pf.get_stats()
+    assert st["total_predictions"] == 2 and st["hits"] == 2 and st["history_depth"] == {0: 3}
+
+    # the SM split balances transfer and GEMM time: more bytes per FLOP -> more SMs for the exchange
+    narrow = AdaptiveSMAllocator().compute_optimal_sms(4096, 2048, 2816, 8, 2)
+    wide = AdaptiveSMAllocator().compute_optimal_sms(4096, 2048, 128, 8, 2)
+    assert 4 <= narrow < wide <= 144
+    sched = CoupledEPScheduler(8, 2048, 128)
+    even = sched.schedule(torch.full((8,), 512.0), 4096, 2)
+    skew = CoupledEPScheduler(8, 2048, 128).schedule(torch.tensor([64.0, 960.0] * 4), 4096, 2)
+    assert even.dispatch_mode == "fast" and skew.imbalance_coefficient > even.imbalance_coefficient
+    assert skew.num_sms >= even.num_sms and skew.prefetch_confidence < even.prefetch_confidence
