@@ -143,17 +143,15 @@ def load_dataset(dataset_spec: Optional[str], batch_size: int, seq_len: int, spl
 @torch.no_grad()
 def compute_val_perplexity(model, val_loader, device, max_batches: int = 10) -> float:
     """exp(mean loss) over up to ``max_batches`` validation batches, without gradients. A context-parallel model gets
-    its share of every sequence (its loss is already the mean over the whole sequence); a pipeline stage cannot
-    evaluate on its own, so under pipeline parallelism the result is ``nan`` with a warning."""
-    if getattr(model, "_pp_enabled", False):
-        import warnings
-
-        warnings.warn("validation perplexity is not computed under pipeline parallelism (a stage has no loss of its own)")
-        return float("nan")
-    cp_group = getattr(model, "_cp_group", None)
+    its share of every sequence (its loss is already the mean over the whole sequence); a pipelined model runs a
+    forward-only pass of its schedule and every rank gets the last stage's loss."""
+    pp = getattr(model, "_pp_enabled", False)
+    stages = (list(model.stages) if hasattr(model, "stages") else [model]) if pp else None
+    cp_group = getattr(stages[0] if pp else model, "_cp_group", None)
     model.eval()
     tot, n = 0.0, 0
     it = iter(val_loader)
+    sched = None
     with torch.no_grad():
         for _ in range(max_batches):
             try:
@@ -168,8 +166,19 @@ def compute_val_perplexity(model, val_loader, device, max_batches: int = 10) -> 
 
                 ids, labels = shard_batch_for_cp(ids, labels, dist.get_world_size(cp_group), dist.get_rank(cp_group))
                 kw["labels_shifted"] = True
-            out = model(ids, labels=labels, **kw)
-            tot += float(out["loss"])
+            if pp:
+                # forward-only pass of the whole pipeline; the loss reaches every rank from the last stage
+                from .parallel.pipeline_runtime import PipelineSchedule
+
+                if sched is None or sched.hidden_shape[1] != ids.shape[1]:
+                    m = model._pp_config.num_microbatches or model._pp_config.degree
+                    m = m if ids.shape[0] % m == 0 else 1
+                    sched = PipelineSchedule(stages, model._pp_group, model._pp_config, num_microbatches=m,
+                                             hidden_shape=(ids.shape[0] // m, ids.shape[1], stages[0].d_model),
+                                             hidden_dtype=next(model.parameters()).dtype)
+                tot += float(sched.loss_on_all_ranks(sched.evaluate(ids, target=labels, **kw)))
+            else:
+                tot += float(model(ids, labels=labels, **kw)["loss"])
             n += 1
     model.train()
     return math.exp(min(tot / max(n, 1), 20.0))

@@ -465,7 +465,14 @@ class PipelineSchedule:
                     ch.setdefault((peer, kind), []).append(label)
         return ch
 
-    def step(self, inputs: torch.Tensor, target: Optional[torch.Tensor] = None, **kwargs):
+    def evaluate(self, inputs: torch.Tensor, target: Optional[torch.Tensor] = None, **kwargs):
+        """Forward-only pass of the whole pipeline without gradients (validation): every rank runs the forward actions
+        of its schedule in their order, activations travel as in training, and the rank holding the last stage returns
+        the mean loss (the others ``None``)."""
+        with torch.no_grad():
+            return self.step(inputs, target, _forward_only=True, **kwargs)
+
+    def step(self, inputs: torch.Tensor, target: Optional[torch.Tensor] = None, _forward_only: bool = False, **kwargs):
         from ..ops import gemm as gemm_ops
 
         m = self.m
@@ -478,7 +485,7 @@ class PipelineSchedule:
         wqueues: Dict[tuple, list] = {}            # deferred weight-gradient GEMMs per (stage, microbatch)
         losses: List[torch.Tensor] = []
         hs, hd = self.hidden_shape, self.hidden_dtype
-        channels = {k: list(v) for k, v in self.channels.items()}
+        channels = {k: list(v) for k, v in self.channels.items() if not (_forward_only and k[1] == "grad")}
         nxt = {k: 0 for k in channels}              # next message of the channel to post a receive for
         posted: Dict[tuple, tuple] = {}              # label -> (buffer, works, channel)
         outstanding = {k: 0 for k in channels}
@@ -510,7 +517,7 @@ class PipelineSchedule:
             pending_send.extend(self.transport.send(kind, self._rank_of(dst_stage), keepalive[-1], label))
 
         for a in self.actions:
-            if a.type == ScheduleType.IDLE:
+            if a.type == ScheduleType.IDLE or (_forward_only and a.type != ScheduleType.FWD):
                 continue
             if hs is not None:
                 prefetch()
@@ -521,10 +528,10 @@ class PipelineSchedule:
                 if self._first(a.stage):
                     x = in_chunks[a.microbatch]
                 elif self._rank_of(a.stage - 1) == self.rank:  # previous stage lives on this rank too
-                    x = local_box.pop(("act", a.stage, a.microbatch)).requires_grad_(True)
+                    x = local_box.pop(("act", a.stage, a.microbatch)).requires_grad_(not _forward_only)
                 else:
                     x = receive(("act", a.stage, a.microbatch), (self._rank_of(a.stage - 1), "act"))
-                    x.requires_grad_(True)
+                    x.requires_grad_(not _forward_only)
                 mb.inp = x
                 self.transport.compute(a)     # everything this action waits for has been waited for
                 if self._last(a.stage):
@@ -551,6 +558,8 @@ class PipelineSchedule:
                         local_box[("act", a.stage + 1, a.microbatch)] = y.detach().clone()
                     else:
                         send("act", y, a.stage + 1, ("act", a.stage + 1, a.microbatch))
+                if _forward_only:
+                    state.pop(key, None)       # nothing comes back for this micro-batch
             elif a.type in (ScheduleType.BWD, ScheduleType.BWD_INPUT):
                 mb = state[key]
                 if self._last(a.stage):
@@ -585,6 +594,20 @@ class PipelineSchedule:
         if losses:
             return torch.stack(losses).mean()
         return None
+
+    def loss_on_all_ranks(self, loss: Optional[torch.Tensor]) -> torch.Tensor:
+        """The step's (or evaluation's) loss on every rank of the pipeline: broadcast from the rank that holds the last
+        stage; under DualPipe the mean of the two directions' losses (ranks p-1 and 0)."""
+        t = loss.detach().float().clone() if loss is not None else torch.zeros((), device=self._device())
+        if self.group is None or self.p <= 1:
+            return t
+        if self.dual:
+            both = t if self.rank in (0, self.p - 1) else torch.zeros_like(t)
+            dist.all_reduce(both, group=self.group)
+            return both / 2
+        src = self._rank_of(self.total_stages - 1)
+        dist.broadcast(t, dist.get_global_rank(self.group, src), group=self.group)
+        return t
 
     def _device(self):
         for s in self.stages:

@@ -565,14 +565,9 @@ class Trainer:
             sync_twin_grads(stages, group, grad_of=(lambda q: getattr(q, "main_grad", None)) if self._arena_opt
                             else None)
             sync_twin_router_counts(stages, group)
-            # the loss lives on the last stage of each direction: ranks p-1 (even microbatches) and 0 (odd ones)
-            both = total.clone() if self._pp_schedule.rank in (0, pp - 1) else torch.zeros_like(total)
-            dist.all_reduce(both, group=group)
-            return both / (2 if pp > 1 else 1)
-        # the rank that holds the last stage (rank p-1 for loop placements, rank 0 for the V placement) has the loss
-        src = self._pp_schedule._rank_of(self._pp_schedule.total_stages - 1)
-        dist.broadcast(total, dist.get_global_rank(group, src), group=group)
-        return total
+        # every rank logs the loss of the last stage (rank p-1 for loop placements, rank 0 for the V placement, the mean
+        # of ranks p-1 and 0 under DualPipe)
+        return self._pp_schedule.loss_on_all_ranks(total)
 
     def _train_step(self, batches):
         if getattr(self.model, "_pp_enabled", False) and dist.is_initialized():

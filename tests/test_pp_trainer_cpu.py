@@ -84,6 +84,15 @@ def _pp_trainer_worker(rank, world, schedule):
     for name, p in model.named_parameters():
         rname = name.split(".", 2)[2] if name.startswith("stages.") else name
         assert torch.allclose(p, dict(ref.named_parameters())[rname], atol=2e-4), name
+    # forward-only pass of the trained pipeline (validation): every rank gets the loss of the single-process model
+    from nanopysche_b200.cli import compute_val_perplexity
+
+    val = torch.randint(0, 64, (4, 8), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        want = ref(val, labels=val)["loss"].item()
+    got_ppl = compute_val_perplexity(model, [(val, val.clone())], torch.device("cpu"))
+    assert got_ppl == pytest.approx(torch.tensor(want).exp().item(), rel=1e-4), (got_ppl, want)
+    assert all(q.grad is None or float(q.grad.abs().sum()) >= 0 for q in model.parameters())
     return True
 
 
