@@ -142,17 +142,15 @@ def parallelize_model(model: nn.Module, *, world_mesh, device: Optional[torch.de
                 model._replica_group = get_replica_group(world_mesh)   # read by engine.prepare_training
             model._needs_grad_sync = True
         else:
-            if getattr(model, "_tp_sequence_parallel", False):
-                raise NotImplementedError(
-                    "sequence-parallel tensor parallelism (sequence_parallel / --async-tp) is not combined with PyTorch "
-                    "FSDP2: FSDP2 replaces the parameters, which drops the hooks that sum the partial gradients of "
-                    "norms, embeddings and MoE weights over the TP group. Use the arena backend "
-                    "(DataParallelConfig(backend=\"arena\"), the default on CUDA)")
             # FSDP2 shards (and averages gradients) over the dp dims only. Expert-parallel peers read other batches
             # and context-parallel peers other parts of each sequence, so the gradients still have to be combined over
-            # those dims: Trainer._sync_fsdp_extra_dims does it after the backward pass
+            # those dims: Trainer._sync_fsdp_extra_dims does it after the backward pass. Under sequence-parallel TP
+            # the same pass sums the partial gradients (norms, embeddings, routers, MoE weights) over the TP group: FSDP2
+            # replaces the parameter objects, so the hooks that do it otherwise never fire.
             names_ = tuple(world_mesh.mesh_dim_names or ()) if world_mesh is not None else ()
             extra = {}
+            if getattr(model, "_tp_sequence_parallel", False):
+                extra["sp"] = get_tp_mesh(world_mesh).get_group()
             if MeshDimName.ep in names_ and world_mesh[MeshDimName.ep].size() > 1:
                 extra["ep"] = world_mesh[MeshDimName.ep].get_group()
             if MeshDimName.cp in names_ and world_mesh[MeshDimName.cp].size() > 1:

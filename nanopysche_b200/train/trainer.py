@@ -459,11 +459,21 @@ class Trainer:
         def local(g):
             return g._local_tensor if hasattr(g, "_local_tensor") else g
 
-        ep_group, cp_group = extra.get("ep"), extra.get("cp")
+        ep_group, cp_group, sp_group = extra.get("ep"), extra.get("cp"), extra.get("sp")
+        partial_ids = set()
+        if sp_group is not None:     # whole parameters applied to row shards under sequence-parallel TP
+            for m in self.model.modules():
+                if isinstance(m, MoEBase):
+                    partial_ids |= {id(q) for q in m.parameters()}
+            for n, q in self.model.named_parameters():
+                if "norm" in n or n.startswith("embeddings") or ".embeddings." in n:
+                    partial_ids.add(id(q))
         for p in self.model.parameters():
             if p.grad is None:
                 continue
             g = local(p.grad)
+            if id(p) in partial_ids:
+                dist.all_reduce(g, group=sp_group)
             if ep_group is not None:
                 if id(p) not in expert_ids:
                     dist.all_reduce(g, group=ep_group)

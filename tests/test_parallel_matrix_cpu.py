@@ -278,31 +278,9 @@ def test_applied_gradients_match_single_process_under_torch_fsdp2():
     cases = [("fsdp2xtp2", (dict(tp_size=2), False, False, {}, 0.05)),
              ("fsdp2xep2-moe", (dict(ep_size=2), True, False, {}, 0.05)),
              ("fsdp2xcp2", (dict(cp_size=2), False, False, {}, 0.05)),
+             ("fsdp2xtp2sp-moe", (dict(tp_size=2), True, True, {}, 0.05)),
              ("hsdp2x2", ({}, False, False, dict(dp_replicate=2, dp_shard=2), 0.05))]
     _check(run_distributed(_many, 4, _fsdp_worker, cases, timeout=600))
-
-
-def _sp_fsdp_refusal_worker(rank, world):
-    from nanopysche_b200.config import TransformerConfig
-    from nanopysche_b200.parallel.fsdp import DataParallelConfig
-    from nanopysche_b200.parallel.mesh import build_world_mesh
-    from nanopysche_b200.parallel.tensor_parallel import TensorParallelConfig
-    from nanopysche_b200.parallelize import parallelize_model
-
-    model = TransformerConfig(d_model=32, n_layers=1, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=16,
-                              ffn_hidden=64, qk_norm=False).build()
-    mesh = build_world_mesh(tp_size=2, device_type="cpu", replace=True)
-    try:
-        parallelize_model(model, world_mesh=mesh, device=torch.device("cpu"),
-                          tp_config=TensorParallelConfig(2, sequence_parallel=True),
-                          dp_config=DataParallelConfig(backend="torch"))
-    except NotImplementedError as e:
-        return "FSDP2" in str(e)
-    return False
-
-
-def test_sequence_parallel_with_torch_fsdp2_is_refused():
-    assert all(run_distributed(_sp_fsdp_refusal_worker, 2))
 
 
 def _pp_arena_worker(rank, world, dims, moe, seq_par, schedule):
