@@ -423,7 +423,42 @@ class ExpertMLP(nn.Module):
         from .feed_forward import FeedForward
 
         self.ffn = FeedForward(d_model=d_model, hidden_size=hidden_size, dtype=dtype, device=device)
-        self.w1, self.w2, self.w3 = self.ffn.w1, self.ffn.w2, self.ffn.w3
+        self._register_load_state_dict_pre_hook(self._reference_keys_in)
+
+    # The reference keeps three bare parameters ``w1``, ``w3`` (hidden, d_model) and ``w2`` (hidden, d_model, applied as
+    # ``h @ w2``). The computation here runs through ``FeedForward`` (one fused gate|up GEMM), whose ``w2.weight`` is
+    # the transpose; the state dict is written and read in the reference's names and layout, so checkpoints move
+    # between the two code bases.
+    @property
+    def w1(self) -> torch.Tensor:
+        return self.ffn.w1.weight
+
+    @property
+    def w3(self) -> torch.Tensor:
+        return self.ffn.w3.weight
+
+    @property
+    def w2(self) -> torch.Tensor:
+        return self.ffn.w2.weight.t()
+
+    def state_dict(self, *args, destination=None, prefix="", keep_vars=False):
+        if destination is None:
+            from collections import OrderedDict
+
+            destination = OrderedDict()
+            destination._metadata = OrderedDict()
+        for name in ("w1", "w2", "w3"):
+            t = getattr(self, name)
+            destination[prefix + name] = t if keep_vars else t.detach()
+        return destination
+
+    @staticmethod
+    def _reference_keys_in(state_dict, prefix, *_):
+        for name in ("w1", "w2", "w3"):
+            state_dict.pop(f"{prefix}{name}.weight", None)      # alias entries of this package's earlier checkpoints
+            if prefix + name in state_dict:
+                t = state_dict.pop(prefix + name)
+                state_dict[f"{prefix}ffn.{name}.weight"] = t.t() if name == "w2" else t
 
     def forward(self, x):
         return self.ffn(x)

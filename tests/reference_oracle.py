@@ -1,0 +1,128 @@
+"""Runs the unmodified reference (installed under ``baseline/_ref``) on small CPU cases and writes what it computed
+to a file: ``python tests/reference_oracle.py out.pt``. ``tests/test_reference_parity_cpu.py`` loads the same weights
+and inputs into this package and compares. It is a separate process because the reference's top-level package name
+(``nanopsyche``) is the name of this repository's alias package.
+
+Nothing of this package is imported here."""
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+
+BASE = dict(d_model=64, vocab_size=128, n_layers=2)
+BLOCK = dict(n_heads=4, n_kv_heads=2, rope_base=10000.0, max_seq_len=64, ffn_hidden=128)
+MOE = dict(d_model=64, hidden_size=96, num_experts=4, top_k=2)
+
+# name -> (Transformer kwargs, block kwargs, MoEBase kwargs or None); enum values by name
+MODEL_CASES = {
+    "dense": ({}, dict(qk_norm=False), None),
+    "dense_qk_norm": ({}, dict(qk_norm=True), None),
+    "dense_tied": (dict(tie_word_embeddings=True), dict(qk_norm=False), None),
+    "dense_mha_head_dim": ({}, dict(qk_norm=False, n_kv_heads=4, head_dim=32), None),
+    "moe": ({}, dict(qk_norm=False), {}),
+    "moe_capacity_1": ({}, dict(qk_norm=False), dict(capacity_factor=1.0)),
+    "moe_capacity_1p25": ({}, dict(qk_norm=False), dict(capacity_factor=1.25)),
+    "moe_sigmoid": ({}, dict(qk_norm=False), dict(gating_function="SIGMOID")),
+    "moe_z_loss": ({}, dict(qk_norm=False), dict(z_loss_multiplier=1e-3)),
+    "moe_gate_bias": ({}, dict(qk_norm=False), dict(bias=True)),
+    "moe_shared_expert": ({}, dict(qk_norm=False), dict(shared_expert=True)),
+    "moe_score_bias": ({}, dict(qk_norm=False), dict(bias_gamma=1e-2)),
+    "moe_top1_8_experts": ({}, dict(qk_norm=False), dict(num_experts=8, top_k=1, capacity_factor=1.5)),
+}
+
+
+def build(transformer_cls, moe_module, case, seed=0):
+    tkw, bkw, mkw = MODEL_CASES[case]
+    torch.manual_seed(seed)
+    model = transformer_cls(**BASE, **tkw, block=dict(BLOCK, **bkw))
+    if mkw is not None:
+        kw = dict(MOE, **mkw)
+        if "gating_function" in kw:
+            kw["gating_function"] = getattr(moe_module.GatingFunction, kw["gating_function"])
+        for i in range(BASE["n_layers"]):
+            model.replace_block_with_moe_hybrid(i, moe_module.MoEBase(**kw))
+    return model
+
+
+def run_model(model, ids):
+    model.train()
+    out = model(ids, labels=ids)
+    out["loss"].backward()
+    return {"logits": out["logits"].detach(), "loss": out["loss"].detach(),
+            "aux_loss": None if out.get("aux_loss") is None else out["aux_loss"].detach(),
+            "grads": {n: p.grad.detach().clone() for n, p in model.named_parameters() if p.grad is not None}}
+
+
+def main(path):
+    if not os.path.isdir(os.path.join(REF, "nanopsyche")):
+        print("reference not installed")
+        return 3
+    sys.path.insert(0, REF)
+    from nanopsyche.model import moe as ref_moe
+    from nanopsyche.model import rope as ref_rope
+    from nanopsyche.model.transformer import Transformer
+    from nanopsyche.optim.adamw import AdamW, create_adamw
+    from nanopsyche.train import scheduler as ref_sched
+
+    res = {"models": {}, "sched": {}, "rope": {}, "adamw": {}}
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, BASE["vocab_size"], (2, 32), generator=g)
+    res["ids"] = ids
+    for case in MODEL_CASES:
+        m = build(Transformer, ref_moe, case)
+        sd = {k: v.detach().clone() for k, v in m.state_dict().items()}
+        res["models"][case] = dict(run_model(m, ids), state_dict=sd)
+
+    steps = list(range(0, 130, 3))
+    res["sched"]["steps"] = steps
+    res["sched"]["cosine"] = [ref_sched.cosine_with_warmup(s, 10, 100, 1e-5, 3e-4) for s in steps]
+    res["sched"]["wsd"] = [ref_sched.warmup_stable_decay(s, 10, 50, 40, 1e-5, 3e-4) for s in steps]
+    res["sched"]["exp"] = [ref_sched.exponential_decay(s, 10, 0.97, 1e-5, 3e-4) for s in steps]
+    for name, make in (("CosineWithWarmup", lambda o: ref_sched.CosineWithWarmup(o, warmup_steps=5, max_steps=40)),
+                       ("WarmupStableDecay", lambda o: ref_sched.WarmupStableDecay(o, warmup_steps=5, stable_steps=20,
+                                                                                   decay_steps=15))):
+        p = torch.nn.Parameter(torch.zeros(2))
+        opt = torch.optim.SGD([p], lr=3e-4)
+        sch = make(opt)
+        lrs = []
+        for _ in range(50):
+            lrs.append(opt.param_groups[0]["lr"])
+            opt.step()
+            sch.step()
+        res["sched"][name] = lrs
+
+    for name, kw in (("plain", dict(base=10000.0)), ("theta_500k", dict(base=500000.0)),
+                     ("partial", dict(base=10000.0, partial_rotary_factor=0.5)),
+                     ("scaled", dict(base=500000.0, scaling=ref_rope.RoPEScalingConfig(
+                         factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=64)))):
+        rope = ref_rope.RotaryEmbedding(32, max_seq_len=256, **kw)
+        cos, sin = rope(48, offset=7, device=torch.device("cpu"))
+        x = torch.randn(2, 48, 4, 32, generator=g)
+        rot = int(32 * kw.get("partial_rotary_factor", 1.0))
+        y = ref_rope.apply_rotary_emb(x, cos, sin) if rot == 32 else None
+        res["rope"][name] = {"cos": cos, "sin": sin, "x": x, "y": y}
+
+    # optimizer: five steps on fixed gradients; the decay / no-decay split of create_adamw by parameter name
+    m = build(Transformer, ref_moe, "moe_gate_bias")
+    opt = create_adamw(m, lr=1e-2, weight_decay=0.1)
+    res["adamw"]["groups"] = [sorted(n for n, p in m.named_parameters() if any(p is q for q in grp["params"]))
+                              for grp in opt.param_groups]
+    ws = [torch.nn.Parameter(torch.randn(7, 5, generator=g)), torch.nn.Parameter(torch.randn(11, generator=g))]
+    w0 = [w.detach().clone() for w in ws]
+    grads = [[torch.randn(w.shape, generator=g) for w in ws] for _ in range(5)]
+    opt = AdamW([{"params": [ws[0]], "weight_decay": 0.1}, {"params": [ws[1]], "weight_decay": 0.0}], lr=1e-2,
+                betas=(0.9, 0.95), eps=1e-8)
+    for gs in grads:
+        for w, gr in zip(ws, gs):
+            w.grad = gr.clone()
+        opt.step()
+    res["adamw"].update(w0=w0, grads=grads, w=[w.detach().clone() for w in ws])
+    torch.save(res, path)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main(sys.argv[1]))

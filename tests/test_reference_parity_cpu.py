@@ -1,0 +1,130 @@
+"""Numerical parity with the unmodified reference on CPU, in fp32: the reference (installed under ``baseline/_ref``)
+runs in a child process (``tests/reference_oracle.py``) and writes weights, inputs and results; here the same weights
+go into this package's classes through ``load_state_dict`` - the state-dict keys and layouts are the reference's, which
+is what lets a checkpoint move between the two - and logits, loss and every gradient are compared. Also the LR
+schedules, RoPE tables, AdamW update and the decay / no-decay parameter split. Skipped when the reference is not
+installed."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import reference_oracle as oracle  # noqa: E402  (only its case tables and builder; it imports nothing of either package)
+
+
+@pytest.fixture(scope="module")
+def ref(tmp_path_factory):
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "nanopsyche")):
+        pytest.skip("the reference is not installed under baseline/_ref")
+    out = str(tmp_path_factory.mktemp("oracle") / "ref.pt")
+    env = dict(os.environ, PYTHONPATH="")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_oracle.py"), out], env=env,
+                       capture_output=True, text=True, timeout=600)
+    if r.returncode == 3:
+        pytest.skip("the reference is not installed under baseline/_ref")
+    assert r.returncode == 0, r.stderr[-2000:]
+    return torch.load(out, weights_only=False)
+
+
+def _to_reference_names(model):
+    """This package's ``named_parameters`` under the reference's names and layouts (only the shared expert differs:
+    it computes through a FeedForward, whose ``w2.weight`` is the transpose of the reference's ``w2``)."""
+    out = {}
+    for n, p in model.named_parameters():
+        if ".shared_expert.ffn." in n:
+            short = n.replace(".ffn.", ".").rsplit(".weight", 1)[0]
+            out[short] = p.grad.t() if short.endswith(".w2") else p.grad
+        else:
+            out[n] = p.grad
+    return out
+
+
+@pytest.mark.parametrize("case", list(oracle.MODEL_CASES))
+def test_model_matches_the_reference(ref, case):
+    from nanopysche_b200.models import moe as our_moe
+    from nanopysche_b200.models.transformer import Transformer
+
+    want = ref["models"][case]
+    model = oracle.build(Transformer, our_moe, case, seed=99)      # other initial weights: everything comes from the load
+    assert set(model.state_dict().keys()) == set(want["state_dict"].keys())
+    for k, v in model.state_dict().items():
+        assert v.shape == want["state_dict"][k].shape, k
+    model.load_state_dict(want["state_dict"], strict=True)
+    for k, v in model.state_dict().items():                          # and what is written back is what was read
+        assert torch.equal(v, want["state_dict"][k]), k
+    got = oracle.run_model(model, ref["ids"])
+    assert torch.allclose(got["logits"], want["logits"], atol=2e-5, rtol=1e-4), case
+    assert abs(float(got["loss"]) - float(want["loss"])) < 1e-5
+    grads = _to_reference_names(model)
+    assert set(want["grads"]) <= set(grads)
+    for n, g in want["grads"].items():
+        assert grads[n] is not None, n
+        scale = g.abs().max().item() + 1e-12
+        assert (grads[n] - g).abs().max().item() / scale < 2e-4, (case, n)
+
+
+def test_lr_schedules_match_the_reference(ref):
+    from nanopysche_b200.train import scheduler as S
+
+    s = ref["sched"]
+    for name, fn in (("cosine", lambda t: S.cosine_with_warmup(t, 10, 100, 1e-5, 3e-4)),
+                     ("wsd", lambda t: S.warmup_stable_decay(t, 10, 50, 40, 1e-5, 3e-4)),
+                     ("exp", lambda t: S.exponential_decay(t, 10, 0.97, 1e-5, 3e-4))):
+        for t, want in zip(s["steps"], s[name]):
+            assert fn(t) == pytest.approx(want, rel=1e-12, abs=1e-15), (name, t)
+    for name, make in (("CosineWithWarmup", lambda o: S.CosineWithWarmup(o, warmup_steps=5, max_steps=40)),
+                       ("WarmupStableDecay", lambda o: S.WarmupStableDecay(o, warmup_steps=5, stable_steps=20,
+                                                                           decay_steps=15))):
+        p = torch.nn.Parameter(torch.zeros(2))
+        opt = torch.optim.SGD([p], lr=3e-4)
+        sch = make(opt)
+        for want in s[name]:
+            assert opt.param_groups[0]["lr"] == pytest.approx(want, rel=1e-12, abs=1e-18), name
+            opt.step()
+            sch.step()
+
+
+def test_rope_tables_and_rotation_match_the_reference(ref):
+    from nanopysche_b200.models import rope as R
+
+    kws = {"plain": dict(base=10000.0), "theta_500k": dict(base=500000.0),
+           "partial": dict(base=10000.0, partial_rotary_factor=0.5),
+           "scaled": dict(base=500000.0, scaling=R.RoPEScalingConfig(factor=8.0, low_freq_factor=1.0,
+                                                                     high_freq_factor=4.0,
+                                                                     original_max_position_embeddings=64))}
+    for name, kw in kws.items():
+        want = ref["rope"][name]
+        rope = R.RotaryEmbedding(32, max_seq_len=256, **kw)
+        cos, sin = rope(48, offset=7, device=torch.device("cpu"))
+        assert cos.shape == want["cos"].shape, name
+        assert torch.allclose(cos, want["cos"], atol=2e-6) and torch.allclose(sin, want["sin"], atol=2e-6), name
+        if want["y"] is not None:
+            y = R.apply_rotary_emb(want["x"], cos, sin)
+            assert torch.allclose(y, want["y"], atol=1e-5), name
+
+
+def test_adamw_and_parameter_groups_match_the_reference(ref):
+    from nanopysche_b200.models import moe as our_moe
+    from nanopysche_b200.models.transformer import Transformer
+    from nanopysche_b200.optim.adamw import AdamW, create_adamw
+
+    a = ref["adamw"]
+    m = oracle.build(Transformer, our_moe, "moe_gate_bias")
+    opt = create_adamw(m, lr=1e-2, weight_decay=0.1)
+    groups = [sorted(n for n, p in m.named_parameters() if any(p is q for q in grp["params"]))
+              for grp in opt.param_groups]
+    assert [g["weight_decay"] for g in opt.param_groups] == [0.1, 0.0]
+    assert groups == a["groups"]
+    ws = [torch.nn.Parameter(w.clone()) for w in a["w0"]]
+    opt = AdamW([{"params": [ws[0]], "weight_decay": 0.1}, {"params": [ws[1]], "weight_decay": 0.0}], lr=1e-2,
+                betas=(0.9, 0.95), eps=1e-8)
+    for gs in a["grads"]:
+        for w, g in zip(ws, gs):
+            w.grad = g.clone()
+        opt.step()
+    for w, want in zip(ws, a["w"]):
+        assert torch.allclose(w, want, atol=1e-6, rtol=1e-5)
