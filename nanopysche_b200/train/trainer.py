@@ -621,18 +621,28 @@ class Trainer:
             total = loss.detach() if total is None else total + loss.detach()
         return total / accum
 
+    @staticmethod
+    def _as_pair(batch):
+        """``(input_ids, labels)`` from what a loader yields: a pair, or the reference's mapping with ``input_ids`` and
+        ``labels`` (train/trainer.py:322-324; without ``labels`` the inputs are their own targets)."""
+        if isinstance(batch, dict):
+            ids = batch["input_ids"]
+            labels = batch.get("labels")
+            return ids, (ids if labels is None else labels)
+        return batch
+
     def _get_batch(self):
         c = self.config
         if self.data_loader is not None:
             if self._data_iter is None:
                 self._data_iter = iter(self.data_loader)
             try:
-                return next(self._data_iter)
+                return self._as_pair(next(self._data_iter))
             except StopIteration:
                 if hasattr(self.data_loader, "set_epoch"):
                     self.data_loader.set_epoch(getattr(self.data_loader, "epoch", 0) + 1)
                 self._data_iter = iter(self.data_loader)
-                return next(self._data_iter)
+                return self._as_pair(next(self._data_iter))
         ids = torch.randint(0, c.vocab_size, (c.micro_batch_size, c.sequence_length))
         return ids, ids.clone()
 

@@ -56,6 +56,41 @@ def run_model(model, ids):
             "grads": {n: p.grad.detach().clone() for n, p in model.named_parameters() if p.grad is not None}}
 
 
+class DictLoader:
+    """Yields the reference's batch format; the reference Trainer calls ``next()`` on its loader."""
+
+    def __init__(self, batches):
+        self.batches, self.i = batches, 0
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        b = self.batches[self.i % len(self.batches)]
+        self.i += 1
+        return {"input_ids": b, "labels": b}
+
+
+TRAIN_STEPS, ACCUM = 6, 2
+
+
+def run_trainer(model, batches, trainer_cls, config_cls, scheduler_cls, create_adamw):
+    """Six optimizer steps (two micro-batches each, warm-up + cosine, clipping at 0.5) through the Trainer's own step."""
+    opt = create_adamw(model, lr=1e-2, weight_decay=0.1)
+    sch = scheduler_cls(opt, warmup_steps=2, max_steps=TRAIN_STEPS)
+    B, S = batches[0].shape
+    tc = config_cls(global_batch_size=ACCUM * B * S, micro_batch_size=B, sequence_length=S, max_steps=TRAIN_STEPS,
+                    dtype=torch.float32, save_interval=10 ** 9, log_interval=10 ** 9, max_grad_norm=0.5)
+    tr = trainer_cls(tc, model, opt, sch, DictLoader(batches), [])
+    tr.device = torch.device("cpu")
+    losses = []
+    for i in range(TRAIN_STEPS):
+        tr.step = i + 1
+        tr._train_step_with_callbacks()
+        losses.append(float(tr._metrics.get("train/CE loss")))
+    return losses, {k: v.detach().clone() for k, v in model.state_dict().items()}
+
+
 def main(path):
     if not os.path.isdir(os.path.join(REF, "nanopsyche")):
         print("reference not installed")
@@ -66,6 +101,8 @@ def main(path):
     from nanopsyche.model.transformer import Transformer
     from nanopsyche.optim.adamw import AdamW, create_adamw
     from nanopsyche.train import scheduler as ref_sched
+
+    from nanopsyche.train.trainer import Trainer, TrainingConfig
 
     res = {"models": {}, "sched": {}, "rope": {}, "adamw": {}}
     g = torch.Generator().manual_seed(5)
@@ -120,6 +157,12 @@ def main(path):
             w.grad = gr.clone()
         opt.step()
     res["adamw"].update(w0=w0, grads=grads, w=[w.detach().clone() for w in ws])
+
+    m = build(Transformer, ref_moe, "dense", seed=4)
+    init = {k: v.detach().clone() for k, v in m.state_dict().items()}
+    batches = [torch.randint(0, BASE["vocab_size"], (2, 32), generator=g) for _ in range(TRAIN_STEPS * ACCUM)]
+    losses, final = run_trainer(m, batches, Trainer, TrainingConfig, ref_sched.CosineWithWarmup, create_adamw)
+    res["trainer"] = dict(init=init, batches=batches, losses=losses, final=final)
     torch.save(res, path)
     return 0
 

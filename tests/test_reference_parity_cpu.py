@@ -128,3 +128,24 @@ def test_adamw_and_parameter_groups_match_the_reference(ref):
         opt.step()
     for w, want in zip(ws, a["w"]):
         assert torch.allclose(w, want, atol=1e-6, rtol=1e-5)
+
+
+def test_trainer_trajectory_matches_the_reference(ref):
+    """Six optimizer steps through ``Trainer._train_step_with_callbacks`` - gradient accumulation over two micro-batches,
+    clipping, AdamW with the decay split, warm-up and cosine schedule, batches in the reference's mapping format - end in
+    the same weights. The logged loss is the mean over the micro-batches here; the reference logs their sum
+    (train/trainer.py:326-333 multiplies the already divided loss back by the accumulation count)."""
+    from nanopysche_b200.models import moe as our_moe
+    from nanopysche_b200.models.transformer import Transformer
+    from nanopysche_b200.optim.adamw import create_adamw
+    from nanopysche_b200.train.scheduler import CosineWithWarmup
+    from nanopysche_b200.train.trainer import Trainer, TrainingConfig
+
+    t = ref["trainer"]
+    m = oracle.build(Transformer, our_moe, "dense", seed=77)
+    m.load_state_dict(t["init"])
+    losses, final = oracle.run_trainer(m, t["batches"], Trainer, TrainingConfig, CosineWithWarmup, create_adamw)
+    for a, b in zip(losses, t["losses"]):
+        assert a == pytest.approx(b / oracle.ACCUM, rel=1e-5)
+    for k, v in t["final"].items():
+        assert torch.allclose(final[k], v, atol=1e-5, rtol=1e-4), k
