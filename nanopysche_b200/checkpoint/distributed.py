@@ -377,6 +377,10 @@ class DistributedCheckpointer:
 
     def _collect(self, step, model, optimizer, scheduler, extra, ephemeral, config):
         rank, world = self._rank_world()
+        if hasattr(config, "as_dict"):
+            config = config.as_dict()
+        elif config is not None and not isinstance(config, dict):
+            config = {"repr": str(config)}
         sd = model.state_dict() if hasattr(model, "state_dict") else dict(model)
         staged = self.stager.stage_state_dict(sd)
         self.plan_cache.get(staged)
@@ -405,9 +409,34 @@ class DistributedCheckpointer:
         return rank, world, payload, meta
 
     # ------------------------------------------------------------------ save
-    def save(self, step: int, model, optimizer=None, scheduler=None, extra: Optional[dict] = None,
-             ephemeral: bool = False, config: Optional[dict] = None) -> str:
-        """Synchronous save; every rank must call it."""
+    @staticmethod
+    def _save_args(args, kw):
+        """``(step, model, optimizer, scheduler, extra, ephemeral, config)`` from either calling convention: this
+        package's ``save(step, model, optimizer, scheduler, extra, ephemeral, config)`` or the reference's
+        ``save(model, optimizer, scheduler, step, config, extra, ephemeral)`` (checkpoint/distributed.py:444-453),
+        told apart by whether the first positional argument is a module."""
+        ours = ("step", "model", "optimizer", "scheduler", "extra", "ephemeral", "config")
+        theirs = ("model", "optimizer", "scheduler", "step", "config", "extra", "ephemeral")
+        names = theirs if (args and isinstance(args[0], torch.nn.Module)) else ours
+        if len(args) > len(names):
+            raise TypeError(f"save() takes at most {len(names)} positional arguments")
+        vals = dict(zip(names, args))
+        for k, v in kw.items():
+            if k not in ours:
+                raise TypeError(f"save() got an unexpected keyword argument {k!r}")
+            if k in vals:
+                raise TypeError(f"save() got multiple values for argument {k!r}")
+            vals[k] = v
+        if "model" not in vals:
+            raise TypeError("save() needs a model")
+        return (int(vals.get("step", 0)), vals["model"], vals.get("optimizer"), vals.get("scheduler"),
+                vals.get("extra"), bool(vals.get("ephemeral", False)), vals.get("config"))
+
+    def save(self, *args, **kw) -> str:
+        """Synchronous save; every rank must call it. ``save(step, model, optimizer=None, scheduler=None, extra=None,
+        ephemeral=False, config=None)``; the reference's positional order ``save(model, optimizer, scheduler, step, ...)``
+        is accepted as well."""
+        step, model, optimizer, scheduler, extra, ephemeral, config = self._save_args(args, kw)
         self.wait()
         rank, world, payload, meta = self._collect(step, model, optimizer, scheduler, extra, ephemeral, config)
         step_dir = self._step_dir(step)
@@ -432,10 +461,10 @@ class DistributedCheckpointer:
         self._save_count += 1
         return step_dir
 
-    def save_async(self, step: int, model, optimizer=None, scheduler=None, extra: Optional[dict] = None,
-                   ephemeral: bool = False, config: Optional[dict] = None) -> Future:
+    def save_async(self, *args, **kw) -> Future:
         """Stage on the caller, write in a worker process (a process rather than a thread keeps the
-        GIL free for the training loop). Multi-rank jobs publish in ``wait()``."""
+        GIL free for the training loop). Multi-rank jobs publish in ``wait()``. Arguments as for ``save``."""
+        step, model, optimizer, scheduler, extra, ephemeral, config = self._save_args(args, kw)
         self.wait()
         rank, world, payload, meta = self._collect(step, model, optimizer, scheduler, extra, ephemeral, config)
         step_dir = self._step_dir(step)

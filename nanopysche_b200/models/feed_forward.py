@@ -34,10 +34,11 @@ class FeedForward(nn.Module):
         self.d_model, self.hidden_size = d_model, hidden
         self.activation = ActivationFunction(activation)
         kw = dict(dtype=dtype, device=device)
-        # w1 and w3 are registered back to back so a flat parameter arena can fuse them into one GEMM
+        # registered in the reference's order (model/feed_forward.py: w1, w2, w3), which is the order optimizer state is
+        # stored in; the flat parameter arena lays w1 and w3 out back to back by itself (one gate|up GEMM)
         self.w1 = nn.Linear(d_model, hidden, bias=bias, **kw)
-        self.w3 = nn.Linear(d_model, hidden, bias=bias, **kw)
         self.w2 = nn.Linear(hidden, d_model, bias=bias, **kw)
+        self.w3 = nn.Linear(d_model, hidden, bias=bias, **kw)
         self._tp_size = 1
         self._tp_group = None
         self._fused_w13: Optional[torch.Tensor] = None

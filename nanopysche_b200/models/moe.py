@@ -416,52 +416,43 @@ class ExpertParallelConfig:
 # Experts
 # ------------------------------------------------------------------------------------------------
 class ExpertMLP(nn.Module):
-    """Shared-expert SwiGLU MLP (reference: model/moe.py:1164-1183)."""
+    """Shared-expert SwiGLU MLP with the reference's parameters (model/moe.py:1164-1183): ``w1``, ``w3`` and ``w2`` all
+    ``(hidden, d_model)``, ``forward(x) = (silu(x w1^T) * (x w3^T)) w2``. Names, shapes and registration order are the
+    reference's, so model and optimizer state move between the two code bases. On CUDA in bf16 the three products run
+    on the tcgen05 GEMM; ``w2`` is stored input-major, so it is handed over as a transposed copy (hidden x d_model
+    elements per forward, against a GEMM over all tokens)."""
 
-    def __init__(self, d_model: int, hidden_size: int, dtype=None, device=None):
+    def __init__(self, d_model: int, hidden_size: int, dtype=None, device=None, init_std: float = 0.01):
         super().__init__()
-        from .feed_forward import FeedForward
-
-        self.ffn = FeedForward(d_model=d_model, hidden_size=hidden_size, dtype=dtype, device=device)
-        self._register_load_state_dict_pre_hook(self._reference_keys_in)
-
-    # The reference keeps three bare parameters ``w1``, ``w3`` (hidden, d_model) and ``w2`` (hidden, d_model, applied as
-    # ``h @ w2``). The computation here runs through ``FeedForward`` (one fused gate|up GEMM), whose ``w2.weight`` is
-    # the transpose; the state dict is written and read in the reference's names and layout, so checkpoints move
-    # between the two code bases.
-    @property
-    def w1(self) -> torch.Tensor:
-        return self.ffn.w1.weight
-
-    @property
-    def w3(self) -> torch.Tensor:
-        return self.ffn.w3.weight
-
-    @property
-    def w2(self) -> torch.Tensor:
-        return self.ffn.w2.weight.t()
-
-    def state_dict(self, *args, destination=None, prefix="", keep_vars=False):
-        if destination is None:
-            from collections import OrderedDict
-
-            destination = OrderedDict()
-            destination._metadata = OrderedDict()
-        for name in ("w1", "w2", "w3"):
-            t = getattr(self, name)
-            destination[prefix + name] = t if keep_vars else t.detach()
-        return destination
+        self.d_model, self.hidden_size = d_model, hidden_size
+        kw = dict(dtype=dtype, device=device)
+        self.w1 = nn.Parameter(torch.empty(hidden_size, d_model, **kw))
+        self.w2 = nn.Parameter(torch.empty(hidden_size, d_model, **kw))
+        self.w3 = nn.Parameter(torch.empty(hidden_size, d_model, **kw))
+        for w in (self.w1, self.w2, self.w3):
+            nn.init.normal_(w, std=init_std)
+        self._register_load_state_dict_pre_hook(self._earlier_keys_in)
 
     @staticmethod
-    def _reference_keys_in(state_dict, prefix, *_):
+    def _earlier_keys_in(state_dict, prefix, *_):
+        """Checkpoints of this package written while the shared expert wrapped a ``FeedForward``
+        (``ffn.w1.weight`` ..., ``w2`` output-major, plus alias entries ``w1.weight`` ...)."""
         for name in ("w1", "w2", "w3"):
-            state_dict.pop(f"{prefix}{name}.weight", None)      # alias entries of this package's earlier checkpoints
-            if prefix + name in state_dict:
-                t = state_dict.pop(prefix + name)
-                state_dict[f"{prefix}ffn.{name}.weight"] = t.t() if name == "w2" else t
+            state_dict.pop(f"{prefix}{name}.weight", None)
+            old = f"{prefix}ffn.{name}.weight"
+            if old in state_dict:
+                t = state_dict.pop(old)
+                state_dict[prefix + name] = t.t() if name == "w2" else t
 
     def forward(self, x):
-        return self.ffn(x)
+        if _lib.on(x) and x.dtype == torch.bfloat16 and self.w1.dtype == torch.bfloat16:
+            from ..ops import activation as act_ops
+            from ..ops import gemm as gemm_ops
+
+            gu = torch.cat([gemm_ops.linear(x, self.w1), gemm_ops.linear(x, self.w3)], dim=-1)
+            return gemm_ops.linear(act_ops.glu(gu, "silu"), self.w2.t().contiguous())
+        w1, w2, w3 = (w if w.dtype == x.dtype else w.to(x.dtype) for w in (self.w1, self.w2, self.w3))
+        return (F.silu(x @ w1.t()) * (x @ w3.t())) @ w2
 
 
 @dataclass
@@ -524,12 +515,13 @@ class MoEBase(nn.Module):
         self.num_local_experts = num_experts
         self.expert_offset = 0
         kw = dict(dtype=dtype, device=device)
-        # flattened expert weights, expert e = rows [e*H, (e+1)*H); w1/w3 adjacent for the fused GEMM
+        # flattened expert weights, expert e = rows [e*H, (e+1)*H); registered in the reference's order
+        # (model/moe.py:1282-1284), which is the order optimizer state is stored in
         self.w1 = nn.Parameter(torch.empty(num_experts * self.hidden_size, d_model, **kw))
-        self.w3 = nn.Parameter(torch.empty(num_experts * self.hidden_size, d_model, **kw))
         self.w2 = nn.Parameter(torch.empty(num_experts * self.hidden_size, d_model, **kw))
+        self.w3 = nn.Parameter(torch.empty(num_experts * self.hidden_size, d_model, **kw))
         self._init_weights()
-        self.shared_expert = ExpertMLP(d_model, self.hidden_size, **kw) if shared_expert else None
+        self.shared_expert = ExpertMLP(d_model, self.hidden_size, **kw) if shared_expert else None   # reference init
         self.ep = ep or ExpertParallelConfig()
         self._use_grouped_gemm = True
         self.fp8_flow_moe_enabled = fp8_flow_moe

@@ -133,7 +133,7 @@ class ParamArena:
         self._epoch = 0
         self.regions: Dict[str, _Region] = {}
         seen = set()
-        for n, p in params:
+        for n, p in self._gate_up_adjacent(params):
             if id(p) in seen:
                 continue
             seen.add(id(p))
@@ -171,6 +171,25 @@ class ParamArena:
         self._fuse_views()
 
     # ------------------------------------------------------------------ construction
+    @staticmethod
+    def _gate_up_adjacent(params):
+        """The layout order: the model's parameter order, except that a feed-forward's up projection ``w3.weight``
+        follows its gate projection ``w1.weight`` directly (the module registers w1, w2, w3), so that ``_fuse_views`` can
+        hand the layer one ``[w1; w3]`` matrix for a single gate|up GEMM."""
+        by_name = dict(params)
+        out, done = [], set()
+        for n, p in params:
+            if n in done:
+                continue
+            out.append((n, p))
+            done.add(n)
+            if n.endswith("w1.weight"):
+                partner = n[:-len("w1.weight")] + "w3.weight"
+                if partner in by_name and partner not in done:
+                    out.append((partner, by_name[partner]))
+                    done.add(partner)
+        return out
+
     @staticmethod
     def _adjacent_ok(r: _Region, p) -> bool:
         # sizes that are multiples of ALIGN keep alignment without padding, so neighbours stay adjacent

@@ -163,6 +163,27 @@ def main(path):
     batches = [torch.randint(0, BASE["vocab_size"], (2, 32), generator=g) for _ in range(TRAIN_STEPS * ACCUM)]
     losses, final = run_trainer(m, batches, Trainer, TrainingConfig, ref_sched.CosineWithWarmup, create_adamw)
     res["trainer"] = dict(init=init, batches=batches, losses=losses, final=final)
+
+    # a checkpoint directory written by the reference's checkpointer after three optimizer steps
+    from nanopsyche.checkpoint.distributed import CheckpointConfig, DistributedCheckpointer
+
+    m = build(Transformer, ref_moe, "moe_shared_expert", seed=6)
+    opt = create_adamw(m, lr=1e-2, weight_decay=0.1)
+    sch = ref_sched.CosineWithWarmup(opt, warmup_steps=2, max_steps=6)
+    for _ in range(3):
+        m(ids, labels=ids)["loss"].backward()
+        opt.step()
+        sch.step()
+        opt.zero_grad()
+    ck_dir = os.path.join(os.path.dirname(os.path.abspath(path)), "reference_checkpoints")
+    ck = DistributedCheckpointer(CheckpointConfig(save_dir=ck_dir, pinned_memory=False))
+    ck.save(m, opt, sch, 3, None, {"tokens_seen": 192})
+    saved = {k: v.detach().clone() for k, v in m.state_dict().items()}
+    last_epoch, lr = sch.last_epoch, opt.param_groups[0]["lr"]
+    m(ids, labels=ids)["loss"].backward()      # the step after the checkpoint: what a resumed run has to reproduce
+    opt.step()
+    res["checkpoint"] = dict(dir=ck_dir, model=saved, last_epoch=last_epoch, lr=lr,
+                             after_next_step={k: v.detach().clone() for k, v in m.state_dict().items()})
     torch.save(res, path)
     return 0
 

@@ -30,19 +30,6 @@ def ref(tmp_path_factory):
     return torch.load(out, weights_only=False)
 
 
-def _to_reference_names(model):
-    """This package's ``named_parameters`` under the reference's names and layouts (only the shared expert differs:
-    it computes through a FeedForward, whose ``w2.weight`` is the transpose of the reference's ``w2``)."""
-    out = {}
-    for n, p in model.named_parameters():
-        if ".shared_expert.ffn." in n:
-            short = n.replace(".ffn.", ".").rsplit(".weight", 1)[0]
-            out[short] = p.grad.t() if short.endswith(".w2") else p.grad
-        else:
-            out[n] = p.grad
-    return out
-
-
 @pytest.mark.parametrize("case", list(oracle.MODEL_CASES))
 def test_model_matches_the_reference(ref, case):
     from nanopysche_b200.models import moe as our_moe
@@ -50,7 +37,8 @@ def test_model_matches_the_reference(ref, case):
 
     want = ref["models"][case]
     model = oracle.build(Transformer, our_moe, case, seed=99)      # other initial weights: everything comes from the load
-    assert set(model.state_dict().keys()) == set(want["state_dict"].keys())
+    # same keys in the same order: torch optimizers store their state by parameter position
+    assert list(model.state_dict().keys()) == list(want["state_dict"].keys())
     for k, v in model.state_dict().items():
         assert v.shape == want["state_dict"][k].shape, k
     model.load_state_dict(want["state_dict"], strict=True)
@@ -59,7 +47,8 @@ def test_model_matches_the_reference(ref, case):
     got = oracle.run_model(model, ref["ids"])
     assert torch.allclose(got["logits"], want["logits"], atol=2e-5, rtol=1e-4), case
     assert abs(float(got["loss"]) - float(want["loss"])) < 1e-5
-    grads = _to_reference_names(model)
+    grads = {n: p.grad for n, p in model.named_parameters()}
+    assert list(grads) == [k for k in want["state_dict"] if k in grads]
     assert set(want["grads"]) <= set(grads)
     for n, g in want["grads"].items():
         assert grads[n] is not None, n
@@ -149,3 +138,38 @@ def test_trainer_trajectory_matches_the_reference(ref):
         assert a == pytest.approx(b / oracle.ACCUM, rel=1e-5)
     for k, v in t["final"].items():
         assert torch.allclose(final[k], v, atol=1e-5, rtol=1e-4), k
+
+
+def test_checkpoint_written_by_the_reference_loads_here(ref, tmp_path):
+    """A checkpoint directory from the reference's ``DistributedCheckpointer`` (model with MoE layers and shared
+    experts, its AdamW, its scheduler) restores model, optimizer moments and schedule position here; saving again in the
+    reference's positional order ``save(model, optimizer, scheduler, step)`` writes the same file set."""
+    from nanopysche_b200.checkpoint.distributed import CheckpointConfig, DistributedCheckpointer
+    from nanopysche_b200.models import moe as our_moe
+    from nanopysche_b200.models.transformer import Transformer
+    from nanopysche_b200.optim.adamw import create_adamw
+    from nanopysche_b200.train.scheduler import CosineWithWarmup
+
+    c = ref["checkpoint"]
+    m = oracle.build(Transformer, our_moe, "moe_shared_expert", seed=123)
+    opt = create_adamw(m, lr=1e-2, weight_decay=0.1)
+    sch = CosineWithWarmup(opt, warmup_steps=2, max_steps=6)
+    ck = DistributedCheckpointer(CheckpointConfig(save_dir=c["dir"], pinned_memory=False))
+    meta = ck.load(model=m, optimizer=opt, scheduler=sch)
+    assert meta["step"] == 3 and meta["extra"]["tokens_seen"] == 192
+    for k, v in m.state_dict().items():
+        assert torch.equal(v, c["model"][k]), k
+    assert sch.last_epoch == c["last_epoch"] and opt.param_groups[0]["lr"] == pytest.approx(c["lr"])
+    for p_, st in opt.state.items():                     # every moment landed on the parameter of its shape
+        assert st["exp_avg"].shape == p_.shape
+    m.train()
+    m(ref["ids"], labels=ref["ids"])["loss"].backward()  # the resumed run's next step equals the reference's
+    opt.step()
+    for k, v in m.state_dict().items():
+        assert torch.allclose(v, c["after_next_step"][k], atol=1e-6, rtol=1e-5), k
+    ck2 = DistributedCheckpointer(CheckpointConfig(save_dir=str(tmp_path), pinned_memory=False))
+    opt.zero_grad()
+    d = ck2.save(m, opt, sch, 4, None, {"tokens_seen": 256})
+    assert os.path.basename(d) == "step_000004"
+    want_files = {f for f in os.listdir(os.path.join(c["dir"], "step_000003")) if not f.endswith("dataloader.json")}
+    assert want_files <= set(os.listdir(d))

@@ -172,6 +172,26 @@ def test_arena_adamw_cpu_matches_torch_adamw():
     assert sd["step"] == 3 and arena.num_params() == sum(p.numel() for p in m2.parameters())
 
 
+def test_arena_lays_gate_and_up_projections_back_to_back():
+    """The feed-forward registers w1, w2, w3 (the reference's order, which optimizer state follows); the arena still
+    places w3 right behind w1, so that one ``[w1; w3]`` view serves the gate|up GEMM."""
+    m = tiny_model()
+    names = [n for n, _ in m.named_parameters()]
+    i1, i2, i3 = (names.index(f"blocks.0.feed_forward.{w}.weight") for w in ("w1", "w2", "w3"))
+    assert i1 < i2 < i3
+    arena = ParamArena(m)
+    for blk in m.blocks.values():
+        ff = blk.feed_forward
+        if not hasattr(ff, "w3") or not hasattr(ff.w1, "weight"):
+            continue
+        w13 = arena._fused_view([ff.w1.weight, ff.w3.weight])
+        assert w13 is not None and torch.equal(w13, torch.cat([ff.w1.weight, ff.w3.weight], 0))
+        assert w13.main_grad.shape == w13.shape and w13._covers[0] is ff.w1.weight
+        att = blk.attention
+        qkv = arena._fused_view([att.w_q.weight, att.w_k.weight, att.w_v.weight])
+        assert qkv is not None and torch.equal(qkv, torch.cat([att.w_q.weight, att.w_k.weight, att.w_v.weight], 0))
+
+
 def test_diloco_compressor_roundtrip_and_error_feedback():
     ps = [torch.nn.Parameter(torch.zeros(1000))]
     before = torch.random.get_rng_state()
