@@ -20,10 +20,10 @@ from typing import Optional
 import torch
 
 MODEL_PRESETS = {
-    "125m": dict(d_model=768, n_layers=12, n_heads=12, ffn_hidden=2048),
-    "350m": dict(d_model=1024, n_layers=24, n_heads=16, ffn_hidden=2816),
-    "1b": dict(d_model=2048, n_layers=24, n_heads=32, ffn_hidden=5632),
-    "7b": dict(d_model=4096, n_layers=32, n_heads=32, ffn_hidden=11008),
+    "125m": dict(d_model=768, n_layers=12, n_heads=12, n_kv_heads=12, ffn_hidden=2048),
+    "350m": dict(d_model=1024, n_layers=24, n_heads=16, n_kv_heads=16, ffn_hidden=2816),
+    "1b": dict(d_model=2048, n_layers=24, n_heads=32, n_kv_heads=32, ffn_hidden=5632),
+    "7b": dict(d_model=4096, n_layers=32, n_heads=32, n_kv_heads=32, ffn_hidden=11008),
     # the benchmark shapes: 16 layers, 16 query / 8 KV heads of dim 128
     "1b-gqa": dict(d_model=2048, n_layers=16, n_heads=16, n_kv_heads=8, ffn_hidden=5632, rope_base=10000.0,
                    qk_norm=False),

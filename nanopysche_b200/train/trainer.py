@@ -643,7 +643,7 @@ class Trainer:
                     self.data_loader.set_epoch(getattr(self.data_loader, "epoch", 0) + 1)
                 self._data_iter = iter(self.data_loader)
                 return self._as_pair(next(self._data_iter))
-        ids = torch.randint(0, c.vocab_size, (c.micro_batch_size, c.sequence_length))
+        ids = torch.randint(0, self.get_vocab_size(), (c.micro_batch_size, c.sequence_length))
         return ids, ids.clone()
 
     # ------------------------------------------------------------------ checkpoints

@@ -91,6 +91,31 @@ def run_trainer(model, batches, trainer_cls, config_cls, scheduler_cls, create_a
     return losses, {k: v.detach().clone() for k, v in model.state_dict().items()}
 
 
+def run_fit_with_callbacks(model, trainer_cls, config_cls, callback_base, callbacks, create_adamw, save_dir):
+    """``Trainer.fit()`` for three steps on the Trainer's own synthetic batches with the stock monitor callbacks and
+    a tap: returns the metric names that reach ``log_metrics`` and the order of the lifecycle hooks."""
+    seen, events = {}, []
+
+    class Tap(callback_base):
+        def log_metrics(self, metrics, step, trainer=None):
+            seen.update({k: type(v).__name__ for k, v in metrics.items()})
+
+    for hook in ("pre_train", "post_train", "pre_load_batch", "pre_step", "post_train_batch", "pre_optim_step",
+                 "post_step", "pre_log_metrics", "post_log_metrics", "close"):
+        setattr(Tap, hook, (lambda h: lambda self, *a, **k: events.append(h))(hook))
+    opt = create_adamw(model, lr=1e-2)
+    tc = config_cls(global_batch_size=2 * 32, micro_batch_size=2, sequence_length=32, max_steps=3, dtype=torch.float32,
+                    save_interval=10 ** 9, log_interval=1, max_grad_norm=1.0, save_dir=save_dir)
+    tr = trainer_cls(tc, model, opt, None, None, [cb() for cb in callbacks] + [Tap()])
+    tr.device = torch.device("cpu")
+    import contextlib
+    import io
+
+    with contextlib.redirect_stdout(io.StringIO()):
+        tr.fit()
+    return sorted(seen), events
+
+
 def main(path):
     if not os.path.isdir(os.path.join(REF, "nanopsyche")):
         print("reference not installed")
@@ -184,6 +209,15 @@ def main(path):
     opt.step()
     res["checkpoint"] = dict(dir=ck_dir, model=saved, last_epoch=last_epoch, lr=lr,
                              after_next_step={k: v.detach().clone() for k, v in m.state_dict().items()})
+
+    from nanopsyche.train.callbacks import GPUMemoryMonitorCallback, SpeedMonitorCallback, StabilityMonitorCallback
+    from nanopsyche.train.callbacks.base import Callback
+
+    names, events = run_fit_with_callbacks(
+        build(Transformer, ref_moe, "dense"), Trainer, TrainingConfig, Callback,
+        [SpeedMonitorCallback, StabilityMonitorCallback, GPUMemoryMonitorCallback], create_adamw,
+        os.path.join(os.path.dirname(os.path.abspath(path)), "fit_ckpt"))
+    res["fit"] = dict(metric_names=names, events=events)
     torch.save(res, path)
     return 0
 

@@ -173,3 +173,23 @@ def test_checkpoint_written_by_the_reference_loads_here(ref, tmp_path):
     assert os.path.basename(d) == "step_000004"
     want_files = {f for f in os.listdir(os.path.join(c["dir"], "step_000003")) if not f.endswith("dataloader.json")}
     assert want_files <= set(os.listdir(d))
+
+
+def test_fit_emits_the_reference_metric_names_and_hook_order(ref, tmp_path):
+    """``Trainer.fit()`` on its own synthetic batches with the stock monitor callbacks: every metric name the
+    reference's run reports is reported here, and the lifecycle hooks fire in the reference's order (plus ``pre_step``
+    and ``post_train``, which the reference declares in its base class and never calls)."""
+    from nanopysche_b200.models import moe as our_moe
+    from nanopysche_b200.models.transformer import Transformer
+    from nanopysche_b200.optim.adamw import create_adamw
+    from nanopysche_b200.train.callbacks import (GPUMemoryMonitorCallback, SpeedMonitorCallback,
+                                                 StabilityMonitorCallback)
+    from nanopysche_b200.train.callbacks.base import Callback
+    from nanopysche_b200.train.trainer import Trainer, TrainingConfig
+
+    names, events = oracle.run_fit_with_callbacks(
+        oracle.build(Transformer, our_moe, "dense"), Trainer, TrainingConfig, Callback,
+        [SpeedMonitorCallback, StabilityMonitorCallback, GPUMemoryMonitorCallback], create_adamw, str(tmp_path))
+    assert set(ref["fit"]["metric_names"]) <= set(names), set(ref["fit"]["metric_names"]) - set(names)
+    assert [e for e in events if e not in ("pre_step", "post_train")] == ref["fit"]["events"]
+    assert events.count("pre_step") == 3 and events[-2:] == ["post_train", "close"]
