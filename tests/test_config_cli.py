@@ -60,7 +60,7 @@ def test_experiment_build():
 
 
 def test_presets_and_parser():
-    assert MODEL_PRESETS["125m"] == dict(d_model=768, n_layers=12, n_heads=12, ffn_hidden=2048)
+    assert MODEL_PRESETS["125m"] == dict(d_model=768, n_layers=12, n_heads=12, n_kv_heads=12, ffn_hidden=2048)
     assert MODEL_PRESETS["7b"]["ffn_hidden"] == 11008 and MODEL_PRESETS["1b"]["n_heads"] == 32
     p = build_parser()
     a = p.parse_args(["train", "--model", "350m", "--use-moe", "--num-experts", "4", "--top-k", "1", "--fp8-recipe",
