@@ -14,7 +14,13 @@ Public names and constructor signatures follow the reference. What differs, by d
   its experts is dropped whole, in index order) but is computed with prefix sums instead of a Python
   loop over experts.
 * ``post_batch`` moves the DeepSeek-V3 bias *against* the load (over-loaded experts are pushed
-  down); ``bias_update_sign=+1`` restores the reference's direction.
+  down); ``bias_update_sign=+1`` restores the reference's direction. The load fraction is the expert's share of
+  all assignments (the shares sum to 1, so the update has zero mean); the reference divides the counts by the
+  number of tokens (shares sum to top-k), which is this update with ``gamma`` times top-k plus a shift common to all
+  experts - invisible to top-k selection and softmax gating, a drift under sigmoid gating.
+* ``last_dropped`` / ``total_dropped`` / ``drop_rate`` count dropped *tokens*; the reference adds up the per-expert
+  overflows, which counts a token once per over-full expert it chose (its rate can exceed 1). ``per_expert_drops``
+  and the adaptive-capacity estimate are the reference's.
 """
 from __future__ import annotations
 

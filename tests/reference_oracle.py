@@ -116,6 +116,31 @@ def run_fit_with_callbacks(model, trainer_cls, config_cls, callback_base, callba
     return sorted(seen), events
 
 
+def run_moe_sequence(moe_module, state_dict=None, bias_gamma=None, sign=None, steps=8):
+    """Eight training forwards of one MoE layer with capacity 1.0 and adaptive capacity: outputs, drop statistics, the
+    adapted capacity factor and (with ``bias_gamma``) the router's score bias after each ``post_batch``."""
+    torch.manual_seed(0)
+    m = moe_module.MoEBase(d_model=32, hidden_size=64, num_experts=4, top_k=2, capacity_factor=1.0,
+                           adaptive_capacity=True, bias_gamma=bias_gamma)
+    if sign is not None:
+        m.router.config.bias_update_sign = sign
+    if state_dict is not None:
+        m.load_state_dict(state_dict)
+    sd = {k: v.detach().clone() for k, v in m.state_dict().items()}
+    g = torch.Generator().manual_seed(1)
+    m.train()
+    rows = []
+    for _ in range(steps):
+        x = torch.randn(2, 16, 32, generator=g)
+        y = m(x)
+        m.router.post_batch()
+        rows.append(dict(y=y.detach().clone(), per_expert=[int(v) for v in m.per_expert_drops.tolist()],
+                         capacity_factor=float(m.capacity_factor), ema=float(m.adaptive_drop_rate_ema),
+                         routed=int(m.total_tokens_routed), aux=float(m.aux_loss.detach()),
+                         bias=None if m.router.score_bias is None else m.router.score_bias.detach().clone()))
+    return sd, rows
+
+
 def main(path):
     if not os.path.isdir(os.path.join(REF, "nanopsyche")):
         print("reference not installed")
@@ -218,6 +243,10 @@ def main(path):
         [SpeedMonitorCallback, StabilityMonitorCallback, GPUMemoryMonitorCallback], create_adamw,
         os.path.join(os.path.dirname(os.path.abspath(path)), "fit_ckpt"))
     res["fit"] = dict(metric_names=names, events=events)
+
+    sd, rows = run_moe_sequence(ref_moe)
+    sd_b, rows_b = run_moe_sequence(ref_moe, bias_gamma=0.05)
+    res["moe_sequence"] = dict(state_dict=sd, rows=rows, state_dict_bias=sd_b, rows_bias=rows_b)
     torch.save(res, path)
     return 0
 

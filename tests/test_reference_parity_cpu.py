@@ -193,3 +193,25 @@ def test_fit_emits_the_reference_metric_names_and_hook_order(ref, tmp_path):
     assert set(ref["fit"]["metric_names"]) <= set(names), set(ref["fit"]["metric_names"]) - set(names)
     assert [e for e in events if e not in ("pre_step", "post_train")] == ref["fit"]["events"]
     assert events.count("pre_step") == 3 and events[-2:] == ["post_train", "close"]
+
+
+def test_moe_layer_over_several_steps_matches_the_reference(ref):
+    """Eight training forwards of a MoE layer with capacity drops and adaptive capacity: outputs, per-expert drop
+    counts, the adapted capacity factor and its drop-rate average follow the reference step by step. With the score bias
+    on, the reference's update ``bias += gamma * (count / tokens - 1 / E)`` is, up to a shift common to all experts
+    (which top-k selection and softmax gating do not see), this package's ``sign * gamma * (count / assignments - 1 / E)``
+    with ``sign = +1`` and ``gamma`` times top-k: run that way, routing and outputs stay the reference's."""
+    from nanopysche_b200.models import moe as our_moe
+
+    q = ref["moe_sequence"]
+    _, rows = oracle.run_moe_sequence(our_moe, q["state_dict"])
+    for i, (a, b) in enumerate(zip(rows, q["rows"])):
+        assert torch.allclose(a["y"], b["y"], atol=1e-6), i
+        assert a["per_expert"] == b["per_expert"] and a["routed"] == b["routed"], i
+        assert a["capacity_factor"] == pytest.approx(b["capacity_factor"]) and a["ema"] == pytest.approx(b["ema"]), i
+        assert a["aux"] == pytest.approx(b["aux"], rel=1e-5), i
+    _, rows = oracle.run_moe_sequence(our_moe, q["state_dict_bias"], bias_gamma=0.05 * 2, sign=+1.0)
+    for i, (a, b) in enumerate(zip(rows, q["rows_bias"])):
+        assert torch.allclose(a["bias"] - a["bias"].mean(), b["bias"] - b["bias"].mean(), atol=1e-6), i
+        assert torch.allclose(a["y"], b["y"], atol=1e-6), i
+        assert a["per_expert"] == b["per_expert"], i
