@@ -9,7 +9,7 @@ box every dimension has the same all-to-all bandwidth, so the order only fixes r
 from __future__ import annotations
 
 import logging
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import List, Optional
 
 import torch.distributed as dist
@@ -233,7 +233,8 @@ class ParallelDims:
     pp: int = 1
     cp: int = 1
     ep: int = 1
-    _mesh: Optional[DeviceMesh] = None
+    _world_size: Optional[int] = field(default=None, repr=False)
+    _mesh: Optional[DeviceMesh] = field(default=None, repr=False)
 
     def __post_init__(self):
         self._validate()
@@ -259,14 +260,18 @@ class ParallelDims:
         if world_size % rest:
             raise ValueError(f"world_size {world_size} not divisible by tp*pp*cp*ep = {rest}")
         dp = world_size // rest
+        self._world_size = world_size
         if self.dp_shard == -1:
             if dp % self.dp_replicate:
                 raise ValueError("dp_replicate does not divide the data-parallel size")
             self.dp_shard = dp // self.dp_replicate
-        else:
+        elif self.dp_replicate == 1:
             if dp % self.dp_shard:
                 raise ValueError("dp_shard does not divide the data-parallel size")
             self.dp_replicate = dp // self.dp_shard
+        elif self.world_size != world_size:
+            # both data-parallel factors were given: they have to fit (reference: parallel.py:273-297)
+            raise ValueError(f"parallel dims multiply to {self.world_size}, world_size is {world_size}")
         return self
 
     @property
