@@ -1,6 +1,7 @@
 """Token datasets and loaders (reference: train/data.py:33-158).
 
-``DistributedDataset`` cuts a flat token array into fixed-length ``(input_ids, labels)`` pairs. Labels
+``DistributedDataset`` cuts a flat token array into fixed-length ``(input_ids, labels)`` pairs (``Batch``: unpacks as a
+pair and indexes by the reference's keys). Labels
 are the *same* window as the inputs (the model shifts by one internally); the reference pre-shifts
 them in the dataset and the model shifts again. ``DistributedDataLoader`` is an iterator (the
 reference's is only iterable although its Trainer calls ``next`` on it), shards over the
@@ -9,11 +10,43 @@ restarts with a new epoch seed when exhausted.
 """
 from __future__ import annotations
 
+from collections import namedtuple
 from typing import Iterator, Optional
 
 import numpy as np
 import torch
 from torch.utils.data import DataLoader, Dataset, DistributedSampler, RandomSampler
+
+
+class Batch(namedtuple("Batch", ("input_ids", "labels"))):
+    """One sample or batch. A pair - ``input_ids, labels = batch`` - that also reads like the reference's mapping:
+    ``batch["input_ids"]``, ``batch.get("labels")``, ``batch.keys()`` (train/data.py:63-71 returns a dict). A named tuple
+    keeps its type through ``default_collate`` and the DataLoader's memory pinning."""
+
+    __slots__ = ()
+
+    def __getitem__(self, key):
+        if isinstance(key, str):
+            try:
+                return tuple.__getitem__(self, self._fields.index(key))
+            except ValueError:
+                raise KeyError(key) from None
+        return tuple.__getitem__(self, key)
+
+    def __contains__(self, key):
+        return key in self._fields if isinstance(key, str) else any(key is v for v in self)
+
+    def get(self, key, default=None):
+        return self[key] if key in self._fields else default
+
+    def keys(self):
+        return list(self._fields)
+
+    def values(self):
+        return list(self)
+
+    def items(self):
+        return list(zip(self._fields, self))
 
 
 class DistributedDataset(Dataset):
@@ -35,7 +68,7 @@ class DistributedDataset(Dataset):
         s = i * self.seq_len
         window = np.asarray(self.tokens[s:s + self.seq_len]).astype(np.int64)
         ids = torch.from_numpy(window)
-        return ids, ids.clone()
+        return Batch(ids, ids.clone())
 
 
 class DistributedDataLoader:

@@ -121,8 +121,13 @@ def test_dataset_and_loader_iterator_protocol():
     ids, labels = ds[3]
     assert len(ds) == 99 and ids.tolist() == list(range(30, 40)) and torch.equal(ids, labels)
     dl = DistributedDataLoader(ds, 4, shuffle=False, dp_rank=1, dp_world=2)
-    a, _ = next(dl)
+    first = next(dl)
+    a, _ = first
     assert a.shape == (4, 10) and a[0, 0].item() == 10  # rank 1 of 2 takes odd samples
+    # the reference's mapping access on samples and collated batches alike
+    assert first["input_ids"] is a and torch.equal(first["labels"], first.labels) and "labels" in first
+    assert first.keys() == ["input_ids", "labels"] and first.get("attention_mask") is None
+    assert torch.equal(ds[3]["input_ids"], ids) and dict(ds[3].items())["labels"] is not None
     n = len(dl)
     for _ in range(n + 2):  # runs past the end of an epoch without StopIteration
         next(dl)
