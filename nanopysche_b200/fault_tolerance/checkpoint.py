@@ -135,7 +135,13 @@ class FaultTolerantCheckpointer:
             out.append((step, p))
         return out
 
-    def find_latest_checkpoint(self) -> Optional[str]:
+    def find_latest_checkpoint(self) -> Optional[int]:
+        """Step number of the newest loadable checkpoint, ``None`` without one (reference:
+        fault_tolerance/checkpoint.py:124-129 returns the step, too); ``find_latest_checkpoint_dir`` gives its path."""
+        path = self.find_latest_checkpoint_dir()
+        return None if path is None else int(os.path.basename(path).split("_")[1])
+
+    def find_latest_checkpoint_dir(self) -> Optional[str]:
         """Newest checkpoint that EVERY rank can load: each rank lists the steps whose own shard is intact and the
         ranks agree on the newest common one, so a truncated shard on one rank moves all ranks back together."""
         mine = self._loadable_steps()
@@ -149,7 +155,7 @@ class FaultTolerantCheckpointer:
 
     def resume(self, model, optimizer=None, scheduler=None) -> int:
         self.wait()
-        path = self.find_latest_checkpoint()
+        path = self.find_latest_checkpoint_dir()
         if path is None:
             return 0
         rank, _ = self._rank_world()

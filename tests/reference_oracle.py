@@ -244,6 +244,16 @@ def main(path):
         os.path.join(os.path.dirname(os.path.abspath(path)), "fit_ckpt"))
     res["fit"] = dict(metric_names=names, events=events)
 
+    # the fault-tolerant checkpointer's directory, written by the reference
+    from nanopsyche.fault_tolerance.checkpoint import FaultTolerantCheckpointer
+
+    ft_dir = os.path.join(os.path.dirname(os.path.abspath(path)), "reference_ft")
+    ft = FaultTolerantCheckpointer(ft_dir, save_interval=2, async_save=False)
+    for step in (2, 3, 4):
+        ft.save(m, opt, step)                       # step 3 is off the interval and skipped
+    res["ft"] = dict(dir=ft_dir, latest=ft.find_latest_checkpoint(),
+                     model={k: v.detach().clone() for k, v in m.state_dict().items()})
+
     sd, rows = run_moe_sequence(ref_moe)
     sd_b, rows_b = run_moe_sequence(ref_moe, bias_gamma=0.05)
     res["moe_sequence"] = dict(state_dict=sd, rows=rows, state_dict_bias=sd_b, rows_bias=rows_b)

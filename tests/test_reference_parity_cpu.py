@@ -215,3 +215,21 @@ def test_moe_layer_over_several_steps_matches_the_reference(ref):
         assert torch.allclose(a["bias"] - a["bias"].mean(), b["bias"] - b["bias"].mean(), atol=1e-6), i
         assert torch.allclose(a["y"], b["y"], atol=1e-6), i
         assert a["per_expert"] == b["per_expert"], i
+
+
+def test_fault_tolerant_checkpoint_of_the_reference_resumes_here(ref):
+    from nanopysche_b200.fault_tolerance.checkpoint import FaultTolerantCheckpointer
+    from nanopysche_b200.models import moe as our_moe
+    from nanopysche_b200.models.transformer import Transformer
+    from nanopysche_b200.optim.adamw import create_adamw
+
+    f = ref["ft"]
+    m = oracle.build(Transformer, our_moe, "moe_shared_expert", seed=31)
+    opt = create_adamw(m, lr=1e-2, weight_decay=0.1)
+    ft = FaultTolerantCheckpointer(f["dir"], save_interval=2, async_save=False)
+    assert ft.find_latest_checkpoint() == f["latest"] == 4
+    assert ft.resume(m, opt) == 4
+    for k, v in m.state_dict().items():
+        assert torch.equal(v, f["model"][k]), k
+    for p_, st in opt.state.items():
+        assert st["exp_avg"].shape == p_.shape
