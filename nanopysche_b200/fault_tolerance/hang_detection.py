@@ -67,13 +67,20 @@ class HangDetector:
                 return
 
     @staticmethod
-    def check_collective_timeout(fn: Callable, *a, **k):
-        """Run ``fn``; exceptions that look like a collective timeout become ``CommTimeoutError``."""
+    def check_collective_timeout(collective_fn: Callable, timeout: float = 60.0, *, raise_on_timeout: bool = False) -> bool:
+        """Run ``collective_fn()``; returns True when it ended in what looks like a collective timeout, False when it
+        completed (reference: fault_tolerance/hang_detection.py:113-129); any other exception propagates. With
+        ``raise_on_timeout`` the timeout is raised as ``CommTimeoutError`` instead. ``timeout`` is accepted for the
+        reference's signature: how long a collective may take is a property of its process group
+        (``init_process_group(timeout=...)``), not of this call."""
         try:
-            return fn(*a, **k)
+            collective_fn()
+            return False
         except Exception as e:  # noqa: BLE001
             if "timeout" in str(e).lower() or "timed out" in str(e).lower():
-                raise CommTimeoutError(str(e)) from e
+                if raise_on_timeout:
+                    raise CommTimeoutError(str(e)) from e
+                return True
             raise
 
 
@@ -161,10 +168,13 @@ class HeartbeatCoordinator:
             self._thread.join(timeout=self.check_interval + 1)
             self._thread = None
 
-    def sync_heartbeats(self) -> List[int]:
-        """One monitoring pass (rank 0): returns the ranks whose counter has stalled."""
+    def sync_heartbeats(self) -> dict:
+        """One monitoring pass: every rank's step counter as ``{rank: counter}`` (-1: never reported), as the reference
+        returns it (fault_tolerance/hang_detection.py:189-196) - read from the store, though, not by an all-gather that
+        a hung rank would block. The ranks whose counter has not moved for ``hang_timeout`` are left in
+        ``stalled_ranks``."""
         now = time.monotonic()
-        stalled = []
+        stalled, counters = [], {}
         for r in range(self.world_size):
             key = f"{self.prefix}/{r}"
             try:
@@ -174,17 +184,19 @@ class HeartbeatCoordinator:
                     val = int(self.store.get(key).decode())
             except Exception:  # noqa: BLE001
                 val = -1
+            counters[r] = val
             prev = self._seen.get(r)
             if prev is None or prev[0] != val:
                 self._seen[r] = (val, now)
             elif now - prev[1] >= self.hang_timeout:
                 stalled.append(r)
         self.stalled_ranks = stalled
-        return stalled
+        return counters
 
     def _run(self):
         while not self._stop.wait(self.check_interval):
-            stalled = self.sync_heartbeats()
+            self.sync_heartbeats()
+            stalled = self.stalled_ranks
             if stalled:
                 if self.on_stall is not None:
                     self.on_stall(stalled)

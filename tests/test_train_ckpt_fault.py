@@ -370,8 +370,12 @@ def test_hang_detector_fires_and_heartbeat_prevents():
     time.sleep(0.6)
     hd.stop()
     assert fired and hd.hang_detected
+    def timed_out():
+        raise RuntimeError("NCCL watchdog timeout")
+
+    assert hd.check_collective_timeout(timed_out, timeout=1.0) is True and hd.check_collective_timeout(lambda: 3) is False
     with pytest.raises(CommTimeoutError):
-        HangDetector.check_collective_timeout(lambda: (_ for _ in ()).throw(RuntimeError("NCCL watchdog timeout")))
+        HangDetector.check_collective_timeout(timed_out, raise_on_timeout=True)
     with pytest.raises(ValueError):
         HangDetector.check_collective_timeout(lambda: (_ for _ in ()).throw(ValueError("other")))
 
@@ -399,11 +403,15 @@ def _hb_worker(rank, world):
         if rank == 0 or s < 2:  # rank 1 stops making progress after its first step
             hb.heartbeat(s)
         time.sleep(0.1)
-    stalled = hb.sync_heartbeats() if rank == 0 else []
+    stalled = []
+    if rank == 0:
+        hb.sync_heartbeats()
     time.sleep(0.35)
     if rank == 0:
         hb.heartbeat(99)
-        stalled = hb.sync_heartbeats()
+        counters = hb.sync_heartbeats()
+        assert counters[0] == 99 and counters[1] == 1      # every rank's counter, as the reference returns them
+        stalled = hb.stalled_ranks
     import torch.distributed as dist
     dist.barrier()
     return stalled
