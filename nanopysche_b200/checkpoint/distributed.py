@@ -22,6 +22,7 @@ import shutil
 import time
 from concurrent.futures import Future, ProcessPoolExecutor
 from dataclasses import asdict, dataclass, field
+from pathlib import Path
 from typing import Any, Dict, List, Optional
 
 import torch
@@ -432,7 +433,7 @@ class DistributedCheckpointer:
         return (int(vals.get("step", 0)), vals["model"], vals.get("optimizer"), vals.get("scheduler"),
                 vals.get("extra"), bool(vals.get("ephemeral", False)), vals.get("config"))
 
-    def save(self, *args, **kw) -> str:
+    def save(self, *args, **kw) -> Path:
         """Synchronous save; every rank must call it. ``save(step, model, optimizer=None, scheduler=None, extra=None,
         ephemeral=False, config=None)``; the reference's positional order ``save(model, optimizer, scheduler, step, ...)``
         is accepted as well."""
@@ -459,7 +460,7 @@ class DistributedCheckpointer:
             self._cleanup_checkpoints()
         self._barrier()
         self._save_count += 1
-        return step_dir
+        return Path(step_dir)
 
     def save_async(self, *args, **kw) -> Future:
         """Stage on the caller, write in a worker process (a process rather than a thread keeps the

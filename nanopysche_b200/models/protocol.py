@@ -41,5 +41,14 @@ def warn_unsupported_parallelism(model: nn.Module, **kw) -> list[str]:
     return missing
 
 
-def count_parameters(model: nn.Module, trainable_only: bool = False) -> int:
-    return sum(p.numel() for p in model.parameters() if p.requires_grad or not trainable_only)
+def count_parameters(model: nn.Module, trainable_only: bool = False) -> dict:
+    """``{"num_params", "num_non_embed_params"}`` (reference: model/protocol.py:81-91); the embedding is looked up as
+    ``model.embeddings`` or ``model.embed``."""
+    num = sum(p.numel() for p in model.parameters() if p.requires_grad or not trainable_only)
+    emb = 0
+    for name in ("embeddings", "embed"):
+        w = getattr(getattr(model, name, None), "weight", None)
+        if w is not None and (w.requires_grad or not trainable_only):
+            emb = w.numel()
+            break
+    return {"num_params": num, "num_non_embed_params": num - emb}

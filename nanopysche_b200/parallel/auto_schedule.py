@@ -90,11 +90,13 @@ class AutoScheduleGenerator:
         hidden = sum(min(s.comm_time, s.fwd_time) for s in self.profiles)
         return hidden / comm
 
-    def validate_memory(self) -> bool:
-        """1F1B keeps at most ``p - rank`` microbatches of activations alive on a rank (DualPipe: about
-        ``p + 1`` over both directions); they must fit the per-GPU budget."""
+    def validate_memory(self) -> tuple:
+        """``(fits, peak_activations_gb)`` as in the reference (distributed/auto_schedule.py:249-259). 1F1B keeps at
+        most ``p - rank`` microbatches of activations alive on a rank (DualPipe: about ``p + 1`` over both
+        directions); the largest of those has to fit the per-GPU budget. (The reference charges every rank
+        ``min(p, m)`` microbatches of the largest stage, the first rank's figure.)"""
         worst = 0.0
         for r, s in enumerate(self.profiles):
             inflight = (self.p + 1) if self.config.dualpipe_ratio > 0 else (self.p - r)
             worst = max(worst, s.mem_gb * min(inflight, self.m))
-        return worst <= self.config.memory_budget_gb
+        return worst <= self.config.memory_budget_gb, worst

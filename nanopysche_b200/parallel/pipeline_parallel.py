@@ -113,7 +113,36 @@ class PipelineStage(nn.Module):
 F, B, BI, W = ScheduleType.FWD, ScheduleType.BWD, ScheduleType.BWD_INPUT, ScheduleType.BWD_WEIGHT
 
 
+class PerRankSchedule(list):
+    """What every generator returns: ``schedule[rank]`` is that rank's action list. Also reads like the mapping that
+    the reference's DualPipe generator returns (``for rank, actions in schedule.items()``;
+    distributed/pipeline_parallel.py), so code written against either shape keeps working."""
+
+    def keys(self):
+        return range(len(self))
+
+    def values(self):
+        return list(self)
+
+    def items(self):
+        return list(enumerate(self))
+
+    def get(self, rank, default=None):
+        return self[rank] if isinstance(rank, int) and 0 <= rank < len(self) else default
+
+
 class _Schedule:
+    def __init_subclass__(cls, **kw):
+        super().__init_subclass__(**kw)
+        fn = cls.__dict__.get("generate_schedule")
+        if fn is not None:
+            def generate_schedule(self, *a, _fn=fn, **k):
+                out = _fn(self, *a, **k)
+                return out if isinstance(out, PerRankSchedule) else PerRankSchedule(out)
+
+            generate_schedule.__doc__ = fn.__doc__
+            cls.generate_schedule = generate_schedule
+
     def __init__(self, num_stages=None, num_microbatches: int = 1, *, stages=None):
         """``num_stages``: the pipeline depth, or - the reference's form, ``GPipeSchedule(stages, num_microbatches)``
         (distributed/pipeline_parallel.py) - the list of stage modules, of which only the length matters here."""

@@ -132,12 +132,14 @@ class PipelineParallelConfig:
 
 
 def split_model(model: nn.Module, pp_mesh=None, pp_config: Optional[PipelineParallelConfig] = None, *, device=None,
-                pp_rank: Optional[int] = None, pp_group=None) -> List[nn.Module]:
+                pp_rank: Optional[int] = None, pp_group=None):
     """One module per stage owned by this rank: a deep copy of the model trimmed to the stage's
-    layers (embeddings only on the first stage, head only on the last). ``pp_mesh``: the pipeline mesh or group;
-    the reference's keyword form ``split_model(model, pp_config=, pp_rank=, device=, pp_group=)``
-    (distributed/pipeline_runtime.py) works as well."""
+    layers (embeddings only on the first stage, head only on the last). ``pp_mesh``: the pipeline mesh or group.
+    Called in the reference's keyword form ``split_model(model, pp_config=, pp_rank=, device=, pp_group=)``
+    (distributed/pipeline_runtime.py:209-260) it returns the reference's pair ``(stages, model_chunks)``; a stage *is*
+    its module here, so both are the same list, ready for ``PipelineSchedule(stages, ...)`` and for the optimizer."""
     assert pp_config is not None, "split_model needs pp_config"
+    reference_form = pp_mesh is None and pp_rank is not None
     if pp_mesh is None:
         pp_mesh = pp_group
     group = pp_mesh.get_group() if hasattr(pp_mesh, "get_group") else pp_mesh
@@ -158,7 +160,7 @@ def split_model(model: nn.Module, pp_mesh=None, pp_config: Optional[PipelinePara
         m._stage_id = sid
         m._direction = len(stages)
         stages.append(m)
-    return stages
+    return (stages, list(stages)) if reference_form else stages
 
 
 class PipelineStages(nn.Module):

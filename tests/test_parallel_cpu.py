@@ -261,10 +261,11 @@ def test_bubble_closed_forms_and_auto_schedule():
     g = AutoScheduleGenerator([StageProfile()] * 4, AutoScheduleConfig(num_microbatches=8, num_stages=4))
     s = g.generate()
     assert len(s) == 4 and s[3][0].type == "FWD" and 0 < g.compute_bubble_fraction() < 0.5
-    assert g.validate_memory() and g.compute_overlap_efficiency() == 1.0
+    assert g.validate_memory()[0] and g.compute_overlap_efficiency() == 1.0
     d = AutoScheduleGenerator([StageProfile()] * 4, AutoScheduleConfig(8, 4, dualpipe_ratio=0.5))
     assert d.compute_bubble_fraction() <= g.compute_bubble_fraction() + 1e-9
-    assert not AutoScheduleGenerator([StageProfile(mem_gb=100)] * 4, AutoScheduleConfig(8, 4)).validate_memory()
+    fits, peak = AutoScheduleGenerator([StageProfile(mem_gb=100)] * 4, AutoScheduleConfig(8, 4)).validate_memory()
+    assert not fits and peak == 400.0
 
 
 def test_stage_layer_ranges():
@@ -299,7 +300,12 @@ def _pp_worker(rank, world, schedule):
     g_last = model.blocks["3"].attention.w_q.weight.grad.clone()
     model.zero_grad()
     pcfg = PipelineParallelConfig(degree=world, schedule=PipelineScheduleType(schedule), num_microbatches=4)
-    stages = split_model(model, dist.group.WORLD, pcfg)
+    if schedule == "1F1B":      # the reference's keyword form returns its pair (stages, model chunks)
+        stages, chunks = split_model(model, pp_config=pcfg, pp_rank=rank, device=torch.device("cpu"),
+                                     pp_group=dist.group.WORLD)
+        assert len(chunks) == len(stages) and all(a is b for a, b in zip(stages, chunks))
+    else:
+        stages = split_model(model, dist.group.WORLD, pcfg)
     sched = PipelineSchedule(stages, dist.group.WORLD, pcfg, hidden_shape=(1, 8, 32), hidden_dtype=torch.float32)
     loss = sched.step(x, target=x)
     def block(idx):
