@@ -35,10 +35,14 @@ def has_fp8_tensor_cores(device: Optional[torch.device] = None) -> bool:
 
 
 def get_peak_flops(device: Optional[torch.device] = None, fp8: bool = False) -> float:
+    """Dense peak of the device; 0.0 for anything that is not a CUDA device, which makes ``compute_mfu`` report 0
+    there (reference: bench_utils.py:72-103)."""
+    if not torch.cuda.is_available() or (device is not None and torch.device(device).type != "cuda"):
+        return 0.0
     table = FP8_PEAK_FLOPS if fp8 else PEAK_FLOPS
     k = _gpu_key(device, table)
     if k is None:
-        return PEAK_FLOPS["A100"] if torch.cuda.is_available() else 1e12
+        return PEAK_FLOPS["A100"]
     return table[k]
 
 
