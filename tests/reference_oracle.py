@@ -141,6 +141,30 @@ def run_moe_sequence(moe_module, state_dict=None, bias_gamma=None, sign=None, st
     return sd, rows
 
 
+ATTENTION_CASES = {"bias": dict(bias=True), "qk_norm": dict(qk_norm=True), "mha": dict(n_kv_heads=None),
+                   "scaled_rope": dict(rope_scaling=dict(factor=4.0, original_max_position_embeddings=16))}
+
+
+def run_attention(attention_cls, scaling_cls, state_dicts=None):
+    """The attention module alone: causal, bidirectional and with an explicit boolean mask."""
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2, 12, 64, generator=g)
+    mask = (torch.rand(12, 12, generator=g) > 0.3) | torch.eye(12, dtype=torch.bool)
+    out, sds = {}, {}
+    for name, kw in ATTENTION_CASES.items():
+        kw = dict(kw)
+        if "rope_scaling" in kw:
+            kw["rope_scaling"] = scaling_cls(**kw["rope_scaling"])
+        torch.manual_seed(1)
+        a = attention_cls(**dict(dict(d_model=64, n_heads=4, n_kv_heads=2, max_seq_len=64), **kw))
+        if state_dicts is not None:
+            a.load_state_dict(state_dicts[name])
+        sds[name] = {k: v.detach().clone() for k, v in a.state_dict().items()}
+        out[name] = {"causal": a(x).detach(), "bidirectional": a(x, causal=False).detach(),
+                     "masked": a(x, causal=False, attn_mask=mask).detach()}
+    return out, sds
+
+
 def main(path):
     if not os.path.isdir(os.path.join(REF, "nanopsyche")):
         print("reference not installed")
@@ -253,6 +277,11 @@ def main(path):
         ft.save(m, opt, step)                       # step 3 is off the interval and skipped
     res["ft"] = dict(dir=ft_dir, latest=ft.find_latest_checkpoint(),
                      model={k: v.detach().clone() for k, v in m.state_dict().items()})
+
+    from nanopsyche.model.attention import Attention
+
+    att_out, att_sd = run_attention(Attention, ref_rope.RoPEScalingConfig)
+    res["attention"] = dict(out=att_out, state_dicts=att_sd)
 
     sd, rows = run_moe_sequence(ref_moe)
     sd_b, rows_b = run_moe_sequence(ref_moe, bias_gamma=0.05)

@@ -233,3 +233,14 @@ def test_fault_tolerant_checkpoint_of_the_reference_resumes_here(ref):
         assert torch.equal(v, f["model"][k]), k
     for p_, st in opt.state.items():
         assert st["exp_avg"].shape == p_.shape
+
+
+def test_attention_module_options_match_the_reference(ref):
+    """Projection biases, qk-norm, full multi-head, scaled RoPE; causal, bidirectional and boolean-mask calls."""
+    from nanopysche_b200.models.attention import Attention
+    from nanopysche_b200.models.rope import RoPEScalingConfig
+
+    got, _ = oracle.run_attention(Attention, RoPEScalingConfig, ref["attention"]["state_dicts"])
+    for name, outs in ref["attention"]["out"].items():
+        for call, want in outs.items():
+            assert torch.allclose(got[name][call], want, atol=1e-6), (name, call)
