@@ -197,6 +197,32 @@ def test_arena_lays_gate_and_up_projections_back_to_back():
         assert qkv is not None and torch.equal(qkv, torch.cat([att.w_q.weight, att.w_k.weight, att.w_v.weight], 0))
 
 
+def test_arena_view_fusion_pass_finds_every_gate_up_and_qkv_group():
+    """The pass that the CUDA path runs at arena construction (``_fuse_views``; skipped on a CPU arena), run here on a
+    bf16 CPU model by naming the device: every attention gets one ``[q; k; v]`` view and every feed-forward one
+    ``[w1; w3]`` view, for the dense 1B shapes' ratios as for a hybrid MoE model (whose dense layers alternate with
+    expert layers in the same regions)."""
+    for moe in (False, True):
+        torch.manual_seed(0)
+        m = TransformerConfig(d_model=64, n_layers=4, n_heads=4, n_kv_heads=2, vocab_size=64, max_seq_len=16,
+                              ffn_hidden=176, qk_norm=False, use_moe=moe, num_experts=4, moe_interval=2, moe_offset=1,
+                              moe_hidden=64).build(dtype=torch.bfloat16)
+        arena = ParamArena(m)
+        arena.device = torch.device("cuda")      # only read by the pass; nothing here touches a GPU
+        arena._fuse_views()
+        n_ff = 0
+        for blk in m.blocks.values():
+            att = blk.attention
+            assert att._fused_qkv is not None
+            assert torch.equal(att._fused_qkv, torch.cat([att.w_q.weight, att.w_k.weight, att.w_v.weight], 0))
+            ff = blk.feed_forward
+            if hasattr(ff, "_fused_w13"):
+                n_ff += 1
+                assert ff._fused_w13 is not None, "gate and up projections are not adjacent in the arena"
+                assert torch.equal(ff._fused_w13, torch.cat([ff.w1.weight, ff.w3.weight], 0))
+        assert n_ff == (2 if moe else 4)
+
+
 def test_diloco_compressor_roundtrip_and_error_feedback():
     ps = [torch.nn.Parameter(torch.zeros(1000))]
     before = torch.random.get_rng_state()
