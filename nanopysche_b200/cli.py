@@ -56,6 +56,9 @@ def build_parser() -> argparse.ArgumentParser:
     common.add_argument("--moe-hidden", type=int, default=None)
     common.add_argument("--capacity-factor", type=float, default=None)
     common.add_argument("--moe-keep-dense-ffn", action="store_true")
+    common.add_argument("--xent-chunk-rows", type=int, default=0,
+                        help="head projection and loss over this many rows at a time: the full logits (and their "
+                             "gradient) are never formed, at the price of one more head GEMM in the backward pass")
     common.add_argument("--tp-size", type=int, default=1)
     common.add_argument("--async-tp", action="store_true",
                         help="tensor parallelism with the all-gather / reduce-scatter fused into the GEMM kernels "
@@ -300,6 +303,8 @@ def cmd_train(args) -> int:
     train_loader, val_loader, vocab = load_dataset(args.dataset, args.batch_size, args.seq_len, device=args.device)
     ctx = _model_build_context(args, vocab)
     model, f_opt, f_sched = build_model(ctx, factory_spec=args.model_factory)
+    if getattr(args, "xent_chunk_rows", 0) and hasattr(model, "loss_chunk_rows"):
+        model.loss_chunk_rows = args.xent_chunk_rows
     model = model.to(device)
     model, mesh = _maybe_parallelize_model(model, args, device)
     if getattr(args, "compile", False) and mesh is None and hasattr(model, "apply_compile"):
@@ -357,6 +362,8 @@ def cmd_bench(args) -> int:
     _, val_loader, vocab = load_dataset(args.dataset, args.batch_size, args.seq_len, device=args.device)
     ctx = _model_build_context(args, vocab)
     model, _, _ = build_model(ctx, factory_spec=args.model_factory)
+    if getattr(args, "xent_chunk_rows", 0) and hasattr(model, "loss_chunk_rows"):
+        model.loss_chunk_rows = args.xent_chunk_rows
     model = model.to(device)
     model, _ = _maybe_parallelize_model(model, args, device)
     model.train()

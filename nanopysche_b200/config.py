@@ -179,6 +179,7 @@ class TransformerConfig(Config):
     rope_scaling_type: str = "piecewise"
     dtype: str = "float32"
     init_std: Optional[float] = None
+    xent_chunk_rows: int = 0     # > 0: head projection + loss over this many rows at a time (full logits never formed)
 
     def build(self, **kwargs):
         import torch
@@ -212,6 +213,7 @@ class TransformerConfig(Config):
                            jitter_eps=self.moe_jitter_eps, z_loss_multiplier=self.moe_z_loss)
         if self.init_std is not None:
             model.init_weights(std=self.init_std)
+        model.loss_chunk_rows = int(self.xent_chunk_rows or 0)
         return model
 
 

@@ -173,6 +173,9 @@ class Transformer(nn.Module):
         self._cp_group = None
         self._is_first_stage = True
         self._is_last_stage = True
+        # > 0: with labels given, head projection and loss run together over this many rows at a time
+        # (``ops.xent.linear_cross_entropy``); the full logits are then never formed and ``"logits"`` is None
+        self.loss_chunk_rows = 0
 
     @property
     def num_params(self) -> int:
@@ -221,6 +224,15 @@ class Transformer(nn.Module):
             return {"hidden_states": x, "aux_loss": aux}
         if self.final_norm is not None:
             x = self.final_norm(x)
+        w = self.lm_head.weight if self.lm_head is not None else self.embeddings.weight
+        plain_head = not (self._fsdp_enabled and self.lm_head is not None) and \
+            (self.lm_head is None or self.lm_head.bias is None) and \
+            not any(hasattr(w, a) for a in ("_fsdp_rt", "_fp8_recipe", "_tp_sharded")) and type(w).__name__ != "DTensor"
+        if labels is not None and self.loss_chunk_rows > 0 and plain_head:
+            tgt = self._shift_labels(labels, labels_shifted)
+            local = xent_ops.linear_cross_entropy(x.reshape(-1, x.shape[-1]), w, tgt.reshape(-1), ignore_index=-100,
+                                                  chunk_rows=self.loss_chunk_rows)
+            return {"logits": None, "aux_loss": aux, "loss": self._loss_over_cp_group(local, tgt)}
         if self._fsdp_enabled and self.lm_head is not None:
             logits = self.lm_head(x)  # through the module so its FSDP unshard hook runs
         else:
@@ -231,19 +243,26 @@ class Transformer(nn.Module):
             out["loss"] = self.loss_from_logits(logits, labels, labels_shifted=labels_shifted)
         return out
 
+    @staticmethod
+    def _shift_labels(labels, labels_shifted: bool):
+        if labels_shifted:
+            return labels
+        tgt = torch.full_like(labels, -100)
+        tgt[:, :-1] = labels[:, 1:]
+        return tgt
+
     def loss_from_logits(self, logits, labels, labels_shifted: bool = False):
         B, S, V = logits.shape
-        if not labels_shifted:
-            tgt = torch.full_like(labels, -100)
-            tgt[:, :-1] = labels[:, 1:]
-        else:
-            tgt = labels
+        tgt = self._shift_labels(labels, labels_shifted)
+        local = xent_ops.cross_entropy(logits.reshape(B * S, V), tgt.reshape(-1), ignore_index=-100)
+        return self._loss_over_cp_group(local, tgt)
+
+    def _loss_over_cp_group(self, local, tgt):
         if self._cp_group is None:
-            return xent_ops.cross_entropy(logits.reshape(B * S, V), tgt.reshape(-1), ignore_index=-100)
+            return local
         # context parallel: mean over the *global* token count; gradients are summed over the CP group
         import torch.distributed as dist
 
-        local = xent_ops.cross_entropy(logits.reshape(B * S, V), tgt.reshape(-1), ignore_index=-100)
         n_local = (tgt != -100).sum().float()
         n_glob = n_local.clone()
         dist.all_reduce(n_glob, group=self._cp_group)

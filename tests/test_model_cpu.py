@@ -334,3 +334,49 @@ def test_routing_prefetcher_votes_with_recency_and_scores_itself():
     skew = CoupledEPScheduler(8, 2048, 128).schedule(torch.tensor([64.0, 960.0] * 4), 4096, 2)
     assert even.dispatch_mode == "fast" and skew.imbalance_coefficient > even.imbalance_coefficient
     assert skew.num_sms >= even.num_sms and skew.prefetch_confidence < even.prefetch_confidence
+
+
+def test_chunked_head_and_loss_equal_the_full_logits_path():
+    """``loss_chunk_rows``: head projection and cross-entropy over a few rows at a time give the loss and every
+    gradient of the path that forms all logits - with a chunk that does not divide the row count, ignored labels,
+    tied embeddings, a scaled loss, and under the parameter arena (head gradient accumulated chunk by chunk into
+    the arena buffer)."""
+    import copy
+
+    from nanopysche_b200.config import TransformerConfig
+    from nanopysche_b200.optim.arena import ParamArena
+
+    for tied in (False, True):
+        torch.manual_seed(0)
+        cfg = TransformerConfig(vocab_size=96, d_model=32, n_layers=2, n_heads=2, max_seq_len=16, ffn_hidden=256,
+                                qk_norm=False, tie_word_embeddings=tied, xent_chunk_rows=5)
+        chunked = cfg.build()
+        assert chunked.loss_chunk_rows == 5
+        full = copy.deepcopy(chunked)
+        full.loss_chunk_rows = 0
+        ids = torch.randint(0, 96, (3, 9))
+        labels = ids.clone()
+        labels[0, 3:6] = -100
+        a, b = chunked(ids, labels=labels), full(ids, labels=labels)
+        assert a["logits"] is None and b["logits"] is not None
+        assert torch.allclose(a["loss"], b["loss"], atol=1e-6)
+        (a["loss"] * 0.37).backward()
+        (b["loss"] * 0.37).backward()
+        for (n, p), q in zip(chunked.named_parameters(), full.parameters()):
+            assert torch.allclose(p.grad, q.grad, atol=1e-6), n
+    # arena: gradients of both paths land in the flat buffers
+    torch.manual_seed(1)
+    cfg = TransformerConfig(vocab_size=96, d_model=32, n_layers=1, n_heads=2, max_seq_len=16, ffn_hidden=256,
+                            qk_norm=False)
+    m1 = cfg.build()
+    m2 = copy.deepcopy(m1)
+    m1.loss_chunk_rows = 4
+    a1, a2 = ParamArena(m1), ParamArena(m2)
+    ids = torch.randint(0, 96, (2, 7))
+    m1(ids, labels=ids)["loss"].backward()
+    m2(ids, labels=ids)["loss"].backward()
+    a1.collect_stray_grads() if hasattr(a1, "collect_stray_grads") else None
+    a2.collect_stray_grads() if hasattr(a2, "collect_stray_grads") else None
+    g1, g2 = dict(a1.named_main_grads()), dict(a2.named_main_grads())
+    for n in g1:
+        assert torch.allclose(g1[n], g2[n], atol=1e-6), n
