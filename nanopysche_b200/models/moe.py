@@ -19,8 +19,8 @@ Public names and constructor signatures follow the reference. What differs, by d
   number of tokens (shares sum to top-k), which is this update with ``gamma`` times top-k plus a shift common to all
   experts - invisible to top-k selection and softmax gating, a drift under sigmoid gating.
 * ``last_dropped`` / ``total_dropped`` / ``drop_rate`` count dropped *tokens*; the reference adds up the per-expert
-  overflows, which counts a token once per over-full expert it chose (its rate can exceed 1). ``per_expert_drops``
-  and the adaptive-capacity estimate are the reference's.
+  overflows, which counts a token once per over-full expert it chose (its rate can exceed 1): that figure is
+  ``last_dropped_slots``. ``per_expert_drops`` and the adaptive-capacity estimate are the reference's.
 """
 from __future__ import annotations
 
@@ -757,6 +757,13 @@ class MoEBase(nn.Module):
     @property
     def last_dropped(self) -> int:
         return self._stat(0)
+
+    @property
+    def last_dropped_slots(self) -> int:
+        """Sum of the per-expert overflows of the last forward: the figure the reference reports as ``last_dropped``
+        (a token is counted once per over-full expert it chose, so the figure can exceed the token count)."""
+        c = self._per_expert_drop_counts
+        return 0 if c is None else int(c.sum().item())
 
     @property
     def total_dropped(self) -> int:

@@ -380,3 +380,16 @@ def test_chunked_head_and_loss_equal_the_full_logits_path():
     g1, g2 = dict(a1.named_main_grads()), dict(a2.named_main_grads())
     for n in g1:
         assert torch.allclose(g1[n], g2[n], atol=1e-6), n
+
+
+def test_token_dropping_benchmark_counts():
+    """``benchmarks.token_dropping``: overflow slots are what is left after every expert has filled its capacity, a
+    dropped token is counted once however many of its experts were full, more capacity drops less."""
+    from benchmarks.token_dropping import run
+
+    rows = run(2048, 8, 2, 5.0, "cpu")
+    by_cf = {r["capacity_factor"]: r for r in rows}
+    assert by_cf[1.0]["overflow_slots"] == 2048 * 2 - 8 * 256          # every expert is over capacity at cf 1
+    assert all(r["tokens_dropped"] <= r["overflow_slots"] for r in rows)
+    drops = [by_cf[c]["tokens_dropped"] for c in (1.0, 1.25, 1.5, 2.0, 4.0)]
+    assert drops == sorted(drops, reverse=True) and by_cf["dropless"]["tokens_dropped"] == 0
