@@ -224,15 +224,17 @@ class Transformer(nn.Module):
             return {"hidden_states": x, "aux_loss": aux}
         if self.final_norm is not None:
             x = self.final_norm(x)
-        w = self.lm_head.weight if self.lm_head is not None else self.embeddings.weight
-        plain_head = not (self._fsdp_enabled and self.lm_head is not None) and \
-            (self.lm_head is None or self.lm_head.bias is None) and \
-            not any(hasattr(w, a) for a in ("_fsdp_rt", "_fp8_recipe", "_tp_sharded")) and type(w).__name__ != "DTensor"
-        if labels is not None and self.loss_chunk_rows > 0 and plain_head:
-            tgt = self._shift_labels(labels, labels_shifted)
-            local = xent_ops.linear_cross_entropy(x.reshape(-1, x.shape[-1]), w, tgt.reshape(-1), ignore_index=-100,
-                                                  chunk_rows=self.loss_chunk_rows)
-            return {"logits": None, "aux_loss": aux, "loss": self._loss_over_cp_group(local, tgt)}
+        if labels is not None and getattr(self, "loss_chunk_rows", 0) > 0:
+            w = self.lm_head.weight if self.lm_head is not None else self.embeddings.weight
+            # a head weight that is sharded, quantised or wrapped takes the ordinary path below
+            plain_head = not (self._fsdp_enabled and self.lm_head is not None) and \
+                (self.lm_head is None or self.lm_head.bias is None) and type(w).__name__ != "DTensor" and \
+                not any(hasattr(w, a) for a in ("_fsdp_rt", "_fp8_recipe", "_tp_sharded"))
+            if plain_head:
+                tgt = self._shift_labels(labels, labels_shifted)
+                local = xent_ops.linear_cross_entropy(x.reshape(-1, x.shape[-1]), w, tgt.reshape(-1),
+                                                      ignore_index=-100, chunk_rows=self.loss_chunk_rows)
+                return {"logits": None, "aux_loss": aux, "loss": self._loss_over_cp_group(local, tgt)}
         if self._fsdp_enabled and self.lm_head is not None:
             logits = self.lm_head(x)  # through the module so its FSDP unshard hook runs
         else:
