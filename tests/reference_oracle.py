@@ -165,6 +165,53 @@ def run_attention(attention_cls, scaling_cls, state_dicts=None):
     return out, sds
 
 
+TP_BLOCK = dict(n_heads=8, n_kv_heads=4, rope_base=10000.0, max_seq_len=64, qk_norm=False, ffn_hidden=128)
+
+
+def tp_rank_result(transformer_cls, full_state_dict, tp_mesh):
+    """One rank of a tensor-parallel run: the full weights go in, ``apply_tp`` cuts this rank's shards; returns the
+    shards, the loss and the gradients of a fixed batch."""
+    torch.manual_seed(0)
+    m = transformer_cls(**BASE, block=dict(TP_BLOCK))
+    if full_state_dict is not None:
+        m.load_state_dict(full_state_dict)
+    full = {k: v.detach().clone() for k, v in m.state_dict().items()}
+    m.apply_tp(tp_mesh)
+    ids = torch.arange(2 * 16).reshape(2, 16) % BASE["vocab_size"]
+    out = m(ids, labels=ids)
+    out["loss"].backward()
+    return dict(full=full, shards={k: v.detach().clone() for k, v in m.state_dict().items()},
+                loss=out["loss"].detach().clone(),
+                grads={n: q.grad.detach().clone() for n, q in m.named_parameters() if q.grad is not None})
+
+
+def _reference_tp_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, REF)
+    from nanopsyche.model.transformer import Transformer
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("tp",))
+    torch.save(tp_rank_result(Transformer, None, mesh["tp"]), os.path.join(out_dir, f"tp_rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def run_reference_tp(out_dir, world=2):
+    import socket
+
+    import torch.multiprocessing as mp
+
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    mp.spawn(_reference_tp_worker, args=(world, port, out_dir), nprocs=world)
+    return [torch.load(os.path.join(out_dir, f"tp_rank{r}.pt")) for r in range(world)]
+
+
 def main(path):
     if not os.path.isdir(os.path.join(REF, "nanopsyche")):
         print("reference not installed")
@@ -282,6 +329,8 @@ def main(path):
 
     att_out, att_sd = run_attention(Attention, ref_rope.RoPEScalingConfig)
     res["attention"] = dict(out=att_out, state_dicts=att_sd)
+
+    res["tp"] = run_reference_tp(os.path.dirname(os.path.abspath(path)))
 
     sd, rows = run_moe_sequence(ref_moe)
     sd_b, rows_b = run_moe_sequence(ref_moe, bias_gamma=0.05)
