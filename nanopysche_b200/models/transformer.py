@@ -191,7 +191,8 @@ class Transformer(nn.Module):
     # ------------------------------------------------------------------ forward
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None, *,
                 labels_shifted: bool = False, return_logits: bool = True, **kwargs):
-        """Returns ``{"logits", "loss", "aux_loss"}`` (a stage without a head returns hidden states)."""
+        """Returns ``{"logits", "loss"}`` plus ``"aux_loss"`` when MoE layers produced one (a stage without a head returns
+        hidden states)."""
         if self.embeddings is not None and not input_ids.is_floating_point():
             emb = self.embeddings
             if type(emb) is nn.Embedding and emb.padding_idx is None and emb.max_norm is None and \
@@ -221,7 +222,7 @@ class Transformer(nn.Module):
             x = gather_rows_replicated(x.reshape(tp_rt.Ms, -1), self._tp_group).view(B0, S0, -1)
         aux = self._collect_aux(x)
         if not self._is_last_stage or (self.lm_head is None and not self.tie_word_embeddings):
-            return {"hidden_states": x, "aux_loss": aux}
+            return self._with_aux({"hidden_states": x}, aux)
         if self.final_norm is not None:
             x = self.final_norm(x)
         if labels is not None and getattr(self, "loss_chunk_rows", 0) > 0:
@@ -234,15 +235,24 @@ class Transformer(nn.Module):
                 tgt = self._shift_labels(labels, labels_shifted)
                 local = xent_ops.linear_cross_entropy(x.reshape(-1, x.shape[-1]), w, tgt.reshape(-1),
                                                       ignore_index=-100, chunk_rows=self.loss_chunk_rows)
-                return {"logits": None, "aux_loss": aux, "loss": self._loss_over_cp_group(local, tgt)}
+                return self._with_aux({"logits": None, "loss": self._loss_over_cp_group(local, tgt)}, aux)
         if self._fsdp_enabled and self.lm_head is not None:
             logits = self.lm_head(x)  # through the module so its FSDP unshard hook runs
         else:
             w = self.lm_head.weight if self.lm_head is not None else self.embeddings.weight
             logits = gemm_ops.linear(x, w)
-        out = {"logits": logits if return_logits else None, "aux_loss": aux}
+        out = self._with_aux({"logits": logits if return_logits else None}, aux)
         if labels is not None:
             out["loss"] = self.loss_from_logits(logits, labels, labels_shifted=labels_shifted)
+        return out
+
+    @staticmethod
+    def _with_aux(out: dict, aux):
+        """``"aux_loss"`` is present only when a MoE layer produced one, as in the reference
+        (model/transformer.py:472-473), so ``if "aux_loss" in out: loss = loss + out["aux_loss"]`` - the reference
+        Trainer's form - works on dense models."""
+        if aux is not None:
+            out["aux_loss"] = aux
         return out
 
     @staticmethod
