@@ -51,7 +51,7 @@ def run_model(model, ids):
     model.train()
     out = model(ids, labels=ids)
     out["loss"].backward()
-    return {"logits": out["logits"].detach(), "loss": out["loss"].detach(),
+    return {"keys": sorted(out.keys()), "logits": out["logits"].detach(), "loss": out["loss"].detach(),
             "aux_loss": None if out.get("aux_loss") is None else out["aux_loss"].detach(),
             "grads": {n: p.grad.detach().clone() for n, p in model.named_parameters() if p.grad is not None}}
 

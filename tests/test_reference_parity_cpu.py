@@ -47,6 +47,8 @@ def test_model_matches_the_reference(ref, case):
     got = oracle.run_model(model, ref["ids"])
     assert torch.allclose(got["logits"], want["logits"], atol=2e-5, rtol=1e-4), case
     assert abs(float(got["loss"]) - float(want["loss"])) < 1e-5
+    if case.startswith("dense"):
+        assert got["keys"] == want["keys"] == ["logits", "loss"]       # no "aux_loss" entry without MoE layers
     grads = {n: p.grad for n, p in model.named_parameters()}
     assert list(grads) == [k for k in want["state_dict"] if k in grads]
     assert set(want["grads"]) <= set(grads)
