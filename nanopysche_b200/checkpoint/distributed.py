@@ -297,6 +297,7 @@ class DistributedCheckpointer:
     def __init__(self, config: Optional[CheckpointConfig] = None, **kw):
         self.config = config or CheckpointConfig(**kw)
         os.makedirs(self.config.save_dir, exist_ok=True)
+        self.save_dir = Path(self.config.save_dir)        # as the reference exposes it (checkpoint/distributed.py:414)
         self.stager = PinnedMemoryStager(self.config.pinned_pool_size, self.config.pinned_memory)
         self.plan_cache = PlanCache()
         self.incremental = IncrementalCheckpointer(self.config.incremental_threshold, self.config.full_save_interval)

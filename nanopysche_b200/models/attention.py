@@ -49,7 +49,11 @@ class Attention(nn.Module):
         self.rope = RotaryEmbedding(self.head_dim, base=rope_base, max_seq_len=max_seq_len,
                                     head_first=rope_head_first, partial_rotary_factor=partial_rotary_factor,
                                     scaling=rope_scaling)
-        self.dropout = nn.Dropout(output_dropout) if output_dropout > 0 else nn.Identity()
+        # as in the reference (model/attention.py:81,109-110,186-187): dropout on the attention output *before* the
+        # output projection, ``None`` when off; ``w_g`` is the reference's unused gate slot
+        self.output_dropout = nn.Dropout(output_dropout) if output_dropout > 0 else None
+        self.rope_head_first = rope_head_first
+        self.w_g: Optional[nn.Linear] = None
         self._tp_size = 1
         self._tp_group = None
         self._cp_module = None
@@ -136,6 +140,8 @@ class Attention(nn.Module):
         else:
             o = self.sdpa(q, k, v, causal=causal, attn_mask=attn_mask)
         o = o.reshape(B, S, self._local_heads * self.head_dim)
+        if self.output_dropout is not None:
+            o = self.output_dropout(o)
         if rt is not None:
             from ..ops import tp_fused
 
@@ -146,7 +152,6 @@ class Attention(nn.Module):
             out = differentiable_all_reduce(out, self._tp_group, self._tp_size)
         if self.w_out.bias is not None:
             out = out + self.w_out.bias
-        out = self.dropout(out)
         if return_kv:
             return out, (k, v)
         return out

@@ -22,6 +22,7 @@ MODEL_CASES = {
     "dense_qk_norm": ({}, dict(qk_norm=True), None),
     "dense_tied": (dict(tie_word_embeddings=True), dict(qk_norm=False), None),
     "dense_mha_head_dim": ({}, dict(qk_norm=False, n_kv_heads=4, head_dim=32), None),
+    "dense_dropout": ({}, dict(qk_norm=False, dropout=0.1), None),
     "moe": ({}, dict(qk_norm=False), {}),
     "moe_capacity_1": ({}, dict(qk_norm=False), dict(capacity_factor=1.0)),
     "moe_capacity_1p25": ({}, dict(qk_norm=False), dict(capacity_factor=1.25)),
@@ -49,6 +50,7 @@ def build(transformer_cls, moe_module, case, seed=0):
 
 def run_model(model, ids):
     model.train()
+    torch.manual_seed(3)                     # dropout masks of the case that has dropout
     out = model(ids, labels=ids)
     out["loss"].backward()
     return {"keys": sorted(out.keys()), "logits": out["logits"].detach(), "loss": out["loss"].detach(),
@@ -142,6 +144,7 @@ def run_moe_sequence(moe_module, state_dict=None, bias_gamma=None, sign=None, st
 
 
 ATTENTION_CASES = {"bias": dict(bias=True), "qk_norm": dict(qk_norm=True), "mha": dict(n_kv_heads=None),
+                   "output_dropout": dict(output_dropout=0.5),
                    "scaled_rope": dict(rope_scaling=dict(factor=4.0, original_max_position_embeddings=16))}
 
 
@@ -160,8 +163,13 @@ def run_attention(attention_cls, scaling_cls, state_dicts=None):
         if state_dicts is not None:
             a.load_state_dict(state_dicts[name])
         sds[name] = {k: v.detach().clone() for k, v in a.state_dict().items()}
-        out[name] = {"causal": a(x).detach(), "bidirectional": a(x, causal=False).detach(),
-                     "masked": a(x, causal=False, attn_mask=mask).detach()}
+        a.train()
+        calls = {}
+        for call, kw2 in (("causal", {}), ("bidirectional", dict(causal=False)),
+                          ("masked", dict(causal=False, attn_mask=mask))):
+            torch.manual_seed(7)             # the dropout mask of the case that has one
+            calls[call] = a(x, **kw2).detach()
+        out[name] = calls
     return out, sds
 
 
