@@ -44,6 +44,7 @@ class GatingFunction(str, Enum):
 
 class MoELoadBalancingLossGranularity(str, Enum):
     LOCAL_BATCH = "local_batch"
+    GLOBAL = "global"           # the reference's second member (model/moe.py:49-51)
     INSTANCE = "instance"
 
 

@@ -17,17 +17,26 @@ import torch.nn as nn
 from .protocol import PARALLEL_HOOKS, has_hook
 from .tp_utils import copy_to_tp_region, differentiable_all_reduce
 
-_LAYER_NAMES = ("blocks", "layers", "layer", "h")
-_EMBED_NAMES = ("embeddings", "embed", "wte", "token_embedding")
-_HEAD_NAMES = ("lm_head", "head", "output", "proj")
+# attribute names a generic model may use (reference: model/parallel_adapter.py:26-28)
+LAYER_STACK_ATTRS = ("blocks", "layers", "layer", "h")
+EMBED_ATTRS = ("embeddings", "embed", "wte", "token_embedding")
+HEAD_ATTRS = ("lm_head", "head", "output", "proj")
+_LAYER_NAMES, _EMBED_NAMES, _HEAD_NAMES = LAYER_STACK_ATTRS, EMBED_ATTRS, HEAD_ATTRS
 
 
 def find_layer_stack(model: nn.Module):
-    for n in _LAYER_NAMES:
+    """``(attribute name, container)`` of the model's repeated layers, ``None`` when it has none (reference:
+    model/parallel_adapter.py:31-38)."""
+    for n in LAYER_STACK_ATTRS:
         m = getattr(model, n, None)
-        if isinstance(m, (nn.ModuleList, nn.ModuleDict, nn.Sequential)):
+        if isinstance(m, (nn.ModuleList, nn.ModuleDict, nn.Sequential)) and len(m) > 0:
             return n, m
-    return None, None
+    return None
+
+
+def _layer_stack(model: nn.Module):
+    """``find_layer_stack`` for unpacking: ``(None, None)`` when there is no stack."""
+    return find_layer_stack(model) or (None, None)
 
 
 def find_embeddings(model: nn.Module):
@@ -57,13 +66,13 @@ def _layers(stack):
 
 def layer_count(model: nn.Module) -> int:
     """Number of layers in the model's layer stack, 0 when none is found (reference: model/parallel_adapter.py:41-45)."""
-    _, stack = find_layer_stack(model)
+    _, stack = _layer_stack(model)
     return len(stack) if stack is not None else 0
 
 
 def iter_layers(model: nn.Module):
     """The model's layers in execution order (reference: model/parallel_adapter.py:48-57)."""
-    _, stack = find_layer_stack(model)
+    _, stack = _layer_stack(model)
     return iter(_layers(stack)) if stack is not None else iter(())
 
 
@@ -106,7 +115,7 @@ def apply_generic_tp(model: nn.Module, tp_mesh, **_):
 
     group = tp_mesh.get_group() if hasattr(tp_mesh, "get_group") else tp_mesh
     tp, rank = dist.get_world_size(group), dist.get_rank(group)
-    _, stack = find_layer_stack(model)
+    _, stack = _layer_stack(model)
     if stack is None or tp <= 1:
         return model
     for layer in _layers(stack):
@@ -143,7 +152,7 @@ def apply_generic_pp(model: nn.Module, pp_mesh, *, num_stages: Optional[int] = N
     group = pp_mesh.get_group() if hasattr(pp_mesh, "get_group") else pp_mesh
     num_stages = num_stages or dist.get_world_size(group)
     stage_idx = dist.get_rank(group) if stage_idx is None else stage_idx
-    name, stack = find_layer_stack(model)
+    name, stack = _layer_stack(model)
     if stack is None:
         return model
     layers = _layers(stack)
@@ -177,7 +186,7 @@ def apply_generic_fsdp(model: nn.Module, dp_mesh=None, *, param_dtype=None, redu
     from ..parallel.fsdp import MixedPrecision, shard_module
 
     mp = MixedPrecision(param_dtype=param_dtype, reduce_dtype=reduce_dtype)
-    _, stack = find_layer_stack(model)
+    _, stack = _layer_stack(model)
     if stack is not None:
         for layer in _layers(stack):
             shard_module(layer, dp_mesh, mp_policy=mp)
@@ -198,7 +207,8 @@ def init_generic_weights(model: nn.Module, device=None, world_mesh=None, std: fl
 
 
 _GENERIC = {"apply_tp": apply_generic_tp, "apply_cp": apply_generic_cp, "apply_pp": apply_generic_pp,
-            "apply_ep": apply_generic_ep, "apply_fsdp": apply_generic_fsdp, "apply_compile": apply_generic_compile}
+            "apply_ep": apply_generic_ep, "apply_fsdp": apply_generic_fsdp, "apply_compile": apply_generic_compile,
+            "init_weights": init_generic_weights}
 
 
 def missing_parallel_hooks(model: nn.Module) -> list[str]:
@@ -210,6 +220,4 @@ def ensure_parallel_hooks(model: nn.Module) -> nn.Module:
     for name in missing_parallel_hooks(model):
         fn = _GENERIC[name]
         setattr(model, name, types.MethodType(lambda self, *a, _fn=fn, **k: _fn(self, *a, **k), model))
-    if not has_hook(model, "init_weights"):
-        model.init_weights = types.MethodType(lambda self, *a, **k: init_generic_weights(self, *a, **k), model)
     return model

@@ -7,7 +7,7 @@ from typing import Optional
 
 import torch.nn as nn
 
-PARALLEL_HOOKS = ("apply_pp", "apply_tp", "apply_cp", "apply_ep", "apply_fsdp", "apply_compile")
+PARALLEL_HOOKS = ("apply_pp", "apply_tp", "apply_cp", "apply_ep", "apply_fsdp", "apply_compile", "init_weights")
 MOE_HOOKS = ("replace_block_with_moe_hybrid",)
 _HOOK_OF = {"pp": "apply_pp", "tp": "apply_tp", "cp": "apply_cp", "ep": "apply_ep", "fsdp": "apply_fsdp",
             "compile": "apply_compile"}

@@ -59,7 +59,7 @@ class AutoScheduleGenerator:
         for acts in raw:
             row = []
             for i, a in enumerate(acts):
-                kind = {"fwd": "FWD", "bwd": "BWD", "bwd_b": "BWD", "bwd_w": "BWD_W"}.get(a.type.value)
+                kind = {"FWD": "FWD", "BWD": "BWD", "BWD_INPUT": "BWD", "BWD_WEIGHT": "BWD_W"}.get(a.type.name)
                 if kind:
                     row.append(Action(kind, a.microbatch, a.stage, i))
             out.append(row)

@@ -96,7 +96,7 @@ def apply_activation_checkpointing(model: nn.Module, mode: str = "full", block_i
     """``full``: every block; ``selected_blocks``: every ``block_interval``-th block."""
     from ..models.parallel_adapter import find_layer_stack
 
-    _, stack = find_layer_stack(model)
+    _, stack = find_layer_stack(model) or (None, None)
     if stack is None or mode in (None, "none"):
         return model
     keys = list(stack.keys()) if isinstance(stack, nn.ModuleDict) else list(range(len(stack)))

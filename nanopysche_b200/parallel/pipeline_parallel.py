@@ -20,12 +20,13 @@ import torch.distributed as dist
 import torch.nn as nn
 
 
-class ScheduleType(str, Enum):
-    FWD = "fwd"
-    BWD = "bwd"          # full backward (input + weight gradients)
-    BWD_INPUT = "bwd_b"  # zero-bubble "B": input gradients only
-    BWD_WEIGHT = "bwd_w"  # zero-bubble "W": weight gradients only
-    IDLE = "idle"
+class ScheduleType(Enum):
+    # FWD / BWD / IDLE with the reference's values (distributed/pipeline_parallel.py: auto() = 1, 2, 3)
+    FWD = 1
+    BWD = 2              # full backward (input + weight gradients)
+    IDLE = 3
+    BWD_INPUT = 4        # zero-bubble "B": input gradients only
+    BWD_WEIGHT = 5       # zero-bubble "W": weight gradients only
 
 
 @dataclass(frozen=True)
@@ -44,7 +45,8 @@ class Action:
         return self.stage
 
     def __repr__(self):
-        tag = {"fwd": "F", "bwd": "B", "bwd_b": "Bi", "bwd_w": "W", "idle": "-"}[self.type.value]
+        tag = {ScheduleType.FWD: "F", ScheduleType.BWD: "B", ScheduleType.BWD_INPUT: "Bi", ScheduleType.BWD_WEIGHT: "W",
+               ScheduleType.IDLE: "-"}[self.type]
         return f"{tag}{self.microbatch}@{self.stage}" if self.type != ScheduleType.IDLE else "-"
 
 

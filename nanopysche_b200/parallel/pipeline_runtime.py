@@ -32,6 +32,8 @@ from .pipeline_parallel import (Action, DualPipeSchedule, GPipeSchedule, Interle
                                 compute_bubble_fraction)  # noqa: F401
 
 
+from ..models.parallel_adapter import EMBED_ATTRS, HEAD_ATTRS  # noqa: E402,F401  (re-exported as in the reference)
+
 class PipelineScheduleType(str, Enum):
     single_1F1B = "1F1B"
     interleaved_1F1B = "Interleaved1F1B"
