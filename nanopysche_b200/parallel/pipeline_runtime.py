@@ -20,7 +20,7 @@ from __future__ import annotations
 
 import copy
 from dataclasses import dataclass, field
-from enum import Enum
+from enum import Enum, StrEnum  # noqa: F401  (StrEnum: a name the reference module exposes)
 from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
