@@ -144,10 +144,15 @@ def load_dataset(dataset_spec: Optional[str], batch_size: int, seq_len: int, spl
 
 
 @torch.no_grad()
-def compute_val_perplexity(model, val_loader, device, max_batches: int = 10) -> float:
-    """exp(mean loss) over up to ``max_batches`` validation batches, without gradients. A context-parallel model gets
+def compute_val_perplexity(model, val_loader, max_batches=10, device=None) -> float:
+    """exp(mean loss) over up to ``max_batches`` validation batches, without gradients; arguments in the reference's
+    order (cli.py:287), a device given in third place is recognised. A context-parallel model gets
     its share of every sequence (its loss is already the mean over the whole sequence); a pipelined model runs a
     forward-only pass of its schedule and every rank gets the last stage's loss."""
+    if not isinstance(max_batches, int):            # (model, val_loader, device[, max_batches])
+        max_batches, device = (device if isinstance(device, int) else 10), max_batches
+    if device is None:
+        device = next(model.parameters()).device
     pp = getattr(model, "_pp_enabled", False)
     stages = (list(model.stages) if hasattr(model, "stages") else [model]) if pp else None
     cp_group = getattr(stages[0] if pp else model, "_cp_group", None)

@@ -19,13 +19,11 @@ import torch.distributed as dist
 
 
 class FaultTolerantCheckpointer:
-    def __init__(self, save_dir: str = "checkpoints", save_interval: int = 1000, keep_last_n: int = 3,
-                 async_save: bool = False, max_stale_steps: Optional[int] = None):
-        """``max_stale_steps`` (reference: fault_tolerance/checkpoint.py, fourth positional argument there): checkpoints
-        more than this many steps behind the newest one are removed as well; a bool in the ``keep_last_n`` position is
-        read as the reference's ``async_save`` (its third positional argument)."""
-        if isinstance(keep_last_n, bool):
-            keep_last_n, async_save = 3, keep_last_n
+    def __init__(self, save_dir: str = "checkpoints", save_interval: int = 100, async_save: bool = True,
+                 max_stale_steps: Optional[int] = None, keep_last_n: int = 3):
+        """Arguments and defaults in the reference's order (fault_tolerance/checkpoint.py:56-63). ``max_stale_steps``:
+        checkpoints more than this many steps behind the newest one are removed as well (``None``: only
+        ``keep_last_n`` limits them; the reference stores the value and never uses it)."""
         self.save_dir, self.save_interval, self.keep_last_n, self.async_save = save_dir, save_interval, keep_last_n, \
             async_save
         self.max_stale_steps = max_stale_steps

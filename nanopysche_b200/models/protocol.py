@@ -34,8 +34,12 @@ def unsupported_parallelism(model: nn.Module, *, tp: int = 1, pp: int = 1, cp: i
     return [k for k, on in wanted.items() if on and not has_hook(model, _HOOK_OF[k])]
 
 
-def warn_unsupported_parallelism(model: nn.Module, **kw) -> list[str]:
-    missing = unsupported_parallelism(model, **kw)
+def warn_unsupported_parallelism(model: nn.Module, missing=None, **kw) -> list[str]:
+    """Warns about the parallel modes in ``missing`` (the reference's form, model/protocol.py:61-72); without a list
+    the modes asked for by keyword (``tp=2, pp=2, ...``) are checked against the model's hooks first."""
+    if missing is None:
+        missing = unsupported_parallelism(model, **kw)
+    missing = list(missing)
     if missing:
         warnings.warn(f"{model_display_name(model)} has no hook for: {', '.join(missing)}; those are skipped")
     return missing

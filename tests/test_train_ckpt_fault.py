@@ -367,7 +367,7 @@ def test_checkpoint_two_ranks_single_directory(tmp_path):
 def test_fault_tolerant_checkpointer_skips_truncated_shard(tmp_path):
     m = tiny_model()
     opt = torch.optim.AdamW(m.parameters(), lr=1e-2)
-    ft = FaultTolerantCheckpointer(str(tmp_path), save_interval=5, keep_last_n=5)
+    ft = FaultTolerantCheckpointer(str(tmp_path), save_interval=5, keep_last_n=5, async_save=False)
     assert ft.save(3, m, opt) is None and ft.should_save(5)
     ft.save(5, m, opt)
     with torch.no_grad():
@@ -463,7 +463,7 @@ def _ft_resume_worker(rank, world, save_dir):
     from nanopysche_b200.fault_tolerance.checkpoint import FaultTolerantCheckpointer
 
     m = tiny_model()
-    ck = FaultTolerantCheckpointer(save_dir, save_interval=1, keep_last_n=5)
+    ck = FaultTolerantCheckpointer(save_dir, save_interval=1, keep_last_n=5, async_save=False)
     ck.save(1, m, force=True)
     ck.save(2, m, force=True)
     dist.barrier()
