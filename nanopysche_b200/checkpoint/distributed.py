@@ -31,17 +31,19 @@ import torch.distributed as dist
 
 @dataclass
 class CheckpointConfig:
+    # fields and defaults of the reference (checkpoint/distributed.py:44-66): by default every tenth save is a full
+    # one and the saves between them hold only the tensors that changed
     save_dir: str = "checkpoints"
     save_interval: int = 1000
-    load_thread_count: int = 4
+    load_thread_count: int = 2
     keep_last_n: int = 3
-    async_saves: bool = False
+    async_saves: bool = True
     save_overwrite: bool = False
-    incremental: bool = False
+    incremental: bool = True
     incremental_threshold: float = 0.01
     full_save_interval: int = 10
     pinned_memory: bool = True
-    pinned_pool_size: int = 2
+    pinned_pool_size: int = 4
     save_dataloader_state: bool = True
 
 

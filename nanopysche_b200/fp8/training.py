@@ -22,15 +22,18 @@ from fp8_flow_moe import ops as fp8_ops
 
 @dataclass
 class FP8Config:
+    # fields, order and defaults of the reference (fp8/training.py:70-76). ``recipe_name``: "mxfp8" selects the 1x32
+    # e8m0 recipe, every other value (the reference's "max" / "delayed" included) the 1x128 / 128x128 block-scaled
+    # one; the dtype names are kept for the record (forward operands are e4m3 here, gradients stay bf16)
     enabled: bool = False
-    forward_dtype: torch.dtype = torch.float8_e4m3fn
-    backward_dtype: torch.dtype = torch.float8_e5m2
-    recipe_name: str = "blockwise"
-    force_recompute_fp8_weight_in_bwd: bool = False
+    forward_dtype: str = "float8_e4m3fn"
+    backward_dtype: str = "float8_e5m2"
+    recipe_name: str = "max"
+    force_recompute_fp8_weight_in_bwd: bool = True
+    cast_input_text: bool = True            # activations are always cast here
+    filter_fn: Optional[str] = None         # substring a module's name must contain
     ignored_modules: List[str] = field(default_factory=lambda: ["lm_head", "gate"])
     min_features: int = 128
-    cast_input_text: bool = True            # reference field (fp8/training.py:75): activations are always cast here
-    filter_fn: Optional[str] = None         # reference field (fp8/training.py:76): substring a module's name must contain
 
     def build_torchao_config(self):
         """The reference hands its linears to torchao (fp8/training.py:78-90). Here the fp8 linears run on this

@@ -33,8 +33,8 @@ class ModelBuildContext:
     num_experts: int = 8
     moe_top_k: int = 2
     fp8_recipe: str = "none"
-    fp8_gemm_threshold: int = 1000000
     dtype: torch.dtype = torch.float32
+    fp8_gemm_threshold: int = 1000000
     moe_interval: int = 2
     moe_offset: int = 0
     moe_hidden: Optional[int] = None

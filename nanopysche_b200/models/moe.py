@@ -464,7 +464,8 @@ class ExpertMLP(nn.Module):
 
 @dataclass
 class MoEConfig:
-    d_model: int = 2048
+    # the reference's fields in its order (model/moe.py:1191-1212), this package's additions behind them
+    d_model: int = 512
     hidden_size: Optional[int] = None
     num_experts: int = 8
     top_k: int = 2
@@ -474,15 +475,15 @@ class MoEConfig:
     gating_function: GatingFunction = GatingFunction.SOFTMAX
     bias_gamma: Optional[float] = None
     capacity_factor: Optional[float] = None
+    shared_expert: bool = False
+    ep: Optional["ExpertParallelConfig"] = None      # expert-parallel placement
+    fp8_flow_moe: bool = False
+    fp8_recipe: str = "none"
+    fp8_gemm_threshold: int = 1000000
     adaptive_capacity: bool = False
     adaptive_capacity_target: float = 0.01
     adaptive_capacity_ema: float = 0.3
     routing_replay: bool = False
-    shared_expert: bool = False
-    ep: Optional["ExpertParallelConfig"] = None      # expert-parallel placement (reference: model/moe.py:1209)
-    fp8_flow_moe: bool = False
-    fp8_recipe: str = "none"
-    fp8_gemm_threshold: int = 1000000
     extra: dict = field(default_factory=dict)
 
     def build(self, **kw) -> "MoEBase":
@@ -728,7 +729,7 @@ class MoEBase(nn.Module):
             p._sp_reduce_group = group
             p.register_hook(hook_for(p))
 
-    def apply_fp8_flow_moe(self, fp8_flow_moe: bool = True, fp8_recipe: str = "blockwise",
+    def apply_fp8_flow_moe(self, fp8_flow_moe: bool = True, fp8_recipe: str = "flow_moe",
                            fp8_gemm_threshold: Optional[int] = None):
         enabled = fp8_flow_moe
         self.fp8_flow_moe_enabled = enabled

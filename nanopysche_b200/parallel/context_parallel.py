@@ -175,7 +175,7 @@ class RingAttention(nn.Module):
     (zig-zag layout when ``use_zigzag``); the output has q's shape.
     """
 
-    def __init__(self, group=None, *, use_ulysses: bool = False, use_zigzag: bool = True,
+    def __init__(self, group=None, use_ulysses: bool = False, use_zigzag: bool = True, *,
                  fused: Optional[bool] = None):
         super().__init__()
         self.group = group

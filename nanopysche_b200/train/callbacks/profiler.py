@@ -15,13 +15,15 @@ log = logging.getLogger(__name__)
 
 
 class ProfilerCallback(Callback):
-    def __init__(self, save_dir: str = "profiler", skip_first: int = 2, wait: int = 0, warmup: int = 1, active: int = 3,
-                 repeat: int = 1, profile_ranks: Optional[str] = None, with_stack: bool = False,
-                 profile_memory: bool = False, record_shapes: bool = False, with_flops: bool = False,
-                 row_limit: int = 20, output_dir: Optional[str] = None, enable_cuda_sync_events: bool = False):
-        """``output_dir`` / ``enable_cuda_sync_events``: the reference's names (train/callbacks/profiler.py); the latter
-        is accepted and ignored (the Kineto switch it set only adds synchronisation records to the trace)."""
-        save_dir = output_dir or save_dir
+    def __init__(self, skip_first: int = 10, wait: int = 5, warmup: int = 5, active: int = 10, repeat: int = 1,
+                 with_stack: bool = True, profile_memory: bool = True, enable_cuda_sync_events: bool = True,
+                 output_dir: str = "profiler", profile_ranks: Optional[str] = None, *,
+                 save_dir: Optional[str] = None, record_shapes: bool = False, with_flops: bool = False,
+                 row_limit: int = 20):
+        """Arguments and defaults in the reference's order (train/callbacks/profiler.py:39-50); ``save_dir`` is another
+        name for ``output_dir``; ``enable_cuda_sync_events`` is accepted and ignored (the Kineto switch it set only
+        adds synchronisation records to the trace)."""
+        save_dir = save_dir or output_dir
         self.save_dir = save_dir
         self.skip_first, self.wait, self.warmup, self.active, self.repeat = skip_first, wait, warmup, active, repeat
         self.profile_ranks = profile_ranks

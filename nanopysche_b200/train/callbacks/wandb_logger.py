@@ -11,11 +11,14 @@ log = logging.getLogger(__name__)
 
 
 class WandBCallback(Callback):
-    def __init__(self, project: str = "nanopsyche", name: Optional[str] = None, config: Optional[dict] = None,
-                 entity: Optional[str] = None, tags: Optional[list] = None, cancel_tags: Optional[list] = None,
-                 cancel_check_interval: int = 25, enabled: bool = True, group: Optional[str] = None,
-                 notes: Optional[str] = None):
+    def __init__(self, project: str = "nanopsyche", entity: Optional[str] = None, group: Optional[str] = None,
+                 name: Optional[str] = None, tags: Optional[list] = None, notes: Optional[str] = None,
+                 cancel_check_interval: float = 300, *, config: Optional[dict] = None,
+                 cancel_tags: Optional[list] = None, enabled: bool = True):
+        """Arguments in the reference's order (train/callbacks/wandb_logger.py:30-39); ``cancel_check_interval`` is
+        in seconds, as there: the run's tags are looked up at most that often."""
         self.group, self.notes = group, notes       # passed to wandb.init like the reference does
+        self._last_cancel_check = 0.0
         self.project, self.name, self.config, self.entity, self.tags = project, name, config, entity, tags
         self.cancel_tags = cancel_tags or ["cancel", "canceled", "cancelled"]
         self.cancel_check_interval = cancel_check_interval
@@ -41,8 +44,11 @@ class WandBCallback(Callback):
             self._run.log(metrics, step=step)
 
     def post_step(self, trainer: Any) -> None:
-        if self._run is None or trainer.step % self.cancel_check_interval:
+        import time
+
+        if self._run is None or time.monotonic() - self._last_cancel_check < self.cancel_check_interval:
             return
+        self._last_cancel_check = time.monotonic()
         try:
             api_run = self._wandb.Api().run(self._run.path)
             if any(t.lower() in self.cancel_tags for t in api_run.tags):

@@ -77,9 +77,11 @@ class DistributedDataLoader:
     peers read the same batch) - is resolved at the first batch, not at construction: the CLI builds its loaders before
     the mesh exists. Without a mesh every rank is its own data-parallel index (plain DDP)."""
 
-    def __init__(self, dataset: Dataset, batch_size: int, *, num_workers: int = 0, seed: int = 0,
-                 dp_rank: Optional[int] = None, dp_world: Optional[int] = None, shuffle: bool = True,
-                 pin_memory: Optional[bool] = None, drop_last: bool = True):
+    def __init__(self, dataset: Dataset, batch_size: int, num_workers: int = 0, pin_memory: Optional[bool] = None,
+                 drop_last: bool = True, *, seed: int = 0, dp_rank: Optional[int] = None,
+                 dp_world: Optional[int] = None, shuffle: bool = True):
+        """The first five arguments in the reference's order (train/data.py:87-94). Defaults that differ: no worker
+        processes (the reference starts four per loader) and pinning only when CUDA is present."""
         self.dataset, self.batch_size, self.seed = dataset, batch_size, seed
         self.epoch = 0
         self._args = dict(num_workers=num_workers, dp_rank=dp_rank, dp_world=dp_world, shuffle=shuffle,

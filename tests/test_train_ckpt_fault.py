@@ -248,7 +248,7 @@ def test_checkpoint_layout_roundtrip_and_retention(tmp_path):
     m(x, labels=x)["loss"].backward()
     opt.step()
     sched.step()
-    ck = DistributedCheckpointer(CheckpointConfig(save_dir=str(tmp_path), keep_last_n=2))
+    ck = DistributedCheckpointer(CheckpointConfig(save_dir=str(tmp_path), keep_last_n=2, incremental=False))
     ck.dataloader_tracker.update(4)
     for step in (10, 20, 30):
         d = ck.save(step, m, opt, scheduler=sched, extra={"tokens_seen": step * 16})
@@ -451,7 +451,7 @@ def test_heartbeat_over_process_group_store():
 def test_profiler_callback_window(tmp_path):
     m = tiny_model()
     opt = torch.optim.SGD(m.parameters(), lr=0.01)
-    prof = ProfilerCallback(save_dir=str(tmp_path), skip_first=1, warmup=0, active=2)
+    prof = ProfilerCallback(save_dir=str(tmp_path), skip_first=1, wait=0, warmup=0, active=2)
     tc = TrainingConfig(global_batch_size=32, micro_batch_size=2, sequence_length=16, max_steps=5, log_interval=0,
                         save_interval=0, dtype=torch.float32, vocab_size=64)
     Trainer(tc, m, opt, None, None, [prof]).fit()
