@@ -82,12 +82,20 @@ class PipelineStage(nn.Module):
     def is_last(self) -> bool:
         return self.stage_id == self.num_stages - 1
 
-    def forward_chunk(self, x, **kw):
+    def forward_chunk(self, x, labels=None, is_last_chunk: bool = False, **kw):
+        """The stage's layers on ``x``; on the last chunk, with ``labels`` and a ``loss_fn`` (the head), also the
+        cross-entropy of ``loss_fn(x)``: ``(x, loss)`` (reference: distributed/pipeline_parallel.py:101-129)."""
         if isinstance(self.layers, (nn.ModuleList, nn.Sequential)):
             for l in self.layers:
                 x = l(x, **kw) if kw else l(x)
-            return x
-        return self.layers(x, **kw)
+        else:
+            x = self.layers(x, **kw)
+        if is_last_chunk and self.loss_fn is not None and labels is not None:
+            logits = self.loss_fn(x)
+            loss = torch.nn.functional.cross_entropy(logits.reshape(-1, logits.size(-1)).float(), labels.reshape(-1),
+                                                     ignore_index=-100)
+            return x, loss
+        return x
 
     forward = forward_chunk
 

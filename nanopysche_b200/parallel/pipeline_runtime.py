@@ -625,9 +625,21 @@ class DualPipeScheduleRuntime(PipelineSchedule):
     enter at rank 0, odd ones at rank p-1 (reference: distributed/pipeline_runtime.py:303-397, which
     runs the phases sequentially on one direction only)."""
 
-    def __init__(self, stages, pp_mesh, pp_config=None, **kw):
+    def __init__(self, stages, pp_mesh=None, pp_config=None, loss_fn=None, **kw):
+        """``DualPipeScheduleRuntime(stages, pp_mesh, pp_config)`` with this rank's two stage copies, or the
+        reference's ``(stages_forward, stages_reverse, num_microbatches, loss_fn)``
+        (distributed/pipeline_runtime.py:303-320): two lists of stages, told apart by the second argument being a list."""
+        if isinstance(pp_mesh, (list, tuple, nn.ModuleList)):
+            stages_reverse, num_microbatches = pp_mesh, pp_config
+            stages = list(stages) + list(stages_reverse)
+            pp_mesh = kw.pop("group", None)
+            pp_config = PipelineParallelConfig(degree=max(len(stages) // 2, 1), schedule=PipelineScheduleType.dualpipe,
+                                               num_microbatches=num_microbatches if isinstance(num_microbatches, int)
+                                               else None)
         cfg = pp_config or PipelineParallelConfig(schedule=PipelineScheduleType.dualpipe)
         cfg.schedule = PipelineScheduleType.dualpipe
+        if loss_fn is not None:
+            kw["loss_fn"] = loss_fn
         super().__init__(stages, pp_mesh, cfg, **kw)
 
 

@@ -18,6 +18,8 @@ class StabilityMonitorCallback(Callback):
             threshold = threshold_std
         if metric_name is not None:
             metrics = (metric_name,)
+        if isinstance(metrics, str):        # the reference's third positional argument is one metric name
+            metrics = (metrics,)
         self.window_size, self.threshold, self.metrics = window_size, threshold, tuple(metrics)
         self._hist = {m: deque(maxlen=window_size) for m in metrics}
         self._total_spikes = 0

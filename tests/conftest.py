@@ -53,9 +53,28 @@ def _worker(rank, world, port, backend, fn, args, q):
             pass
 
 
+class _RendezvousTrouble(Exception):
+    """A rank failed while the process group was being set up or torn down (a port taken between choosing and
+    binding it, a connection reset by a process that is still exiting), not in the code under test."""
+
+
 def run_distributed(fn, world: int, *args, backend: str = "gloo", timeout: float = 240.0):
     """Run ``fn(rank, world, *args)`` on ``world`` ranks; returns the per-rank results, raises on any
-    failure. ``fn`` must be a module-level function (spawned processes import it by name)."""
+    failure. ``fn`` must be a module-level function (spawned processes import it by name). A failure of the
+    rendezvous itself (gloo, on the CPU box) is retried once on a fresh port; a failure in ``fn`` never is."""
+    if backend != "gloo":
+        return _run_distributed_once(fn, world, args, backend, timeout)
+    try:
+        return _run_distributed_once(fn, world, args, backend, timeout)
+    except _RendezvousTrouble:
+        return _run_distributed_once(fn, world, args, backend, timeout)
+
+
+_RENDEZVOUS_MARKS = ("Address already in use", "Connection reset by peer", "Connection refused",
+                     "connectFullMesh", "Socket Timeout", "store-based barrier")
+
+
+def _run_distributed_once(fn, world, args, backend, timeout):
     import torch.multiprocessing as mp
 
     ctx = mp.get_context("spawn")
@@ -69,6 +88,8 @@ def run_distributed(fn, world: int, *args, backend: str = "gloo", timeout: float
         for _ in range(world):
             rank, status, payload = q.get(timeout=timeout)
             if status != "ok":
+                if "AssertionError" not in payload and any(m in payload for m in _RENDEZVOUS_MARKS):
+                    raise _RendezvousTrouble(payload)
                 raise AssertionError(f"rank {rank} failed:\n{payload}")
             out[rank] = payload
     finally:
