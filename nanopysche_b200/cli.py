@@ -81,13 +81,13 @@ def build_parser() -> argparse.ArgumentParser:
     common.add_argument("--ulysses", action="store_true", help="Ulysses instead of ring attention under CP")
     t = sub.add_parser("train", parents=[common], help="Train a model")
     t.add_argument("--compile", action="store_true")
-    t.add_argument("--val-interval", type=int, default=0)
-    t.add_argument("--val-steps", type=int, default=10)
+    t.add_argument("--val-interval", type=int, default=10)      # defaults of the reference's CLI (cli.py:96-135)
+    t.add_argument("--val-steps", type=int, default=5)
     t.add_argument("--wandb", action="store_true")
     t.add_argument("--wandb-project", type=str, default="nanopsyche")
     t.add_argument("--resume", type=str, default=None)
-    t.add_argument("--save-dir", type=str, default="checkpoints")
-    t.add_argument("--save-interval", type=int, default=0)
+    t.add_argument("--save-dir", type=str, default=None, help="default: checkpoints/<model>")
+    t.add_argument("--save-interval", type=int, default=1000)
     t.add_argument("--global-batch-size", type=int, default=None, help="tokens per optimizer step")
     t.add_argument("--log-interval", type=int, default=10)
     b = sub.add_parser("bench", parents=[common], help="Benchmark throughput")
@@ -302,6 +302,7 @@ def cmd_train(args) -> int:
     from .train.trainer import Trainer, TrainingConfig
 
     torch.manual_seed(42)
+    args.save_dir = args.save_dir or f"checkpoints/{args.model}"       # the reference's default (cli.py:502)
     rank, world = _init_distributed(args)
     device = torch.device(args.device if not str(args.device).startswith("cuda") else
                           f"cuda:{int(os.environ.get('LOCAL_RANK', 0))}")
