@@ -71,7 +71,8 @@ def run_distributed(fn, world: int, *args, backend: str = "gloo", timeout: float
 
 
 _RENDEZVOUS_MARKS = ("Address already in use", "Connection reset by peer", "Connection refused",
-                     "connectFullMesh", "Socket Timeout", "store-based barrier")
+                     "Connection closed by peer", "Broken pipe", "connectFullMesh", "Socket Timeout",
+                     "store-based barrier")
 
 
 def _run_distributed_once(fn, world, args, backend, timeout):
