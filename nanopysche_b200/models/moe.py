@@ -105,8 +105,16 @@ class MoERouter(nn.Module):
         return w / (w.sum(dim=-1, keepdim=True) + 1e-8), idx
 
     def _routing_replay_gating(self, logits, mask):
-        """R3 replay: restrict the choice to the experts recorded at inference time."""
-        mask = mask.to(logits.device).reshape(logits.shape).bool()
+        """R3 replay: restrict the choice to the experts recorded at inference time. ``mask``: the recorded expert
+        *indices*, ``(B, S, K)`` or ``(N, K)`` - what the reference's ``set_replay_mask`` takes and scatters
+        (model/moe.py:186-240) - or a boolean ``(..., num_experts)`` mask of allowed experts. The weights are the
+        softmax of the training logits over the replayed experts, so the router still receives gradients."""
+        mask = mask.to(logits.device)
+        if mask.dtype != torch.bool and mask.shape[-1] == self.top_k and self.top_k != self.num_experts:
+            idx = mask.reshape(-1, self.top_k).long()
+            allowed = torch.zeros(idx.shape[0], self.num_experts, dtype=torch.bool, device=logits.device)
+            mask = allowed.scatter_(1, idx, True)
+        mask = mask.reshape(logits.shape).bool()
         masked = logits.masked_fill(~mask, float("-inf"))
         # rows whose mask allows fewer than top_k experts fall back to the unmasked logits
         enough = mask.sum(-1, keepdim=True) >= self.top_k

@@ -220,6 +220,34 @@ def run_reference_tp(out_dir, world=2):
     return [torch.load(os.path.join(out_dir, f"tp_rank{r}.pt")) for r in range(world)]
 
 
+def run_routing_replay(moe_module, state_dict=None):
+    """R3 routing replay: the expert choice recorded in an evaluation pass is replayed in a training pass on
+    perturbed inputs (so the training logits would choose differently); outputs, router gradient and the replayed
+    indices."""
+    torch.manual_seed(0)
+    m = moe_module.MoEBase(d_model=32, hidden_size=64, num_experts=4, top_k=2, routing_replay=True)
+    if state_dict is not None:
+        m.load_state_dict(state_dict)
+    sd = {k: v.detach().clone() for k, v in m.state_dict().items()}
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(2, 8, 32, generator=g)
+    m.eval()
+    with torch.no_grad():
+        _, idx, _ = m.router(x)
+    m.train()
+    m.router.set_replay_mask(idx)
+    x2 = (x + 0.5 * torch.randn(2, 8, 32, generator=g)).requires_grad_(True)
+    w2, idx2, _ = m.router(x2)
+    y = m(x2)
+    y.square().sum().backward()
+    out = dict(idx=idx, weights=w2.detach().clone(), idx_replayed=idx2.detach().clone(), y=y.detach().clone(),
+               gate_grad=m.router.gate.weight.grad.detach().clone(), x_grad=x2.grad.detach().clone())
+    m.router.clear_replay_mask()
+    _, idx3, _ = m.router(x2.detach())
+    out["idx_after_clear"] = idx3.detach().clone()
+    return sd, out
+
+
 def main(path):
     if not os.path.isdir(os.path.join(REF, "nanopsyche")):
         print("reference not installed")
@@ -339,6 +367,9 @@ def main(path):
     res["attention"] = dict(out=att_out, state_dicts=att_sd)
 
     res["tp"] = run_reference_tp(os.path.dirname(os.path.abspath(path)))
+
+    rr_sd, rr = run_routing_replay(ref_moe)
+    res["routing_replay"] = dict(state_dict=rr_sd, out=rr)
 
     sd, rows = run_moe_sequence(ref_moe)
     sd_b, rows_b = run_moe_sequence(ref_moe, bias_gamma=0.05)

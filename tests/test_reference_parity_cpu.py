@@ -296,3 +296,20 @@ def test_tensor_parallel_shards_are_the_reference_s(ref, tmp_path):
         assert torch.allclose(a["grads"][k], full_grads[k][rank * rows:(rank + 1) * rows], atol=1e-6)
         # the known difference: the reference's upstream gradients are partial sums
         assert not torch.allclose(b["grads"]["embeddings.weight"], full_grads["embeddings.weight"], atol=1e-4)
+
+
+def test_routing_replay_matches_the_reference(ref):
+    """R3 routing replay (``set_replay_mask`` / ``clear_replay_mask``): the replayed choice, the renormalised weights,
+    the layer output and the gradients of router and input are the reference's; without the mask the router goes back
+    to its own choice."""
+    from nanopysche_b200.models import moe as our_moe
+
+    want = ref["routing_replay"]["out"]
+    _, got = oracle.run_routing_replay(our_moe, ref["routing_replay"]["state_dict"])
+    assert torch.equal(got["idx"], want["idx"])
+    assert torch.equal(got["idx_replayed"].sort(-1).values, want["idx_replayed"].sort(-1).values)
+    assert torch.allclose(got["weights"].sort(-1).values, want["weights"].sort(-1).values, atol=1e-6)
+    assert torch.allclose(got["y"], want["y"], atol=1e-6)
+    assert torch.allclose(got["gate_grad"], want["gate_grad"], atol=1e-6)
+    assert torch.allclose(got["x_grad"], want["x_grad"], atol=1e-6)
+    assert torch.equal(got["idx_after_clear"].sort(-1).values, want["idx_after_clear"].sort(-1).values)
