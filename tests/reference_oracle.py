@@ -248,6 +248,36 @@ def run_routing_replay(moe_module, state_dict=None):
     return sd, out
 
 
+def run_moe_options(moe_module, state_dicts=None):
+    """Router jitter (seeded), L2-normalised expert weights, and the phase API
+    (route -> dispatch -> local_compute -> combine -> reassemble) of a single-rank layer with capacity drops."""
+    out, sds = {}, {}
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(2, 12, 32, generator=g)
+    for name, kw, l2 in (("jitter", dict(jitter_eps=0.1), False), ("l2", {}, True),
+                         ("phases", dict(capacity_factor=1.0, shared_expert=True), False)):
+        torch.manual_seed(0)
+        m = moe_module.MoEBase(d_model=32, hidden_size=64, num_experts=4, top_k=2, **kw)
+        if l2:
+            m.router.config.normalize_expert_weights = "l2"
+        if state_dicts is not None:
+            m.load_state_dict(state_dicts[name])
+        sds[name] = {k: v.detach().clone() for k, v in m.state_dict().items()}
+        m.train()
+        torch.manual_seed(9)
+        if name != "phases":
+            out[name] = m(x).detach().clone()
+            continue
+        B, S, D = x.shape
+        x_flat, w_flat, i_flat, aux, dropped, keep = m.route(x)
+        lx, lw, li, meta = m.dispatch(x_flat, i_flat, w_flat)
+        eo = m.local_compute(lx, lw, li)
+        y = m.reassemble(m.combine(eo, meta, x_flat, w_flat, i_flat), dropped=dropped, keep_mask=keep, B=B, S=S, D=D)
+        out[name] = dict(y=y.detach().clone(), whole=m(x).detach().clone(), kept=int(x_flat.shape[0]),
+                         dropped=int(dropped), keep=None if keep is None else keep.clone(), aux=float(aux.detach()))
+    return out, sds
+
+
 def main(path):
     if not os.path.isdir(os.path.join(REF, "nanopsyche")):
         print("reference not installed")
@@ -370,6 +400,9 @@ def main(path):
 
     rr_sd, rr = run_routing_replay(ref_moe)
     res["routing_replay"] = dict(state_dict=rr_sd, out=rr)
+
+    mo_out, mo_sd = run_moe_options(ref_moe)
+    res["moe_options"] = dict(out=mo_out, state_dicts=mo_sd)
 
     sd, rows = run_moe_sequence(ref_moe)
     sd_b, rows_b = run_moe_sequence(ref_moe, bias_gamma=0.05)

@@ -313,3 +313,19 @@ def test_routing_replay_matches_the_reference(ref):
     assert torch.allclose(got["gate_grad"], want["gate_grad"], atol=1e-6)
     assert torch.allclose(got["x_grad"], want["x_grad"], atol=1e-6)
     assert torch.equal(got["idx_after_clear"].sort(-1).values, want["idx_after_clear"].sort(-1).values)
+
+
+def test_moe_options_and_phase_api_match_the_reference(ref):
+    """Seeded router jitter, L2-normalised expert weights, and the five-phase API of the hybrid block
+    (route, dispatch, local_compute, combine, reassemble) with capacity drops and a shared expert: same kept tokens,
+    same output as the layer's own forward, same as the reference."""
+    from nanopysche_b200.models import moe as our_moe
+
+    want = ref["moe_options"]["out"]
+    got, _ = oracle.run_moe_options(our_moe, ref["moe_options"]["state_dicts"])
+    assert torch.allclose(got["jitter"], want["jitter"], atol=1e-6)
+    assert torch.allclose(got["l2"], want["l2"], atol=1e-6)
+    a, b = got["phases"], want["phases"]
+    assert a["kept"] == b["kept"] and torch.equal(a["keep"], b["keep"])
+    assert torch.allclose(a["y"], b["y"], atol=1e-6) and torch.allclose(a["whole"], b["whole"], atol=1e-6)
+    assert torch.allclose(a["y"], a["whole"], atol=1e-6) and a["aux"] == pytest.approx(b["aux"], rel=1e-5)
