@@ -278,6 +278,28 @@ def run_moe_options(moe_module, state_dicts=None):
     return out, sds
 
 
+def run_small_modules(ffn_cls, norm_cls, state_dicts=None):
+    """FeedForward (biases, GeGLU) and RMSNorm (fp32 and bf16 inputs, ``full_precision`` on and off) on their own."""
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(3, 5, 48, generator=g)
+    out, sds = {}, {}
+    for name, kw in (("swiglu_bias", dict(bias=True)), ("geglu", dict(activation="gelu_tanh")),
+                     ("default_hidden", {})):
+        torch.manual_seed(0)
+        m = ffn_cls(d_model=48, **({"hidden_size": 80} if name != "default_hidden" else {}), **kw)
+        if state_dicts is not None:
+            m.load_state_dict(state_dicts[name])
+        sds[name] = {k: v.detach().clone() for k, v in m.state_dict().items()}
+        out[name] = m(x).detach().clone()
+    for name, kw, dt in (("norm_fp32", {}, torch.float32), ("norm_bf16", {}, torch.bfloat16),
+                         ("norm_low_precision", dict(full_precision=False), torch.bfloat16)):
+        n = norm_cls(48, eps=1e-5, **kw)
+        with torch.no_grad():
+            n.weight.copy_(torch.linspace(0.5, 1.5, 48))
+        out[name] = n(x.to(dt)).detach().clone()
+    return out, sds
+
+
 def main(path):
     if not os.path.isdir(os.path.join(REF, "nanopsyche")):
         print("reference not installed")
@@ -403,6 +425,12 @@ def main(path):
 
     mo_out, mo_sd = run_moe_options(ref_moe)
     res["moe_options"] = dict(out=mo_out, state_dicts=mo_sd)
+
+    from nanopsyche.model.feed_forward import FeedForward
+    from nanopsyche.model.norm import RMSNorm
+
+    sm_out, sm_sd = run_small_modules(FeedForward, RMSNorm)
+    res["small_modules"] = dict(out=sm_out, state_dicts=sm_sd)
 
     sd, rows = run_moe_sequence(ref_moe)
     sd_b, rows_b = run_moe_sequence(ref_moe, bias_gamma=0.05)

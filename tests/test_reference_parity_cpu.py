@@ -329,3 +329,21 @@ def test_moe_options_and_phase_api_match_the_reference(ref):
     assert a["kept"] == b["kept"] and torch.equal(a["keep"], b["keep"])
     assert torch.allclose(a["y"], b["y"], atol=1e-6) and torch.allclose(a["whole"], b["whole"], atol=1e-6)
     assert torch.allclose(a["y"], a["whole"], atol=1e-6) and a["aux"] == pytest.approx(b["aux"], rel=1e-5)
+
+
+def test_feed_forward_and_rmsnorm_match_the_reference(ref):
+    from nanopysche_b200.models.feed_forward import FeedForward
+    from nanopysche_b200.models.norm import RMSNorm
+
+    want = ref["small_modules"]["out"]
+    got, _ = oracle.run_small_modules(FeedForward, RMSNorm, ref["small_modules"]["state_dicts"])
+    for name, w in want.items():
+        assert got[name].shape == w.shape, name
+        if name == "norm_bf16":
+            # "same dtype as input" says the reference's docstring; its code rebinds x to the fp32 copy before casting
+            # back, so a bf16 input comes out fp32 (model/norm.py:38-50). Here the output has the input's dtype.
+            assert got[name].dtype == torch.bfloat16 and w.dtype == torch.float32
+        else:
+            assert got[name].dtype == w.dtype, name
+        tol = 1e-6 if got[name].dtype == torch.float32 else 2e-2
+        assert torch.allclose(got[name].float(), w.float(), atol=tol, rtol=tol), name
