@@ -23,6 +23,7 @@ MODEL_CASES = {
     "dense_tied": (dict(tie_word_embeddings=True), dict(qk_norm=False), None),
     "dense_mha_head_dim": ({}, dict(qk_norm=False, n_kv_heads=4, head_dim=32), None),
     "dense_dropout": ({}, dict(qk_norm=False, dropout=0.1), None),
+    "dense_embedding_norm": (dict(embedding_norm="RMSNorm"), dict(qk_norm=True), None),
     "moe": ({}, dict(qk_norm=False), {}),
     "moe_capacity_1": ({}, dict(qk_norm=False), dict(capacity_factor=1.0)),
     "moe_capacity_1p25": ({}, dict(qk_norm=False), dict(capacity_factor=1.25)),
@@ -37,6 +38,9 @@ MODEL_CASES = {
 
 def build(transformer_cls, moe_module, case, seed=0):
     tkw, bkw, mkw = MODEL_CASES[case]
+    tkw = dict(tkw)
+    if tkw.get("embedding_norm") == "RMSNorm":       # the norm class that the Transformer's own module uses
+        tkw["embedding_norm"] = getattr(sys.modules[transformer_cls.__module__], "RMSNorm")(BASE["d_model"])
     torch.manual_seed(seed)
     model = transformer_cls(**BASE, **tkw, block=dict(BLOCK, **bkw))
     if mkw is not None:
