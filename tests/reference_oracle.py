@@ -173,6 +173,11 @@ def run_attention(attention_cls, scaling_cls, state_dicts=None):
                           ("masked", dict(causal=False, attn_mask=mask))):
             torch.manual_seed(7)             # the dropout mask of the case that has one
             calls[call] = a(x, **kw2).detach()
+        # decode step: four new positions behind a cache of eight (keys already rotated, as a cache holds them)
+        n_kv = kw.get("n_kv_heads", 2) or 4
+        kc, vc = torch.randn(2, 8, n_kv, 16, generator=g), torch.randn(2, 8, n_kv, 16, generator=g)
+        torch.manual_seed(7)
+        calls["cached"] = a(x[:, :4], causal=False, kv_cache=(kc, vc), start_pos=8).detach()
         out[name] = calls
     return out, sds
 
